@@ -1,0 +1,84 @@
+"""Builds the native library ``gonn_b200/_C/libgonn_b200.so`` for sm_100a.
+
+Every ``csrc/*.cu`` file is one translation unit compiled by ``nvcc`` with
+``-gencode arch=compute_100a,code=sm_100a`` and linked into one shared object
+with a C ABI (loaded through ``ctypes`` by :mod:`gonn_b200.lib`).  No GPU is
+needed to build.  Run ``python -m gonn_b200.build`` (add ``-v`` for
+``-Xptxas -v`` resource usage, ``-f`` to force a full rebuild).
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import hashlib
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+OUT_DIR = os.path.join(HERE, "_C")
+OBJ_DIR = os.path.join(OUT_DIR, "obj")
+LIB = os.path.join(OUT_DIR, "libgonn_b200.so")
+
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON = ["-O3", "-std=c++17", "-lineinfo", "--use_fast_math", "-Xcompiler", "-fPIC",
+          "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr", "-I", CSRC]
+
+
+def _sources():
+    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+
+
+def _digest(path: str) -> str:
+    h = hashlib.sha256()
+    for name in sorted(os.listdir(CSRC)):
+        if name.endswith((".cuh", ".h")):
+            with open(os.path.join(CSRC, name), "rb") as f:
+                h.update(f.read())
+    with open(path, "rb") as f:
+        h.update(f.read())
+    h.update(" ".join(ARCH + COMMON).encode())
+    return h.hexdigest()
+
+
+def _compile(name: str, verbose: bool, force: bool):
+    src = os.path.join(CSRC, name)
+    obj = os.path.join(OBJ_DIR, name[:-3] + ".o")
+    stamp = obj + ".sha"
+    dig = _digest(src)
+    if not force and os.path.exists(obj) and os.path.exists(stamp):
+        with open(stamp) as f:
+            if f.read().strip() == dig:
+                return name, False, ""
+    cmd = [NVCC] + ARCH + COMMON + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {name}:\n{r.stdout}\n{r.stderr}")
+    with open(stamp, "w") as f:
+        f.write(dig)
+    return name, True, r.stderr
+
+
+def build(verbose: bool = False, force: bool = False) -> str:
+    """Compiles what changed and links the shared library; returns its path."""
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    srcs = _sources()
+    rebuilt = False
+    with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
+        for name, did, log in ex.map(lambda n: _compile(n, verbose, force), srcs):
+            rebuilt |= did
+            if verbose and log:
+                print(f"--- {name}\n{log}")
+    if rebuilt or not os.path.exists(LIB):
+        objs = [os.path.join(OBJ_DIR, n[:-3] + ".o") for n in srcs]
+        cmd = [NVCC] + ARCH + ["-shared", "-o", LIB] + objs + ["-lcudart", "-lpthread"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return LIB
+
+
+if __name__ == "__main__":
+    path = build(verbose="-v" in sys.argv, force="-f" in sys.argv)
+    print(path)
