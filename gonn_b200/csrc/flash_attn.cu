@@ -1,0 +1,902 @@
+// Flash attention for sm_100a: forward and backward on tcgen05 tensor cores
+// with the score tile, the probability tile and the output accumulator in
+// tensor memory.
+//
+// Math follows the reference's fused kernels (backend/cuda/gonn_cuda.cu:302-450
+// forward with online softmax and L = m + log(l); :333-383 backward identities
+// p = exp(s*scale - L), D = dO.O, dV += p^T dO, dS = p (dO.v - D) scale,
+// dQ += dS k, dK += dS^T q) and the scale 1/sqrt(d) and causal rule k <= q of
+// nn/attention.go:124-147.  The design is new: 128-row tiles, bf16/fp16 operands,
+// fp32 accumulation, no atomics (dQ and dK/dV are produced by two kernels so that
+// every output tile has one owner and a fixed summation order).
+//
+// Forward CTA (192 threads) owns 128 query rows of one (batch, head):
+//   warp 0      TMA loads of Q once and the K / V tiles (2-stage rings)
+//   warp 1      MMA issue: S = Q K^T into one of two TMEM score buffers, then
+//               O += P V with P read from TMEM (written there by the softmax warps)
+//   warps 2-5   softmax: one thread per row; running max / sum in registers;
+//               O is rescaled only when the max moved by more than 2^8
+// Tensors are addressed through 4-D tensor maps (d, s, h, b) with arbitrary
+// strides, so (B,S,H,D) and (B,H,S,D) layouts both work without copies.
+#include "common.cuh"
+
+using namespace gb;
+
+namespace {
+
+constexpr int BQ = 128;   // query rows per tile
+constexpr int BKV = 128;  // key rows per tile
+constexpr int kFwdThreads = 192;
+
+struct AttnArgs {
+  int B, H, Sq, Sk;
+  float scale_log2;  // scale * log2(e)
+  float scale;
+  int causal;
+  int in_bf16;
+  // element strides of O / dO / dQ / dK / dV style tensors: (b, s, h); d is contiguous
+  long long o_sb, o_ss, o_sh;
+  void* O;
+  float* LSE;  // [B, H, Sq]
+  // backward
+  const float* Delta;  // [B, H, Sq]
+  void* dQ; void* dK; void* dV;
+  long long dq_sb, dq_ss, dq_sh;
+  long long dk_sb, dk_ss, dk_sh;
+  long long dv_sb, dv_ss, dv_sh;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t pack16(float a, float b, int bf) {
+  return bf ? pack_bf16(a, b) : pack_f16(a, b);
+}
+
+// Stores `n` fp32 values (n multiple of 8) as 16-bit to a 16-byte aligned row.
+template <int N>
+__device__ __forceinline__ void store_row16(void* dst, const float* v, int bf) {
+#pragma unroll
+  for (int j = 0; j < N; j += 8) {
+    uint4 o;
+    o.x = pack16(v[j], v[j + 1], bf);
+    o.y = pack16(v[j + 2], v[j + 3], bf);
+    o.z = pack16(v[j + 4], v[j + 5], bf);
+    o.w = pack16(v[j + 6], v[j + 7], bf);
+    *reinterpret_cast<uint4*>((uint16_t*)dst + j) = o;
+  }
+}
+
+template <int HD>
+struct FwdCfg {
+  static constexpr int CH = HD / 64;               // 64-column chunks per row
+  static constexpr int TILE_BYTES = CH * BQ * 128;  // one 128-row tile of Q, K or V
+  static constexpr int STAGES = 2;
+  static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * STAGES) + 1024 + 256;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int COL_S0 = 0, COL_S1 = 128, COL_O = 256;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+              const __grid_constant__ CUtensorMap tmV, const AttnArgs args) {
+  using C = FwdCfg<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + C::TILE_BYTES;                // [STAGES]
+  uint8_t* sV = sK + C::STAGES * C::TILE_BYTES;    // [STAGES]
+  uint64_t* bars = (uint64_t*)(sV + C::STAGES * C::TILE_BYTES);
+  uint64_t* q_full = bars;          // 1
+  uint64_t* k_full = bars + 1;      // 2
+  uint64_t* k_empty = bars + 3;     // 2
+  uint64_t* v_full = bars + 5;      // 2
+  uint64_t* v_empty = bars + 7;     // 2
+  uint64_t* s_full = bars + 9;      // 2
+  uint64_t* p_full = bars + 11;     // 2
+  uint64_t* pv_done = bars + 13;    // 2
+  uint32_t* tmem_slot = (uint32_t*)(bars + 15);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_q_tiles = (args.Sq + BQ - 1) / BQ;
+  // heavy (late) query tiles first when causal
+  const int q_tile = args.causal ? (num_q_tiles - 1 - (int)blockIdx.x) : (int)blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = q_tile * BQ;
+  int n_kv = (args.Sk + BKV - 1) / BKV;
+  if (args.causal) n_kv = min(n_kv, q_tile + 1);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; i++) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 128);
+      mbar_init(&pv_done[i], 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, C::TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < C::CH; c++) tma_load_4d(sQ + c * BQ * 128, &tmQ, q_full, c * 64, q0, h, b);
+      for (int j = 0; j < n_kv; j++) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 1)) break;
+        mbar_expect_tx(&k_full[st], C::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < C::CH; c++)
+          tma_load_4d(sK + st * C::TILE_BYTES + c * BKV * 128, &tmK, &k_full[st], c * 64, j * BKV, h, b);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 2)) break;
+        mbar_expect_tx(&v_full[st], C::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < C::CH; c++)
+          tma_load_4d(sV + st * C::TILE_BYTES + c * BKV * 128, &tmV, &v_full[st], c * 64, j * BKV, h, b);
+      }
+    }
+  } else if (warp == 1) {
+    const uint32_t fmt = args.in_bf16 ? 1u : 0u;
+    const uint32_t idesc_s = make_idesc(1u, fmt, false, false, BQ, BKV);
+    const uint32_t idesc_o = make_idesc(1u, fmt, false, true, BQ, HD);
+    bool ok = mbar_wait(q_full, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 3);
+    auto issue_s = [&](int j) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(&k_full[st], ph, abort_flag, args.status, ST_ATTN_TIMEOUT, 4)) return false;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + st * C::TILE_BYTES);
+        const uint32_t d = tmem_base + (st ? C::COL_S1 : C::COL_S0);
+#pragma unroll
+        for (int k = 0; k < HD / 16; k++) {
+          const uint32_t off = (k / 4) * (BQ * 128) + (k % 4) * 32;
+          tc_mma_f16(d, make_smem_desc_sw128(qa + off, 16, 1024),
+                     make_smem_desc_sw128(ka + off, 16, 1024), idesc_s, k != 0);
+        }
+        tc_commit(&k_empty[st]);
+        tc_commit(&s_full[st]);
+      }
+      __syncwarp();
+      return true;
+    };
+    if (ok && n_kv > 0) ok = issue_s(0);
+    for (int j = 0; j < n_kv && ok; j++) {
+      if (j + 1 < n_kv) {
+        ok = issue_s(j + 1);
+        if (!ok) break;
+      }
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      ok = mbar_wait(&p_full[st], ph, abort_flag, args.status, ST_ATTN_TIMEOUT, 5);
+      if (!ok) break;
+      ok = mbar_wait(&v_full[st], ph, abort_flag, args.status, ST_ATTN_TIMEOUT, 6);
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t va = smem_u32(sV + st * C::TILE_BYTES);
+        const uint32_t p_tmem = tmem_base + (st ? C::COL_S1 : C::COL_S0);
+        const uint32_t d = tmem_base + C::COL_O;
+#pragma unroll
+        for (int k = 0; k < BKV / 16; k++) {
+          // V is the MN-major B operand: 64-wide d chunks are BKV*128 B apart,
+          // 8-row groups 1024 B apart, one MMA step covers 16 key rows.
+          tc_mma_f16_ts(d, p_tmem + k * 8, make_smem_desc_sw128(va + k * 16 * 128, BKV * 128, 1024),
+                        idesc_o, (j | k) != 0);
+        }
+        tc_commit(&v_empty[st]);
+        tc_commit(&pv_done[st]);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ---------------- softmax warps ----------------
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // row inside the tile
+    const int qrow = q0 + r;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    float m_used = -INFINITY;  // in log2 units, already scaled
+    float l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; j++) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      ok = mbar_wait(&s_full[st], ph, abort_flag, args.status, ST_ATTN_TIMEOUT, 7);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t s_addr = lane_addr + (st ? C::COL_S1 : C::COL_S0);
+      float s[BKV];
+#pragma unroll
+      for (int c = 0; c < BKV / 32; c++) {
+        uint32_t rr[32];
+        tmem_ld32(s_addr + c * 32, rr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) s[c * 32 + i] = __uint_as_float(rr[i]);
+      }
+      const int kv0 = j * BKV;
+      const bool need_mask = (args.causal && j == q_tile) || (kv0 + BKV > args.Sk);
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < BKV; c++) {
+          const int kv = kv0 + c;
+          if (kv >= args.Sk || (args.causal && kv > qrow)) s[c] = -INFINITY;
+        }
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < BKV; c++) mx = fmaxf(mx, s[c]);
+      float m_new = fmaxf(m_used, mx * args.scale_log2);
+      if (m_new == -INFINITY) m_new = 0.f;
+      // rescale O only when the running max moved by more than 8 (a factor 256)
+      const bool need = (m_new - m_used) > 8.f;
+      float alpha = 1.f;
+      if (need) {
+        alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
+        m_used = m_new;
+        l *= alpha;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, need)) {
+        const int pst = (j - 1) & 1;
+        ok = mbar_wait(&pv_done[pst], ((j - 1) >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 8);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < HD / 32; c++) {
+          uint32_t rr[32];
+          tmem_ld32(lane_addr + C::COL_O + c * 32, rr);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i++) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * alpha);
+          tmem_st32(lane_addr + C::COL_O + c * 32, rr);
+        }
+        tmem_st_wait();
+      }
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < BKV / 32; c++) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+          float p0 = exp2f(s[c * 32 + 2 * i] * args.scale_log2 - m_used);
+          float p1 = exp2f(s[c * 32 + 2 * i + 1] * args.scale_log2 - m_used);
+          sum += p0 + p1;
+          pk[i] = pack16(p0, p1, args.in_bf16);
+        }
+        tmem_st16(s_addr + c * 16, pk);
+      }
+      l += sum;
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&p_full[st]);
+    }
+    if (ok && n_kv > 0) {
+      const int lst = (n_kv - 1) & 1;
+      ok = mbar_wait(&pv_done[lst], ((n_kv - 1) >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 9);
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const bool row_ok = qrow < args.Sq;
+      uint16_t* orow = (uint16_t*)args.O + (long long)b * args.o_sb + (long long)qrow * args.o_ss +
+                       (long long)h * args.o_sh;
+#pragma unroll
+      for (int c = 0; c < HD / 32; c++) {
+        uint32_t rr[32];
+        if (n_kv > 0) {
+          tmem_ld32(lane_addr + C::COL_O + c * 32, rr);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i++) rr[i] = 0;
+        }
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) v[i] = __uint_as_float(rr[i]) * inv;
+        if (row_ok) store_row16<32>(orow + c * 32, v, args.in_bf16);
+      }
+      if (row_ok && args.LSE) {
+        // natural-log LSE of the scaled scores
+        args.LSE[((long long)b * args.H + h) * args.Sq + qrow] =
+            l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// Delta[b,h,q] = sum_d dO[b,q,h,d] * O[b,q,h,d]  (fp32), one warp per row
+template <typename T>
+__global__ void fa_delta_kernel(const T* __restrict__ O, const T* __restrict__ dO,
+                                float* __restrict__ delta, int B, int H, int S, int D,
+                                long long o_sb, long long o_ss, long long o_sh, long long g_sb,
+                                long long g_ss, long long g_sh) {
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long total = (long long)B * H * S;
+  for (long long i = (long long)blockIdx.x * warps + warp; i < total; i += (long long)gridDim.x * warps) {
+    const int q = (int)(i % S);
+    const int h = (int)((i / S) % H);
+    const int b = (int)(i / ((long long)S * H));
+    const T* o = O + b * o_sb + q * o_ss + h * o_sh;
+    const T* g = dO + b * g_sb + q * g_ss + h * g_sh;
+    float s = 0.f;
+    for (int d = lane; d < D; d += 32) s += (float)o[d] * (float)g[d];
+    s = warp_sum(s);
+    if (lane == 0) delta[i] = s;
+  }
+}
+
+
+// ---------------------------------------------------------------------------
+// Backward
+// ---------------------------------------------------------------------------
+constexpr int kBwdThreads = 192;
+
+template <int HD>
+struct BwdCfg {
+  static constexpr int CH = HD / 64;
+  static constexpr int TILE_BYTES = CH * 128 * 128;
+  // resident pair (K,V or Q,dO) + 2-stage ring of the streamed pair
+  static constexpr int SMEM_BYTES = TILE_BYTES * (2 + 2 * 2) + 2 * 2 * 128 * 4 + 1024 + 256;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int COL_S = 0, COL_DP = 128, COL_ACC0 = 256, COL_ACC1 = 384;
+};
+
+__device__ __forceinline__ void named_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// K-major operand descriptor for step k (16 columns) of a [128 x HD] tile
+__device__ __forceinline__ uint64_t kdesc(uint32_t base, int k) {
+  return make_smem_desc_sw128(base + (k / 4) * (128 * 128) + (k % 4) * 32, 16, 1024);
+}
+// MN-major operand descriptor for step k (16 rows) of a [128 rows x HD] tile
+__device__ __forceinline__ uint64_t mndesc(uint32_t base, int k) {
+  return make_smem_desc_sw128(base + k * 16 * 128, 128 * 128, 1024);
+}
+
+// dK / dV: one CTA per key tile; streams the query tiles.  Works in the
+// transposed domain (rows = keys) so that P^T and dS^T are A operands in TMEM.
+template <int HD>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                  const AttnArgs args) {
+  using C = BwdCfg<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + C::TILE_BYTES;
+  uint8_t* sQ = sV + C::TILE_BYTES;        // [2]
+  uint8_t* sdO = sQ + 2 * C::TILE_BYTES;   // [2]
+  float* sLSE = (float*)(sdO + 2 * C::TILE_BYTES);  // [2][128]
+  float* sDelta = sLSE + 2 * 128;                   // [2][128]
+  uint64_t* bars = (uint64_t*)(sDelta + 2 * 128);
+  uint64_t* kv_full = bars;       // 1
+  uint64_t* q_full = bars + 1;    // 2
+  uint64_t* q_empty = bars + 3;   // 2
+  uint64_t* sdp_full = bars + 5;  // 1
+  uint64_t* p_full = bars + 6;    // 1
+  uint64_t* acc_done = bars + 7;  // 1
+  uint32_t* tmem_slot = (uint32_t*)(bars + 8);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int kv0 = kv_tile * BKV;
+  const int num_q_tiles = (args.Sq + BQ - 1) / BQ;
+  const int i_begin = args.causal ? kv_tile : 0;
+  const int n_it = num_q_tiles - i_begin;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; i++) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
+    mbar_init(sdp_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * C::TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < C::CH; c++) {
+        tma_load_4d(sK + c * 128 * 128, &tmK, kv_full, c * 64, kv0, h, b);
+        tma_load_4d(sV + c * 128 * 128, &tmV, kv_full, c * 64, kv0, h, b);
+      }
+      for (int it = 0; it < n_it; it++) {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&q_empty[st], ph ^ 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 11)) break;
+        mbar_expect_tx(&q_full[st], 2 * C::TILE_BYTES);
+        const int q0 = (i_begin + it) * BQ;
+#pragma unroll
+        for (int c = 0; c < C::CH; c++) {
+          tma_load_4d(sQ + st * C::TILE_BYTES + c * 128 * 128, &tmQ, &q_full[st], c * 64, q0, h, b);
+          tma_load_4d(sdO + st * C::TILE_BYTES + c * 128 * 128, &tmdO, &q_full[st], c * 64, q0, h, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    const uint32_t fmt = args.in_bf16 ? 1u : 0u;
+    const uint32_t idesc_s = make_idesc(1u, fmt, false, false, 128, 128);
+    const uint32_t idesc_acc = make_idesc(1u, fmt, false, true, 128, HD);
+    bool ok = mbar_wait(kv_full, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 12);
+    for (int it = 0; it < n_it && ok; it++) {
+      const int st = it & 1;
+      const uint32_t ph = (it >> 1) & 1;
+      ok = mbar_wait(&q_full[st], ph, abort_flag, args.status, ST_ATTN_TIMEOUT, 13);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+      const uint32_t qa = smem_u32(sQ + st * C::TILE_BYTES), ga = smem_u32(sdO + st * C::TILE_BYTES);
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < HD / 16; k++)  // S^T = K Q^T
+          tc_mma_f16(tmem_base + C::COL_S, kdesc(ka, k), kdesc(qa, k), idesc_s, k != 0);
+#pragma unroll
+        for (int k = 0; k < HD / 16; k++)  // dP^T = V dO^T
+          tc_mma_f16(tmem_base + C::COL_DP, kdesc(va, k), kdesc(ga, k), idesc_s, k != 0);
+        tc_commit(sdp_full);
+      }
+      __syncwarp();
+      ok = mbar_wait(p_full, it & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 14);
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < BQ / 16; k++)  // dV += P^T dO
+          tc_mma_f16_ts(tmem_base + C::COL_ACC0, tmem_base + C::COL_S + k * 8, mndesc(ga, k),
+                        idesc_acc, (it | k) != 0);
+#pragma unroll
+        for (int k = 0; k < BQ / 16; k++)  // dK += dS^T Q
+          tc_mma_f16_ts(tmem_base + C::COL_ACC1, tmem_base + C::COL_DP + k * 8, mndesc(qa, k),
+                        idesc_acc, (it | k) != 0);
+        tc_commit(&q_empty[st]);
+        if (it == n_it - 1) tc_commit(acc_done);
+      }
+      __syncwarp();
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // key row inside the tile
+    const int kvrow = kv0 + r;
+    const int t = (warp - 2) * 32 + lane;  // 0..127, loader index for LSE / Delta
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const float* lse_g = args.LSE + ((long long)b * args.H + h) * args.Sq;
+    const float* dl_g = args.Delta + ((long long)b * args.H + h) * args.Sq;
+    bool ok = true;
+    for (int it = 0; it < n_it; it++) {
+      const int q0 = (i_begin + it) * BQ;
+      const int pb = it & 1;
+      {
+        const int q = q0 + t;
+        float lv = INFINITY, dv = 0.f;
+        if (q < args.Sq) {
+          lv = lse_g[q] * 1.4426950408889634f;
+          dv = dl_g[q];
+          if (lv == -INFINITY) lv = INFINITY;
+        }
+        sLSE[pb * 128 + t] = lv;
+        sDelta[pb * 128 + t] = dv;
+      }
+      named_sync_128();
+      ok = mbar_wait(sdp_full, it & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 15);
+      if (!ok) break;
+      tc_fence_after();
+      float p[BQ];
+      const bool diag = args.causal && (i_begin + it) == kv_tile;
+#pragma unroll
+      for (int c = 0; c < BQ / 32; c++) {
+        uint32_t rr[32];
+        tmem_ld32(lane_addr + C::COL_S + c * 32, rr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          const int qc = c * 32 + i;
+          float v = exp2f(__uint_as_float(rr[i]) * args.scale_log2 - sLSE[pb * 128 + qc]);
+          if (kvrow >= args.Sk || (diag && kvrow > q0 + qc)) v = 0.f;
+          p[qc] = v;
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < BQ / 32; c++) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) pk[i] = pack16(p[c * 32 + 2 * i], p[c * 32 + 2 * i + 1], args.in_bf16);
+        tmem_st16(lane_addr + C::COL_S + c * 16, pk);
+      }
+#pragma unroll
+      for (int c = 0; c < BQ / 32; c++) {
+        uint32_t rr[32];
+        tmem_ld32(lane_addr + C::COL_DP + c * 32, rr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          const int qc = c * 32 + i;
+          p[qc] = p[qc] * (__uint_as_float(rr[i]) - sDelta[pb * 128 + qc]) * args.scale;
+        }
+      }
+      // all of dP^T has been read (above) before its columns are overwritten
+#pragma unroll
+      for (int c = 0; c < BQ / 32; c++) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) pk[i] = pack16(p[c * 32 + 2 * i], p[c * 32 + 2 * i + 1], args.in_bf16);
+        tmem_st16(lane_addr + C::COL_DP + c * 16, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    if (ok && n_it > 0) ok = mbar_wait(acc_done, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 16);
+    if (ok) {
+      tc_fence_after();
+      const bool row_ok = kvrow < args.Sk;
+      uint16_t* dvrow = (uint16_t*)args.dV + (long long)b * args.dv_sb + (long long)kvrow * args.dv_ss + (long long)h * args.dv_sh;
+      uint16_t* dkrow = (uint16_t*)args.dK + (long long)b * args.dk_sb + (long long)kvrow * args.dk_ss + (long long)h * args.dk_sh;
+#pragma unroll
+      for (int c = 0; c < HD / 32; c++) {
+        uint32_t rr[32];
+        float v[32];
+        if (n_it > 0) { tmem_ld32(lane_addr + C::COL_ACC0 + c * 32, rr); tmem_ld_wait(); }
+#pragma unroll
+        for (int i = 0; i < 32; i++) v[i] = n_it > 0 ? __uint_as_float(rr[i]) : 0.f;
+        if (row_ok) store_row16<32>(dvrow + c * 32, v, args.in_bf16);
+        if (n_it > 0) { tmem_ld32(lane_addr + C::COL_ACC1 + c * 32, rr); tmem_ld_wait(); }
+#pragma unroll
+        for (int i = 0; i < 32; i++) v[i] = n_it > 0 ? __uint_as_float(rr[i]) : 0.f;
+        if (row_ok) store_row16<32>(dkrow + c * 32, v, args.in_bf16);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, C::TMEM_COLS); }
+}
+
+// dQ: one CTA per query tile; streams the key tiles.
+template <int HD>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                 const AttnArgs args) {
+  using C = BwdCfg<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sdO = sQ + C::TILE_BYTES;
+  uint8_t* sK = sdO + C::TILE_BYTES;      // [2]
+  uint8_t* sV = sK + 2 * C::TILE_BYTES;   // [2]
+  uint64_t* bars = (uint64_t*)(sV + 2 * C::TILE_BYTES + 2 * 2 * 128 * 4);
+  uint64_t* q_full = bars;        // 1
+  uint64_t* kv_full = bars + 1;   // 2
+  uint64_t* kv_empty = bars + 3;  // 2
+  uint64_t* sdp_full = bars + 5;  // 1
+  uint64_t* p_full = bars + 6;    // 1
+  uint64_t* acc_done = bars + 7;  // 1
+  uint32_t* tmem_slot = (uint32_t*)(bars + 8);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_q_tiles = (args.Sq + BQ - 1) / BQ;
+  const int q_tile = args.causal ? (num_q_tiles - 1 - (int)blockIdx.x) : (int)blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = q_tile * BQ;
+  int n_kv = (args.Sk + BKV - 1) / BKV;
+  if (args.causal) n_kv = min(n_kv, q_tile + 1);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    mbar_init(sdp_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * C::TILE_BYTES);
+#pragma unroll
+      for (int c = 0; c < C::CH; c++) {
+        tma_load_4d(sQ + c * 128 * 128, &tmQ, q_full, c * 64, q0, h, b);
+        tma_load_4d(sdO + c * 128 * 128, &tmdO, q_full, c * 64, q0, h, b);
+      }
+      for (int j = 0; j < n_kv; j++) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 21)) break;
+        mbar_expect_tx(&kv_full[st], 2 * C::TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < C::CH; c++) {
+          tma_load_4d(sK + st * C::TILE_BYTES + c * 128 * 128, &tmK, &kv_full[st], c * 64, j * BKV, h, b);
+          tma_load_4d(sV + st * C::TILE_BYTES + c * 128 * 128, &tmV, &kv_full[st], c * 64, j * BKV, h, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    const uint32_t fmt = args.in_bf16 ? 1u : 0u;
+    const uint32_t idesc_s = make_idesc(1u, fmt, false, false, 128, 128);
+    const uint32_t idesc_acc = make_idesc(1u, fmt, false, true, 128, HD);
+    bool ok = mbar_wait(q_full, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 22);
+    for (int j = 0; j < n_kv && ok; j++) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      ok = mbar_wait(&kv_full[st], ph, abort_flag, args.status, ST_ATTN_TIMEOUT, 23);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t qa = smem_u32(sQ), ga = smem_u32(sdO);
+      const uint32_t ka = smem_u32(sK + st * C::TILE_BYTES), va = smem_u32(sV + st * C::TILE_BYTES);
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < HD / 16; k++)  // S = Q K^T
+          tc_mma_f16(tmem_base + C::COL_S, kdesc(qa, k), kdesc(ka, k), idesc_s, k != 0);
+#pragma unroll
+        for (int k = 0; k < HD / 16; k++)  // dP = dO V^T
+          tc_mma_f16(tmem_base + C::COL_DP, kdesc(ga, k), kdesc(va, k), idesc_s, k != 0);
+        tc_commit(sdp_full);
+      }
+      __syncwarp();
+      ok = mbar_wait(p_full, j & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 24);
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < BKV / 16; k++)  // dQ += dS K
+          tc_mma_f16_ts(tmem_base + C::COL_ACC0, tmem_base + C::COL_DP + k * 8, mndesc(ka, k),
+                        idesc_acc, (j | k) != 0);
+        tc_commit(&kv_empty[st]);
+        if (j == n_kv - 1) tc_commit(acc_done);
+      }
+      __syncwarp();
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int qrow = q0 + r;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    float lse = INFINITY, delta = 0.f;
+    if (qrow < args.Sq) {
+      lse = args.LSE[((long long)b * args.H + h) * args.Sq + qrow] * 1.4426950408889634f;
+      delta = args.Delta[((long long)b * args.H + h) * args.Sq + qrow];
+      if (lse == -INFINITY) lse = INFINITY;
+    }
+    bool ok = true;
+    for (int j = 0; j < n_kv; j++) {
+      ok = mbar_wait(sdp_full, j & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 25);
+      if (!ok) break;
+      tc_fence_after();
+      const int kv0 = j * BKV;
+      const bool need_mask = (args.causal && j == q_tile) || (kv0 + BKV > args.Sk);
+      float p[BKV];
+#pragma unroll
+      for (int c = 0; c < BKV / 32; c++) {
+        uint32_t rr[32];
+        tmem_ld32(lane_addr + C::COL_S + c * 32, rr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          const int kc = c * 32 + i;
+          float v = exp2f(__uint_as_float(rr[i]) * args.scale_log2 - lse);
+          if (need_mask && (kv0 + kc >= args.Sk || (args.causal && kv0 + kc > qrow))) v = 0.f;
+          p[kc] = v;
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < BKV / 32; c++) {
+        uint32_t rr[32];
+        tmem_ld32(lane_addr + C::COL_DP + c * 32, rr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          const int kc = c * 32 + i;
+          p[kc] = p[kc] * (__uint_as_float(rr[i]) - delta) * args.scale;
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < BKV / 32; c++) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) pk[i] = pack16(p[c * 32 + 2 * i], p[c * 32 + 2 * i + 1], args.in_bf16);
+        tmem_st16(lane_addr + C::COL_DP + c * 16, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    if (ok && n_kv > 0) ok = mbar_wait(acc_done, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 26);
+    if (ok) {
+      tc_fence_after();
+      const bool row_ok = qrow < args.Sq;
+      uint16_t* dqrow = (uint16_t*)args.dQ + (long long)b * args.dq_sb + (long long)qrow * args.dq_ss + (long long)h * args.dq_sh;
+#pragma unroll
+      for (int c = 0; c < HD / 32; c++) {
+        uint32_t rr[32];
+        float v[32];
+        if (n_kv > 0) { tmem_ld32(lane_addr + C::COL_ACC0 + c * 32, rr); tmem_ld_wait(); }
+#pragma unroll
+        for (int i = 0; i < 32; i++) v[i] = n_kv > 0 ? __uint_as_float(rr[i]) : 0.f;
+        if (row_ok) store_row16<32>(dqrow + c * 32, v, args.in_bf16);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, C::TMEM_COLS); }
+}
+
+int make_qkv_map(CUtensorMap* m, const void* p, int in_bf16, int B, int H, int S, int D,
+                 long long sb, long long ss, long long sh, int box_rows) {
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)S, (uint64_t)H, (uint64_t)B};
+  uint64_t strides[3] = {(uint64_t)ss * 2, (uint64_t)sh * 2, (uint64_t)sb * 2};
+  uint32_t box[4] = {64, (uint32_t)box_rows, 1, 1};
+  return gbh::encode_tmap(m, in_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                          4, p, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+template <int HD>
+int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+               const AttnArgs& a, cudaStream_t s) {
+  using C = FwdCfg<HD>;
+  static bool configured = false;
+  if (!configured) {
+    GB_CUDA_OK(cudaFuncSetAttribute(fa_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    C::SMEM_BYTES));
+    configured = true;
+  }
+  dim3 grid((a.Sq + BQ - 1) / BQ, a.H, a.B);
+  fa_fwd_kernel<HD><<<grid, kFwdThreads, C::SMEM_BYTES, s>>>(tq, tk, tv, a);
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}
+
+template <int HD>
+int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+               const CUtensorMap& tg, const AttnArgs& a, cudaStream_t s) {
+  using C = BwdCfg<HD>;
+  static bool configured = false;
+  if (!configured) {
+    GB_CUDA_OK(cudaFuncSetAttribute(fa_bwd_dkv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    GB_CUDA_OK(cudaFuncSetAttribute(fa_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    configured = true;
+  }
+  dim3 gkv((a.Sk + BKV - 1) / BKV, a.H, a.B);
+  fa_bwd_dkv_kernel<HD><<<gkv, kBwdThreads, C::SMEM_BYTES, s>>>(tq, tk, tv, tg, a);
+  GB_CUDA_OK(cudaGetLastError());
+  dim3 gq((a.Sq + BQ - 1) / BQ, a.H, a.B);
+  fa_bwd_dq_kernel<HD><<<gq, kBwdThreads, C::SMEM_BYTES, s>>>(tq, tk, tv, tg, a);
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}
+
+}  // namespace
+
+enum { DT_BF16 = 0, DT_F16 = 1 };
+
+// Forward.  q/k/v/o: 16-bit tensors addressed as [b][s][h][d] through element
+// strides (sb, ss, sh) with d contiguous; head_dim 64 or 128.  lse (fp32,
+// [B,H,Sq], natural log of the scaled scores' softmax denominator) may be null.
+GB_EXPORT int gb_flash_fwd(int dtype, const void* q, const void* k, const void* v, void* o,
+                           float* lse, int B, int H, int Sq, int Sk, int D, long long q_sb,
+                           long long q_ss, long long q_sh, long long k_sb, long long k_ss,
+                           long long k_sh, long long v_sb, long long v_ss, long long v_sh,
+                           long long o_sb, long long o_ss, long long o_sh, float scale, int causal,
+                           void* stream) {
+  if (D != 64 && D != 128) {
+    gbh::set_error("gb_flash_fwd: head_dim must be 64 or 128 (got %d)", D);
+    return gbh::E_BAD_ARG;
+  }
+  if (causal && Sq != Sk) {
+    gbh::set_error("gb_flash_fwd: causal attention needs Sq == Sk");
+    return gbh::E_BAD_ARG;
+  }
+  if ((o_sb | o_ss | o_sh) & 7 || ((uintptr_t)o & 15)) {
+    gbh::set_error("gb_flash_fwd: output strides must be multiples of 8 elements");
+    return gbh::E_BAD_ARG;
+  }
+  AttnArgs a;
+  memset(&a, 0, sizeof(a));
+  a.B = B; a.H = H; a.Sq = Sq; a.Sk = Sk;
+  a.scale = scale; a.scale_log2 = scale * 1.4426950408889634f;
+  a.causal = causal; a.in_bf16 = dtype == DT_BF16;
+  a.O = o; a.LSE = lse; a.o_sb = o_sb; a.o_ss = o_ss; a.o_sh = o_sh;
+  a.status = gbh::status_ptr();
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_qkv_map(&tq, q, a.in_bf16, B, H, Sq, D, q_sb, q_ss, q_sh, BQ))) return rc;
+  if ((rc = make_qkv_map(&tk, k, a.in_bf16, B, H, Sk, D, k_sb, k_ss, k_sh, BKV))) return rc;
+  if ((rc = make_qkv_map(&tv, v, a.in_bf16, B, H, Sk, D, v_sb, v_ss, v_sh, BKV))) return rc;
+  if (D == 128) return launch_fwd<128>(tq, tk, tv, a, (cudaStream_t)stream);
+  return launch_fwd<64>(tq, tk, tv, a, (cudaStream_t)stream);
+}
+
+GB_EXPORT int gb_flash_delta(int dtype, const void* o, const void* dout, float* delta, int B, int H,
+                             int S, int D, long long o_sb, long long o_ss, long long o_sh,
+                             long long g_sb, long long g_ss, long long g_sh, void* stream) {
+  long long total = (long long)B * H * S;
+  int grid = (int)((total + 7) / 8 < 148 * 16 ? (total + 7) / 8 : 148 * 16);
+  if (grid < 1) return gbh::E_OK;
+  if (dtype == DT_BF16)
+    fa_delta_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, B, H, S, D, o_sb, o_ss, o_sh, g_sb, g_ss, g_sh);
+  else
+    fa_delta_kernel<__half><<<grid, 256, 0, (cudaStream_t)stream>>>(
+        (const __half*)o, (const __half*)dout, delta, B, H, S, D, o_sb, o_ss, o_sh, g_sb, g_ss, g_sh);
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}
+
+// Backward.  All tensors are [b][s][h][d] through element strides, d contiguous.
+// lse: the forward's output; delta: from gb_flash_delta.  Writes dq, dk, dv.
+GB_EXPORT int gb_flash_bwd(int dtype, const void* q, const void* k, const void* v, const void* dout,
+                           const float* lse, const float* delta, void* dq, void* dk, void* dv,
+                           int B, int H, int Sq, int Sk, int D, const long long* strides,
+                           float scale, int causal, void* stream) {
+  // strides: 7 triples (sb, ss, sh) for q, k, v, dout, dq, dk, dv
+  if (D != 64 && D != 128) {
+    gbh::set_error("gb_flash_bwd: head_dim must be 64 or 128 (got %d)", D);
+    return gbh::E_BAD_ARG;
+  }
+  if (causal && Sq != Sk) {
+    gbh::set_error("gb_flash_bwd: causal attention needs Sq == Sk");
+    return gbh::E_BAD_ARG;
+  }
+  for (int i = 12; i < 21; i++)
+    if (strides[i] & 7) {
+      gbh::set_error("gb_flash_bwd: gradient strides must be multiples of 8 elements");
+      return gbh::E_BAD_ARG;
+    }
+  AttnArgs a;
+  memset(&a, 0, sizeof(a));
+  a.B = B; a.H = H; a.Sq = Sq; a.Sk = Sk;
+  a.scale = scale; a.scale_log2 = scale * 1.4426950408889634f;
+  a.causal = causal; a.in_bf16 = dtype == DT_BF16;
+  a.LSE = const_cast<float*>(lse); a.Delta = delta;
+  a.dQ = dq; a.dK = dk; a.dV = dv;
+  a.dq_sb = strides[12]; a.dq_ss = strides[13]; a.dq_sh = strides[14];
+  a.dk_sb = strides[15]; a.dk_ss = strides[16]; a.dk_sh = strides[17];
+  a.dv_sb = strides[18]; a.dv_ss = strides[19]; a.dv_sh = strides[20];
+  a.status = gbh::status_ptr();
+  CUtensorMap tq, tk, tv, tg;
+  int rc;
+  if ((rc = make_qkv_map(&tq, q, a.in_bf16, B, H, Sq, D, strides[0], strides[1], strides[2], 128))) return rc;
+  if ((rc = make_qkv_map(&tk, k, a.in_bf16, B, H, Sk, D, strides[3], strides[4], strides[5], 128))) return rc;
+  if ((rc = make_qkv_map(&tv, v, a.in_bf16, B, H, Sk, D, strides[6], strides[7], strides[8], 128))) return rc;
+  if ((rc = make_qkv_map(&tg, dout, a.in_bf16, B, H, Sq, D, strides[9], strides[10], strides[11], 128))) return rc;
+  if (D == 128) return launch_bwd<128>(tq, tk, tv, tg, a, (cudaStream_t)stream);
+  return launch_bwd<64>(tq, tk, tv, tg, a, (cudaStream_t)stream);
+}

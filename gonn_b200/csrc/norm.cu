@@ -1,0 +1,452 @@
+// LayerNorm / RMSNorm over the last dimension: one-pass forward that keeps the
+// row in registers (statistics in fp32, variance from centred values), and a
+// backward that produces dx and per-CTA partial sums of dgamma / dbeta, reduced
+// by a second small kernel in a fixed order (deterministic).
+//
+// The reference composes these norms from ~10 elementwise / reduce tape nodes
+// (nn/norm.go:50-78, 115-148); eps 1e-5 for LayerNorm, 1e-6 for RMSNorm, biased
+// variance, RMSNorm = x / sqrt(mean(x^2) + eps) * w.
+#include "common.cuh"
+
+using namespace gb;
+
+namespace {
+
+template <typename T> struct IO;
+template <> struct IO<__nv_bfloat16> {
+  static constexpr int V = 8;
+  static __device__ __forceinline__ void ld(const __nv_bfloat16* p, float* f) {
+    uint4 u = *reinterpret_cast<const uint4*>(p);
+    float2 a;
+    a = unpack_bf16(u.x); f[0] = a.x; f[1] = a.y;
+    a = unpack_bf16(u.y); f[2] = a.x; f[3] = a.y;
+    a = unpack_bf16(u.z); f[4] = a.x; f[5] = a.y;
+    a = unpack_bf16(u.w); f[6] = a.x; f[7] = a.y;
+  }
+  static __device__ __forceinline__ void st(__nv_bfloat16* p, const float* f) {
+    uint4 u;
+    u.x = pack_bf16(f[0], f[1]); u.y = pack_bf16(f[2], f[3]);
+    u.z = pack_bf16(f[4], f[5]); u.w = pack_bf16(f[6], f[7]);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+template <> struct IO<__half> {
+  static constexpr int V = 8;
+  static __device__ __forceinline__ void ld(const __half* p, float* f) {
+    uint4 u = *reinterpret_cast<const uint4*>(p);
+    float2 a;
+    a = unpack_f16(u.x); f[0] = a.x; f[1] = a.y;
+    a = unpack_f16(u.y); f[2] = a.x; f[3] = a.y;
+    a = unpack_f16(u.z); f[4] = a.x; f[5] = a.y;
+    a = unpack_f16(u.w); f[6] = a.x; f[7] = a.y;
+  }
+  static __device__ __forceinline__ void st(__half* p, const float* f) {
+    uint4 u;
+    u.x = pack_f16(f[0], f[1]); u.y = pack_f16(f[2], f[3]);
+    u.z = pack_f16(f[4], f[5]); u.w = pack_f16(f[6], f[7]);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+template <> struct IO<float> {
+  static constexpr int V = 4;
+  static __device__ __forceinline__ void ld(const float* p, float* f) {
+    float4 u = *reinterpret_cast<const float4*>(p);
+    f[0] = u.x; f[1] = u.y; f[2] = u.z; f[3] = u.w;
+  }
+  static __device__ __forceinline__ void st(float* p, const float* f) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+};
+
+// Reduction over the G threads that share a row (G = 32: a warp; G = 256: the
+// whole CTA, through `red`).
+template <int G>
+__device__ __forceinline__ float group_sum(float v, float* red) {
+  if (G == 32) return warp_sum(v);
+  return block_sum(v, red);
+}
+
+// Forward.  A group of G threads owns one row; thread t of the group holds
+// vectors t, t+G, ... (VPT of them) of the row in registers.
+template <typename T, typename TW, int G, int VPT, bool RMS>
+__global__ void __launch_bounds__(256)
+norm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b,
+                T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                long long rows, int D, float eps) {
+  constexpr int V = IO<T>::V;
+  __shared__ float red[32];
+  const int gpb = 256 / G;
+  const int g = threadIdx.x / G, t = threadIdx.x % G;
+  const int nvec = D / V;
+  for (long long row = (long long)blockIdx.x * gpb + g; row < rows; row += (long long)gridDim.x * gpb) {
+    const T* xr = x + row * D;
+    float v[VPT][V];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int vi = t + i * G;
+      if (vi < nvec) {
+        IO<T>::ld(xr + vi * V, v[i]);
+#pragma unroll
+        for (int j = 0; j < V; j++) s += RMS ? v[i][j] * v[i][j] : v[i][j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; j++) v[i][j] = 0.f;
+      }
+    }
+    s = group_sum<G>(s, red);
+    float mean = 0.f, rstd;
+    if (RMS) {
+      rstd = rsqrtf(s / D + eps);
+    } else {
+      mean = s / D;
+      float q = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; i++) {
+        const int vi = t + i * G;
+        if (vi < nvec) {
+#pragma unroll
+          for (int j = 0; j < V; j++) { float d = v[i][j] - mean; q += d * d; }
+        }
+      }
+      q = group_sum<G>(q, red);
+      rstd = rsqrtf(q / D + eps);
+    }
+    if (t == 0) {
+      if (mean_out) mean_out[row] = mean;
+      rstd_out[row] = rstd;
+    }
+    T* yr = y + row * D;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int vi = t + i * G;
+      if (vi < nvec) {
+        float o[V];
+#pragma unroll
+        for (int j = 0; j < V; j++) {
+          const int c = vi * V + j;
+          float h = (v[i][j] - mean) * rstd;
+          if (w) h *= (float)w[c];
+          if (!RMS && b) h += (float)b[c];
+          o[j] = h;
+        }
+        IO<T>::st(yr + vi * V, o);
+      }
+    }
+  }
+}
+
+// Backward.  dx per row; dgamma / dbeta accumulated per thread over the rows
+// the group visits, then combined across the groups of the CTA in shared
+// memory and written to part[blockIdx.x][2][D].
+template <typename T, typename TW, int G, int VPT, bool RMS>
+__global__ void __launch_bounds__(256)
+norm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TW* __restrict__ w,
+                const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                T* __restrict__ dx, float* __restrict__ part, long long rows, int D) {
+  constexpr int V = IO<T>::V;
+  extern __shared__ float sm[];  // [2][D] when G == 32
+  __shared__ float red[32];
+  const int gpb = 256 / G;
+  const int g = threadIdx.x / G, t = threadIdx.x % G;
+  const int nvec = D / V;
+  float dg[VPT][V], db[VPT][V];
+#pragma unroll
+  for (int i = 0; i < VPT; i++)
+#pragma unroll
+    for (int j = 0; j < V; j++) { dg[i][j] = 0.f; db[i][j] = 0.f; }
+
+  for (long long row = (long long)blockIdx.x * gpb + g; row < rows; row += (long long)gridDim.x * gpb) {
+    const float mean = RMS ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float xh[VPT][V], gy[VPT][V];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int vi = t + i * G;
+      if (vi < nvec) {
+        float a[V], d[V];
+        IO<T>::ld(x + row * D + vi * V, a);
+        IO<T>::ld(dy + row * D + vi * V, d);
+#pragma unroll
+        for (int j = 0; j < V; j++) {
+          const int c = vi * V + j;
+          float h = (a[j] - mean) * rstd;
+          float gw = w ? d[j] * (float)w[c] : d[j];
+          xh[i][j] = h;
+          gy[i][j] = gw;
+          s1 += gw;
+          s2 += gw * h;
+          dg[i][j] += d[j] * h;
+          db[i][j] += d[j];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; j++) { xh[i][j] = 0.f; gy[i][j] = 0.f; }
+      }
+    }
+    if (!RMS) s1 = group_sum<G>(s1, red);
+    s2 = group_sum<G>(s2, red);
+    const float m1 = RMS ? 0.f : s1 / D, m2 = s2 / D;
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int vi = t + i * G;
+      if (vi < nvec) {
+        float o[V];
+#pragma unroll
+        for (int j = 0; j < V; j++) o[j] = rstd * (gy[i][j] - m1 - xh[i][j] * m2);
+        IO<T>::st(dx + row * D + vi * V, o);
+      }
+    }
+  }
+  if (part == nullptr) return;
+  float* out = part + (long long)blockIdx.x * 2 * D;
+  if (G == 32) {
+    // combine the 8 warps of the CTA, one warp at a time
+    for (int i = threadIdx.x; i < 2 * D; i += 256) sm[i] = 0.f;
+    __syncthreads();
+    for (int turn = 0; turn < gpb; turn++) {
+      if (g == turn) {
+#pragma unroll
+        for (int i = 0; i < VPT; i++) {
+          const int vi = t + i * G;
+          if (vi < nvec) {
+#pragma unroll
+            for (int j = 0; j < V; j++) {
+              sm[vi * V + j] += dg[i][j];
+              sm[D + vi * V + j] += db[i][j];
+            }
+          }
+        }
+      }
+      __syncthreads();
+    }
+    for (int i = threadIdx.x; i < 2 * D; i += 256) out[i] = sm[i];
+  } else {
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int vi = t + i * G;
+      if (vi < nvec) {
+#pragma unroll
+        for (int j = 0; j < V; j++) {
+          out[vi * V + j] = dg[i][j];
+          out[D + vi * V + j] = db[i][j];
+        }
+      }
+    }
+  }
+}
+
+// dgamma[c] = sum_p part[p][0][c], dbeta[c] = sum_p part[p][1][c], fixed order.
+template <typename TW>
+__global__ void norm_param_reduce_kernel(const float* __restrict__ part, int P, int D,
+                                         TW* __restrict__ dgamma, TW* __restrict__ dbeta) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= 2 * D) return;
+  float s = 0.f;
+  for (int p = 0; p < P; p++) s += part[(long long)p * 2 * D + c];
+  if (c < D) {
+    if (dgamma) dgamma[c] = (TW)s;
+  } else if (dbeta) {
+    dbeta[c - D] = (TW)s;
+  }
+}
+
+// Scalar fallback for D not a multiple of the vector width: one CTA per row.
+template <typename T, typename TW, bool RMS>
+__global__ void norm_fwd_generic(const T* __restrict__ x, const TW* __restrict__ w,
+                                 const TW* __restrict__ b, T* __restrict__ y, float* mean_out,
+                                 float* rstd_out, int D, float eps) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const T* xr = x + row * D;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) { float v = (float)xr[i]; s += RMS ? v * v : v; }
+  s = block_sum(s, red);
+  float mean = 0.f, rstd;
+  if (RMS) {
+    rstd = rsqrtf(s / D + eps);
+  } else {
+    mean = s / D;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) { float d = (float)xr[i] - mean; q += d * d; }
+    q = block_sum(q, red);
+    rstd = rsqrtf(q / D + eps);
+  }
+  if (threadIdx.x == 0) { if (mean_out) mean_out[row] = mean; rstd_out[row] = rstd; }
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float h = ((float)xr[i] - mean) * rstd;
+    if (w) h *= (float)w[i];
+    if (!RMS && b) h += (float)b[i];
+    y[row * D + i] = (T)h;
+  }
+}
+
+template <typename T, typename TW, bool RMS>
+__global__ void norm_bwd_generic(const T* __restrict__ x, const T* __restrict__ dy,
+                                 const TW* __restrict__ w, const float* mean_in,
+                                 const float* rstd_in, T* __restrict__ dx, int D) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const float mean = RMS ? 0.f : mean_in[row], rstd = rstd_in[row];
+  float s1 = 0.f, s2 = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float h = ((float)x[row * D + i] - mean) * rstd;
+    float gw = (float)dy[row * D + i] * (w ? (float)w[i] : 1.f);
+    s1 += gw; s2 += gw * h;
+  }
+  s1 = block_sum(s1, red);
+  s2 = block_sum(s2, red);
+  const float m1 = RMS ? 0.f : s1 / D, m2 = s2 / D;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float h = ((float)x[row * D + i] - mean) * rstd;
+    float gw = (float)dy[row * D + i] * (w ? (float)w[i] : 1.f);
+    dx[row * D + i] = (T)(rstd * (gw - m1 - h * m2));
+  }
+}
+
+// column sums of dy * xhat and dy for the generic path: thread per column
+template <typename T, typename TW, bool RMS>
+__global__ void norm_param_generic(const T* __restrict__ x, const T* __restrict__ dy,
+                                   const float* mean_in, const float* rstd_in, long long rows, int D,
+                                   TW* dgamma, TW* dbeta) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= D) return;
+  float g = 0.f, b = 0.f;
+  for (long long r = 0; r < rows; r++) {
+    float h = ((float)x[r * D + c] - (RMS ? 0.f : mean_in[r])) * rstd_in[r];
+    float d = (float)dy[r * D + c];
+    g += d * h; b += d;
+  }
+  if (dgamma) dgamma[c] = (TW)g;
+  if (dbeta) dbeta[c] = (TW)b;
+}
+
+int pick_grid(long long rows, int gpb) {
+  long long need = (rows + gpb - 1) / gpb;
+  long long cap = 148 * 4;
+  return (int)(need < cap ? need : cap);
+}
+
+template <typename T, typename TW, bool RMS>
+int norm_fwd_t(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+               long long rows, int D, float eps, cudaStream_t s) {
+  constexpr int V = IO<T>::V;
+  const bool aligned = (D % V == 0) && ((((uintptr_t)x | (uintptr_t)y) & 15) == 0);
+  const int nvec = D / V;
+#define GB_FWD(G, VPT)                                                                           \
+  norm_fwd_kernel<T, TW, G, VPT, RMS><<<pick_grid(rows, 256 / G), 256, 0, s>>>(                  \
+      (const T*)x, (const TW*)w, (const TW*)b, (T*)y, mean, rstd, rows, D, eps)
+  if (aligned && nvec <= 32) GB_FWD(32, 1);
+  else if (aligned && nvec <= 64) GB_FWD(32, 2);
+  else if (aligned && nvec <= 96) GB_FWD(32, 3);
+  else if (aligned && nvec <= 128) GB_FWD(32, 4);
+  else if (aligned && nvec <= 256) GB_FWD(256, 1);
+  else if (aligned && nvec <= 512) GB_FWD(256, 2);
+  else if (aligned && nvec <= 1024) GB_FWD(256, 4);
+  else
+    norm_fwd_generic<T, TW, RMS><<<(unsigned)rows, 256, 0, s>>>((const T*)x, (const TW*)w,
+                                                               (const TW*)b, (T*)y, mean, rstd, D, eps);
+#undef GB_FWD
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}
+
+template <typename T, typename TW, bool RMS>
+int norm_bwd_t(const void* x, const void* dy, const void* w, const float* mean, const float* rstd,
+               void* dx, void* dgamma, void* dbeta, float* part, int part_rows, long long rows,
+               int D, cudaStream_t s) {
+  constexpr int V = IO<T>::V;
+  const bool aligned = (D % V == 0) && ((((uintptr_t)x | (uintptr_t)dy | (uintptr_t)dx) & 15) == 0);
+  const int nvec = D / V;
+  const bool want_param = dgamma != nullptr || dbeta != nullptr;
+  if (!aligned || nvec > 1024) {
+    norm_bwd_generic<T, TW, RMS><<<(unsigned)rows, 256, 0, s>>>((const T*)x, (const T*)dy,
+                                                               (const TW*)w, mean, rstd, (T*)dx, D);
+    if (want_param)
+      norm_param_generic<T, TW, RMS><<<(D + 127) / 128, 128, 0, s>>>(
+          (const T*)x, (const T*)dy, mean, rstd, rows, D, (TW*)dgamma, (TW*)dbeta);
+    GB_CUDA_OK(cudaGetLastError());
+    return gbh::E_OK;
+  }
+  int grid = 0;
+#define GB_BWD(G, VPT)                                                                           \
+  {                                                                                              \
+    grid = pick_grid(rows, 256 / G);                                                             \
+    if (grid > part_rows) grid = part_rows;                                                      \
+    size_t shm = (G == 32) ? 2 * (size_t)D * sizeof(float) : 0;                                  \
+    norm_bwd_kernel<T, TW, G, VPT, RMS><<<grid, 256, shm, s>>>(                                  \
+        (const T*)x, (const T*)dy, (const TW*)w, mean, rstd, (T*)dx, want_param ? part : nullptr, rows, D); \
+  }
+  if (want_param && (part == nullptr || part_rows < 1)) {
+    gbh::set_error("norm backward: scratch for the parameter gradients is missing");
+    return gbh::E_BAD_ARG;
+  }
+  if (!want_param) part_rows = 1 << 30;
+  if (nvec <= 32) GB_BWD(32, 1)
+  else if (nvec <= 64) GB_BWD(32, 2)
+  else if (nvec <= 96) GB_BWD(32, 3)
+  else if (nvec <= 128) GB_BWD(32, 4)
+  else if (nvec <= 256) GB_BWD(256, 1)
+  else if (nvec <= 512) GB_BWD(256, 2)
+  else GB_BWD(256, 4)
+#undef GB_BWD
+  GB_CUDA_OK(cudaGetLastError());
+  if (want_param) {
+    norm_param_reduce_kernel<TW><<<(2 * D + 255) / 256, 256, 0, s>>>(part, grid, D, (TW*)dgamma,
+                                                                    (TW*)dbeta);
+    GB_CUDA_OK(cudaGetLastError());
+  }
+  return gbh::E_OK;
+}
+
+}  // namespace
+
+enum { DT_BF16 = 0, DT_F16 = 1, DT_F32 = 2 };
+
+// Maximum number of partial rows the backward may use; scratch must hold
+// gb_norm_bwd_scratch_rows() * 2 * D floats.
+GB_EXPORT int gb_norm_bwd_scratch_rows() { return 148 * 4; }
+
+// kind: 0 = LayerNorm, 1 = RMSNorm.  dtype of x / y; wdtype of weight / bias
+// (the same as dtype, or fp32).  mean may be null for RMSNorm.
+GB_EXPORT int gb_norm_fwd(int kind, int dtype, int wdtype, const void* x, const void* w,
+                          const void* b, void* y, float* mean, float* rstd, long long rows, int D,
+                          float eps, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (rows <= 0 || D <= 0) return gbh::E_OK;
+#define GB_N(DTI, T, WDI, TW)                                                              \
+  if (dtype == DTI && wdtype == WDI)                                                       \
+    return kind ? norm_fwd_t<T, TW, true>(x, w, b, y, mean, rstd, rows, D, eps, s)         \
+                : norm_fwd_t<T, TW, false>(x, w, b, y, mean, rstd, rows, D, eps, s);
+  GB_N(DT_BF16, __nv_bfloat16, DT_BF16, __nv_bfloat16)
+  GB_N(DT_BF16, __nv_bfloat16, DT_F32, float)
+  GB_N(DT_F16, __half, DT_F16, __half)
+  GB_N(DT_F16, __half, DT_F32, float)
+  GB_N(DT_F32, float, DT_F32, float)
+#undef GB_N
+  gbh::set_error("gb_norm_fwd: unsupported dtype pair %d/%d", dtype, wdtype);
+  return gbh::E_BAD_ARG;
+}
+
+GB_EXPORT int gb_norm_bwd(int kind, int dtype, int wdtype, const void* x, const void* dy,
+                          const void* w, const float* mean, const float* rstd, void* dx,
+                          void* dgamma, void* dbeta, float* scratch, int scratch_rows,
+                          long long rows, int D, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (rows <= 0 || D <= 0) return gbh::E_OK;
+#define GB_N(DTI, T, WDI, TW)                                                                        \
+  if (dtype == DTI && wdtype == WDI)                                                                 \
+    return kind ? norm_bwd_t<T, TW, true>(x, dy, w, mean, rstd, dx, dgamma, dbeta, scratch,          \
+                                          scratch_rows, rows, D, s)                                  \
+                : norm_bwd_t<T, TW, false>(x, dy, w, mean, rstd, dx, dgamma, dbeta, scratch,         \
+                                           scratch_rows, rows, D, s);
+  GB_N(DT_BF16, __nv_bfloat16, DT_BF16, __nv_bfloat16)
+  GB_N(DT_BF16, __nv_bfloat16, DT_F32, float)
+  GB_N(DT_F16, __half, DT_F16, __half)
+  GB_N(DT_F16, __half, DT_F32, float)
+  GB_N(DT_F32, float, DT_F32, float)
+#undef GB_N
+  gbh::set_error("gb_norm_bwd: unsupported dtype pair %d/%d", dtype, wdtype);
+  return gbh::E_BAD_ARG;
+}

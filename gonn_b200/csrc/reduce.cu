@@ -1,0 +1,239 @@
+// Axis reductions over a tensor viewed as (outer, R, inner): sum, mean, max,
+// min (values) and argmax / argmin (first extremum wins, like the reference's
+// ArgMax tie rule, tensor/ops_reduce.go:6-271).  Two layouts:
+//   inner == 1  row reduction, one warp (short rows) or one CTA (long rows) per row
+//   inner  > 1  column reduction, coalesced along inner, R optionally split
+//               across CTAs with a second fixed-order pass (deterministic)
+// The column form with outer == 1 is the bias-gradient reduction of Linear.
+#include "common.cuh"
+
+using namespace gb;
+
+namespace {
+
+enum ROp : int { R_SUM = 0, R_MEAN = 1, R_MAX = 2, R_MIN = 3, R_ARGMAX = 4, R_ARGMIN = 5 };
+
+template <typename T> struct Acc { using CT = float; };
+template <> struct Acc<double> { using CT = double; };
+
+template <typename CT, int OP>
+__device__ __forceinline__ CT r_init() {
+  if (OP == R_MAX || OP == R_ARGMAX) return (CT)-INFINITY;
+  if (OP == R_MIN || OP == R_ARGMIN) return (CT)INFINITY;
+  return CT(0);
+}
+template <typename CT, int OP>
+__device__ __forceinline__ CT r_comb(CT a, CT b) {
+  if (OP == R_MAX) return a > b ? a : b;
+  if (OP == R_MIN) return a < b ? a : b;
+  return a + b;
+}
+
+template <typename CT, int OP>
+__device__ __forceinline__ CT warp_red(CT v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = r_comb<CT, OP>(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// rows: (outer) rows of length R, contiguous.  One CTA per row.
+template <typename T, typename TO, int OP>
+__global__ void row_reduce_kernel(const T* __restrict__ x, TO* __restrict__ y, long long R) {
+  using CT = typename Acc<T>::CT;
+  __shared__ CT red[32];
+  const T* xr = x + (long long)blockIdx.x * R;
+  CT a = r_init<CT, OP>();
+  for (long long i = threadIdx.x; i < R; i += blockDim.x) a = r_comb<CT, OP>(a, (CT)xr[i]);
+  a = warp_red<CT, OP>(a);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  if (lane == 0) red[w] = a;
+  __syncthreads();
+  if (w == 0) {
+    CT b = lane < nw ? red[lane] : r_init<CT, OP>();
+    b = warp_red<CT, OP>(b);
+    if (lane == 0) {
+      if (OP == R_MEAN) b = b / (CT)R;
+      y[blockIdx.x] = (TO)b;
+    }
+  }
+}
+
+// argmax / argmin over rows: first extremum wins
+template <typename T, int OP>
+__global__ void row_arg_kernel(const T* __restrict__ x, long long* __restrict__ y, long long R) {
+  using CT = typename Acc<T>::CT;
+  __shared__ CT rv[32];
+  __shared__ long long ri[32];
+  const T* xr = x + (long long)blockIdx.x * R;
+  CT best = r_init<CT, OP>();
+  long long bi = 0x7fffffffffffffffLL;
+  for (long long i = threadIdx.x; i < R; i += blockDim.x) {
+    CT v = (CT)xr[i];
+    bool better = OP == R_ARGMAX ? v > best : v < best;
+    if (better || (v == best && i < bi)) { best = v; bi = i; }
+  }
+  auto comb = [&](CT ov, long long oi) {
+    bool better = OP == R_ARGMAX ? ov > best : ov < best;
+    if (better || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    CT ov = __shfl_xor_sync(0xffffffffu, best, o);
+    long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    comb(ov, oi);
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  if (lane == 0) { rv[w] = best; ri[w] = bi; }
+  __syncthreads();
+  if (w == 0) {
+    best = lane < nw ? rv[lane] : r_init<CT, OP>();
+    bi = lane < nw ? ri[lane] : 0x7fffffffffffffffLL;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      CT ov = __shfl_xor_sync(0xffffffffu, best, o);
+      long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      comb(ov, oi);
+    }
+    if (lane == 0) y[blockIdx.x] = bi == 0x7fffffffffffffffLL ? 0 : bi;
+  }
+}
+
+// Column reduction: CTA = 32 columns x 8 row lanes; grid (col tiles, splits, outer).
+// With splits > 1 the result goes to part[outer][split][inner] (CT precision).
+template <typename T, typename TO, int OP>
+__global__ void col_reduce_kernel(const T* __restrict__ x, TO* __restrict__ y,
+                                  typename Acc<T>::CT* __restrict__ part, long long R, long long inner,
+                                  int splits, int to_part) {
+  using CT = typename Acc<T>::CT;
+  __shared__ CT sm[8][33];
+  const long long col = (long long)blockIdx.x * 32 + threadIdx.x;
+  const long long o = blockIdx.z;
+  const long long per = (R + splits - 1) / splits;
+  const long long r0 = (long long)blockIdx.y * per, r1 = min(r0 + per, R);
+  CT a = r_init<CT, OP>();
+  if (col < inner) {
+    const T* xp = x + o * R * inner + col;
+    for (long long r = r0 + threadIdx.y; r < r1; r += 8) a = r_comb<CT, OP>(a, (CT)xp[r * inner]);
+  }
+  sm[threadIdx.y][threadIdx.x] = a;
+  __syncthreads();
+  if (threadIdx.y == 0 && col < inner) {
+#pragma unroll
+    for (int k = 1; k < 8; k++) a = r_comb<CT, OP>(a, sm[k][threadIdx.x]);
+    if (to_part) {
+      part[(o * splits + blockIdx.y) * inner + col] = a;
+    } else {
+      if (OP == R_MEAN) a = a / (CT)R;
+      y[o * inner + col] = (TO)a;
+    }
+  }
+}
+
+template <typename CT, typename TO, int OP>
+__global__ void col_finish_kernel(const CT* __restrict__ part, TO* __restrict__ y, long long R,
+                                  long long inner, int splits, long long total, int accumulate) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long o = i / inner, col = i % inner;
+  CT a = r_init<CT, OP>();
+  for (int s = 0; s < splits; s++) a = r_comb<CT, OP>(a, part[(o * splits + s) * inner + col]);
+  if (OP == R_MEAN) a = a / (CT)R;
+  if (accumulate) a += (CT)y[i];
+  y[i] = (TO)a;
+}
+
+template <typename T, int OP>
+__global__ void col_arg_kernel(const T* __restrict__ x, long long* __restrict__ y, long long R,
+                               long long inner, long long total) {
+  using CT = typename Acc<T>::CT;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long o = i / inner, col = i % inner;
+  const T* xp = x + o * R * inner + col;
+  CT best = (CT)xp[0];
+  long long bi = 0;
+  for (long long r = 1; r < R; r++) {
+    CT v = (CT)xp[r * inner];
+    if (OP == R_ARGMAX ? v > best : v < best) { best = v; bi = r; }
+  }
+  y[i] = bi;
+}
+
+template <typename T, typename TO>
+int reduce_t(int op, const void* x, void* y, void* scratch, long long scratch_bytes, long long outer,
+             long long R, long long inner, int accumulate, cudaStream_t s) {
+  using CT = typename Acc<T>::CT;
+  if (outer <= 0 || inner <= 0 || R <= 0) return gbh::E_OK;
+  if (op == R_ARGMAX || op == R_ARGMIN) {
+    if (inner == 1) {
+      int blk = R >= 1024 ? 256 : (R >= 128 ? 128 : 32);
+      if (op == R_ARGMAX) row_arg_kernel<T, R_ARGMAX><<<(unsigned)outer, blk, 0, s>>>((const T*)x, (long long*)y, R);
+      else row_arg_kernel<T, R_ARGMIN><<<(unsigned)outer, blk, 0, s>>>((const T*)x, (long long*)y, R);
+    } else {
+      long long total = outer * inner;
+      if (op == R_ARGMAX) col_arg_kernel<T, R_ARGMAX><<<(unsigned)((total + 127) / 128), 128, 0, s>>>((const T*)x, (long long*)y, R, inner, total);
+      else col_arg_kernel<T, R_ARGMIN><<<(unsigned)((total + 127) / 128), 128, 0, s>>>((const T*)x, (long long*)y, R, inner, total);
+    }
+    GB_CUDA_OK(cudaGetLastError());
+    return gbh::E_OK;
+  }
+#define GB_R(OPID)                                                                                   \
+  case OPID:                                                                                         \
+    if (inner == 1 && !accumulate) {                                                                 \
+      int blk = R >= 4096 ? 512 : (R >= 512 ? 256 : (R >= 64 ? 64 : 32));                            \
+      row_reduce_kernel<T, TO, OPID><<<(unsigned)outer, blk, 0, s>>>((const T*)x, (TO*)y, R);        \
+    } else {                                                                                         \
+      long long tiles = (inner + 31) / 32;                                                           \
+      int splits = 1;                                                                                \
+      if (tiles * outer < 148 * 4 && R >= 256) {                                                     \
+        splits = (int)((148 * 4 + tiles * outer - 1) / (tiles * outer));                             \
+        if (splits > R / 64) splits = (int)(R / 64);                                                 \
+        if (splits < 1) splits = 1;                                                                  \
+        while (splits > 1 && (long long)splits * outer * inner * (long long)sizeof(CT) > scratch_bytes) splits--; \
+      }                                                                                              \
+      const bool two = splits > 1 || accumulate;                                                     \
+      if (two && (long long)splits * outer * inner * (long long)sizeof(CT) > scratch_bytes) {        \
+        gbh::set_error("reduce: accumulate needs %lld bytes of scratch", (long long)splits * outer * inner * (long long)sizeof(CT)); \
+        return gbh::E_BAD_ARG;                                                                       \
+      }                                                                                              \
+      dim3 grid((unsigned)tiles, splits, (unsigned)outer), blk(32, 8);                               \
+      col_reduce_kernel<T, TO, OPID><<<grid, blk, 0, s>>>((const T*)x, (TO*)y, (CT*)scratch, R, inner, splits, two ? 1 : 0); \
+      if (two) {                                                                                     \
+        long long total = outer * inner;                                                             \
+        col_finish_kernel<CT, TO, OPID><<<(unsigned)((total + 255) / 256), 256, 0, s>>>((const CT*)scratch, (TO*)y, R, inner, splits, total, accumulate); \
+      }                                                                                              \
+    }                                                                                                \
+    break;
+  switch (op) {
+    GB_R(R_SUM) GB_R(R_MEAN) GB_R(R_MAX) GB_R(R_MIN)
+    default:
+      gbh::set_error("reduce: unknown op %d", op);
+      return gbh::E_BAD_ARG;
+  }
+#undef GB_R
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}
+
+}  // namespace
+
+enum { DT_BF16 = 0, DT_F16 = 1, DT_F32 = 2, DT_F64 = 3 };
+
+// y[o, i] = reduce_r x[o, r, i].  op: 0 sum, 1 mean, 2 max, 3 min, 4 argmax,
+// 5 argmin (y is int64).  out_dtype: the input dtype, or fp32 for 16-bit inputs.
+// scratch (optional, scratch_bytes long) lets a column reduction split R across
+// CTAs; accumulate adds the result onto y (sum / mean only, needs scratch).
+GB_EXPORT int gb_reduce(int op, int dtype, int out_dtype, const void* x, void* y, void* scratch,
+                        long long scratch_bytes, long long outer, long long R, long long inner,
+                        int accumulate, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (scratch == nullptr) scratch_bytes = 0;
+  if (dtype == DT_BF16 && out_dtype == DT_BF16) return reduce_t<__nv_bfloat16, __nv_bfloat16>(op, x, y, scratch, scratch_bytes, outer, R, inner, accumulate, s);
+  if (dtype == DT_BF16 && out_dtype == DT_F32) return reduce_t<__nv_bfloat16, float>(op, x, y, scratch, scratch_bytes, outer, R, inner, accumulate, s);
+  if (dtype == DT_F16 && out_dtype == DT_F16) return reduce_t<__half, __half>(op, x, y, scratch, scratch_bytes, outer, R, inner, accumulate, s);
+  if (dtype == DT_F16 && out_dtype == DT_F32) return reduce_t<__half, float>(op, x, y, scratch, scratch_bytes, outer, R, inner, accumulate, s);
+  if (dtype == DT_F32 && out_dtype == DT_F32) return reduce_t<float, float>(op, x, y, scratch, scratch_bytes, outer, R, inner, accumulate, s);
+  if (dtype == DT_F64 && out_dtype == DT_F64) return reduce_t<double, double>(op, x, y, scratch, scratch_bytes, outer, R, inner, accumulate, s);
+  gbh::set_error("gb_reduce: unsupported dtype pair %d -> %d", dtype, out_dtype);
+  return gbh::E_BAD_ARG;
+}
