@@ -1,0 +1,493 @@
+// Peer-memory collectives over NVLink / NVSwitch, issued from inside kernels.
+//
+// Every rank owns one "symmetric" allocation of identical layout (a flag area
+// followed by data).  Ranks exchange CUDA IPC handles once and map each other's
+// allocation; after that a kernel reaches any peer with plain loads and stores.
+//
+//   gb_comm_fused_step   reduce-scatter of a gradient bucket in fixed rank
+//                        order -> 1/W scale -> (a) write the mean to every
+//                        rank (all-reduce-mean) or (b) AdamW on the owned 1/W
+//                        shard (fp32 master, m, v) and write the updated 16-bit
+//                        parameters to every rank (ZeRO-1 step): one kernel does
+//                        the collective and the math.
+//   gb_comm_allreduce_small  one-shot sum of a short fp32 vector
+//   gb_comm_broadcast    root's data region -> every rank
+//   gb_comm_barrier      flag barrier
+//
+// The reference's collectives are a TCP star through rank 0 with a
+// deterministic rank-order sum and identical bytes on every rank
+// (distributed/distributed.go:249-416); DDPStep is all-reduce then step
+// (:422-428).  Here each slice of a bucket is reduced by exactly one rank, in
+// rank order, and that rank's result is what every rank receives, so the
+// "identical bytes everywhere, run to run" contract still holds.
+//
+// Synchronisation uses epoch-numbered flags (never reset): CTA b of rank r
+// writes epoch e into slot [b][r] of every peer's flag area and waits until its
+// own slots [b][*] hold e.  Waits are bounded; on expiry the kernel records
+// ST_COMM_TIMEOUT in the status word and returns.
+//
+// A test on one GPU can run all W ranks inside ONE cooperative launch
+// (gridDim.y = W emulated ranks): separate launches that wait on each other are
+// never used on a single device.
+#include <string.h>
+
+#include "common.cuh"
+
+using namespace gb;
+
+namespace {
+
+constexpr int kMaxWorld = 16;
+constexpr int kMaxCtas = 64;
+constexpr size_t kFlagBytes = 1 << 20;  // flag area at the start of each symmetric buffer
+
+struct PeerTable {
+  void* base[kMaxWorld];  // base address of every rank's symmetric buffer, as mapped here
+};
+
+struct Comm {
+  int rank = 0, world = 1;
+  void* local = nullptr;
+  size_t bytes = 0;
+  PeerTable peers;
+  bool opened[kMaxWorld] = {false};
+  unsigned int epoch = 0;
+};
+
+Comm g_comm;
+
+// flag slot: [channel][cta][rank]
+__device__ __forceinline__ unsigned int* flag_slot(void* base, int channel, int cta, int rank) {
+  return (unsigned int*)base + ((channel * kMaxCtas + cta) * kMaxWorld + rank);
+}
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Barrier between CTA `cta` of all ranks.  Thread t < world handles peer t.
+// Returns false when the wait ran out of budget.
+__device__ bool cta_barrier(const PeerTable& pt, int rank, int world, int channel, int cta,
+                            unsigned int epoch, int* status, int* sm_flag) {
+  __syncthreads();  // everything this CTA wrote so far precedes the signal
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(flag_slot(pt.base[threadIdx.x], channel, cta, rank), epoch);
+    const unsigned int* mine = flag_slot(pt.base[rank], channel, cta, threadIdx.x);
+    const uint64_t t0 = globaltimer_ns();
+    unsigned int spins = 0;
+    // epochs increase monotonically: ">=" tolerates a peer that is already one call ahead
+    while ((int)(ld_acquire_sys(mine) - epoch) < 0) {
+      if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) {
+        set_status(status, ST_COMM_TIMEOUT, channel * 1000 + threadIdx.x);
+        *sm_flag = 1;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return *sm_flag == 0;
+}
+
+struct StepArgs {
+  PeerTable pt;
+  int rank, world;
+  int emulate;               // 1: gridDim.y emulated ranks inside one launch (single-GPU tests)
+  long long grad_off;        // byte offset of the bucket's gradients inside the symmetric buffer
+  long long param_off;       // byte offset of the bucket's parameters (mode 1)
+  long long n;               // elements in the bucket (multiple of world * 8)
+  int mode;                  // 0: all-reduce-mean into the gradients; 1: sharded AdamW + all-gather
+  int dtype_bf16;            // 16-bit flavour: 1 bf16, 0 fp16
+  unsigned int epoch;        // barrier epochs epoch (start) and epoch+1 (end)
+  float* master[kMaxWorld];  // per emulated rank (index 0 in real runs): fp32 shard state
+  float* m[kMaxWorld];
+  float* v[kMaxWorld];
+  float lr, wd, b1, b2, eps, bc1, bc2, gscale;
+  int* status;
+};
+
+__device__ __forceinline__ void unpack8(const uint4& u, float* f, int bf) {
+  float2 a;
+  a = bf ? unpack_bf16(u.x) : unpack_f16(u.x); f[0] = a.x; f[1] = a.y;
+  a = bf ? unpack_bf16(u.y) : unpack_f16(u.y); f[2] = a.x; f[3] = a.y;
+  a = bf ? unpack_bf16(u.z) : unpack_f16(u.z); f[4] = a.x; f[5] = a.y;
+  a = bf ? unpack_bf16(u.w) : unpack_f16(u.w); f[6] = a.x; f[7] = a.y;
+}
+__device__ __forceinline__ uint4 pack8(const float* f, int bf) {
+  uint4 u;
+  u.x = bf ? pack_bf16(f[0], f[1]) : pack_f16(f[0], f[1]);
+  u.y = bf ? pack_bf16(f[2], f[3]) : pack_f16(f[2], f[3]);
+  u.z = bf ? pack_bf16(f[4], f[5]) : pack_f16(f[4], f[5]);
+  u.w = bf ? pack_bf16(f[6], f[7]) : pack_f16(f[6], f[7]);
+  return u;
+}
+
+// One kernel = start barrier, reduce-scatter of this rank's slice (+ optimizer),
+// all-gather by remote stores, end barrier.
+__global__ void __launch_bounds__(512)
+fused_step_kernel(const StepArgs a) {
+  __shared__ int sm_flag;
+  const int rank = a.emulate ? (int)blockIdx.y : a.rank;
+  const int W = a.world;
+  const int cta = blockIdx.x, G = gridDim.x;
+  if (threadIdx.x == 0) sm_flag = 0;
+  __syncthreads();
+  if (W > 1 && !cta_barrier(a.pt, rank, W, 0, cta, a.epoch, a.status, &sm_flag)) return;
+
+  const long long L = a.n / W;          // elements in one rank's slice
+  const long long nvec = L / 8;         // 16-byte vectors in the slice
+  const long long per = (nvec + G - 1) / G;
+  const long long v0 = (long long)cta * per;
+  const long long v1 = min(v0 + per, nvec);
+  const long long slice_vec0 = (long long)rank * nvec;  // vector index of the slice start
+  const float inv = a.gscale / (float)W;
+  const int sidx = a.emulate ? rank : 0;
+  float* master = a.master[sidx];
+  float* mm = a.m[sidx];
+  float* vv = a.v[sidx];
+
+  for (long long i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) acc[j] = 0.f;
+    // fixed rank order => the sum does not depend on who computes it or when
+    for (int p = 0; p < W; p++) {
+      const uint4* src = (const uint4*)((const char*)a.pt.base[p] + a.grad_off) + slice_vec0 + i;
+      uint4 u = __ldcg(src);  // L2 only: a peer's data is never served from this SM's L1
+      float f[8];
+      unpack8(u, f, a.dtype_bf16);
+#pragma unroll
+      for (int j = 0; j < 8; j++) acc[j] += f[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) acc[j] *= inv;
+    uint4 out;
+    long long dst_off;
+    if (a.mode == 0) {
+      out = pack8(acc, a.dtype_bf16);
+      dst_off = a.grad_off;
+    } else {
+      float4* mp = (float4*)(master + i * 8);
+      float4* m4 = (float4*)(mm + i * 8);
+      float4* v4 = (float4*)(vv + i * 8);
+      float pw[8], pm[8], pv[8];
+      *(float4*)&pw[0] = mp[0]; *(float4*)&pw[4] = mp[1];
+      *(float4*)&pm[0] = m4[0]; *(float4*)&pm[4] = m4[1];
+      *(float4*)&pv[0] = v4[0]; *(float4*)&pv[4] = v4[1];
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        float g = acc[j];
+        float p = pw[j];
+        p -= a.lr * a.wd * p;  // decoupled decay first, like optim/adamw.go:77-81
+        float m_ = a.b1 * pm[j] + (1.f - a.b1) * g;
+        float v_ = a.b2 * pv[j] + (1.f - a.b2) * g * g;
+        p -= a.lr * (m_ / a.bc1) / (sqrtf(v_ / a.bc2) + a.eps);
+        pw[j] = p; pm[j] = m_; pv[j] = v_;
+      }
+      mp[0] = *(float4*)&pw[0]; mp[1] = *(float4*)&pw[4];
+      m4[0] = *(float4*)&pm[0]; m4[1] = *(float4*)&pm[4];
+      v4[0] = *(float4*)&pv[0]; v4[1] = *(float4*)&pv[4];
+      out = pack8(pw, a.dtype_bf16);
+      dst_off = a.param_off;
+    }
+    for (int p = 0; p < W; p++) {
+      // own copy last-to-first makes no difference; start with the next rank to spread traffic
+      const int q = (rank + 1 + p) % W;
+      uint4* dst = (uint4*)((char*)a.pt.base[q] + dst_off) + slice_vec0 + i;
+      *dst = out;
+    }
+  }
+  if (W > 1) cta_barrier(a.pt, rank, W, 1, cta, a.epoch + 1, a.status, &sm_flag);
+}
+
+struct SmallArgs {
+  PeerTable pt;
+  int rank, world, emulate;
+  long long slot_off;  // byte offset of the exchange area: world slots of n floats
+  int n;
+  unsigned int epoch;
+  float* io[kMaxWorld];  // in/out vector per emulated rank (index 0 in real runs)
+  int* status;
+};
+
+// One-shot all-reduce-sum of a short fp32 vector: every rank stores its vector
+// into slot[rank] of every peer, then sums the slots in rank order.
+__global__ void __launch_bounds__(256)
+allreduce_small_kernel(const SmallArgs a) {
+  __shared__ int sm_flag;
+  const int rank = a.emulate ? (int)blockIdx.y : a.rank;
+  const int W = a.world;
+  if (threadIdx.x == 0) sm_flag = 0;
+  __syncthreads();
+  float* io = a.io[a.emulate ? rank : 0];
+  for (int p = 0; p < W; p++) {
+    float* slot = (float*)((char*)a.pt.base[p] + a.slot_off) + (long long)rank * a.n;
+    for (int i = threadIdx.x; i < a.n; i += blockDim.x) slot[i] = io[i];
+  }
+  if (!cta_barrier(a.pt, rank, W, 2, 0, a.epoch, a.status, &sm_flag)) return;
+  const float* mine = (const float*)((const char*)a.pt.base[rank] + a.slot_off);
+  for (int i = threadIdx.x; i < a.n; i += blockDim.x) {
+    float s = 0.f;
+    for (int p = 0; p < W; p++) s += __ldcg(mine + (long long)p * a.n + i);
+    io[i] = s;
+  }
+  // slots may be reused by the next call only after everyone has read them
+  cta_barrier(a.pt, rank, W, 3, 0, a.epoch + 1, a.status, &sm_flag);
+}
+
+struct BcastArgs {
+  PeerTable pt;
+  int rank, world, emulate, root;
+  long long off, bytes;
+  unsigned int epoch;
+  int* status;
+};
+
+// Root pushes [off, off+bytes) of its symmetric buffer into every peer's.
+__global__ void __launch_bounds__(512)
+broadcast_kernel(const BcastArgs a) {
+  __shared__ int sm_flag;
+  const int rank = a.emulate ? (int)blockIdx.y : a.rank;
+  const int W = a.world;
+  const int cta = blockIdx.x, G = gridDim.x;
+  if (threadIdx.x == 0) sm_flag = 0;
+  __syncthreads();
+  // everyone must have finished with the old contents before root overwrites them
+  if (!cta_barrier(a.pt, rank, W, 4, cta, a.epoch, a.status, &sm_flag)) return;
+  if (rank == a.root) {
+    const long long nvec = a.bytes / 16;
+    const uint4* src = (const uint4*)((const char*)a.pt.base[rank] + a.off);
+    for (long long i = (long long)cta * blockDim.x + threadIdx.x; i < nvec; i += (long long)G * blockDim.x) {
+      uint4 u = src[i];
+      for (int p = 0; p < W; p++)
+        if (p != rank) ((uint4*)((char*)a.pt.base[p] + a.off))[i] = u;
+    }
+  }
+  cta_barrier(a.pt, rank, W, 5, cta, a.epoch + 1, a.status, &sm_flag);
+}
+
+__global__ void barrier_kernel(const PeerTable pt, int rank_arg, int world, int emulate,
+                               unsigned int epoch, int* status) {
+  __shared__ int sm_flag;
+  const int rank = emulate ? (int)blockIdx.y : rank_arg;
+  if (threadIdx.x == 0) sm_flag = 0;
+  __syncthreads();
+  cta_barrier(pt, rank, world, 6, 0, epoch, status, &sm_flag);
+}
+
+// Wait for a flag that nobody sets: used by tests of the time-out path.  budget_ns
+// bounds the wait; the kernel then records ST_COMM_TIMEOUT and returns.
+__global__ void wait_flag_kernel(const unsigned int* flag, unsigned int want, unsigned long long budget_ns,
+                                 int* status) {
+  const uint64_t t0 = globaltimer_ns();
+  while (ld_acquire_sys(flag) != want) {
+    if (globaltimer_ns() - t0 > budget_ns) {
+      set_status(status, ST_COMM_TIMEOUT, 999);
+      return;
+    }
+  }
+}
+
+int launch_maybe_coop(const void* kern, dim3 grid, dim3 block, void** args, int emulate, cudaStream_t s) {
+  if (emulate) {
+    // emulated ranks wait on each other inside one launch: all CTAs must be co-resident
+    GB_CUDA_OK(cudaLaunchCooperativeKernel(kern, grid, block, args, 0, s));
+  } else {
+    GB_CUDA_OK(cudaLaunchKernel(kern, grid, block, args, 0, s));
+  }
+  return gbh::E_OK;
+}
+
+}  // namespace
+
+GB_EXPORT long long gb_comm_flag_bytes() { return (long long)kFlagBytes; }
+GB_EXPORT int gb_comm_max_world() { return kMaxWorld; }
+GB_EXPORT int gb_comm_max_ctas() { return kMaxCtas; }
+
+// Allocates this rank's symmetric buffer (flag area + data_bytes), zeroes the
+// flags and writes the 64-byte IPC handle to handle_out.  Returns the base.
+GB_EXPORT int gb_comm_alloc(long long data_bytes, void** base_out, void* handle_out) {
+  if (g_comm.local != nullptr) {
+    gbh::set_error("gb_comm_alloc: a symmetric buffer already exists; call gb_comm_free first");
+    return gbh::E_BAD_ARG;
+  }
+  size_t bytes = kFlagBytes + (size_t)data_bytes;
+  void* p = nullptr;
+  GB_CUDA_OK(cudaMalloc(&p, bytes));
+  GB_CUDA_OK(cudaMemset(p, 0, kFlagBytes));
+  GB_CUDA_OK(cudaDeviceSynchronize());
+  cudaIpcMemHandle_t h;
+  GB_CUDA_OK(cudaIpcGetMemHandle(&h, p));
+  memcpy(handle_out, &h, sizeof(h));
+  g_comm.local = p;
+  g_comm.bytes = bytes;
+  g_comm.epoch = 0;
+  *base_out = p;
+  return gbh::E_OK;
+}
+
+// Maps every peer's buffer.  handles: world x 64 bytes, in rank order.
+GB_EXPORT int gb_comm_open(int rank, int world, const void* handles) {
+  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) {
+    gbh::set_error("gb_comm_open: bad rank/world %d/%d", rank, world);
+    return gbh::E_BAD_ARG;
+  }
+  g_comm.rank = rank;
+  g_comm.world = world;
+  for (int p = 0; p < world; p++) {
+    if (p == rank) {
+      g_comm.peers.base[p] = g_comm.local;
+      continue;
+    }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, (const char*)handles + 64 * p, sizeof(h));
+    void* q = nullptr;
+    GB_CUDA_OK(cudaIpcOpenMemHandle(&q, h, cudaIpcMemLazyEnablePeerAccess));
+    g_comm.peers.base[p] = q;
+    g_comm.opened[p] = true;
+  }
+  return gbh::E_OK;
+}
+
+// Single-process set-up for tests: `world` emulated ranks whose buffers are the
+// given device pointers (all on the current GPU).
+GB_EXPORT int gb_comm_emulate(int world, void* const* bases) {
+  if (world < 1 || world > kMaxWorld) {
+    gbh::set_error("gb_comm_emulate: bad world %d", world);
+    return gbh::E_BAD_ARG;
+  }
+  g_comm.rank = 0;
+  g_comm.world = world;
+  for (int p = 0; p < world; p++) g_comm.peers.base[p] = bases[p];
+  g_comm.epoch = 0;
+  return gbh::E_OK;
+}
+
+GB_EXPORT int gb_comm_free() {
+  for (int p = 0; p < kMaxWorld; p++) {
+    if (g_comm.opened[p]) {
+      cudaIpcCloseMemHandle(g_comm.peers.base[p]);
+      g_comm.opened[p] = false;
+    }
+    g_comm.peers.base[p] = nullptr;
+  }
+  if (g_comm.local) cudaFree(g_comm.local);
+  g_comm.local = nullptr;
+  g_comm.world = 1;
+  g_comm.rank = 0;
+  return gbh::E_OK;
+}
+
+static unsigned int next_epochs(int count) {
+  unsigned int e = g_comm.epoch + 1;
+  g_comm.epoch += count;
+  return e;
+}
+
+// Fused bucket step (see the top of the file).  Offsets are bytes from the
+// start of the symmetric buffer (flag area included).  n: elements, a multiple
+// of world*8.  mode 0: mean of the gradients written to every rank; mode 1:
+// sharded AdamW (master/m/v: this rank's shard of the bucket, n/world floats
+// each) and all-gather of the 16-bit parameters.  hyper: {lr, wd, b1, b2, eps,
+// bc1, bc2, gscale}.  emulate != 0: master/m/v are arrays of `world` pointers.
+GB_EXPORT int gb_comm_fused_step(int mode, int dtype_bf16, long long grad_off, long long param_off,
+                                 long long n, float* const* master, float* const* m, float* const* v,
+                                 const float* hyper, int ctas, int emulate, void* stream) {
+  const int W = g_comm.world;
+  if (n % ((long long)W * 8) != 0) {
+    gbh::set_error("gb_comm_fused_step: bucket length %lld is not a multiple of world*8", n);
+    return gbh::E_BAD_ARG;
+  }
+  if (ctas < 1) ctas = 1;
+  if (ctas > kMaxCtas) ctas = kMaxCtas;
+  if (emulate && ctas * W > 128) ctas = 128 / W;
+  StepArgs a;
+  memset(&a, 0, sizeof(a));
+  a.pt = g_comm.peers;
+  a.rank = g_comm.rank; a.world = W; a.emulate = emulate;
+  a.grad_off = grad_off; a.param_off = param_off; a.n = n; a.mode = mode; a.dtype_bf16 = dtype_bf16;
+  a.epoch = W > 1 ? next_epochs(2) : 0;
+  const int ns = emulate ? W : 1;
+  for (int i = 0; i < ns; i++) {
+    a.master[i] = master ? master[i] : nullptr;
+    a.m[i] = m ? m[i] : nullptr;
+    a.v[i] = v ? v[i] : nullptr;
+  }
+  a.lr = hyper[0]; a.wd = hyper[1]; a.b1 = hyper[2]; a.b2 = hyper[3]; a.eps = hyper[4];
+  a.bc1 = hyper[5]; a.bc2 = hyper[6]; a.gscale = hyper[7];
+  a.status = gbh::status_ptr();
+  void* args[] = {&a};
+  dim3 grid(ctas, emulate ? W : 1);
+  return launch_maybe_coop((const void*)fused_step_kernel, grid, dim3(512), args, emulate && W > 1,
+                           (cudaStream_t)stream);
+}
+
+// In-place sum over ranks of an fp32 vector of n <= 4096 elements.  slot_off:
+// byte offset of an exchange area of world*n floats inside the symmetric buffer.
+GB_EXPORT int gb_comm_allreduce_small(float* const* io, int n, long long slot_off, int emulate,
+                                      void* stream) {
+  const int W = g_comm.world;
+  if (W == 1) return gbh::E_OK;
+  SmallArgs a;
+  memset(&a, 0, sizeof(a));
+  a.pt = g_comm.peers;
+  a.rank = g_comm.rank; a.world = W; a.emulate = emulate;
+  a.slot_off = slot_off; a.n = n;
+  a.epoch = next_epochs(2);
+  for (int i = 0; i < (emulate ? W : 1); i++) a.io[i] = io[i];
+  a.status = gbh::status_ptr();
+  void* args[] = {&a};
+  return launch_maybe_coop((const void*)allreduce_small_kernel, dim3(1, emulate ? W : 1), dim3(256), args,
+                           emulate, (cudaStream_t)stream);
+}
+
+GB_EXPORT int gb_comm_broadcast(int root, long long off, long long bytes, int ctas, int emulate,
+                                void* stream) {
+  const int W = g_comm.world;
+  if (W == 1) return gbh::E_OK;
+  if (bytes % 16 != 0 || off % 16 != 0) {
+    gbh::set_error("gb_comm_broadcast: offset and size must be multiples of 16 bytes");
+    return gbh::E_BAD_ARG;
+  }
+  if (ctas < 1) ctas = 1;
+  if (ctas > kMaxCtas) ctas = kMaxCtas;
+  if (emulate && ctas * W > 128) ctas = 128 / W;
+  BcastArgs a;
+  memset(&a, 0, sizeof(a));
+  a.pt = g_comm.peers;
+  a.rank = g_comm.rank; a.world = W; a.emulate = emulate; a.root = root;
+  a.off = off; a.bytes = bytes;
+  a.epoch = next_epochs(2);
+  a.status = gbh::status_ptr();
+  void* args[] = {&a};
+  return launch_maybe_coop((const void*)broadcast_kernel, dim3(ctas, emulate ? W : 1), dim3(512), args,
+                           emulate, (cudaStream_t)stream);
+}
+
+GB_EXPORT int gb_comm_barrier(int emulate, void* stream) {
+  const int W = g_comm.world;
+  if (W == 1) return gbh::E_OK;
+  PeerTable pt = g_comm.peers;
+  int rank = g_comm.rank, world = W, emu = emulate;
+  unsigned int epoch = next_epochs(1);
+  int* status = gbh::status_ptr();
+  void* args[] = {&pt, &rank, &world, &emu, &epoch, &status};
+  return launch_maybe_coop((const void*)barrier_kernel, dim3(1, emulate ? W : 1), dim3(32), args, emulate,
+                           (cudaStream_t)stream);
+}
+
+// Launches a single thread that waits (at most budget_ns) for *flag == want.
+// With a flag nobody sets this exercises the time-out path: the kernel returns
+// normally and the status word holds ST_COMM_TIMEOUT.
+GB_EXPORT int gb_comm_wait_flag(const unsigned int* flag, unsigned int want, long long budget_ns,
+                                void* stream) {
+  wait_flag_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(flag, want, (unsigned long long)budget_ns,
+                                                      gbh::status_ptr());
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}

@@ -1,0 +1,299 @@
+"""Data-parallel engine over symmetric peer memory.
+
+``DistributedDataParallel`` re-homes a module's parameters and gradients in two
+flat regions of this rank's symmetric buffer, cuts them into buckets, and hands
+each bucket to ONE kernel as soon as backward has produced its gradients:
+
+* ``optimizer=None``: the kernel leaves the mean gradient on every rank
+  (all-reduce-mean); any optimizer can then step (``DDPStep`` semantics of the
+  reference, distributed/distributed.go:422-428).
+* ``optimizer={"kind": "adamw", ...}``: the kernel reduce-scatters the bucket,
+  runs AdamW on the shard this rank owns (fp32 master, m, v: 1/W of the state per
+  rank, ZeRO-1) and all-gathers the updated 16-bit parameters — gradient
+  collective, scale/cast, optimizer and parameter collective in one launch,
+  overlapped with the rest of backward on a side stream.
+
+The reference reduces one flat vector after the whole backward, through rank 0
+over TCP, without overlap or bucketing (distributed.go:249-293, :84-86).  Kept
+from it: the mean over ranks, a gradient that is missing on a rank counts as
+zeros, and every rank ends a step with bit-identical parameters.
+
+Layers cooperate through *gradient sinks*: an op that computes a parameter
+gradient writes it straight into the bucket (``param._gb_sink``) and reports the
+parameter ready; gradients that arrive through autograd's own accumulation are
+caught by a post-accumulate hook.
+"""
+from __future__ import annotations
+
+import contextlib
+from typing import Dict, List, Optional
+
+import torch
+
+from .nvlink import SymmetricMemory
+
+_SLOT_BYTES = 1 << 20
+
+
+def ordered_parameters(module: torch.nn.Module) -> List[torch.nn.Parameter]:
+    """Trainable parameters in registration order, except that groups a module declares in
+    ``fuse_groups()`` are kept adjacent (e.g. the q/k/v weights of an attention layer)."""
+    fused: Dict[int, List[torch.nn.Parameter]] = {}
+    for m in module.modules():
+        fg = getattr(m, "fuse_groups", None)
+        if fg is None:
+            continue
+        for grp in fg():
+            grp = [p for p in grp if p is not None and p.requires_grad]
+            for p in grp:
+                fused[id(p)] = grp
+    out, seen = [], set()
+    for p in module.parameters():
+        if not p.requires_grad or id(p) in seen:
+            continue
+        for q in fused.get(id(p), [p]):
+            if id(q) not in seen:
+                seen.add(id(q))
+                out.append(q)
+    return out
+
+
+class _Bucket:
+    __slots__ = ("index", "start", "length", "params", "pending", "launched", "master", "m", "v")
+
+    def __init__(self, index, start):
+        self.index, self.start, self.length = index, start, 0
+        self.params: List[torch.nn.Parameter] = []
+        self.pending = 0
+        self.launched = False
+        self.master = self.m = self.v = None
+
+
+class DistributedDataParallel(torch.nn.Module):
+    def __init__(self, module: torch.nn.Module, process_group=None, optimizer: Optional[dict] = None,
+                 bucket_mb: float = 32.0, comm_ctas: int = 32, overlap: bool = True,
+                 rank: Optional[int] = None, world: Optional[int] = None):
+        super().__init__()
+        self.module = module
+        if rank is None or world is None:
+            import torch.distributed as dist
+            if dist.is_available() and dist.is_initialized():
+                rank, world = dist.get_rank(process_group), dist.get_world_size(process_group)
+            else:
+                rank, world = 0, 1
+        self.rank, self.world = rank, world
+        self.overlap, self.comm_ctas = overlap, comm_ctas
+        params = ordered_parameters(module)
+        if not params:
+            raise ValueError("DistributedDataParallel: the module has no trainable parameters")
+        dt = params[0].dtype
+        dev = params[0].device
+        if dt not in (torch.bfloat16, torch.float16):
+            raise TypeError("DistributedDataParallel: parameters must be bf16/fp16; use "
+                            "distributed.Group (TCP) for fp32 / fp64 data parallelism")
+        self.host = dev.type != "cuda"
+        if self.host and world != 1:
+            raise TypeError("DistributedDataParallel: multi-rank runs need CUDA devices")
+        if any(p.dtype != dt or p.device != dev for p in params):
+            raise TypeError("DistributedDataParallel: all parameters must share dtype and device")
+        self.dtype, self.device = dt, dev
+        self.params = params
+
+        # ---- layout -------------------------------------------------------------------
+        align = world * 8
+        limit = max(int(bucket_mb * (1 << 20) / 2), align)
+        self.buckets: List[_Bucket] = []
+        self._where: Dict[int, tuple] = {}
+        off = 0
+        cur = _Bucket(0, 0)
+        for p in params:
+            n = p.numel()
+            # 8-element alignment keeps every parameter 16-byte aligned for TMA / vector access
+            n_pad = (n + 7) // 8 * 8
+            self._where[id(p)] = (cur, off, n)
+            cur.params.append(p)
+            off += n_pad
+            if off - cur.start >= limit:
+                off = cur.start + (off - cur.start + align - 1) // align * align
+                cur.length = off - cur.start
+                self.buckets.append(cur)
+                cur = _Bucket(len(self.buckets), off)
+        if cur.params:
+            off = cur.start + (off - cur.start + align - 1) // align * align
+            cur.length = off - cur.start
+            self.buckets.append(cur)
+        self.total = off
+        nbytes = self.total * 2
+        self._param_off = _SLOT_BYTES
+        self._grad_off = _SLOT_BYTES + (nbytes + 255) // 256 * 256
+        self.symm = SymmetricMemory(self._grad_off + nbytes, rank, world, process_group, device=dev)
+        self.flat_params = self.symm.view(self._param_off, self.total, dt)
+        self.flat_grads = self.symm.view(self._grad_off, self.total, dt)
+
+        # ---- re-home parameters and gradients ---------------------------------------------
+        with torch.no_grad():
+            for p in params:
+                _, o, n = self._where[id(p)]
+                dst = self.flat_params[o:o + n].view(p.shape)
+                dst.copy_(p.data)
+                p.data = dst
+                p.grad = self.flat_grads[o:o + n].view(p.shape)
+                p._gb_sink = self
+                p.register_post_accumulate_grad_hook(self._autograd_hook)
+        if world > 1:
+            # every rank starts from rank 0's values (BroadcastParams of the reference)
+            self.symm.broadcast(0, self._param_off, self.total * 2)
+            torch.cuda.synchronize()
+
+        self._fresh = {id(p): True for p in params}
+        self._autograd_params: Dict[int, torch.nn.Parameter] = {}
+        self._sync = True
+        self._comm_stream = None if self.host else torch.cuda.Stream(device=dev, priority=-1)
+        self.t = 0
+        self.opt = dict(optimizer) if optimizer is not None else None
+        if self.opt is not None:
+            kind = self.opt.get("kind", "adamw").lower()
+            if kind != "adamw":
+                raise ValueError("DistributedDataParallel: the fused sharded optimizer is AdamW")
+            self.lr = float(self.opt.get("lr", 1e-3))
+            self.weight_decay = float(self.opt.get("weight_decay", 0.01))
+            self.betas = tuple(self.opt.get("betas", (0.9, 0.999)))
+            self.eps = float(self.opt.get("eps", 1e-8))
+            for b in self.buckets:
+                L = b.length // world
+                lo = b.start + rank * L
+                b.master = self.flat_params[lo:lo + L].to(torch.float32)
+                b.m = torch.zeros(L, dtype=torch.float32, device=dev)
+                b.v = torch.zeros(L, dtype=torch.float32, device=dev)
+        self._reset_step()
+
+    # ---- sink protocol (called by ops) ------------------------------------------------------
+    def target(self, p):
+        """(flat gradient view of ``p``, whether it has not been written yet this step)."""
+        _, o, n = self._where[id(p)]
+        return self.flat_grads[o:o + n], self._fresh[id(p)]
+
+    def ready(self, p):
+        self._fresh[id(p)] = False
+        self._mark(p)
+
+    def _autograd_hook(self, p):
+        # The hook also fires when the producing op returned no gradient because it had
+        # already written into the bucket through the sink: nothing to do then.
+        if id(p) in self._ready:
+            return
+        # autograd added into p.grad (our flat view); make sure that is still the case
+        _, o, n = self._where[id(p)]
+        view = self.flat_grads[o:o + n].view(p.shape)
+        if p.grad is None or p.grad.data_ptr() != view.data_ptr():
+            if p.grad is not None:
+                if self._fresh[id(p)]:
+                    view.copy_(p.grad)
+                else:
+                    view.add_(p.grad)
+            p.grad = view
+        self._autograd_params[id(p)] = p
+        self._fresh[id(p)] = False
+        self._mark(p)
+
+    def _mark(self, p):
+        b = self._where[id(p)][0]
+        if id(p) in self._ready:
+            # a second contribution in one backward (a shared parameter): it was accumulated
+            # into the bucket, but if the bucket has already been reduced it is too late
+            if b.launched and self._sync and self.overlap:
+                raise RuntimeError("a gradient arrived after its bucket was reduced (a parameter is "
+                                   "used more than once); construct the wrapper with overlap=False")
+            return
+        self._ready.add(id(p))
+        b.pending -= 1
+        if b.pending == 0 and self._sync and self.overlap:
+            self._launch(b)
+
+    # ---- bucket launch ------------------------------------------------------------------------
+    def _hyper(self):
+        if self.opt is None:
+            return [0, 0, 0, 0, 0, 1, 1, 1.0]
+        t = self.t + 1
+        b1, b2 = self.betas
+        return [self.lr, self.weight_decay, b1, b2, self.eps, 1 - b1 ** t, 1 - b2 ** t, 1.0]
+
+    def _launch(self, b: _Bucket):
+        b.launched = True
+        if self.world == 1 and self.opt is None:
+            return  # nothing to reduce and nobody to update
+        args = (1 if self.opt is not None else 0, self.dtype, self._grad_off + b.start * 2,
+                self._param_off + b.start * 2, b.length, b.master, b.m, b.v, self._hyper(), self.comm_ctas)
+        if self.host:
+            self.symm.fused_step(*args)
+            return
+        cur = torch.cuda.current_stream()
+        self._comm_stream.wait_stream(cur)
+        with torch.cuda.stream(self._comm_stream):
+            self.symm.fused_step(*args)
+        self._launched_any = True
+
+    def _reset_step(self):
+        self._ready = set()
+        self._launched_any = False
+        for b in self.buckets:
+            b.pending = len(b.params)
+            b.launched = False
+
+    # ---- user interface -------------------------------------------------------------------------
+    def forward(self, *a, **kw):
+        return self.module(*a, **kw)
+
+    @contextlib.contextmanager
+    def no_sync(self):
+        """Accumulate gradients locally: no collective, no update, until the next
+        backward outside this context."""
+        old = self._sync
+        self._sync = False
+        try:
+            yield
+        finally:
+            self._sync = old
+            # parameters stay "written" so that the next backward accumulates
+            self._ready = set()
+            for b in self.buckets:
+                b.pending = len(b.params)
+
+    def step(self):
+        """Finishes the step: reduces buckets that are still pending, waits for the side
+        stream, and prepares the gradient buffers for the next backward."""
+        for p in self.params:
+            if self._fresh[id(p)]:
+                # no gradient this step on this rank: contributes zeros, like a nil grad
+                # in the reference (distributed.go:253-258)
+                _, o, n = self._where[id(p)]
+                self.flat_grads[o:o + n].zero_()
+        for b in reversed(self.buckets):
+            if not b.launched:
+                self._launch(b)
+        if self._launched_any:
+            torch.cuda.current_stream().wait_stream(self._comm_stream)
+        self.t += 1
+        for k in self._fresh:
+            self._fresh[k] = True
+        # gradients that autograd accumulates in place must start the next step from zero
+        for p in self._autograd_params.values():
+            _, o, n = self._where[id(p)]
+            self.flat_grads[o:o + n].zero_()
+        self._reset_step()
+
+    synchronize = step
+
+    def zero_grad(self):
+        self.flat_grads.zero_()
+        for k in self._fresh:
+            self._fresh[k] = True
+
+    def check(self):
+        self.symm.check()
+
+    def state_bytes_per_rank(self) -> int:
+        return sum(3 * 4 * (b.length // self.world) for b in self.buckets) if self.opt is not None else 0
+
+    def close(self):
+        self.symm.close()

@@ -1,0 +1,164 @@
+"""Symmetric peer memory and the in-kernel collectives built on it.
+
+``SymmetricMemory`` owns this rank's buffer (flag area + data), exchanges CUDA IPC
+handles over an existing ``torch.distributed`` process group (used only as the
+bootstrap channel) and exposes torch views of the local data region.  The
+collectives themselves are the kernels of ``csrc/comm.cu``: they read and write
+the peers' buffers directly over NVLink.
+
+With ``world == 1`` no IPC is involved; with ``emulate=W`` the W "ranks" are W
+buffers on one GPU driven by a single cooperative launch (for tests).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+
+from .. import lib as _l
+
+
+class _Raw:
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 2}
+
+
+class CollectiveTimeout(RuntimeError):
+    """A peer did not reach a collective within the kernel's wait budget."""
+
+
+class SymmetricMemory:
+    """This rank's symmetric buffer.  Offsets handed to kernels count from the buffer's
+    base (the flag area comes first); ``view`` takes offsets into the data region."""
+
+    def __init__(self, data_bytes: int, rank: int = 0, world: int = 1, process_group=None,
+                 emulate: int = 0, device: Optional[torch.device] = None):
+        self.rank, self.world, self.emulate = rank, world, emulate
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        self.device = device
+        self.data_bytes = (int(data_bytes) + 255) // 256 * 256
+        self._raw: List[torch.Tensor] = []
+        self.host = device.type != "cuda"
+        if self.host:
+            # oracle path: one rank, host memory, the collectives evaluated with tensor math
+            if world != 1 or emulate:
+                raise ValueError("SymmetricMemory on the host supports a single rank")
+            self.flag_bytes = 0
+            self._raw.append(torch.zeros(self.data_bytes, dtype=torch.uint8))
+            return
+        L = _l.lib()
+        L.gb_comm_flag_bytes.restype = _l.L
+        self.flag_bytes = int(L.gb_comm_flag_bytes())
+        if emulate:
+            self.world = emulate
+            for _ in range(emulate):
+                t = torch.zeros(self.flag_bytes + self.data_bytes, dtype=torch.uint8, device=self.device)
+                self._raw.append(t)
+            arr = (ctypes.c_void_p * emulate)(*[t.data_ptr() for t in self._raw])
+            _l.call("gb_comm_emulate", _l.I(emulate), arr)
+        elif world == 1:
+            t = torch.zeros(self.flag_bytes + self.data_bytes, dtype=torch.uint8, device=self.device)
+            self._raw.append(t)
+            arr = (ctypes.c_void_p * 1)(t.data_ptr())
+            _l.call("gb_comm_emulate", _l.I(1), arr)
+        else:
+            import torch.distributed as dist
+            base = ctypes.c_void_p()
+            handle = (ctypes.c_ubyte * 64)()
+            _l.call("gb_comm_alloc", _l.L(self.data_bytes), ctypes.byref(base), handle)
+            handles = [None] * world
+            dist.all_gather_object(handles, bytes(handle), group=process_group)
+            blob = b"".join(handles)
+            _l.call("gb_comm_open", _l.I(rank), _l.I(world), ctypes.c_char_p(blob))
+            self._ipc = True
+            self._raw.append(torch.as_tensor(_Raw(base.value, self.flag_bytes + self.data_bytes),
+                                             device=self.device))
+            self._raw[0][self.flag_bytes:].zero_()
+            torch.cuda.synchronize()
+            dist.barrier(group=process_group)
+
+    def view(self, offset_bytes: int, numel: int, dtype: torch.dtype, rank: int = 0) -> torch.Tensor:
+        """A typed view of ``numel`` elements at ``offset_bytes`` of the data region
+        (``rank`` selects the emulated rank's buffer; real runs only see their own)."""
+        esz = torch.empty((), dtype=dtype).element_size()
+        raw = self._raw[rank if self.emulate else 0]
+        lo = self.flag_bytes + offset_bytes
+        return raw[lo:lo + numel * esz].view(dtype)
+
+    def abs_offset(self, offset_bytes: int) -> int:
+        return self.flag_bytes + offset_bytes
+
+    # ---- collectives ------------------------------------------------------------------
+    def fused_step(self, mode: int, dtype: torch.dtype, grad_off: int, param_off: int, n: int,
+                   master, m, v, hyper, ctas: int = 32):
+        """See ``gb_comm_fused_step``.  master/m/v: tensors (lists of tensors when emulating)."""
+        if self.host:
+            return self._fused_step_host(mode, dtype, grad_off, param_off, n, master, m, v, hyper)
+
+        def arr(x):
+            if x is None:
+                return None
+            xs = x if isinstance(x, (list, tuple)) else [x]
+            return (ctypes.c_void_p * len(xs))(*[t.data_ptr() for t in xs])
+        hy = (ctypes.c_float * 8)(*[float(h) for h in hyper])
+        _l.call("gb_comm_fused_step", _l.I(mode), _l.I(1 if dtype == torch.bfloat16 else 0),
+                _l.L(self.abs_offset(grad_off)), _l.L(self.abs_offset(param_off)), _l.L(n),
+                arr(master), arr(m), arr(v), hy, _l.I(ctas), _l.I(1 if self.emulate else 0),
+                _l.stream_ptr())
+
+    def _fused_step_host(self, mode, dtype, grad_off, param_off, n, master, m, v, hyper):
+        """Single-rank restatement of the kernel's arithmetic (fp32, same operation order)."""
+        lr, wd, b1, b2, eps, bc1, bc2, gscale = [float(h) for h in hyper]
+        g = self.view(grad_off, n, dtype).float() * gscale
+        if mode == 0:
+            self.view(grad_off, n, dtype).copy_(g.to(dtype))
+            return
+        p = master
+        p.mul_(1 - lr * wd)
+        m.mul_(b1).add_(g, alpha=1 - b1)
+        v.mul_(b2).addcmul_(g, g, value=1 - b2)
+        p.sub_(lr * (m / bc1) / ((v / bc2).sqrt() + eps))
+        self.view(param_off, n, dtype).copy_(p.to(dtype))
+
+    def allreduce_small(self, vec, slot_off: int):
+        """In-place sum over ranks of a short fp32 vector (list of vectors when emulating)."""
+        if self.host:
+            return
+        xs = vec if isinstance(vec, (list, tuple)) else [vec]
+        n = xs[0].numel()
+        if n * self.world * 4 > (1 << 20):
+            raise ValueError("allreduce_small: vector too long for the exchange area")
+        arr = (ctypes.c_void_p * len(xs))(*[t.data_ptr() for t in xs])
+        _l.call("gb_comm_allreduce_small", arr, _l.I(n), _l.L(self.abs_offset(slot_off)),
+                _l.I(1 if self.emulate else 0), _l.stream_ptr())
+
+    def broadcast(self, root: int, offset_bytes: int, nbytes: int, ctas: int = 16):
+        if self.host:
+            return
+        _l.call("gb_comm_broadcast", _l.I(root), _l.L(self.abs_offset(offset_bytes)), _l.L(nbytes),
+                _l.I(ctas), _l.I(1 if self.emulate else 0), _l.stream_ptr())
+
+    def barrier(self):
+        if self.host:
+            return
+        _l.call("gb_comm_barrier", _l.I(1 if self.emulate else 0), _l.stream_ptr())
+
+    def check(self):
+        """Raises ``CollectiveTimeout`` if a kernel gave up waiting (synchronises)."""
+        if self.host:
+            return
+        code, detail, block, count = _l.read_status()
+        if code == 3:
+            raise CollectiveTimeout(f"collective wait ran out of budget (detail {detail}, block {block})")
+        if code != 0:
+            raise _l.KernelStatusError(f"kernel status {code} (detail {detail}, block {block})")
+
+    def close(self):
+        if getattr(self, "_ipc", False):
+            torch.cuda.synchronize()
+            self._raw.clear()
+            _l.call("gb_comm_free")
+            self._ipc = False

@@ -26,7 +26,15 @@ _DT = {torch.bfloat16: DT_BF16, torch.float16: DT_F16, torch.float32: DT_F32,
 
 _lib = None
 _lock = threading.Lock()
-launch_count = 0  # kernels launched through this binding (read by bench.py)
+launch_count = 0  # native entry points called through this binding
+kernel_count = 0  # kernels those calls launched (read by bench.py)
+
+# kernels launched per entry point when it is not exactly one
+KERNELS_PER_CALL = {
+    "gb_norm_bwd": 2, "gb_ce_fwd": 2, "gb_flash_bwd": 2, "gb_embedding_bwd": 5,
+    "gb_status_read": 0, "gb_comm_alloc": 0, "gb_comm_open": 0, "gb_comm_emulate": 0,
+    "gb_comm_free": 0, "gb_reduce": 1,
+}
 
 
 class NativeError(RuntimeError):
@@ -88,10 +96,11 @@ def check(rc: int, what: str = "native call") -> None:
 
 def call(name: str, *args) -> None:
     """Calls ``name`` with ctypes-converted ``args`` and raises on a non-zero status."""
-    global launch_count
+    global launch_count, kernel_count
     fn = getattr(lib(), name)
     rc = fn(*args)
     launch_count += 1
+    kernel_count += KERNELS_PER_CALL.get(name, 1)
     if rc != 0:
         check(rc, name)
 

@@ -1,0 +1,218 @@
+"""Module system: registration-ordered parameters with dotted names, buffers,
+train/eval flag, containers.
+
+``Module`` is ``torch.nn.Module`` plus the reference's vocabulary
+(nn/module.go:12-209): ``Parameters()`` / ``NamedParameters()`` / ``Buffers()``
+/ ``SetTraining()`` aliases, ``FilterParams`` for building optimizer groups by
+name, ``Sequential`` whose children are named "0", "1", ...  Parameter order is
+the module's own parameters in registration order, then children depth-first —
+the same order torch uses, so state-dict keys match the reference's naming
+contract.
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+from typing import Callable, Dict, Iterable, List, Tuple
+
+import torch
+from torch import nn as _tnn
+
+
+class Module(_tnn.Module):
+    """Base class of every layer."""
+
+    # ---- reference-style accessors -------------------------------------------------
+    def Parameters(self) -> List[torch.nn.Parameter]:
+        return list(self.parameters())
+
+    def NamedParameters(self) -> List[Tuple[str, torch.nn.Parameter]]:
+        return list(self.named_parameters())
+
+    def Buffers(self) -> List[Tuple[str, torch.Tensor]]:
+        return list(self.named_buffers())
+
+    def SetTraining(self, flag: bool) -> "Module":
+        return self.train(flag)
+
+    def Train(self) -> "Module":
+        return self.train(True)
+
+    def Eval(self) -> "Module":
+        return self.train(False)
+
+    @property
+    def Training(self) -> bool:
+        return self.training
+
+    # ---- registration helpers (reference: Base.reg / regBuf / regChild) --------------
+    def reg(self, name: str, tensor: torch.Tensor) -> torch.nn.Parameter:
+        p = tensor if isinstance(tensor, torch.nn.Parameter) else torch.nn.Parameter(tensor)
+        self.register_parameter(name, p)
+        return p
+
+    RegisterParam = reg
+
+    def reg_buf(self, name: str, tensor: torch.Tensor) -> torch.Tensor:
+        self.register_buffer(name, tensor)
+        return tensor
+
+    RegisterBuffer = reg_buf
+
+    def reg_child(self, name: str, child: _tnn.Module) -> _tnn.Module:
+        self.add_module(name, child)
+        return child
+
+    RegisterChild = reg_child
+
+    def num_parameters(self) -> int:
+        return sum(p.numel() for p in self.parameters())
+
+
+def FilterParams(module: _tnn.Module, pred: Callable[[str, torch.nn.Parameter], bool]):
+    """Parameters whose (dotted name, tensor) satisfy ``pred`` (nn/module.go:167-175)."""
+    return [p for n, p in module.named_parameters() if pred(n, p)]
+
+
+filter_params = FilterParams
+
+
+class Sequential(Module):
+    """Runs children in order; children are named "0", "1", ... (nn/module.go:178-209).
+    Children are invoked through ``__call__`` so hooks fire, like the reference's ``Call``."""
+
+    def __init__(self, *layers: _tnn.Module):
+        super().__init__()
+        for l in layers:
+            self.Add(l)
+
+    def Add(self, layer: _tnn.Module) -> "Sequential":
+        self.add_module(str(len(self._modules)), layer)
+        return self
+
+    add = Add
+
+    def __len__(self):
+        return len(self._modules)
+
+    def __getitem__(self, i):
+        if isinstance(i, slice):
+            return Sequential(*list(self._modules.values())[i])
+        return list(self._modules.values())[i]
+
+    def __iter__(self):
+        return iter(self._modules.values())
+
+    def forward(self, x):
+        for m in self._modules.values():
+            x = m(x)
+        return x
+
+
+class ModuleList(_tnn.ModuleList, Module):
+    """Indexable list of children named by position (nn/containers.go:27-80)."""
+
+    def Append(self, m):
+        self.append(m)
+        return self
+
+    def Len(self):
+        return len(self)
+
+
+class ModuleDict(Module):
+    """Children keyed by name, iterated in sorted key order (nn/containers.go:82-140)."""
+
+    def __init__(self, modules: Dict[str, _tnn.Module] = None):
+        super().__init__()
+        for k in sorted(modules or {}):
+            self.add_module(k, modules[k])
+
+    def Set(self, key: str, m: _tnn.Module):
+        self._modules[key] = m
+        self._modules = OrderedDict(sorted(self._modules.items()))
+        return self
+
+    __setitem__ = Set
+
+    def Get(self, key: str):
+        return self._modules[key]
+
+    __getitem__ = Get
+
+    def Keys(self):
+        return list(self._modules.keys())
+
+    keys = Keys
+
+    def __len__(self):
+        return len(self._modules)
+
+    def __contains__(self, k):
+        return k in self._modules
+
+    def items(self):
+        return self._modules.items()
+
+    def values(self):
+        return self._modules.values()
+
+
+class ParameterList(_tnn.ParameterList, Module):
+    """Parameters named "0", "1", ... (nn/containers.go:142-185)."""
+
+    def Append(self, p):
+        self.append(p if isinstance(p, torch.nn.Parameter) else torch.nn.Parameter(p))
+        return self
+
+
+class ParameterDict(Module):
+    """Parameters keyed by name, sorted key order (nn/containers.go:187-229)."""
+
+    def __init__(self, params: Dict[str, torch.Tensor] = None):
+        super().__init__()
+        for k in sorted(params or {}):
+            self.Set(k, params[k])
+
+    def Set(self, key: str, p: torch.Tensor):
+        p = p if isinstance(p, torch.nn.Parameter) else torch.nn.Parameter(p)
+        self._parameters[key] = p
+        self._parameters = OrderedDict(sorted(self._parameters.items()))
+        return self
+
+    __setitem__ = Set
+
+    def Get(self, key: str):
+        return self._parameters[key]
+
+    __getitem__ = Get
+
+    def Keys(self):
+        return list(self._parameters.keys())
+
+    def __len__(self):
+        return len(self._parameters)
+
+
+class Identity(Module):
+    def forward(self, x):
+        return x
+
+
+class Flatten(Module):
+    """Flattens dims [start, end] (default: everything but the batch dim)."""
+
+    def __init__(self, start_dim: int = 1, end_dim: int = -1):
+        super().__init__()
+        self.start_dim, self.end_dim = start_dim, end_dim
+
+    def forward(self, x):
+        return x.flatten(self.start_dim, self.end_dim)
+
+
+class Unflatten(Module):
+    def __init__(self, dim: int, sizes: Iterable[int]):
+        super().__init__()
+        self.dim, self.sizes = dim, tuple(sizes)
+
+    def forward(self, x):
+        return x.unflatten(self.dim, self.sizes)

@@ -124,3 +124,116 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: b
     if _kernel_ok(q, k, v) and not (causal and q.shape[1] != k.shape[1]):
         return _FlashAttn.apply(q, k, v, bool(causal), scale)
     return attention_ref(q, k, v, causal, scale)
+
+
+# ---------------------------------------------------------------------------
+# Fused self-attention core: QKV projection (one GEMM) + flash attention.
+# ---------------------------------------------------------------------------
+def fused_view(parts):
+    """If the tensors in ``parts`` lie back to back in one storage, returns one tensor that
+    spans them (rows concatenated); otherwise None."""
+    first = parts[0]
+    if any(not p.is_contiguous() for p in parts):
+        return None
+    esz = first.element_size()
+    ptr = first.data_ptr()
+    for p in parts:
+        if p.data_ptr() != ptr or p.dtype != first.dtype or p.shape[1:] != first.shape[1:]:
+            return None
+        ptr += p.numel() * esz
+    rows = sum(p.shape[0] for p in parts)
+    shape = (rows,) + tuple(first.shape[1:])
+    strides = first.stride()
+    try:
+        return torch.as_strided(first, shape, strides)
+    except RuntimeError:
+        return None
+
+
+def _emit_fused(params, grad_fn_into, grad_fn_new):
+    """Writes one fused gradient for adjacent parameters, through sinks when present.
+
+    ``grad_fn_into(out, beta)`` computes into a given buffer; ``grad_fn_new()`` returns
+    a new tensor.  Returns the per-parameter gradients for autograd (None when sunk).
+    """
+    sinks = [getattr(p, "_gb_sink", None) for p in params]
+    if all(s is not None for s in sinks):
+        targets = [s.target(p) for s, p in zip(sinks, params)]
+        bufs = [t[0].view(p.shape) for t, p in zip(targets, params)]
+        fresh = [t[1] for t in targets]
+        fused = fused_view(bufs) if len(set(fresh)) == 1 else None
+        if fused is not None:
+            grad_fn_into(fused, not fresh[0])
+            for s, p in zip(sinks, params):
+                s.ready(p)
+            return [None] * len(params)
+    g = grad_fn_new()
+    outs, r0 = [], 0
+    from .linear import emit_grad
+    for p in params:
+        outs.append(emit_grad(p, g[r0:r0 + p.shape[0]]))
+        r0 += p.shape[0]
+    return outs
+
+
+class _SelfAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, wq, wk, wv, bq, bk, bv, wqkv, bqkv, H, causal, scale):
+        from .gemm import gemm
+        B, S, E = x.shape
+        D = E // H
+        x2 = x.reshape(B * S, E)
+        qkv = gemm(x2, wqkv, trans_b=True, bias=bqkv)          # (B*S, 3E)
+        qkv5 = qkv.view(B, S, 3, H, D)
+        out, lse = flash_fwd(qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2], causal, scale)
+        ctx.save_for_backward(x2, wqkv, qkv, out, lse)
+        ctx.params = (wq, wk, wv, bq, bk, bv)
+        ctx.meta = (B, S, E, H, D, causal, scale)
+        return out.view(B, S, E)
+
+    @staticmethod
+    def backward(ctx, dout):
+        from .gemm import gemm
+        from .reduce import column_sum
+        x2, wqkv, qkv, out, lse = ctx.saved_tensors
+        wq, wk, wv, bq, bk, bv = ctx.params
+        B, S, E, H, D, causal, scale = ctx.meta
+        qkv5 = qkv.view(B, S, 3, H, D)
+        dq, dk, dv, dqkv = flash_bwd(qkv5[:, :, 0], qkv5[:, :, 1], qkv5[:, :, 2], out,
+                                     dout.reshape(B, S, H, D), lse, causal, scale)
+        d2 = dqkv.view(B * S, 3 * E)
+        dx = gemm(d2, wqkv).view(B, S, E) if ctx.needs_input_grad[0] else None
+        gw = _emit_fused([wq, wk, wv],
+                         lambda o, beta: gemm(d2, x2, trans_a=True, out=o, beta=beta),
+                         lambda: gemm(d2, x2, trans_a=True))
+        if bq is not None:
+            gb = _emit_fused([bq, bk, bv],
+                             lambda o, beta: column_sum(d2, out=o, accumulate=beta),
+                             lambda: column_sum(d2))
+        else:
+            gb = [None, None, None]
+        return (dx, gw[0], gw[1], gw[2], gb[0], gb[1], gb[2], None, None, None, None, None)
+
+
+def self_attention_qkv(x, wq, wk, wv, bq, bk, bv, num_heads: int, causal: bool, scale=None):
+    """``flash(x Wq^T + bq, x Wk^T + bk, x Wv^T + bv)`` for (B, S, E) input.
+
+    Takes the one-GEMM path when the three weights (and biases) are adjacent in memory,
+    bf16/fp16 on CUDA and head_dim is 64 or 128; returns None when that path does not
+    apply so that the caller can fall back to separate projections.
+    """
+    E = x.shape[-1]
+    D = E // num_heads
+    if not (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and D in (64, 128) and x.dim() == 3):
+        return None
+    wqkv = fused_view([wq, wk, wv])
+    if wqkv is None:
+        return None
+    bqkv = None
+    if bq is not None:
+        bqkv = fused_view([bq, bk, bv])
+        if bqkv is None:
+            return None
+    scale = (1.0 / math.sqrt(D)) if scale is None else float(scale)
+    return _SelfAttention.apply(x, wq, wk, wv, bq, bk, bv, wqkv.detach(), None if bqkv is None else bqkv.detach(),
+                                num_heads, bool(causal), scale)

@@ -51,11 +51,20 @@ class _Embedding(torch.autograd.Function):
     def forward(ctx, weight, idx, padding_idx):
         ctx.save_for_backward(idx)
         ctx.V, ctx.padding_idx = weight.shape[0], padding_idx
+        ctx.param = weight
         return gather_rows(weight, idx)
 
     @staticmethod
     def backward(ctx, dy):
         (idx,) = ctx.saved_tensors
+        sink = getattr(ctx.param, "_gb_sink", None)
+        if sink is not None:
+            # written straight into the data-parallel bucket (overwrite on first use)
+            buf, fresh = sink.target(ctx.param)
+            embedding_backward(dy, idx, ctx.V, ctx.padding_idx, out=buf.view(ctx.param.shape),
+                               accumulate=not fresh)
+            sink.ready(ctx.param)
+            return None, None, None
         return embedding_backward(dy, idx, ctx.V, ctx.padding_idx), None, None
 
 

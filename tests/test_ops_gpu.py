@@ -1,0 +1,219 @@
+"""Memory-bound kernels (elementwise, norms, softmax / cross-entropy, embedding,
+reductions, optimizers, dropout) against fp32 / fp64 torch references on the GPU.
+Pattern: tensor/cuda_dispatch_test.go of the reference (GPU vs host at tight tolerance)."""
+import math
+
+import pytest
+import torch
+
+from gonn_b200.ops import elementwise as ew
+from gonn_b200.ops.embedding import embedding
+from gonn_b200.ops.norm import layer_norm, norm_ref, rms_norm
+from gonn_b200.ops.reduce import reduce_axis
+from gonn_b200.ops.softmax import cross_entropy, cross_entropy_ref, log_softmax, softmax
+
+pytestmark = pytest.mark.gpu
+F = torch.nn.functional
+
+_POS = {"log", "sqrt", "reciprocal", "pow"}
+_PARAMS = {"pow": (2.5, 0), "clip": (-0.5, 0.7), "leakyrelu": (0.1, 0), "elu": (1.3, 0), "hardshrink": (0.4, 0),
+           "softshrink": (0.4, 0), "softplusbeta": (2.0, 10.0), "threshold": (0.2, -1.0), "celu": (1.5, 0),
+           "scale_add": (1.5, -0.25)}
+
+
+@pytest.mark.parametrize("name", sorted(ew.UNARY_IDS))
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32, torch.bfloat16])
+def test_unary_forward_backward(name, dtype, status_ok):
+    n = 10007
+    x = torch.randn(n, device="cuda", dtype=torch.float64) * 2
+    if name in _POS:
+        x = x.abs() + 0.1
+    if name == "tan":
+        x = x.clamp(-1.2, 1.2)
+    x = x.to(dtype)
+    p0, p1 = _PARAMS.get(name, (0.0, 0.0))
+    y = ew.unary_forward(name, x, p0, p1)
+    fwd, bwd = ew._REF[name]
+    xr = x.double()
+    tol = {torch.float64: 1e-9, torch.float32: 2e-4, torch.bfloat16: 3e-2}[dtype]
+    ref = fwd(xr, p0, p1)
+    assert ((y.double() - ref).abs() / (1 + ref.abs())).max().item() < tol
+    dy = torch.randn(n, device="cuda", dtype=torch.float64).to(dtype)
+    dx = ew.unary_backward(name, x, dy, p0, p1)
+    refd = dy.double() * bwd(xr, p0, p1)
+    assert ((dx.double() - refd).abs() / (1 + refd.abs())).max().item() < tol
+
+
+def test_registry_has_25_names():
+    assert len(ew.REGISTERED_UNARY) == 25
+
+
+@pytest.mark.parametrize("name", ["add", "sub", "mul", "div"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float64])
+def test_binary_broadcast_and_grad(name, dtype, status_ok):
+    a = torch.randn(4, 1, 33, device="cuda", dtype=dtype).requires_grad_(True)
+    b = (torch.randn(5, 33, device="cuda", dtype=dtype).abs() + 0.5).requires_grad_(True)
+    y = ew.binary(name, a, b)
+    ref = getattr(torch, name)(a.detach().double(), b.detach().double())
+    tol = {torch.float64: 1e-12, torch.float32: 1e-5, torch.bfloat16: 5e-2}[dtype]
+    assert y.shape == ref.shape
+    assert (y.double() - ref).abs().max().item() < tol * (1 + ref.abs().max().item())
+    g = torch.randn_like(y)
+    y.backward(g)
+    ad, bd = a.detach().double().requires_grad_(True), b.detach().double().requires_grad_(True)
+    getattr(torch, name)(ad, bd).backward(g.double())
+    assert (a.grad.double() - ad.grad).abs().max().item() < 20 * tol * (1 + ad.grad.abs().max().item())
+    assert (b.grad.double() - bd.grad).abs().max().item() < 20 * tol * (1 + bd.grad.abs().max().item())
+
+
+@pytest.mark.parametrize("D", [64, 768, 1000, 2048, 4096, 50])
+@pytest.mark.parametrize("dtype,wdtype", [(torch.bfloat16, torch.bfloat16), (torch.float32, torch.float32),
+                                          (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("rms", [False, True])
+def test_norms(D, dtype, wdtype, rms, status_ok):
+    rows = 300
+    x = torch.randn(rows, D, device="cuda", dtype=dtype).requires_grad_(True)
+    w = (torch.randn(D, device="cuda") * 0.5 + 1).to(wdtype).requires_grad_(True)
+    b = None if rms else torch.randn(D, device="cuda").to(wdtype).requires_grad_(True)
+    y = rms_norm(x, w, 1e-6) if rms else layer_norm(x, w, b, 1e-5)
+    xr, wr = x.detach().double().requires_grad_(True), w.detach().double().requires_grad_(True)
+    br = None if rms else b.detach().double().requires_grad_(True)
+    ref = norm_ref(xr, wr, br, 1e-6 if rms else 1e-5, rms)
+    tol = 3e-2 if dtype == torch.bfloat16 else 1e-4
+    assert (y.double() - ref).abs().max().item() < tol
+    g = torch.randn_like(y)
+    y.backward(g)
+    ref.backward(g.double())
+    assert (x.grad.double() - xr.grad).abs().max().item() < tol * 3
+    wt = 0.5 if wdtype == torch.bfloat16 else (0.15 if dtype == torch.bfloat16 else 1e-3)
+    assert (w.grad.double() - wr.grad).abs().max().item() < wt * (1 + wr.grad.abs().max().item() * 0.05)
+    if not rms:
+        assert (b.grad.double() - br.grad).abs().max().item() < wt * (1 + br.grad.abs().max().item() * 0.05)
+
+
+@pytest.mark.parametrize("D", [10, 1000, 32000, 50304])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_softmax_family(D, dtype, status_ok):
+    x = (torch.randn(37, D, device="cuda") * 3).to(dtype).requires_grad_(True)
+    for fn, tfn in ((softmax, torch.softmax), (log_softmax, torch.log_softmax)):
+        x.grad = None
+        y = fn(x, -1)
+        xr = x.detach().double().requires_grad_(True)
+        ref = tfn(xr, -1)
+        tol = 3e-2 if dtype == torch.bfloat16 else 1e-5
+        assert (y.double() - ref).abs().max().item() < tol * (1 + ref.abs().max().item() * 0.1)
+        g = torch.randn_like(y)
+        y.backward(g)
+        ref.backward(g.double())
+        assert (x.grad.double() - xr.grad).abs().max().item() < tol * (1 + xr.grad.abs().max().item())
+
+
+def test_softmax_other_axis(status_ok):
+    x = torch.randn(4, 7, 9, device="cuda")
+    assert (softmax(x, 1) - torch.softmax(x, 1)).abs().max().item() < 1e-6
+
+
+@pytest.mark.parametrize("C", [10, 1000, 32000])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("opts", [dict(), dict(ignore_index=3), dict(label_smoothing=0.1), dict(weighted=True),
+                                  dict(weighted=True, label_smoothing=0.2, ignore_index=1), dict(reduction="sum"),
+                                  dict(reduction="none")])
+def test_cross_entropy(C, dtype, opts, status_ok):
+    opts = dict(opts)
+    N = 129
+    x = (torch.randn(N, C, device="cuda") * 2).to(dtype).requires_grad_(True)
+    t = torch.randint(0, C, (N,), device="cuda")
+    t[:5] = torch.tensor([3, 1, 3, 1, 0], device="cuda")
+    w = (torch.rand(C, device="cuda") + 0.5) if opts.pop("weighted", False) else None
+    loss = cross_entropy(x, t, weight=w, **opts)
+    xr = x.detach().double().requires_grad_(True)
+    ref = cross_entropy_ref(xr, t, weight=w, **opts)
+    tl = F.cross_entropy(xr.detach(), t, weight=None if w is None else w.double(),
+                         ignore_index=opts.get("ignore_index", -100),
+                         label_smoothing=opts.get("label_smoothing", 0.0),
+                         reduction=opts.get("reduction", "mean"))
+    assert (ref.detach() - tl).abs().max().item() < 1e-9  # the oracle equals torch's semantics
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    assert (loss.double() - ref.detach()).abs().max().item() < tol * (1 + ref.abs().max().item())
+    g = torch.randn_like(loss) if loss.dim() else torch.tensor(1.7, device="cuda")
+    loss.backward(g)
+    ref.backward(g.double())
+    assert (x.grad.double() - xr.grad).abs().max().item() < tol * (0.02 + xr.grad.abs().max().item())
+
+
+def test_cross_entropy_inplace_backward(status_ok):
+    x = torch.randn(64, 500, device="cuda", dtype=torch.bfloat16)
+    t = torch.randint(0, 500, (64,), device="cuda")
+    lin = torch.nn.Parameter(x.clone())
+    logits = lin * 1.0
+    loss = cross_entropy(logits, t, inplace_backward=True)
+    loss.backward()
+    xr = x.double().requires_grad_(True)
+    F.cross_entropy(xr, t).backward()
+    assert (lin.grad.double() - xr.grad).abs().max().item() < 1e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float64])
+def test_embedding(dtype, status_ok):
+    V, D = 1000, 96
+    w = torch.randn(V, D, device="cuda", dtype=dtype).requires_grad_(True)
+    idx = torch.randint(0, V, (7, 61), device="cuda")
+    idx[0, :20] = 5  # a heavily repeated row
+    y = embedding(w, idx, padding_idx=7)
+    assert torch.equal(y, w.detach()[idx])
+    g = torch.randn_like(y)
+    y.backward(g)
+    wr = w.detach().double().requires_grad_(True)
+    F.embedding(idx, wr, padding_idx=7).backward(g.double())
+    tol = {torch.bfloat16: 0.15, torch.float32: 1e-5, torch.float64: 1e-12}[dtype]
+    assert (w.grad.double() - wr.grad).abs().max().item() < tol
+    # deterministic: a second run gives the same bytes
+    w2 = w.detach().clone().requires_grad_(True)
+    embedding(w2, idx, padding_idx=7).backward(g)
+    assert torch.equal(w.grad, w2.grad)
+
+
+@pytest.mark.parametrize("op", ["sum", "mean", "max", "min", "argmax", "argmin"])
+@pytest.mark.parametrize("shape,axis", [((37, 1000), 1), ((5000, 96), 0), ((16384, 768), 0), ((4, 50, 6), 1), ((3, 70000), 1)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float64])
+def test_reduce(op, shape, axis, dtype, status_ok):
+    x = torch.randn(shape, device="cuda", dtype=dtype)
+    y = reduce_axis(x, axis, op)
+    xr = x.double()
+    if op in ("argmax", "argmin"):
+        ref = getattr(torch, op)(xr, dim=axis)
+        assert torch.equal(y, ref)
+        return
+    ref = getattr(torch, op)(xr, dim=axis)
+    ref = ref.values if op in ("max", "min") else ref
+    tol = {torch.float32: 1e-3, torch.bfloat16: 0.6, torch.float64: 1e-9}[dtype]
+    if op in ("max", "min"):
+        tol = 1e-9
+    assert (y.double() - ref).abs().max().item() <= tol * (1 + 0.01 * ref.abs().max().item())
+
+
+def test_bias_grad_fp32_accumulate(status_ok):
+    x = torch.randn(16384, 768, device="cuda", dtype=torch.bfloat16)
+    out = torch.ones(768, device="cuda", dtype=torch.float32)
+    reduce_axis(x, 0, "sum", out=out, accumulate=True)
+    ref = x.double().sum(0) + 1
+    assert (out.double() - ref).abs().max().item() < 1e-2
+
+
+def test_cast(status_ok):
+    x = torch.randn(1001, device="cuda", dtype=torch.float64)
+    for dt in (torch.float32, torch.bfloat16, torch.float16):
+        assert torch.equal(ew.cast(x, dt), x.to(dt))
+    xb = x.to(torch.bfloat16)
+    assert torch.equal(ew.cast(xb, torch.float32), xb.float())
+
+
+def test_dropout_statistics_and_backward(status_ok):
+    from gonn_b200.ops.dropout import dropout
+    x = torch.ones(1 << 20, device="cuda", dtype=torch.float32, requires_grad=True)
+    y = dropout(x, 0.25)
+    keep = (y != 0).float().mean().item()
+    assert abs(keep - 0.75) < 5e-3
+    assert abs(y.max().item() - 1 / 0.75) < 1e-6
+    y.backward(torch.ones_like(y))
+    assert torch.equal(x.grad, y.detach())  # same mask regenerated in backward
