@@ -38,7 +38,7 @@ using namespace gb;
 namespace {
 
 constexpr int kMaxWorld = 16;
-constexpr int kMaxCtas = 64;
+constexpr int kMaxCtas = 304;
 constexpr size_t kFlagBytes = 1 << 20;  // flag area at the start of each symmetric buffer
 
 struct PeerTable {

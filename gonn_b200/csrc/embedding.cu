@@ -93,6 +93,9 @@ __global__ void emb_rank_kernel(const long long* __restrict__ idx, long long n, 
   }
 }
 
+template <typename T> struct EAcc { using CT = float; };
+template <> struct EAcc<double> { using CT = double; };
+
 template <typename T, typename TO>
 __global__ void emb_reduce_kernel(const T* __restrict__ dy, const int* __restrict__ offs,
                                   const int* __restrict__ perm, TO* __restrict__ dw, long long V,
@@ -102,19 +105,20 @@ __global__ void emb_reduce_kernel(const T* __restrict__ dy, const int* __restric
     const int b = offs[v], e = (v == padding_idx) ? b : offs[v + 1];
     TO* out = dw + v * D;
     for (int c0 = lane * 4; c0 < D; c0 += 128) {
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      using CT = typename EAcc<T>::CT;
+      CT a0 = 0, a1 = 0, a2 = 0, a3 = 0;
       for (int j = b; j < e; j++) {
         const T* src = dy + (long long)perm[j] * D + c0;
-        a0 += (float)src[0];
-        if (c0 + 1 < D) a1 += (float)src[1];
-        if (c0 + 2 < D) a2 += (float)src[2];
-        if (c0 + 3 < D) a3 += (float)src[3];
+        a0 += (CT)src[0];
+        if (c0 + 1 < D) a1 += (CT)src[1];
+        if (c0 + 2 < D) a2 += (CT)src[2];
+        if (c0 + 3 < D) a3 += (CT)src[3];
       }
       if (accumulate) {
-        a0 += (float)out[c0];
-        if (c0 + 1 < D) a1 += (float)out[c0 + 1];
-        if (c0 + 2 < D) a2 += (float)out[c0 + 2];
-        if (c0 + 3 < D) a3 += (float)out[c0 + 3];
+        a0 += (CT)out[c0];
+        if (c0 + 1 < D) a1 += (CT)out[c0 + 1];
+        if (c0 + 2 < D) a2 += (CT)out[c0 + 2];
+        if (c0 + 3 < D) a3 += (CT)out[c0 + 3];
       }
       out[c0] = (TO)a0;
       if (c0 + 1 < D) out[c0 + 1] = (TO)a1;

@@ -11,11 +11,11 @@
 // reference's Gemm contract (backend/backend.go:61-78) that its MatMul backward
 // relies on (tensor/ops_matmul.go:36-46).
 //
-// Kernel structure (one persistent CTA per SM, 192 threads):
+// Kernel structure (one persistent CTA per SM, 320 threads):
 //   warp 0     TMA producer: fills a ring of shared-memory stages
 //   warp 1     MMA issuer: one lane issues tcgen05.mma, commits to mbarriers
-//   warps 2-5  epilogue: tcgen05.ld the accumulator, apply bias / activation /
-//              auxiliary tensor, store to global
+//   warps 2-9  epilogue: tcgen05.ld the accumulator, apply bias / activation /
+//              auxiliary tensor, store to global (two warps per TMEM lane quarter)
 // Two accumulator buffers in TMEM let the epilogue of tile i overlap the MMAs
 // of tile i+1.
 #include "common.cuh"
@@ -26,7 +26,7 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int kSwizzleBytes = 128;  // one swizzle atom along the contiguous dim
-constexpr int kThreads = 192;
+constexpr int kMaxThreads = 64 + 32 * 8;
 
 enum Act : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU_TANH = 2, ACT_GELU_ERF = 3 };
 enum AuxMode : int {
@@ -57,6 +57,7 @@ struct GemmArgs {
   int q_per_channel;
   int in_bf16;  // 1 = bf16 inputs, 0 = fp16 inputs (ignored for int8)
   int bcastA, bcastB;  // operand shared by every batch entry (batch stride 0)
+  int group_m;         // row blocks per rasterisation group
   int* status;
 };
 
@@ -69,8 +70,21 @@ struct Cfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ +
+                                    3 * 2 * 256 * 4 /*per-column epilogue constants*/;
 };
+
+// Tile order: groups of `gm` row blocks are swept across all column blocks before the
+// next group starts, so that the CTAs running at the same time share A and B tiles in L2.
+__device__ __forceinline__ void tile_coords(int r, int num_m, int num_n, int gm, int& mb, int& nb) {
+  const int per_group = gm * num_n;
+  const int g = r / per_group;
+  const int first = g * gm;
+  const int rows = min(gm, num_m - first);
+  const int in_g = r - g * per_group;
+  mb = first + in_g % rows;
+  nb = in_g / rows;
+}
 
 template <typename T>
 __device__ __forceinline__ float act_apply(float v, int act) {
@@ -85,11 +99,14 @@ __device__ __forceinline__ float act_apply(float v, int act) {
 __device__ __forceinline__ float2 unpack16(uint32_t u, int in_bf16) {
   return in_bf16 ? unpack_bf16(u) : unpack_f16(u);
 }
+__device__ __forceinline__ uint32_t pack16x(float a, float b, int bf) {
+  return bf ? pack_bf16(a, b) : pack_f16(a, b);
+}
 
 // ESZ: operand element size (2 = bf16/fp16, 1 = int8).  A_MN / B_MN: operand
 // is MN-major.  BN: tile width.
-template <int ESZ, bool A_MN, bool B_MN, int BN>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int ESZ, bool A_MN, bool B_MN, int BN, int EW>
+__global__ void __launch_bounds__(64 + 32 * EW, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const GemmArgs args) {
   using C = Cfg<ESZ, BN>;
@@ -102,6 +119,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint64_t* tempty_bar = tfull_bar + 2;         // [2]
   uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  float* s_bias = (float*)((uint8_t*)bars + 256);  // [2][256]
+  float* s_qsw = s_bias + 512;                     // [2][256]
+  int* s_qrs = (int*)(s_qsw + 512);                // [2][256]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -116,7 +136,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int i = 0; i < 2; i++) {
       mbar_init(&tfull_bar[i], 1);
-      mbar_init(&tempty_bar[i], 4);  // one arrive per epilogue warp
+      mbar_init(&tempty_bar[i], EW);  // one arrive per epilogue warp
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -141,8 +161,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const int b = t / tiles_per_batch;
         const int r = t - b * tiles_per_batch;
-        const int m0 = (r % args.num_m) * BM;
-        const int n0 = (r / args.num_m) * BN;
+        int mb, nb;
+        tile_coords(r, args.num_m, args.num_n, args.group_m, mb, nb);
+        const int m0 = mb * BM, n0 = nb * BN;
         for (int kb = 0; kb < num_kb; kb++) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, args.status, ST_GEMM_TIMEOUT, 1);
           if (!ok) break;
@@ -233,8 +254,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
   } else {
-    // ---------------- epilogue (warps 2..5) ----------------
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    // ---------------- epilogue (warps 2..9) ----------------
+    // Two warps per TMEM lane quarter; each handles half of the tile's columns.
+    // Everything that does not depend on the accumulator (bias, residual / saved
+    // pre-activation) is fetched BEFORE waiting for the MMAs, so those latencies
+    // overlap the main loop of the tile.
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;  // which column part this warp owns
+    const int et = threadIdx.x - 64;  // 0..255 among the epilogue threads
+    constexpr int COLS = BN / (EW / 4);  // columns per thread per tile
+    constexpr int NCH = COLS / 32;
     uint32_t tphase[2] = {0, 0};
     int local_tile = 0;
     const bool vec_ok = ((args.ldc & 7) == 0) && ((args.strideC & 7) == 0) &&
@@ -242,6 +271,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const bool aux_vec_ok = args.aux_mode == AUX_NONE ||
                             (((args.ldaux & 7) == 0) && ((args.strideAux & 7) == 0) &&
                              (((uintptr_t)args.aux & 15) == 0));
+    const bool aux_in = args.aux_mode != AUX_NONE && args.aux_mode != AUX_STORE_PRE;
+    const bool has_cols = args.bias != nullptr || ESZ == 1;
     float q_sx = 1.f;
     int q_zx = 0;
     if (ESZ == 1) {
@@ -253,177 +284,211 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int buf = local_tile & 1;
       const int b = t / tiles_per_batch;
       const int r = t - b * tiles_per_batch;
-      const int m0 = (r % args.num_m) * BM;
-      const int n0 = (r / args.num_m) * BN;
-      ok = mbar_wait(&tfull_bar[buf], tphase[buf], abort_flag, args.status, ST_GEMM_TIMEOUT, 4);
-      if (!ok) break;
-      tphase[buf] ^= 1;
-      tc_fence_after();
+      int mb, nb;
+      tile_coords(r, args.num_m, args.num_n, args.group_m, mb, nb);
+      const int m0 = mb * BM, n0 = nb * BN;
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < args.M;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= args.N) break;  // warp-uniform
-        uint32_t rr[32];
-        tmem_ld32(taddr + c * 32, rr);
-        tmem_ld_wait();
-        float v[32];
-        if (ESZ == 1) {
-#pragma unroll
-          for (int j = 0; j < 32; j++) {
-            const int col = col0 + j;
+      const int cbase = n0 + half * COLS;  // first column of this thread
+      // ---- per-column constants into shared memory (double buffered by tile parity) ----
+      if (has_cols) {
+        for (int e2 = et; e2 < BN; e2 += 32 * EW) {
+          const int et_ = e2;
+          const int col = n0 + et_;
+          float bv = 0.f;
+          if (args.bias && col < args.N) {
+            if (args.bias_f32) bv = __ldg((const float*)args.bias + col);
+            else {
+              uint32_t u = __ldg((const uint16_t*)args.bias + col);
+              bv = args.in_bf16 ? __uint_as_float(u << 16) : __half2float(__ushort_as_half((unsigned short)u));
+            }
+          }
+          s_bias[buf * 256 + et_] = bv;
+          if (ESZ == 1) {
             float sw = 1.f;
             int rs = 0;
             if (col < args.N) {
               sw = args.q_per_channel ? __ldg(args.q_sw + col) : __ldg(args.q_sw);
               rs = args.q_rowsum ? __ldg(args.q_rowsum + col) : 0;
             }
-            v[j] = q_sx * sw * (float)((int)rr[j] - q_zx * rs);
+            s_qsw[buf * 256 + et_] = sw;
+            s_qrs[buf * 256 + et_] = rs;
           }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");
+      }
+      // ---- prefetch the first chunk of the auxiliary input (next chunks: one ahead) ----
+      const bool aux_fast = aux_in && aux_vec_ok && row_ok && (cbase + COLS <= args.N);
+      const uint4* aux_row = reinterpret_cast<const uint4*>(
+          (const uint16_t*)args.aux + (long long)b * args.strideAux + (long long)row * args.ldaux + cbase);
+      uint4 auxn[4];
+      if (aux_fast) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) auxn[j] = __ldg(aux_row + j);
+      }
+      ok = mbar_wait(&tfull_bar[buf], tphase[buf], abort_flag, args.status, ST_GEMM_TIMEOUT, 4);
+      if (!ok) break;
+      tphase[buf] ^= 1;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * COLS;
+      // The chunk loop is deliberately not unrolled: the body is large and eight warps
+      // run it; keeping one copy keeps it resident in the instruction cache.
+#pragma unroll 1
+      for (int c = 0; c < NCH; c++) {
+        uint32_t rr[32];
+        tmem_ld32(taddr + c * 32, rr);
+        uint4 auxc[4];
+        if (aux_fast) {
+#pragma unroll
+          for (int j = 0; j < 4; j++) auxc[j] = auxn[j];
+          if (c + 1 < NCH) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) auxn[j] = __ldg(aux_row + (c + 1) * 4 + j);
+          }
+        }
+        tmem_ld_wait();
+        const int col0 = cbase + c * 32;
+        if (col0 >= args.N || !row_ok) continue;
+        const int sc = buf * 256 + half * COLS + c * 32;  // index into the per-column arrays
+        float v[32];
+        if (ESZ == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; j++)
+            v[j] = q_sx * s_qsw[sc + j] * (float)((int)rr[j] - q_zx * s_qrs[sc + j]);
         } else {
 #pragma unroll
           for (int j = 0; j < 32; j++) v[j] = __uint_as_float(rr[j]) * args.alpha;
         }
         if (args.bias) {
-          if (args.bias_f32) {
-            const float* bp = (const float*)args.bias;
 #pragma unroll
-            for (int j = 0; j < 32; j++)
-              if (col0 + j < args.N) v[j] += __ldg(bp + col0 + j);
+          for (int j = 0; j < 32; j++) v[j] += s_bias[sc + j];
+        }
+        const bool full_cols = col0 + 32 <= args.N;
+        // ---- auxiliary tensor ----
+        if (args.aux_mode == AUX_STORE_PRE) {
+          uint16_t* ap = (uint16_t*)args.aux + (long long)b * args.strideAux + (long long)row * args.ldaux + col0;
+          if (full_cols && aux_vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 o;
+              o.x = pack16x(v[j], v[j + 1], args.in_bf16); o.y = pack16x(v[j + 2], v[j + 3], args.in_bf16);
+              o.z = pack16x(v[j + 4], v[j + 5], args.in_bf16); o.w = pack16x(v[j + 6], v[j + 7], args.in_bf16);
+              *reinterpret_cast<uint4*>(ap + j) = o;
+            }
           } else {
-            const uint16_t* bp = (const uint16_t*)args.bias;
-#pragma unroll
             for (int j = 0; j < 32; j++)
               if (col0 + j < args.N) {
-                uint32_t u = __ldg(bp + col0 + j);
-                v[j] += args.in_bf16 ? __uint_as_float(u << 16) : __half2float(__ushort_as_half((unsigned short)u));
+                if (args.in_bf16) ((__nv_bfloat16*)ap)[j] = __float2bfloat16_rn(v[j]);
+                else ((__half*)ap)[j] = __float2half_rn(v[j]);
               }
           }
         }
-        const bool full_cols = col0 + 32 <= args.N;
-        if (row_ok) {
-          // ---- auxiliary tensor ----
-          if (args.aux_mode != AUX_NONE) {
-            uint16_t* ap = (uint16_t*)args.aux + (long long)b * args.strideAux +
-                           (long long)row * args.ldaux + col0;
-            if (args.aux_mode == AUX_STORE_PRE) {
-              if (full_cols && aux_vec_ok) {
+        switch (args.act) {
+          case ACT_RELU:
 #pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                  uint4 o;
-                  if (args.in_bf16) {
-                    o.x = pack_bf16(v[j], v[j + 1]); o.y = pack_bf16(v[j + 2], v[j + 3]);
-                    o.z = pack_bf16(v[j + 4], v[j + 5]); o.w = pack_bf16(v[j + 6], v[j + 7]);
-                  } else {
-                    o.x = pack_f16(v[j], v[j + 1]); o.y = pack_f16(v[j + 2], v[j + 3]);
-                    o.z = pack_f16(v[j + 4], v[j + 5]); o.w = pack_f16(v[j + 6], v[j + 7]);
-                  }
-                  *reinterpret_cast<uint4*>(ap + j) = o;
-                }
-              } else {
-                for (int j = 0; j < 32; j++)
-                  if (col0 + j < args.N) {
-                    if (args.in_bf16) ((__nv_bfloat16*)ap)[j] = __float2bfloat16_rn(v[j]);
-                    else ((__half*)ap)[j] = __float2half_rn(v[j]);
-                  }
-              }
+            for (int j = 0; j < 32; j++) v[j] = fmaxf(v[j], 0.f);
+            break;
+          case ACT_GELU_TANH:
 #pragma unroll
-              for (int j = 0; j < 32; j++) v[j] = act_apply<float>(v[j], args.act);
-            } else {
-              float a[32];
-              if (full_cols && aux_vec_ok) {
+            for (int j = 0; j < 32; j++) v[j] = gelu_tanh_f(v[j]);
+            break;
+          case ACT_GELU_ERF:
 #pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                  uint4 u = *reinterpret_cast<const uint4*>(ap + j);
-                  float2 f;
-                  f = unpack16(u.x, args.in_bf16); a[j] = f.x; a[j + 1] = f.y;
-                  f = unpack16(u.y, args.in_bf16); a[j + 2] = f.x; a[j + 3] = f.y;
-                  f = unpack16(u.z, args.in_bf16); a[j + 4] = f.x; a[j + 5] = f.y;
-                  f = unpack16(u.w, args.in_bf16); a[j + 6] = f.x; a[j + 7] = f.y;
-                }
-              } else {
-                for (int j = 0; j < 32; j++) {
-                  a[j] = 0.f;
-                  if (col0 + j < args.N)
-                    a[j] = args.in_bf16 ? __bfloat162float(((__nv_bfloat16*)ap)[j])
-                                        : __half2float(((__half*)ap)[j]);
-                }
-              }
+            for (int j = 0; j < 32; j++) v[j] = gelu_erf_f(v[j]);
+            break;
+          default: break;
+        }
+        if (aux_in) {
+          float a[32];
+          if (aux_fast) {
 #pragma unroll
-              for (int j = 0; j < 32; j++) {
-                float x = act_apply<float>(v[j], args.act);
-                switch (args.aux_mode) {
-                  case AUX_ADD: x += a[j]; break;
-                  case AUX_MUL_DGELU_TANH: x *= dgelu_tanh_f(a[j]); break;
-                  case AUX_MUL_DRELU: x = a[j] > 0.f ? x : 0.f; break;
-                  case AUX_MUL_DGELU_ERF: x *= dgelu_erf_f(a[j]); break;
-                  default: break;
-                }
-                v[j] = x;
-              }
-            }
-          } else if (args.act != ACT_NONE) {
-#pragma unroll
-            for (int j = 0; j < 32; j++) v[j] = act_apply<float>(v[j], args.act);
-          }
-          // ---- store ----
-          if (args.out_kind == OUT_F32) {
-            float* cp = (float*)args.C + (long long)b * args.strideC + (long long)row * args.ldc + col0;
-            const bool v4 = full_cols && ((args.ldc & 3) == 0) && ((args.strideC & 3) == 0) &&
-                            (((uintptr_t)args.C & 15) == 0);
-            if (v4) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                if (args.beta) {
-                  float4 old = *reinterpret_cast<const float4*>(cp + j);
-                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                }
-                *reinterpret_cast<float4*>(cp + j) = o;
-              }
-            } else {
-              for (int j = 0; j < 32; j++)
-                if (col0 + j < args.N) cp[j] = args.beta ? cp[j] + v[j] : v[j];
+            for (int j = 0; j < 4; j++) {
+              const uint4 u = auxc[j];
+              float2 f;
+              f = unpack16(u.x, args.in_bf16); a[j * 8] = f.x; a[j * 8 + 1] = f.y;
+              f = unpack16(u.y, args.in_bf16); a[j * 8 + 2] = f.x; a[j * 8 + 3] = f.y;
+              f = unpack16(u.z, args.in_bf16); a[j * 8 + 4] = f.x; a[j * 8 + 5] = f.y;
+              f = unpack16(u.w, args.in_bf16); a[j * 8 + 6] = f.x; a[j * 8 + 7] = f.y;
             }
           } else {
-            uint16_t* cp = (uint16_t*)args.C + (long long)b * args.strideC + (long long)row * args.ldc + col0;
-            const bool bf = args.out_kind == OUT_BF16;
-            if (full_cols && vec_ok) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                if (args.beta) {
-                  uint4 u = *reinterpret_cast<const uint4*>(cp + j);
-                  float2 f;
-                  f = unpack16(u.x, bf); v[j] += f.x; v[j + 1] += f.y;
-                  f = unpack16(u.y, bf); v[j + 2] += f.x; v[j + 3] += f.y;
-                  f = unpack16(u.z, bf); v[j + 4] += f.x; v[j + 5] += f.y;
-                  f = unpack16(u.w, bf); v[j + 6] += f.x; v[j + 7] += f.y;
-                }
-                uint4 o;
-                if (bf) {
-                  o.x = pack_bf16(v[j], v[j + 1]); o.y = pack_bf16(v[j + 2], v[j + 3]);
-                  o.z = pack_bf16(v[j + 4], v[j + 5]); o.w = pack_bf16(v[j + 6], v[j + 7]);
-                } else {
-                  o.x = pack_f16(v[j], v[j + 1]); o.y = pack_f16(v[j + 2], v[j + 3]);
-                  o.z = pack_f16(v[j + 4], v[j + 5]); o.w = pack_f16(v[j + 6], v[j + 7]);
-                }
-                *reinterpret_cast<uint4*>(cp + j) = o;
-              }
-            } else {
-              for (int j = 0; j < 32; j++)
-                if (col0 + j < args.N) {
-                  float x = v[j];
-                  if (bf) {
-                    if (args.beta) x += __bfloat162float(((__nv_bfloat16*)cp)[j]);
-                    ((__nv_bfloat16*)cp)[j] = __float2bfloat16_rn(x);
-                  } else {
-                    if (args.beta) x += __half2float(((__half*)cp)[j]);
-                    ((__half*)cp)[j] = __float2half_rn(x);
-                  }
-                }
+            const uint16_t* ap = (const uint16_t*)args.aux + (long long)b * args.strideAux + (long long)row * args.ldaux + col0;
+            for (int j = 0; j < 32; j++) {
+              a[j] = 0.f;
+              if (col0 + j < args.N)
+                a[j] = args.in_bf16 ? __bfloat162float(((const __nv_bfloat16*)ap)[j])
+                                    : __half2float(((const __half*)ap)[j]);
             }
+          }
+          switch (args.aux_mode) {
+            case AUX_ADD:
+#pragma unroll
+              for (int j = 0; j < 32; j++) v[j] += a[j];
+              break;
+            case AUX_MUL_DGELU_TANH:
+#pragma unroll
+              for (int j = 0; j < 32; j++) v[j] *= dgelu_tanh_f(a[j]);
+              break;
+            case AUX_MUL_DRELU:
+#pragma unroll
+              for (int j = 0; j < 32; j++) v[j] = a[j] > 0.f ? v[j] : 0.f;
+              break;
+            case AUX_MUL_DGELU_ERF:
+#pragma unroll
+              for (int j = 0; j < 32; j++) v[j] *= dgelu_erf_f(a[j]);
+              break;
+            default: break;
+          }
+        }
+        // ---- store ----
+        if (args.out_kind == OUT_F32) {
+          float* cp = (float*)args.C + (long long)b * args.strideC + (long long)row * args.ldc + col0;
+          const bool v4 = full_cols && ((args.ldc & 3) == 0) && ((args.strideC & 3) == 0) &&
+                          (((uintptr_t)args.C & 15) == 0);
+          if (v4) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              if (args.beta) {
+                float4 old = *reinterpret_cast<const float4*>(cp + j);
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              *reinterpret_cast<float4*>(cp + j) = o;
+            }
+          } else {
+            for (int j = 0; j < 32; j++)
+              if (col0 + j < args.N) cp[j] = args.beta ? cp[j] + v[j] : v[j];
+          }
+        } else {
+          uint16_t* cp = (uint16_t*)args.C + (long long)b * args.strideC + (long long)row * args.ldc + col0;
+          const bool bf = args.out_kind == OUT_BF16;
+          if (full_cols && vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (args.beta) {
+                uint4 u = *reinterpret_cast<const uint4*>(cp + j);
+                float2 f;
+                f = unpack16(u.x, bf); v[j] += f.x; v[j + 1] += f.y;
+                f = unpack16(u.y, bf); v[j + 2] += f.x; v[j + 3] += f.y;
+                f = unpack16(u.z, bf); v[j + 4] += f.x; v[j + 5] += f.y;
+                f = unpack16(u.w, bf); v[j + 6] += f.x; v[j + 7] += f.y;
+              }
+              uint4 o;
+              o.x = pack16x(v[j], v[j + 1], bf); o.y = pack16x(v[j + 2], v[j + 3], bf);
+              o.z = pack16x(v[j + 4], v[j + 5], bf); o.w = pack16x(v[j + 6], v[j + 7], bf);
+              *reinterpret_cast<uint4*>(cp + j) = o;
+            }
+          } else {
+            for (int j = 0; j < 32; j++)
+              if (col0 + j < args.N) {
+                float x = v[j];
+                if (bf) {
+                  if (args.beta) x += __bfloat162float(((__nv_bfloat16*)cp)[j]);
+                  ((__nv_bfloat16*)cp)[j] = __float2bfloat16_rn(x);
+                } else {
+                  if (args.beta) x += __half2float(((__half*)cp)[j]);
+                  ((__half*)cp)[j] = __float2half_rn(x);
+                }
+              }
           }
         }
       }
@@ -511,11 +576,13 @@ __global__ void gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ 
   }
 }
 
-template <int ESZ, bool A_MN, bool B_MN, int BN>
-int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args, int num_sms,
-              cudaStream_t stream) {
+int g_epi_warps = 8;
+
+template <int ESZ, bool A_MN, bool B_MN, int BN, int EW>
+int launch_tc_ew(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args, int num_sms,
+                 cudaStream_t stream) {
   using C = Cfg<ESZ, BN>;
-  auto kern = gemm_tcgen05_kernel<ESZ, A_MN, B_MN, BN>;
+  auto kern = gemm_tcgen05_kernel<ESZ, A_MN, B_MN, BN, EW>;
   static bool configured = false;
   if (!configured) {
     GB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
@@ -523,9 +590,16 @@ int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& ar
   }
   int tiles = args.num_m * args.num_n * args.batch;
   int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmA, tmB, args);
+  kern<<<grid, 64 + 32 * EW, C::SMEM_BYTES, stream>>>(tmA, tmB, args);
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;
+}
+
+template <int ESZ, bool A_MN, bool B_MN, int BN>
+int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args, int num_sms,
+              cudaStream_t stream) {
+  if (g_epi_warps == 4) return launch_tc_ew<ESZ, A_MN, B_MN, BN, 4>(tmA, tmB, args, num_sms, stream);
+  return launch_tc_ew<ESZ, A_MN, B_MN, BN, 8>(tmA, tmB, args, num_sms, stream);
 }
 
 template <int ESZ, int BN>
@@ -542,6 +616,7 @@ int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorM
 }
 
 int g_num_sms = 0;
+int g_group_m = 8;
 
 // Builds the two tensor maps and launches.  esz: 2 (bf16/fp16) or 1 (int8).
 int gemm_tc(int esz, const void* A, const void* B, GemmArgs& args, int transA, int transB,
@@ -570,6 +645,7 @@ int gemm_tc(int esz, const void* A, const void* B, GemmArgs& args, int transA, i
   args.num_m = (M + BM - 1) / BM;
   args.num_n = (N + bn - 1) / bn;
   args.status = gbh::status_ptr();
+  args.group_m = g_group_m;
 
   CUtensorMapDataType dt = esz == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                     : (args.in_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -618,6 +694,13 @@ int gemm_tc(int esz, const void* A, const void* B, GemmArgs& args, int transA, i
 }
 
 }  // namespace
+
+// Tuning knobs: epilogue warps (4 or 8) and rasterisation group height (row blocks).
+GB_EXPORT int gb_gemm_tune(int epi_warps, int group_m) {
+  if (epi_warps == 4 || epi_warps == 8) g_epi_warps = epi_warps;
+  if (group_m >= 1) g_group_m = group_m;
+  return 0;
+}
 
 // dtype codes shared with the Python side
 enum { DT_BF16 = 0, DT_F16 = 1, DT_F32 = 2, DT_F64 = 3, DT_I8 = 4 };

@@ -237,18 +237,26 @@ norm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TW* __r
   }
 }
 
-// dgamma[c] = sum_p part[p][0][c], dbeta[c] = sum_p part[p][1][c], fixed order.
+// dgamma[c] = sum_p part[p][0][c], dbeta[c] = sum_p part[p][1][c]: CTA of 32 columns
+// x 32 row lanes, fixed summation order.
 template <typename TW>
 __global__ void norm_param_reduce_kernel(const float* __restrict__ part, int P, int D,
                                          TW* __restrict__ dgamma, TW* __restrict__ dbeta) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * D) return;
+  __shared__ float sm[32][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  for (int p = 0; p < P; p++) s += part[(long long)p * 2 * D + c];
-  if (c < D) {
-    if (dgamma) dgamma[c] = (TW)s;
-  } else if (dbeta) {
-    dbeta[c - D] = (TW)s;
+  if (c < 2 * D)
+    for (int p = threadIdx.y; p < P; p += 32) s += part[(long long)p * 2 * D + c];
+  sm[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < 2 * D) {
+#pragma unroll
+    for (int k = 1; k < 32; k++) s += sm[k][threadIdx.x];
+    if (c < D) {
+      if (dgamma) dgamma[c] = (TW)s;
+    } else if (dbeta) {
+      dbeta[c - D] = (TW)s;
+    }
   }
 }
 
@@ -324,7 +332,7 @@ __global__ void norm_param_generic(const T* __restrict__ x, const T* __restrict_
 
 int pick_grid(long long rows, int gpb) {
   long long need = (rows + gpb - 1) / gpb;
-  long long cap = 148 * 4;
+  long long cap = 148 * 2;
   return (int)(need < cap ? need : cap);
 }
 
@@ -393,8 +401,8 @@ int norm_bwd_t(const void* x, const void* dy, const void* w, const float* mean, 
 #undef GB_BWD
   GB_CUDA_OK(cudaGetLastError());
   if (want_param) {
-    norm_param_reduce_kernel<TW><<<(2 * D + 255) / 256, 256, 0, s>>>(part, grid, D, (TW*)dgamma,
-                                                                    (TW*)dbeta);
+    norm_param_reduce_kernel<TW><<<(2 * D + 31) / 32, dim3(32, 32), 0, s>>>(part, grid, D, (TW*)dgamma,
+                                                                           (TW*)dbeta);
     GB_CUDA_OK(cudaGetLastError());
   }
   return gbh::E_OK;
@@ -406,7 +414,7 @@ enum { DT_BF16 = 0, DT_F16 = 1, DT_F32 = 2 };
 
 // Maximum number of partial rows the backward may use; scratch must hold
 // gb_norm_bwd_scratch_rows() * 2 * D floats.
-GB_EXPORT int gb_norm_bwd_scratch_rows() { return 148 * 4; }
+GB_EXPORT int gb_norm_bwd_scratch_rows() { return 148 * 2; }
 
 // kind: 0 = LayerNorm, 1 = RMSNorm.  dtype of x / y; wdtype of weight / bias
 // (the same as dtype, or fp32).  mean may be null for RMSNorm.

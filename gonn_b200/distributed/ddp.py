@@ -71,7 +71,7 @@ class _Bucket:
 
 class DistributedDataParallel(torch.nn.Module):
     def __init__(self, module: torch.nn.Module, process_group=None, optimizer: Optional[dict] = None,
-                 bucket_mb: float = 32.0, comm_ctas: int = 32, overlap: bool = True,
+                 bucket_mb: float = 32.0, comm_ctas: Optional[int] = None, overlap: bool = True,
                  rank: Optional[int] = None, world: Optional[int] = None):
         super().__init__()
         self.module = module
@@ -82,7 +82,10 @@ class DistributedDataParallel(torch.nn.Module):
             else:
                 rank, world = 0, 1
         self.rank, self.world = rank, world
-        self.overlap, self.comm_ctas = overlap, comm_ctas
+        # one rank: the step kernel is a plain memory-bound pass and may fill the GPU; several
+        # ranks: it runs beside backward, so it gets a slice of the SMs
+        self.overlap = overlap
+        self.comm_ctas = comm_ctas if comm_ctas is not None else (296 if world == 1 else 48)
         params = ordered_parameters(module)
         if not params:
             raise ValueError("DistributedDataParallel: the module has no trainable parameters")

@@ -10,3 +10,9 @@ from .attention import MultiHeadAttention  # noqa
 from .transformer import (TransformerEncoderLayer, TransformerEncoder, TransformerDecoderLayer,  # noqa
                           TransformerDecoder, Transformer)
 from . import init  # noqa
+from .loss import *  # noqa
+from .loss import (MSELoss, MAELoss, L1Loss, HuberLoss, SmoothL1Loss, CrossEntropyLoss, NLLLoss, BCELoss,  # noqa
+                   BCEWithLogitsLoss, KLDivLoss, PoissonNLLLoss, GaussianNLLLoss, MarginRankingLoss,
+                   HingeEmbeddingLoss, CosineEmbeddingLoss, TripletMarginLoss, MultiMarginLoss, SoftMarginLoss,
+                   MultiLabelSoftMarginLoss, MultiLabelMarginLoss, TripletMarginWithDistanceLoss, CTCLoss,
+                   PairwiseL2Distance)
