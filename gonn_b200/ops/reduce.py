@@ -59,7 +59,7 @@ def reduce_axis(x: torch.Tensor, axis: int, op: str = "sum", keepdim: bool = Fal
     else:
         del oshape[axis]
     arg = op in ("argmax", "argmin")
-    odt = torch.int64 if arg else (out_dtype or x.dtype)
+    odt = torch.int64 if arg else (out.dtype if out is not None else (out_dtype or x.dtype))
     if out is None:
         out = torch.empty(oshape, dtype=odt, device=x.device)
         accumulate = False
@@ -72,7 +72,7 @@ def reduce_axis(x: torch.Tensor, axis: int, op: str = "sum", keepdim: bool = Fal
         need = outer * inner * esz
     scratch = _get_scratch(x.device, need) if need else None
     _l.call("gb_reduce", _l.I(_OPS[op]), _l.I(_l.dtype_code(x.dtype)),
-            _l.I(0 if arg else _l.dtype_code(odt)), _l.ptr(xc), _l.ptr(out), _l.ptr(scratch),
+            _l.I(_l.dtype_code(x.dtype) if arg else _l.dtype_code(odt)), _l.ptr(xc), _l.ptr(out), _l.ptr(scratch),
             _l.L(scratch.numel() if scratch is not None else 0), _l.L(outer), _l.L(R), _l.L(inner),
             _l.I(int(accumulate)), _l.stream_ptr())
     return out
