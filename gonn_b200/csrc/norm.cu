@@ -458,3 +458,47 @@ GB_EXPORT int gb_norm_bwd(int kind, int dtype, int wdtype, const void* x, const 
   gbh::set_error("gb_norm_bwd: unsupported dtype pair %d/%d", dtype, wdtype);
   return gbh::E_BAD_ARG;
 }
+
+// ---------------------------------------------------------------------------
+// LayerNorm / RMSNorm backward without any allocation (see norm_noalloc.h)
+// ---------------------------------------------------------------------------
+// The partial dgamma / dbeta sums of the backward kernel normally live in a
+// buffer the caller allocates.  This variant keeps them in a fixed array inside
+// the library image instead.  Every GPU that loads the library holds the array
+// (kNoAllocRows * 2 * kNoAllocMaxD floats, about 4.6 MiB) until the process exits.
+namespace {
+constexpr int kNoAllocRows = 148;    // partial rows: at most one CTA per SM
+constexpr int kNoAllocMaxD = 4096;   // widest row this entry point accepts
+constexpr int kNoAllocDevices = 16;
+static __device__ __align__(256) float g_noalloc_scratch[(size_t)kNoAllocRows * 2 * kNoAllocMaxD];
+// Device address of the array per device.  In host code the array's name only stands in
+// for the symbol; the address a kernel can use comes from cudaGetSymbolAddress.
+float* g_noalloc_ptr[kNoAllocDevices] = {nullptr};
+}  // namespace
+
+GB_EXPORT int gb_norm_bwd_noalloc_max_dim() { return kNoAllocMaxD; }
+
+GB_EXPORT int gb_norm_bwd_noalloc(int kind, int dtype, int wdtype, const void* x, const void* dy,
+                                  const void* w, const float* mean, const float* rstd, void* dx,
+                                  void* dgamma, void* dbeta, long long rows, int D, void* stream) {
+  if (D > kNoAllocMaxD) {
+    gbh::set_error("gb_norm_bwd_noalloc: row width %d exceeds the built-in scratch (max %d)", D,
+                   kNoAllocMaxD);
+    return gbh::E_TOO_LARGE;
+  }
+  int dev = 0;
+  GB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kNoAllocDevices) {
+    gbh::set_error("gb_norm_bwd_noalloc: device index %d out of range", dev);
+    return gbh::E_BAD_ARG;
+  }
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // one-time set-up for this device (it is the current device here)
+    float* p = nullptr;
+    GB_CUDA_OK(cudaGetSymbolAddress((void**)&p, g_noalloc_scratch));
+    g_noalloc_ptr[dev] = p;
+  }
+  // The kernels write every partial row they later read, so nothing needs clearing.
+  return gb_norm_bwd(kind, dtype, wdtype, x, dy, w, mean, rstd, dx, dgamma, dbeta, g_noalloc_ptr[dev],
+                     kNoAllocRows, rows, D, stream);
+}
