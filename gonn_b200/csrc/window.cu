@@ -1,0 +1,216 @@
+// Sliding-window core shared by convolution, pooling, fold / unfold and padding.
+//
+// The reference builds, for every sliding-window layer, a dense 0/1 "gather
+// matrix" G (numWin*winSize x prod(In)) and applies it with a GEMM
+// (nn/gather.go:99-181, nn/conv.go:341-380, nn/pool.go:340-370).  Here the same
+// information is an int32 index map idx[win][tap] (-1 = padding) and the gather
+// is done by address: no multiply by zeros, no dense matrix.  The transpose of
+// the gather (col2im, pooling backward) uses the inverted map in CSR form, so it
+// is a gather too: deterministic, no atomics.
+//
+//   window_gather   col[n][win][c*T + tap] = x[n][c][idx[win][tap]]   (im2col; the row
+//                   of one window is K-major for the GEMM that follows)
+//   window_scatter  dx[n][c][i] = sum over (win,tap) with idx[win][tap]==i of
+//                   dcol[n][win][c*T + tap]                              (col2im)
+//   pool_fwd / pool_bwd   max (with argmax), average, LP-norm pooling over idx
+#include "common.cuh"
+
+using namespace gb;
+
+namespace {
+
+template <typename T>
+__global__ void window_gather_kernel(const T* __restrict__ x, const int* __restrict__ idx,
+                                     T* __restrict__ col, int N, int C, long long S, int nwin, int T_,
+                                     int kpad, float fill) {
+  // one thread per (n, win, k) with k = c*T + tap; k in [0, kpad), zero beyond C*T
+  const long long total = (long long)N * nwin * kpad;
+  const int K = C * T_;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int k = (int)(i % kpad);
+    const long long r = i / kpad;
+    const int win = (int)(r % nwin);
+    const int n = (int)(r / nwin);
+    T v = (T)0.f;
+    if (k < K) {
+      const int c = k / T_, tap = k - c * T_;
+      const int src = idx[win * T_ + tap];
+      v = src >= 0 ? x[((long long)n * C + c) * S + src] : (T)fill;
+    }
+    col[i] = v;
+  }
+}
+
+// dx[n][c][i] = sum_{e in csr(i)} dcol[n][win(e)][c*T + tap(e)], csr_cols[e] = win*T + tap
+template <typename T>
+__global__ void window_scatter_kernel(const T* __restrict__ dcol, const int* __restrict__ offs,
+                                      const int* __restrict__ cols, T* __restrict__ dx, int N, int C,
+                                      long long S, int nwin, int T_, int kpad, int accumulate) {
+  const long long total = (long long)N * C * S;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long pos = i % S;
+    const long long r = i / S;
+    const int c = (int)(r % C);
+    const int n = (int)(r / C);
+    float acc = 0.f;
+    for (int e = offs[pos]; e < offs[pos + 1]; e++) {
+      const int wt = cols[e];
+      const int win = wt / T_, tap = wt - win * T_;
+      acc += (float)dcol[((long long)n * nwin + win) * kpad + c * T_ + tap];
+    }
+    dx[i] = accumulate ? (T)((float)dx[i] + acc) : (T)acc;
+  }
+}
+
+enum PoolMode : int { POOL_MAX = 0, POOL_AVG = 1, POOL_LP = 2 };
+
+// y[b][win] over taps idx[win][*]; b = n*C + c.  arg[b][win] = winning tap (max).
+template <typename T>
+__global__ void pool_fwd_kernel(const T* __restrict__ x, const int* __restrict__ idx,
+                                T* __restrict__ y, int* __restrict__ arg, long long B, long long S,
+                                int nwin, int T_, int mode, int count_include_pad, float p) {
+  const long long total = B * nwin;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int win = (int)(i % nwin);
+    const long long b = i / nwin;
+    const T* xb = x + b * S;
+    const int* iw = idx + (long long)win * T_;
+    if (mode == POOL_MAX) {
+      float best = -INFINITY;
+      int bt = -1;
+      for (int t = 0; t < T_; t++) {
+        const int src = iw[t];
+        if (src < 0) continue;
+        const float v = (float)xb[src];
+        if (v > best || bt < 0) { best = v; bt = t; }
+      }
+      y[i] = (T)(bt < 0 ? 0.f : best);
+      if (arg) arg[i] = bt;
+    } else if (mode == POOL_AVG) {
+      float s = 0.f;
+      int cnt = 0;
+      for (int t = 0; t < T_; t++) {
+        const int src = iw[t];
+        if (src >= 0) { s += (float)xb[src]; cnt++; }
+      }
+      const int div = count_include_pad ? T_ : (cnt > 0 ? cnt : 1);
+      y[i] = (T)(s / (float)div);
+    } else {
+      float s = 0.f;
+      for (int t = 0; t < T_; t++) {
+        const int src = iw[t];
+        if (src >= 0) s += powf((float)xb[src], p);
+      }
+      y[i] = (T)powf(s, 1.f / p);
+    }
+  }
+}
+
+// dx[b][i] = sum over (win,tap) covering i of the window's gradient share
+template <typename T>
+__global__ void pool_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                const T* __restrict__ y, const int* __restrict__ arg,
+                                const int* __restrict__ idx, const int* __restrict__ offs,
+                                const int* __restrict__ cols, T* __restrict__ dx, long long B,
+                                long long S, int nwin, int T_, int mode, int count_include_pad,
+                                float p) {
+  const long long total = B * S;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long pos = i % S;
+    const long long b = i / S;
+    float acc = 0.f;
+    for (int e = offs[pos]; e < offs[pos + 1]; e++) {
+      const int wt = cols[e];
+      const int win = wt / T_, tap = wt - win * T_;
+      const long long o = b * nwin + win;
+      if (mode == POOL_MAX) {
+        if (arg[o] == tap) acc += (float)dy[o];
+      } else if (mode == POOL_AVG) {
+        int div = T_;
+        if (!count_include_pad) {
+          int cnt = 0;
+          for (int t = 0; t < T_; t++) cnt += idx[(long long)win * T_ + t] >= 0;
+          div = cnt > 0 ? cnt : 1;
+        }
+        acc += (float)dy[o] / (float)div;
+      } else {
+        // d/dx (sum x^p)^(1/p) = x^(p-1) * y^(1-p)
+        const float yv = (float)y[o];
+        if (yv != 0.f) acc += (float)dy[o] * powf((float)x[i], p - 1.f) * powf(yv, 1.f - p);
+      }
+    }
+    dx[i] = (T)acc;
+  }
+}
+
+inline int grid_for(long long work) {
+  long long g = (work + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+}  // namespace
+
+enum { DT_BF16 = 0, DT_F16 = 1, DT_F32 = 2, DT_F64 = 3 };
+
+#define GB_DISPATCH_T(CALL)                                   \
+  switch (dtype) {                                            \
+    case DT_BF16: { using T = __nv_bfloat16; CALL; } break;   \
+    case DT_F16: { using T = __half; CALL; } break;           \
+    case DT_F32: { using T = float; CALL; } break;            \
+    default:                                                  \
+      gbh::set_error("window op: unsupported dtype %d", dtype); \
+      return gbh::E_BAD_ARG;                                  \
+  }
+
+// im2col: x (N,C,S) -> col (N, nwin, kpad) with K = C*T real columns (zero padded to kpad)
+GB_EXPORT int gb_window_gather(int dtype, const void* x, const int* idx, void* col, int N, int C,
+                               long long S, int nwin, int T_, int kpad, float fill, void* stream) {
+  const long long total = (long long)N * nwin * kpad;
+  if (total <= 0) return gbh::E_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  GB_DISPATCH_T((window_gather_kernel<T><<<grid_for(total), 256, 0, s>>>((const T*)x, idx, (T*)col, N, C, S, nwin, T_, kpad, fill)));
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}
+
+// col2im: dcol (N, nwin, kpad) -> dx (N,C,S) through the inverted index map (CSR over S)
+GB_EXPORT int gb_window_scatter(int dtype, const void* dcol, const int* offs, const int* cols,
+                                void* dx, int N, int C, long long S, int nwin, int T_, int kpad,
+                                int accumulate, void* stream) {
+  const long long total = (long long)N * C * S;
+  if (total <= 0) return gbh::E_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  GB_DISPATCH_T((window_scatter_kernel<T><<<grid_for(total), 256, 0, s>>>((const T*)dcol, offs, cols, (T*)dx, N, C, S, nwin, T_, kpad, accumulate)));
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}
+
+// mode: 0 max (arg receives the winning tap per window, may be null), 1 average, 2 LP norm
+GB_EXPORT int gb_pool_fwd(int dtype, const void* x, const int* idx, void* y, int* arg, long long B,
+                          long long S, int nwin, int T_, int mode, int count_include_pad, float p,
+                          void* stream) {
+  const long long total = B * nwin;
+  if (total <= 0) return gbh::E_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  GB_DISPATCH_T((pool_fwd_kernel<T><<<grid_for(total), 256, 0, s>>>((const T*)x, idx, (T*)y, arg, B, S, nwin, T_, mode, count_include_pad, p)));
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}
+
+GB_EXPORT int gb_pool_bwd(int dtype, const void* dy, const void* x, const void* y, const int* arg,
+                          const int* idx, const int* offs, const int* cols, void* dx, long long B,
+                          long long S, int nwin, int T_, int mode, int count_include_pad, float p,
+                          void* stream) {
+  const long long total = B * S;
+  if (total <= 0) return gbh::E_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  GB_DISPATCH_T((pool_bwd_kernel<T><<<grid_for(total), 256, 0, s>>>((const T*)dy, (const T*)x, (const T*)y, arg, idx, offs, cols, (T*)dx, B, S, nwin, T_, mode, count_include_pad, p)));
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}

@@ -29,6 +29,14 @@ class CollectiveTimeout(RuntimeError):
     """A peer did not reach a collective within the kernel's wait budget."""
 
 
+_current = [None]
+
+
+def current():
+    """The process's symmetric memory (the native communicator is one per process), or None."""
+    return _current[0]
+
+
 class SymmetricMemory:
     """This rank's symmetric buffer.  Offsets handed to kernels count from the buffer's
     base (the flag area comes first); ``view`` takes offsets into the data region."""
@@ -36,6 +44,7 @@ class SymmetricMemory:
     def __init__(self, data_bytes: int, rank: int = 0, world: int = 1, process_group=None,
                  emulate: int = 0, device: Optional[torch.device] = None):
         self.rank, self.world, self.emulate = rank, world, emulate
+        _current[0] = self
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device())
         self.device = device
