@@ -16,3 +16,21 @@ from .loss import (MSELoss, MAELoss, L1Loss, HuberLoss, SmoothL1Loss, CrossEntro
                    HingeEmbeddingLoss, CosineEmbeddingLoss, TripletMarginLoss, MultiMarginLoss, SoftMarginLoss,
                    MultiLabelSoftMarginLoss, MultiLabelMarginLoss, TripletMarginWithDistanceLoss, CTCLoss,
                    PairwiseL2Distance)
+from .conv import (Conv1d, Conv2d, Conv3d, ConvTranspose1d, ConvTranspose2d, ConvTranspose3d, Unfold, Fold)  # noqa
+from .pool import *  # noqa
+from .batchnorm import (BatchNorm1d, BatchNorm2d, BatchNorm3d, GroupNorm, InstanceNorm1d, InstanceNorm2d,  # noqa
+                        InstanceNorm3d, LocalResponseNorm)
+from .shape_layers import *  # noqa
+from .rnn import (RNNCell, LSTMCell, GRUCell, RNN, LSTM, GRU, Seq2Seq, PackedSequence, PadSequence,  # noqa
+                  UnpadSequence, PackPaddedSequence, PackSequence, PadPackedSequence)
+from .adaptive_softmax import AdaptiveLogSoftmaxWithLoss  # noqa
+from .hooks import (RegisterForwardPreHook, RegisterForwardHook, RegisterFullBackwardHook, RemoveHook,  # noqa
+                    RegisterModuleForwardPreHook, RegisterModuleForwardHook, RegisterModuleFullBackwardHook,
+                    RemoveModuleHook, Call)
+from .stateless import (WithReplacedParams, FunctionalCall, FunctionalCallMulti, FunctionalCallGrad,  # noqa
+                        FunctionalCallGradMulti)
+from .lazy import *  # noqa
+from .lazy import IsLazy  # noqa
+from .fuse import FuseConvBNEval, FuseLinearBNEval  # noqa
+from .parametrize import *  # noqa
+from . import prune  # noqa
