@@ -1,0 +1,126 @@
+"""Optimizers: convergence on a quadratic, exact first steps, groups, schedulers' LR traces,
+clipping and vector utilities (optim/*_test.go patterns of the reference)."""
+import math
+
+import pytest
+import torch
+
+from gonn_b200 import optim
+
+ALL = [(optim.SGD, dict(lr=0.1, momentum=0.9)), (optim.SGD, dict(lr=0.1, momentum=0.9, nesterov=True)),
+       (optim.Adam, dict(lr=0.1)), (optim.AdamW, dict(lr=0.1)), (optim.Lion, dict(lr=0.02)), (optim.LAMB, dict(lr=0.05)),
+       (optim.RMSprop, dict(lr=0.05)), (optim.Adagrad, dict(lr=0.5)), (optim.Adadelta, dict(lr=5.0)),
+       (optim.NAdam, dict(lr=0.1)), (optim.Adamax, dict(lr=0.1)), (optim.RAdam, dict(lr=0.1)), (optim.Rprop, dict(lr=0.1)),
+       (optim.Adafactor, dict(lr=0.1)), (optim.ASGD, dict(lr=0.1)), (optim.SparseAdam, dict(lr=0.1))]
+
+
+@pytest.mark.parametrize("cls,kw", ALL, ids=[f"{c.__name__}{i}" for i, (c, _) in enumerate(ALL)])
+def test_converges_on_quadratic(cls, kw):
+    w = torch.nn.Parameter(torch.tensor([3.0, -2.0], dtype=torch.float64))
+    o = cls([w], **kw)
+    for _ in range(400):
+        o.zero_grad()
+        ((w - torch.tensor([1.0, 0.5], dtype=torch.float64)) ** 2).sum().backward()
+        o.step()
+    assert (w.detach() - torch.tensor([1.0, 0.5], dtype=torch.float64)).abs().max().item() < 0.15
+
+
+def test_exact_update_rules():
+    # SGD momentum: v = mu v + g, p -= lr v (no dampening)
+    w = torch.nn.Parameter(torch.tensor([1.0], dtype=torch.float64))
+    o = optim.SGD([w], lr=0.1, momentum=0.9)
+    for expected in (1 - 0.1 * 2.0, None):
+        o.zero_grad(); (w * 2).sum().backward(); o.step()
+        if expected is not None:
+            assert w.item() == pytest.approx(expected, abs=1e-15)
+    assert w.item() == pytest.approx(0.8 - 0.1 * (0.9 * 2 + 2), abs=1e-15)
+    # AdamW: decay before the Adam term, eps outside the root
+    w = torch.nn.Parameter(torch.tensor([2.0], dtype=torch.float64))
+    o = optim.AdamW([w], lr=0.1, weight_decay=0.5)
+    o.zero_grad(); (w * 3).sum().backward(); o.step()
+    p = 2.0 - 0.1 * 0.5 * 2.0
+    m, v = 0.1 * 3, 0.001 * 9
+    assert w.item() == pytest.approx(p - 0.1 * (m / 0.1) / (math.sqrt(v / 0.001) + 1e-8), abs=1e-12)
+    assert sorted(o.state(w).bufs) == ["m", "v"]
+    # the single-list AdamW defaults to 0.01 decay; group constructors inject nothing
+    assert optim.AdamW([w]).groups[0].weight_decay == 0.01
+    assert optim.NewAdamWGroups([optim.Group([w], lr=1e-3)]).groups[0].weight_decay == 0.0
+
+
+def test_groups_and_schedulers():
+    a, b = (torch.nn.Parameter(torch.ones(1)) for _ in range(2))
+    o = optim.SGD([optim.Group([a], lr=1.0), optim.Group([b], lr=0.1)])
+    s = optim.StepLR(o, 2, 0.5)
+    tr = []
+    for _ in range(4):
+        s.step(); tr.append((o.groups[0].lr, o.groups[1].lr))
+    assert tr == [(1.0, 0.1), (0.5, 0.05), (0.5, 0.05), (0.25, 0.025)]
+    o.set_lr(0.3)
+    assert [g.lr for g in o.groups] == [0.3, 0.3]
+    o = optim.SGD([a], lr=1.0)
+    lin = optim.LinearLR(o, 0.5, 1.0, 4)
+    assert o.lr() == 0.5
+    vals = []
+    for _ in range(5):
+        lin.step(); vals.append(round(o.lr(), 6))
+    assert vals == [0.625, 0.75, 0.875, 1.0, 1.0]
+    o = optim.SGD([a], lr=1.0)
+    oc = optim.OneCycleLR(o, 3.0, 4)
+    vals = []
+    for _ in range(5):
+        oc.step(); vals.append(o.lr())
+    assert vals == [2.0, 3.0, 2.0, 1.0, 1.0]
+    o = optim.SGD([a], lr=1.0)
+    pl = optim.ReduceLROnPlateau(o, 0.1, 0.0, 1)
+    for v in (1.0, 1.0, 1.0, 1.0):
+        pl.step(v)
+    assert o.lr() == pytest.approx(0.1)
+    o = optim.SGD([a], lr=1.0)
+    sq = optim.SequentialLR([optim.ExponentialLR(o, 0.5), optim.ExponentialLR(o, 2.0)], [2])
+    vals = []
+    for _ in range(4):
+        sq.step(); vals.append(o.lr())
+    assert vals == [0.5, 0.25, 0.5, 1.0]
+    o = optim.SGD([a], lr=1.0)
+    cy = optim.CyclicLR(o, 0.1, 1.1, 2)
+    vals = []
+    for _ in range(4):
+        cy.step(); vals.append(round(o.lr(), 6))
+    assert vals == [0.6, 1.1, 0.6, 0.1]
+    o = optim.SGD([a], lr=1.0)
+    po = optim.PolynomialLR(o, 4, 2.0)
+    po.step()
+    assert o.lr() == pytest.approx(0.5625)
+    o = optim.SGD([a], lr=1.0)
+    optim.ChainedScheduler(optim.ExponentialLR(o, 0.5), optim.MultiStepLR(o, [1], 0.1)).step()
+    assert o.lr() == pytest.approx(0.05)
+
+
+def test_clip_and_vectors():
+    a, b = torch.nn.Parameter(torch.zeros(2)), torch.nn.Parameter(torch.zeros(1))
+    a.grad, b.grad = torch.tensor([3.0, 0.0]), torch.tensor([4.0])
+    n = optim.ClipGradNorm([a, b], 1.0)
+    assert n == pytest.approx(5.0)
+    assert optim.TotalGradNorm([a, b]) == pytest.approx(5.0 / (5.0 + 1e-6), rel=1e-6)
+    optim.ClipGradValue([a, b], 0.5)
+    assert a.grad.max().item() <= 0.5
+    v = optim.ParametersToVector([a, b])
+    optim.VectorToParameters(v + 1, [a, b])
+    assert a.tolist() == [1.0, 1.0] and b.tolist() == [1.0]
+    b.grad = None
+    assert optim.GradsToVector([a, b]).shape == (3,)
+    with pytest.raises(ValueError):
+        optim.VectorToParameters(torch.zeros(2), [a, b])
+
+
+def test_lbfgs_minimises_rosenbrock_like():
+    w = torch.nn.Parameter(torch.tensor([-1.0, 1.5], dtype=torch.float64))
+    o = optim.LBFGS([w], max_iter=60)
+
+    def closure():
+        l = (1 - w[0]) ** 2 + 5 * (w[1] - w[0] ** 2) ** 2
+        l.backward()
+        return l
+    for _ in range(5):
+        loss = o.step(closure)
+    assert loss < 1e-6
