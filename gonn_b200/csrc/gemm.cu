@@ -58,6 +58,8 @@ struct GemmArgs {
   int in_bf16;  // 1 = bf16 inputs, 0 = fp16 inputs (ignored for int8)
   int bcastA, bcastB;  // operand shared by every batch entry (batch stride 0)
   int group_m;         // row blocks per rasterisation group
+  int pf_dist;         // L2 prefetch distance in k-blocks (0 = off)
+  int tma_epi;         // 1: results leave through shared memory and TMA stores (16-bit outputs)
   int* status;
 };
 
@@ -69,9 +71,23 @@ struct Cfg {
   static constexpr int B_BYTES = BN * kSwizzleBytes;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ +
-                                    3 * 2 * 256 * 4 /*per-column epilogue constants*/;
+};
+
+// Dynamic shared memory of both kernels (the base must be 1024-byte aligned, which the
+// kernels check):  [operand ring] [epilogue staging: 2 x 2 KB per epilogue warp, 16-bit
+// path only] [512 B of barriers] [per-column epilogue constants, double buffered].
+template <int ESZ, int RING, int EW>
+struct SmemLayout {
+  static constexpr int kStageBuf = 2048;  // 32 rows x 64 B, 64-byte swizzle
+  static constexpr int OFF_STAGING = RING;
+  static constexpr int STAGING = ESZ == 2 ? EW * 2 * kStageBuf : 0;
+  static constexpr int OFF_BARS = OFF_STAGING + STAGING;
+  static constexpr int OFF_COLS = OFF_BARS + 512;
+  static constexpr int COL_BYTES = (ESZ == 1 ? 3 : 1) * 2 * 256 * 4;
+  static constexpr int BYTES = OFF_COLS + COL_BYTES;
+  static_assert(BYTES <= 232448, "shared memory layout exceeds 227 KB");
 };
 
 // Tile order: groups of `gm` row blocks are swept across all column blocks before the
@@ -103,25 +119,459 @@ __device__ __forceinline__ uint32_t pack16x(float a, float b, int bf) {
   return bf ? pack_bf16(a, b) : pack_f16(a, b);
 }
 
+// Per-warp constants of the epilogue.
+struct EpiCtx {
+  int q, half, et, lane;
+  bool vec_ok, aux_vec_ok, aux_in, has_cols;
+  float q_sx;
+  int q_zx;
+  float* s_bias;
+  float* s_qsw;
+  int* s_qrs;
+};
+
+template <int ESZ>
+__device__ __forceinline__ EpiCtx make_epi_ctx(const GemmArgs& args, int warp, int lane, int et, float* s_bias,
+                                               float* s_qsw, int* s_qrs) {
+  EpiCtx c;
+  c.q = warp & 3;
+  c.half = (warp - 2) >> 2;
+  c.et = et;
+  c.lane = lane;
+  c.vec_ok = ((args.ldc & 7) == 0) && ((args.strideC & 7) == 0) && (((uintptr_t)args.C & 15) == 0);
+  c.aux_vec_ok = args.aux_mode == AUX_NONE || (((args.ldaux & 7) == 0) && ((args.strideAux & 7) == 0) &&
+                                               (((uintptr_t)args.aux & 15) == 0));
+  c.aux_in = args.aux_mode != AUX_NONE && args.aux_mode != AUX_STORE_PRE;
+  c.has_cols = args.bias != nullptr || ESZ == 1;
+  c.q_sx = 1.f;
+  c.q_zx = 0;
+  if (ESZ == 1) {
+    c.q_sx = *args.q_sx;
+    c.q_zx = args.q_zx ? *args.q_zx : 0;
+  }
+  c.s_bias = s_bias; c.s_qsw = s_qsw; c.s_qrs = s_qrs;
+  return c;
+}
+
+// Epilogue of one 128-row x BN-column accumulator held in this CTA's TMEM at column
+// `tmem_acc`: everything that does not depend on the accumulator (bias, residual / saved
+// pre-activation) is fetched BEFORE waiting for the MMAs, so those latencies overlap the
+// main loop of the tile.  Returns false when the wait ran out of budget.
+template <int ESZ, int BN, int EW>
+__device__ __forceinline__ bool epilogue_tile(const GemmArgs& args, const EpiCtx& cx, int buf, int b, int m0,
+                                              int n0, uint32_t tmem_acc, uint64_t* tfull, uint32_t tfull_phase,
+                                              volatile int* abort_flag) {
+  constexpr int COLS = BN / (EW / 4);  // columns per thread per tile
+  constexpr int NCH = COLS / 32;
+  const int q = cx.q, half = cx.half, et = cx.et, lane = cx.lane;
+  const bool vec_ok = cx.vec_ok, aux_vec_ok = cx.aux_vec_ok, aux_in = cx.aux_in, has_cols = cx.has_cols;
+  const float q_sx = cx.q_sx;
+  const int q_zx = cx.q_zx;
+  float* s_bias = cx.s_bias;
+  float* s_qsw = cx.s_qsw;
+  int* s_qrs = cx.s_qrs;
+    const int row = m0 + q * 32 + lane;
+    const bool row_ok = row < args.M;
+    const int cbase = n0 + half * COLS;  // first column of this thread
+    // ---- per-column constants into shared memory (double buffered by tile parity) ----
+    if (has_cols) {
+      for (int e2 = et; e2 < BN; e2 += 32 * EW) {
+        const int et_ = e2;
+        const int col = n0 + et_;
+        float bv = 0.f;
+        if (args.bias && col < args.N) {
+          if (args.bias_f32) bv = __ldg((const float*)args.bias + col);
+          else {
+            uint32_t u = __ldg((const uint16_t*)args.bias + col);
+            bv = args.in_bf16 ? __uint_as_float(u << 16) : __half2float(__ushort_as_half((unsigned short)u));
+          }
+        }
+        s_bias[buf * 256 + et_] = bv;
+        if (ESZ == 1) {
+          float sw = 1.f;
+          int rs = 0;
+          if (col < args.N) {
+            sw = args.q_per_channel ? __ldg(args.q_sw + col) : __ldg(args.q_sw);
+            rs = args.q_rowsum ? __ldg(args.q_rowsum + col) : 0;
+          }
+          s_qsw[buf * 256 + et_] = sw;
+          s_qrs[buf * 256 + et_] = rs;
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");
+    }
+    // ---- prefetch the first chunk of the auxiliary input (next chunks: one ahead) ----
+    const bool aux_fast = aux_in && aux_vec_ok && row_ok && (cbase + COLS <= args.N);
+    const uint4* aux_row = reinterpret_cast<const uint4*>(
+        (const uint16_t*)args.aux + (long long)b * args.strideAux + (long long)row * args.ldaux + cbase);
+    uint4 auxn[4];
+    if (aux_fast) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) auxn[j] = __ldg(aux_row + j);
+    }
+    if (!mbar_wait(tfull, tfull_phase, abort_flag, args.status, ST_GEMM_TIMEOUT, 4)) return false;
+    tc_fence_after();
+    const uint32_t taddr = tmem_acc + ((uint32_t)(q * 32) << 16) + half * COLS;
+    // The chunk loop is deliberately not unrolled: the body is large and eight warps
+    // run it; keeping one copy keeps it resident in the instruction cache.
+#pragma unroll 1
+    for (int c = 0; c < NCH; c++) {
+      uint32_t rr[32];
+      tmem_ld32(taddr + c * 32, rr);
+      uint4 auxc[4];
+      if (aux_fast) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) auxc[j] = auxn[j];
+        if (c + 1 < NCH) {
+#pragma unroll
+          for (int j = 0; j < 4; j++) auxn[j] = __ldg(aux_row + (c + 1) * 4 + j);
+        }
+      }
+      tmem_ld_wait();
+      const int col0 = cbase + c * 32;
+      if (col0 >= args.N || !row_ok) continue;
+      const int sc = buf * 256 + half * COLS + c * 32;  // index into the per-column arrays
+      float v[32];
+      if (ESZ == 1) {
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+          v[j] = q_sx * s_qsw[sc + j] * (float)((int)rr[j] - q_zx * s_qrs[sc + j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = __uint_as_float(rr[j]) * args.alpha;
+      }
+      if (args.bias) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] += s_bias[sc + j];
+      }
+      const bool full_cols = col0 + 32 <= args.N;
+      // ---- auxiliary tensor ----
+      if (args.aux_mode == AUX_STORE_PRE) {
+        uint16_t* ap = (uint16_t*)args.aux + (long long)b * args.strideAux + (long long)row * args.ldaux + col0;
+        if (full_cols && aux_vec_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 o;
+            o.x = pack16x(v[j], v[j + 1], args.in_bf16); o.y = pack16x(v[j + 2], v[j + 3], args.in_bf16);
+            o.z = pack16x(v[j + 4], v[j + 5], args.in_bf16); o.w = pack16x(v[j + 6], v[j + 7], args.in_bf16);
+            *reinterpret_cast<uint4*>(ap + j) = o;
+          }
+        } else {
+          for (int j = 0; j < 32; j++)
+            if (col0 + j < args.N) {
+              if (args.in_bf16) ((__nv_bfloat16*)ap)[j] = __float2bfloat16_rn(v[j]);
+              else ((__half*)ap)[j] = __float2half_rn(v[j]);
+            }
+        }
+      }
+      switch (args.act) {
+        case ACT_RELU:
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = fmaxf(v[j], 0.f);
+          break;
+        case ACT_GELU_TANH:
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = gelu_tanh_f(v[j]);
+          break;
+        case ACT_GELU_ERF:
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = gelu_erf_f(v[j]);
+          break;
+        default: break;
+      }
+      if (aux_in) {
+        float a[32];
+        if (aux_fast) {
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const uint4 u = auxc[j];
+            float2 f;
+            f = unpack16(u.x, args.in_bf16); a[j * 8] = f.x; a[j * 8 + 1] = f.y;
+            f = unpack16(u.y, args.in_bf16); a[j * 8 + 2] = f.x; a[j * 8 + 3] = f.y;
+            f = unpack16(u.z, args.in_bf16); a[j * 8 + 4] = f.x; a[j * 8 + 5] = f.y;
+            f = unpack16(u.w, args.in_bf16); a[j * 8 + 6] = f.x; a[j * 8 + 7] = f.y;
+          }
+        } else {
+          const uint16_t* ap = (const uint16_t*)args.aux + (long long)b * args.strideAux + (long long)row * args.ldaux + col0;
+          for (int j = 0; j < 32; j++) {
+            a[j] = 0.f;
+            if (col0 + j < args.N)
+              a[j] = args.in_bf16 ? __bfloat162float(((const __nv_bfloat16*)ap)[j])
+                                  : __half2float(((const __half*)ap)[j]);
+          }
+        }
+        switch (args.aux_mode) {
+          case AUX_ADD:
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] += a[j];
+            break;
+          case AUX_MUL_DGELU_TANH:
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] *= dgelu_tanh_f(a[j]);
+            break;
+          case AUX_MUL_DRELU:
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = a[j] > 0.f ? v[j] : 0.f;
+            break;
+          case AUX_MUL_DGELU_ERF:
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] *= dgelu_erf_f(a[j]);
+            break;
+          default: break;
+        }
+      }
+      // ---- store ----
+      if (args.out_kind == OUT_F32) {
+        float* cp = (float*)args.C + (long long)b * args.strideC + (long long)row * args.ldc + col0;
+        const bool v4 = full_cols && ((args.ldc & 3) == 0) && ((args.strideC & 3) == 0) &&
+                        (((uintptr_t)args.C & 15) == 0);
+        if (v4) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            if (args.beta) {
+              float4 old = *reinterpret_cast<const float4*>(cp + j);
+              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            }
+            *reinterpret_cast<float4*>(cp + j) = o;
+          }
+        } else {
+          for (int j = 0; j < 32; j++)
+            if (col0 + j < args.N) cp[j] = args.beta ? cp[j] + v[j] : v[j];
+        }
+      } else {
+        uint16_t* cp = (uint16_t*)args.C + (long long)b * args.strideC + (long long)row * args.ldc + col0;
+        const bool bf = args.out_kind == OUT_BF16;
+        if (full_cols && vec_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (args.beta) {
+              uint4 u = *reinterpret_cast<const uint4*>(cp + j);
+              float2 f;
+              f = unpack16(u.x, bf); v[j] += f.x; v[j + 1] += f.y;
+              f = unpack16(u.y, bf); v[j + 2] += f.x; v[j + 3] += f.y;
+              f = unpack16(u.z, bf); v[j + 4] += f.x; v[j + 5] += f.y;
+              f = unpack16(u.w, bf); v[j + 6] += f.x; v[j + 7] += f.y;
+            }
+            uint4 o;
+            o.x = pack16x(v[j], v[j + 1], bf); o.y = pack16x(v[j + 2], v[j + 3], bf);
+            o.z = pack16x(v[j + 4], v[j + 5], bf); o.w = pack16x(v[j + 6], v[j + 7], bf);
+            *reinterpret_cast<uint4*>(cp + j) = o;
+          }
+        } else {
+          for (int j = 0; j < 32; j++)
+            if (col0 + j < args.N) {
+              float x = v[j];
+              if (bf) {
+                if (args.beta) x += __bfloat162float(((__nv_bfloat16*)cp)[j]);
+                ((__nv_bfloat16*)cp)[j] = __float2bfloat16_rn(x);
+              } else {
+                if (args.beta) x += __half2float(((__half*)cp)[j]);
+                ((__half*)cp)[j] = __float2half_rn(x);
+              }
+            }
+        }
+      }
+    }
+  return true;
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr)
+               : "memory");
+  return v;
+}
+
+// Per-warp staging state of the TMA epilogue: two 2 KB buffers (32 rows x 32 sixteen-bit
+// columns, 64-byte swizzle), one mbarrier per buffer for auxiliary loads, their parities.
+struct EpiStage {
+  uint8_t* buf;
+  uint64_t* bar;
+  uint32_t phase;
+};
+
+// Epilogue through shared memory for 16-bit outputs.  A thread owns one accumulator row, so
+// direct stores would touch 32 different rows per instruction (16-byte pieces of 32 lines);
+// here every warp writes its 32 x 32 chunk into a swizzled staging buffer and one TMA store
+// moves it out as whole lines, clipped at the matrix edge by the tensor map.  An auxiliary
+// input (residual, saved pre-activation) arrives the same way, one chunk ahead, and the
+// result overwrites it in place.  With a second output (saved pre-activation) buffer 0 holds
+// the result and buffer 1 the pre-activation.
+template <int BN, int EW>
+__device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs& args, const EpiCtx& cx, EpiStage& st,
+                                                  const CUtensorMap* tmC, const CUtensorMap* tmX, int buf, int b,
+                                                  int m0, int n0, uint32_t tmem_acc, uint64_t* tfull,
+                                                  uint32_t tfull_phase, volatile int* abort_flag) {
+  constexpr int COLS = BN / (EW / 4);
+  constexpr int NCH = COLS / 32;
+  static_assert(NCH % 2 == 0, "chunks alternate between two staging buffers");
+  const int q = cx.q, half = cx.half, et = cx.et, lane = cx.lane;
+  float* s_bias = cx.s_bias;
+  const int mrow0 = m0 + q * 32;
+  const int cbase = n0 + half * COLS;
+  const bool live = mrow0 < args.M;  // warp-uniform
+  const bool aux_in = cx.aux_in;
+  const bool two_out = args.aux_mode == AUX_STORE_PRE;
+  const int out_bf = args.out_kind == OUT_BF16;
+  if (args.bias) {
+    for (int e2 = et; e2 < BN; e2 += 32 * EW) {
+      const int col = n0 + e2;
+      float bv = 0.f;
+      if (col < args.N) {
+        if (args.bias_f32) bv = __ldg((const float*)args.bias + col);
+        else {
+          uint32_t u = __ldg((const uint16_t*)args.bias + col);
+          bv = args.in_bf16 ? __uint_as_float(u << 16) : __half2float(__ushort_as_half((unsigned short)u));
+        }
+      }
+      s_bias[buf * 256 + e2] = bv;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");
+  }
+  const uint32_t sb0 = smem_u32(st.buf);
+  const uint32_t myrow = (uint32_t)lane * 64u;
+  const uint32_t swz = ((uint32_t)lane >> 1) & 3u;
+  if (aux_in && live && cbase < args.N && lane == 0) {
+    tma_store_wait_read<0>();  // the buffer's last store has been read out
+    mbar_expect_tx(&st.bar[0], 2048);
+    tma_load_3d(st.buf, tmX, &st.bar[0], cbase, mrow0, b);
+  }
+  if (!mbar_wait(tfull, tfull_phase, abort_flag, args.status, ST_GEMM_TIMEOUT, 4)) return false;
+  tc_fence_after();
+  const uint32_t taddr = tmem_acc + ((uint32_t)(q * 32) << 16) + half * COLS;
+#pragma unroll 1
+  for (int c = 0; c < NCH; c++) {
+    uint32_t rr[32];
+    tmem_ld32(taddr + c * 32, rr);
+    tmem_ld_wait();
+    const int col0 = cbase + c * 32;
+    if (!live || col0 >= args.N) continue;
+    const int sc = buf * 256 + half * COLS + c * 32;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; j++) v[j] = __uint_as_float(rr[j]) * args.alpha;
+    if (args.bias) {
+#pragma unroll
+      for (int j = 0; j < 32; j++) v[j] += s_bias[sc + j];
+    }
+    const int bi = c & 1;
+    const uint32_t sbc = sb0 + bi * 2048;
+    if (two_out) {
+      if (lane == 0) tma_store_wait_read<0>();
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        uint4 o;
+        o.x = pack16x(v[j * 8], v[j * 8 + 1], args.in_bf16); o.y = pack16x(v[j * 8 + 2], v[j * 8 + 3], args.in_bf16);
+        o.z = pack16x(v[j * 8 + 4], v[j * 8 + 5], args.in_bf16); o.w = pack16x(v[j * 8 + 6], v[j * 8 + 7], args.in_bf16);
+        st_shared_v4(sb0 + 2048 + myrow + (((uint32_t)j ^ swz) << 4), o);
+      }
+    }
+    switch (args.act) {
+      case ACT_RELU:
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = fmaxf(v[j], 0.f);
+        break;
+      case ACT_GELU_TANH:
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = gelu_tanh_f(v[j]);
+        break;
+      case ACT_GELU_ERF:
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = gelu_erf_f(v[j]);
+        break;
+      default: break;
+    }
+    if (aux_in) {
+      if (c + 1 < NCH && col0 + 32 < args.N && lane == 0) {
+        tma_store_wait_read<0>();
+        mbar_expect_tx(&st.bar[bi ^ 1], 2048);
+        tma_load_3d(st.buf + (bi ^ 1) * 2048, tmX, &st.bar[bi ^ 1], col0 + 32, mrow0, b);
+      }
+      if (!mbar_wait(&st.bar[bi], (st.phase >> bi) & 1u, abort_flag, args.status, ST_GEMM_TIMEOUT, 5)) return false;
+      st.phase ^= 1u << bi;
+      float a[32];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const uint4 u = ld_shared_v4(sbc + myrow + (((uint32_t)j ^ swz) << 4));
+        float2 f;
+        f = unpack16(u.x, args.in_bf16); a[j * 8] = f.x; a[j * 8 + 1] = f.y;
+        f = unpack16(u.y, args.in_bf16); a[j * 8 + 2] = f.x; a[j * 8 + 3] = f.y;
+        f = unpack16(u.z, args.in_bf16); a[j * 8 + 4] = f.x; a[j * 8 + 5] = f.y;
+        f = unpack16(u.w, args.in_bf16); a[j * 8 + 6] = f.x; a[j * 8 + 7] = f.y;
+      }
+      switch (args.aux_mode) {
+        case AUX_ADD:
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] += a[j];
+          break;
+        case AUX_MUL_DGELU_TANH:
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] *= dgelu_tanh_f(a[j]);
+          break;
+        case AUX_MUL_DRELU:
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = a[j] > 0.f ? v[j] : 0.f;
+          break;
+        case AUX_MUL_DGELU_ERF:
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] *= dgelu_erf_f(a[j]);
+          break;
+        default: break;
+      }
+    } else if (!two_out) {
+      if (lane == 0) tma_store_wait_read<1>();  // the store from two chunks ago used this buffer
+      __syncwarp();
+    }
+    const uint32_t so = two_out ? sb0 : sbc;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      uint4 o;
+      o.x = pack16x(v[j * 8], v[j * 8 + 1], out_bf); o.y = pack16x(v[j * 8 + 2], v[j * 8 + 3], out_bf);
+      o.z = pack16x(v[j * 8 + 4], v[j * 8 + 5], out_bf); o.w = pack16x(v[j * 8 + 6], v[j * 8 + 7], out_bf);
+      st_shared_v4(so + myrow + (((uint32_t)j ^ swz) << 4), o);
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_3d(tmC, two_out ? st.buf : st.buf + bi * 2048, col0, mrow0, b);
+      if (two_out) tma_store_3d(tmX, st.buf + 2048, col0, mrow0, b);
+      tma_store_commit();
+    }
+  }
+  return true;
+}
+
 // ESZ: operand element size (2 = bf16/fp16, 1 = int8).  A_MN / B_MN: operand
 // is MN-major.  BN: tile width.
 template <int ESZ, bool A_MN, bool B_MN, int BN, int EW>
 __global__ void __launch_bounds__(64 + 32 * EW, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
                     const GemmArgs args) {
   using C = Cfg<ESZ, BN>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = (uint64_t*)(smem + C::STAGES * C::STAGE_BYTES);
+  using SL = SmemLayout<ESZ, C::RING_BYTES, EW>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {  // the swizzled layouts below assume this
+    if (threadIdx.x == 0) set_status(args.status, ST_BAD_INDEX, 1024);
+    return;
+  }
+  uint64_t* bars = (uint64_t*)(smem + SL::OFF_BARS);
   uint64_t* full_bar = bars;                    // [STAGES]
   uint64_t* empty_bar = bars + C::STAGES;       // [STAGES]
   uint64_t* tfull_bar = bars + 2 * C::STAGES;   // [2]
   uint64_t* tempty_bar = tfull_bar + 2;         // [2]
   uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-  float* s_bias = (float*)((uint8_t*)bars + 256);  // [2][256]
-  float* s_qsw = s_bias + 512;                     // [2][256]
-  int* s_qrs = (int*)(s_qsw + 512);                // [2][256]
+  uint64_t* aux_bar = bars + 32;                // [EW][2], 16-bit path
+  float* s_bias = (float*)(smem + SL::OFF_COLS);   // [2][256]
+  float* s_qsw = s_bias + 512;                     // [2][256]  (8-bit path only)
+  int* s_qrs = (int*)(s_qsw + 512);                // [2][256]  (8-bit path only)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -138,10 +588,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       mbar_init(&tfull_bar[i], 1);
       mbar_init(&tempty_bar[i], EW);  // one arrive per epilogue warp
     }
+    for (int i = 0; i < 2 * EW; i++) mbar_init(&aux_bar[i], 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (args.tma_epi) {
+      tma_prefetch_desc(&tmC);
+      if (args.aux_mode != AUX_NONE) tma_prefetch_desc(&tmX);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -158,13 +613,58 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      // L2 prefetch cursor: runs `pf_dist` k-blocks ahead of the loads (across tile
+      // boundaries), so that the loads that fill shared memory find their lines in L2 and
+      // the ring of shared-memory stages only has to cover the L2 latency, not DRAM's.
+      int pt = blockIdx.x, pkb = 0, pm0 = 0, pn0 = 0, pba = 0, pbb = 0;
+      auto pf_coords = [&]() {
+        if (pt >= num_tiles) return;
+        const int b = pt / tiles_per_batch;
+        const int r = pt - b * tiles_per_batch;
+        int mb, nb;
+        tile_coords(r, args.num_m, args.num_n, args.group_m, mb, nb);
+        pm0 = mb * BM;
+        pn0 = nb * BN;
+        pba = args.bcastA ? 0 : b;
+        pbb = args.bcastB ? 0 : b;
+      };
+      auto pf_step = [&](bool issue) {
+        if (pt >= num_tiles) return;
+        if (issue) {
+          const int k0 = pkb * C::BK;
+          constexpr int MN_ATOM = kSwizzleBytes / ESZ;
+          if (!A_MN) {
+            tma_prefetch_3d(&tmA, k0, pm0, pba);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / MN_ATOM; i++) tma_prefetch_3d(&tmA, pm0 + i * MN_ATOM, k0, pba);
+          }
+          if (!B_MN) {
+            tma_prefetch_3d(&tmB, k0, pn0, pbb);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / MN_ATOM; i++) tma_prefetch_3d(&tmB, pn0 + i * MN_ATOM, k0, pbb);
+          }
+        }
+        if (++pkb == num_kb) {
+          pkb = 0;
+          pt += gridDim.x;
+          pf_coords();
+        }
+      };
+      const int pf_dist = args.pf_dist == 999 ? 0 : args.pf_dist;
+      if (pf_dist > 0) {
+        pf_coords();
+        for (int i = 0; i < pf_dist; i++) pf_step(i >= C::STAGES);
+      }
+      for (int t = blockIdx.x; t < num_tiles && ok && args.pf_dist != 999; t += gridDim.x) {
         const int b = t / tiles_per_batch;
         const int r = t - b * tiles_per_batch;
         int mb, nb;
         tile_coords(r, args.num_m, args.num_n, args.group_m, mb, nb);
         const int m0 = mb * BM, n0 = nb * BN;
         for (int kb = 0; kb < num_kb; kb++) {
+          if (pf_dist > 0) pf_step(true);
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, args.status, ST_GEMM_TIMEOUT, 1);
           if (!ok) break;
           uint8_t* sa = smem + stage * C::STAGE_BYTES;
@@ -209,23 +709,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     } else if (args.in_bf16) {
       id |= (1u << 7) | (1u << 10);  // bf16 A and B
     }
-    int stage = 0;
-    uint32_t phase = 0;
-    uint32_t tphase[2] = {0, 0};
-    int local_tile = 0;
-    bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, local_tile++) {
-      const int buf = local_tile & 1;
-      ok = mbar_wait(&tempty_bar[buf], tphase[buf] ^ 1, abort_flag, args.status, ST_GEMM_TIMEOUT, 2);
-      if (!ok) break;
-      tphase[buf] ^= 1;
-      tc_fence_after();
-      const uint32_t d_tmem = tmem_base + buf * BN;
-      for (int kb = 0; kb < num_kb; kb++) {
-        ok = mbar_wait(&full_bar[stage], phase, abort_flag, args.status, ST_GEMM_TIMEOUT, 3);
+    // One elected thread runs the whole issue loop (waits included): no per-k-block
+    // reconvergence of the warp, and the compiler sees a single-thread instruction stream.
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t tphase[2] = {0, 0};
+      int local_tile = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, local_tile++) {
+        const int buf = local_tile & 1;
+        ok = mbar_wait(&tempty_bar[buf], tphase[buf] ^ 1, abort_flag, args.status, ST_GEMM_TIMEOUT, 2);
         if (!ok) break;
+        tphase[buf] ^= 1;
         tc_fence_after();
-        if (lane == 0) {
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; kb++) {
+          if (args.pf_dist != 999)
+            ok = mbar_wait(&full_bar[stage], phase, abort_flag, args.status, ST_GEMM_TIMEOUT, 3);
+          if (!ok) break;
+          tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
           const uint32_t sb = sa + C::A_BYTES;
 #pragma unroll
@@ -248,37 +751,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           tc_commit(&empty_bar[stage]);
           if (kb == num_kb - 1) tc_commit(&tfull_bar[buf]);
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
         }
-        __syncwarp();
-        if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
       }
     }
+    __syncwarp();
   } else {
     // ---------------- epilogue (warps 2..9) ----------------
     // Two warps per TMEM lane quarter; each handles half of the tile's columns.
     // Everything that does not depend on the accumulator (bias, residual / saved
     // pre-activation) is fetched BEFORE waiting for the MMAs, so those latencies
     // overlap the main loop of the tile.
-    const int q = warp & 3;
-    const int half = (warp - 2) >> 2;  // which column part this warp owns
-    const int et = threadIdx.x - 64;  // 0..255 among the epilogue threads
-    constexpr int COLS = BN / (EW / 4);  // columns per thread per tile
-    constexpr int NCH = COLS / 32;
+    const EpiCtx cx = make_epi_ctx<ESZ>(args, warp, lane, threadIdx.x - 64, s_bias, s_qsw, s_qrs);
+    EpiStage est;
+    est.buf = smem + SL::OFF_STAGING + (warp - 2) * 2 * SL::kStageBuf;
+    est.bar = aux_bar + (warp - 2) * 2;
+    est.phase = 0;
     uint32_t tphase[2] = {0, 0};
     int local_tile = 0;
-    const bool vec_ok = ((args.ldc & 7) == 0) && ((args.strideC & 7) == 0) &&
-                        (((uintptr_t)args.C & 15) == 0);
-    const bool aux_vec_ok = args.aux_mode == AUX_NONE ||
-                            (((args.ldaux & 7) == 0) && ((args.strideAux & 7) == 0) &&
-                             (((uintptr_t)args.aux & 15) == 0));
-    const bool aux_in = args.aux_mode != AUX_NONE && args.aux_mode != AUX_STORE_PRE;
-    const bool has_cols = args.bias != nullptr || ESZ == 1;
-    float q_sx = 1.f;
-    int q_zx = 0;
-    if (ESZ == 1) {
-      q_sx = *args.q_sx;
-      q_zx = args.q_zx ? *args.q_zx : 0;
-    }
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, local_tile++) {
       const int buf = local_tile & 1;
@@ -287,216 +777,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int mb, nb;
       tile_coords(r, args.num_m, args.num_n, args.group_m, mb, nb);
       const int m0 = mb * BM, n0 = nb * BN;
-      const int row = m0 + q * 32 + lane;
-      const bool row_ok = row < args.M;
-      const int cbase = n0 + half * COLS;  // first column of this thread
-      // ---- per-column constants into shared memory (double buffered by tile parity) ----
-      if (has_cols) {
-        for (int e2 = et; e2 < BN; e2 += 32 * EW) {
-          const int et_ = e2;
-          const int col = n0 + et_;
-          float bv = 0.f;
-          if (args.bias && col < args.N) {
-            if (args.bias_f32) bv = __ldg((const float*)args.bias + col);
-            else {
-              uint32_t u = __ldg((const uint16_t*)args.bias + col);
-              bv = args.in_bf16 ? __uint_as_float(u << 16) : __half2float(__ushort_as_half((unsigned short)u));
-            }
-          }
-          s_bias[buf * 256 + et_] = bv;
-          if (ESZ == 1) {
-            float sw = 1.f;
-            int rs = 0;
-            if (col < args.N) {
-              sw = args.q_per_channel ? __ldg(args.q_sw + col) : __ldg(args.q_sw);
-              rs = args.q_rowsum ? __ldg(args.q_rowsum + col) : 0;
-            }
-            s_qsw[buf * 256 + et_] = sw;
-            s_qrs[buf * 256 + et_] = rs;
-          }
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");
+      bool done;
+      if (ESZ == 2 && args.tma_epi)
+        done = epilogue_tile_tma<BN, EW>(args, cx, est, &tmC, &tmX, buf, b, m0, n0, tmem_base + buf * BN,
+                                         &tfull_bar[buf], tphase[buf], abort_flag);
+      else
+        done = epilogue_tile<ESZ, BN, EW>(args, cx, buf, b, m0, n0, tmem_base + buf * BN, &tfull_bar[buf],
+                                          tphase[buf], abort_flag);
+      if (!done) {
+        ok = false;
+        break;
       }
-      // ---- prefetch the first chunk of the auxiliary input (next chunks: one ahead) ----
-      const bool aux_fast = aux_in && aux_vec_ok && row_ok && (cbase + COLS <= args.N);
-      const uint4* aux_row = reinterpret_cast<const uint4*>(
-          (const uint16_t*)args.aux + (long long)b * args.strideAux + (long long)row * args.ldaux + cbase);
-      uint4 auxn[4];
-      if (aux_fast) {
-#pragma unroll
-        for (int j = 0; j < 4; j++) auxn[j] = __ldg(aux_row + j);
-      }
-      ok = mbar_wait(&tfull_bar[buf], tphase[buf], abort_flag, args.status, ST_GEMM_TIMEOUT, 4);
-      if (!ok) break;
       tphase[buf] ^= 1;
-      tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * COLS;
-      // The chunk loop is deliberately not unrolled: the body is large and eight warps
-      // run it; keeping one copy keeps it resident in the instruction cache.
-#pragma unroll 1
-      for (int c = 0; c < NCH; c++) {
-        uint32_t rr[32];
-        tmem_ld32(taddr + c * 32, rr);
-        uint4 auxc[4];
-        if (aux_fast) {
-#pragma unroll
-          for (int j = 0; j < 4; j++) auxc[j] = auxn[j];
-          if (c + 1 < NCH) {
-#pragma unroll
-            for (int j = 0; j < 4; j++) auxn[j] = __ldg(aux_row + (c + 1) * 4 + j);
-          }
-        }
-        tmem_ld_wait();
-        const int col0 = cbase + c * 32;
-        if (col0 >= args.N || !row_ok) continue;
-        const int sc = buf * 256 + half * COLS + c * 32;  // index into the per-column arrays
-        float v[32];
-        if (ESZ == 1) {
-#pragma unroll
-          for (int j = 0; j < 32; j++)
-            v[j] = q_sx * s_qsw[sc + j] * (float)((int)rr[j] - q_zx * s_qrs[sc + j]);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; j++) v[j] = __uint_as_float(rr[j]) * args.alpha;
-        }
-        if (args.bias) {
-#pragma unroll
-          for (int j = 0; j < 32; j++) v[j] += s_bias[sc + j];
-        }
-        const bool full_cols = col0 + 32 <= args.N;
-        // ---- auxiliary tensor ----
-        if (args.aux_mode == AUX_STORE_PRE) {
-          uint16_t* ap = (uint16_t*)args.aux + (long long)b * args.strideAux + (long long)row * args.ldaux + col0;
-          if (full_cols && aux_vec_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 o;
-              o.x = pack16x(v[j], v[j + 1], args.in_bf16); o.y = pack16x(v[j + 2], v[j + 3], args.in_bf16);
-              o.z = pack16x(v[j + 4], v[j + 5], args.in_bf16); o.w = pack16x(v[j + 6], v[j + 7], args.in_bf16);
-              *reinterpret_cast<uint4*>(ap + j) = o;
-            }
-          } else {
-            for (int j = 0; j < 32; j++)
-              if (col0 + j < args.N) {
-                if (args.in_bf16) ((__nv_bfloat16*)ap)[j] = __float2bfloat16_rn(v[j]);
-                else ((__half*)ap)[j] = __float2half_rn(v[j]);
-              }
-          }
-        }
-        switch (args.act) {
-          case ACT_RELU:
-#pragma unroll
-            for (int j = 0; j < 32; j++) v[j] = fmaxf(v[j], 0.f);
-            break;
-          case ACT_GELU_TANH:
-#pragma unroll
-            for (int j = 0; j < 32; j++) v[j] = gelu_tanh_f(v[j]);
-            break;
-          case ACT_GELU_ERF:
-#pragma unroll
-            for (int j = 0; j < 32; j++) v[j] = gelu_erf_f(v[j]);
-            break;
-          default: break;
-        }
-        if (aux_in) {
-          float a[32];
-          if (aux_fast) {
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-              const uint4 u = auxc[j];
-              float2 f;
-              f = unpack16(u.x, args.in_bf16); a[j * 8] = f.x; a[j * 8 + 1] = f.y;
-              f = unpack16(u.y, args.in_bf16); a[j * 8 + 2] = f.x; a[j * 8 + 3] = f.y;
-              f = unpack16(u.z, args.in_bf16); a[j * 8 + 4] = f.x; a[j * 8 + 5] = f.y;
-              f = unpack16(u.w, args.in_bf16); a[j * 8 + 6] = f.x; a[j * 8 + 7] = f.y;
-            }
-          } else {
-            const uint16_t* ap = (const uint16_t*)args.aux + (long long)b * args.strideAux + (long long)row * args.ldaux + col0;
-            for (int j = 0; j < 32; j++) {
-              a[j] = 0.f;
-              if (col0 + j < args.N)
-                a[j] = args.in_bf16 ? __bfloat162float(((const __nv_bfloat16*)ap)[j])
-                                    : __half2float(((const __half*)ap)[j]);
-            }
-          }
-          switch (args.aux_mode) {
-            case AUX_ADD:
-#pragma unroll
-              for (int j = 0; j < 32; j++) v[j] += a[j];
-              break;
-            case AUX_MUL_DGELU_TANH:
-#pragma unroll
-              for (int j = 0; j < 32; j++) v[j] *= dgelu_tanh_f(a[j]);
-              break;
-            case AUX_MUL_DRELU:
-#pragma unroll
-              for (int j = 0; j < 32; j++) v[j] = a[j] > 0.f ? v[j] : 0.f;
-              break;
-            case AUX_MUL_DGELU_ERF:
-#pragma unroll
-              for (int j = 0; j < 32; j++) v[j] *= dgelu_erf_f(a[j]);
-              break;
-            default: break;
-          }
-        }
-        // ---- store ----
-        if (args.out_kind == OUT_F32) {
-          float* cp = (float*)args.C + (long long)b * args.strideC + (long long)row * args.ldc + col0;
-          const bool v4 = full_cols && ((args.ldc & 3) == 0) && ((args.strideC & 3) == 0) &&
-                          (((uintptr_t)args.C & 15) == 0);
-          if (v4) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-              if (args.beta) {
-                float4 old = *reinterpret_cast<const float4*>(cp + j);
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-              }
-              *reinterpret_cast<float4*>(cp + j) = o;
-            }
-          } else {
-            for (int j = 0; j < 32; j++)
-              if (col0 + j < args.N) cp[j] = args.beta ? cp[j] + v[j] : v[j];
-          }
-        } else {
-          uint16_t* cp = (uint16_t*)args.C + (long long)b * args.strideC + (long long)row * args.ldc + col0;
-          const bool bf = args.out_kind == OUT_BF16;
-          if (full_cols && vec_ok) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (args.beta) {
-                uint4 u = *reinterpret_cast<const uint4*>(cp + j);
-                float2 f;
-                f = unpack16(u.x, bf); v[j] += f.x; v[j + 1] += f.y;
-                f = unpack16(u.y, bf); v[j + 2] += f.x; v[j + 3] += f.y;
-                f = unpack16(u.z, bf); v[j + 4] += f.x; v[j + 5] += f.y;
-                f = unpack16(u.w, bf); v[j + 6] += f.x; v[j + 7] += f.y;
-              }
-              uint4 o;
-              o.x = pack16x(v[j], v[j + 1], bf); o.y = pack16x(v[j + 2], v[j + 3], bf);
-              o.z = pack16x(v[j + 4], v[j + 5], bf); o.w = pack16x(v[j + 6], v[j + 7], bf);
-              *reinterpret_cast<uint4*>(cp + j) = o;
-            }
-          } else {
-            for (int j = 0; j < 32; j++)
-              if (col0 + j < args.N) {
-                float x = v[j];
-                if (bf) {
-                  if (args.beta) x += __bfloat162float(((__nv_bfloat16*)cp)[j]);
-                  ((__nv_bfloat16*)cp)[j] = __float2bfloat16_rn(x);
-                } else {
-                  if (args.beta) x += __half2float(((__half*)cp)[j]);
-                  ((__half*)cp)[j] = __float2half_rn(x);
-                }
-              }
-          }
-        }
-      }
       // accumulator buffer is free again
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
     }
+    // shared memory must outlive the stores that read from it
+    if (ESZ == 2 && args.tma_epi && lane == 0) tma_store_wait<0>();
   }
 
   tc_fence_before();
@@ -504,6 +803,272 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Two-CTA variant: a cluster of two CTAs (two SMs) computes one 256 x 256 tile with
+// tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of A and its own 128 of
+// the 256 columns of B (so B crosses the L2 -> SM path once per pair instead of twice,
+// and a stage is 32 KB instead of 48 KB: six stages fit), and owns 128 rows of the
+// accumulator in its TMEM.  CTA 0 issues the MMAs for the pair.  Every TMA load is an
+// ordinary per-CTA load; nothing is broadcast across the cluster.
+// ---------------------------------------------------------------------------
+constexpr uint32_t kPeerBit = 1u << 24;  // shared::cluster address bit that selects CTA 1 of a pair
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_3d_2sm(void* dst, const CUtensorMap* m, uint32_t bar_addr, int c0,
+                                                int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(dst)),
+      "l"((uint64_t)m), "r"(bar_addr), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_2sm(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_2sm() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_2sm(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16_2sm(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive (when the issuing thread's earlier MMAs retire) on the barrier at a shared::cluster address
+__device__ __forceinline__ void tc_commit_2sm(uint32_t bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_addr) : "memory");
+}
+
+struct Cfg2 {
+  static constexpr int BN = 256;                 // columns of the pair tile (each CTA stages 128 of them)
+  static constexpr int BK = 64;
+  static constexpr int UMMA_K = 16;
+  static constexpr int A_BYTES = 128 * kSwizzleBytes;
+  static constexpr int B_BYTES = 128 * kSwizzleBytes;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 6;
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int TMEM_COLS = 512;
+};
+
+template <bool A_MN, bool B_MN, int EW>
+__global__ void __launch_bounds__(64 + 32 * EW, 1)
+gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmX,
+                         const GemmArgs args) {
+  using C = Cfg2;
+  using SL = SmemLayout<2, C::RING_BYTES, EW>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {
+    if (threadIdx.x == 0) set_status(args.status, ST_BAD_INDEX, 1024);
+    return;
+  }
+  uint64_t* bars = (uint64_t*)(smem + SL::OFF_BARS);
+  uint64_t* full_bar = bars;                   // [STAGES]  used in CTA 0
+  uint64_t* empty_bar = bars + C::STAGES;      // [STAGES]  per CTA
+  uint64_t* tfull_bar = bars + 2 * C::STAGES;  // [2]       per CTA
+  uint64_t* tempty_bar = tfull_bar + 2;        // [2]       used in CTA 0
+  uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  uint64_t* aux_bar = bars + 32;               // [EW][2]   per CTA
+  float* s_bias = (float*)(smem + SL::OFF_COLS);
+  float* s_qsw = s_bias;   // 8-bit constants are not used by this kernel
+  int* s_qrs = (int*)s_bias;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();      // 0: leader (issues the MMAs), 1: peer
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int num_kb = (args.K + C::BK - 1) / C::BK;
+  // num_m / num_n count 256 x 256 pair tiles here
+  const int tiles_per_batch = args.num_m * args.num_n;
+  const int num_tiles = tiles_per_batch * args.batch;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; s++) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; i++) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], 2 * EW);  // the epilogue warps of both CTAs
+    }
+    for (int i = 0; i < 2 * EW; i++) mbar_init(&aux_bar[i], 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    if (args.tma_epi) {
+      tma_prefetch_desc(&tmC);
+      if (args.aux_mode != AUX_NONE) tma_prefetch_desc(&tmX);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc_2sm(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish_2sm();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // barriers of both CTAs are initialised before anyone touches the peer's
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (one per CTA) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        const int b = t / tiles_per_batch;
+        const int r = t - b * tiles_per_batch;
+        int mb, nb;
+        tile_coords(r, args.num_m, args.num_n, args.group_m, mb, nb);
+        const int m0 = mb * 256 + (int)cta * 128;   // this CTA's rows of A
+        const int n0 = nb * 256 + (int)cta * 128;   // this CTA's columns of B
+        for (int kb = 0; kb < num_kb; kb++) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, args.status, ST_GEMM_TIMEOUT, 11);
+          if (!ok) break;
+          uint8_t* sa = smem + stage * C::STAGE_BYTES;
+          uint8_t* sb = sa + C::A_BYTES;
+          // bytes of both CTAs land on the leader's barrier
+          const uint32_t fb = smem_u32(&full_bar[stage]) & ~kPeerBit;
+          if (cta == 0) mbar_expect_tx(&full_bar[stage], 2 * C::STAGE_BYTES);
+          const int k0 = kb * C::BK;
+          const int ba = args.bcastA ? 0 : b, bb = args.bcastB ? 0 : b;
+          if (!A_MN) {
+            tma_load_3d_2sm(sa, &tmA, fb, k0, m0, ba);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 2; i++) tma_load_3d_2sm(sa + i * (C::BK * kSwizzleBytes), &tmA, fb, m0 + i * 64, k0, ba);
+          }
+          if (!B_MN) {
+            tma_load_3d_2sm(sb, &tmB, fb, k0, n0, bb);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 2; i++) tma_load_3d_2sm(sb + i * (C::BK * kSwizzleBytes), &tmB, fb, n0 + i * 64, k0, bb);
+          }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) { }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (cta == 0 && elect_one()) {
+      uint32_t id = make_idesc(1u, args.in_bf16 ? 1u : 0u, A_MN, B_MN, 256, 256);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t tphase[2] = {0, 0};
+      int local_tile = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs, local_tile++) {
+        const int buf = local_tile & 1;
+        ok = mbar_wait(&tempty_bar[buf], tphase[buf] ^ 1, abort_flag, args.status, ST_GEMM_TIMEOUT, 12);
+        if (!ok) break;
+        tphase[buf] ^= 1;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * 256;
+        for (int kb = 0; kb < num_kb; kb++) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, args.status, ST_GEMM_TIMEOUT, 13);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+          const uint32_t sb = sa + C::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < C::BK / C::UMMA_K; k++) {
+            const uint64_t adesc =
+                A_MN ? make_smem_desc_sw128(sa + k * C::UMMA_K * kSwizzleBytes, C::BK * kSwizzleBytes, 1024)
+                     : make_smem_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t bdesc =
+                B_MN ? make_smem_desc_sw128(sb + k * C::UMMA_K * kSwizzleBytes, C::BK * kSwizzleBytes, 1024)
+                     : make_smem_desc_sw128(sb + k * 32, 16, 1024);
+            tc_mma_f16_2sm(d_tmem, adesc, bdesc, id, (kb | k) != 0);
+          }
+          // free the stage in both CTAs
+          const uint32_t eb = smem_u32(&empty_bar[stage]);
+          tc_commit_2sm(eb);
+          tc_commit_2sm(eb | kPeerBit);
+          if (kb == num_kb - 1) {
+            const uint32_t tb = smem_u32(&tfull_bar[buf]);
+            tc_commit_2sm(tb);
+            tc_commit_2sm(tb | kPeerBit);
+          }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue: this CTA's 128 rows x 256 columns ----------------
+    const EpiCtx cx = make_epi_ctx<2>(args, warp, lane, threadIdx.x - 64, s_bias, s_qsw, s_qrs);
+    EpiStage est;
+    est.buf = smem + SL::OFF_STAGING + (warp - 2) * 2 * SL::kStageBuf;
+    est.bar = aux_bar + (warp - 2) * 2;
+    est.phase = 0;
+    uint32_t tphase[2] = {0, 0};
+    int local_tile = 0;
+    bool ok = true;
+    for (int t = pair; t < num_tiles && ok; t += num_pairs, local_tile++) {
+      const int buf = local_tile & 1;
+      const int b = t / tiles_per_batch;
+      const int r = t - b * tiles_per_batch;
+      int mb, nb;
+      tile_coords(r, args.num_m, args.num_n, args.group_m, mb, nb);
+      const int m0 = mb * 256 + (int)cta * 128, n0 = nb * 256;
+      bool done;
+      if (args.tma_epi)
+        done = epilogue_tile_tma<256, EW>(args, cx, est, &tmC, &tmX, buf, b, m0, n0, tmem_base + buf * 256,
+                                          &tfull_bar[buf], tphase[buf], abort_flag);
+      else
+        done = epilogue_tile<2, 256, EW>(args, cx, buf, b, m0, n0, tmem_base + buf * 256, &tfull_bar[buf],
+                                         tphase[buf], abort_flag);
+      if (!done) {
+        ok = false;
+        break;
+      }
+      tphase[buf] ^= 1;
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(smem_u32(&tempty_bar[buf]) & ~kPeerBit);
+    }
+    if (args.tma_epi && lane == 0) tma_store_wait<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // neither CTA leaves while the other may still use its memory or barriers
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_2sm(tmem_base, C::TMEM_COLS);
   }
 }
 
@@ -578,45 +1143,82 @@ __global__ void gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ 
 
 int g_epi_warps = 8;
 
+struct TMaps {
+  CUtensorMap a, b, c, x;  // operands, output, auxiliary tensor
+};
+
 template <int ESZ, bool A_MN, bool B_MN, int BN, int EW>
-int launch_tc_ew(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args, int num_sms,
-                 cudaStream_t stream) {
+int launch_tc_ew(const TMaps& tm, const GemmArgs& args, int num_sms, cudaStream_t stream) {
   using C = Cfg<ESZ, BN>;
+  using SL = SmemLayout<ESZ, C::RING_BYTES, EW>;
   auto kern = gemm_tcgen05_kernel<ESZ, A_MN, B_MN, BN, EW>;
   static bool configured = false;
   if (!configured) {
-    GB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    GB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SL::BYTES));
     configured = true;
   }
   int tiles = args.num_m * args.num_n * args.batch;
   int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, 64 + 32 * EW, C::SMEM_BYTES, stream>>>(tmA, tmB, args);
+  kern<<<grid, 64 + 32 * EW, SL::BYTES, stream>>>(tm.a, tm.b, tm.c, tm.x, args);
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;
 }
 
 template <int ESZ, bool A_MN, bool B_MN, int BN>
-int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args, int num_sms,
-              cudaStream_t stream) {
-  if (g_epi_warps == 4) return launch_tc_ew<ESZ, A_MN, B_MN, BN, 4>(tmA, tmB, args, num_sms, stream);
-  return launch_tc_ew<ESZ, A_MN, B_MN, BN, 8>(tmA, tmB, args, num_sms, stream);
+int launch_tc(const TMaps& tm, const GemmArgs& args, int num_sms, cudaStream_t stream) {
+  if (g_epi_warps == 4) return launch_tc_ew<ESZ, A_MN, B_MN, BN, 4>(tm, args, num_sms, stream);
+  return launch_tc_ew<ESZ, A_MN, B_MN, BN, 8>(tm, args, num_sms, stream);
 }
 
 template <int ESZ, int BN>
-int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB,
-                   const GemmArgs& args, int num_sms, cudaStream_t stream) {
-  if (!a_mn && !b_mn) return launch_tc<ESZ, false, false, BN>(tmA, tmB, args, num_sms, stream);
+int dispatch_major(bool a_mn, bool b_mn, const TMaps& tm, const GemmArgs& args, int num_sms,
+                   cudaStream_t stream) {
+  if (!a_mn && !b_mn) return launch_tc<ESZ, false, false, BN>(tm, args, num_sms, stream);
   if (ESZ == 2) {
-    if (!a_mn && b_mn) return launch_tc<2, false, true, BN>(tmA, tmB, args, num_sms, stream);
-    if (a_mn && !b_mn) return launch_tc<2, true, false, BN>(tmA, tmB, args, num_sms, stream);
-    return launch_tc<2, true, true, BN>(tmA, tmB, args, num_sms, stream);
+    if (!a_mn && b_mn) return launch_tc<2, false, true, BN>(tm, args, num_sms, stream);
+    if (a_mn && !b_mn) return launch_tc<2, true, false, BN>(tm, args, num_sms, stream);
+    return launch_tc<2, true, true, BN>(tm, args, num_sms, stream);
   }
   gbh::set_error("int8 GEMM supports only A (M,K) row-major with B (N,K) row-major");
   return gbh::E_BAD_ARG;
 }
 
+
+int g_use_2cta = 0;
+
+template <bool A_MN, bool B_MN>
+int launch_2cta(const TMaps& tm, const GemmArgs& args, int num_sms, cudaStream_t stream) {
+  using SL = SmemLayout<2, Cfg2::RING_BYTES, 8>;
+  auto kern = gemm_tcgen05_2cta_kernel<A_MN, B_MN, 8>;
+  static bool configured = false;
+  if (!configured) {
+    GB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SL::BYTES));
+    configured = true;
+  }
+  int tiles = args.num_m * args.num_n * args.batch;
+  int pairs = num_sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(64 + 32 * 8);
+  cfg.dynamicSmemBytes = SL::BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  GB_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tm.a, tm.b, tm.c, tm.x, args));
+  return gbh::E_OK;
+}
+
 int g_num_sms = 0;
 int g_group_m = 8;
+int g_pf_dist = 0;
+int g_tma_epi = 1;
 
 // Builds the two tensor maps and launches.  esz: 2 (bf16/fp16) or 1 (int8).
 int gemm_tc(int esz, const void* A, const void* B, GemmArgs& args, int transA, int transB,
@@ -642,15 +1244,52 @@ int gemm_tc(int esz, const void* A, const void* B, GemmArgs& args, int transA, i
     if (N <= 128 || tiles256 < g_num_sms) bn = 128;
   }
   if (force_bn == 128 || force_bn == 256) bn = force_bn;
-  args.num_m = (M + BM - 1) / BM;
-  args.num_n = (N + bn - 1) / bn;
+  // two-CTA 256 x 256 tiles when they can fill the GPU (force_bn == 512 forces them)
+  bool use2 = false;
+  if (esz == 2) {
+    long long pair_tiles = (long long)((M + 255) / 256) * ((N + 255) / 256) * batch;
+    use2 = force_bn == 512 || (force_bn == 0 && g_use_2cta && pair_tiles >= g_num_sms / 2 && M >= 256 && N >= 256);
+  }
+  if (use2) bn = 128;   // each CTA of a pair stages 128 of the tile's 256 columns
+  args.num_m = use2 ? (M + 255) / 256 : (M + BM - 1) / BM;
+  args.num_n = use2 ? (N + 255) / 256 : (N + bn - 1) / bn;
   args.status = gbh::status_ptr();
   args.group_m = g_group_m;
+  args.pf_dist = g_pf_dist;
 
   CUtensorMapDataType dt = esz == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                     : (args.in_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                     : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
-  CUtensorMap tmA, tmB;
+  TMaps tm;
+  memset(&tm, 0, sizeof(tm));
+  CUtensorMap& tmA = tm.a;
+  CUtensorMap& tmB = tm.b;
+  // Results of 16-bit kernels leave through shared memory and TMA stores when the output
+  // (and the auxiliary tensor) can be described by a tensor map and nothing is accumulated.
+  args.tma_epi = 0;
+  if (esz == 2 && g_tma_epi && args.out_kind != OUT_F32 && !args.beta) {
+    auto mappable = [&](const void* p, long long ld, long long bs) {
+      return (((uintptr_t)p & 15) == 0) && (ld % 8 == 0) && (batch == 1 || bs % 8 == 0);
+    };
+    bool ok = mappable(args.C, args.ldc, args.strideC) &&
+              (args.aux_mode == AUX_NONE || mappable(args.aux, args.ldaux, args.strideAux));
+    if (ok) {
+      auto encode_out = [&](CUtensorMap* m, const void* p, long long ld, long long bs) {
+        uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)batch};
+        uint64_t strides[2] = {(uint64_t)ld * 2, (uint64_t)(batch > 1 ? bs : (long long)M * ld) * 2};
+        uint32_t box[3] = {32, 32, 1};
+        return gbh::encode_tmap(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, p, dims, strides, box,
+                                CU_TENSOR_MAP_SWIZZLE_64B);
+      };
+      int rc = encode_out(&tm.c, args.C, args.ldc, args.strideC);
+      if (rc) return rc;
+      if (args.aux_mode != AUX_NONE) {
+        rc = encode_out(&tm.x, args.aux, args.ldaux, args.strideAux);
+        if (rc) return rc;
+      }
+      args.tma_epi = 1;
+    }
+  }
   {
     uint64_t dims[3], strides[2];
     uint32_t box[3];
@@ -685,20 +1324,37 @@ int gemm_tc(int esz, const void* A, const void* B, GemmArgs& args, int transA, i
     int rc = gbh::encode_tmap(&tmB, dt, 3, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   }
-  if (esz == 2) {
-    if (bn == 256) return dispatch_major<2, 256>(a_mn, b_mn, tmA, tmB, args, g_num_sms, stream);
-    return dispatch_major<2, 128>(a_mn, b_mn, tmA, tmB, args, g_num_sms, stream);
+  if (use2) {
+    if (!a_mn && !b_mn) return launch_2cta<false, false>(tm, args, g_num_sms, stream);
+    if (!a_mn && b_mn) return launch_2cta<false, true>(tm, args, g_num_sms, stream);
+    if (a_mn && !b_mn) return launch_2cta<true, false>(tm, args, g_num_sms, stream);
+    return launch_2cta<true, true>(tm, args, g_num_sms, stream);
   }
-  if (bn == 256) return dispatch_major<1, 256>(a_mn, b_mn, tmA, tmB, args, g_num_sms, stream);
-  return dispatch_major<1, 128>(a_mn, b_mn, tmA, tmB, args, g_num_sms, stream);
+  if (esz == 2) {
+    if (bn == 256) return dispatch_major<2, 256>(a_mn, b_mn, tm, args, g_num_sms, stream);
+    return dispatch_major<2, 128>(a_mn, b_mn, tm, args, g_num_sms, stream);
+  }
+  if (bn == 256) return dispatch_major<1, 256>(a_mn, b_mn, tm, args, g_num_sms, stream);
+  return dispatch_major<1, 128>(a_mn, b_mn, tm, args, g_num_sms, stream);
 }
 
 }  // namespace
 
 // Tuning knobs: epilogue warps (4 or 8) and rasterisation group height (row blocks).
-GB_EXPORT int gb_gemm_tune(int epi_warps, int group_m) {
+GB_EXPORT int gb_gemm_tune(int epi_warps, int group_m, int pf_dist) {
   if (epi_warps == 4 || epi_warps == 8) g_epi_warps = epi_warps;
   if (group_m >= 1) g_group_m = group_m;
+  if (pf_dist >= 0) g_pf_dist = pf_dist;
+  return 0;
+}
+// Enables (1) or disables (0) the automatic choice of the two-CTA kernel.
+GB_EXPORT int gb_gemm_use_2cta(int on) {
+  g_use_2cta = on;
+  return 0;
+}
+// Enables (1) or disables (0) the shared-memory + TMA-store epilogue of the 16-bit kernels.
+GB_EXPORT int gb_gemm_tma_epilogue(int on) {
+  g_tma_epi = on;
   return 0;
 }
 

@@ -1,6 +1,6 @@
 """Small, self-contained workloads for profiling one kernel at a time.
 
-    python -m gonn_b200.utils.profile_cases gemm 4096 4096 4096 [nt|nn|tn] [bias_gelu]
+    python -m gonn_b200.utils.profile_cases gemm 4096 4096 4096 [nt|nn|tn] [bias_gelu|bias_res|pair]
     python -m gonn_b200.utils.profile_cases flash_fwd 4 2048 16 128 [causal]
     python -m gonn_b200.utils.profile_cases flash_bwd 4 2048 16 128 [causal]
     python -m gonn_b200.utils.profile_cases norm 16384 768
@@ -54,6 +54,10 @@ def main(argv):
         elif epi == "bias_res":
             kw = dict(bias=torch.randn(N, device=dev, dtype=torch.bfloat16),
                       aux=torch.randn(M, N, device=dev, dtype=torch.bfloat16), aux_mode="add")
+        elif epi == "noload":
+            lib.lib().gb_gemm_tune(8, 8, 999)
+        elif epi == "pair":
+            kw = dict(force_bn=512)  # the two-CTA (256 x 256 per SM pair) kernel
         ms = _time(lambda: gemm(a, b, trans_a=ta, trans_b=tb, out=out, **kw))
         print(f"gemm {M}x{N}x{K} {layout} {epi}: {ms:.4f} ms, {2 * M * N * K / ms / 1e9:.1f} TFLOP/s")
     elif kind in ("flash_fwd", "flash_bwd"):
