@@ -1184,7 +1184,7 @@ int dispatch_major(bool a_mn, bool b_mn, const TMaps& tm, const GemmArgs& args, 
 }
 
 
-int g_use_2cta = 0;
+int g_use_2cta = 1;
 
 template <bool A_MN, bool B_MN>
 int launch_2cta(const TMaps& tm, const GemmArgs& args, int num_sms, cudaStream_t stream) {
@@ -1248,7 +1248,11 @@ int gemm_tc(int esz, const void* A, const void* B, GemmArgs& args, int transA, i
   bool use2 = false;
   if (esz == 2) {
     long long pair_tiles = (long long)((M + 255) / 256) * ((N + 255) / 256) * batch;
-    use2 = force_bn == 512 || (force_bn == 0 && g_use_2cta && pair_tiles >= g_num_sms / 2 && M >= 256 && N >= 256);
+    // measured: the pair kernel wins when the main loop dominates (long K, or a plain
+    // epilogue); with short K and a heavy epilogue the one-CTA kernel is slightly ahead
+    const bool light = args.act == ACT_NONE && args.aux_mode == AUX_NONE;
+    use2 = force_bn == 512 || (force_bn == 0 && g_use_2cta && pair_tiles >= g_num_sms / 2 && M >= 256 &&
+                               N >= 256 && (K >= 1536 || light));
   }
   if (use2) bn = 128;   // each CTA of a pair stages 128 of the tile's 256 columns
   args.num_m = use2 ? (M + 255) / 256 : (M + BM - 1) / BM;
