@@ -45,7 +45,15 @@ struct AttnArgs {
   long long dk_sb, dk_ss, dk_sh;
   long long dv_sb, dv_ss, dv_sh;
   int* status;
+  // optional timeline of CTA (0,0,0) of the dK/dV kernel: [3 lanes][kTraceSlots] SM clock stamps
+  long long* trace;
 };
+
+constexpr int kTraceSlots = 512;
+// lane: 0 = MMA thread, 1 / 2 = first warp of elementwise group 0 / 1
+__device__ __forceinline__ void trace_stamp(long long* trace, int lane_id, int& n) {
+  if (trace && n < kTraceSlots) trace[lane_id * kTraceSlots + n++] = clock64();
+}
 
 __device__ __forceinline__ uint32_t pack16(float a, float b, int bf) {
   return bf ? pack_bf16(a, b) : pack_f16(a, b);
@@ -352,32 +360,50 @@ __global__ void fa_delta_kernel(const T* __restrict__ O, const T* __restrict__ d
 // ---------------------------------------------------------------------------
 // Backward
 // ---------------------------------------------------------------------------
-constexpr int kBwdThreads = 192;
+constexpr int kBwdEW = 16;                       // elementwise warps: two groups of eight
+constexpr int kBwdThreads = 64 + kBwdEW * 32;    // + TMA warp and MMA warp
+constexpr int BSUB = 64;                  // rows of one streamed sub-tile
 
+// Backward tiling.  The resident operand pair is a 128-row tile; the streamed pair comes in
+// 64-row sub-tiles through a ring of NS stages.  Scores and dP of a sub-tile are 128 x 64
+// fp32 blocks in TMEM, double buffered, so the tensor core computes sub-tile i+1 (and the
+// accumulations of sub-tile i-1) while the elementwise warps work on sub-tile i.  The
+// elementwise warps form two groups of eight; group g owns TMEM buffer g and every second
+// sub-tile, so the TMEM round trips of one group hide behind the arithmetic of the other.
 template <int HD>
 struct BwdCfg {
   static constexpr int CH = HD / 64;
   static constexpr int TILE_BYTES = CH * 128 * 128;
-  // resident pair (K,V or Q,dO) + 2-stage ring of the streamed pair
-  static constexpr int SMEM_BYTES = TILE_BYTES * (2 + 2 * 2) + 2 * 2 * 128 * 4 + 1024 + 256;
+  static constexpr int SUB_BYTES = CH * BSUB * 128;
+  static constexpr int NS = 4;
+  static constexpr int STAT_BYTES = NS * 2 * BSUB * 4;  // per stage: 64 x LSE*log2(e), 64 x Delta*scale
+  static constexpr int SMEM_BYTES = 2 * TILE_BYTES + NS * 2 * SUB_BYTES + STAT_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int COL_S = 0, COL_DP = 128, COL_ACC0 = 256, COL_ACC1 = 384;
+  // buffer b: scores at b*128, dP at b*128 + 64; accumulators behind them
+  static constexpr int COL_ACC0 = 256, COL_ACC1 = 256 + HD;
 };
-
-__device__ __forceinline__ void named_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // K-major operand descriptor for step k (16 columns) of a [128 x HD] tile
 __device__ __forceinline__ uint64_t kdesc(uint32_t base, int k) {
   return make_smem_desc_sw128(base + (k / 4) * (128 * 128) + (k % 4) * 32, 16, 1024);
 }
-// MN-major operand descriptor for step k (16 rows) of a [128 rows x HD] tile
-__device__ __forceinline__ uint64_t mndesc(uint32_t base, int k) {
-  return make_smem_desc_sw128(base + k * 16 * 128, 128 * 128, 1024);
+// the same for a [64 x HD] sub-tile (64-column chunks are 64 rows apart)
+__device__ __forceinline__ uint64_t kdesc_sub(uint32_t base, int k) {
+  return make_smem_desc_sw128(base + (k / 4) * (BSUB * 128) + (k % 4) * 32, 16, 1024);
+}
+// MN-major operand descriptor for step k (16 rows) of a [64 rows x HD] sub-tile
+__device__ __forceinline__ uint64_t mndesc_sub(uint32_t base, int k) {
+  return make_smem_desc_sw128(base + k * 16 * 128, BSUB * 128, 1024);
 }
 
-// dK / dV: one CTA per key tile; streams the query tiles.  Works in the
+template <bool BF>
+__device__ __forceinline__ uint32_t pack16t(float a, float b) {
+  return BF ? pack_bf16(a, b) : pack_f16(a, b);
+}
+
+// dK / dV: one CTA per 128-key tile; streams 64-row query sub-tiles.  Works in the
 // transposed domain (rows = keys) so that P^T and dS^T are A operands in TMEM.
-template <int HD>
+template <int HD, bool BF>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -387,32 +413,32 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sK = smem;
   uint8_t* sV = sK + C::TILE_BYTES;
-  uint8_t* sQ = sV + C::TILE_BYTES;        // [2]
-  uint8_t* sdO = sQ + 2 * C::TILE_BYTES;   // [2]
-  float* sLSE = (float*)(sdO + 2 * C::TILE_BYTES);  // [2][128]
-  float* sDelta = sLSE + 2 * 128;                   // [2][128]
-  uint64_t* bars = (uint64_t*)(sDelta + 2 * 128);
-  uint64_t* kv_full = bars;       // 1
-  uint64_t* q_full = bars + 1;    // 2
-  uint64_t* q_empty = bars + 3;   // 2
-  uint64_t* sdp_full = bars + 5;  // 1
-  uint64_t* p_full = bars + 6;    // 1
-  uint64_t* acc_done = bars + 7;  // 1
-  uint32_t* tmem_slot = (uint32_t*)(bars + 8);
+  uint8_t* ring = sV + C::TILE_BYTES;  // [NS] x {Q sub-tile, dO sub-tile}
+  float* sStat = (float*)(ring + C::NS * 2 * C::SUB_BYTES);  // [NS][2][64]
+  uint64_t* bars = (uint64_t*)((uint8_t*)sStat + C::STAT_BYTES);
+  uint64_t* kv_full = bars;                 // 1
+  uint64_t* q_full = bars + 1;              // NS
+  uint64_t* q_empty = q_full + C::NS;       // NS
+  uint64_t* sdp_full = q_empty + C::NS;     // 2
+  uint64_t* p_full = sdp_full + 2;          // 2
+  uint64_t* acc_done = p_full + 2;          // 1
+  uint32_t* tmem_slot = (uint32_t*)(acc_done + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kv_tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int kv0 = kv_tile * BKV;
-  const int num_q_tiles = (args.Sq + BQ - 1) / BQ;
-  const int i_begin = args.causal ? kv_tile : 0;
-  const int n_it = num_q_tiles - i_begin;
+  const int num_sub = (args.Sq + BSUB - 1) / BSUB;
+  const int i_begin = args.causal ? kv_tile * (BKV / BSUB) : 0;
+  const int n_it = max(num_sub - i_begin, 0);
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; i++) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
-    mbar_init(sdp_full, 1);
-    mbar_init(p_full, 128);
+    for (int i = 0; i < C::NS; i++) {
+      mbar_init(&q_full[i], 1 + 32);  // the TMA transaction + the 32 lanes that stage the row statistics
+      mbar_init(&q_empty[i], 1);
+    }
+    for (int i = 0; i < 2; i++) { mbar_init(&sdp_full[i], 1); mbar_init(&p_full[i], 8); }
     mbar_init(acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -424,6 +450,7 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
+    // ---- producer: TMA for the tiles (lane 0), row statistics by all lanes ----
     if (lane == 0) {
       mbar_expect_tx(kv_full, 2 * C::TILE_BYTES);
 #pragma unroll
@@ -431,150 +458,198 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tma_load_4d(sK + c * 128 * 128, &tmK, kv_full, c * 64, kv0, h, b);
         tma_load_4d(sV + c * 128 * 128, &tmV, kv_full, c * 64, kv0, h, b);
       }
-      for (int it = 0; it < n_it; it++) {
-        const int st = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(&q_empty[st], ph ^ 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 11)) break;
-        mbar_expect_tx(&q_full[st], 2 * C::TILE_BYTES);
-        const int q0 = (i_begin + it) * BQ;
+    }
+    const float* stat_g = (lane < 16 ? args.LSE : args.Delta) + ((long long)b * args.H + h) * args.Sq;
+    const bool vec = (args.Sq & 3) == 0;
+    int st = 0;
+    uint32_t ph = 0;
+    for (int it = 0; it < n_it; it++) {
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait(&q_empty[st], ph ^ 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 11);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      const int q0 = (i_begin + it) * BSUB;
+      if (lane == 0) {
+        mbar_expect_tx(&q_full[st], 2 * C::SUB_BYTES);
+        uint8_t* sQ = ring + st * 2 * C::SUB_BYTES;
+        uint8_t* sdO = sQ + C::SUB_BYTES;
 #pragma unroll
         for (int c = 0; c < C::CH; c++) {
-          tma_load_4d(sQ + st * C::TILE_BYTES + c * 128 * 128, &tmQ, &q_full[st], c * 64, q0, h, b);
-          tma_load_4d(sdO + st * C::TILE_BYTES + c * 128 * 128, &tmdO, &q_full[st], c * 64, q0, h, b);
+          tma_load_4d(sQ + c * BSUB * 128, &tmQ, &q_full[st], c * 64, q0, h, b);
+          tma_load_4d(sdO + c * BSUB * 128, &tmdO, &q_full[st], c * 64, q0, h, b);
         }
       }
+      // lanes 0-15: LSE * log2(e) (rows past the end and fully masked rows read +inf, so
+      // their probabilities come out 0); lanes 16-31: Delta * scale
+      const int qs = q0 + (lane & 15) * 4;
+      float4 t;
+      if (vec && qs + 4 <= args.Sq) {
+        t = __ldg(reinterpret_cast<const float4*>(stat_g + qs));
+      } else {
+        const float fill = lane < 16 ? INFINITY : 0.f;
+        t.x = qs < args.Sq ? __ldg(stat_g + qs) : fill;
+        t.y = qs + 1 < args.Sq ? __ldg(stat_g + qs + 1) : fill;
+        t.z = qs + 2 < args.Sq ? __ldg(stat_g + qs + 2) : fill;
+        t.w = qs + 3 < args.Sq ? __ldg(stat_g + qs + 3) : fill;
+      }
+      if (lane < 16) {
+        const float k = 1.4426950408889634f;
+        t.x = t.x == -INFINITY ? INFINITY : t.x * k;
+        t.y = t.y == -INFINITY ? INFINITY : t.y * k;
+        t.z = t.z == -INFINITY ? INFINITY : t.z * k;
+        t.w = t.w == -INFINITY ? INFINITY : t.w * k;
+      } else {
+        t.x *= args.scale; t.y *= args.scale; t.z *= args.scale; t.w *= args.scale;
+      }
+      *reinterpret_cast<float4*>(sStat + st * 128 + lane * 4) = t;
+      mbar_arrive(&q_full[st]);
+      if (++st == C::NS) { st = 0; ph ^= 1; }
     }
   } else if (warp == 1) {
-    const uint32_t fmt = args.in_bf16 ? 1u : 0u;
-    const uint32_t idesc_s = make_idesc(1u, fmt, false, false, 128, 128);
-    const uint32_t idesc_acc = make_idesc(1u, fmt, false, true, 128, HD);
-    bool ok = mbar_wait(kv_full, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 12);
-    for (int it = 0; it < n_it && ok; it++) {
-      const int st = it & 1;
-      const uint32_t ph = (it >> 1) & 1;
-      ok = mbar_wait(&q_full[st], ph, abort_flag, args.status, ST_ATTN_TIMEOUT, 13);
-      if (!ok) break;
-      tc_fence_after();
+    if (elect_one()) {
+      const uint32_t fmt = BF ? 1u : 0u;
+      const uint32_t idesc_s = make_idesc(1u, fmt, false, false, 128, BSUB);
+      const uint32_t idesc_acc = make_idesc(1u, fmt, false, true, 128, HD);
       const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
-      const uint32_t qa = smem_u32(sQ + st * C::TILE_BYTES), ga = smem_u32(sdO + st * C::TILE_BYTES);
-      if (lane == 0) {
+      bool ok = mbar_wait(kv_full, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 12);
+      int st_s = 0;        // ring stage of the next S / dP issue
+      uint32_t ph_s = 0;
+      auto issue_sdp = [&](int it) {
+        if (!mbar_wait(&q_full[st_s], ph_s, abort_flag, args.status, ST_ATTN_TIMEOUT, 13)) return false;
+        tc_fence_after();
+        const uint32_t qa = smem_u32(ring + st_s * 2 * C::SUB_BYTES), ga = qa + C::SUB_BYTES;
+        const uint32_t d = tmem_base + (it & 1) * 128;
+        // two independent accumulation chains, interleaved so that an MMA never has to wait
+        // for the one just before it
 #pragma unroll
-        for (int k = 0; k < HD / 16; k++)  // S^T = K Q^T
-          tc_mma_f16(tmem_base + C::COL_S, kdesc(ka, k), kdesc(qa, k), idesc_s, k != 0);
+        for (int k = 0; k < HD / 16; k++) {
+          tc_mma_f16(d, kdesc(ka, k), kdesc_sub(qa, k), idesc_s, k != 0);       // S^T = K Q^T
+          tc_mma_f16(d + 64, kdesc(va, k), kdesc_sub(ga, k), idesc_s, k != 0);  // dP^T = V dO^T
+        }
+        tc_commit(&sdp_full[it & 1]);
+        if (++st_s == C::NS) { st_s = 0; ph_s ^= 1; }
+        return true;
+      };
+      long long* tr = (blockIdx.x | blockIdx.y | blockIdx.z) == 0 ? args.trace : nullptr;
+      int ntr = 0;
+      trace_stamp(tr, 0, ntr);
+      if (ok && n_it > 0) ok = issue_sdp(0);
+      int st = 0;
+      for (int it = 0; it < n_it && ok; it++) {
+        if (it + 1 < n_it) {
+          ok = issue_sdp(it + 1);
+          if (!ok) break;
+        }
+        trace_stamp(tr, 0, ntr);  // S / dP of the next sub-tile issued
+        const int bb = it & 1;
+        ok = mbar_wait(&p_full[bb], (it >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 14);
+        if (!ok) break;
+        trace_stamp(tr, 0, ntr);  // P / dS of this sub-tile ready
+        tc_fence_after();
+        const uint32_t qa = smem_u32(ring + st * 2 * C::SUB_BYTES), ga = qa + C::SUB_BYTES;
+        const uint32_t pt = tmem_base + bb * 128;
+        // each elementwise warp left 16 packed columns at the start of its own 32-column
+        // range, so MMA step k reads from (k / 2) * 32 + (k % 2) * 8
 #pragma unroll
-        for (int k = 0; k < HD / 16; k++)  // dP^T = V dO^T
-          tc_mma_f16(tmem_base + C::COL_DP, kdesc(va, k), kdesc(ga, k), idesc_s, k != 0);
-        tc_commit(sdp_full);
-      }
-      __syncwarp();
-      ok = mbar_wait(p_full, it & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 14);
-      if (!ok) break;
-      tc_fence_after();
-      if (lane == 0) {
-#pragma unroll
-        for (int k = 0; k < BQ / 16; k++)  // dV += P^T dO
-          tc_mma_f16_ts(tmem_base + C::COL_ACC0, tmem_base + C::COL_S + k * 8, mndesc(ga, k),
-                        idesc_acc, (it | k) != 0);
-#pragma unroll
-        for (int k = 0; k < BQ / 16; k++)  // dK += dS^T Q
-          tc_mma_f16_ts(tmem_base + C::COL_ACC1, tmem_base + C::COL_DP + k * 8, mndesc(qa, k),
-                        idesc_acc, (it | k) != 0);
+        for (int k = 0; k < BSUB / 16; k++) {
+          tc_mma_f16_ts(tmem_base + C::COL_ACC0, pt + (k >> 1) * 32 + (k & 1) * 8, mndesc_sub(ga, k), idesc_acc,
+                        (it | k) != 0);  // dV += P^T dO
+          tc_mma_f16_ts(tmem_base + C::COL_ACC1, pt + 64 + (k >> 1) * 32 + (k & 1) * 8, mndesc_sub(qa, k),
+                        idesc_acc, (it | k) != 0);  // dK += dS^T Q
+        }
         tc_commit(&q_empty[st]);
         if (it == n_it - 1) tc_commit(acc_done);
+        if (++st == C::NS) st = 0;
       }
-      __syncwarp();
     }
+    __syncwarp();
   } else {
+    const int e = warp - 2;
+    const int group = e >> 3;                // sub-tiles it with (it & 1) == group, TMEM buffer `group`
+    const int half = (e >> 2) & 1;           // which 32 of the sub-tile's 64 query columns
     const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;  // key row inside the tile
+    const int r = quarter * 32 + lane;       // key row inside the tile
     const int kvrow = kv0 + r;
-    const int t = (warp - 2) * 32 + lane;  // 0..127, loader index for LSE / Delta
+    const bool row_dead = kvrow >= args.Sk;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    const float* lse_g = args.LSE + ((long long)b * args.H + h) * args.Sq;
-    const float* dl_g = args.Delta + ((long long)b * args.H + h) * args.Sq;
+    const uint32_t my = lane_addr + group * 128 + half * 32;
     bool ok = true;
-    for (int it = 0; it < n_it; it++) {
-      const int q0 = (i_begin + it) * BQ;
-      const int pb = it & 1;
-      {
-        const int q = q0 + t;
-        float lv = INFINITY, dv = 0.f;
-        if (q < args.Sq) {
-          lv = lse_g[q] * 1.4426950408889634f;
-          dv = dl_g[q];
-          if (lv == -INFINITY) lv = INFINITY;
-        }
-        sLSE[pb * 128 + t] = lv;
-        sDelta[pb * 128 + t] = dv;
-      }
-      named_sync_128();
-      ok = mbar_wait(sdp_full, it & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 15);
+    long long* tr = ((blockIdx.x | blockIdx.y | blockIdx.z) == 0 && (e & 7) == 0 && lane == 0) ? args.trace : nullptr;
+    int ntr = 0;
+    for (int it = group; it < n_it; it += 2) {
+      const int st = it % C::NS;
+      trace_stamp(tr, 1 + group, ntr);  // starts waiting
+      ok = mbar_wait(&q_full[st], (it / C::NS) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 17);
       if (!ok) break;
+      ok = mbar_wait(&sdp_full[group], (it >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 15);
+      if (!ok) break;
+      trace_stamp(tr, 1 + group, ntr);  // scores ready
       tc_fence_after();
-      float p[BQ];
-      const bool diag = args.causal && (i_begin + it) == kv_tile;
+      uint32_t rs[32], rd[32];
+      tmem_ld32(my, rs);
+      tmem_ld32(my + 64, rd);
+      const float4* l4 = reinterpret_cast<const float4*>(sStat + st * 128 + half * 32);
+      const float4* d4 = reinterpret_cast<const float4*>(sStat + st * 128 + 64 + half * 32);
+      tmem_ld_wait();
+      trace_stamp(tr, 1 + group, ntr);  // loaded
+      const int q0 = (i_begin + it) * BSUB + half * 32;  // first query column of this thread
+      const bool masked = row_dead || (args.causal && it < BKV / BSUB);  // warp-uniform except row_dead
+      uint32_t pp[16], pd[16];
 #pragma unroll
-      for (int c = 0; c < BQ / 32; c++) {
-        uint32_t rr[32];
-        tmem_ld32(lane_addr + C::COL_S + c * 32, rr);
-        tmem_ld_wait();
+      for (int g = 0; g < 8; g++) {
+        const float4 l = l4[g], d = d4[g];
+        const float ls[4] = {l.x, l.y, l.z, l.w};
+        const float ds[4] = {d.x, d.y, d.z, d.w};
+        float p[4], q[4];
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
-          const int qc = c * 32 + i;
-          float v = exp2f(__uint_as_float(rr[i]) * args.scale_log2 - sLSE[pb * 128 + qc]);
-          if (kvrow >= args.Sk || (diag && kvrow > q0 + qc)) v = 0.f;
-          p[qc] = v;
+        for (int u = 0; u < 4; u++) {
+          const int j = 4 * g + u;
+          p[u] = exp2f(fmaf(__uint_as_float(rs[j]), args.scale_log2, -ls[u]));
+          if (masked && (row_dead || kvrow > q0 + j)) p[u] = 0.f;
+          q[u] = p[u] * fmaf(__uint_as_float(rd[j]), args.scale, -ds[u]);
         }
+        pp[2 * g] = pack16t<BF>(p[0], p[1]);
+        pp[2 * g + 1] = pack16t<BF>(p[2], p[3]);
+        pd[2 * g] = pack16t<BF>(q[0], q[1]);
+        pd[2 * g + 1] = pack16t<BF>(q[2], q[3]);
       }
-#pragma unroll
-      for (int c = 0; c < BQ / 32; c++) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; i++) pk[i] = pack16(p[c * 32 + 2 * i], p[c * 32 + 2 * i + 1], args.in_bf16);
-        tmem_st16(lane_addr + C::COL_S + c * 16, pk);
-      }
-#pragma unroll
-      for (int c = 0; c < BQ / 32; c++) {
-        uint32_t rr[32];
-        tmem_ld32(lane_addr + C::COL_DP + c * 32, rr);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i++) {
-          const int qc = c * 32 + i;
-          p[qc] = p[qc] * (__uint_as_float(rr[i]) - sDelta[pb * 128 + qc]) * args.scale;
-        }
-      }
-      // all of dP^T has been read (above) before its columns are overwritten
-#pragma unroll
-      for (int c = 0; c < BQ / 32; c++) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; i++) pk[i] = pack16(p[c * 32 + 2 * i], p[c * 32 + 2 * i + 1], args.in_bf16);
-        tmem_st16(lane_addr + C::COL_DP + c * 16, pk);
-      }
+      // each warp overwrites only columns it has read itself
+      trace_stamp(tr, 1 + group, ntr);  // computed
+      tmem_st16(my, pp);
+      tmem_st16(my + 64, pd);
       tmem_st_wait();
+      trace_stamp(tr, 1 + group, ntr);  // stored
       tc_fence_before();
-      mbar_arrive(p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[group]);
     }
     if (ok && n_it > 0) ok = mbar_wait(acc_done, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 16);
     if (ok) {
       tc_fence_after();
-      const bool row_ok = kvrow < args.Sk;
-      uint16_t* dvrow = (uint16_t*)args.dV + (long long)b * args.dv_sb + (long long)kvrow * args.dv_ss + (long long)h * args.dv_sh;
-      uint16_t* dkrow = (uint16_t*)args.dK + (long long)b * args.dk_sb + (long long)kvrow * args.dk_ss + (long long)h * args.dk_sh;
-#pragma unroll
-      for (int c = 0; c < HD / 32; c++) {
-        uint32_t rr[32];
-        float v[32];
-        if (n_it > 0) { tmem_ld32(lane_addr + C::COL_ACC0 + c * 32, rr); tmem_ld_wait(); }
-#pragma unroll
-        for (int i = 0; i < 32; i++) v[i] = n_it > 0 ? __uint_as_float(rr[i]) : 0.f;
-        if (row_ok) store_row16<32>(dvrow + c * 32, v, args.in_bf16);
-        if (n_it > 0) { tmem_ld32(lane_addr + C::COL_ACC1 + c * 32, rr); tmem_ld_wait(); }
-#pragma unroll
-        for (int i = 0; i < 32; i++) v[i] = n_it > 0 ? __uint_as_float(rr[i]) : 0.f;
-        if (row_ok) store_row16<32>(dkrow + c * 32, v, args.in_bf16);
+      constexpr int W = HD / 4;  // columns of dV / dK per warp
+      const int cw = (group * 2 + half) * W;
+      uint16_t* dvrow = (uint16_t*)args.dV + (long long)b * args.dv_sb + (long long)kvrow * args.dv_ss +
+                        (long long)h * args.dv_sh + cw;
+      uint16_t* dkrow = (uint16_t*)args.dK + (long long)b * args.dk_sb + (long long)kvrow * args.dk_ss +
+                        (long long)h * args.dk_sh + cw;
+      uint32_t ra[W], rb[W];
+      float v[W];
+      if (n_it > 0) {
+        if constexpr (W == 32) {
+          tmem_ld32(lane_addr + C::COL_ACC0 + cw, ra);
+          tmem_ld32(lane_addr + C::COL_ACC1 + cw, rb);
+        } else {
+          tmem_ld16(lane_addr + C::COL_ACC0 + cw, ra);
+          tmem_ld16(lane_addr + C::COL_ACC1 + cw, rb);
+        }
+        tmem_ld_wait();
       }
+#pragma unroll
+      for (int i = 0; i < W; i++) v[i] = n_it > 0 ? __uint_as_float(ra[i]) : 0.f;
+      if (!row_dead) store_row16<W>(dvrow, v, BF);
+#pragma unroll
+      for (int i = 0; i < W; i++) v[i] = n_it > 0 ? __uint_as_float(rb[i]) : 0.f;
+      if (!row_dead) store_row16<W>(dkrow, v, BF);
     }
   }
   tc_fence_before();
@@ -582,8 +657,8 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, C::TMEM_COLS); }
 }
 
-// dQ: one CTA per query tile; streams the key tiles.
-template <int HD>
+// dQ: one CTA per 128-row query tile; streams 64-row key sub-tiles.
+template <int HD, bool BF>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -593,16 +668,15 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
   uint8_t* sdO = sQ + C::TILE_BYTES;
-  uint8_t* sK = sdO + C::TILE_BYTES;      // [2]
-  uint8_t* sV = sK + 2 * C::TILE_BYTES;   // [2]
-  uint64_t* bars = (uint64_t*)(sV + 2 * C::TILE_BYTES + 2 * 2 * 128 * 4);
-  uint64_t* q_full = bars;        // 1
-  uint64_t* kv_full = bars + 1;   // 2
-  uint64_t* kv_empty = bars + 3;  // 2
-  uint64_t* sdp_full = bars + 5;  // 1
-  uint64_t* p_full = bars + 6;    // 1
-  uint64_t* acc_done = bars + 7;  // 1
-  uint32_t* tmem_slot = (uint32_t*)(bars + 8);
+  uint8_t* ring = sdO + C::TILE_BYTES;  // [NS] x {K sub-tile, V sub-tile}
+  uint64_t* bars = (uint64_t*)(ring + C::NS * 2 * C::SUB_BYTES + C::STAT_BYTES);
+  uint64_t* q_full = bars;                  // 1
+  uint64_t* kv_full = bars + 1;             // NS
+  uint64_t* kv_empty = kv_full + C::NS;     // NS
+  uint64_t* sdp_full = kv_empty + C::NS;    // 2
+  uint64_t* p_full = sdp_full + 2;          // 2
+  uint64_t* acc_done = p_full + 2;          // 1
+  uint32_t* tmem_slot = (uint32_t*)(acc_done + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -610,14 +684,13 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int q_tile = args.causal ? (num_q_tiles - 1 - (int)blockIdx.x) : (int)blockIdx.x;
   const int h = blockIdx.y, b = blockIdx.z;
   const int q0 = q_tile * BQ;
-  int n_kv = (args.Sk + BKV - 1) / BKV;
-  if (args.causal) n_kv = min(n_kv, q_tile + 1);
+  int n_sub = (args.Sk + BSUB - 1) / BSUB;
+  if (args.causal) n_sub = min(n_sub, (q_tile + 1) * (BQ / BSUB));
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
-    mbar_init(sdp_full, 1);
-    mbar_init(p_full, 128);
+    for (int i = 0; i < C::NS; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 2; i++) { mbar_init(&sdp_full[i], 1); mbar_init(&p_full[i], 8); }
     mbar_init(acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -629,129 +702,138 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (elect_one()) {
       mbar_expect_tx(q_full, 2 * C::TILE_BYTES);
 #pragma unroll
       for (int c = 0; c < C::CH; c++) {
         tma_load_4d(sQ + c * 128 * 128, &tmQ, q_full, c * 64, q0, h, b);
         tma_load_4d(sdO + c * 128 * 128, &tmdO, q_full, c * 64, q0, h, b);
       }
-      for (int j = 0; j < n_kv; j++) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+      int st = 0;
+      uint32_t ph = 0;
+      for (int j = 0; j < n_sub; j++) {
         if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 21)) break;
-        mbar_expect_tx(&kv_full[st], 2 * C::TILE_BYTES);
+        mbar_expect_tx(&kv_full[st], 2 * C::SUB_BYTES);
+        uint8_t* sK = ring + st * 2 * C::SUB_BYTES;
+        uint8_t* sV = sK + C::SUB_BYTES;
 #pragma unroll
         for (int c = 0; c < C::CH; c++) {
-          tma_load_4d(sK + st * C::TILE_BYTES + c * 128 * 128, &tmK, &kv_full[st], c * 64, j * BKV, h, b);
-          tma_load_4d(sV + st * C::TILE_BYTES + c * 128 * 128, &tmV, &kv_full[st], c * 64, j * BKV, h, b);
+          tma_load_4d(sK + c * BSUB * 128, &tmK, &kv_full[st], c * 64, j * BSUB, h, b);
+          tma_load_4d(sV + c * BSUB * 128, &tmV, &kv_full[st], c * 64, j * BSUB, h, b);
         }
+        if (++st == C::NS) { st = 0; ph ^= 1; }
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
-    const uint32_t fmt = args.in_bf16 ? 1u : 0u;
-    const uint32_t idesc_s = make_idesc(1u, fmt, false, false, 128, 128);
-    const uint32_t idesc_acc = make_idesc(1u, fmt, false, true, 128, HD);
-    bool ok = mbar_wait(q_full, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 22);
-    for (int j = 0; j < n_kv && ok; j++) {
-      const int st = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      ok = mbar_wait(&kv_full[st], ph, abort_flag, args.status, ST_ATTN_TIMEOUT, 23);
-      if (!ok) break;
-      tc_fence_after();
+    if (elect_one()) {
+      const uint32_t fmt = BF ? 1u : 0u;
+      const uint32_t idesc_s = make_idesc(1u, fmt, false, false, 128, BSUB);
+      const uint32_t idesc_acc = make_idesc(1u, fmt, false, true, 128, HD);
       const uint32_t qa = smem_u32(sQ), ga = smem_u32(sdO);
-      const uint32_t ka = smem_u32(sK + st * C::TILE_BYTES), va = smem_u32(sV + st * C::TILE_BYTES);
-      if (lane == 0) {
+      bool ok = mbar_wait(q_full, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 22);
+      int st_s = 0;
+      uint32_t ph_s = 0;
+      auto issue_sdp = [&](int j) {
+        if (!mbar_wait(&kv_full[st_s], ph_s, abort_flag, args.status, ST_ATTN_TIMEOUT, 23)) return false;
+        tc_fence_after();
+        const uint32_t ka = smem_u32(ring + st_s * 2 * C::SUB_BYTES), va = ka + C::SUB_BYTES;
+        const uint32_t d = tmem_base + (j & 1) * 128;
 #pragma unroll
-        for (int k = 0; k < HD / 16; k++)  // S = Q K^T
-          tc_mma_f16(tmem_base + C::COL_S, kdesc(qa, k), kdesc(ka, k), idesc_s, k != 0);
+        for (int k = 0; k < HD / 16; k++) {
+          tc_mma_f16(d, kdesc(qa, k), kdesc_sub(ka, k), idesc_s, k != 0);       // S = Q K^T
+          tc_mma_f16(d + 64, kdesc(ga, k), kdesc_sub(va, k), idesc_s, k != 0);  // dP = dO V^T
+        }
+        tc_commit(&sdp_full[j & 1]);
+        if (++st_s == C::NS) { st_s = 0; ph_s ^= 1; }
+        return true;
+      };
+      if (ok && n_sub > 0) ok = issue_sdp(0);
+      int st = 0;
+      for (int j = 0; j < n_sub && ok; j++) {
+        if (j + 1 < n_sub) {
+          ok = issue_sdp(j + 1);
+          if (!ok) break;
+        }
+        const int bb = j & 1;
+        ok = mbar_wait(&p_full[bb], (j >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 24);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t ka = smem_u32(ring + st * 2 * C::SUB_BYTES);
+        const uint32_t pt = tmem_base + bb * 128 + 64;
 #pragma unroll
-        for (int k = 0; k < HD / 16; k++)  // dP = dO V^T
-          tc_mma_f16(tmem_base + C::COL_DP, kdesc(ga, k), kdesc(va, k), idesc_s, k != 0);
-        tc_commit(sdp_full);
-      }
-      __syncwarp();
-      ok = mbar_wait(p_full, j & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 24);
-      if (!ok) break;
-      tc_fence_after();
-      if (lane == 0) {
-#pragma unroll
-        for (int k = 0; k < BKV / 16; k++)  // dQ += dS K
-          tc_mma_f16_ts(tmem_base + C::COL_ACC0, tmem_base + C::COL_DP + k * 8, mndesc(ka, k),
-                        idesc_acc, (j | k) != 0);
+        for (int k = 0; k < BSUB / 16; k++)  // dQ += dS K
+          tc_mma_f16_ts(tmem_base + C::COL_ACC0, pt + (k >> 1) * 32 + (k & 1) * 8, mndesc_sub(ka, k), idesc_acc,
+                        (j | k) != 0);
         tc_commit(&kv_empty[st]);
-        if (j == n_kv - 1) tc_commit(acc_done);
+        if (j == n_sub - 1) tc_commit(acc_done);
+        if (++st == C::NS) st = 0;
       }
-      __syncwarp();
     }
+    __syncwarp();
   } else {
+    const int e = warp - 2;
+    const int group = e >> 3;
+    const int half = (e >> 2) & 1;
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const int qrow = q0 + r;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    float lse = INFINITY, delta = 0.f;
+    const uint32_t my = lane_addr + group * 128 + half * 32;
+    float lse2 = INFINITY, dls = 0.f;
     if (qrow < args.Sq) {
-      lse = args.LSE[((long long)b * args.H + h) * args.Sq + qrow] * 1.4426950408889634f;
-      delta = args.Delta[((long long)b * args.H + h) * args.Sq + qrow];
-      if (lse == -INFINITY) lse = INFINITY;
+      lse2 = args.LSE[((long long)b * args.H + h) * args.Sq + qrow] * 1.4426950408889634f;
+      dls = args.Delta[((long long)b * args.H + h) * args.Sq + qrow] * args.scale;
+      if (lse2 == -INFINITY) lse2 = INFINITY;
     }
     bool ok = true;
-    for (int j = 0; j < n_kv; j++) {
-      ok = mbar_wait(sdp_full, j & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 25);
+    for (int j = group; j < n_sub; j += 2) {
+      ok = mbar_wait(&sdp_full[group], (j >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 25);
       if (!ok) break;
       tc_fence_after();
-      const int kv0 = j * BKV;
-      const bool need_mask = (args.causal && j == q_tile) || (kv0 + BKV > args.Sk);
-      float p[BKV];
+      const int kv0 = j * BSUB + half * 32;  // first key column of this thread
+      const bool need_mask = (args.causal && kv0 + 31 > q0) || (kv0 + 32 > args.Sk);
+      uint32_t rs[32], rd[32];
+      tmem_ld32(my, rs);
+      tmem_ld32(my + 64, rd);
+      tmem_ld_wait();
+      uint32_t pd[16];
 #pragma unroll
-      for (int c = 0; c < BKV / 32; c++) {
-        uint32_t rr[32];
-        tmem_ld32(lane_addr + C::COL_S + c * 32, rr);
-        tmem_ld_wait();
+      for (int i = 0; i < 16; i++) {
+        float dv[2];
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
-          const int kc = c * 32 + i;
-          float v = exp2f(__uint_as_float(rr[i]) * args.scale_log2 - lse);
-          if (need_mask && (kv0 + kc >= args.Sk || (args.causal && kv0 + kc > qrow))) v = 0.f;
-          p[kc] = v;
+        for (int u = 0; u < 2; u++) {
+          const int c = 2 * i + u;
+          float p = exp2f(fmaf(__uint_as_float(rs[c]), args.scale_log2, -lse2));
+          if (need_mask && (kv0 + c >= args.Sk || (args.causal && kv0 + c > qrow))) p = 0.f;
+          dv[u] = p * fmaf(__uint_as_float(rd[c]), args.scale, -dls);
         }
+        pd[i] = pack16t<BF>(dv[0], dv[1]);
       }
-#pragma unroll
-      for (int c = 0; c < BKV / 32; c++) {
-        uint32_t rr[32];
-        tmem_ld32(lane_addr + C::COL_DP + c * 32, rr);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i++) {
-          const int kc = c * 32 + i;
-          p[kc] = p[kc] * (__uint_as_float(rr[i]) - delta) * args.scale;
-        }
-      }
-#pragma unroll
-      for (int c = 0; c < BKV / 32; c++) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; i++) pk[i] = pack16(p[c * 32 + 2 * i], p[c * 32 + 2 * i + 1], args.in_bf16);
-        tmem_st16(lane_addr + C::COL_DP + c * 16, pk);
-      }
+      tmem_st16(my + 64, pd);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[group]);
     }
-    if (ok && n_kv > 0) ok = mbar_wait(acc_done, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 26);
+    if (ok && n_sub > 0) ok = mbar_wait(acc_done, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 26);
     if (ok) {
       tc_fence_after();
+      constexpr int W = HD / 4;
+      const int cw = (group * 2 + half) * W;
       const bool row_ok = qrow < args.Sq;
-      uint16_t* dqrow = (uint16_t*)args.dQ + (long long)b * args.dq_sb + (long long)qrow * args.dq_ss + (long long)h * args.dq_sh;
-#pragma unroll
-      for (int c = 0; c < HD / 32; c++) {
-        uint32_t rr[32];
-        float v[32];
-        if (n_kv > 0) { tmem_ld32(lane_addr + C::COL_ACC0 + c * 32, rr); tmem_ld_wait(); }
-#pragma unroll
-        for (int i = 0; i < 32; i++) v[i] = n_kv > 0 ? __uint_as_float(rr[i]) : 0.f;
-        if (row_ok) store_row16<32>(dqrow + c * 32, v, args.in_bf16);
+      uint16_t* dqrow = (uint16_t*)args.dQ + (long long)b * args.dq_sb + (long long)qrow * args.dq_ss +
+                        (long long)h * args.dq_sh + cw;
+      uint32_t rr[W];
+      float v[W];
+      if (n_sub > 0) {
+        if constexpr (W == 32) tmem_ld32(lane_addr + C::COL_ACC0 + cw, rr);
+        else tmem_ld16(lane_addr + C::COL_ACC0 + cw, rr);
+        tmem_ld_wait();
       }
+#pragma unroll
+      for (int i = 0; i < W; i++) v[i] = n_sub > 0 ? __uint_as_float(rr[i]) : 0.f;
+      if (row_ok) store_row16<W>(dqrow, v, BF);
     }
   }
   tc_fence_before();
@@ -784,28 +866,41 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   return gbh::E_OK;
 }
 
-template <int HD>
-int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-               const CUtensorMap& tg, const AttnArgs& a, cudaStream_t s) {
+struct BwdMaps {
+  CUtensorMap q128, k128, v128, g128;  // 128-row boxes (resident tiles)
+  CUtensorMap q64, k64, v64, g64;      // 64-row boxes (streamed sub-tiles)
+};
+
+template <int HD, bool BF>
+int launch_bwd(const BwdMaps& m, const AttnArgs& a, cudaStream_t s) {
   using C = BwdCfg<HD>;
   static bool configured = false;
   if (!configured) {
-    GB_CUDA_OK(cudaFuncSetAttribute(fa_bwd_dkv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    GB_CUDA_OK(cudaFuncSetAttribute(fa_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    GB_CUDA_OK(cudaFuncSetAttribute(fa_bwd_dkv_kernel<HD, BF>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    GB_CUDA_OK(cudaFuncSetAttribute(fa_bwd_dq_kernel<HD, BF>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     configured = true;
   }
   dim3 gkv((a.Sk + BKV - 1) / BKV, a.H, a.B);
-  fa_bwd_dkv_kernel<HD><<<gkv, kBwdThreads, C::SMEM_BYTES, s>>>(tq, tk, tv, tg, a);
+  fa_bwd_dkv_kernel<HD, BF><<<gkv, kBwdThreads, C::SMEM_BYTES, s>>>(m.q64, m.k128, m.v128, m.g64, a);
   GB_CUDA_OK(cudaGetLastError());
   dim3 gq((a.Sq + BQ - 1) / BQ, a.H, a.B);
-  fa_bwd_dq_kernel<HD><<<gq, kBwdThreads, C::SMEM_BYTES, s>>>(tq, tk, tv, tg, a);
+  fa_bwd_dq_kernel<HD, BF><<<gq, kBwdThreads, C::SMEM_BYTES, s>>>(m.q128, m.k64, m.v64, m.g128, a);
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;
 }
 
+long long* g_trace = nullptr;
+
 }  // namespace
 
 enum { DT_BF16 = 0, DT_F16 = 1 };
+
+// Timeline tracing of the dK/dV kernel: `buf` is a device buffer of 3 * 512 int64 (zeroed by
+// the caller) that CTA (0,0,0) fills with SM clock stamps; null switches tracing off.
+GB_EXPORT int gb_flash_trace(long long* buf) {
+  g_trace = buf;
+  return 0;
+}
 
 // Forward.  q/k/v/o: 16-bit tensors addressed as [b][s][h][d] through element
 // strides (sb, ss, sh) with d contiguous; head_dim 64 or 128.  lse (fp32,
@@ -891,12 +986,20 @@ GB_EXPORT int gb_flash_bwd(int dtype, const void* q, const void* k, const void* 
   a.dk_sb = strides[15]; a.dk_ss = strides[16]; a.dk_sh = strides[17];
   a.dv_sb = strides[18]; a.dv_ss = strides[19]; a.dv_sh = strides[20];
   a.status = gbh::status_ptr();
-  CUtensorMap tq, tk, tv, tg;
+  a.trace = g_trace;
+  BwdMaps m;
   int rc;
-  if ((rc = make_qkv_map(&tq, q, a.in_bf16, B, H, Sq, D, strides[0], strides[1], strides[2], 128))) return rc;
-  if ((rc = make_qkv_map(&tk, k, a.in_bf16, B, H, Sk, D, strides[3], strides[4], strides[5], 128))) return rc;
-  if ((rc = make_qkv_map(&tv, v, a.in_bf16, B, H, Sk, D, strides[6], strides[7], strides[8], 128))) return rc;
-  if ((rc = make_qkv_map(&tg, dout, a.in_bf16, B, H, Sq, D, strides[9], strides[10], strides[11], 128))) return rc;
-  if (D == 128) return launch_bwd<128>(tq, tk, tv, tg, a, (cudaStream_t)stream);
-  return launch_bwd<64>(tq, tk, tv, tg, a, (cudaStream_t)stream);
+  if ((rc = make_qkv_map(&m.q128, q, a.in_bf16, B, H, Sq, D, strides[0], strides[1], strides[2], 128))) return rc;
+  if ((rc = make_qkv_map(&m.k128, k, a.in_bf16, B, H, Sk, D, strides[3], strides[4], strides[5], 128))) return rc;
+  if ((rc = make_qkv_map(&m.v128, v, a.in_bf16, B, H, Sk, D, strides[6], strides[7], strides[8], 128))) return rc;
+  if ((rc = make_qkv_map(&m.g128, dout, a.in_bf16, B, H, Sq, D, strides[9], strides[10], strides[11], 128))) return rc;
+  if ((rc = make_qkv_map(&m.q64, q, a.in_bf16, B, H, Sq, D, strides[0], strides[1], strides[2], 64))) return rc;
+  if ((rc = make_qkv_map(&m.k64, k, a.in_bf16, B, H, Sk, D, strides[3], strides[4], strides[5], 64))) return rc;
+  if ((rc = make_qkv_map(&m.v64, v, a.in_bf16, B, H, Sk, D, strides[6], strides[7], strides[8], 64))) return rc;
+  if ((rc = make_qkv_map(&m.g64, dout, a.in_bf16, B, H, Sq, D, strides[9], strides[10], strides[11], 64))) return rc;
+  if (D == 128)
+    return a.in_bf16 ? launch_bwd<128, true>(m, a, (cudaStream_t)stream)
+                     : launch_bwd<128, false>(m, a, (cudaStream_t)stream);
+  return a.in_bf16 ? launch_bwd<64, true>(m, a, (cudaStream_t)stream)
+                   : launch_bwd<64, false>(m, a, (cudaStream_t)stream);
 }
