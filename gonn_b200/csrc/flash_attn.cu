@@ -357,6 +357,37 @@ __global__ void fa_delta_kernel(const T* __restrict__ O, const T* __restrict__ d
 }
 
 
+// The same for 16-byte aligned rows of D = 8 * TPR elements: TPR threads per row, one
+// 16-byte load of O and of dO each.
+template <typename T, int TPR>
+__global__ void __launch_bounds__(256)
+fa_delta_vec_kernel(const T* __restrict__ O, const T* __restrict__ dO, float* __restrict__ delta, int B,
+                    int H, int S, long long o_sb, long long o_ss, long long o_sh, long long g_sb,
+                    long long g_ss, long long g_sh) {
+  const long long total = (long long)B * H * S;
+  const int sub = threadIdx.x % TPR;
+  constexpr int RPB = 256 / TPR;  // rows per CTA pass; every thread of the CTA runs the same trip count
+  for (long long base = (long long)blockIdx.x * RPB; base < total; base += (long long)gridDim.x * RPB) {
+    const long long i = base + threadIdx.x / TPR;
+    // rows are visited in (b, s, h) order so that neighbouring threads read neighbouring memory
+    const bool live = i < total;
+    const long long ii = live ? i : 0;
+    const int h = (int)(ii % H);
+    const int q = (int)((ii / H) % S);
+    const int b = (int)(ii / ((long long)S * H));
+    const uint4 uo = *reinterpret_cast<const uint4*>(O + b * o_sb + q * o_ss + h * o_sh + sub * 8);
+    const uint4 ug = *reinterpret_cast<const uint4*>(dO + b * g_sb + q * g_ss + h * g_sh + sub * 8);
+    const T* eo = reinterpret_cast<const T*>(&uo);
+    const T* eg = reinterpret_cast<const T*>(&ug);
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) s += (float)eo[j] * (float)eg[j];
+#pragma unroll
+    for (int o = TPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (live && sub == 0) delta[((long long)b * H + h) * S + q] = s;
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Backward
 // ---------------------------------------------------------------------------
@@ -943,8 +974,23 @@ GB_EXPORT int gb_flash_delta(int dtype, const void* o, const void* dout, float* 
                              int S, int D, long long o_sb, long long o_ss, long long o_sh,
                              long long g_sb, long long g_ss, long long g_sh, void* stream) {
   long long total = (long long)B * H * S;
+  if (total < 1) return gbh::E_OK;
+  const bool vec = (D == 64 || D == 128) && !((o_sb | o_ss | o_sh | g_sb | g_ss | g_sh) & 7) &&
+                   !(((uintptr_t)o | (uintptr_t)dout) & 15);
+  if (vec) {
+    const int tpr = D / 8, rpb = 256 / tpr;
+    int grid = (int)((total + rpb - 1) / rpb < 148 * 8 ? (total + rpb - 1) / rpb : 148 * 8);
+    cudaStream_t st = (cudaStream_t)stream;
+#define GB_DELTA(T, TPR)                                                                               \
+  fa_delta_vec_kernel<T, TPR><<<grid, 256, 0, st>>>((const T*)o, (const T*)dout, delta, B, H, S, o_sb, \
+                                                    o_ss, o_sh, g_sb, g_ss, g_sh)
+    if (dtype == DT_BF16) { if (D == 64) GB_DELTA(__nv_bfloat16, 8); else GB_DELTA(__nv_bfloat16, 16); }
+    else { if (D == 64) GB_DELTA(__half, 8); else GB_DELTA(__half, 16); }
+#undef GB_DELTA
+    GB_CUDA_OK(cudaGetLastError());
+    return gbh::E_OK;
+  }
   int grid = (int)((total + 7) / 8 < 148 * 16 ? (total + 7) / 8 : 148 * 16);
-  if (grid < 1) return gbh::E_OK;
   if (dtype == DT_BF16)
     fa_delta_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, B, H, S, D, o_sb, o_ss, o_sh, g_sb, g_ss, g_sh);

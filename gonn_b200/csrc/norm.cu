@@ -74,63 +74,81 @@ norm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, const TW* __r
                 T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
                 long long rows, int D, float eps) {
   constexpr int V = IO<T>::V;
+  constexpr int NR = (G == 32) ? 2 : 1;  // rows in flight per group (more loads outstanding)
   __shared__ float red[32];
   const int gpb = 256 / G;
   const int g = threadIdx.x / G, t = threadIdx.x % G;
   const int nvec = D / V;
-  for (long long row = (long long)blockIdx.x * gpb + g; row < rows; row += (long long)gridDim.x * gpb) {
-    const T* xr = x + row * D;
-    float v[VPT][V];
-    float s = 0.f;
+  // the thread's columns are the same for every row: keep weight and bias in registers
+  float wr[VPT][V], br[VPT][V];
 #pragma unroll
-    for (int i = 0; i < VPT; i++) {
-      const int vi = t + i * G;
-      if (vi < nvec) {
-        IO<T>::ld(xr + vi * V, v[i]);
+  for (int i = 0; i < VPT; i++) {
+    const int vi = t + i * G;
 #pragma unroll
-        for (int j = 0; j < V; j++) s += RMS ? v[i][j] * v[i][j] : v[i][j];
-      } else {
+    for (int j = 0; j < V; j++) {
+      wr[i][j] = (w && vi < nvec) ? (float)w[vi * V + j] : 1.f;
+      br[i][j] = (!RMS && b && vi < nvec) ? (float)b[vi * V + j] : 0.f;
+    }
+  }
+  const long long stride = (long long)gridDim.x * gpb;
+  for (long long row0 = (long long)blockIdx.x * gpb + g; row0 < rows; row0 += stride * NR) {
+    float v[NR][VPT][V];
+    float s[NR];
 #pragma unroll
-        for (int j = 0; j < V; j++) v[i][j] = 0.f;
+    for (int r = 0; r < NR; r++) {
+      const long long row = row0 + r * stride;
+      s[r] = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; i++) {
+        const int vi = t + i * G;
+        if (vi < nvec && row < rows) {
+          IO<T>::ld(x + row * D + vi * V, v[r][i]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; j++) v[r][i][j] = 0.f;
+        }
       }
     }
-    s = group_sum<G>(s, red);
-    float mean = 0.f, rstd;
-    if (RMS) {
-      rstd = rsqrtf(s / D + eps);
-    } else {
-      mean = s / D;
-      float q = 0.f;
+#pragma unroll
+    for (int r = 0; r < NR; r++) {
+      const long long row = row0 + r * stride;
+      if (G == 32 && row >= rows) continue;  // warp-uniform
+#pragma unroll
+      for (int i = 0; i < VPT; i++)
+#pragma unroll
+        for (int j = 0; j < V; j++) s[r] += RMS ? v[r][i][j] * v[r][i][j] : v[r][i][j];
+      const float sum = group_sum<G>(s[r], red);
+      float mean = 0.f, rstd;
+      if (RMS) {
+        rstd = rsqrtf(sum / D + eps);
+      } else {
+        mean = sum / D;
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPT; i++) {
+          const int vi = t + i * G;
+          if (vi < nvec) {
+#pragma unroll
+            for (int j = 0; j < V; j++) { float d = v[r][i][j] - mean; q += d * d; }
+          }
+        }
+        q = group_sum<G>(q, red);
+        rstd = rsqrtf(q / D + eps);
+      }
+      if (t == 0) {
+        if (mean_out) mean_out[row] = mean;
+        rstd_out[row] = rstd;
+      }
+      T* yr = y + row * D;
 #pragma unroll
       for (int i = 0; i < VPT; i++) {
         const int vi = t + i * G;
         if (vi < nvec) {
+          float o[V];
 #pragma unroll
-          for (int j = 0; j < V; j++) { float d = v[i][j] - mean; q += d * d; }
+          for (int j = 0; j < V; j++) o[j] = (v[r][i][j] - mean) * rstd * wr[i][j] + br[i][j];
+          IO<T>::st(yr + vi * V, o);
         }
-      }
-      q = group_sum<G>(q, red);
-      rstd = rsqrtf(q / D + eps);
-    }
-    if (t == 0) {
-      if (mean_out) mean_out[row] = mean;
-      rstd_out[row] = rstd;
-    }
-    T* yr = y + row * D;
-#pragma unroll
-    for (int i = 0; i < VPT; i++) {
-      const int vi = t + i * G;
-      if (vi < nvec) {
-        float o[V];
-#pragma unroll
-        for (int j = 0; j < V; j++) {
-          const int c = vi * V + j;
-          float h = (v[i][j] - mean) * rstd;
-          if (w) h *= (float)w[c];
-          if (!RMS && b) h += (float)b[c];
-          o[j] = h;
-        }
-        IO<T>::st(yr + vi * V, o);
       }
     }
   }
@@ -156,7 +174,32 @@ norm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TW* __r
 #pragma unroll
     for (int j = 0; j < V; j++) { dg[i][j] = 0.f; db[i][j] = 0.f; }
 
-  for (long long row = (long long)blockIdx.x * gpb + g; row < rows; row += (long long)gridDim.x * gpb) {
+  float wr[VPT][V];
+#pragma unroll
+  for (int i = 0; i < VPT; i++) {
+    const int vi = t + i * G;
+#pragma unroll
+    for (int j = 0; j < V; j++) wr[i][j] = (w && vi < nvec) ? (float)w[vi * V + j] : 1.f;
+  }
+  const long long stride = (long long)gridDim.x * gpb;
+  long long row = (long long)blockIdx.x * gpb + g;
+  // software pipeline: the loads of the next row are issued before this row's arithmetic
+  float an[VPT][V], dn[VPT][V];
+  auto fetch = [&](long long r) {
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int vi = t + i * G;
+      if (vi < nvec && r < rows) {
+        IO<T>::ld(x + r * D + vi * V, an[i]);
+        IO<T>::ld(dy + r * D + vi * V, dn[i]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; j++) { an[i][j] = 0.f; dn[i][j] = 0.f; }
+      }
+    }
+  };
+  fetch(row);
+  for (; row < rows; row += stride) {
     const float mean = RMS ? 0.f : mean_in[row];
     const float rstd = rstd_in[row];
     float xh[VPT][V], gy[VPT][V];
@@ -165,26 +208,23 @@ norm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TW* __r
     for (int i = 0; i < VPT; i++) {
       const int vi = t + i * G;
       if (vi < nvec) {
-        float a[V], d[V];
-        IO<T>::ld(x + row * D + vi * V, a);
-        IO<T>::ld(dy + row * D + vi * V, d);
 #pragma unroll
         for (int j = 0; j < V; j++) {
-          const int c = vi * V + j;
-          float h = (a[j] - mean) * rstd;
-          float gw = w ? d[j] * (float)w[c] : d[j];
+          float h = (an[i][j] - mean) * rstd;
+          float gw = dn[i][j] * wr[i][j];
           xh[i][j] = h;
           gy[i][j] = gw;
           s1 += gw;
           s2 += gw * h;
-          dg[i][j] += d[j] * h;
-          db[i][j] += d[j];
+          dg[i][j] += dn[i][j] * h;
+          db[i][j] += dn[i][j];
         }
       } else {
 #pragma unroll
         for (int j = 0; j < V; j++) { xh[i][j] = 0.f; gy[i][j] = 0.f; }
       }
     }
+    fetch(row + stride);
     if (!RMS) s1 = group_sum<G>(s1, red);
     s2 = group_sum<G>(s2, red);
     const float m1 = RMS ? 0.f : s1 / D, m2 = s2 / D;

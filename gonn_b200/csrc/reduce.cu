@@ -129,6 +129,57 @@ __global__ void col_reduce_kernel(const T* __restrict__ x, TO* __restrict__ y,
   }
 }
 
+// Column reduction for 16-bit inputs whose row length is a multiple of 8: a thread owns 8
+// adjacent columns and reads them as one 16-byte load; a CTA covers 256 columns x 8 row
+// lanes with four rows in flight per thread.  Same outputs as col_reduce_kernel.
+template <typename T, typename TO, int OP>
+__global__ void __launch_bounds__(256)
+col_reduce_vec_kernel(const T* __restrict__ x, TO* __restrict__ y, float* __restrict__ part, long long R,
+                      long long inner, int splits, int to_part) {
+  __shared__ float sm[8][8 * 32];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const long long col0 = ((long long)blockIdx.x * 32 + tx) * 8;
+  const long long o = blockIdx.z;
+  const long long per = (R + splits - 1) / splits;
+  const long long r0 = (long long)blockIdx.y * per, r1 = min(r0 + per, R);
+  float a[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) a[j] = r_init<float, OP>();
+  if (col0 < inner) {
+    const T* xp = x + o * R * inner + col0;
+    auto take = [&](const uint4& u) {
+      const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+      for (int j = 0; j < 8; j++) a[j] = r_comb<float, OP>(a[j], (float)e[j]);
+    };
+    long long r = r0 + ty;
+    for (; r + 24 < r1; r += 32) {
+      const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(xp + r * inner));
+      const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(xp + (r + 8) * inner));
+      const uint4 u2 = __ldg(reinterpret_cast<const uint4*>(xp + (r + 16) * inner));
+      const uint4 u3 = __ldg(reinterpret_cast<const uint4*>(xp + (r + 24) * inner));
+      take(u0); take(u1); take(u2); take(u3);
+    }
+    for (; r < r1; r += 8) take(__ldg(reinterpret_cast<const uint4*>(xp + r * inner)));
+  }
+#pragma unroll
+  for (int j = 0; j < 8; j++) sm[ty][j * 32 + tx] = a[j];
+  __syncthreads();
+  // thread (tx, ty) finishes column tx * 8 + ty of the CTA's 256
+  const long long col = ((long long)blockIdx.x * 32 + tx) * 8 + ty;
+  if (col < inner) {
+    float v = sm[0][ty * 32 + tx];
+#pragma unroll
+    for (int k = 1; k < 8; k++) v = r_comb<float, OP>(v, sm[k][ty * 32 + tx]);
+    if (to_part) {
+      part[(o * splits + blockIdx.y) * inner + col] = v;
+    } else {
+      if (OP == R_MEAN) v = v / (float)R;
+      y[o * inner + col] = (TO)v;
+    }
+  }
+}
+
 template <typename CT, typename TO, int OP>
 __global__ void col_finish_kernel(const CT* __restrict__ part, TO* __restrict__ y, long long R,
                                   long long inner, int splits, long long total, int accumulate) {
@@ -159,6 +210,15 @@ __global__ void col_arg_kernel(const T* __restrict__ x, long long* __restrict__ 
   y[i] = bi;
 }
 
+template <typename T, typename TO, int OP>
+void launch_col_vec(dim3 grid, dim3 blk, cudaStream_t s, const void* x, void* y, void* scratch, long long R,
+                    long long inner, int splits, int to_part) {
+  if constexpr (sizeof(T) == 2) {
+    col_reduce_vec_kernel<T, TO, OP><<<grid, blk, 0, s>>>((const T*)x, (TO*)y, (float*)scratch, R, inner, splits,
+                                                          to_part);
+  }
+}
+
 template <typename T, typename TO>
 int reduce_t(int op, const void* x, void* y, void* scratch, long long scratch_bytes, long long outer,
              long long R, long long inner, int accumulate, cudaStream_t s) {
@@ -183,7 +243,8 @@ int reduce_t(int op, const void* x, void* y, void* scratch, long long scratch_by
       int blk = R >= 4096 ? 512 : (R >= 512 ? 256 : (R >= 64 ? 64 : 32));                            \
       row_reduce_kernel<T, TO, OPID><<<(unsigned)outer, blk, 0, s>>>((const T*)x, (TO*)y, R);        \
     } else {                                                                                         \
-      long long tiles = (inner + 31) / 32;                                                           \
+      const bool vec = sizeof(T) == 2 && (inner & 7) == 0 && (((uintptr_t)x & 15) == 0);             \
+      long long tiles = vec ? (inner + 255) / 256 : (inner + 31) / 32;                               \
       int splits = 1;                                                                                \
       if (tiles * outer < 148 * 4 && R >= 256) {                                                     \
         splits = (int)((148 * 4 + tiles * outer - 1) / (tiles * outer));                             \
@@ -197,7 +258,8 @@ int reduce_t(int op, const void* x, void* y, void* scratch, long long scratch_by
         return gbh::E_BAD_ARG;                                                                       \
       }                                                                                              \
       dim3 grid((unsigned)tiles, splits, (unsigned)outer), blk(32, 8);                               \
-      col_reduce_kernel<T, TO, OPID><<<grid, blk, 0, s>>>((const T*)x, (TO*)y, (CT*)scratch, R, inner, splits, two ? 1 : 0); \
+      if (vec) launch_col_vec<T, TO, OPID>(grid, blk, s, x, y, scratch, R, inner, splits, two ? 1 : 0); \
+      else col_reduce_kernel<T, TO, OPID><<<grid, blk, 0, s>>>((const T*)x, (TO*)y, (CT*)scratch, R, inner, splits, two ? 1 : 0); \
       if (two) {                                                                                     \
         long long total = outer * inner;                                                             \
         col_finish_kernel<CT, TO, OPID><<<(unsigned)((total + 255) / 256), 256, 0, s>>>((const CT*)scratch, (TO*)y, R, inner, splits, total, accumulate); \

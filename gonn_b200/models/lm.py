@@ -18,7 +18,7 @@ from ..nn.module import Module, ModuleList
 from ..nn.norm import LayerNorm, RMSNorm
 from ..nn.transformer import TransformerEncoderLayer
 from ..ops.elementwise import binary as _binary
-from ..ops.linear import linear as _linear
+from ..ops.linear import feed_forward as _feed_forward
 from ..ops.softmax import cross_entropy
 
 
@@ -66,8 +66,8 @@ class GPTBlock(Module):
     def forward(self, x):
         n = self.norm1(x)
         x = self.attn(n, n, n, True, residual=x)
-        h = _linear(self.norm2(x), self.ff1.weight, self.ff1.bias, "gelu")
-        return self.ff2(h, residual=x)
+        return _feed_forward(self.norm2(x), self.ff1.weight, self.ff1.bias, self.ff2.weight, self.ff2.bias,
+                             "gelu", x)
 
 
 class GPT(Module):

@@ -42,10 +42,11 @@ class TransformerEncoderLayer(Module):
         kind = getattr(self.act, "kind", None)
         plain = not (self.training and self.dropff.p > 0)
         if kind in _FUSABLE and plain and type(self.act) is Activation:
-            # activation fused into the first GEMM's epilogue, residual into the second's
-            from ..ops.linear import linear
-            h = linear(x, self.ff1.weight, self.ff1.bias, _FUSABLE[kind])
-            return self.ff2(h, residual=residual)
+            # activation fused into the first GEMM's epilogue, residual into the second's,
+            # the activation's derivative into the second layer's data-gradient GEMM
+            from ..ops.linear import feed_forward
+            return feed_forward(x, self.ff1.weight, self.ff1.bias, self.ff2.weight, self.ff2.bias,
+                                _FUSABLE[kind], residual)
         y = self.ff2(self.dropff(self.act(self.ff1(x))))
         return y if residual is None else residual + y
 

@@ -114,6 +114,53 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return _Linear.apply(x, weight, bias, act, residual)
 
 
+class _FeedForward(torch.autograd.Function):
+    """``act(x W1^T + b1) W2^T + b2 (+ residual)`` as one tape node.
+
+    Keeping both products in one node lets the backward fold the activation's derivative
+    into the epilogue of the data-gradient GEMM of the second layer
+    (``dpre = (dy W2) * act'(pre)``), so no separate elementwise pass over the hidden
+    activations runs in either direction.
+    """
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2, act, residual):
+        K, F, N = x.shape[-1], w1.shape[0], w2.shape[0]
+        x2 = x.reshape(-1, K)
+        pre = torch.empty((x2.shape[0], F), dtype=x.dtype, device=x.device)
+        h = gemm(x2, w1, trans_b=True, bias=b1, act=act, aux=pre, aux_mode="store_pre")
+        res2 = residual.reshape(-1, N) if residual is not None else None
+        y = gemm(h, w2, trans_b=True, bias=b2, aux=res2, aux_mode="add" if res2 is not None else None)
+        ctx.save_for_backward(x2, w1, w2, pre, h)
+        ctx.act, ctx.xshape, ctx.has_res = act, x.shape, residual is not None
+        ctx.b1, ctx.b2 = b1, b2
+        return y.reshape(*x.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w1, w2, pre, h = ctx.saved_tensors
+        N = w2.shape[0]
+        dy2 = dy.reshape(-1, N)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dres = dy if ctx.has_res else None
+        # second layer: weight / bias gradients from dy, data gradient with act' folded in
+        dw2 = emit_weight_grad(w2, dy2, h, True, False) if ctx.needs_input_grad[3] else None
+        db2 = emit_vector_grad(ctx.b2, dy2) if (ctx.b2 is not None and ctx.needs_input_grad[4]) else None
+        dpre = gemm(dy2, w2, aux=pre, aux_mode=_DACT_MODE[ctx.act])
+        dw1 = emit_weight_grad(w1, dpre, x2, True, False) if ctx.needs_input_grad[1] else None
+        db1 = emit_vector_grad(ctx.b1, dpre) if (ctx.b1 is not None and ctx.needs_input_grad[2]) else None
+        dx = gemm(dpre, w1).reshape(ctx.xshape) if ctx.needs_input_grad[0] else None
+        return dx, dw1, db1, dw2, db2, None, dres
+
+
+def feed_forward(x, w1, b1, w2, b2, act: str = "gelu", residual: Optional[torch.Tensor] = None):
+    """Two-layer feed-forward block with a fusable activation (relu / gelu / geluexact)."""
+    if act not in _DACT_MODE:
+        raise ValueError(f"feed_forward: activation {act!r} cannot be fused")
+    return _FeedForward.apply(x, w1, b1, w2, b2, act, residual)
+
+
 class _MatMul(torch.autograd.Function):
     """C = A @ B for 2-D / batched operands; backward via trans flags (no transposes)."""
 

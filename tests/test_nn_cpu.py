@@ -199,3 +199,26 @@ def test_hooks_functional_call_and_train_flag():
     seq.Eval()
     assert not seq[1].training and torch.equal(seq[0](x), x)
     assert [id(p) for p in nn.FilterParams(seq, lambda n, p: n.endswith("bias"))] == [id(seq[1].bias)]
+
+
+def test_feed_forward_matches_composed_layers():
+    """The fused two-layer node must give the gradients of the composed expression."""
+    from gonn_b200.ops.linear import feed_forward
+    torch.manual_seed(3)
+    for act, ref in (("gelu", lambda t: torch.nn.functional.gelu(t, approximate="tanh")),
+                     ("relu", torch.relu),
+                     ("geluexact", torch.nn.functional.gelu)):
+        x = torch.randn(5, 7, 12, dtype=torch.float64, requires_grad=True)
+        w1 = torch.randn(20, 12, dtype=torch.float64, requires_grad=True)
+        b1 = torch.randn(20, dtype=torch.float64, requires_grad=True)
+        w2 = torch.randn(12, 20, dtype=torch.float64, requires_grad=True)
+        b2 = torch.randn(12, dtype=torch.float64, requires_grad=True)
+        res = torch.randn(5, 7, 12, dtype=torch.float64, requires_grad=True)
+        y = feed_forward(x, w1, b1, w2, b2, act, res)
+        g = torch.randn_like(y)
+        got = torch.autograd.grad(y, (x, w1, b1, w2, b2, res), g)
+        yr = ref(x @ w1.t() + b1) @ w2.t() + b2 + res
+        want = torch.autograd.grad(yr, (x, w1, b1, w2, b2, res), g)
+        assert torch.allclose(y, yr, atol=1e-9)
+        for a, b in zip(got, want):
+            assert torch.allclose(a, b, atol=1e-8), act
