@@ -58,8 +58,8 @@ struct GemmArgs {
   int in_bf16;  // 1 = bf16 inputs, 0 = fp16 inputs (ignored for int8)
   int bcastA, bcastB;  // operand shared by every batch entry (batch stride 0)
   int group_m;         // row blocks per rasterisation group
-  int pf_dist;         // L2 prefetch distance in k-blocks (0 = off)
   int tma_epi;         // 1: results leave through shared memory and TMA stores (16-bit outputs)
+  int splits, kb_per;  // split-K: slice s of a tile covers k-blocks [s * kb_per, (s + 1) * kb_per)
   int* status;
 };
 
@@ -100,6 +100,22 @@ __device__ __forceinline__ void tile_coords(int r, int num_m, int num_n, int gm,
   const int in_g = r - g * per_group;
   mb = first + in_g % rows;
   nb = in_g / rows;
+}
+
+// Work unit t of a launch -> K slice, batch entry and tile coordinates.  Slices are the
+// slowest index, so the CTAs first sweep slice 0 of every tile, then slice 1, ...
+struct Unit {
+  int s, b, mb, nb;
+};
+__device__ __forceinline__ Unit decode_unit(int t, const GemmArgs& args) {
+  const int tiles_per_batch = args.num_m * args.num_n;
+  const int per_slice = tiles_per_batch * args.batch;
+  Unit u;
+  u.s = t / per_slice;
+  const int t2 = t - u.s * per_slice;
+  u.b = t2 / tiles_per_batch;
+  tile_coords(t2 - u.b * tiles_per_batch, args.num_m, args.num_n, args.group_m, u.mb, u.nb);
+  return u;
 }
 
 template <typename T>
@@ -459,6 +475,28 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs& args, const Ep
 #pragma unroll
       for (int j = 0; j < 32; j++) v[j] += s_bias[sc + j];
     }
+    if (args.out_kind == OUT_F32) {
+      // 32 fp32 columns are two 64-byte-wide boxes: columns 0-15 in buffer 0, 16-31 in buffer 1
+      if (lane == 0) tma_store_wait_read<0>();
+      __syncwarp();
+#pragma unroll
+      for (int hb = 0; hb < 2; hb++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          uint4 o;
+          o.x = __float_as_uint(v[hb * 16 + j * 4]); o.y = __float_as_uint(v[hb * 16 + j * 4 + 1]);
+          o.z = __float_as_uint(v[hb * 16 + j * 4 + 2]); o.w = __float_as_uint(v[hb * 16 + j * 4 + 3]);
+          st_shared_v4(sb0 + hb * 2048 + myrow + (((uint32_t)j ^ swz) << 4), o);
+        }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_3d(tmC, st.buf, col0, mrow0, b);
+        if (col0 + 16 < args.N) tma_store_3d(tmC, st.buf + 2048, col0 + 16, mrow0, b);
+        tma_store_commit();
+      }
+      continue;
+    }
     const int bi = c & 1;
     const uint32_t sbc = sb0 + bi * 2048;
     if (two_out) {
@@ -576,8 +614,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (args.K + C::BK - 1) / C::BK;
-  const int tiles_per_batch = args.num_m * args.num_n;
-  const int num_tiles = tiles_per_batch * args.batch;
+  const int num_tiles = args.num_m * args.num_n * args.batch * args.splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; s++) {
@@ -613,58 +650,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      // L2 prefetch cursor: runs `pf_dist` k-blocks ahead of the loads (across tile
-      // boundaries), so that the loads that fill shared memory find their lines in L2 and
-      // the ring of shared-memory stages only has to cover the L2 latency, not DRAM's.
-      int pt = blockIdx.x, pkb = 0, pm0 = 0, pn0 = 0, pba = 0, pbb = 0;
-      auto pf_coords = [&]() {
-        if (pt >= num_tiles) return;
-        const int b = pt / tiles_per_batch;
-        const int r = pt - b * tiles_per_batch;
-        int mb, nb;
-        tile_coords(r, args.num_m, args.num_n, args.group_m, mb, nb);
-        pm0 = mb * BM;
-        pn0 = nb * BN;
-        pba = args.bcastA ? 0 : b;
-        pbb = args.bcastB ? 0 : b;
-      };
-      auto pf_step = [&](bool issue) {
-        if (pt >= num_tiles) return;
-        if (issue) {
-          const int k0 = pkb * C::BK;
-          constexpr int MN_ATOM = kSwizzleBytes / ESZ;
-          if (!A_MN) {
-            tma_prefetch_3d(&tmA, k0, pm0, pba);
-          } else {
-#pragma unroll
-            for (int i = 0; i < BM / MN_ATOM; i++) tma_prefetch_3d(&tmA, pm0 + i * MN_ATOM, k0, pba);
-          }
-          if (!B_MN) {
-            tma_prefetch_3d(&tmB, k0, pn0, pbb);
-          } else {
-#pragma unroll
-            for (int i = 0; i < BN / MN_ATOM; i++) tma_prefetch_3d(&tmB, pn0 + i * MN_ATOM, k0, pbb);
-          }
-        }
-        if (++pkb == num_kb) {
-          pkb = 0;
-          pt += gridDim.x;
-          pf_coords();
-        }
-      };
-      const int pf_dist = args.pf_dist == 999 ? 0 : args.pf_dist;
-      if (pf_dist > 0) {
-        pf_coords();
-        for (int i = 0; i < pf_dist; i++) pf_step(i >= C::STAGES);
-      }
-      for (int t = blockIdx.x; t < num_tiles && ok && args.pf_dist != 999; t += gridDim.x) {
-        const int b = t / tiles_per_batch;
-        const int r = t - b * tiles_per_batch;
-        int mb, nb;
-        tile_coords(r, args.num_m, args.num_n, args.group_m, mb, nb);
-        const int m0 = mb * BM, n0 = nb * BN;
-        for (int kb = 0; kb < num_kb; kb++) {
-          if (pf_dist > 0) pf_step(true);
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const Unit u = decode_unit(t, args);
+        const int b = u.b;
+        const int m0 = u.mb * BM, n0 = u.nb * BN;
+        const int kb_end = min(num_kb, (u.s + 1) * args.kb_per);
+        for (int kb = u.s * args.kb_per; kb < kb_end; kb++) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, args.status, ST_GEMM_TIMEOUT, 1);
           if (!ok) break;
           uint8_t* sa = smem + stage * C::STAGE_BYTES;
@@ -724,9 +715,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tphase[buf] ^= 1;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < num_kb; kb++) {
-          if (args.pf_dist != 999)
-            ok = mbar_wait(&full_bar[stage], phase, abort_flag, args.status, ST_GEMM_TIMEOUT, 3);
+        const int slice = t / (num_tiles / args.splits);
+        const int kb_begin = slice * args.kb_per, kb_end = min(num_kb, kb_begin + args.kb_per);
+        for (int kb = kb_begin; kb < kb_end; kb++) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, args.status, ST_GEMM_TIMEOUT, 3);
           if (!ok) break;
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
@@ -745,12 +737,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                             C::BK * kSwizzleBytes, 1024)
                      : make_smem_desc_sw128(sb + k * 32, 16, 1024);
             if (ESZ == 1)
-              tc_mma_i8(d_tmem, adesc, bdesc, id, (kb | k) != 0);
+              tc_mma_i8(d_tmem, adesc, bdesc, id, (kb > kb_begin) || k != 0);
             else
-              tc_mma_f16(d_tmem, adesc, bdesc, id, (kb | k) != 0);
+              tc_mma_f16(d_tmem, adesc, bdesc, id, (kb > kb_begin) || k != 0);
           }
           tc_commit(&empty_bar[stage]);
-          if (kb == num_kb - 1) tc_commit(&tfull_bar[buf]);
+          if (kb == kb_end - 1) tc_commit(&tfull_bar[buf]);
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -772,11 +764,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, local_tile++) {
       const int buf = local_tile & 1;
-      const int b = t / tiles_per_batch;
-      const int r = t - b * tiles_per_batch;
-      int mb, nb;
-      tile_coords(r, args.num_m, args.num_n, args.group_m, mb, nb);
-      const int m0 = mb * BM, n0 = nb * BN;
+      const Unit u = decode_unit(t, args);
+      const int b = u.s * args.batch + u.b;  // slices of a split launch are stacked like batch entries
+      const int m0 = u.mb * BM, n0 = u.nb * BN;
       bool done;
       if (ESZ == 2 && args.tma_epi)
         done = epilogue_tile_tma<BN, EW>(args, cx, est, &tmC, &tmX, buf, b, m0, n0, tmem_base + buf * BN,
@@ -906,8 +896,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const int num_pairs = gridDim.x >> 1;
   const int num_kb = (args.K + C::BK - 1) / C::BK;
   // num_m / num_n count 256 x 256 pair tiles here
-  const int tiles_per_batch = args.num_m * args.num_n;
-  const int num_tiles = tiles_per_batch * args.batch;
+  const int num_tiles = args.num_m * args.num_n * args.batch * args.splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; s++) {
@@ -945,13 +934,12 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t phase = 0;
       bool ok = true;
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-        const int b = t / tiles_per_batch;
-        const int r = t - b * tiles_per_batch;
-        int mb, nb;
-        tile_coords(r, args.num_m, args.num_n, args.group_m, mb, nb);
-        const int m0 = mb * 256 + (int)cta * 128;   // this CTA's rows of A
-        const int n0 = nb * 256 + (int)cta * 128;   // this CTA's columns of B
-        for (int kb = 0; kb < num_kb; kb++) {
+        const Unit u = decode_unit(t, args);
+        const int b = u.b;
+        const int m0 = u.mb * 256 + (int)cta * 128;   // this CTA's rows of A
+        const int n0 = u.nb * 256 + (int)cta * 128;   // this CTA's columns of B
+        const int kb_end = min(num_kb, (u.s + 1) * args.kb_per);
+        for (int kb = u.s * args.kb_per; kb < kb_end; kb++) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, args.status, ST_GEMM_TIMEOUT, 11);
           if (!ok) break;
           uint8_t* sa = smem + stage * C::STAGE_BYTES;
@@ -997,7 +985,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         tphase[buf] ^= 1;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * 256;
-        for (int kb = 0; kb < num_kb; kb++) {
+        const int slice = t / (num_tiles / args.splits);
+        const int kb_begin = slice * args.kb_per, kb_end = min(num_kb, kb_begin + args.kb_per);
+        for (int kb = kb_begin; kb < kb_end; kb++) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, args.status, ST_GEMM_TIMEOUT, 13);
           if (!ok) break;
           tc_fence_after();
@@ -1011,13 +1001,13 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             const uint64_t bdesc =
                 B_MN ? make_smem_desc_sw128(sb + k * C::UMMA_K * kSwizzleBytes, C::BK * kSwizzleBytes, 1024)
                      : make_smem_desc_sw128(sb + k * 32, 16, 1024);
-            tc_mma_f16_2sm(d_tmem, adesc, bdesc, id, (kb | k) != 0);
+            tc_mma_f16_2sm(d_tmem, adesc, bdesc, id, (kb > kb_begin) || k != 0);
           }
           // free the stage in both CTAs
           const uint32_t eb = smem_u32(&empty_bar[stage]);
           tc_commit_2sm(eb);
           tc_commit_2sm(eb | kPeerBit);
-          if (kb == num_kb - 1) {
+          if (kb == kb_end - 1) {
             const uint32_t tb = smem_u32(&tfull_bar[buf]);
             tc_commit_2sm(tb);
             tc_commit_2sm(tb | kPeerBit);
@@ -1039,11 +1029,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     bool ok = true;
     for (int t = pair; t < num_tiles && ok; t += num_pairs, local_tile++) {
       const int buf = local_tile & 1;
-      const int b = t / tiles_per_batch;
-      const int r = t - b * tiles_per_batch;
-      int mb, nb;
-      tile_coords(r, args.num_m, args.num_n, args.group_m, mb, nb);
-      const int m0 = mb * 256 + (int)cta * 128, n0 = nb * 256;
+      const Unit u = decode_unit(t, args);
+      const int b = u.s * args.batch + u.b;
+      const int m0 = u.mb * 256 + (int)cta * 128, n0 = u.nb * 256;
       bool done;
       if (args.tma_epi)
         done = epilogue_tile_tma<256, EW>(args, cx, est, &tmC, &tmX, buf, b, m0, n0, tmem_base + buf * 256,
@@ -1157,7 +1145,7 @@ int launch_tc_ew(const TMaps& tm, const GemmArgs& args, int num_sms, cudaStream_
     GB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SL::BYTES));
     configured = true;
   }
-  int tiles = args.num_m * args.num_n * args.batch;
+  int tiles = args.num_m * args.num_n * args.batch * args.splits;
   int grid = tiles < num_sms ? tiles : num_sms;
   kern<<<grid, 64 + 32 * EW, SL::BYTES, stream>>>(tm.a, tm.b, tm.c, tm.x, args);
   GB_CUDA_OK(cudaGetLastError());
@@ -1195,7 +1183,7 @@ int launch_2cta(const TMaps& tm, const GemmArgs& args, int num_sms, cudaStream_t
     GB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SL::BYTES));
     configured = true;
   }
-  int tiles = args.num_m * args.num_n * args.batch;
+  int tiles = args.num_m * args.num_n * args.batch * args.splits;
   int pairs = num_sms / 2;
   if (tiles < pairs) pairs = tiles;
   cudaLaunchConfig_t cfg;
@@ -1215,15 +1203,56 @@ int launch_2cta(const TMaps& tm, const GemmArgs& args, int num_sms, cudaStream_t
   return gbh::E_OK;
 }
 
+// Sums the K slices of a split launch in slice order and writes the result in the
+// caller's type: C = (beta ? C : 0) + sum_s ws[s].
+template <typename TO>
+__global__ void splitk_finish_kernel(const float* __restrict__ ws, TO* __restrict__ C, int M, int N, int batch,
+                                     int splits, long long ldc, long long strideC, int beta) {
+  const long long per = (long long)M * N;
+  const long long total = per * batch;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < total;
+       i += (long long)gridDim.x * blockDim.x * 4) {
+    // N is a multiple of 4 here, so the four elements share a row
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; s++) {
+      const float4 v = *reinterpret_cast<const float4*>(ws + s * total + i);
+      a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+    }
+    const long long b = i / per, r = i - b * per;
+    const long long m = r / N, n = r - m * N;
+    TO* c = C + b * strideC + m * ldc + n;
+    if (beta) { a.x += (float)c[0]; a.y += (float)c[1]; a.z += (float)c[2]; a.w += (float)c[3]; }
+    c[0] = (TO)a.x; c[1] = (TO)a.y; c[2] = (TO)a.z; c[3] = (TO)a.w;
+  }
+}
+
+int g_splitk = 1;
+
+// Number of K slices for a launch with `tiles` output tiles on `slots` concurrently running
+// CTAs (or CTA pairs): the count that fills whole waves best, with a small bias towards
+// fewer slices (less workspace traffic).  1 = do not split.
+int pick_splits(long long tiles, int slots, int num_kb, long long slice_bytes, long long workspace_bytes) {
+  if (tiles * 4 > (long long)slots * 3 || num_kb < 32) return 1;
+  int best = 1;
+  double best_score = (double)tiles / slots - 0.01;
+  for (int s = 2; s <= 16; s++) {
+    if (num_kb / s < 16 || slice_bytes * s > workspace_bytes) break;
+    const long long units = tiles * s;
+    const long long waves = (units + slots - 1) / slots;
+    const double score = (double)units / (double)(waves * slots) - 0.01 * s;
+    if (score > best_score + 1e-9) { best_score = score; best = s; }
+  }
+  return best;
+}
+
 int g_num_sms = 0;
 int g_group_m = 8;
-int g_pf_dist = 0;
 int g_tma_epi = 1;
 
 // Builds the two tensor maps and launches.  esz: 2 (bf16/fp16) or 1 (int8).
 int gemm_tc(int esz, const void* A, const void* B, GemmArgs& args, int transA, int transB,
             long long lda, long long ldb, long long sA, long long sB, int force_bn,
-            cudaStream_t stream) {
+            cudaStream_t stream, void* workspace = nullptr, long long workspace_bytes = 0) {
   if (g_num_sms == 0) {
     int dev = 0;
     GB_CUDA_OK(cudaGetDevice(&dev));
@@ -1254,12 +1283,46 @@ int gemm_tc(int esz, const void* A, const void* B, GemmArgs& args, int transA, i
     use2 = force_bn == 512 || (force_bn == 0 && g_use_2cta && pair_tiles >= g_num_sms / 2 && M >= 256 &&
                                N >= 256 && (K >= 1536 || light));
   }
+  // Split-K: a product with few output tiles and a long K is cut into K slices that run as
+  // separate work units into an fp32 workspace; a second kernel adds them in slice order.
+  args.splits = 1;
+  args.kb_per = (K + atom - 1) / atom;
+  int splits = 1;
+  const bool plain = args.bias == nullptr && args.act == ACT_NONE && args.aux_mode == AUX_NONE;
+  const bool big = 2.0 * M * N * (double)K * batch >= 8e9;  // below this the second launch costs more than it saves
+  if (esz == 2 && g_splitk && force_bn == 0 && plain && big && workspace != nullptr && (N & 3) == 0 &&
+      M >= 128 && N >= 128) {
+    const int num_kb = (K + atom - 1) / atom;
+    const long long slice_bytes = (long long)M * N * batch * 4;
+    const long long t1 = (long long)((M + BM - 1) / BM) * ((N + 255) / 256) * batch;
+    const long long t2 = (long long)((M + 255) / 256) * ((N + 255) / 256) * batch;
+    const bool pair_ok = g_use_2cta && M >= 256 && N >= 256;
+    const int s2 = pair_ok ? pick_splits(t2, g_num_sms / 2, num_kb, slice_bytes, workspace_bytes) : 1;
+    const int s1 = pick_splits(t1, g_num_sms, num_kb, slice_bytes, workspace_bytes);
+    if (s2 > 1) { splits = s2; use2 = true; }
+    else if (s1 > 1) { splits = s1; use2 = false; bn = 256; }
+  }
+  void* user_C = args.C;
+  const long long user_ldc = args.ldc, user_strideC = args.strideC;
+  const int user_out = args.out_kind, user_beta = args.beta;
+  if (splits > 1) {
+    const int num_kb = (K + atom - 1) / atom;
+    args.splits = splits;
+    args.kb_per = (num_kb + splits - 1) / splits;
+    if ((long long)(splits - 1) * args.kb_per >= num_kb) {  // the last slice would be empty
+      args.splits = splits = (num_kb + args.kb_per - 1) / args.kb_per;
+    }
+    args.C = workspace;
+    args.ldc = N;
+    args.strideC = (long long)M * N;
+    args.out_kind = OUT_F32;
+    args.beta = 0;
+  }
   if (use2) bn = 128;   // each CTA of a pair stages 128 of the tile's 256 columns
   args.num_m = use2 ? (M + 255) / 256 : (M + BM - 1) / BM;
   args.num_n = use2 ? (N + 255) / 256 : (N + bn - 1) / bn;
   args.status = gbh::status_ptr();
   args.group_m = g_group_m;
-  args.pf_dist = g_pf_dist;
 
   CUtensorMapDataType dt = esz == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                     : (args.in_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -1271,24 +1334,28 @@ int gemm_tc(int esz, const void* A, const void* B, GemmArgs& args, int transA, i
   // Results of 16-bit kernels leave through shared memory and TMA stores when the output
   // (and the auxiliary tensor) can be described by a tensor map and nothing is accumulated.
   args.tma_epi = 0;
-  if (esz == 2 && g_tma_epi && args.out_kind != OUT_F32 && !args.beta) {
+  const bool f32_out = args.out_kind == OUT_F32;
+  if (esz == 2 && g_tma_epi && !args.beta && !(f32_out && (args.act != ACT_NONE || args.aux_mode != AUX_NONE))) {
+    const int osz = f32_out ? 4 : 2;
     auto mappable = [&](const void* p, long long ld, long long bs) {
-      return (((uintptr_t)p & 15) == 0) && (ld % 8 == 0) && (batch == 1 || bs % 8 == 0);
+      return (((uintptr_t)p & 15) == 0) && (ld * osz % 16 == 0) && (bs * osz % 16 == 0);
     };
     bool ok = mappable(args.C, args.ldc, args.strideC) &&
               (args.aux_mode == AUX_NONE || mappable(args.aux, args.ldaux, args.strideAux));
     if (ok) {
-      auto encode_out = [&](CUtensorMap* m, const void* p, long long ld, long long bs) {
-        uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)batch};
-        uint64_t strides[2] = {(uint64_t)ld * 2, (uint64_t)(batch > 1 ? bs : (long long)M * ld) * 2};
-        uint32_t box[3] = {32, 32, 1};
-        return gbh::encode_tmap(m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, p, dims, strides, box,
-                                CU_TENSOR_MAP_SWIZZLE_64B);
+      // a split launch stacks its K slices like batch entries
+      const int nb = batch * args.splits;
+      auto encode_out = [&](CUtensorMap* m, const void* p, long long ld, long long bs, int sz) {
+        uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)nb};
+        uint64_t strides[2] = {(uint64_t)ld * sz, (uint64_t)(nb > 1 ? bs : (long long)M * ld) * sz};
+        uint32_t box[3] = {(uint32_t)(64 / sz), 32, 1};
+        return gbh::encode_tmap(m, sz == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, p,
+                                dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
       };
-      int rc = encode_out(&tm.c, args.C, args.ldc, args.strideC);
+      int rc = encode_out(&tm.c, args.C, args.ldc, args.strideC, osz);
       if (rc) return rc;
       if (args.aux_mode != AUX_NONE) {
-        rc = encode_out(&tm.x, args.aux, args.ldaux, args.strideAux);
+        rc = encode_out(&tm.x, args.aux, args.ldaux, args.strideAux, 2);
         if (rc) return rc;
       }
       args.tma_epi = 1;
@@ -1328,32 +1395,54 @@ int gemm_tc(int esz, const void* A, const void* B, GemmArgs& args, int transA, i
     int rc = gbh::encode_tmap(&tmB, dt, 3, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   }
+  int rc;
   if (use2) {
-    if (!a_mn && !b_mn) return launch_2cta<false, false>(tm, args, g_num_sms, stream);
-    if (!a_mn && b_mn) return launch_2cta<false, true>(tm, args, g_num_sms, stream);
-    if (a_mn && !b_mn) return launch_2cta<true, false>(tm, args, g_num_sms, stream);
-    return launch_2cta<true, true>(tm, args, g_num_sms, stream);
+    if (!a_mn && !b_mn) rc = launch_2cta<false, false>(tm, args, g_num_sms, stream);
+    else if (!a_mn && b_mn) rc = launch_2cta<false, true>(tm, args, g_num_sms, stream);
+    else if (a_mn && !b_mn) rc = launch_2cta<true, false>(tm, args, g_num_sms, stream);
+    else rc = launch_2cta<true, true>(tm, args, g_num_sms, stream);
+  } else if (esz == 2) {
+    if (bn == 256) rc = dispatch_major<2, 256>(a_mn, b_mn, tm, args, g_num_sms, stream);
+    else rc = dispatch_major<2, 128>(a_mn, b_mn, tm, args, g_num_sms, stream);
+  } else {
+    if (bn == 256) rc = dispatch_major<1, 256>(a_mn, b_mn, tm, args, g_num_sms, stream);
+    else rc = dispatch_major<1, 128>(a_mn, b_mn, tm, args, g_num_sms, stream);
   }
-  if (esz == 2) {
-    if (bn == 256) return dispatch_major<2, 256>(a_mn, b_mn, tm, args, g_num_sms, stream);
-    return dispatch_major<2, 128>(a_mn, b_mn, tm, args, g_num_sms, stream);
+  if (rc != gbh::E_OK || splits == 1) return rc;
+  {
+    const long long quads = (long long)M * N * batch / 4;
+    const int grid = (int)(quads + 255) / 256 < g_num_sms * 8 ? (int)((quads + 255) / 256) : g_num_sms * 8;
+    const float* ws = (const float*)workspace;
+    if (user_out == OUT_F32)
+      splitk_finish_kernel<float><<<grid, 256, 0, stream>>>(ws, (float*)user_C, M, N, batch, splits, user_ldc,
+                                                            user_strideC, user_beta);
+    else if (user_out == OUT_BF16)
+      splitk_finish_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(ws, (__nv_bfloat16*)user_C, M, N, batch,
+                                                                    splits, user_ldc, user_strideC, user_beta);
+    else
+      splitk_finish_kernel<__half><<<grid, 256, 0, stream>>>(ws, (__half*)user_C, M, N, batch, splits,
+                                                             user_ldc, user_strideC, user_beta);
+    GB_CUDA_OK(cudaGetLastError());
   }
-  if (bn == 256) return dispatch_major<1, 256>(a_mn, b_mn, tm, args, g_num_sms, stream);
-  return dispatch_major<1, 128>(a_mn, b_mn, tm, args, g_num_sms, stream);
+  return gbh::E_OK;
 }
 
 }  // namespace
 
 // Tuning knobs: epilogue warps (4 or 8) and rasterisation group height (row blocks).
-GB_EXPORT int gb_gemm_tune(int epi_warps, int group_m, int pf_dist) {
+GB_EXPORT int gb_gemm_tune(int epi_warps, int group_m) {
   if (epi_warps == 4 || epi_warps == 8) g_epi_warps = epi_warps;
   if (group_m >= 1) g_group_m = group_m;
-  if (pf_dist >= 0) g_pf_dist = pf_dist;
   return 0;
 }
 // Enables (1) or disables (0) the automatic choice of the two-CTA kernel.
 GB_EXPORT int gb_gemm_use_2cta(int on) {
   g_use_2cta = on;
+  return 0;
+}
+// Enables (1) or disables (0) split-K for products with few output tiles.
+GB_EXPORT int gb_gemm_splitk(int on) {
+  g_splitk = on;
   return 0;
 }
 // Enables (1) or disables (0) the shared-memory + TMA-store epilogue of the 16-bit kernels.
@@ -1374,7 +1463,7 @@ GB_EXPORT int gb_gemm16(const void* A, const void* B, void* C, const void* bias,
                         long long lda, long long ldb, long long ldc, long long ldaux,
                         long long sA, long long sB, long long sC, long long sAux, int in_dtype,
                         int out_dtype, int act, int aux_mode, int beta, float alpha, int force_bn,
-                        void* stream) {
+                        void* workspace, long long workspace_bytes, void* stream) {
   if (in_dtype != DT_BF16 && in_dtype != DT_F16) {
     gbh::set_error("gb_gemm16: inputs must be bf16 or fp16");
     return gbh::E_BAD_ARG;
@@ -1393,7 +1482,8 @@ GB_EXPORT int gb_gemm16(const void* A, const void* B, void* C, const void* bias,
   a.act = act; a.aux_mode = aux ? aux_mode : AUX_NONE; a.beta = beta; a.alpha = alpha;
   a.out_kind = out_dtype == DT_F32 ? OUT_F32 : (out_dtype == DT_BF16 ? OUT_BF16 : OUT_F16);
   a.in_bf16 = in_dtype == DT_BF16;
-  return gemm_tc(2, A, B, a, transA, transB, lda, ldb, sA, sB, force_bn, (cudaStream_t)stream);
+  return gemm_tc(2, A, B, a, transA, transB, lda, ldb, sA, sB, force_bn, (cudaStream_t)stream, workspace,
+                 workspace_bytes);
 }
 
 // int8 x int8 -> int32 GEMM with the dequantising epilogue of the reference's

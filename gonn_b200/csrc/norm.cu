@@ -15,6 +15,15 @@ namespace {
 template <typename T> struct IO;
 template <> struct IO<__nv_bfloat16> {
   static constexpr int V = 8;
+  using Raw = uint4;
+  static __device__ __forceinline__ Raw ldraw(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+  static __device__ __forceinline__ void unpack(const Raw& u, float* f) {
+    float2 a;
+    a = unpack_bf16(u.x); f[0] = a.x; f[1] = a.y;
+    a = unpack_bf16(u.y); f[2] = a.x; f[3] = a.y;
+    a = unpack_bf16(u.z); f[4] = a.x; f[5] = a.y;
+    a = unpack_bf16(u.w); f[6] = a.x; f[7] = a.y;
+  }
   static __device__ __forceinline__ void ld(const __nv_bfloat16* p, float* f) {
     uint4 u = *reinterpret_cast<const uint4*>(p);
     float2 a;
@@ -32,6 +41,15 @@ template <> struct IO<__nv_bfloat16> {
 };
 template <> struct IO<__half> {
   static constexpr int V = 8;
+  using Raw = uint4;
+  static __device__ __forceinline__ Raw ldraw(const __half* p) { return *reinterpret_cast<const uint4*>(p); }
+  static __device__ __forceinline__ void unpack(const Raw& u, float* f) {
+    float2 a;
+    a = unpack_f16(u.x); f[0] = a.x; f[1] = a.y;
+    a = unpack_f16(u.y); f[2] = a.x; f[3] = a.y;
+    a = unpack_f16(u.z); f[4] = a.x; f[5] = a.y;
+    a = unpack_f16(u.w); f[6] = a.x; f[7] = a.y;
+  }
   static __device__ __forceinline__ void ld(const __half* p, float* f) {
     uint4 u = *reinterpret_cast<const uint4*>(p);
     float2 a;
@@ -49,6 +67,11 @@ template <> struct IO<__half> {
 };
 template <> struct IO<float> {
   static constexpr int V = 4;
+  using Raw = float4;
+  static __device__ __forceinline__ Raw ldraw(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void unpack(const Raw& u, float* f) {
+    f[0] = u.x; f[1] = u.y; f[2] = u.z; f[3] = u.w;
+  }
   static __device__ __forceinline__ void ld(const float* p, float* f) {
     float4 u = *reinterpret_cast<const float4*>(p);
     f[0] = u.x; f[1] = u.y; f[2] = u.z; f[3] = u.w;
@@ -158,7 +181,7 @@ norm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, const TW* __r
 // the group visits, then combined across the groups of the CTA in shared
 // memory and written to part[blockIdx.x][2][D].
 template <typename T, typename TW, int G, int VPT, bool RMS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 norm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TW* __restrict__ w,
                 const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                 T* __restrict__ dx, float* __restrict__ part, long long rows, int D) {
@@ -174,57 +197,49 @@ norm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TW* __r
 #pragma unroll
     for (int j = 0; j < V; j++) { dg[i][j] = 0.f; db[i][j] = 0.f; }
 
-  float wr[VPT][V];
-#pragma unroll
-  for (int i = 0; i < VPT; i++) {
-    const int vi = t + i * G;
-#pragma unroll
-    for (int j = 0; j < V; j++) wr[i][j] = (w && vi < nvec) ? (float)w[vi * V + j] : 1.f;
-  }
+  using Raw = typename IO<T>::Raw;
   const long long stride = (long long)gridDim.x * gpb;
   long long row = (long long)blockIdx.x * gpb + g;
-  // software pipeline: the loads of the next row are issued before this row's arithmetic
-  float an[VPT][V], dn[VPT][V];
-  auto fetch = [&](long long r) {
+  // Rows stay packed in registers (the arithmetic unpacks them twice) so that the next
+  // row's loads can be in flight during this row's reductions without pushing the
+  // register count past two CTAs per SM.
+  Raw ax[VPT], ad[VPT], nx[VPT], nd[VPT];
+  auto fetch = [&](long long r, Raw* px, Raw* pd) {
 #pragma unroll
     for (int i = 0; i < VPT; i++) {
       const int vi = t + i * G;
       if (vi < nvec && r < rows) {
-        IO<T>::ld(x + r * D + vi * V, an[i]);
-        IO<T>::ld(dy + r * D + vi * V, dn[i]);
-      } else {
-#pragma unroll
-        for (int j = 0; j < V; j++) { an[i][j] = 0.f; dn[i][j] = 0.f; }
+        px[i] = IO<T>::ldraw(x + r * D + vi * V);
+        pd[i] = IO<T>::ldraw(dy + r * D + vi * V);
       }
     }
   };
-  fetch(row);
+  constexpr bool PF = VPT * V <= 24;  // wider rows would spill with two rows resident
+  if (PF) fetch(row, ax, ad);
   for (; row < rows; row += stride) {
     const float mean = RMS ? 0.f : mean_in[row];
     const float rstd = rstd_in[row];
-    float xh[VPT][V], gy[VPT][V];
+    if (PF) fetch(row + stride, nx, nd);
+    else fetch(row, ax, ad);
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; i++) {
       const int vi = t + i * G;
       if (vi < nvec) {
+        float a[V], d[V];
+        IO<T>::unpack(ax[i], a);
+        IO<T>::unpack(ad[i], d);
 #pragma unroll
         for (int j = 0; j < V; j++) {
-          float h = (an[i][j] - mean) * rstd;
-          float gw = dn[i][j] * wr[i][j];
-          xh[i][j] = h;
-          gy[i][j] = gw;
+          const float h = (a[j] - mean) * rstd;
+          const float gw = w ? d[j] * (float)w[vi * V + j] : d[j];
           s1 += gw;
           s2 += gw * h;
-          dg[i][j] += dn[i][j] * h;
-          db[i][j] += dn[i][j];
+          dg[i][j] += d[j] * h;
+          db[i][j] += d[j];
         }
-      } else {
-#pragma unroll
-        for (int j = 0; j < V; j++) { xh[i][j] = 0.f; gy[i][j] = 0.f; }
       }
     }
-    fetch(row + stride);
     if (!RMS) s1 = group_sum<G>(s1, red);
     s2 = group_sum<G>(s2, red);
     const float m1 = RMS ? 0.f : s1 / D, m2 = s2 / D;
@@ -232,11 +247,21 @@ norm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TW* __r
     for (int i = 0; i < VPT; i++) {
       const int vi = t + i * G;
       if (vi < nvec) {
-        float o[V];
+        float a[V], d[V], o[V];
+        IO<T>::unpack(ax[i], a);
+        IO<T>::unpack(ad[i], d);
 #pragma unroll
-        for (int j = 0; j < V; j++) o[j] = rstd * (gy[i][j] - m1 - xh[i][j] * m2);
+        for (int j = 0; j < V; j++) {
+          const float h = (a[j] - mean) * rstd;
+          const float gw = w ? d[j] * (float)w[vi * V + j] : d[j];
+          o[j] = rstd * (gw - m1 - h * m2);
+        }
         IO<T>::st(dx + row * D + vi * V, o);
       }
+    }
+    if (PF) {
+#pragma unroll
+      for (int i = 0; i < VPT; i++) { ax[i] = nx[i]; ad[i] = nd[i]; }
     }
   }
   if (part == nullptr) return;

@@ -180,17 +180,26 @@ col_reduce_vec_kernel(const T* __restrict__ x, TO* __restrict__ y, float* __rest
   }
 }
 
+// Combines the per-split partial results: CTA = 32 columns x 8 split lanes, fixed order.
 template <typename CT, typename TO, int OP>
 __global__ void col_finish_kernel(const CT* __restrict__ part, TO* __restrict__ y, long long R,
-                                  long long inner, int splits, long long total, int accumulate) {
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= total) return;
-  const long long o = i / inner, col = i % inner;
+                                  long long inner, int splits, long long outer, int accumulate) {
+  __shared__ CT sm[8][33];
+  const long long col = (long long)blockIdx.x * 32 + threadIdx.x;
+  const long long o = blockIdx.y;
   CT a = r_init<CT, OP>();
-  for (int s = 0; s < splits; s++) a = r_comb<CT, OP>(a, part[(o * splits + s) * inner + col]);
-  if (OP == R_MEAN) a = a / (CT)R;
-  if (accumulate) a += (CT)y[i];
-  y[i] = (TO)a;
+  if (col < inner)
+    for (int s = threadIdx.y; s < splits; s += 8) a = r_comb<CT, OP>(a, part[(o * splits + s) * inner + col]);
+  sm[threadIdx.y][threadIdx.x] = a;
+  __syncthreads();
+  if (threadIdx.y == 0 && col < inner) {
+#pragma unroll
+    for (int k = 1; k < 8; k++) a = r_comb<CT, OP>(a, sm[k][threadIdx.x]);
+    if (OP == R_MEAN) a = a / (CT)R;
+    const long long i = o * inner + col;
+    if (accumulate) a += (CT)y[i];
+    y[i] = (TO)a;
+  }
 }
 
 template <typename T, int OP>
@@ -261,8 +270,8 @@ int reduce_t(int op, const void* x, void* y, void* scratch, long long scratch_by
       if (vec) launch_col_vec<T, TO, OPID>(grid, blk, s, x, y, scratch, R, inner, splits, two ? 1 : 0); \
       else col_reduce_kernel<T, TO, OPID><<<grid, blk, 0, s>>>((const T*)x, (TO*)y, (CT*)scratch, R, inner, splits, two ? 1 : 0); \
       if (two) {                                                                                     \
-        long long total = outer * inner;                                                             \
-        col_finish_kernel<CT, TO, OPID><<<(unsigned)((total + 255) / 256), 256, 0, s>>>((const CT*)scratch, (TO*)y, R, inner, splits, total, accumulate); \
+        dim3 fgrid((unsigned)((inner + 31) / 32), (unsigned)outer);                                  \
+        col_finish_kernel<CT, TO, OPID><<<fgrid, dim3(32, 8), 0, s>>>((const CT*)scratch, (TO*)y, R, inner, splits, outer, accumulate); \
       }                                                                                              \
     }                                                                                                \
     break;

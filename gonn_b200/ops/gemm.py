@@ -43,6 +43,21 @@ def _dact_ref(pre, mode):
     return g
 
 
+_WS_BYTES = 256 << 20
+_ws_cache = {}
+
+
+def _workspace(device: torch.device) -> torch.Tensor:
+    """fp32 scratch for split-K partial products, one per (device, stream) so that launches
+    on different streams never share it."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _ws_cache.get(key)
+    if buf is None:
+        buf = torch.empty(_WS_BYTES, dtype=torch.uint8, device=device)
+        _ws_cache[key] = buf
+    return buf
+
+
 def _gemm_ref(a, b, trans_a, trans_b, bias, act, aux, aux_mode, out_dtype, beta, out, alpha):
     """Oracle path (CPU, or any dtype the kernels do not take): fp32/fp64 math in torch."""
     ct = torch.float64 if a.dtype == torch.float64 else torch.float32
@@ -177,13 +192,18 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         bias = bias.contiguous()
     if out.dtype not in (a.dtype, torch.float32):
         raise TypeError("gemm: out dtype must be the input dtype or float32")
+    # split-K scratch: only products with a long K and few output tiles use it
+    ws = None
+    if K >= 2048 and bias is None and not ACT[act] and not am and M * N * batch * 4 * 2 <= _WS_BYTES:
+        ws = _workspace(a.device)
     _l.call("gb_gemm16", _l.ptr(a2), _l.ptr(b2), _l.ptr(out), _l.ptr(bias), _l.I(bias_f32),
             _l.ptr(aux), _l.I(M), _l.I(N), _l.I(K), _l.I(batch), _l.I(int(trans_a)),
             _l.I(int(trans_b)), _l.L(lda), _l.L(ldb), _l.L(out.stride(-2)),
             _l.L(aux.stride(-2) if aux is not None else 0), _l.L(sA), _l.L(sB), _l.L(sC),
             _l.L(aux.stride(0) if (aux is not None and batched) else 0),
             _l.I(_l.dtype_code(a.dtype)), _l.I(_l.dtype_code(out.dtype)), _l.I(ACT[act]), _l.I(am),
-            _l.I(int(beta)), _l.F(alpha), _l.I(force_bn), _l.stream_ptr())
+            _l.I(int(beta)), _l.F(alpha), _l.I(force_bn), _l.ptr(ws), _l.L(_WS_BYTES if ws is not None else 0),
+            _l.stream_ptr())
     return out
 
 

@@ -54,8 +54,6 @@ def main(argv):
         elif epi == "bias_res":
             kw = dict(bias=torch.randn(N, device=dev, dtype=torch.bfloat16),
                       aux=torch.randn(M, N, device=dev, dtype=torch.bfloat16), aux_mode="add")
-        elif epi == "noload":
-            lib.lib().gb_gemm_tune(8, 8, 999)
         elif epi == "pair":
             kw = dict(force_bn=512)  # the two-CTA (256 x 256 per SM pair) kernel
         ms = _time(lambda: gemm(a, b, trans_a=ta, trans_b=tb, out=out, **kw))
