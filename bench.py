@@ -49,17 +49,17 @@ CONFIGS = {
 
 
 def reference_arm(args):
-    # The reference is a Go module.  `pip install --no-index --target baseline/_ref
-    # /root/reference` stops with "Neither 'setup.py' nor 'pyproject.toml' found", no Go
-    # toolchain or module cache exists offline, and the reference has no GPU training path
-    # and publishes no training-throughput number: this metric cannot be produced by it here.
+    # The reference is a Go module.  An offline `pip install --target baseline/_ref` of its
+    # source tree stops with "Neither 'setup.py' nor 'pyproject.toml' found", no Go toolchain
+    # or module cache exists offline, and the reference has no GPU training path and publishes
+    # no training-throughput number: this metric cannot be produced by it here.
     print(json.dumps({"impl": "reference",
                       "unavailable": "reference is a Go module (not pip-installable, no Go toolchain "
                                      "offline) and has no GPU training path for tokens/s"}))
     return 0
 
 
-def build(cfg_name, device, dtype, batch):
+def build(cfg_name, device, dtype, batch, world=1):
     import torch
     from gonn_b200.models import GPT, TransformerLM
     torch.manual_seed(1234)
@@ -71,7 +71,8 @@ def build(cfg_name, device, dtype, batch):
                     dtype=dtype, device=device)
     else:
         from gonn_b200.models.cnn import SmallCNN
-        model = SmallCNN(dtype=dtype, device=device)
+        # several ranks: batch statistics are exchanged inside the normalisation kernels
+        model = SmallCNN(sync_bn=world > 1, dtype=dtype, device=device)
     return model
 
 
@@ -101,7 +102,7 @@ def main():
     B = args.batch or cfg["batch"]
     S, V = cfg["seq"], cfg["vocab"]
     dtype = torch.bfloat16
-    model = build(args.config, device, dtype, B)
+    model = build(args.config, device, dtype, B, world)
     from gonn_b200.distributed.ddp import DistributedDataParallel
     ddp = DistributedDataParallel(model, optimizer=dict(kind="adamw", lr=3e-4, weight_decay=0.1,
                                                         betas=(0.9, 0.999), eps=1e-8))
@@ -179,7 +180,8 @@ def main():
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "impl": "ours",
-            "config": {"model": cfg["model"], "global_batch": B * world, "seq_len": S,
+            "config": {"model": cfg["model"] + ("+syncbn" if args.config == "cnn" and world > 1 else ""),
+                       "global_batch": B * world, "seq_len": S,
                        "parallelism": f"dp{world}" + ("+zero1-fused-rs-adamw-ag" if world >= 1 else ""),
                        "optimizer": "adamw lr3e-4 wd0.1 (fp32 master, sharded 1/W)",
                        "cache": "per-step working set (weights, activations, logits) is > 1 GB, far "

@@ -58,7 +58,7 @@ struct StepArgs {
   long long param_off;       // byte offset of the bucket's parameters (mode 1)
   long long n;               // elements in the bucket (multiple of world * 8)
   int mode;                  // 0: all-reduce-mean into the gradients; 1: sharded AdamW + all-gather
-  int dtype_bf16;            // 16-bit flavour: 1 bf16, 0 fp16
+  int dtype_bf16;            // element type: 0 fp16, 1 bf16, 2 fp32 (mode 0 only)
   unsigned int epoch;        // barrier epochs epoch (start) and epoch+1 (end)
   float* master[kMaxWorld];  // per emulated rank (index 0 in real runs): fp32 shard state
   float* m[kMaxWorld];
@@ -95,8 +95,9 @@ fused_step_kernel(const StepArgs a) {
   __syncthreads();
   if (W > 1 && !cta_barrier(a.pt, rank, W, 0, cta, a.epoch, a.status, &sm_flag)) return;
 
+  const int epv = a.dtype_bf16 == 2 ? 4 : 8;  // elements per 16-byte vector
   const long long L = a.n / W;          // elements in one rank's slice
-  const long long nvec = L / 8;         // 16-byte vectors in the slice
+  const long long nvec = L / epv;       // 16-byte vectors in the slice
   const long long per = (nvec + G - 1) / G;
   const long long v0 = (long long)cta * per;
   const long long v1 = min(v0 + per, nvec);
@@ -107,6 +108,23 @@ fused_step_kernel(const StepArgs a) {
   float* mm = a.m[sidx];
   float* vv = a.v[sidx];
 
+  if (a.dtype_bf16 == 2) {
+    // fp32 all-reduce (mode 0): the same two-shot scheme on vectors of four floats
+    for (long long i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int p = 0; p < W; p++) {
+        const float4 u = __ldcg((const float4*)((const char*)a.pt.base[p] + a.grad_off) + slice_vec0 + i);
+        acc.x += u.x; acc.y += u.y; acc.z += u.z; acc.w += u.w;
+      }
+      acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+      for (int p = 0; p < W; p++) {
+        const int q = (rank + 1 + p) % W;
+        ((float4*)((char*)a.pt.base[q] + a.grad_off))[slice_vec0 + i] = acc;
+      }
+    }
+    if (W > 1) cta_barrier(a.pt, rank, W, 1, cta, a.epoch + 1, a.status, &sm_flag);
+    return;
+  }
   for (long long i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
     float acc[8];
 #pragma unroll
@@ -366,6 +384,10 @@ GB_EXPORT int gb_comm_fused_step(int mode, int dtype_bf16, long long grad_off, l
   const int W = g_comm.world;
   if (n % ((long long)W * 8) != 0) {
     gbh::set_error("gb_comm_fused_step: bucket length %lld is not a multiple of world*8", n);
+    return gbh::E_BAD_ARG;
+  }
+  if (dtype_bf16 == 2 && mode != 0) {
+    gbh::set_error("gb_comm_fused_step: fp32 buckets support the all-reduce mode only");
     return gbh::E_BAD_ARG;
   }
   if (ctas < 1) ctas = 1;

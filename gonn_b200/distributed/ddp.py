@@ -91,9 +91,14 @@ class DistributedDataParallel(torch.nn.Module):
             raise ValueError("DistributedDataParallel: the module has no trainable parameters")
         dt = params[0].dtype
         dev = params[0].device
-        if dt not in (torch.bfloat16, torch.float16):
-            raise TypeError("DistributedDataParallel: parameters must be bf16/fp16; use "
-                            "distributed.Group (TCP) for fp32 / fp64 data parallelism")
+        if dt == torch.float32:
+            if optimizer is not None:
+                raise TypeError("DistributedDataParallel: the fused sharded optimizer needs bf16/fp16 "
+                                "parameters; fp32 parameters are all-reduced (optimizer=None)")
+        elif dt not in (torch.bfloat16, torch.float16):
+            raise TypeError("DistributedDataParallel: parameters must be bf16/fp16/fp32; use "
+                            "distributed.Group (TCP) for fp64 data parallelism")
+        self._esz = 4 if dt == torch.float32 else 2
         self.host = dev.type != "cuda"
         if self.host and world != 1:
             raise TypeError("DistributedDataParallel: multi-rank runs need CUDA devices")
@@ -104,7 +109,7 @@ class DistributedDataParallel(torch.nn.Module):
 
         # ---- layout -------------------------------------------------------------------
         align = world * 8
-        limit = max(int(bucket_mb * (1 << 20) / 2), align)
+        limit = max(int(bucket_mb * (1 << 20) / self._esz), align)
         self.buckets: List[_Bucket] = []
         self._where: Dict[int, tuple] = {}
         off = 0
@@ -126,7 +131,7 @@ class DistributedDataParallel(torch.nn.Module):
             cur.length = off - cur.start
             self.buckets.append(cur)
         self.total = off
-        nbytes = self.total * 2
+        nbytes = self.total * self._esz
         self._param_off = _SLOT_BYTES
         self._grad_off = _SLOT_BYTES + (nbytes + 255) // 256 * 256
         self.symm = SymmetricMemory(self._grad_off + nbytes, rank, world, process_group, device=dev)
@@ -145,7 +150,7 @@ class DistributedDataParallel(torch.nn.Module):
                 p.register_post_accumulate_grad_hook(self._autograd_hook)
         if world > 1:
             # every rank starts from rank 0's values (BroadcastParams of the reference)
-            self.symm.broadcast(0, self._param_off, self.total * 2)
+            self.symm.broadcast(0, self._param_off, self.total * self._esz)
             torch.cuda.synchronize()
 
         self._fresh = {id(p): True for p in params}
@@ -225,8 +230,8 @@ class DistributedDataParallel(torch.nn.Module):
         b.launched = True
         if self.world == 1 and self.opt is None:
             return  # nothing to reduce and nobody to update
-        args = (1 if self.opt is not None else 0, self.dtype, self._grad_off + b.start * 2,
-                self._param_off + b.start * 2, b.length, b.master, b.m, b.v, self._hyper(), self.comm_ctas)
+        args = (1 if self.opt is not None else 0, self.dtype, self._grad_off + b.start * self._esz,
+                self._param_off + b.start * self._esz, b.length, b.master, b.m, b.v, self._hyper(), self.comm_ctas)
         if self.host:
             self.symm.fused_step(*args)
             return

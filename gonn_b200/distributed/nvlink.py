@@ -113,10 +113,20 @@ class SymmetricMemory:
             xs = x if isinstance(x, (list, tuple)) else [x]
             return (ctypes.c_void_p * len(xs))(*[t.data_ptr() for t in xs])
         hy = (ctypes.c_float * 8)(*[float(h) for h in hyper])
-        _l.call("gb_comm_fused_step", _l.I(mode), _l.I(1 if dtype == torch.bfloat16 else 0),
+        code = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[dtype]
+        _l.call("gb_comm_fused_step", _l.I(mode), _l.I(code),
                 _l.L(self.abs_offset(grad_off)), _l.L(self.abs_offset(param_off)), _l.L(n),
                 arr(master), arr(m), arr(v), hy, _l.I(ctas), _l.I(1 if self.emulate else 0),
                 _l.stream_ptr())
+
+    def all_reduce(self, offset_bytes: int, n: int, dtype: torch.dtype, op: str = "sum", ctas: int = 64):
+        """In-place all-reduce (``sum`` or ``mean``) of ``n`` elements at ``offset_bytes`` of
+        every rank's symmetric buffer: two-shot (each rank reduces one slice in rank order
+        through peer loads and writes it back to every peer).  ``n`` must be a multiple of
+        ``world * 8``; fp16 / bf16 / fp32."""
+        scale = float(self.world) if op == "sum" else 1.0
+        self.fused_step(0, dtype, offset_bytes, offset_bytes, n, None, None, None,
+                        [0, 0, 0, 0, 0, 1, 1, scale], ctas)
 
     def _fused_step_host(self, mode, dtype, grad_off, param_off, n, master, m, v, hyper):
         """Single-rank restatement of the kernel's arithmetic (fp32, same operation order)."""

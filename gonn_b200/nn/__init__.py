@@ -28,7 +28,7 @@ from .hooks import (RegisterForwardPreHook, RegisterForwardHook, RegisterFullBac
                     RegisterModuleForwardPreHook, RegisterModuleForwardHook, RegisterModuleFullBackwardHook,
                     RemoveModuleHook, Call)
 from .stateless import (WithReplacedParams, FunctionalCall, FunctionalCallMulti, FunctionalCallGrad,  # noqa
-                        FunctionalCallGradMulti)
+                        FunctionalCallGradMulti, WithGradsToReplacements)
 from .lazy import *  # noqa
 from .lazy import IsLazy  # noqa
 from .fuse import FuseConvBNEval, FuseLinearBNEval  # noqa

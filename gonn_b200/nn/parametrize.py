@@ -160,6 +160,10 @@ class InvertibleParametrization(Parametrization):
         return self.Inv(v)
 
 
+# the reference's name for the same contract (nn/parametrize_generic.go:57-80)
+ParametrizationWithInverse = InvertibleParametrization
+
+
 def _as_param(p):
     return p if isinstance(p, Parametrization) else ParametrizationFunc(p)
 

@@ -40,17 +40,34 @@ def FunctionalCallMulti(module: torch.nn.Module, replace: Dict[str, torch.Tensor
     return torch.func.functional_call(module, dict(replace), inputs)
 
 
+def WithGradsToReplacements():
+    """Option for ``FunctionalCallGrad`` / ``FunctionalCallGradMulti``: besides returning the
+    gradients by name, accumulate each one into the ``.grad`` of the tensor that replaced the
+    parameter (allocated when missing), the way ``torch.func.functional_call`` users expect
+    (nn/stateless.go:144-152).  The module's own parameters keep their ``.grad`` untouched."""
+    return "grads_to_replacements"
+
+
+def _harvest(rep, replace, loss, opts):
+    grads = torch.autograd.grad(loss, list(rep.values()), allow_unused=True)
+    out = {k: g for k, g in zip(rep, grads) if g is not None}
+    if "grads_to_replacements" in opts:
+        for k, g in out.items():
+            t = replace[k]
+            t.grad = g.detach().clone() if t.grad is None else t.grad + g.detach()
+    return out
+
+
 def FunctionalCallGrad(module: torch.nn.Module, x, replace: Dict[str, torch.Tensor],
-                       loss_fn: Callable[[torch.Tensor], torch.Tensor]):
-    """Returns (loss, {name: dloss/dreplacement})."""
+                       loss_fn: Callable[[torch.Tensor], torch.Tensor], *opts):
+    """Returns (loss, {name: dloss/dreplacement}); parameters that received no gradient are
+    omitted (nn/stateless.go:214-231)."""
     rep = {k: v.detach().clone().requires_grad_(True) for k, v in replace.items()}
     loss = loss_fn(FunctionalCall(module, x, rep))
-    grads = torch.autograd.grad(loss, list(rep.values()), allow_unused=True)
-    return loss.detach(), {k: g for k, g in zip(rep, grads)}
+    return loss.detach(), _harvest(rep, replace, loss, opts)
 
 
-def FunctionalCallGradMulti(module, replace, loss_fn, *inputs):
+def FunctionalCallGradMulti(module, replace, loss_fn, *inputs, opts=()):
     rep = {k: v.detach().clone().requires_grad_(True) for k, v in replace.items()}
     loss = loss_fn(FunctionalCallMulti(module, rep, *inputs))
-    grads = torch.autograd.grad(loss, list(rep.values()), allow_unused=True)
-    return loss.detach(), {k: g for k, g in zip(rep, grads)}
+    return loss.detach(), _harvest(rep, replace, loss, tuple(opts))

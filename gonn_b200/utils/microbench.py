@@ -1,0 +1,228 @@
+"""Micro-benchmarks of the kernels, one JSON line per measurement.
+
+    python -m gonn_b200.utils.microbench gemm
+    python -m gonn_b200.utils.microbench elementwise
+    python -m gonn_b200.utils.microbench flash
+    python -m gonn_b200.utils.microbench norm
+    python -m gonn_b200.utils.microbench mlp                      # CPU, config of the reference's quick start
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
+        -m gonn_b200.utils.microbench allreduce                   # bus-bandwidth sweep, NVLink kernels vs NCCL
+
+The shapes are the ones the reference's own benchmark programs use (square matmul
+N = 256..2048 of benchmark/gonn/main.go, elementwise add / relu at 1e6 and 1e7 elements,
+attention at (BH, S, d) = (16, 2048, 64), (32, 1024, 64), (64, 512, 64) of
+benchmark/flashattn/main.go) plus the shapes of the transformer configurations.
+
+Timing: CUDA events around every call, 3 warm-up calls, the median of the timed calls;
+a 256 MB buffer is rewritten between calls so that no operand is served from L2.  Every
+line carries the same measurement of the stock PyTorch op for comparison.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+import statistics
+import sys
+import time
+
+import torch
+
+_flush_buf = None
+
+
+def _flush():
+    global _flush_buf
+    if _flush_buf is None:
+        _flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _flush_buf.zero_()
+
+
+def timeit(fn, iters: int = 10, flush: bool = True) -> float:
+    """Median device time of ``fn`` in milliseconds."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush:
+            _flush()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return statistics.median(times)
+
+
+def _emit(**kw):
+    print(json.dumps(kw), flush=True)
+
+
+def bench_gemm():
+    from ..ops.gemm import gemm
+    shapes = [(n, n, n, "nt") for n in (256, 512, 1024, 2048, 4096, 8192)]
+    shapes += [(16384, 768, 768, "nt"), (16384, 2304, 768, "nt"), (16384, 3072, 768, "nt"),
+               (16384, 768, 3072, "nt"), (16384, 32000, 768, "nt"), (16384, 768, 3072, "nn"),
+               (768, 3072, 16384, "tn"), (2304, 768, 16384, "tn"), (8192, 8192, 2048, "nt"),
+               (8192, 2048, 8192, "nn"), (8192, 50304, 2048, "nt"), (2048, 8192, 8192, "tn")]
+    for M, N, K, lay in shapes:
+        ta, tb = lay[0] == "t", lay[1] == "t"
+        a = torch.randn((K, M) if ta else (M, K), device="cuda", dtype=torch.bfloat16)
+        b = torch.randn((N, K) if tb else (K, N), device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        A, B = (a.t() if ta else a), (b.t() if tb else b)
+        ours = timeit(lambda: gemm(a, b, trans_a=ta, trans_b=tb, out=out))
+        ref = timeit(lambda: torch.matmul(A, B, out=out))
+        fl = 2.0 * M * N * K
+        _emit(bench="gemm", dtype="bf16", M=M, N=N, K=K, layout=lay, ms=ours, tflops=fl / ours / 1e9,
+              torch_ms=ref, torch_tflops=fl / ref / 1e9)
+
+
+def bench_elementwise():
+    from ..ops.elementwise import binary, unary
+    for dt in (torch.float32, torch.bfloat16):
+        for n in (10 ** 6, 10 ** 7, 10 ** 8):
+            x = torch.randn(n, device="cuda", dtype=dt)
+            y = torch.randn(n, device="cuda", dtype=dt)
+            esz = x.element_size()
+            t = timeit(lambda: binary("add", x, y))
+            r = timeit(lambda: torch.add(x, y))
+            _emit(bench="add", dtype=str(dt), n=n, ms=t, gbs=3 * n * esz / t / 1e6, torch_ms=r,
+                  torch_gbs=3 * n * esz / r / 1e6)
+            t = timeit(lambda: unary("relu", x))
+            r = timeit(lambda: torch.relu(x))
+            _emit(bench="relu", dtype=str(dt), n=n, ms=t, gbs=2 * n * esz / t / 1e6, torch_ms=r,
+                  torch_gbs=2 * n * esz / r / 1e6)
+
+
+def bench_flash():
+    from ..ops.attention import flash_bwd, flash_fwd
+    F = torch.nn.functional
+    cases = [(8, 4096, 16, 128, True), (8, 4096, 16, 128, False), (16, 1024, 12, 64, True),
+             (4, 2048, 16, 128, True), (1, 2048, 16, 64, False), (1, 1024, 32, 64, False),
+             (1, 512, 64, 64, False), (1, 2048, 16, 64, True)]
+    for B, S, H, D, causal in cases:
+        q, k, v = (torch.randn(B, S, H, D, device="cuda", dtype=torch.bfloat16) for _ in range(3))
+        scale = 1 / math.sqrt(D)
+        out, lse = flash_fwd(q, k, v, causal, scale)
+        do = torch.randn_like(out)
+        fl = 4.0 * B * H * S * S * D * (0.5 if causal else 1.0)
+        tf = timeit(lambda: flash_fwd(q, k, v, causal, scale))
+        tb = timeit(lambda: flash_bwd(q, k, v, out, do, lse, causal, scale))
+        qt, kt, vt = (t.permute(0, 2, 1, 3).contiguous().requires_grad_(True) for t in (q, k, v))
+        o = F.scaled_dot_product_attention(qt, kt, vt, is_causal=causal)
+        g = torch.randn_like(o)
+        rf = timeit(lambda: F.scaled_dot_product_attention(qt, kt, vt, is_causal=causal))
+        rb = timeit(lambda: torch.autograd.grad(o, (qt, kt, vt), g, retain_graph=True))
+        _emit(bench="flash", dtype="bf16", B=B, S=S, H=H, D=D, causal=causal, fwd_ms=tf,
+              fwd_tflops=fl / tf / 1e9, bwd_ms=tb, bwd_tflops=2.5 * fl / tb / 1e9, torch_fwd_ms=rf,
+              torch_bwd_ms=rb, flop_convention="4*B*H*S*S*D, halved when causal; backward 2.5x")
+
+
+def bench_norm():
+    from ..ops.norm import layer_norm
+    for rows, D in ((16384, 768), (65536, 768), (16384, 2048), (65536, 2048)):
+        x = torch.randn(rows, D, device="cuda", dtype=torch.bfloat16)
+        w = torch.ones(D, device="cuda", dtype=torch.bfloat16)
+        b = torch.zeros(D, device="cuda", dtype=torch.bfloat16)
+        t = timeit(lambda: layer_norm(x, w, b))
+        r = timeit(lambda: torch.nn.functional.layer_norm(x, (D,), w, b))
+        by = 2.0 * rows * D * 2
+        _emit(bench="layer_norm_fwd", rows=rows, D=D, ms=t, gbs=by / t / 1e6, torch_ms=r, torch_gbs=by / r / 1e6)
+
+
+def bench_mlp_cpu():
+    """MLP 784 -> 256 -> 128 -> 10, batch 64, SGD with momentum, fp64 on the CPU oracle path;
+    then the same step with two data-parallel ranks over the TCP star (threads)."""
+    from ..models.mlp import MLP
+    from ..nn.loss import CrossEntropyLoss
+    from ..optim import SGD
+    torch.manual_seed(0)
+    model = MLP([784, 256, 128, 10], dtype=torch.float64)
+    opt = SGD(model.parameters(), lr=0.05, momentum=0.9)
+    x = torch.randn(64, 784, dtype=torch.float64)
+    y = torch.randint(0, 10, (64,))
+
+    def step():
+        opt.zero_grad()
+        loss = CrossEntropyLoss(model(x), y)
+        loss.backward()
+        opt.step()
+        return loss
+
+    for _ in range(5):
+        step()
+    t0 = time.perf_counter()
+    n = 50
+    for _ in range(n):
+        step()
+    dt = (time.perf_counter() - t0) / n
+    _emit(bench="mlp_cpu", dtype="fp64", batch=64, ms_per_step=dt * 1e3, steps_per_s=1 / dt, images_per_s=64 / dt)
+
+
+def bench_allreduce():
+    """Bus bandwidth of the peer-memory all-reduce against NCCL: 1 KB .. 1 GB."""
+    import torch.distributed as dist
+    from ..distributed.nvlink import SymmetricMemory
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    max_bytes = 1 << 30
+    symm = SymmetricMemory(max_bytes, rank, world, device=torch.device("cuda", local))
+    for dt in (torch.bfloat16, torch.float32):
+        esz = 2 if dt == torch.bfloat16 else 4
+        nbytes = 1 << 10
+        while nbytes <= max_bytes:
+            n = nbytes // esz
+            n = max(n // (world * 8) * (world * 8), world * 8)
+            buf = symm.view(0, n, dt)
+            buf.fill_(1.0)
+            ref = torch.ones(n, device="cuda", dtype=dt)
+            ctas = 8 if nbytes <= (1 << 16) else (32 if nbytes <= (1 << 22) else 128)
+
+            def ours():
+                symm.all_reduce(0, n, dt, "mean", ctas)
+
+            def nccl():
+                dist.all_reduce(ref, op=dist.ReduceOp.AVG)
+
+            res = []
+            for fn in (ours, nccl):
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                dist.barrier()
+                iters = 20 if nbytes <= (1 << 24) else 5
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(iters):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)   # slowest rank
+                res.append(float(t.item()))
+            symm.check()
+            if rank == 0:
+                bus = lambda ms: 2.0 * (world - 1) / world * n * esz / ms / 1e6
+                _emit(bench="allreduce", dtype=str(dt), bytes=n * esz, world=world, ms=res[0], bus_gbs=bus(res[0]),
+                      nccl_ms=res[1], nccl_bus_gbs=bus(res[1]), timing="back-to-back calls, max over ranks")
+            nbytes *= 4
+    symm.close()
+    dist.destroy_process_group()
+
+
+def main(argv):
+    kind = argv[0] if argv else "gemm"
+    fn = {"gemm": bench_gemm, "elementwise": bench_elementwise, "flash": bench_flash, "norm": bench_norm,
+          "mlp": bench_mlp_cpu, "allreduce": bench_allreduce}.get(kind)
+    if fn is None:
+        raise SystemExit(f"unknown benchmark {kind!r}")
+    fn()
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])

@@ -222,3 +222,19 @@ def test_feed_forward_matches_composed_layers():
         assert torch.allclose(y, yr, atol=1e-9)
         for a, b in zip(got, want):
             assert torch.allclose(a, b, atol=1e-8), act
+
+
+def test_functional_call_grads_to_replacements():
+    import gonn_b200.nn as gnn
+    torch.manual_seed(0)
+    lin = gnn.Linear(4, 3, dtype=torch.float64)
+    x = torch.randn(5, 4, dtype=torch.float64)
+    w2 = torch.randn(3, 4, dtype=torch.float64)
+    loss, grads = gnn.FunctionalCallGrad(lin, x, {"weight": w2}, lambda y: (y ** 2).mean(),
+                                         gnn.WithGradsToReplacements())
+    assert set(grads) == {"weight"} and lin.weight.grad is None
+    assert torch.allclose(w2.grad, grads["weight"])
+    # a second call accumulates
+    gnn.FunctionalCallGrad(lin, x, {"weight": w2}, lambda y: (y ** 2).mean(), gnn.WithGradsToReplacements())
+    assert torch.allclose(w2.grad, 2 * grads["weight"])
+    assert gnn.ParametrizationWithInverse is gnn.InvertibleParametrization
