@@ -97,7 +97,7 @@ norm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, const TW* __r
                 T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
                 long long rows, int D, float eps) {
   constexpr int V = IO<T>::V;
-  constexpr int NR = (G == 32) ? 2 : 1;  // rows in flight per group (more loads outstanding)
+  constexpr int NR = (G == 32) ? 2 : 4;  // rows in flight per group (more loads outstanding)
   __shared__ float red[32];
   const int gpb = 256 / G;
   const int g = threadIdx.x / G, t = threadIdx.x % G;
@@ -135,7 +135,7 @@ norm_fwd_kernel(const T* __restrict__ x, const TW* __restrict__ w, const TW* __r
 #pragma unroll
     for (int r = 0; r < NR; r++) {
       const long long row = row0 + r * stride;
-      if (G == 32 && row >= rows) continue;  // warp-uniform
+      if (row >= rows) continue;  // uniform across the group (a warp, or the whole CTA)
 #pragma unroll
       for (int i = 0; i < VPT; i++)
 #pragma unroll
@@ -395,9 +395,9 @@ __global__ void norm_param_generic(const T* __restrict__ x, const T* __restrict_
   if (dbeta) dbeta[c] = (TW)b;
 }
 
-int pick_grid(long long rows, int gpb) {
+int pick_grid(long long rows, int gpb, int per_sm = 2) {
   long long need = (rows + gpb - 1) / gpb;
-  long long cap = 148 * 2;
+  long long cap = 148 * per_sm;
   return (int)(need < cap ? need : cap);
 }
 
@@ -408,7 +408,7 @@ int norm_fwd_t(const void* x, const void* w, const void* b, void* y, float* mean
   const bool aligned = (D % V == 0) && ((((uintptr_t)x | (uintptr_t)y) & 15) == 0);
   const int nvec = D / V;
 #define GB_FWD(G, VPT)                                                                           \
-  norm_fwd_kernel<T, TW, G, VPT, RMS><<<pick_grid(rows, 256 / G), 256, 0, s>>>(                  \
+  norm_fwd_kernel<T, TW, G, VPT, RMS><<<pick_grid(rows, 256 / G, 4), 256, 0, s>>>(               \
       (const T*)x, (const TW*)w, (const TW*)b, (T*)y, mean, rstd, rows, D, eps)
   if (aligned && nvec <= 32) GB_FWD(32, 1);
   else if (aligned && nvec <= 64) GB_FWD(32, 2);

@@ -284,10 +284,14 @@ class DistributedDataParallel(torch.nn.Module):
         self.t += 1
         for k in self._fresh:
             self._fresh[k] = True
-        # gradients that autograd accumulates in place must start the next step from zero
-        for p in self._autograd_params.values():
-            _, o, n = self._where[id(p)]
-            self.flat_grads[o:o + n].zero_()
+        if self.opt is not None:
+            # the fused optimizer has consumed the gradients; those that autograd accumulates
+            # in place must start the next step from zero
+            for p in self._autograd_params.values():
+                _, o, n = self._where[id(p)]
+                self.flat_grads[o:o + n].zero_()
+        # all-reduce mode: the averaged gradients stay readable in ``p.grad`` for the caller's
+        # optimizer, which clears them (``zero_grad``) before the next backward as usual
         self._reset_step()
 
     synchronize = step

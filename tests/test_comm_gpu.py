@@ -37,6 +37,27 @@ def test_allreduce_mean_emulated(world, dtype, status_ok):
     sm.check()
 
 
+@pytest.mark.parametrize("world", [2, 8])
+def test_allreduce_fp32_sum_emulated(world, status_ok):
+    """fp32 buffers through the same two-shot kernel (``all_reduce`` with op sum)."""
+    n = world * 8 * 777
+    sm = _symm(world, 4 * n + 4096)
+    vals = [torch.randn(n, device="cuda") for _ in range(world)]
+    for r in range(world):
+        sm.view(0, n, torch.float32, rank=r).copy_(vals[r])
+    sm.all_reduce(0, n, torch.float32, "sum", ctas=8)
+    torch.cuda.synchronize()
+    acc = torch.zeros(n, device="cuda")
+    for v in vals:
+        acc += v
+    # the kernel sums in rank order, multiplies by W/W = 1
+    outs = [sm.view(0, n, torch.float32, rank=r) for r in range(world)]
+    assert torch.allclose(outs[0], acc, rtol=1e-6, atol=1e-6)
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+    sm.check()
+
+
 @pytest.mark.parametrize("world", [1, 2, 4])
 def test_zero1_adamw_step_emulated(world, status_ok):
     from gonn_b200.distributed.nvlink import SymmetricMemory

@@ -97,3 +97,99 @@ def test_two_rank_fused_step_matches_single_process(tmp_path):
         if off - start >= limit:
             off = start + (off - start + align - 1) // align * align
             start = off
+
+
+CHILD_FP32_SYNCBN = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["GB_ROOT"])
+from gonn_b200.distributed.ddp import DistributedDataParallel
+from gonn_b200.models.mlp import MLP
+from gonn_b200.models.cnn import SmallCNN
+from gonn_b200.nn.loss import MSELoss
+rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+out = {}
+# ---- fp32 parameters: gradients are all-reduced (mean), any optimizer may follow ----
+torch.manual_seed(0)
+mlp = MLP([16, 32, 8], dtype=torch.float32, device="cuda")
+ddp = DistributedDataParallel(mlp, optimizer=None, bucket_mb=0.001)
+g = torch.Generator().manual_seed(1)
+x = torch.randn(8, 16, generator=g).cuda(); y = torch.randn(8, 8, generator=g).cuda()
+lo = rank * 4
+MSELoss(mlp(x[lo:lo + 4]), y[lo:lo + 4]).backward()
+ddp.step()
+torch.cuda.synchronize(); ddp.check()
+out["fp32_grads"] = ddp.flat_grads.clone().cpu()
+ddp.close()
+# ---- SyncBatchNorm inside the CNN: halves of a batch on two ranks == the whole batch on one ----
+torch.manual_seed(0)
+cnn = SmallCNN(sync_bn=True, dtype=torch.bfloat16, device="cuda")
+ddp2 = DistributedDataParallel(cnn, optimizer=None)
+g = torch.Generator().manual_seed(2)
+img = torch.randn(16, 3, 32, 32, generator=g).to(torch.bfloat16).cuda()
+lab = torch.randint(0, 10, (16,), generator=g).cuda()
+lo = rank * 8
+logits = cnn(img[lo:lo + 8])
+torch.nn.functional.cross_entropy(logits.float(), lab[lo:lo + 8]).backward()
+ddp2.step()
+torch.cuda.synchronize(); ddp2.check()
+gathered = [torch.empty_like(logits) for _ in range(world)]
+dist.all_gather(gathered, logits.detach().contiguous())
+out["logits"] = torch.cat(gathered).float().cpu()
+out["running_mean"] = cnn.bn1.running_mean.float().cpu()
+out["running_var"] = cnn.bn1.running_var.float().cpu()
+out["conv1_grad"] = cnn.conv1.weight.grad.float().cpu()
+if rank == 0:
+    torch.save(out, os.environ["GB_OUT"])
+dist.barrier()
+ddp2.close()
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_fp32_allreduce_and_syncbn_match_single_process(tmp_path):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "child2.py"
+    script.write_text(CHILD_FP32_SYNCBN)
+    out = tmp_path / "out2.pt"
+    env = dict(os.environ, GB_ROOT=root, GB_OUT=str(out), NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29534", str(script)],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    res = torch.load(out)
+
+    from gonn_b200.models.cnn import SmallCNN
+    from gonn_b200.models.mlp import MLP
+    from gonn_b200.nn.loss import MSELoss
+    torch.manual_seed(0)
+    mlp = MLP([16, 32, 8], dtype=torch.float32, device="cuda")
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(8, 16, generator=g).cuda()
+    y = torch.randn(8, 8, generator=g).cuda()
+    MSELoss(mlp(x), y).backward()
+    want = torch.cat([p.grad.reshape(-1) for p in mlp.parameters()]).cpu()
+    got = res["fp32_grads"]
+    # the flat buffer pads every parameter to a multiple of 8 elements: compare parameter by parameter
+    off = 0
+    for p in mlp.parameters():
+        n = p.numel()
+        assert torch.allclose(got[off:off + n], p.grad.reshape(-1).cpu(), rtol=1e-4, atol=1e-6)
+        off += (n + 7) // 8 * 8
+    assert want.numel() > 0
+
+    torch.manual_seed(0)
+    cnn = SmallCNN(sync_bn=False, dtype=torch.bfloat16, device="cuda")
+    g = torch.Generator().manual_seed(2)
+    img = torch.randn(16, 3, 32, 32, generator=g).to(torch.bfloat16).cuda()
+    lab = torch.randint(0, 10, (16,), generator=g).cuda()
+    logits = cnn(img)
+    torch.nn.functional.cross_entropy(logits.float(), lab).backward()
+    assert torch.allclose(res["logits"], logits.float().cpu(), rtol=5e-2, atol=5e-2)
+    assert torch.allclose(res["running_mean"], cnn.bn1.running_mean.float().cpu(), rtol=2e-2, atol=2e-3)
+    assert torch.allclose(res["running_var"], cnn.bn1.running_var.float().cpu(), rtol=2e-2, atol=2e-3)
+    ref_g = cnn.conv1.weight.grad.float().cpu()
+    err = (res["conv1_grad"] - ref_g).abs().max() / ref_g.abs().max().clamp_min(1e-6)
+    assert err < 0.1, err
