@@ -10,8 +10,8 @@
 // fp32 accumulation, no atomics (dQ and dK/dV are produced by two kernels so that
 // every output tile has one owner and a fixed summation order).
 //
-// Forward CTA (192 threads) owns 128 query rows of one (batch, head):
-//   warp 0      TMA loads of Q once and the K / V tiles (2-stage rings)
+// Forward CTA (192 threads, two CTAs per SM) owns 128 query rows of one (batch, head):
+//   warp 0      TMA loads of Q once and the K / V sub-tiles of 64 keys (rings)
 //   warp 1      MMA issue: S = Q K^T into one of two TMEM score buffers, then
 //               O += P V with P read from TMEM (written there by the softmax warps)
 //   warps 2-5   softmax: one thread per row; running max / sum in registers;
@@ -19,6 +19,8 @@
 // Tensors are addressed through 4-D tensor maps (d, s, h, b) with arbitrary
 // strides, so (B,S,H,D) and (B,H,S,D) layouts both work without copies.
 #include "common.cuh"
+
+#include <type_traits>
 
 using namespace gb;
 
@@ -73,36 +75,43 @@ __device__ __forceinline__ void store_row16(void* dst, const float* v, int bf) {
   }
 }
 
+constexpr int BKF = 64;  // key rows per forward sub-tile
+
+// Forward tiling: 128 query rows per CTA, keys in 64-row sub-tiles.  Two score buffers of 64
+// columns and the output accumulator need 128 + HD <= 256 TMEM columns, and the shared
+// memory of one CTA stays under half an SM, so two CTAs share an SM: while the softmax warps
+// of one are busy, the tensor core serves the other.
 template <int HD>
 struct FwdCfg {
-  static constexpr int CH = HD / 64;               // 64-column chunks per row
-  static constexpr int TILE_BYTES = CH * BQ * 128;  // one 128-row tile of Q, K or V
-  static constexpr int STAGES = 2;
-  static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * STAGES) + 1024 + 256;
-  static constexpr int TMEM_COLS = 512;
-  static constexpr int COL_S0 = 0, COL_S1 = 128, COL_O = 256;
+  static constexpr int CH = HD / 64;                   // 64-column chunks per row
+  static constexpr int Q_BYTES = CH * BQ * 128;        // the resident query tile
+  static constexpr int SUB_BYTES = CH * BKF * 128;     // one K or V sub-tile
+  static constexpr int STAGES = HD == 64 ? 3 : 2;
+  static constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * SUB_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = 256;
+  static constexpr int COL_S0 = 0, COL_S1 = 64, COL_O = 128;
 };
 
-template <int HD>
-__global__ void __launch_bounds__(kFwdThreads, 1)
+template <int HD, bool BF>
+__global__ void __launch_bounds__(kFwdThreads, 2)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
               const __grid_constant__ CUtensorMap tmV, const AttnArgs args) {
   using C = FwdCfg<HD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + C::TILE_BYTES;                // [STAGES]
-  uint8_t* sV = sK + C::STAGES * C::TILE_BYTES;    // [STAGES]
-  uint64_t* bars = (uint64_t*)(sV + C::STAGES * C::TILE_BYTES);
-  uint64_t* q_full = bars;          // 1
-  uint64_t* k_full = bars + 1;      // 2
-  uint64_t* k_empty = bars + 3;     // 2
-  uint64_t* v_full = bars + 5;      // 2
-  uint64_t* v_empty = bars + 7;     // 2
-  uint64_t* s_full = bars + 9;      // 2
-  uint64_t* p_full = bars + 11;     // 2
-  uint64_t* pv_done = bars + 13;    // 2
-  uint32_t* tmem_slot = (uint32_t*)(bars + 15);
+  uint8_t* sK = sQ + C::Q_BYTES;                   // [STAGES]
+  uint8_t* sV = sK + C::STAGES * C::SUB_BYTES;     // [STAGES]
+  uint64_t* bars = (uint64_t*)(sV + C::STAGES * C::SUB_BYTES);
+  uint64_t* q_full = bars;                    // 1
+  uint64_t* k_full = bars + 1;                // STAGES
+  uint64_t* k_empty = k_full + C::STAGES;     // STAGES
+  uint64_t* v_full = k_empty + C::STAGES;     // STAGES
+  uint64_t* v_empty = v_full + C::STAGES;     // STAGES
+  uint64_t* s_full = v_empty + C::STAGES;     // 2
+  uint64_t* p_full = s_full + 2;              // 2
+  uint64_t* pv_done = p_full + 2;             // 2
+  uint32_t* tmem_slot = (uint32_t*)(pv_done + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -111,18 +120,20 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const int q_tile = args.causal ? (num_q_tiles - 1 - (int)blockIdx.x) : (int)blockIdx.x;
   const int h = blockIdx.y, b = blockIdx.z;
   const int q0 = q_tile * BQ;
-  int n_kv = (args.Sk + BKV - 1) / BKV;
-  if (args.causal) n_kv = min(n_kv, q_tile + 1);
+  int n_kv = (args.Sk + BKF - 1) / BKF;
+  if (args.causal) n_kv = min(n_kv, (q_tile + 1) * (BQ / BKF));
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; i++) {
+    for (int i = 0; i < C::STAGES; i++) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
+    }
+    for (int i = 0; i < 2; i++) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 128);
+      mbar_init(&p_full[i], 4);  // one arrival per softmax warp
       mbar_init(&pv_done[i], 1);
     }
     *abort_flag = 0;
@@ -141,79 +152,80 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    if (lane == 0) {
-      mbar_expect_tx(q_full, C::TILE_BYTES);
+    if (elect_one()) {
+      mbar_expect_tx(q_full, C::Q_BYTES);
 #pragma unroll
       for (int c = 0; c < C::CH; c++) tma_load_4d(sQ + c * BQ * 128, &tmQ, q_full, c * 64, q0, h, b);
+      int st = 0;
+      uint32_t ph = 0;
       for (int j = 0; j < n_kv; j++) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 1)) break;
-        mbar_expect_tx(&k_full[st], C::TILE_BYTES);
+        mbar_expect_tx(&k_full[st], C::SUB_BYTES);
 #pragma unroll
         for (int c = 0; c < C::CH; c++)
-          tma_load_4d(sK + st * C::TILE_BYTES + c * BKV * 128, &tmK, &k_full[st], c * 64, j * BKV, h, b);
+          tma_load_4d(sK + st * C::SUB_BYTES + c * BKF * 128, &tmK, &k_full[st], c * 64, j * BKF, h, b);
         if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 2)) break;
-        mbar_expect_tx(&v_full[st], C::TILE_BYTES);
+        mbar_expect_tx(&v_full[st], C::SUB_BYTES);
 #pragma unroll
         for (int c = 0; c < C::CH; c++)
-          tma_load_4d(sV + st * C::TILE_BYTES + c * BKV * 128, &tmV, &v_full[st], c * 64, j * BKV, h, b);
+          tma_load_4d(sV + st * C::SUB_BYTES + c * BKF * 128, &tmV, &v_full[st], c * 64, j * BKF, h, b);
+        if (++st == C::STAGES) { st = 0; ph ^= 1; }
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
-    const uint32_t fmt = args.in_bf16 ? 1u : 0u;
-    const uint32_t idesc_s = make_idesc(1u, fmt, false, false, BQ, BKV);
-    const uint32_t idesc_o = make_idesc(1u, fmt, false, true, BQ, HD);
-    bool ok = mbar_wait(q_full, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 3);
-    auto issue_s = [&](int j) {
-      const int st = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      if (!mbar_wait(&k_full[st], ph, abort_flag, args.status, ST_ATTN_TIMEOUT, 4)) return false;
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + st * C::TILE_BYTES);
-        const uint32_t d = tmem_base + (st ? C::COL_S1 : C::COL_S0);
+    if (elect_one()) {
+      const uint32_t fmt = BF ? 1u : 0u;
+      const uint32_t idesc_s = make_idesc(1u, fmt, false, false, BQ, BKF);
+      const uint32_t idesc_o = make_idesc(1u, fmt, false, true, BQ, HD);
+      const uint32_t qa = smem_u32(sQ);
+      bool ok = mbar_wait(q_full, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 3);
+      int st_s = 0;
+      uint32_t ph_s = 0;
+      auto issue_s = [&](int j) {
+        if (!mbar_wait(&k_full[st_s], ph_s, abort_flag, args.status, ST_ATTN_TIMEOUT, 4)) return false;
+        tc_fence_after();
+        const uint32_t ka = smem_u32(sK + st_s * C::SUB_BYTES);
+        const uint32_t d = tmem_base + ((j & 1) ? C::COL_S1 : C::COL_S0);
 #pragma unroll
-        for (int k = 0; k < HD / 16; k++) {
-          const uint32_t off = (k / 4) * (BQ * 128) + (k % 4) * 32;
-          tc_mma_f16(d, make_smem_desc_sw128(qa + off, 16, 1024),
-                     make_smem_desc_sw128(ka + off, 16, 1024), idesc_s, k != 0);
+        for (int k = 0; k < HD / 16; k++)
+          tc_mma_f16(d, make_smem_desc_sw128(qa + (k / 4) * (BQ * 128) + (k % 4) * 32, 16, 1024),
+                     make_smem_desc_sw128(ka + (k / 4) * (BKF * 128) + (k % 4) * 32, 16, 1024), idesc_s, k != 0);
+        tc_commit(&k_empty[st_s]);
+        tc_commit(&s_full[j & 1]);
+        if (++st_s == C::STAGES) { st_s = 0; ph_s ^= 1; }
+        return true;
+      };
+      if (ok && n_kv > 0) ok = issue_s(0);
+      int st = 0;
+      uint32_t ph = 0;
+      for (int j = 0; j < n_kv && ok; j++) {
+        if (j + 1 < n_kv) {
+          ok = issue_s(j + 1);
+          if (!ok) break;
         }
-        tc_commit(&k_empty[st]);
-        tc_commit(&s_full[st]);
-      }
-      __syncwarp();
-      return true;
-    };
-    if (ok && n_kv > 0) ok = issue_s(0);
-    for (int j = 0; j < n_kv && ok; j++) {
-      if (j + 1 < n_kv) {
-        ok = issue_s(j + 1);
+        const int sb = j & 1;
+        ok = mbar_wait(&p_full[sb], (j >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 5);
         if (!ok) break;
-      }
-      const int st = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      ok = mbar_wait(&p_full[st], ph, abort_flag, args.status, ST_ATTN_TIMEOUT, 5);
-      if (!ok) break;
-      ok = mbar_wait(&v_full[st], ph, abort_flag, args.status, ST_ATTN_TIMEOUT, 6);
-      if (!ok) break;
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t va = smem_u32(sV + st * C::TILE_BYTES);
-        const uint32_t p_tmem = tmem_base + (st ? C::COL_S1 : C::COL_S0);
+        ok = mbar_wait(&v_full[st], ph, abort_flag, args.status, ST_ATTN_TIMEOUT, 6);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t va = smem_u32(sV + st * C::SUB_BYTES);
+        const uint32_t p_tmem = tmem_base + (sb ? C::COL_S1 : C::COL_S0);
         const uint32_t d = tmem_base + C::COL_O;
 #pragma unroll
-        for (int k = 0; k < BKV / 16; k++) {
-          // V is the MN-major B operand: 64-wide d chunks are BKV*128 B apart,
-          // 8-row groups 1024 B apart, one MMA step covers 16 key rows.
-          tc_mma_f16_ts(d, p_tmem + k * 8, make_smem_desc_sw128(va + k * 16 * 128, BKV * 128, 1024),
-                        idesc_o, (j | k) != 0);
+        for (int k = 0; k < BKF / 16; k++) {
+          // V is the MN-major B operand: 64-wide d chunks are BKF*128 B apart, 8-row groups
+          // 1024 B apart, one MMA step covers 16 key rows.
+          tc_mma_f16_ts(d, p_tmem + k * 8, make_smem_desc_sw128(va + k * 16 * 128, BKF * 128, 1024), idesc_o,
+                        (j | k) != 0);
         }
         tc_commit(&v_empty[st]);
-        tc_commit(&pv_done[st]);
+        tc_commit(&pv_done[sb]);
+        if (++st == C::STAGES) { st = 0; ph ^= 1; }
       }
-      __syncwarp();
     }
+    __syncwarp();
   } else {
     // ---------------- softmax warps ----------------
     const int quarter = warp & 3;
@@ -224,33 +236,30 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     float l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; j++) {
-      const int st = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      ok = mbar_wait(&s_full[st], ph, abort_flag, args.status, ST_ATTN_TIMEOUT, 7);
+      const int sb = j & 1;
+      ok = mbar_wait(&s_full[sb], (j >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 7);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t s_addr = lane_addr + (st ? C::COL_S1 : C::COL_S0);
-      float s[BKV];
+      const uint32_t s_addr = lane_addr + (sb ? C::COL_S1 : C::COL_S0);
+      uint32_t rr[BKF];
+      tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&rr[0]));
+      tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&rr[32]));
+      tmem_ld_wait();
+      float s[BKF];
 #pragma unroll
-      for (int c = 0; c < BKV / 32; c++) {
-        uint32_t rr[32];
-        tmem_ld32(s_addr + c * 32, rr);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i++) s[c * 32 + i] = __uint_as_float(rr[i]);
-      }
-      const int kv0 = j * BKV;
-      const bool need_mask = (args.causal && j == q_tile) || (kv0 + BKV > args.Sk);
+      for (int i = 0; i < BKF; i++) s[i] = __uint_as_float(rr[i]);
+      const int kv0 = j * BKF;
+      const bool need_mask = (args.causal && kv0 + BKF - 1 > q0) || (kv0 + BKF > args.Sk);
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < BKV; c++) {
+        for (int c = 0; c < BKF; c++) {
           const int kv = kv0 + c;
           if (kv >= args.Sk || (args.causal && kv > qrow)) s[c] = -INFINITY;
         }
       }
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < BKV; c++) mx = fmaxf(mx, s[c]);
+      for (int c = 0; c < BKF; c++) mx = fmaxf(mx, s[c]);
       float m_new = fmaxf(m_used, mx * args.scale_log2);
       if (m_new == -INFINITY) m_new = 0.f;
       // rescale O only when the running max moved by more than 8 (a factor 256)
@@ -262,43 +271,38 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         l *= alpha;
       }
       if (j > 0 && __any_sync(0xffffffffu, need)) {
-        const int pst = (j - 1) & 1;
-        ok = mbar_wait(&pv_done[pst], ((j - 1) >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 8);
+        ok = mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 8);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < HD / 32; c++) {
-          uint32_t rr[32];
-          tmem_ld32(lane_addr + C::COL_O + c * 32, rr);
+          uint32_t ro[32];
+          tmem_ld32(lane_addr + C::COL_O + c * 32, ro);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; i++) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * alpha);
-          tmem_st32(lane_addr + C::COL_O + c * 32, rr);
+          for (int i = 0; i < 32; i++) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * alpha);
+          tmem_st32(lane_addr + C::COL_O + c * 32, ro);
         }
         tmem_st_wait();
       }
       float sum = 0.f;
+      uint32_t pk[BKF / 2];
 #pragma unroll
-      for (int c = 0; c < BKV / 32; c++) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; i++) {
-          float p0 = exp2f(s[c * 32 + 2 * i] * args.scale_log2 - m_used);
-          float p1 = exp2f(s[c * 32 + 2 * i + 1] * args.scale_log2 - m_used);
-          sum += p0 + p1;
-          pk[i] = pack16(p0, p1, args.in_bf16);
-        }
-        tmem_st16(s_addr + c * 16, pk);
+      for (int i = 0; i < BKF / 2; i++) {
+        const float p0 = exp2f(fmaf(s[2 * i], args.scale_log2, -m_used));
+        const float p1 = exp2f(fmaf(s[2 * i + 1], args.scale_log2, -m_used));
+        sum += p0 + p1;
+        pk[i] = BF ? pack_bf16(p0, p1) : pack_f16(p0, p1);
       }
+      tmem_st32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
       l += sum;
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&p_full[st]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[sb]);
     }
-    if (ok && n_kv > 0) {
-      const int lst = (n_kv - 1) & 1;
-      ok = mbar_wait(&pv_done[lst], ((n_kv - 1) >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 9);
-    }
+    if (ok && n_kv > 0)
+      ok = mbar_wait(&pv_done[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 9);
     if (ok) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -307,18 +311,18 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                        (long long)h * args.o_sh;
 #pragma unroll
       for (int c = 0; c < HD / 32; c++) {
-        uint32_t rr[32];
+        uint32_t ro[32];
         if (n_kv > 0) {
-          tmem_ld32(lane_addr + C::COL_O + c * 32, rr);
+          tmem_ld32(lane_addr + C::COL_O + c * 32, ro);
           tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; i++) rr[i] = 0;
+          for (int i = 0; i < 32; i++) ro[i] = 0;
         }
         float v[32];
 #pragma unroll
-        for (int i = 0; i < 32; i++) v[i] = __uint_as_float(rr[i]) * inv;
-        if (row_ok) store_row16<32>(orow + c * 32, v, args.in_bf16);
+        for (int i = 0; i < 32; i++) v[i] = __uint_as_float(ro[i]) * inv;
+        if (row_ok) store_row16<32>(orow + c * 32, v, BF);
       }
       if (row_ok && args.LSE) {
         // natural-log LSE of the scaled scores
@@ -412,6 +416,11 @@ struct BwdCfg {
   static constexpr int TMEM_COLS = 512;
   // buffer b: scores at b*128, dP at b*128 + 64; accumulators behind them
   static constexpr int COL_ACC0 = 256, COL_ACC1 = 256 + HD;
+  // resident A operands kept in TMEM where the columns allow it: K and V of the dK/dV kernel
+  // (head_dim 64 only), Q and dO of the dQ kernel
+  static constexpr bool KV_IN_TMEM = HD == 64;
+  static constexpr int COL_KT = 256 + 2 * HD, COL_VT = COL_KT + HD / 2;
+  static constexpr int COL_QT = 256 + HD, COL_GT = COL_QT + HD / 2;
 };
 
 // K-major operand descriptor for step k (16 columns) of a [128 x HD] tile
@@ -425,6 +434,29 @@ __device__ __forceinline__ uint64_t kdesc_sub(uint32_t base, int k) {
 // MN-major operand descriptor for step k (16 rows) of a [64 rows x HD] sub-tile
 __device__ __forceinline__ uint64_t mndesc_sub(uint32_t base, int k) {
   return make_smem_desc_sw128(base + k * 16 * 128, BSUB * 128, 1024);
+}
+
+// Copies this thread's row of a resident [128 x HD] 16-bit tile (128-byte swizzled rows in
+// 64-column chunks of 128 rows) into TMEM columns [col, col + HD / 2): the layout of an A
+// operand read from tensor memory, so the MMAs that use the tile stop re-reading it from
+// shared memory on every step.
+template <int HD>
+__device__ __forceinline__ void tile_row_to_tmem(const uint8_t* tile, int r, uint32_t lane_addr, uint32_t col) {
+#pragma unroll
+  for (int c = 0; c < HD / 64; c++) {
+    uint32_t w[32];
+    const uint32_t row = smem_u32(tile + c * 128 * 128 + r * 128);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      uint4 u;
+      asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
+                   : "r"(row + (((uint32_t)j ^ ((uint32_t)r & 7u)) << 4)));
+      w[4 * j] = u.x; w[4 * j + 1] = u.y; w[4 * j + 2] = u.z; w[4 * j + 3] = u.w;
+    }
+    tmem_st32(lane_addr + col + c * 32, w);
+  }
+  tmem_st_wait();
 }
 
 template <bool BF>
@@ -453,7 +485,8 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint64_t* sdp_full = q_empty + C::NS;     // 2
   uint64_t* p_full = sdp_full + 2;          // 2
   uint64_t* acc_done = p_full + 2;          // 1
-  uint32_t* tmem_slot = (uint32_t*)(acc_done + 1);
+  uint64_t* a_ready = acc_done + 1;         // 1: K and V copied into TMEM
+  uint32_t* tmem_slot = (uint32_t*)(a_ready + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -471,6 +504,7 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     }
     for (int i = 0; i < 2; i++) { mbar_init(&sdp_full[i], 1); mbar_init(&p_full[i], 8); }
     mbar_init(acc_done, 1);
+    mbar_init(a_ready, 8);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -543,6 +577,10 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const uint32_t idesc_acc = make_idesc(1u, fmt, false, true, 128, HD);
       const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
       bool ok = mbar_wait(kv_full, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 12);
+      if (ok && C::KV_IN_TMEM) {
+        ok = mbar_wait(a_ready, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 18);
+        tc_fence_after();
+      }
       int st_s = 0;        // ring stage of the next S / dP issue
       uint32_t ph_s = 0;
       auto issue_sdp = [&](int it) {
@@ -554,8 +592,13 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // for the one just before it
 #pragma unroll
         for (int k = 0; k < HD / 16; k++) {
-          tc_mma_f16(d, kdesc(ka, k), kdesc_sub(qa, k), idesc_s, k != 0);       // S^T = K Q^T
-          tc_mma_f16(d + 64, kdesc(va, k), kdesc_sub(ga, k), idesc_s, k != 0);  // dP^T = V dO^T
+          if (C::KV_IN_TMEM) {
+            tc_mma_f16_ts(d, tmem_base + C::COL_KT + k * 8, kdesc_sub(qa, k), idesc_s, k != 0);
+            tc_mma_f16_ts(d + 64, tmem_base + C::COL_VT + k * 8, kdesc_sub(ga, k), idesc_s, k != 0);
+          } else {
+            tc_mma_f16(d, kdesc(ka, k), kdesc_sub(qa, k), idesc_s, k != 0);       // S^T = K Q^T
+            tc_mma_f16(d + 64, kdesc(va, k), kdesc_sub(ga, k), idesc_s, k != 0);  // dP^T = V dO^T
+          }
         }
         tc_commit(&sdp_full[it & 1]);
         if (++st_s == C::NS) { st_s = 0; ph_s ^= 1; }
@@ -605,6 +648,16 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const uint32_t my = lane_addr + group * 128 + half * 32;
     bool ok = true;
+    if (C::KV_IN_TMEM && group == 0) {
+      // the eight warps of group 0 copy K (half 0) and V (half 1) into TMEM once
+      ok = mbar_wait(kv_full, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 19);
+      if (ok) {
+        tile_row_to_tmem<HD>(half == 0 ? sK : sV, r, lane_addr, half == 0 ? C::COL_KT : C::COL_VT);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(a_ready);
+      }
+    }
     long long* tr = ((blockIdx.x | blockIdx.y | blockIdx.z) == 0 && (e & 7) == 0 && lane == 0) ? args.trace : nullptr;
     int ntr = 0;
     for (int it = group; it < n_it; it += 2) {
@@ -624,26 +677,34 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       tmem_ld_wait();
       trace_stamp(tr, 1 + group, ntr);  // loaded
       const int q0 = (i_begin + it) * BSUB + half * 32;  // first query column of this thread
-      const bool masked = row_dead || (args.causal && it < BKV / BSUB);  // warp-uniform except row_dead
+      // masking is needed on the diagonal sub-tiles and for key rows past the end; the common
+      // case runs a loop without any of the compare / select instructions
+      const bool masked = __any_sync(0xffffffffu, row_dead) || (args.causal && it < BKV / BSUB);
       uint32_t pp[16], pd[16];
+      auto body = [&](auto use_mask) {
 #pragma unroll
-      for (int g = 0; g < 8; g++) {
-        const float4 l = l4[g], d = d4[g];
-        const float ls[4] = {l.x, l.y, l.z, l.w};
-        const float ds[4] = {d.x, d.y, d.z, d.w};
-        float p[4], q[4];
+        for (int g = 0; g < 8; g++) {
+          const float4 l = l4[g], d = d4[g];
+          const float ls[4] = {l.x, l.y, l.z, l.w};
+          const float ds[4] = {d.x, d.y, d.z, d.w};
+          float p[4], q[4];
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
-          const int j = 4 * g + u;
-          p[u] = exp2f(fmaf(__uint_as_float(rs[j]), args.scale_log2, -ls[u]));
-          if (masked && (row_dead || kvrow > q0 + j)) p[u] = 0.f;
-          q[u] = p[u] * fmaf(__uint_as_float(rd[j]), args.scale, -ds[u]);
+          for (int u = 0; u < 4; u++) {
+            const int j = 4 * g + u;
+            p[u] = exp2f(fmaf(__uint_as_float(rs[j]), args.scale_log2, -ls[u]));
+            if (decltype(use_mask)::value) {
+              if (row_dead || (args.causal && kvrow > q0 + j)) p[u] = 0.f;
+            }
+            q[u] = p[u] * fmaf(__uint_as_float(rd[j]), args.scale, -ds[u]);
+          }
+          pp[2 * g] = pack16t<BF>(p[0], p[1]);
+          pp[2 * g + 1] = pack16t<BF>(p[2], p[3]);
+          pd[2 * g] = pack16t<BF>(q[0], q[1]);
+          pd[2 * g + 1] = pack16t<BF>(q[2], q[3]);
         }
-        pp[2 * g] = pack16t<BF>(p[0], p[1]);
-        pp[2 * g + 1] = pack16t<BF>(p[2], p[3]);
-        pd[2 * g] = pack16t<BF>(q[0], q[1]);
-        pd[2 * g + 1] = pack16t<BF>(q[2], q[3]);
-      }
+      };
+      if (masked) body(std::true_type{});
+      else body(std::false_type{});
       // each warp overwrites only columns it has read itself
       trace_stamp(tr, 1 + group, ntr);  // computed
       tmem_st16(my, pp);
@@ -707,7 +768,8 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* sdp_full = kv_empty + C::NS;    // 2
   uint64_t* p_full = sdp_full + 2;          // 2
   uint64_t* acc_done = p_full + 2;          // 1
-  uint32_t* tmem_slot = (uint32_t*)(acc_done + 1);
+  uint64_t* a_ready = acc_done + 1;         // 1: Q and dO copied into TMEM
+  uint32_t* tmem_slot = (uint32_t*)(a_ready + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -723,6 +785,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int i = 0; i < C::NS; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
     for (int i = 0; i < 2; i++) { mbar_init(&sdp_full[i], 1); mbar_init(&p_full[i], 8); }
     mbar_init(acc_done, 1);
+    mbar_init(a_ready, 8);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -761,8 +824,11 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t fmt = BF ? 1u : 0u;
       const uint32_t idesc_s = make_idesc(1u, fmt, false, false, 128, BSUB);
       const uint32_t idesc_acc = make_idesc(1u, fmt, false, true, 128, HD);
-      const uint32_t qa = smem_u32(sQ), ga = smem_u32(sdO);
       bool ok = mbar_wait(q_full, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 22);
+      if (ok) {
+        ok = mbar_wait(a_ready, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 28);
+        tc_fence_after();
+      }
       int st_s = 0;
       uint32_t ph_s = 0;
       auto issue_sdp = [&](int j) {
@@ -772,8 +838,8 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t d = tmem_base + (j & 1) * 128;
 #pragma unroll
         for (int k = 0; k < HD / 16; k++) {
-          tc_mma_f16(d, kdesc(qa, k), kdesc_sub(ka, k), idesc_s, k != 0);       // S = Q K^T
-          tc_mma_f16(d + 64, kdesc(ga, k), kdesc_sub(va, k), idesc_s, k != 0);  // dP = dO V^T
+          tc_mma_f16_ts(d, tmem_base + C::COL_QT + k * 8, kdesc_sub(ka, k), idesc_s, k != 0);       // S = Q K^T
+          tc_mma_f16_ts(d + 64, tmem_base + C::COL_GT + k * 8, kdesc_sub(va, k), idesc_s, k != 0);  // dP = dO V^T
         }
         tc_commit(&sdp_full[j & 1]);
         if (++st_s == C::NS) { st_s = 0; ph_s ^= 1; }
@@ -818,6 +884,16 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (lse2 == -INFINITY) lse2 = INFINITY;
     }
     bool ok = true;
+    if (group == 0) {
+      // the eight warps of group 0 copy Q (half 0) and dO (half 1) into TMEM once
+      ok = mbar_wait(q_full, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 29);
+      if (ok) {
+        tile_row_to_tmem<HD>(half == 0 ? sQ : sdO, r, lane_addr, half == 0 ? C::COL_QT : C::COL_GT);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(a_ready);
+      }
+    }
     for (int j = group; j < n_sub; j += 2) {
       ok = mbar_wait(&sdp_full[group], (j >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 25);
       if (!ok) break;
@@ -829,18 +905,24 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_ld32(my + 64, rd);
       tmem_ld_wait();
       uint32_t pd[16];
+      auto body = [&](auto use_mask) {
 #pragma unroll
-      for (int i = 0; i < 16; i++) {
-        float dv[2];
+        for (int i = 0; i < 16; i++) {
+          float dv[2];
 #pragma unroll
-        for (int u = 0; u < 2; u++) {
-          const int c = 2 * i + u;
-          float p = exp2f(fmaf(__uint_as_float(rs[c]), args.scale_log2, -lse2));
-          if (need_mask && (kv0 + c >= args.Sk || (args.causal && kv0 + c > qrow))) p = 0.f;
-          dv[u] = p * fmaf(__uint_as_float(rd[c]), args.scale, -dls);
+          for (int u = 0; u < 2; u++) {
+            const int c = 2 * i + u;
+            float p = exp2f(fmaf(__uint_as_float(rs[c]), args.scale_log2, -lse2));
+            if (decltype(use_mask)::value) {
+              if (kv0 + c >= args.Sk || (args.causal && kv0 + c > qrow)) p = 0.f;
+            }
+            dv[u] = p * fmaf(__uint_as_float(rd[c]), args.scale, -dls);
+          }
+          pd[i] = pack16t<BF>(dv[0], dv[1]);
         }
-        pd[i] = pack16t<BF>(dv[0], dv[1]);
-      }
+      };
+      if (need_mask) body(std::true_type{});
+      else body(std::false_type{});
       tmem_st16(my + 64, pd);
       tmem_st_wait();
       tc_fence_before();
@@ -881,18 +963,18 @@ int make_qkv_map(CUtensorMap* m, const void* p, int in_bf16, int B, int H, int S
                           4, p, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-template <int HD>
+template <int HD, bool BF>
 int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                const AttnArgs& a, cudaStream_t s) {
   using C = FwdCfg<HD>;
   static bool configured = false;
   if (!configured) {
-    GB_CUDA_OK(cudaFuncSetAttribute(fa_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    GB_CUDA_OK(cudaFuncSetAttribute(fa_fwd_kernel<HD, BF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     C::SMEM_BYTES));
     configured = true;
   }
   dim3 grid((a.Sq + BQ - 1) / BQ, a.H, a.B);
-  fa_fwd_kernel<HD><<<grid, kFwdThreads, C::SMEM_BYTES, s>>>(tq, tk, tv, a);
+  fa_fwd_kernel<HD, BF><<<grid, kFwdThreads, C::SMEM_BYTES, s>>>(tq, tk, tv, a);
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;
 }
@@ -964,10 +1046,13 @@ GB_EXPORT int gb_flash_fwd(int dtype, const void* q, const void* k, const void* 
   CUtensorMap tq, tk, tv;
   int rc;
   if ((rc = make_qkv_map(&tq, q, a.in_bf16, B, H, Sq, D, q_sb, q_ss, q_sh, BQ))) return rc;
-  if ((rc = make_qkv_map(&tk, k, a.in_bf16, B, H, Sk, D, k_sb, k_ss, k_sh, BKV))) return rc;
-  if ((rc = make_qkv_map(&tv, v, a.in_bf16, B, H, Sk, D, v_sb, v_ss, v_sh, BKV))) return rc;
-  if (D == 128) return launch_fwd<128>(tq, tk, tv, a, (cudaStream_t)stream);
-  return launch_fwd<64>(tq, tk, tv, a, (cudaStream_t)stream);
+  if ((rc = make_qkv_map(&tk, k, a.in_bf16, B, H, Sk, D, k_sb, k_ss, k_sh, BKF))) return rc;
+  if ((rc = make_qkv_map(&tv, v, a.in_bf16, B, H, Sk, D, v_sb, v_ss, v_sh, BKF))) return rc;
+  if (D == 128)
+    return a.in_bf16 ? launch_fwd<128, true>(tq, tk, tv, a, (cudaStream_t)stream)
+                     : launch_fwd<128, false>(tq, tk, tv, a, (cudaStream_t)stream);
+  return a.in_bf16 ? launch_fwd<64, true>(tq, tk, tv, a, (cudaStream_t)stream)
+                   : launch_fwd<64, false>(tq, tk, tv, a, (cudaStream_t)stream);
 }
 
 GB_EXPORT int gb_flash_delta(int dtype, const void* o, const void* dout, float* delta, int B, int H,
