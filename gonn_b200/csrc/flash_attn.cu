@@ -241,6 +241,20 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       if (!ok) break;
       tc_fence_after();
       const uint32_t s_addr = lane_addr + (sb ? C::COL_S1 : C::COL_S0);
+      const int kv0 = j * BKF;
+      // this warp's 32 rows start at q0 + 32 * quarter: a sub-tile entirely to the right of
+      // them contributes nothing (P = 0, running max and sum unchanged)
+      if (args.causal && kv0 > q0 + quarter * 32 + 31) {
+        uint32_t zero[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) zero[i] = 0u;
+        tmem_st32(s_addr, zero);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[sb]);
+        continue;
+      }
       uint32_t rr[BKF];
       tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&rr[0]));
       tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&rr[32]));
@@ -248,8 +262,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       float s[BKF];
 #pragma unroll
       for (int i = 0; i < BKF; i++) s[i] = __uint_as_float(rr[i]);
-      const int kv0 = j * BKF;
-      const bool need_mask = (args.causal && kv0 + BKF - 1 > q0) || (kv0 + BKF > args.Sk);
+      const bool need_mask = (args.causal && kv0 + BKF - 1 > q0 + quarter * 32) || (kv0 + BKF > args.Sk);
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < BKF; c++) {
@@ -679,7 +692,24 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const int q0 = (i_begin + it) * BSUB + half * 32;  // first query column of this thread
       // masking is needed on the diagonal sub-tiles and for key rows past the end; the common
       // case runs a loop without any of the compare / select instructions
-      const bool masked = __any_sync(0xffffffffu, row_dead) || (args.causal && it < BKV / BSUB);
+      // The warp's 32 key rows against its 32 query columns: entirely above the diagonal
+      // (everything masked: zeros, no arithmetic), entirely on or below it (no masking), or
+      // the 32 x 32 block the diagonal crosses (per-element test).
+      const int rel = kv0 + quarter * 32 - q0;  // first key row minus first query column
+      const bool all_masked = args.causal && rel > 31;
+      const bool masked = __any_sync(0xffffffffu, row_dead) || (args.causal && rel + 31 > 0);
+      if (all_masked) {
+        uint32_t z[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) z[i] = 0u;
+        tmem_st16(my, z);
+        tmem_st16(my + 64, z);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[group]);
+        continue;
+      }
       uint32_t pp[16], pd[16];
       auto body = [&](auto use_mask) {
 #pragma unroll
@@ -899,8 +929,22 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       const int kv0 = j * BSUB + half * 32;  // first key column of this thread
-      const bool need_mask = (args.causal && kv0 + 31 > q0) || (kv0 + 32 > args.Sk);
+      // per warp: 32 query rows (from q0 + 32 * quarter) against 32 key columns (from kv0)
+      const int row0 = q0 + quarter * 32;
+      const bool all_masked = args.causal && kv0 > row0 + 31;
+      const bool need_mask = (args.causal && kv0 + 31 > row0) || (kv0 + 32 > args.Sk);
       uint32_t rs[32], rd[32];
+      if (all_masked) {
+        uint32_t z[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) z[i] = 0u;
+        tmem_st16(my + 64, z);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[group]);
+        continue;
+      }
       tmem_ld32(my, rs);
       tmem_ld32(my + 64, rd);
       tmem_ld_wait();
