@@ -98,9 +98,11 @@ fused_step_kernel(const StepArgs a) {
   const int epv = a.dtype_bf16 == 2 ? 4 : 8;  // elements per 16-byte vector
   const long long L = a.n / W;          // elements in one rank's slice
   const long long nvec = L / epv;       // 16-byte vectors in the slice
-  const long long per = (nvec + G - 1) / G;
-  const long long v0 = (long long)cta * per;
-  const long long v1 = min(v0 + per, nvec);
+  // CTAs interleave at the granularity of one CTA-wide vector row (8 KB): at any moment the
+  // whole grid works on one compact window of each array, which keeps DRAM pages open
+  const long long v0 = (long long)cta * blockDim.x;
+  const long long v1 = nvec;
+  const long long vstep = (long long)G * blockDim.x;
   const long long slice_vec0 = (long long)rank * nvec;  // vector index of the slice start
   const float inv = a.gscale / (float)W;
   const int sidx = a.emulate ? rank : 0;
@@ -110,7 +112,7 @@ fused_step_kernel(const StepArgs a) {
 
   if (a.dtype_bf16 == 2) {
     // fp32 all-reduce (mode 0): the same two-shot scheme on vectors of four floats
-    for (long long i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
+    for (long long i = v0 + threadIdx.x; i < v1; i += vstep) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int p = 0; p < W; p++) {
         const float4 u = __ldcg((const float4*)((const char*)a.pt.base[p] + a.grad_off) + slice_vec0 + i);
@@ -125,7 +127,7 @@ fused_step_kernel(const StepArgs a) {
     if (W > 1) cta_barrier(a.pt, rank, W, 1, cta, a.epoch + 1, a.status, &sm_flag);
     return;
   }
-  for (long long i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
+  for (long long i = v0 + threadIdx.x; i < v1; i += vstep) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) acc[j] = 0.f;

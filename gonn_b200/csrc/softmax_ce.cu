@@ -120,6 +120,54 @@ __global__ void ce_fwd_kernel(const T* __restrict__ x, const long long* __restri
   }
 }
 
+// The same for 16-bit logits without label smoothing and a class count that is a multiple
+// of 8: one pass over global memory with 16-byte loads and a running (max, sum) pair per
+// thread, combined across the CTA at the end.  No shared-memory copy of the row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+ce_fwd_vec_kernel(const T* __restrict__ x, const long long* __restrict__ tgt, const float* __restrict__ cw,
+                  float* __restrict__ loss_row, float* __restrict__ lse_out, float* __restrict__ w_row, int C,
+                  long long ignore_index, int has_ignore, int* status) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * C);
+  const int nvec = C / 8;
+  float m = -INFINITY, s = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 u = __ldg(xr + v);
+    const T* e = reinterpret_cast<const T*>(&u);
+    float f[8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; j++) { f[j] = (float)e[j]; mx = fmaxf(mx, f[j]); }
+    if (mx > m) {
+      s *= __expf(m - mx);  // exp(-inf) = 0 on the first vector
+      m = mx;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) s += __expf(f[j] - m);
+  }
+  const float M = block_max(m, red);
+  s = block_sum(m == -INFINITY ? 0.f : s * __expf(m - M), red);
+  if (threadIdx.x == 0) {
+    const float lse = M + logf(s);
+    lse_out[row] = lse;
+    const long long t = tgt[row];
+    float loss = 0.f, w = 0.f;
+    const bool ignored = has_ignore && t == ignore_index;
+    if (!ignored) {
+      if (t < 0 || t >= C) {
+        set_status(status, ST_BAD_INDEX, (int)row);
+      } else {
+        w = cw ? cw[t] : 1.f;
+        loss = w * (lse - (float)x[row * C + t]);
+      }
+    }
+    loss_row[row] = loss;
+    w_row[row] = w;
+  }
+}
+
 // Sums loss_row and w_row (single CTA, fixed order per thread then tree) and
 // writes out[0] = total loss (mean: / denom), out[1] = denom.
 __global__ void ce_reduce_kernel(const float* __restrict__ loss_row, const float* __restrict__ w_row,
@@ -232,6 +280,14 @@ template <typename T>
 int ce_fwd_t(const void* x, const long long* tgt, const float* cw, float* loss_row, float* lse,
              float* w_row, long long rows, int C, long long ignore_index, int has_ignore, float eps,
              float cw_sum, cudaStream_t s) {
+  if constexpr (sizeof(T) == 2) {
+    if (eps == 0.f && (C & 7) == 0 && (((uintptr_t)x & 15) == 0)) {
+      ce_fwd_vec_kernel<T><<<(unsigned)rows, 256, 0, s>>>((const T*)x, tgt, cw, loss_row, lse, w_row, C,
+                                                          ignore_index, has_ignore, gbh::status_ptr());
+      GB_CUDA_OK(cudaGetLastError());
+      return gbh::E_OK;
+    }
+  }
   int use_smem;
   size_t bytes;
   int rc = set_smem<T>((const void*)ce_fwd_kernel<T>, C, &use_smem, &bytes);
