@@ -51,12 +51,27 @@ class LM(nn.Module):
         return self.head(self.norm(x))
 
 
+class CNN(nn.Module):
+    """conv3x3(3->64) - BN - ReLU - maxpool2 - conv3x3(64->128) - BN - ReLU - global average - linear."""
+
+    def __init__(self):
+        super().__init__()
+        self.c1, self.b1 = nn.Conv2d(3, 64, 3), nn.BatchNorm2d(64)
+        self.c2, self.b2 = nn.Conv2d(64, 128, 3), nn.BatchNorm2d(128)
+        self.fc = nn.Linear(128, 10)
+
+    def forward(self, x):
+        x = F.max_pool2d(F.relu(self.b1(self.c1(x))), 2)
+        x = F.relu(self.b2(self.c2(x))).mean((2, 3))
+        return self.fc(x)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--config", default="lm", choices=["lm", "gpt"])
+    ap.add_argument("--config", default="lm", choices=["lm", "gpt", "cnn"])
     ap.add_argument("--batch", type=int, default=0)
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -67,15 +82,23 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     torch.manual_seed(1234)
-    if a.config == "lm":
+    if a.config == "cnn":
+        model, B, S, V = CNN().to(dev).to(memory_format=torch.channels_last), a.batch or 256, 1, 10
+        if world > 1:
+            model = nn.SyncBatchNorm.convert_sync_batchnorm(model)
+    elif a.config == "lm":
         model, B, S, V = LM(32000, 768, 12, 12, 3072, 1024).to(dev), a.batch or 16, 1024, 32000
     else:
         model, B, S, V = LM(50304, 2048, 24, 16, 8192, 2048, rms=True).to(dev), a.batch or 4, 2048, 50304
     net = nn.parallel.DistributedDataParallel(model, device_ids=[lr], gradient_as_bucket_view=True) if world > 1 else model
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, weight_decay=0.1, fused=True)
     g = torch.Generator().manual_seed(100 + rank)
-    x = torch.randint(0, V, (B, S), generator=g).to(dev)
-    y = torch.roll(x, -1, 1)
+    if a.config == "cnn":
+        x = torch.randn(B, 3, 32, 32, generator=g).to(dev).contiguous(memory_format=torch.channels_last)
+        y = torch.randint(0, 10, (B,), generator=g).to(dev)
+    else:
+        x = torch.randint(0, V, (B, S), generator=g).to(dev)
+        y = torch.roll(x, -1, 1)
 
     def step():
         with torch.autocast("cuda", dtype=torch.bfloat16):
@@ -102,8 +125,8 @@ def main():
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     if rank == 0:
-        print(json.dumps({"impl": "torch-ddp", "metric": "training throughput (tokens/s)", "config": a.config,
-                          "value": B * S * world * a.steps / (ms.item() / 1e3), "unit": "tokens/s", "n_gpus": world,
+        print(json.dumps({"impl": "torch-ddp", "metric": "training throughput", "config": a.config,
+                          "value": B * S * world * a.steps / (ms.item() / 1e3), "unit": "images/s" if a.config == "cnn" else "tokens/s", "n_gpus": world,
                           "ms_per_step": ms.item() / a.steps, "steps": a.steps, "warmup": a.warmup, "dtype": "bf16 autocast"}))
     if world > 1:
         dist.destroy_process_group()

@@ -27,30 +27,81 @@ namespace {
 constexpr int kSplits = 32;
 constexpr int kMaxC = 2048;
 
-// partial[c][split][0..1]; mode 0: (x, x^2); mode 1: (dy, dy * xhat)
+// Four consecutive elements as one 8-byte (16-bit types) or 16-byte (fp32) access.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ void ld(const float* p, float* f) {
+    const float4 u = *reinterpret_cast<const float4*>(p);
+    f[0] = u.x; f[1] = u.y; f[2] = u.z; f[3] = u.w;
+  }
+  static __device__ __forceinline__ void st(float* p, const float* f) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+};
+template <> struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ void ld(const __nv_bfloat16* p, float* f) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+  }
+  static __device__ __forceinline__ void st(__nv_bfloat16* p, const float* f) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]));
+  }
+};
+template <> struct Vec4<__half> {
+  static __device__ __forceinline__ void ld(const __half* p, float* f) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    float2 a = unpack_f16(u.x), b = unpack_f16(u.y);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+  }
+  static __device__ __forceinline__ void st(__half* p, const float* f) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_f16(f[0], f[1]), pack_f16(f[2], f[3]));
+  }
+};
+
+// Work is handed out by (sample, channel) plane: S contiguous elements that share the
+// channel's constants, so the inner loops need no index arithmetic and can be vectorised
+// whenever S is a multiple of 4 (plane starts are then 8- / 16-byte aligned).
 template <typename T>
-__global__ void bn_partial_kernel(const T* __restrict__ a, const T* __restrict__ xin,
+__device__ __forceinline__ bool planes_vectorisable(long long S, const void* p0, const void* p1, const void* p2) {
+  const uintptr_t m = sizeof(T) * 4 - 1;
+  return (S & 3) == 0 && (((uintptr_t)p0 | (uintptr_t)p1 | (uintptr_t)p2) & m) == 0;
+}
+
+// partial[c][split][0..1]; mode 0: (x, x^2); mode 1: (dy, dy * xhat).  CTA (c, split):
+// the samples of the split, one warp per sample plane at a time.
+template <typename T>
+__global__ void __launch_bounds__(256)
+bn_partial_kernel(const T* __restrict__ a, const T* __restrict__ xin,
                                   const float* __restrict__ mean, const float* __restrict__ invstd,
                                   float* __restrict__ part, int N, int C, long long S, int mode) {
   __shared__ float red[32];
   const int c = blockIdx.x, sp = blockIdx.y;
-  const long long per_n = S;
-  const long long total = (long long)N * per_n;
-  const long long chunk = (total + kSplits - 1) / kSplits;
-  const long long lo = sp * chunk, hi = min(lo + chunk, total);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per = (N + kSplits - 1) / kSplits;
+  const int n0 = sp * per, n1 = min(n0 + per, N);
   float s0 = 0.f, s1 = 0.f;
   const float mu = mode ? mean[c] : 0.f, is = mode ? invstd[c] : 0.f;
-  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-    const long long n = i / per_n, p = i - n * per_n;
-    const long long off = (n * C + c) * S + p;
-    const float v = (float)a[off];
-    if (mode == 0) {
-      s0 += v;
-      s1 += v * v;
+  const bool vec = planes_vectorisable<T>(S, a, mode ? xin : a, a);
+  for (int n = n0 + warp; n < n1; n += 8) {
+    const long long base = ((long long)n * C + c) * S;
+    if (vec) {
+      for (long long i = lane * 4; i < S; i += 128) {
+        float v[4], xv[4];
+        Vec4<T>::ld(a + base + i, v);
+        if (mode) Vec4<T>::ld(xin + base + i, xv);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          s0 += v[j];
+          s1 += mode ? v[j] * ((xv[j] - mu) * is) : v[j] * v[j];
+        }
+      }
     } else {
-      const float xh = ((float)xin[off] - mu) * is;
-      s0 += v;
-      s1 += v * xh;
+      for (long long i = lane; i < S; i += 32) {
+        const float v = (float)a[base + i];
+        s0 += v;
+        s1 += mode ? v * (((float)xin[base + i] - mu) * is) : v * v;
+      }
     }
   }
   s0 = block_sum(s0, red);
@@ -79,6 +130,7 @@ struct BnArgs {
   const void* b;
   int* ready;              // device flag: epoch value when stats are valid
   int ready_val;
+  int split;               // 1: the statistics were finalised by a separate launch (one rank): no flag, no wait
   int* status;
 };
 
@@ -140,33 +192,72 @@ __device__ __forceinline__ bool wait_ready(const BnArgs& a) {
   return ok_flag != 0;
 }
 
+// What CTA 0 of the forward does before anybody normalises: combine (and exchange) the
+// sums, publish mean / invstd, update the running statistics.
+__device__ void bn_fwd_finalise(const BnArgs& a, int* sm_flag, float* s_count) {
+  const int C = a.C;
+  if (threadIdx.x == 0) *sm_flag = 0;
+  __syncthreads();
+  float cnt;
+  combine_and_exchange(a, a.sums, &cnt, sm_flag);
+  if (threadIdx.x == 0) *s_count = cnt;
+  __syncthreads();
+  const float n = *s_count;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float mean = a.sums[c] / n;
+    float var = a.sums[C + c] / n - mean * mean;
+    var = var > 0.f ? var : 0.f;
+    a.stats[c] = mean;
+    a.stats[C + c] = rsqrtf(var + a.eps);
+    if (a.running_mean) {
+      const float unbiased = n > 1.f ? var * n / (n - 1.f) : var;
+      a.running_mean[c] = (1.f - a.momentum) * a.running_mean[c] + a.momentum * mean;
+      a.running_var[c] = (1.f - a.momentum) * a.running_var[c] + a.momentum * unbiased;
+    }
+  }
+}
+
+// The same for the backward: local sums become the parameter gradients, the (exchanged)
+// sums divided by the count are left in a.sums.
+__device__ void bn_bwd_finalise(const BnArgs& a, float* dgamma, float* dbeta, int* sm_flag, float* s_count) {
+  const int C = a.C;
+  if (threadIdx.x == 0) *sm_flag = 0;
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float s0 = 0.f, s1 = 0.f;
+    for (int sp = 0; sp < kSplits; sp++) {
+      s0 += a.part[((long long)c * kSplits + sp) * 2];
+      s1 += a.part[((long long)c * kSplits + sp) * 2 + 1];
+    }
+    if (dbeta) dbeta[c] = s0;
+    if (dgamma) dgamma[c] = s1;
+  }
+  float cnt;
+  combine_and_exchange(a, a.sums, &cnt, sm_flag);
+  if (threadIdx.x == 0) *s_count = cnt;
+  __syncthreads();
+  const float n = *s_count;
+  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) a.sums[c] = a.sums[c] / n;
+}
+
+// One-CTA launches of the two functions above, used when there is a single rank: the
+// normalise kernels then need no device flag (and can be captured in a CUDA graph).
+__global__ void __launch_bounds__(256) bn_finalise_kernel(const BnArgs a, float* dgamma, float* dbeta, int backward) {
+  __shared__ int sm_flag;
+  __shared__ float s_count;
+  if (backward) bn_bwd_finalise(a, dgamma, dbeta, &sm_flag, &s_count);
+  else bn_fwd_finalise(a, &sm_flag, &s_count);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 bn_apply_kernel(const T* __restrict__ x, T* __restrict__ y, const BnArgs a) {
   __shared__ int sm_flag;
   __shared__ float s_count;
   const int C = a.C;
-  if (a.training) {
+  if (a.training && !a.split) {
     if (blockIdx.x == 0) {
-      if (threadIdx.x == 0) sm_flag = 0;
-      __syncthreads();
-      float cnt;
-      combine_and_exchange(a, a.sums, &cnt, &sm_flag);
-      if (threadIdx.x == 0) s_count = cnt;
-      __syncthreads();
-      const float n = s_count;
-      for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        const float mean = a.sums[c] / n;
-        float var = a.sums[C + c] / n - mean * mean;
-        var = var > 0.f ? var : 0.f;
-        a.stats[c] = mean;
-        a.stats[C + c] = rsqrtf(var + a.eps);
-        if (a.running_mean) {
-          const float unbiased = n > 1.f ? var * n / (n - 1.f) : var;
-          a.running_mean[c] = (1.f - a.momentum) * a.running_mean[c] + a.momentum * mean;
-          a.running_var[c] = (1.f - a.momentum) * a.running_var[c] + a.momentum * unbiased;
-        }
-      }
+      bn_fwd_finalise(a, &sm_flag, &s_count);
       __threadfence();
       __syncthreads();
       if (threadIdx.x == 0) atomicExch(a.ready, a.ready_val);
@@ -175,10 +266,12 @@ bn_apply_kernel(const T* __restrict__ x, T* __restrict__ y, const BnArgs a) {
   }
   const float* w = (const float*)a.w;
   const float* b = (const float*)a.b;
-  const long long total = (long long)a.N * C * a.S;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int c = (int)((i / a.S) % C);
+  const long long planes = (long long)a.N * C;
+  const long long S = a.S;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool vec = planes_vectorisable<T>(S, x, y, x);
+  for (long long pl = (long long)blockIdx.x * 8 + warp; pl < planes; pl += (long long)gridDim.x * 8) {
+    const int c = (int)(pl % C);
     float mean, is;
     if (a.training) {
       mean = __ldcg(a.stats + c);
@@ -187,11 +280,29 @@ bn_apply_kernel(const T* __restrict__ x, T* __restrict__ y, const BnArgs a) {
       mean = a.running_mean[c];
       is = rsqrtf(a.running_var[c] + a.eps);
     }
-    float v = ((float)x[i] - mean) * is;
-    if (w) v *= w[c];
-    if (b) v += b[c];
-    if (a.relu) v = v > 0.f ? v : 0.f;
-    y[i] = (T)v;
+    // y = x * scale + shift
+    const float scale = w ? is * w[c] : is;
+    const float shift = (b ? b[c] : 0.f) - mean * scale;
+    const T* xp = x + pl * S;
+    T* yp = y + pl * S;
+    if (vec) {
+      for (long long i = lane * 4; i < S; i += 128) {
+        float v[4];
+        Vec4<T>::ld(xp + i, v);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          v[j] = fmaf(v[j], scale, shift);
+          if (a.relu) v[j] = fmaxf(v[j], 0.f);
+        }
+        Vec4<T>::st(yp + i, v);
+      }
+    } else {
+      for (long long i = lane; i < S; i += 32) {
+        float v = fmaf((float)xp[i], scale, shift);
+        if (a.relu) v = fmaxf(v, 0.f);
+        yp[i] = (T)v;
+      }
+    }
   }
 }
 
@@ -203,42 +314,41 @@ bn_bwd_apply_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __rest
   __shared__ int sm_flag;
   __shared__ float s_count;
   const int C = a.C;
-  if (blockIdx.x == 0) {
-    if (threadIdx.x == 0) sm_flag = 0;
-    __syncthreads();
-    // local sums are the parameter gradients (kept before the exchange)
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-      float s0 = 0.f, s1 = 0.f;
-      for (int sp = 0; sp < kSplits; sp++) {
-        s0 += a.part[((long long)c * kSplits + sp) * 2];
-        s1 += a.part[((long long)c * kSplits + sp) * 2 + 1];
-      }
-      if (dbeta) dbeta[c] = s0;
-      if (dgamma) dgamma[c] = s1;
+  if (!a.split) {
+    if (blockIdx.x == 0) {
+      bn_bwd_finalise(a, dgamma, dbeta, &sm_flag, &s_count);
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) atomicExch(a.ready, a.ready_val);
     }
-    float cnt;
-    combine_and_exchange(a, a.sums, &cnt, &sm_flag);
-    if (threadIdx.x == 0) s_count = cnt;
-    __syncthreads();
-    const float n = s_count;
-    for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) a.sums[c] = a.sums[c] / n;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) atomicExch(a.ready, a.ready_val);
+    if (!wait_ready(a)) return;
   }
-  if (!wait_ready(a)) return;
   const float* w = (const float*)a.w;
-  const long long total = (long long)a.N * C * a.S;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int c = (int)((i / a.S) % C);
+  const long long planes = (long long)a.N * C;
+  const long long S = a.S;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool vec = planes_vectorisable<T>(S, x, dy, dx);
+  for (long long pl = (long long)blockIdx.x * 8 + warp; pl < planes; pl += (long long)gridDim.x * 8) {
+    const int c = (int)(pl % C);
     const float mean = a.stats[c], is = a.stats[C + c];
     const float m1 = __ldcg(a.sums + c), m2 = __ldcg(a.sums + C + c);
-    const float xh = ((float)x[i] - mean) * is;
-    float g = (float)dy[i];
-    float v = is * (g - m1 - xh * m2);
-    if (w) v *= w[c];
-    dx[i] = (T)v;
+    const float k = w ? is * w[c] : is;
+    const T* xp = x + pl * S;
+    const T* gp = dy + pl * S;
+    T* op = dx + pl * S;
+    if (vec) {
+      for (long long i = lane * 4; i < S; i += 128) {
+        float xv[4], g[4];
+        Vec4<T>::ld(xp + i, xv);
+        Vec4<T>::ld(gp + i, g);
+#pragma unroll
+        for (int j = 0; j < 4; j++) g[j] = k * (g[j] - m1 - (xv[j] - mean) * is * m2);
+        Vec4<T>::st(op + i, g);
+      }
+    } else {
+      for (long long i = lane; i < S; i += 32)
+        op[i] = (T)(k * ((float)gp[i] - m1 - ((float)xp[i] - mean) * is * m2));
+    }
   }
 }
 
@@ -290,12 +400,14 @@ GB_EXPORT int gb_bn_fwd(int dtype, const void* x, void* y, const float* w, const
   a.ready = (int*)(work + (long long)C * kSplits * 2 + 2 * C);
   a.ready_val = ++g_ready_counter;
   a.running_mean = running_mean; a.running_var = running_var; a.w = w; a.b = b;
+  a.split = a.world == 1;
   a.status = gbh::status_ptr();
   const long long total = (long long)N * C * S;
 #define GB_BN(T)                                                                                      \
   {                                                                                                   \
     if (training)                                                                                     \
       bn_partial_kernel<T><<<dim3(C, kSplits), 256, 0, s>>>((const T*)x, nullptr, nullptr, nullptr, work, N, C, S, 0); \
+    if (training && a.split) bn_finalise_kernel<<<1, 256, 0, s>>>(a, nullptr, nullptr, 0);            \
     bn_apply_kernel<T><<<grid_for(total), 256, 0, s>>>((const T*)x, (T*)y, a);                        \
   }
   switch (dtype) {
@@ -328,11 +440,13 @@ GB_EXPORT int gb_bn_bwd(int dtype, const void* x, const void* dy, void* dx, cons
   a.ready = (int*)(work + (long long)C * kSplits * 2 + 2 * C);
   a.ready_val = ++g_ready_counter;
   a.w = w;
+  a.split = a.world == 1;
   a.status = gbh::status_ptr();
   const long long total = (long long)N * C * S;
 #define GB_BN(T)                                                                                      \
   {                                                                                                   \
     bn_partial_kernel<T><<<dim3(C, kSplits), 256, 0, s>>>((const T*)dy, (const T*)x, stats, stats + C, work, N, C, S, 1); \
+    if (a.split) bn_finalise_kernel<<<1, 256, 0, s>>>(a, dgamma, dbeta, 1);                           \
     bn_bwd_apply_kernel<T><<<grid_for(total), 256, 0, s>>>((const T*)x, (const T*)dy, (T*)dx, dgamma, dbeta, a); \
   }
   switch (dtype) {

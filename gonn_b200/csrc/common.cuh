@@ -64,6 +64,20 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// 2^x on the FMA pipe (no MUFU): round-to-nearest split x = n + f with |f| <= 0.5 by the
+// 1.5 * 2^23 trick, a cubic for 2^f (relative error about 6e-4, below the rounding step of
+// the 16-bit probabilities it feeds), and n added straight into the exponent field.  Valid
+// for x in [-126, 126]; smaller arguments are clamped (the result is then ~1e-38, not 0).
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float t = x + 12582912.f;
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(f, 0.0555041f, 0.2402265f);
+  p = fmaf(p, f, 0.6931472f);
+  p = fmaf(p, f, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
 // ---------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------

@@ -265,6 +265,26 @@ __global__ void binary_bcast_kernel(const T* __restrict__ a, const T* __restrict
                                     long long n, BcastDims d) {
   using CT = typename Conv<T>::CT;
   const long long nth = (long long)gridDim.x * blockDim.x;
+  if (n <= 0x7fffffffLL) {
+    // 32-bit index arithmetic: a 64-bit division per dimension per element dominates otherwise
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += nth) {
+      unsigned r = (unsigned)i;
+      long long oa = 0, ob = 0;
+#pragma unroll
+      for (int k = 5; k >= 0; k--) {
+        if (k < d.rank) {
+          const unsigned sh = (unsigned)d.shape[k];
+          const unsigned q = r / sh;
+          const unsigned idx = r - q * sh;
+          r = q;
+          oa += idx * d.sa[k];
+          ob += idx * d.sb[k];
+        }
+      }
+      c[i] = Conv<T>::st(bin<CT>(OP, Conv<T>::ld(a[oa]), Conv<T>::ld(b[ob])));
+    }
+    return;
+  }
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += nth) {
     long long r = i, oa = 0, ob = 0;
 #pragma unroll

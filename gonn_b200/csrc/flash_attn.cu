@@ -721,7 +721,10 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
           for (int u = 0; u < 4; u++) {
             const int j = 4 * g + u;
-            p[u] = exp2f(fmaf(__uint_as_float(rs[j]), args.scale_log2, -ls[u]));
+            // head_dim 64: every fourth exponential runs on the FMA pipe, because there the MUFU
+            // unit is the busiest resource of this loop (at 128 the tensor core is)
+            const float e = fmaf(__uint_as_float(rs[j]), args.scale_log2, -ls[u]);
+            p[u] = (HD == 64 && u == 3 && !decltype(use_mask)::value) ? exp2_poly(e) : exp2f(e);
             if (decltype(use_mask)::value) {
               if (row_dead || (args.causal && kvrow > q0 + j)) p[u] = 0.f;
             }
@@ -956,7 +959,8 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int u = 0; u < 2; u++) {
             const int c = 2 * i + u;
-            float p = exp2f(fmaf(__uint_as_float(rs[c]), args.scale_log2, -lse2));
+            const float e = fmaf(__uint_as_float(rs[c]), args.scale_log2, -lse2);
+            float p = (HD == 64 && (c & 3) == 3 && !decltype(use_mask)::value) ? exp2_poly(e) : exp2f(e);
             if (decltype(use_mask)::value) {
               if (kv0 + c >= args.Sk || (args.causal && kv0 + c > qrow)) p = 0.f;
             }

@@ -499,15 +499,16 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs& args, const Ep
     }
     const int bi = c & 1;
     const uint32_t sbc = sb0 + bi * 2048;
+    // second output: the pre-activation is packed now and written after the activation has
+    // been computed, so that the wait for the previous chunk's stores overlaps that arithmetic
+    uint4 pre_pk[4];
     if (two_out) {
-      if (lane == 0) tma_store_wait_read<0>();
-      __syncwarp();
 #pragma unroll
       for (int j = 0; j < 4; j++) {
-        uint4 o;
-        o.x = pack16x(v[j * 8], v[j * 8 + 1], args.in_bf16); o.y = pack16x(v[j * 8 + 2], v[j * 8 + 3], args.in_bf16);
-        o.z = pack16x(v[j * 8 + 4], v[j * 8 + 5], args.in_bf16); o.w = pack16x(v[j * 8 + 6], v[j * 8 + 7], args.in_bf16);
-        st_shared_v4(sb0 + 2048 + myrow + (((uint32_t)j ^ swz) << 4), o);
+        pre_pk[j].x = pack16x(v[j * 8], v[j * 8 + 1], args.in_bf16);
+        pre_pk[j].y = pack16x(v[j * 8 + 2], v[j * 8 + 3], args.in_bf16);
+        pre_pk[j].z = pack16x(v[j * 8 + 4], v[j * 8 + 5], args.in_bf16);
+        pre_pk[j].w = pack16x(v[j * 8 + 6], v[j * 8 + 7], args.in_bf16);
       }
     }
     switch (args.act) {
@@ -524,6 +525,12 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmArgs& args, const Ep
         for (int j = 0; j < 32; j++) v[j] = gelu_erf_f(v[j]);
         break;
       default: break;
+    }
+    if (two_out) {
+      if (lane == 0) tma_store_wait_read<0>();
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 4; j++) st_shared_v4(sb0 + 2048 + myrow + (((uint32_t)j ^ swz) << 4), pre_pk[j]);
     }
     if (aux_in) {
       if (c + 1 < NCH && col0 + 32 < args.N && lane == 0) {

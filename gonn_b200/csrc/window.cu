@@ -19,19 +19,34 @@ using namespace gb;
 
 namespace {
 
+// q = i / d, r = i % d; 32-bit arithmetic when both operands fit (64-bit division costs
+// tens of instructions and these kernels do one or two per element).
+__device__ __forceinline__ void divmod(long long i, long long d, bool small, long long& q, long long& r) {
+  if (small) {
+    const unsigned ii = (unsigned)i, dd = (unsigned)d;
+    const unsigned qq = ii / dd;
+    q = qq;
+    r = ii - qq * dd;
+  } else {
+    q = i / d;
+    r = i - q * d;
+  }
+}
+
 template <typename T>
 __global__ void window_gather_kernel(const T* __restrict__ x, const int* __restrict__ idx,
                                      T* __restrict__ col, int N, int C, long long S, int nwin, int T_,
                                      int kpad, float fill) {
   // one thread per (n, win, k) with k = c*T + tap; k in [0, kpad), zero beyond C*T
   const long long total = (long long)N * nwin * kpad;
+  const bool small = total <= 0x7fffffffLL;
   const int K = C * T_;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
-    const int k = (int)(i % kpad);
-    const long long r = i / kpad;
-    const int win = (int)(r % nwin);
-    const int n = (int)(r / nwin);
+    long long r, kk, nn, ww;
+    divmod(i, kpad, small, r, kk);
+    divmod(r, nwin, small, nn, ww);
+    const int k = (int)kk, win = (int)ww, n = (int)nn;
     T v = (T)0.f;
     if (k < K) {
       const int c = k / T_, tap = k - c * T_;
@@ -48,12 +63,13 @@ __global__ void window_scatter_kernel(const T* __restrict__ dcol, const int* __r
                                       const int* __restrict__ cols, T* __restrict__ dx, int N, int C,
                                       long long S, int nwin, int T_, int kpad, int accumulate) {
   const long long total = (long long)N * C * S;
+  const bool small = total <= 0x7fffffffLL;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
-    const long long pos = i % S;
-    const long long r = i / S;
-    const int c = (int)(r % C);
-    const int n = (int)(r / C);
+    long long pos, r, cc, nn;
+    divmod(i, S, small, r, pos);
+    divmod(r, C, small, nn, cc);
+    const int c = (int)cc, n = (int)nn;
     float acc = 0.f;
     for (int e = offs[pos]; e < offs[pos + 1]; e++) {
       const int wt = cols[e];
@@ -72,10 +88,12 @@ __global__ void pool_fwd_kernel(const T* __restrict__ x, const int* __restrict__
                                 T* __restrict__ y, int* __restrict__ arg, long long B, long long S,
                                 int nwin, int T_, int mode, int count_include_pad, float p) {
   const long long total = B * nwin;
+  const bool small = total <= 0x7fffffffLL && B * S <= 0x7fffffffLL;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
-    const int win = (int)(i % nwin);
-    const long long b = i / nwin;
+    long long b, ww;
+    divmod(i, nwin, small, b, ww);
+    const int win = (int)ww;
     const T* xb = x + b * S;
     const int* iw = idx + (long long)win * T_;
     if (mode == POOL_MAX) {
@@ -118,10 +136,11 @@ __global__ void pool_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
                                 long long S, int nwin, int T_, int mode, int count_include_pad,
                                 float p) {
   const long long total = B * S;
+  const bool small = total <= 0x7fffffffLL;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
-    const long long pos = i % S;
-    const long long b = i / S;
+    long long pos, b;
+    divmod(i, S, small, b, pos);
     float acc = 0.f;
     for (int e = offs[pos]; e < offs[pos + 1]; e++) {
       const int wt = cols[e];
