@@ -408,8 +408,7 @@ fa_delta_vec_kernel(const T* __restrict__ O, const T* __restrict__ dO, float* __
 // ---------------------------------------------------------------------------
 // Backward
 // ---------------------------------------------------------------------------
-constexpr int kBwdEW = 16;                       // elementwise warps: two groups of eight
-constexpr int kBwdThreads = 64 + kBwdEW * 32;    // + TMA warp and MMA warp
+constexpr int kBwdThreadsMax = 64 + 16 * 32;     // TMA warp, MMA warp, up to sixteen elementwise warps
 constexpr int BSUB = 64;                  // rows of one streamed sub-tile
 
 // Backward tiling.  The resident operand pair is a 128-row tile; the streamed pair comes in
@@ -418,7 +417,7 @@ constexpr int BSUB = 64;                  // rows of one streamed sub-tile
 // accumulations of sub-tile i-1) while the elementwise warps work on sub-tile i.  The
 // elementwise warps form two groups of eight; group g owns TMEM buffer g and every second
 // sub-tile, so the TMEM round trips of one group hide behind the arithmetic of the other.
-template <int HD>
+template <int HD, bool DUAL_>
 struct BwdCfg {
   static constexpr int CH = HD / 64;
   static constexpr int TILE_BYTES = CH * 128 * 128;
@@ -426,14 +425,25 @@ struct BwdCfg {
   static constexpr int NS = 4;
   static constexpr int STAT_BYTES = NS * 2 * BSUB * 4;  // per stage: 64 x LSE*log2(e), 64 x Delta*scale
   static constexpr int SMEM_BYTES = 2 * TILE_BYTES + NS * 2 * SUB_BYTES + STAT_BYTES + 1024 + 256;
-  static constexpr int TMEM_COLS = 512;
+  // head_dim 64: one S/dP buffer, eight elementwise warps, 256 TMEM columns and < 113 KB of
+  // shared memory, so TWO CTAs share an SM and hide each other's serial chain (S/dP MMAs ->
+  // elementwise -> accumulation MMAs) as well as each other's start-up and epilogue.
+  // head_dim 128: the accumulators alone need 256 columns, so one CTA per SM with two S/dP
+  // buffers and two groups of eight elementwise warps that own alternate sub-tiles.
+  static constexpr bool DUAL = DUAL_;
+  static_assert(!DUAL_ || HD == 64, "two CTAs per SM need head_dim 64");
+  static constexpr int NBUF = DUAL ? 1 : 2;
+  static constexpr int EW = 8 * NBUF;
+  static constexpr int THREADS = 64 + EW * 32;
+  static constexpr int CTAS_PER_SM = DUAL ? 2 : 1;
+  static constexpr int TMEM_COLS = DUAL ? 256 : 512;
   // buffer b: scores at b*128, dP at b*128 + 64; accumulators behind them
-  static constexpr int COL_ACC0 = 256, COL_ACC1 = 256 + HD;
-  // resident A operands kept in TMEM where the columns allow it: K and V of the dK/dV kernel
-  // (head_dim 64 only), Q and dO of the dQ kernel
-  static constexpr bool KV_IN_TMEM = HD == 64;
-  static constexpr int COL_KT = 256 + 2 * HD, COL_VT = COL_KT + HD / 2;
-  static constexpr int COL_QT = 256 + HD, COL_GT = COL_QT + HD / 2;
+  static constexpr int COL_ACC0 = 128 * NBUF, COL_ACC1 = COL_ACC0 + HD;
+  // resident A operands kept in TMEM where the columns allow it
+  static constexpr bool KV_IN_TMEM = HD == 64 && !DUAL;
+  static constexpr bool Q_IN_TMEM = !DUAL;
+  static constexpr int COL_KT = COL_ACC0 + 2 * HD, COL_VT = COL_KT + HD / 2;
+  static constexpr int COL_QT = COL_ACC0 + HD, COL_GT = COL_QT + HD / 2;
 };
 
 // K-major operand descriptor for step k (16 columns) of a [128 x HD] tile
@@ -479,12 +489,12 @@ __device__ __forceinline__ uint32_t pack16t(float a, float b) {
 
 // dK / dV: one CTA per 128-key tile; streams 64-row query sub-tiles.  Works in the
 // transposed domain (rows = keys) so that P^T and dS^T are A operands in TMEM.
-template <int HD, bool BF>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+template <int HD, bool BF, bool DUAL>
+__global__ void __launch_bounds__(BwdCfg<HD, DUAL>::THREADS, BwdCfg<HD, DUAL>::CTAS_PER_SM)
 fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                   const AttnArgs args) {
-  using C = BwdCfg<HD>;
+  using C = BwdCfg<HD, DUAL>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sK = smem;
@@ -600,7 +610,7 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (!mbar_wait(&q_full[st_s], ph_s, abort_flag, args.status, ST_ATTN_TIMEOUT, 13)) return false;
         tc_fence_after();
         const uint32_t qa = smem_u32(ring + st_s * 2 * C::SUB_BYTES), ga = qa + C::SUB_BYTES;
-        const uint32_t d = tmem_base + (it & 1) * 128;
+        const uint32_t d = tmem_base + (it % C::NBUF) * 128;
         // two independent accumulation chains, interleaved so that an MMA never has to wait
         // for the one just before it
 #pragma unroll
@@ -613,7 +623,7 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             tc_mma_f16(d + 64, kdesc(va, k), kdesc_sub(ga, k), idesc_s, k != 0);  // dP^T = V dO^T
           }
         }
-        tc_commit(&sdp_full[it & 1]);
+        tc_commit(&sdp_full[it % C::NBUF]);
         if (++st_s == C::NS) { st_s = 0; ph_s ^= 1; }
         return true;
       };
@@ -623,13 +633,15 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       if (ok && n_it > 0) ok = issue_sdp(0);
       int st = 0;
       for (int it = 0; it < n_it && ok; it++) {
-        if (it + 1 < n_it) {
+        // two buffers: the next sub-tile's S / dP are issued before this one's P / dS are
+        // awaited; one buffer: they follow this sub-tile's accumulation MMAs
+        if (C::NBUF == 2 && it + 1 < n_it) {
           ok = issue_sdp(it + 1);
           if (!ok) break;
         }
         trace_stamp(tr, 0, ntr);  // S / dP of the next sub-tile issued
-        const int bb = it & 1;
-        ok = mbar_wait(&p_full[bb], (it >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 14);
+        const int bb = it % C::NBUF;
+        ok = mbar_wait(&p_full[bb], (it / C::NBUF) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 14);
         if (!ok) break;
         trace_stamp(tr, 0, ntr);  // P / dS of this sub-tile ready
         tc_fence_after();
@@ -647,12 +659,13 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tc_commit(&q_empty[st]);
         if (it == n_it - 1) tc_commit(acc_done);
         if (++st == C::NS) st = 0;
+        if (C::NBUF == 1 && it + 1 < n_it) ok = issue_sdp(it + 1);
       }
     }
     __syncwarp();
   } else {
     const int e = warp - 2;
-    const int group = e >> 3;                // sub-tiles it with (it & 1) == group, TMEM buffer `group`
+    const int group = e >> 3;                // sub-tiles it with it % NBUF == group, TMEM buffer `group`
     const int half = (e >> 2) & 1;           // which 32 of the sub-tile's 64 query columns
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;       // key row inside the tile
@@ -673,12 +686,12 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     }
     long long* tr = ((blockIdx.x | blockIdx.y | blockIdx.z) == 0 && (e & 7) == 0 && lane == 0) ? args.trace : nullptr;
     int ntr = 0;
-    for (int it = group; it < n_it; it += 2) {
+    for (int it = group; it < n_it; it += C::NBUF) {
       const int st = it % C::NS;
       trace_stamp(tr, 1 + group, ntr);  // starts waiting
       ok = mbar_wait(&q_full[st], (it / C::NS) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 17);
       if (!ok) break;
-      ok = mbar_wait(&sdp_full[group], (it >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 15);
+      ok = mbar_wait(&sdp_full[group], (it / C::NBUF) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 15);
       if (!ok) break;
       trace_stamp(tr, 1 + group, ntr);  // scores ready
       tc_fence_after();
@@ -751,7 +764,7 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (ok && n_it > 0) ok = mbar_wait(acc_done, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 16);
     if (ok) {
       tc_fence_after();
-      constexpr int W = HD / 4;  // columns of dV / dK per warp
+      constexpr int W = HD * 4 / C::EW;  // columns of dV / dK per warp
       const int cw = (group * 2 + half) * W;
       uint16_t* dvrow = (uint16_t*)args.dV + (long long)b * args.dv_sb + (long long)kvrow * args.dv_ss +
                         (long long)h * args.dv_sh + cw;
@@ -783,12 +796,12 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 }
 
 // dQ: one CTA per 128-row query tile; streams 64-row key sub-tiles.
-template <int HD, bool BF>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+template <int HD, bool BF, bool DUAL>
+__global__ void __launch_bounds__(BwdCfg<HD, DUAL>::THREADS, BwdCfg<HD, DUAL>::CTAS_PER_SM)
 fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                  const AttnArgs args) {
-  using C = BwdCfg<HD>;
+  using C = BwdCfg<HD, DUAL>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
@@ -857,8 +870,9 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t fmt = BF ? 1u : 0u;
       const uint32_t idesc_s = make_idesc(1u, fmt, false, false, 128, BSUB);
       const uint32_t idesc_acc = make_idesc(1u, fmt, false, true, 128, HD);
+      const uint32_t qa = smem_u32(sQ), ga = smem_u32(sdO);
       bool ok = mbar_wait(q_full, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 22);
-      if (ok) {
+      if (ok && C::Q_IN_TMEM) {
         ok = mbar_wait(a_ready, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 28);
         tc_fence_after();
       }
@@ -868,25 +882,30 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (!mbar_wait(&kv_full[st_s], ph_s, abort_flag, args.status, ST_ATTN_TIMEOUT, 23)) return false;
         tc_fence_after();
         const uint32_t ka = smem_u32(ring + st_s * 2 * C::SUB_BYTES), va = ka + C::SUB_BYTES;
-        const uint32_t d = tmem_base + (j & 1) * 128;
+        const uint32_t d = tmem_base + (j % C::NBUF) * 128;
 #pragma unroll
         for (int k = 0; k < HD / 16; k++) {
-          tc_mma_f16_ts(d, tmem_base + C::COL_QT + k * 8, kdesc_sub(ka, k), idesc_s, k != 0);       // S = Q K^T
-          tc_mma_f16_ts(d + 64, tmem_base + C::COL_GT + k * 8, kdesc_sub(va, k), idesc_s, k != 0);  // dP = dO V^T
+          if (C::Q_IN_TMEM) {
+            tc_mma_f16_ts(d, tmem_base + C::COL_QT + k * 8, kdesc_sub(ka, k), idesc_s, k != 0);       // S = Q K^T
+            tc_mma_f16_ts(d + 64, tmem_base + C::COL_GT + k * 8, kdesc_sub(va, k), idesc_s, k != 0);  // dP = dO V^T
+          } else {
+            tc_mma_f16(d, kdesc(qa, k), kdesc_sub(ka, k), idesc_s, k != 0);
+            tc_mma_f16(d + 64, kdesc(ga, k), kdesc_sub(va, k), idesc_s, k != 0);
+          }
         }
-        tc_commit(&sdp_full[j & 1]);
+        tc_commit(&sdp_full[j % C::NBUF]);
         if (++st_s == C::NS) { st_s = 0; ph_s ^= 1; }
         return true;
       };
       if (ok && n_sub > 0) ok = issue_sdp(0);
       int st = 0;
       for (int j = 0; j < n_sub && ok; j++) {
-        if (j + 1 < n_sub) {
+        if (C::NBUF == 2 && j + 1 < n_sub) {
           ok = issue_sdp(j + 1);
           if (!ok) break;
         }
-        const int bb = j & 1;
-        ok = mbar_wait(&p_full[bb], (j >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 24);
+        const int bb = j % C::NBUF;
+        ok = mbar_wait(&p_full[bb], (j / C::NBUF) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 24);
         if (!ok) break;
         tc_fence_after();
         const uint32_t ka = smem_u32(ring + st * 2 * C::SUB_BYTES);
@@ -898,6 +917,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_commit(&kv_empty[st]);
         if (j == n_sub - 1) tc_commit(acc_done);
         if (++st == C::NS) st = 0;
+        if (C::NBUF == 1 && j + 1 < n_sub) ok = issue_sdp(j + 1);
       }
     }
     __syncwarp();
@@ -917,7 +937,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (lse2 == -INFINITY) lse2 = INFINITY;
     }
     bool ok = true;
-    if (group == 0) {
+    if (C::Q_IN_TMEM && group == 0) {
       // the eight warps of group 0 copy Q (half 0) and dO (half 1) into TMEM once
       ok = mbar_wait(q_full, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 29);
       if (ok) {
@@ -927,8 +947,8 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (lane == 0) mbar_arrive(a_ready);
       }
     }
-    for (int j = group; j < n_sub; j += 2) {
-      ok = mbar_wait(&sdp_full[group], (j >> 1) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 25);
+    for (int j = group; j < n_sub; j += C::NBUF) {
+      ok = mbar_wait(&sdp_full[group], (j / C::NBUF) & 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 25);
       if (!ok) break;
       tc_fence_after();
       const int kv0 = j * BSUB + half * 32;  // first key column of this thread
@@ -980,7 +1000,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (ok && n_sub > 0) ok = mbar_wait(acc_done, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 26);
     if (ok) {
       tc_fence_after();
-      constexpr int W = HD / 4;
+      constexpr int W = HD * 4 / C::EW;
       const int cw = (group * 2 + half) * W;
       const bool row_ok = qrow < args.Sq;
       uint16_t* dqrow = (uint16_t*)args.dQ + (long long)b * args.dq_sb + (long long)qrow * args.dq_ss +
@@ -1032,20 +1052,22 @@ struct BwdMaps {
   CUtensorMap q64, k64, v64, g64;      // 64-row boxes (streamed sub-tiles)
 };
 
-template <int HD, bool BF>
+int g_fa_dual = 1;
+
+template <int HD, bool BF, bool DUAL>
 int launch_bwd(const BwdMaps& m, const AttnArgs& a, cudaStream_t s) {
-  using C = BwdCfg<HD>;
+  using C = BwdCfg<HD, DUAL>;
   static bool configured = false;
   if (!configured) {
-    GB_CUDA_OK(cudaFuncSetAttribute(fa_bwd_dkv_kernel<HD, BF>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    GB_CUDA_OK(cudaFuncSetAttribute(fa_bwd_dq_kernel<HD, BF>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    GB_CUDA_OK(cudaFuncSetAttribute(fa_bwd_dkv_kernel<HD, BF, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    GB_CUDA_OK(cudaFuncSetAttribute(fa_bwd_dq_kernel<HD, BF, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     configured = true;
   }
   dim3 gkv((a.Sk + BKV - 1) / BKV, a.H, a.B);
-  fa_bwd_dkv_kernel<HD, BF><<<gkv, kBwdThreads, C::SMEM_BYTES, s>>>(m.q64, m.k128, m.v128, m.g64, a);
+  fa_bwd_dkv_kernel<HD, BF, DUAL><<<gkv, C::THREADS, C::SMEM_BYTES, s>>>(m.q64, m.k128, m.v128, m.g64, a);
   GB_CUDA_OK(cudaGetLastError());
   dim3 gq((a.Sq + BQ - 1) / BQ, a.H, a.B);
-  fa_bwd_dq_kernel<HD, BF><<<gq, kBwdThreads, C::SMEM_BYTES, s>>>(m.q128, m.k64, m.v64, m.g128, a);
+  fa_bwd_dq_kernel<HD, BF, DUAL><<<gq, C::THREADS, C::SMEM_BYTES, s>>>(m.q128, m.k64, m.v64, m.g128, a);
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;
 }
@@ -1058,6 +1080,13 @@ enum { DT_BF16 = 0, DT_F16 = 1 };
 
 // Timeline tracing of the dK/dV kernel: `buf` is a device buffer of 3 * 512 int64 (zeroed by
 // the caller) that CTA (0,0,0) fills with SM clock stamps; null switches tracing off.
+// head_dim 64 backward: 1 = two CTAs per SM with one S/dP buffer each, 0 = one CTA per SM
+// with two buffers and sixteen elementwise warps.
+GB_EXPORT int gb_flash_tune(int dual) {
+  g_fa_dual = dual;
+  return 0;
+}
+
 GB_EXPORT int gb_flash_trace(long long* buf) {
   g_trace = buf;
   return 0;
@@ -1177,8 +1206,11 @@ GB_EXPORT int gb_flash_bwd(int dtype, const void* q, const void* k, const void* 
   if ((rc = make_qkv_map(&m.v64, v, a.in_bf16, B, H, Sk, D, strides[6], strides[7], strides[8], 64))) return rc;
   if ((rc = make_qkv_map(&m.g64, dout, a.in_bf16, B, H, Sq, D, strides[9], strides[10], strides[11], 64))) return rc;
   if (D == 128)
-    return a.in_bf16 ? launch_bwd<128, true>(m, a, (cudaStream_t)stream)
-                     : launch_bwd<128, false>(m, a, (cudaStream_t)stream);
-  return a.in_bf16 ? launch_bwd<64, true>(m, a, (cudaStream_t)stream)
-                   : launch_bwd<64, false>(m, a, (cudaStream_t)stream);
+    return a.in_bf16 ? launch_bwd<128, true, false>(m, a, (cudaStream_t)stream)
+                     : launch_bwd<128, false, false>(m, a, (cudaStream_t)stream);
+  if (g_fa_dual)
+    return a.in_bf16 ? launch_bwd<64, true, true>(m, a, (cudaStream_t)stream)
+                     : launch_bwd<64, false, true>(m, a, (cudaStream_t)stream);
+  return a.in_bf16 ? launch_bwd<64, true, false>(m, a, (cudaStream_t)stream)
+                   : launch_bwd<64, false, false>(m, a, (cudaStream_t)stream);
 }
