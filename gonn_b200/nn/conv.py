@@ -15,6 +15,7 @@ import torch
 from ..ops.gemm import gemm
 from ..ops.reduce import reduce_axis
 from ..ops.window import _tup, sliding_index, window_gather, window_scatter
+from ..ops.shape import transpose_last2 as _transpose_last2
 from .init import fan_in_uniform_
 from .module import Module
 
@@ -145,7 +146,7 @@ class _ConvTransposeNd(Module):
             if kp > K:
                 w2 = torch.nn.functional.pad(w2, (0, kp - K))
             from ..ops.linear import matmul
-            dcol = matmul(xg.transpose(1, 2).contiguous(), w2)             # (N, L, kp)
+            dcol = matmul(_transpose_last2(xg), w2)             # (N, L, kp)
             ys.append(window_scatter(dcol, idx, og, S))
         y = ys[0] if G == 1 else torch.cat(ys, 1)
         if self.bias is not None:
@@ -194,4 +195,4 @@ class Fold(Module):
         T = idx.shape[1]
         C = col.shape[1] // T
         S = self.out[0] * self.out[1]
-        return window_scatter(col.transpose(1, 2).contiguous(), idx, C, S).reshape(N, C, *self.out)
+        return window_scatter(_transpose_last2(col), idx, C, S).reshape(N, C, *self.out)

@@ -5,7 +5,8 @@ Cells: ``RNNCell`` (tanh / ReLU), ``LSTMCell`` (gate order i, f, g, o; optional 
 ``RNN`` / ``LSTM`` / ``GRU``: batch-first input (B, T, F); options layers, bidirectional,
 dropout between layers, ReLU (RNN), proj_size (LSTM); children ``cells.N``, ``backcells.N``,
 ``dropout.N``.  State layout for stacks: (L * D, B, H).  Gates are computed by the fused
-Linear kernels and the elementwise kernels; the time loop stays on the autograd tape.
+Linear kernels and one fused gate kernel per cell and direction (``ops/rnn.py``); the time
+loop stays on the autograd tape.
 """
 from __future__ import annotations
 
@@ -14,6 +15,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 
 from ..ops import elementwise as _ew
+from ..ops import rnn as _rnn_ops
 from .dropout import Dropout
 from .embedding import Embedding
 from .linear import Linear
@@ -64,11 +66,10 @@ class LSTMCell(Module):
         if state is None:
             state = (x.new_zeros(B, self.hidden_out()), x.new_zeros(B, H))
         h, c = state
-        gates = self.wih(x) + self.whh(h)
-        i, f = _sig(gates[:, :H]), _sig(gates[:, H:2 * H])
-        g, o = _tanh(gates[:, 2 * H:3 * H]), _sig(gates[:, 3 * H:])
-        c_new = f * c + i * g
-        h_new = o * _tanh(c_new)
+        # the second projection adds onto the first in its GEMM epilogue; the gate arithmetic is
+        # one fused kernel per direction (ops/rnn.py)
+        gates = self.whh(h, residual=self.wih(x))
+        h_new, c_new = _rnn_ops.lstm_gates(gates, c)
         if self.whr is not None:
             h_new = self.whr(h_new)
         return h_new, c_new
@@ -85,11 +86,7 @@ class GRUCell(Module):
         H = self.hidden_size
         if h is None:
             h = x.new_zeros(x.shape[0], H)
-        xg, hg = self.wih(x), self.whh(h)
-        r = _sig(xg[:, :H] + hg[:, :H])
-        z = _sig(xg[:, H:2 * H] + hg[:, H:2 * H])
-        n = _tanh(xg[:, 2 * H:] + r * hg[:, 2 * H:])
-        return (1 - z) * n + z * h
+        return _rnn_ops.gru_gates(self.wih(x), self.whh(h), h)
 
 
 # ---------------------------------------------------------------------------------------

@@ -415,7 +415,10 @@ def Where(cond, a, b): return torch.where(cond.bool() if cond.dtype != torch.boo
 @_export
 def MaskedFill(x, mask, value: float): return x.masked_fill(mask.bool(), value)
 @_export
-def Cumsum(x, axis: int): return torch.cumsum(x, dim=axis)
+def Cumsum(x, axis: int):
+    """Inclusive prefix sum along ``axis`` (scan kernel on CUDA tensors)."""
+    from ..ops.shape import cumsum as _cumsum
+    return _cumsum(x, axis)
 @_export
 def Flip(x, *axes): return torch.flip(x, dims=list(axes))
 @_export

@@ -238,3 +238,26 @@ def test_functional_call_grads_to_replacements():
     gnn.FunctionalCallGrad(lin, x, {"weight": w2}, lambda y: (y ** 2).mean(), gnn.WithGradsToReplacements())
     assert torch.allclose(w2.grad, 2 * grads["weight"])
     assert gnn.ParametrizationWithInverse is gnn.InvertibleParametrization
+
+
+def test_lstm_gru_cells_match_torch_cells():
+    """Cell formulas (gate order i,f,g,o / r,z,n) against torch's cells with copied weights."""
+    import gonn_b200.nn as gnn
+    torch.manual_seed(0)
+    x = torch.randn(5, 7, dtype=torch.float64)
+    h = torch.randn(5, 6, dtype=torch.float64)
+    c = torch.randn(5, 6, dtype=torch.float64)
+    mine = gnn.LSTMCell(7, 6, dtype=torch.float64)
+    ref = torch.nn.LSTMCell(7, 6, dtype=torch.float64)
+    with torch.no_grad():
+        ref.weight_ih.copy_(mine.wih.weight); ref.bias_ih.copy_(mine.wih.bias)
+        ref.weight_hh.copy_(mine.whh.weight); ref.bias_hh.zero_()
+    h1, c1 = mine(x, (h, c))
+    h2, c2 = ref(x, (h, c))
+    assert torch.allclose(h1, h2, atol=1e-10) and torch.allclose(c1, c2, atol=1e-10)
+    g1 = gnn.GRUCell(7, 6, dtype=torch.float64)
+    g2 = torch.nn.GRUCell(7, 6, dtype=torch.float64)
+    with torch.no_grad():
+        g2.weight_ih.copy_(g1.wih.weight); g2.bias_ih.copy_(g1.wih.bias)
+        g2.weight_hh.copy_(g1.whh.weight); g2.bias_hh.copy_(g1.whh.bias)
+    assert torch.allclose(g1(x, h), g2(x, h), atol=1e-10)

@@ -217,3 +217,56 @@ def test_dropout_statistics_and_backward(status_ok):
     assert abs(y.max().item() - 1 / 0.75) < 1e-6
     y.backward(torch.ones_like(y))
     assert torch.equal(x.grad, y.detach())  # same mask regenerated in backward
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_rnn_gates_match_oracle(dtype):
+    """LSTM / GRU gate kernels, forward and backward, against the torch expression in fp32."""
+    from gonn_b200.ops import rnn as R
+    torch.manual_seed(0)
+    B, H = 37, 48
+    tol = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
+    gates = torch.randn(B, 4 * H, device="cuda").to(dtype).requires_grad_(True)
+    c = torch.randn(B, H, device="cuda").to(dtype).requires_grad_(True)
+    h1, c1 = R.lstm_gates(gates, c)
+    gf, cf = gates.detach().float().requires_grad_(True), c.detach().float().requires_grad_(True)
+    h2, c2 = R.lstm_gates_ref(gf, cf)
+    dh, dc = torch.randn_like(h2), torch.randn_like(c2)
+    g1 = torch.autograd.grad((h1, c1), (gates, c), (dh.to(dtype), dc.to(dtype)))
+    g2 = torch.autograd.grad((h2, c2), (gf, cf), (dh, dc))
+    assert torch.allclose(h1.float(), h2, **tol) and torch.allclose(c1.float(), c2, **tol)
+    for a, b in zip(g1, g2):
+        assert torch.allclose(a.float(), b, **tol)
+    xg = torch.randn(B, 3 * H, device="cuda").to(dtype).requires_grad_(True)
+    hg = torch.randn(B, 3 * H, device="cuda").to(dtype).requires_grad_(True)
+    h = torch.randn(B, H, device="cuda").to(dtype).requires_grad_(True)
+    y1 = R.gru_gates(xg, hg, h)
+    ref_in = [t.detach().float().requires_grad_(True) for t in (xg, hg, h)]
+    y2 = R.gru_gates_ref(*ref_in)
+    dy = torch.randn_like(y2)
+    g1 = torch.autograd.grad(y1, (xg, hg, h), dy.to(dtype))
+    g2 = torch.autograd.grad(y2, ref_in, dy)
+    assert torch.allclose(y1.float(), y2, **tol)
+    for a, b in zip(g1, g2):
+        assert torch.allclose(a.float(), b, **tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float64])
+def test_transpose_and_cumsum_kernels(dtype):
+    from gonn_b200.ops.shape import cumsum, transpose_last2
+    torch.manual_seed(0)
+    x = torch.randn(3, 45, 70, device="cuda").to(dtype)
+    assert torch.equal(transpose_last2(x), x.transpose(1, 2).contiguous())
+    for axis, n in ((-1, 70), (1, 45)):
+        xr = x.detach().clone().requires_grad_(True)
+        y = cumsum(xr, axis)
+        ref = torch.cumsum(x.double(), dim=axis)
+        tol = 1e-10 if dtype == torch.float64 else (1e-4 if dtype == torch.float32 else 0.15)
+        assert (y.double() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+        g = torch.randn_like(x)
+        (gx,) = torch.autograd.grad(y, xr, g)
+        gref = torch.flip(torch.cumsum(torch.flip(g.double(), [axis]), dim=axis), [axis])
+        assert (gx.double() - gref).abs().max().item() <= tol * max(1.0, gref.abs().max().item())
+    # a row longer than one chunk (carry across chunks)
+    long = torch.randn(2, 5000, device="cuda", dtype=torch.float32)
+    assert torch.allclose(cumsum(long, -1), torch.cumsum(long, -1), rtol=1e-4, atol=1e-3)
