@@ -67,6 +67,7 @@ class _Norm(torch.autograd.Function):
                 _l.L(rows), _l.I(D), _l.F(eps), _l.stream_ptr())
         ctx.save_for_backward(xc, weight, mean, rstd)
         ctx.rms, ctx.has_bias = rms, bias is not None
+        ctx.bias_ref = bias
         return y
 
     @staticmethod
@@ -79,13 +80,42 @@ class _Norm(torch.autograd.Function):
         wdt = _wdt(xc, weight)
         need_w = weight is not None and ctx.needs_input_grad[1]
         need_b = ctx.has_bias and ctx.needs_input_grad[2]
-        dgamma = torch.empty(D, dtype=wdt, device=xc.device) if need_w else None
-        dbeta = torch.empty(D, dtype=wdt, device=xc.device) if need_b else None
+        # Parameters owned by a data-parallel wrapper: the reduction kernel writes straight
+        # into the gradient bucket on the first write of a step (no accumulation pass, no
+        # zero fill); later writes of the same step go through a temporary and are added.
+        sunk = []
+
+        def out_for(param, need):
+            if not need:
+                return None
+            sink = getattr(param, "_gb_sink", None)
+            if sink is not None and xc.is_cuda:
+                buf, fresh = sink.target(param)
+                if fresh and buf.dtype == wdt:
+                    sunk.append((param, sink, None, None))
+                    return buf
+                tmp = torch.empty(D, dtype=wdt, device=xc.device)
+                sunk.append((param, sink, tmp, buf))
+                return tmp
+            return torch.empty(D, dtype=wdt, device=xc.device)
+
+        dgamma = out_for(weight, need_w)
+        dbeta = out_for(ctx.bias_ref, need_b)
         scratch, srows = _scratch_for(xc.device, D) if (need_w or need_b) else (None, 0)
         _l.call("gb_norm_bwd", _l.I(int(ctx.rms)), _l.I(_l.dtype_code(xc.dtype)), _l.I(_l.dtype_code(wdt)),
                 _l.ptr(xc), _l.ptr(dyc), _l.ptr(weight), _l.ptr(mean), _l.ptr(rstd), _l.ptr(dx),
                 _l.ptr(dgamma), _l.ptr(dbeta), _l.ptr(scratch), _l.I(srows), _l.L(rows), _l.I(D),
                 _l.stream_ptr())
+        handled = set()
+        for param, sink, tmp, buf in sunk:
+            if tmp is not None:
+                buf.add_(tmp.to(buf.dtype))
+            sink.ready(param)
+            handled.add(id(param))
+        if weight is not None and id(weight) in handled:
+            dgamma = None
+        if ctx.bias_ref is not None and id(ctx.bias_ref) in handled:
+            dbeta = None
         return dx, dgamma, dbeta, None, None
 
 
