@@ -98,6 +98,21 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
 
+    if world > 1:
+        # set-up, not a step: NCCL builds its communicator at the first collective
+        warm = torch.ones(1, device=device)
+        dist.all_reduce(warm)
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    # set-up, not a step: about 0.3 s of dense work brings the GPU out of its idle power state,
+    # so that the first warm-up steps do not run at ramping clocks
+    spin = torch.randn(8192, 8192, device=device, dtype=torch.bfloat16)
+    for _ in range(300):
+        torch.matmul(spin, spin)
+    torch.cuda.synchronize()
+    del spin
+
     cfg = CONFIGS[args.config]
     B = args.batch or cfg["batch"]
     S, V = cfg["seq"], cfg["vocab"]

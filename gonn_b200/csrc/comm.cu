@@ -59,6 +59,7 @@ struct StepArgs {
   long long n;               // elements in the bucket (multiple of world * 8)
   int mode;                  // 0: all-reduce-mean into the gradients; 1: sharded AdamW + all-gather
   int dtype_bf16;            // element type: 0 fp16, 1 bf16, 2 fp32 (mode 0 only)
+  int interleave;            // work mapping of the CTAs (see the kernel)
   unsigned int epoch;        // barrier epochs epoch (start) and epoch+1 (end)
   float* master[kMaxWorld];  // per emulated rank (index 0 in real runs): fp32 shard state
   float* m[kMaxWorld];
@@ -98,11 +99,21 @@ fused_step_kernel(const StepArgs a) {
   const int epv = a.dtype_bf16 == 2 ? 4 : 8;  // elements per 16-byte vector
   const long long L = a.n / W;          // elements in one rank's slice
   const long long nvec = L / epv;       // 16-byte vectors in the slice
-  // CTAs interleave at the granularity of one CTA-wide vector row (8 KB): at any moment the
-  // whole grid works on one compact window of each array, which keeps DRAM pages open
-  const long long v0 = (long long)cta * blockDim.x;
-  const long long v1 = nvec;
-  const long long vstep = (long long)G * blockDim.x;
+  // interleave = 1: CTAs interleave at the granularity of one CTA-wide vector row (8 KB), so
+  // that at any moment the whole grid works on one compact window of each array (keeps DRAM
+  // pages open: 4.9 instead of 3.6 TB/s on one GPU).  interleave = 0: every CTA owns one
+  // contiguous range.
+  long long v0, v1, vstep;
+  if (a.interleave) {
+    v0 = (long long)cta * blockDim.x;
+    v1 = nvec;
+    vstep = (long long)G * blockDim.x;
+  } else {
+    const long long per = (nvec + G - 1) / G;
+    v0 = (long long)cta * per;
+    v1 = min(v0 + per, nvec);
+    vstep = blockDim.x;
+  }
   const long long slice_vec0 = (long long)rank * nvec;  // vector index of the slice start
   const float inv = a.gscale / (float)W;
   const int sidx = a.emulate ? rank : 0;
@@ -374,6 +385,15 @@ void comm_get(gbc::PeerTable* pt, int* rank, int* world) {
 unsigned int comm_next_epochs(int count) { return next_epochs(count); }
 }  // namespace gbh
 
+// Work mapping of the fused step: 1 interleaved rows, 0 contiguous ranges, -1 (default)
+// interleaved on one GPU (4.9 vs 3.6 TB/s measured) and contiguous with peers (steady-state
+// steps of the 12-layer LM on eight GPUs: 19.5 ms contiguous, 20.0 ms interleaved).
+int g_interleave = -1;
+GB_EXPORT int gb_comm_tune(int interleave) {
+  g_interleave = interleave;
+  return 0;
+}
+
 // Fused bucket step (see the top of the file).  Offsets are bytes from the
 // start of the symmetric buffer (flag area included).  n: elements, a multiple
 // of world*8.  mode 0: mean of the gradients written to every rank; mode 1:
@@ -400,6 +420,7 @@ GB_EXPORT int gb_comm_fused_step(int mode, int dtype_bf16, long long grad_off, l
   a.pt = g_comm.peers;
   a.rank = g_comm.rank; a.world = W; a.emulate = emulate;
   a.grad_off = grad_off; a.param_off = param_off; a.n = n; a.mode = mode; a.dtype_bf16 = dtype_bf16;
+  a.interleave = g_interleave < 0 ? (W == 1) : (g_interleave != 0);
   a.epoch = W > 1 ? next_epochs(2) : 0;
   const int ns = emulate ? W : 1;
   for (int i = 0; i < ns; i++) {

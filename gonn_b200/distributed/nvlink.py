@@ -12,6 +12,7 @@ buffers on one GPU driven by a single cooperative launch (for tests).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional
 
 import torch
@@ -37,12 +38,20 @@ def current():
     return _current[0]
 
 
+def _apply_env_tuning():
+    """``GB_STEP_INTERLEAVE`` = 0 / 1 overrides the work mapping of the fused step kernel."""
+    v = os.environ.get("GB_STEP_INTERLEAVE")
+    if v is not None and _l.available():
+        _l.lib().gb_comm_tune(int(v))
+
+
 class SymmetricMemory:
     """This rank's symmetric buffer.  Offsets handed to kernels count from the buffer's
     base (the flag area comes first); ``view`` takes offsets into the data region."""
 
     def __init__(self, data_bytes: int, rank: int = 0, world: int = 1, process_group=None,
                  emulate: int = 0, device: Optional[torch.device] = None):
+        _apply_env_tuning()
         self.rank, self.world, self.emulate = rank, world, emulate
         _current[0] = self
         if device is None:
