@@ -16,6 +16,11 @@
 //               O += P V with P read from TMEM (written there by the softmax warps)
 //   warps 2-5   softmax: one thread per row; running max / sum in registers;
 //               O is rescaled only when the max moved by more than 2^8
+// Backward: a row-statistics kernel (Delta = dO . O), then one CTA per 128-key tile for
+// dK / dV and one CTA per 128-query tile for dQ; both stream 64-row sub-tiles, keep S and dP
+// in TMEM (two buffers and sixteen elementwise warps at head_dim 128; one buffer, eight
+// warps and two CTAs per SM at head_dim 64) and feed P^T / dS^T back to the tensor core as
+// TMEM A operands.
 // Tensors are addressed through 4-D tensor maps (d, s, h, b) with arbitrary
 // strides, so (B,S,H,D) and (B,H,S,D) layouts both work without copies.
 #include "common.cuh"

@@ -11,13 +11,20 @@
 // reference's Gemm contract (backend/backend.go:61-78) that its MatMul backward
 // relies on (tensor/ops_matmul.go:36-46).
 //
-// Kernel structure (one persistent CTA per SM, 320 threads):
-//   warp 0     TMA producer: fills a ring of shared-memory stages
-//   warp 1     MMA issuer: one lane issues tcgen05.mma, commits to mbarriers
-//   warps 2-9  epilogue: tcgen05.ld the accumulator, apply bias / activation /
-//              auxiliary tensor, store to global (two warps per TMEM lane quarter)
-// Two accumulator buffers in TMEM let the epilogue of tile i overlap the MMAs
-// of tile i+1.
+// Two persistent kernels share one epilogue.
+// One-CTA kernel (one CTA per SM, 320 threads, 128 x 256 or 128 x 128 tiles):
+//   warp 0     TMA producer: one elected thread fills a ring of shared-memory stages
+//   warp 1     MMA issuer: one elected thread runs the whole tcgen05.mma issue loop and
+//              commits to mbarriers (an issue loop spread over a warp with `lane == 0`
+//              branches left the tensor pipe idle a fifth of the time)
+//   warps 2-9  epilogue: tcgen05.ld the accumulator, bias / activation / auxiliary tensor,
+//              then a swizzled staging buffer per warp and TMA stores (direct 16-byte
+//              stores remain for unaligned outputs and accumulation into C)
+// Two-CTA kernel (a cluster of two CTAs per 256 x 256 tile, tcgen05 cta_group::2): each CTA
+// stages its own rows of A and half of the columns of B; the leader issues the MMAs.
+// Two accumulator buffers in TMEM let the epilogue of tile i overlap the MMAs of tile
+// i+1.  Split-K: K slices of a tile run as separate work units into fp32 partials that a
+// finish kernel adds in slice order.
 #include "common.cuh"
 
 using namespace gb;
