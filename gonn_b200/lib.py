@@ -78,8 +78,22 @@ def use_native(t: torch.Tensor) -> bool:
     return t.is_cuda
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
+def current_stream_handle() -> int:
+    """The current CUDA stream of the current device as an integer handle.  The private torch
+    entry points are an order of magnitude cheaper than ``torch.cuda.current_stream()`` (which
+    builds a Stream object: about 16 us per call, 5 ms per training step of the 12-layer LM);
+    the public API is the fallback."""
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
+    return torch.cuda.current_stream().cuda_stream
+
+
 def stream_ptr() -> c_void_p:
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    return c_void_p(current_stream_handle())
 
 
 def ptr(t) -> c_void_p:
@@ -94,10 +108,15 @@ def check(rc: int, what: str = "native call") -> None:
         raise NativeError(f"{what} failed ({rc}): {msg}")
 
 
+_fn_cache = {}
+
+
 def call(name: str, *args) -> None:
     """Calls ``name`` with ctypes-converted ``args`` and raises on a non-zero status."""
     global launch_count, kernel_count
-    fn = getattr(lib(), name)
+    fn = _fn_cache.get(name)
+    if fn is None:
+        fn = _fn_cache[name] = getattr(lib(), name)
     rc = fn(*args)
     launch_count += 1
     kernel_count += KERNELS_PER_CALL.get(name, 1)

@@ -50,7 +50,7 @@ _ws_cache = {}
 def _workspace(device: torch.device) -> torch.Tensor:
     """fp32 scratch for split-K partial products, one per (device, stream) so that launches
     on different streams never share it."""
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    key = (device.index, _l.current_stream_handle())
     buf = _ws_cache.get(key)
     if buf is None:
         buf = torch.empty(_WS_BYTES, dtype=torch.uint8, device=device)
