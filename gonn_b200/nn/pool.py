@@ -86,8 +86,20 @@ class LPPool3d(LPPool1d):
     nd = 3
 
 
+_adaptive_cache = {}
+
+
 def _adaptive_index(in_shape, out_shape):
-    """Windows [floor(i*in/out), ceil((i+1)*in/out)) per dim, padded with -1 to a common size."""
+    """Windows [floor(i*in/out), ceil((i+1)*in/out)) per dim, padded with -1 to a common size
+    (cached per shape pair: the map depends on nothing else)."""
+    key = (tuple(in_shape), tuple(out_shape))
+    hit = _adaptive_cache.get(key)
+    if hit is None:
+        hit = _adaptive_cache[key] = _adaptive_index_build(in_shape, out_shape)
+    return hit
+
+
+def _adaptive_index_build(in_shape, out_shape):
     nd = len(in_shape)
     strides = [1] * nd
     for d in range(nd - 2, -1, -1):
