@@ -162,12 +162,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         return out
 
     # tensor-core path: contiguous dim pitch must be a multiple of 8 elements
-    a2 = _pad_last(a, 8)
-    b2 = _pad_last(b, 8)
-    a2, lda = _row_major_2d(a2)
-    b2, ldb = _row_major_2d(b2)
-    sA = a2.stride(0) if a2.dim() == 3 and a2.shape[0] > 1 else 0
-    sB = b2.stride(0) if b2.dim() == 3 and b2.shape[0] > 1 else 0
+    if (not batched and a.is_contiguous() and b.is_contiguous() and a.shape[1] % 8 == 0
+            and b.shape[1] % 8 == 0 and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0):
+        # the common case (two contiguous, aligned matrices): nothing to pad or copy
+        a2, b2, lda, ldb, sA, sB = a, b, a.shape[1], b.shape[1], 0, 0
+    else:
+        a2 = _pad_last(a, 8)
+        b2 = _pad_last(b, 8)
+        a2, lda = _row_major_2d(a2)
+        b2, ldb = _row_major_2d(b2)
+        sA = a2.stride(0) if a2.dim() == 3 and a2.shape[0] > 1 else 0
+        sB = b2.stride(0) if b2.dim() == 3 and b2.shape[0] > 1 else 0
     if batch > 1 and ((sA % 8) or (sB % 8)):
         a2 = a2.contiguous() if sA % 8 else a2
         b2 = b2.contiguous() if sB % 8 else b2
