@@ -1,0 +1,16 @@
+"""The code blocks of the user guide run (CPU), chapter by chapter, sharing one namespace."""
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_guide_snippets_run():
+    text = open(os.path.join(ROOT, "docs", "GUIDE.md")).read()
+    blocks = re.findall(r"```python\n(.*?)```", text, flags=re.S)
+    assert len(blocks) >= 7
+    ns = {}
+    for code in blocks:
+        if "init_process_group" in code:      # the multi-process chapter needs a launcher
+            continue
+        exec(compile(code, "<guide>", "exec"), ns)
