@@ -109,6 +109,14 @@ def check(rc: int, what: str = "native call") -> None:
 
 
 _fn_cache = {}
+_call_hook = None
+
+
+def set_call_hook(hook) -> None:
+    """Installs ``hook(name, fn, args) -> status`` around every native call (``None`` removes
+    it).  Used by ``gonn_b200.utils.trace``; the hook must call ``fn(*args)`` itself."""
+    global _call_hook
+    _call_hook = hook
 
 
 def call(name: str, *args) -> None:
@@ -117,7 +125,7 @@ def call(name: str, *args) -> None:
     fn = _fn_cache.get(name)
     if fn is None:
         fn = _fn_cache[name] = getattr(lib(), name)
-    rc = fn(*args)
+    rc = fn(*args) if _call_hook is None else _call_hook(name, fn, args)
     launch_count += 1
     kernel_count += KERNELS_PER_CALL.get(name, 1)
     if rc != 0:
