@@ -63,7 +63,19 @@ class Backend:
         pass
 
 
-class NativeBackend(Backend):
+class Elementwiser:
+    """Optional capability (backend/backend.go:89-92): a backend that also evaluates the
+    enum-dispatched elementwise kinds.  ``Unary`` / ``Binary`` return the result, or None to
+    decline, in which case the caller evaluates the op on the host path."""
+
+    def Unary(self, kind: "UnaryKind", x):
+        return None
+
+    def Binary(self, kind: "BinaryKind", a, b):
+        return None
+
+
+class NativeBackend(Backend, Elementwiser):
     def __init__(self, device: str):
         self.device = device
 

@@ -13,7 +13,7 @@ import os
 import struct
 import threading
 import queue
-from typing import Callable, Iterator, List, Optional, Sequence, Tuple
+from typing import Callable, Iterator, List, NamedTuple, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -72,6 +72,12 @@ class ConcatDataset(Dataset):
         return self.parts[k].Get(i - int(self.offsets[k]))
 
 
+class Batch(NamedTuple):
+    """One mini-batch (data/dataloader.go:11-14); unpacks as ``x, y``."""
+    X: torch.Tensor
+    Y: torch.Tensor
+
+
 class DataLoader:
     def __init__(self, dataset: Dataset, batch_size: int = 1, shuffle: bool = False, drop_last: bool = False,
                  seed: int = 0, transform: Optional[Callable] = None, device=None, pin_memory: bool = False,
@@ -97,7 +103,7 @@ class DataLoader:
             xs, ys = zip(*(self.dataset.Get(int(i)) for i in idx))
             if self.transform is not None:
                 xs = [self.transform(x) for x in xs]
-            yield torch.stack(list(xs)), torch.stack(list(ys))
+            yield Batch(torch.stack(list(xs)), torch.stack(list(ys)))
 
     def Iter(self) -> Iterator[Tuple[torch.Tensor, torch.Tensor]]:
         """Batches produced by a background thread (the reference feeds a channel from a goroutine)."""
@@ -126,65 +132,109 @@ class DataLoader:
                 with torch.cuda.stream(copy_stream):
                     xd, yd = x.to(self.device, non_blocking=True), y.to(self.device, non_blocking=True)
                 torch.cuda.current_stream().wait_stream(copy_stream)
-                yield xd, yd
+                yield Batch(xd, yd)
             else:
-                yield x, y
+                yield Batch(x, y)
 
     __iter__ = Iter
 
 
 # ---- transforms (data/transforms.go:13-180) --------------------------------------------------
-class Normalize:
-    """Per leading channel: (x - mean[c]) / std[c]."""
+class Transform:
+    """A per-sample transform: ``Apply(t) -> tensor`` (data/transforms.go:13-15); instances are
+    also callable, which is how the ``DataLoader`` uses them."""
+
+    def Apply(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def __call__(self, x):
+        return self.Apply(x)
+
+
+class Normalize(Transform):
+    """Per leading channel: (x - mean[c]) / std[c]; the lengths must match the channel count and
+    no std may be zero (data/transforms.go:28-49)."""
 
     def __init__(self, mean: Sequence[float], std: Sequence[float]):
         self.Mean, self.Std = list(mean), list(std)
 
-    def __call__(self, x):
+    def Apply(self, x):
+        if x.dim() == 0:
+            raise ValueError("data.Normalize: cannot normalize a 0-D tensor")
+        c = x.shape[0]
+        if len(self.Mean) != c or len(self.Std) != c:
+            raise ValueError(f"data.Normalize: mean/std length {len(self.Mean)}/{len(self.Std)} must match "
+                             f"channel dim {c}")
+        if any(v == 0 for v in self.Std):
+            raise ValueError("data.Normalize: std has a zero entry")
         shape = [-1] + [1] * (x.dim() - 1)
-        return (x - torch.tensor(self.Mean, dtype=x.dtype).reshape(shape)) / torch.tensor(self.Std, dtype=x.dtype).reshape(shape)
+        dt = x.dtype if x.is_floating_point() else torch.float32
+        mean = torch.tensor(self.Mean, dtype=dt, device=x.device).reshape(shape)
+        std = torch.tensor(self.Std, dtype=dt, device=x.device).reshape(shape)
+        return (x.to(dt) - mean) / std
 
 
-class RandomHorizontalFlip:
+class RandomHorizontalFlip(Transform):
+    """Flips the last dimension with probability ``P`` (0 or less: never)."""
+
     def __init__(self, p: float = 0.5, seed: Optional[int] = None):
         self.P, self.Rand = p, np.random.default_rng(seed)
 
-    def __call__(self, x):
-        return x.flip(-1) if self.Rand.random() < self.P else x
+    def Apply(self, x):
+        if self.P <= 0:
+            return x.clone()
+        return x.flip(-1) if self.Rand.random() < self.P else x.clone()
 
 
-class RandomCrop:
-    def __init__(self, size: int, seed: Optional[int] = None):
-        self.Size, self.Rand = size, np.random.default_rng(seed)
+class RandomCrop(Transform):
+    """Crops the trailing ``len(size)`` dimensions to ``size`` at a uniformly drawn offset; an
+    integer crops the last two dimensions to a square (data/transforms.go:103-150)."""
 
-    def __call__(self, x):
-        H, W = x.shape[-2:]
-        if self.Size > H or self.Size > W:
-            raise ValueError("RandomCrop: crop larger than the image")
-        t = int(self.Rand.integers(0, H - self.Size + 1))
-        l = int(self.Rand.integers(0, W - self.Size + 1))
-        return x[..., t:t + self.Size, l:l + self.Size]
+    def __init__(self, size, seed: Optional[int] = None):
+        self.Size = [size, size] if isinstance(size, int) else list(size)
+        self.Rand = np.random.default_rng(seed)
+
+    def Apply(self, x):
+        if not self.Size:
+            return x.clone()
+        if len(self.Size) > x.dim():
+            raise ValueError(f"data.RandomCrop: size {self.Size} has more dims than tensor shape {list(x.shape)}")
+        off = x.dim() - len(self.Size)
+        sl = [slice(None)] * x.dim()
+        for i, s in enumerate(self.Size):
+            dim = x.shape[off + i]
+            if s > dim or s <= 0:
+                raise ValueError(f"data.RandomCrop: crop size {s} invalid for dim {off + i} (size {dim})")
+            o = int(self.Rand.integers(0, dim - s + 1)) if dim > s else 0
+            sl[off + i] = slice(o, o + s)
+        return x[tuple(sl)].clone()
 
 
-class ToFloat:
-    def __init__(self, scale: float = 1.0 / 255):
+class ToFloat(Transform):
+    """Converts to floating point.  The reference's tensors are always float64, so there it is
+    the identity (data/transforms.go:160-162); here integer images become float32, optionally
+    scaled (``scale=1/255`` maps bytes to [0, 1])."""
+
+    def __init__(self, scale: float = 1.0):
         self.scale = scale
 
-    def __call__(self, x):
-        return x.to(torch.float32) * self.scale
+    def Apply(self, x):
+        y = x if x.is_floating_point() else x.to(torch.float32)
+        return y * self.scale if self.scale != 1.0 else y
 
 
-class Compose:
+class Compose(Transform):
     def __init__(self, *ts):
-        self.ts = list(ts)
+        if len(ts) == 1 and isinstance(ts[0], (list, tuple)):
+            ts = tuple(ts[0])
+        self.Transforms = list(ts)
 
-    def __call__(self, x):
-        for t in self.ts:
+    def Apply(self, x):
+        for t in self.Transforms:
             x = t(x)
         return x
 
 
-# ---- loaders (data/mnist.go, data/csv.go) ------------------------------------------------------
 def _read_idx(path):
     opener = gzip.open if path.endswith(".gz") else open
     with opener(path, "rb") as f:
@@ -258,3 +308,13 @@ def MakeMoons(n: int, noise: float = 0.1, seed: int = 0):
     X += noise * r.standard_normal(X.shape)
     y = np.concatenate([np.zeros(n0), np.ones(n - n0)]).astype(np.int64)
     return torch.from_numpy(X), torch.from_numpy(y)
+
+
+def _constructor_aliases(ns) -> None:
+    """``NewX`` for every public class ``X`` (the reference's constructor functions)."""
+    for name, obj in list(ns.items()):
+        if isinstance(obj, type) and name[0].isupper() and "New" + name not in ns:
+            ns["New" + name] = obj
+
+
+_constructor_aliases(globals())

@@ -51,3 +51,15 @@ class Transformer(Estimator):
     def FitTransform(self, X):
         self.Fit(X)
         return self.Transform(X)
+
+
+class LabelArray(np.ndarray):
+    """Cluster labels that read both ways: as the array itself (``m.Labels[i]``) and through
+    the reference's accessor call ``m.Labels()`` (ml/cluster_extras.go:89, 219)."""
+
+    def __call__(self) -> np.ndarray:
+        return np.asarray(self)
+
+
+def as_labels(lab) -> LabelArray:
+    return np.asarray(lab, dtype=np.int64).view(LabelArray)

@@ -9,7 +9,7 @@ import math
 import numpy as np
 import torch
 
-from .base import A, Clusterer, Estimator, T, Transformer
+from .base import A, Clusterer, Estimator, T, Transformer, as_labels
 
 
 class KMeans(Clusterer):
@@ -32,7 +32,7 @@ class KMeans(Clusterer):
             C = newC
             if shift < self.Tol:
                 break
-        self.Centers, self.Labels = C.numpy(), torch.cdist(X, C).argmin(1).numpy()
+        self.Centers, self.Labels = C.numpy(), as_labels(torch.cdist(X, C).argmin(1).numpy())
         self.Inertia = float((torch.cdist(X, C).min(1).values ** 2).sum())
         return self
 
@@ -68,7 +68,7 @@ class DBSCAN(Clusterer):
                 if len(nb[j]) >= self.MinSamples:
                     queue.extend(nb[j])
             c += 1
-        self.Labels = lab
+        self.Labels = as_labels(lab)
         return self
 
 
@@ -91,7 +91,7 @@ class AgglomerativeClustering(Clusterer):
         lab = np.zeros(len(D), dtype=np.int64)
         for k, (_, members) in enumerate(sorted(clusters.items())):
             lab[members] = k
-        self.Labels = lab
+        self.Labels = as_labels(lab)
         return self
 
 
@@ -118,7 +118,7 @@ class MeanShift(Clusterer):
             else:
                 centers.append(p)
                 lab[i] = len(centers) - 1
-        self.Centers, self.Labels = torch.stack(centers).numpy(), lab
+        self.Centers, self.Labels = torch.stack(centers).numpy(), as_labels(lab)
         return self
 
 
@@ -149,7 +149,7 @@ class GaussianMixture(Clusterer):
                 break
             prev = ll
         self.Means, self.Variances, self.Weights, self.Resp = mu, var, pi, R
-        self.Labels = R.argmax(1)
+        self.Labels = as_labels(R.argmax(1))
         return self
 
     def Predict(self, X):
@@ -364,39 +364,92 @@ def Accuracy(y_true, y_pred):
     return float((A(y_true) == A(y_pred)).mean())
 
 
-def ConfusionMatrix(y_true, y_pred):
+def ConfusionMatrix(y_true, y_pred, n_classes=None):
+    """``M[t, p]`` counts.  With ``n_classes`` the labels are indices ``0..n_classes-1`` and pairs
+    outside the range are dropped (ml/metrics.go:23-34); without it the sorted distinct labels of
+    both arrays index the matrix."""
     yt, yp = A(y_true, np.int64), A(y_pred, np.int64)
+    if n_classes is not None:
+        M = np.zeros((n_classes, n_classes), dtype=np.int64)
+        ok = (yt >= 0) & (yt < n_classes) & (yp >= 0) & (yp < n_classes)
+        np.add.at(M, (yt[ok], yp[ok]), 1)
+        return M
     cls = np.unique(np.concatenate([yt, yp]))
     M = np.zeros((len(cls), len(cls)), dtype=np.int64)
-    for a, b in zip(np.searchsorted(cls, yt), np.searchsorted(cls, yp)):
-        M[a, b] += 1
+    np.add.at(M, (np.searchsorted(cls, yt), np.searchsorted(cls, yp)), 1)
     return M
 
 
-def _prf(y_true, y_pred, positive=1):
-    yt, yp = A(y_true) == positive, A(y_pred) == positive
-    tp, fp, fn = (yt & yp).sum(), (~yt & yp).sum(), (yt & ~yp).sum()
-    p = tp / (tp + fp) if tp + fp else 0.0
-    r = tp / (tp + fn) if tp + fn else 0.0
-    return float(p), float(r), float(2 * p * r / (p + r)) if p + r else 0.0
+def _per_class(y_true, y_pred):
+    """Per-class tp / fp / fn / support over the sorted union of labels (ml/metrics.go:52-76)."""
+    M = ConfusionMatrix(y_true, y_pred)
+    tp = np.diag(M).astype(np.float64)
+    return tp, M.sum(0) - tp, M.sum(1) - tp, M.sum(1).astype(np.float64)
 
 
-def Precision(y_true, y_pred, positive=1): return _prf(y_true, y_pred, positive)[0]
-def Recall(y_true, y_pred, positive=1): return _prf(y_true, y_pred, positive)[1]
-def F1(y_true, y_pred, positive=1): return _prf(y_true, y_pred, positive)[2]
-def MSE(y_true, y_pred): return float(((A(y_true) - A(y_pred)) ** 2).mean())
-def MAE(y_true, y_pred): return float(np.abs(A(y_true) - A(y_pred)).mean())
+def _ratio(num, den):
+    return np.divide(num, den, out=np.zeros_like(num, dtype=np.float64), where=den > 0)
 
 
-def R2(y_true, y_pred):
+def _average(vals, support, average):
+    """``"macro"`` (the default: plain mean over classes) or ``"weighted"`` (by support), as in
+    ml/metrics.go:127-147; an integer label selects that class alone (binary use)."""
+    if len(vals) == 0:
+        return 0.0
+    if average == "weighted":
+        w = support.sum()
+        return float((vals * support).sum() / w) if w else 0.0
+    return float(vals.mean())
+
+
+def _prf(y_true, y_pred, average, positive):
+    tp, fp, fn, support = _per_class(y_true, y_pred)
+    prec, rec = _ratio(tp, tp + fp), _ratio(tp, tp + fn)
+    f1 = _ratio(2 * prec * rec, prec + rec)
+    if positive is not None or not isinstance(average, str):
+        cls = np.unique(np.concatenate([A(y_true, np.int64), A(y_pred, np.int64)]))
+        want = positive if positive is not None else average
+        i = np.searchsorted(cls, want)
+        if i >= len(cls) or cls[i] != want:
+            return 0.0, 0.0, 0.0
+        return float(prec[i]), float(rec[i]), float(f1[i])
+    return _average(prec, support, average), _average(rec, support, average), _average(f1, support, average)
+
+
+def Precision(y_true, y_pred, average="macro", positive=None): return _prf(y_true, y_pred, average, positive)[0]
+def Recall(y_true, y_pred, average="macro", positive=None): return _prf(y_true, y_pred, average, positive)[1]
+def F1(y_true, y_pred, average="macro", positive=None): return _prf(y_true, y_pred, average, positive)[2]
+
+
+def MeanSquaredError(y_true, y_pred):
+    yt = A(y_true)
+    return float(((yt - A(y_pred)) ** 2).mean()) if len(yt) else 0.0
+
+
+def MeanAbsoluteError(y_true, y_pred):
+    yt = A(y_true)
+    return float(np.abs(yt - A(y_pred)).mean()) if len(yt) else 0.0
+
+
+def R2Score(y_true, y_pred):
+    """Coefficient of determination; 0 for an empty or constant target (ml/metrics.go:175-195)."""
     yt, yp = A(y_true), A(y_pred)
+    if len(yt) == 0:
+        return 0.0
     ss = ((yt - yt.mean()) ** 2).sum()
     return float(1 - ((yt - yp) ** 2).sum() / ss) if ss else 0.0
 
 
-def Silhouette(X, labels):
-    D = torch.cdist(T(X), T(X)).numpy()
+MSE, MAE, R2 = MeanSquaredError, MeanAbsoluteError, R2Score
+
+
+def SilhouetteScore(X, labels):
+    """Mean silhouette coefficient with Euclidean distances; points alone in their cluster add
+    0, fewer than two clusters give 0 (ml/metrics.go:198-245)."""
     lab = A(labels, np.int64)
+    if len(lab) == 0 or len(np.unique(lab)) < 2:
+        return 0.0
+    D = torch.cdist(T(X), T(X)).numpy()
     s = []
     for i in range(len(D)):
         same = lab == lab[i]
@@ -405,8 +458,11 @@ def Silhouette(X, labels):
             continue
         a = D[i, same].sum() / (same.sum() - 1)
         b = min(D[i, lab == c].mean() for c in np.unique(lab) if c != lab[i])
-        s.append((b - a) / max(a, b))
+        s.append((b - a) / max(a, b) if max(a, b) > 0 else 0.0)
     return float(np.mean(s))
+
+
+Silhouette = SilhouetteScore
 
 
 def ROCAUC(y_true, scores):

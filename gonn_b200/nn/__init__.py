@@ -34,3 +34,20 @@ from .lazy import IsLazy  # noqa
 from .fuse import FuseConvBNEval, FuseLinearBNEval  # noqa
 from .parametrize import *  # noqa
 from . import prune  # noqa
+from .types import *  # noqa
+
+
+def _constructor_aliases(ns) -> None:
+    """``NewX`` for every public class ``X``: the reference builds modules with constructor
+    functions (``nn.NewLinear(3, 4)``), which read the same here."""
+    for name, obj in list(ns.items()):
+        if (isinstance(obj, type) or name.startswith("Lazy")) and name[0].isupper() and "New" + name not in ns:
+            ns["New" + name] = obj
+
+
+_constructor_aliases(globals())
+
+
+def NewLayerNormShape(shape, **kw):
+    """LayerNorm over several trailing dimensions (nn/norm.go:104-113)."""
+    return LayerNorm(tuple(shape), **kw)  # noqa: F405

@@ -118,18 +118,40 @@ class PReLU(Module):
 
 
 class RReLU(Module):
-    """Randomised leaky ReLU: slope ~ U(lower, upper) per element in training, the midpoint
-    in eval (the registry's op uses the midpoint)."""
+    """Randomised leaky ReLU.  Training: negative slopes ~ U(lower, upper), one per element
+    (PyTorch's rule, the default) or one per call with ``per_element=False`` (the reference's
+    rule, nn/activation.go:300-304); eval: the midpoint slope.  ``Seed`` makes the draws
+    reproducible (nn/activation.go:297)."""
 
-    def __init__(self, lower: float = 1.0 / 8, upper: float = 1.0 / 3):
+    def __init__(self, lower: float = 1.0 / 8, upper: float = 1.0 / 3, per_element: bool = True):
         super().__init__()
-        self.lower, self.upper = lower, upper
+        self.lower, self.upper, self.per_element = lower, upper, per_element
+        self._gen = None
+
+    def Seed(self, seed: int) -> "RReLU":
+        self._seed = int(seed)
+        self._gen = None
+        return self
+
+    def _generator(self, device):
+        if getattr(self, "_seed", None) is None:
+            return None
+        if self._gen is None or self._gen.device != device:
+            self._gen = torch.Generator(device=device).manual_seed(self._seed)
+        return self._gen
 
     def forward(self, x):
         if self.training:
-            slope = torch.empty_like(x).uniform_(self.lower, self.upper)
+            g = self._generator(x.device)
+            if not self.per_element:
+                u = torch.rand((), generator=self._generator(torch.device("cpu"))).item()
+                return _ew.unary("leakyrelu", x, self.lower + u * (self.upper - self.lower))
+            slope = torch.empty_like(x).uniform_(self.lower, self.upper, generator=g)
             return torch.where(x >= 0, x, x * slope)
         return _ew.unary("leakyrelu", x, (self.lower + self.upper) / 2)
+
+
+RReLULayer = RReLU
 
 
 class GLU(Module):

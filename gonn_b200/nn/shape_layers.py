@@ -30,20 +30,36 @@ def _pad_index(in_shape, pads, mode):
 
 
 class _PadNd(Module):
-    """Pads the trailing ``nd`` dims.  ``padding`` is given per dim from the LAST dim backwards as
-    (left, right, top, bottom, ...) for 2-D in the order the reference documents for its 2-D layers:
-    (top, bottom, left, right) — see the subclasses."""
+    """Pads the trailing ``nd`` dims.  The amounts are given either as one tuple or as separate
+    integers, in the order of the reference's constructors: the 2-D zero / constant /
+    reflection / replication layers take ``(top, bottom, left, right)`` (nn/padding.go:28-111);
+    the 1-D and 3-D layers and ``CircularPad2d`` take PyTorch's order, last dimension first:
+    ``(left, right[, top, bottom[, front, back]])`` (nn/padding_nd.go:155-375).  A single integer
+    pads every side alike.  The constant layers take the fill value last (or as ``value=``)."""
     nd, mode = 2, "zeros"
+    last_dim_first = False       # argument order: PyTorch's (True) or tensor order (False)
+    takes_value = False
 
-    def __init__(self, padding, value: float = 0.0):
+    def __init__(self, *padding, value: float = 0.0):
         super().__init__()
         nd = self.nd
-        if isinstance(padding, int):
-            padding = (padding,) * (2 * nd)
+        if len(padding) >= 1 and isinstance(padding[0], (tuple, list)):
+            if len(padding) == 2 and self.takes_value:
+                value = float(padding[1])
+            elif len(padding) != 1:
+                raise ValueError(f"{type(self).__name__}: unexpected arguments {padding[1:]}")
+            padding = tuple(padding[0])
+        elif self.takes_value and len(padding) in (2, 2 * nd + 1) and (
+                len(padding) != 2 * nd or isinstance(padding[-1], float)):
+            padding, value = tuple(padding[:-1]), float(padding[-1])
+        if len(padding) == 1:
+            padding = (int(padding[0]),) * (2 * nd)
         if len(padding) != 2 * nd:
             raise ValueError(f"{type(self).__name__}: expected {2 * nd} padding values")
+        padding = [int(v) for v in padding]
         # stored per dim in tensor order: [(before, after)] for each of the nd trailing dims
-        self.pads = [(padding[2 * d], padding[2 * d + 1]) for d in range(nd)]
+        order = range(nd - 1, -1, -1) if self.last_dim_first else range(nd)
+        self.pads = [(padding[2 * d], padding[2 * d + 1]) for d in order]
         self.value = value
 
     def forward(self, x):
@@ -58,57 +74,73 @@ class _PadNd(Module):
         return col.reshape(*lead, *out_shape)
 
 
+class ZeroPad1d(_PadNd):
+    """(left, right)."""
+    nd, mode, last_dim_first = 1, "zeros", True
+
+
 class ZeroPad2d(_PadNd):
-    """padding = (top, bottom, left, right)."""
+    """(top, bottom, left, right)."""
     nd, mode = 2, "zeros"
+
+
+class ZeroPad3d(_PadNd):
+    """(left, right, top, bottom, front, back)."""
+    nd, mode, last_dim_first = 3, "zeros", True
 
 
 class ConstantPad1d(_PadNd):
-    nd, mode = 1, "zeros"
+    """(left, right, value)."""
+    nd, mode, last_dim_first, takes_value = 1, "zeros", True, True
 
 
 class ConstantPad2d(_PadNd):
-    nd, mode = 2, "zeros"
+    """(top, bottom, left, right, value)."""
+    nd, mode, takes_value = 2, "zeros", True
 
 
 class ConstantPad3d(_PadNd):
-    nd, mode = 3, "zeros"
+    """(left, right, top, bottom, front, back, value)."""
+    nd, mode, last_dim_first, takes_value = 3, "zeros", True, True
 
 
 class ReflectionPad1d(_PadNd):
-    nd, mode = 1, "reflect"
+    nd, mode, last_dim_first = 1, "reflect", True
 
 
 class ReflectionPad2d(_PadNd):
+    """(top, bottom, left, right)."""
     nd, mode = 2, "reflect"
 
 
 class ReflectionPad3d(_PadNd):
-    nd, mode = 3, "reflect"
+    nd, mode, last_dim_first = 3, "reflect", True
 
 
 class ReplicationPad1d(_PadNd):
-    nd, mode = 1, "replicate"
+    nd, mode, last_dim_first = 1, "replicate", True
 
 
 class ReplicationPad2d(_PadNd):
+    """(top, bottom, left, right)."""
     nd, mode = 2, "replicate"
 
 
 class ReplicationPad3d(_PadNd):
-    nd, mode = 3, "replicate"
+    nd, mode, last_dim_first = 3, "replicate", True
 
 
 class CircularPad1d(_PadNd):
-    nd, mode = 1, "circular"
+    nd, mode, last_dim_first = 1, "circular", True
 
 
 class CircularPad2d(_PadNd):
-    nd, mode = 2, "circular"
+    """(left, right, top, bottom): PyTorch's order, unlike the other 2-D layers."""
+    nd, mode, last_dim_first = 2, "circular", True
 
 
 class CircularPad3d(_PadNd):
-    nd, mode = 3, "circular"
+    nd, mode, last_dim_first = 3, "circular", True
 
 
 def _cubic(t, a=-0.75):

@@ -20,3 +20,21 @@ def _groups_ctor(cls):
 for _c in (SGD, Adam, AdamW, Lion, LAMB, RMSprop, Adagrad, Adadelta, NAdam, Adamax, RAdam, Rprop, Adafactor, ASGD,
            SparseAdam):
     globals()["New" + _c.__name__ + "Groups"] = _groups_ctor(_c)
+
+
+class MetricScheduler:
+    """A scheduler stepped with a metric, ``Step(metric)`` (optim/scheduler.go:13-15):
+    ``ReduceLROnPlateau`` is the one implementation."""
+
+    def Step(self, metric: float) -> None:
+        raise NotImplementedError
+
+
+def _constructor_aliases(ns) -> None:
+    """``NewX`` for every public class ``X`` (the reference's constructor functions)."""
+    for name, obj in list(ns.items()):
+        if isinstance(obj, type) and name[0].isupper() and "New" + name not in ns:
+            ns["New" + name] = obj
+
+
+_constructor_aliases(globals())

@@ -56,6 +56,9 @@ class QTensor:
     ZeroPoint: int
     Shape: tuple
 
+    def Numel(self) -> int:
+        return self.Data.numel()
+
 
 def Quantize(t: torch.Tensor, scale: Optional[float] = None, zero_point: Optional[int] = None) -> QTensor:
     """Affine per-tensor quantisation; q-parameters from the tensor's min / max when not given."""
@@ -75,6 +78,13 @@ class QTensorPerChannel:
     Scales: torch.Tensor
     Axis: int
     Shape: tuple
+
+    def Numel(self) -> int:
+        return self.Data.numel()
+
+    def Channels(self) -> int:
+        """Number of quantisation channels: the size of ``Axis`` (quant/perchannel.go:28-29)."""
+        return self.Scales.numel()
 
 
 def QuantizePerChannel(t: torch.Tensor, axis: int = 0) -> QTensorPerChannel:
@@ -341,3 +351,34 @@ class QATLinear(Module):
         out.core.WRowSum = out.core.WQ.to(torch.int32).sum(1).to(torch.int32)
         out.core._dev.clear()
         return out
+
+
+# ---------------------------------------------------------------------------------------
+# constructor spellings of the reference (quant/linear.go:163-207, quant/qat.go:114-200)
+# ---------------------------------------------------------------------------------------
+LinearOption = dict        # what WithPerChannelWeights() returns: keyword arguments of the layers
+
+
+def _merge(opts) -> dict:
+    kw = {}
+    for o in opts:
+        kw.update(o)
+    return kw
+
+
+def NewDynamicLinearFrom(l: Linear, *opts: LinearOption) -> DynamicLinear:
+    return DynamicLinear(l, **_merge(opts))
+
+
+def NewStaticLinearFrom(l: Linear, obs: MinMaxObserver, *opts: LinearOption) -> StaticLinear:
+    """Input q-parameters taken from a calibrated observer."""
+    scale, zp = obs.ComputeQParams()
+    return StaticLinear(l, in_scale=scale, in_zero_point=zp, **_merge(opts))
+
+
+def NewFakeQuant(symmetric: bool) -> FakeQuant:
+    return FakeQuant(symmetric)
+
+
+def NewQATLinearFrom(l: Linear) -> QATLinear:
+    return QATLinear(l)

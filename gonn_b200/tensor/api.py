@@ -507,4 +507,57 @@ def GetDispatchPolicy() -> DispatchPolicy:
     return _policy
 
 
-__all__ += ["Tensor", "Float64", "Float32", "Float16", "BFloat16", "UnaryOpDef", "DispatchPolicy", "op_error"]
+# ---------------------------------------------------------------------------------------
+# names of the reference's types
+# ---------------------------------------------------------------------------------------
+DType = torch.dtype                         # tensor/dtype.go:17 (an enum there, real dtypes here)
+from ..backend import UnaryKind             # noqa: E402  (tensor/dispatch.go:29 re-exports it too)
+
+UnaryNone, UnaryReLU, UnarySigmoid, UnaryTanh = (UnaryKind.NoneKind, UnaryKind.ReLU, UnaryKind.Sigmoid,
+                                                 UnaryKind.Tanh)
+UnaryExp, UnaryLog, UnaryGELU, UnarySiLU, UnaryGELUExact = (UnaryKind.Exp, UnaryKind.Log, UnaryKind.GELU,
+                                                            UnaryKind.SiLU, UnaryKind.GELUExact)
+
+
+@_export
+def DTypeString(dt: torch.dtype) -> str:
+    """PyTorch-style name of a dtype: ``"float32"`` (tensor/dtype.go:28-37)."""
+    return str(dt).replace("torch.", "")
+
+
+@_export
+def String(t: Tensor) -> str:
+    """The reference's print format (tensor/tensor.go:152-170): shape, up to 16 values (the
+    first and last 8 beyond that), the dtype unless float64, and the gradient flag."""
+    flat = t.detach().reshape(-1)
+    vals = lambda v: "[" + " ".join(f"{x:g}" for x in v.to("cpu", torch.float64).tolist()) + "]"
+    body = vals(flat) if flat.numel() <= 16 else f"[{vals(flat[:8])} ... {vals(flat[-8:])}]"
+    out = f"Tensor(shape=[{' '.join(str(d) for d in t.shape)}], data={body}"
+    if t.dtype != torch.float64:
+        out += ", dtype=" + DTypeString(t.dtype)
+    if t.requires_grad:
+        out += ", requires_grad=true"
+    return out + ")"
+
+
+@dataclass
+class Function:
+    """A tape node described by value (tensor/autograd.go:36-41): ``Backward(grad, saved,
+    inputs)`` returns one gradient (or None) per input.  ``Apply(out_fn)`` evaluates
+    ``out_fn(*Inputs)`` off the tape and records the node, which is what ``MakeNode`` does
+    with a closure."""
+    Name: str
+    Inputs: Sequence[Tensor]
+    Saved: Sequence[object] = ()
+    Backward: Optional[Callable[[Tensor, Sequence[object], Sequence[Tensor]], Sequence[Optional[Tensor]]]] = None
+
+    def Apply(self, out_fn: Callable[..., Tensor]) -> Tensor:
+        if self.Backward is None:
+            raise op_error("Function.Apply", f"node {self.Name!r} has no Backward")
+        return MakeNode(out_fn, self.Name, self.Inputs,
+                        lambda g: self.Backward(g, self.Saved, self.Inputs))
+
+
+__all__ += ["Tensor", "Float64", "Float32", "Float16", "BFloat16", "UnaryOpDef", "DispatchPolicy", "op_error", "DType", "UnaryKind", "Function",
+            "UnaryNone", "UnaryReLU", "UnarySigmoid", "UnaryTanh", "UnaryExp", "UnaryLog", "UnaryGELU",
+            "UnarySiLU", "UnaryGELUExact"]

@@ -92,7 +92,16 @@ def test_preprocessing_metrics_selection():
     assert ml.PolynomialFeatures(Degree=2).FitTransform(X).shape == (3, 6)
     yt, yp = [1, 0, 1, 1, 0], [1, 0, 0, 1, 1]
     assert ml.ConfusionMatrix(yt, yp).tolist() == [[1, 1], [1, 2]]
-    assert abs(ml.Precision(yt, yp) - 2 / 3) < 1e-12 and abs(ml.Recall(yt, yp) - 2 / 3) < 1e-12
+    assert abs(ml.Precision(yt, yp, positive=1) - 2 / 3) < 1e-12 and abs(ml.Recall(yt, yp, positive=1) - 2 / 3) < 1e-12
+    # macro (default) and support-weighted averages over classes {0: p=r=1/2, 1: p=r=2/3}
+    for f in (ml.Precision, ml.Recall, ml.F1):
+        assert abs(f(yt, yp) - 7 / 12) < 1e-12 and abs(f(yt, yp, "weighted") - 0.6) < 1e-12
+    assert ml.ConfusionMatrix([0, 2, 5], [0, 1, 5], 3).tolist() == [[1, 0, 0], [0, 0, 0], [0, 1, 0]]
+    assert ml.MeanSquaredError([1.0, 3.0], [2.0, 5.0]) == 2.5 and ml.MeanAbsoluteError([1.0, 3.0], [2.0, 5.0]) == 1.5
+    assert ml.MeanSquaredError([], []) == 0.0 and ml.R2Score([2.0, 2.0], [1.0, 3.0]) == 0.0
+    assert abs(ml.R2Score([1.0, 2.0, 3.0], [1.0, 2.0, 4.0]) - 0.5) < 1e-12
+    assert ml.SilhouetteScore([[0.0], [1.0]], [0, 0]) == 0.0
+    assert abs(ml.SilhouetteScore([[0.0], [1.0], [10.0], [11.0]], [0, 0, 1, 1]) - (9.5 / 10.5 + 8.5 / 9.5) / 2) < 1e-12
     assert abs(ml.ROCAUC([0, 0, 1, 1], [0.1, 0.4, 0.35, 0.8]) - 0.75) < 1e-12
     folds = list(ml.KFold(NSplits=4).Split(10))
     assert len(folds) == 4 and sorted(np.concatenate([f for _, f in folds])) == list(range(10))

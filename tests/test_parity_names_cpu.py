@@ -1,0 +1,145 @@
+"""Names and call forms of the reference that have no PyTorch spelling: constructor functions,
+small record types, argument orders of the padding layers, transform objects."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from gonn_b200 import backend, data, ml, nn, optim, quant
+from gonn_b200 import tensor as T
+
+
+def test_padding_argument_orders_follow_the_reference():
+    x = torch.arange(2 * 2 * 3 * 4 * 5, dtype=torch.float64).reshape(2, 2, 3, 4, 5)
+    p3 = (1, 2, 0, 1, 2, 1)                                  # left, right, top, bottom, front, back
+    for cls, mode in ((nn.ZeroPad3d, "constant"), (nn.ReflectionPad3d, "reflect"),
+                      (nn.ReplicationPad3d, "replicate"), (nn.CircularPad3d, "circular")):
+        assert torch.equal(cls(*p3)(x), F.pad(x, p3, mode=mode)), cls.__name__
+        assert torch.equal(cls(p3)(x), F.pad(x, p3, mode=mode))
+    assert torch.equal(nn.ConstantPad3d(*p3, 7.5)(x), F.pad(x, p3, value=7.5))
+    x2 = x[0]
+    # the 2-D zero / constant / reflection / replication layers: top, bottom, left, right
+    assert torch.equal(nn.ZeroPad2d(1, 2, 3, 0)(x2), F.pad(x2, (3, 0, 1, 2)))
+    assert torch.equal(nn.ConstantPad2d(1, 2, 3, 0, -1.0)(x2), F.pad(x2, (3, 0, 1, 2), value=-1.0))
+    assert torch.equal(nn.ConstantPad2d((1, 2, 3, 0), -1.0)(x2), F.pad(x2, (3, 0, 1, 2), value=-1.0))
+    assert torch.equal(nn.ReplicationPad2d(1, 2, 3, 0)(x2), F.pad(x2, (3, 0, 1, 2), mode="replicate"))
+    assert torch.equal(nn.ReflectionPad2d(1)(x2), F.pad(x2, (1, 1, 1, 1), mode="reflect"))
+    # CircularPad2d alone takes PyTorch's order
+    assert torch.equal(nn.CircularPad2d(1, 2, 3, 0)(x2), F.pad(x2, (1, 2, 3, 0), mode="circular"))
+    x1 = x2[0]
+    assert torch.equal(nn.ZeroPad1d(2, 1)(x1), F.pad(x1, (2, 1)))
+    assert torch.equal(nn.ConstantPad1d(2, 1, 9.0)(x1), F.pad(x1, (2, 1), value=9.0))
+    assert torch.equal(nn.ConstantPad1d(2, 9.0)(x1), F.pad(x1, (2, 2), value=9.0))
+    with pytest.raises(ValueError):
+        nn.ZeroPad3d(1, 2, 3)
+
+
+def test_constructor_aliases_and_small_types():
+    lin = nn.NewLinear(3, 4)
+    assert isinstance(lin, nn.Linear) and nn.NewLSTM is nn.LSTM and nn.NewZeroPad1d is nn.ZeroPad1d
+    assert isinstance(nn.NewLazyLinear(5), torch.nn.Module)
+    ln = nn.NewLayerNormShape([3, 4])
+    assert tuple(ln.weight.shape) == (3, 4)
+    assert optim.NewAdam is optim.Adam and optim.NewStepLR is optim.StepLR
+    assert data.NewTensorDataset is data.TensorDataset and data.NewDataLoader is data.DataLoader
+    assert isinstance(lin, nn.Child) and nn.Base is nn.Module
+    assert isinstance(nn.ParametrizedLinear, type)
+    p = nn.Param("weight", lin.weight)
+    assert p.Name == "weight" and p.T is lin.weight
+    assert nn.ReduceSum == "sum" and nn.Reduction.ReduceNone == "none"
+    a, b = torch.randn(4, 3), torch.randn(4, 3)
+    assert torch.equal(nn.MSELoss(a, b, reduction=nn.ReduceSum), nn.MSELoss(a, b, reduction="sum"))
+    assert nn.MSELoss(a, b, reduction=nn.ReduceNone).shape == (4, 3)
+    assert issubclass(backend.NativeBackend, backend.Elementwiser)
+    assert backend.Elementwiser().Unary(backend.UnaryKind.ReLU, a) is None
+
+
+def test_lstm_state_record_and_seeded_rrelu():
+    cell = nn.LSTMCell(3, 5, dtype=torch.float64)
+    x = torch.randn(2, 3, dtype=torch.float64)
+    st = nn.LSTMState(torch.zeros(2, 5, dtype=torch.float64), torch.zeros(2, 5, dtype=torch.float64))
+    h1, c1 = cell(x, st)
+    h2, c2 = cell(x)
+    assert torch.equal(h1, h2) and torch.equal(c1, c2) and st.H is st[0]
+    x = torch.randn(64, dtype=torch.float64)
+    r = nn.RReLULayer(0.1, 0.3, per_element=False)
+    y1, y2 = r.Seed(7)(x), r.Seed(7)(x)
+    assert torch.equal(y1, y2)
+    neg = x < 0
+    slope = (y1[neg] / x[neg])
+    assert torch.allclose(slope, slope[0].expand_as(slope)) and 0.1 <= float(slope[0]) <= 0.3
+    e = nn.RReLU(0.1, 0.3).Seed(3)
+    z1 = e(x)
+    z2 = nn.RReLU(0.1, 0.3).Seed(3)(x)
+    assert torch.equal(z1, z2) and (z1[neg] / x[neg]).min() >= 0.1 - 1e-12
+    r.eval()
+    assert torch.allclose(r(x)[neg], x[neg] * 0.2)
+
+
+def test_tensor_type_names_and_printing():
+    assert T.DType is torch.dtype and T.UnaryKind is backend.UnaryKind and T.UnaryGELUExact == 7
+    assert T.String(torch.tensor([1.0, 2.5], dtype=torch.float64)) == "Tensor(shape=[2], data=[1 2.5])"
+    s = T.String(torch.arange(20, dtype=torch.float32).requires_grad_(True))
+    assert s == ("Tensor(shape=[20], data=[[0 1 2 3 4 5 6 7] ... [12 13 14 15 16 17 18 19]], dtype=float32, "
+                 "requires_grad=true)")
+    x = torch.tensor([1.0, 2.0], requires_grad=True)
+    f = T.Function("square", [x], [2.0], lambda g, saved, ins: [g * saved[0] * ins[0]])
+    f.Apply(lambda a: a * a).sum().backward()
+    assert torch.equal(x.grad, torch.tensor([2.0, 4.0]))
+    with pytest.raises(Exception):
+        T.Function("nograd", [x]).Apply(lambda a: a)
+
+
+def test_transforms_are_objects_with_apply():
+    img = torch.arange(2 * 4 * 6, dtype=torch.float64).reshape(2, 4, 6)
+    n = data.Normalize([1.0, 2.0], [2.0, 4.0])
+    assert isinstance(n, data.Transform) and torch.equal(n.Apply(img), n(img))
+    assert torch.equal(n(img)[1], (img[1] - 2.0) / 4.0)
+    with pytest.raises(ValueError):
+        data.Normalize([0.0], [1.0]).Apply(img)
+    with pytest.raises(ValueError):
+        data.Normalize([0.0, 0.0], [1.0, 0.0]).Apply(img)
+    assert torch.equal(data.RandomHorizontalFlip(1.0).Apply(img), img.flip(-1))
+    assert torch.equal(data.RandomHorizontalFlip(0.0).Apply(img), img)
+    c = data.RandomCrop([1, 2, 3], seed=0).Apply(img)
+    assert c.shape == (1, 2, 3)
+    assert data.RandomCrop(2, seed=1).Apply(img).shape == (2, 2, 2)
+    assert data.RandomCrop([6], seed=1).Apply(img).shape == (2, 4, 6)
+    with pytest.raises(ValueError):
+        data.RandomCrop([5, 7]).Apply(img)
+    assert data.ToFloat().Apply(img) is img
+    assert data.ToFloat(1 / 255).Apply(torch.tensor([255], dtype=torch.uint8)).item() == pytest.approx(1.0)
+    comp = data.Compose([data.RandomCrop([2, 2], seed=0), data.RandomHorizontalFlip(1.0)])
+    assert comp.Apply(img).shape == (2, 2, 2) and len(comp.Transforms) == 2
+    ds = data.TensorDataset(torch.randn(5, 2, 4, 6), torch.arange(5))
+    batch = next(iter(data.DataLoader(ds, batch_size=2, transform=comp)))
+    assert isinstance(batch, data.Batch) and batch.X.shape == (2, 2, 2, 2) and batch.Y.tolist() == [0, 1]
+    xb, yb = batch
+    assert xb is batch.X and yb is batch.Y
+
+
+def test_quant_records_and_constructor_forms():
+    w = torch.randn(6, 4, dtype=torch.float64)
+    q = quant.Quantize(w)
+    qc = quant.QuantizePerChannel(w, 0)
+    assert q.Numel() == 24 and qc.Numel() == 24 and qc.Channels() == 6
+    lin = nn.Linear(4, 6, dtype=torch.float64)
+    x = torch.randn(3, 4, dtype=torch.float64)
+    d = quant.NewDynamicLinearFrom(lin, quant.WithPerChannelWeights())
+    assert torch.equal(d(x), quant.DynamicLinear(lin, per_channel_weights=True)(x))
+    obs = quant.MinMaxObserver()
+    obs.Observe(x)
+    s = quant.NewStaticLinearFrom(lin, obs)
+    assert (s.InScale, s.InZeroPoint) == tuple(obs.ComputeQParams())
+    assert (s(x) - lin(x)).abs().max() < 0.1
+    assert quant.NewFakeQuant(True).Symmetric and isinstance(quant.NewQATLinearFrom(lin), quant.QATLinear)
+
+
+def test_cluster_labels_read_as_array_and_as_call():
+    X = np.concatenate([np.random.default_rng(0).normal(0, 0.1, (20, 2)),
+                        np.random.default_rng(1).normal(5, 0.1, (20, 2))])
+    for m in (ml.KMeans(K=2, Seed=0), ml.DBSCAN(Eps=0.5, MinSamples=3), ml.AgglomerativeClustering(NClusters=2)):
+        m.Fit(X)
+        lab = m.Labels()
+        assert type(lab) is np.ndarray and np.array_equal(lab, np.asarray(m.Labels)) and len(lab) == 40
+        assert len(set(lab[:20])) == 1 and lab[0] != lab[-1], type(m).__name__
