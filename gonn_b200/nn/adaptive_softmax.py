@@ -33,10 +33,11 @@ class AdaptiveLogSoftmaxWithLoss(Module):
 
     def LogProb(self, x):
         """Full (N, n_classes) log-probabilities."""
-        head_lp = torch.log_softmax(self.head(x).float(), 1)
+        ct = torch.float64 if x.dtype == torch.float64 else torch.float32     # 16-bit inputs widen to fp32
+        head_lp = torch.log_softmax(self.head(x).to(ct), 1)
         out = [head_lp[:, :self.shortlist]]
         for i in range(self.n_clusters):
-            tl = torch.log_softmax(self.tail[i](x).float(), 1)
+            tl = torch.log_softmax(self.tail[i](x).to(ct), 1)
             out.append(tl + head_lp[:, self.shortlist + i:self.shortlist + i + 1])
         return torch.cat(out, 1)
 

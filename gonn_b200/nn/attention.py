@@ -106,19 +106,20 @@ class MultiHeadAttention(Module):
         Q = self.qproj(q).reshape(B, Tq, H, D).permute(0, 2, 1, 3)
         K = self.kproj(k).reshape(B, Tk, H, D).permute(0, 2, 1, 3)
         V = self.vproj(v).reshape(B, Tk, H, D).permute(0, 2, 1, 3)
-        s = torch.matmul(Q.float(), K.float().transpose(-1, -2)) / math.sqrt(D)
+        ct = torch.float64 if q.dtype == torch.float64 else torch.float32     # 16-bit inputs widen to fp32
+        s = torch.matmul(Q.to(ct), K.to(ct).transpose(-1, -2)) / math.sqrt(D)
         neg = -1e30
         if causal:
             s = s + torch.triu(torch.ones(Tq, Tk, device=s.device), 1)[None, None] * neg
         if attn_mask is not None:
             m = attn_mask.to(s.device)
-            s = s + (m.float() * neg if m.dtype == torch.bool else m.float())[None, None]
+            s = s + (m.to(ct) * neg if m.dtype == torch.bool else m.to(ct))[None, None]
         if key_padding_mask is not None:
-            s = s + key_padding_mask.to(s.device).float()[:, None, None, :] * neg
+            s = s + key_padding_mask.to(s.device).to(ct)[:, None, None, :] * neg
         p = _softmax(s, -1)
         if attn_dropout > 0 and self.training:
             p = torch.nn.functional.dropout(p, attn_dropout)
-        o = torch.matmul(p, V.float()).to(q.dtype).permute(0, 2, 1, 3).reshape(B, Tq, H * D)
+        o = torch.matmul(p, V.to(ct)).to(q.dtype).permute(0, 2, 1, 3).reshape(B, Tq, H * D)
         return self.outproj(o)
 
     def _check(self, q, k, v):

@@ -25,7 +25,8 @@ class Embedding(Module):
         if self.max_norm is not None:
             with torch.no_grad():
                 rows = torch.unique(idx.reshape(-1).long())
-                w = self.weight.data[rows].float()
+                w = self.weight.data[rows]
+                w = w if w.dtype == torch.float64 else w.float()
                 n = w.norm(self.norm_type, dim=1, keepdim=True)
                 scale = torch.where(n > self.max_norm, self.max_norm / (n + 1e-7), torch.ones_like(n))
                 self.weight.data[rows] = (w * scale).to(self.weight.dtype)

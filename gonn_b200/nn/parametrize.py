@@ -13,6 +13,7 @@
 from __future__ import annotations
 
 import contextlib
+import copy
 from typing import Callable, List, Optional
 
 import torch
@@ -59,7 +60,9 @@ class WeightNormConv2d(_WeightNorm):
 
 
 def _bake(wrapper, w):
-    layer = wrapper._layer[0]
+    """A fresh plain layer holding ``w`` (and a copy of the bias); the wrapper and the layer it
+    wraps are left as they are (nn/parametrize.go:140-155, 391-401)."""
+    layer = copy.deepcopy(wrapper._layer[0])
     with torch.no_grad():
         layer.weight.copy_(w)
     return layer

@@ -146,6 +146,8 @@ class _Unary(torch.autograd.Function):
 
 def unary(name: str, x: torch.Tensor, p0: float = 0.0, p1: float = 0.0) -> torch.Tensor:
     """Differentiable unary op by name (kernel forward, kernel backward)."""
+    if not (x.requires_grad and torch.is_grad_enabled()):
+        return unary_forward(name, x, float(p0), float(p1))      # nothing to record: skip the tape node
     return _Unary.apply(x, name, float(p0), float(p1))
 
 
@@ -165,13 +167,16 @@ def binary_forward(name: str, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
         if a.is_cuda:
             raise TypeError(f"binary {name}: no CUDA kernel for dtype {a.dtype}")
         return {"add": torch.add, "sub": torch.sub, "mul": torch.mul, "div": torch.div}[name](a, b)
+    if a.shape == b.shape and a.is_contiguous() and b.is_contiguous():
+        # the common case, tested before any shape arithmetic (broadcast_shapes alone costs more
+        # host time than the rest of this function)
+        out = torch.empty(a.shape, dtype=a.dtype, device=a.device)
+        _l.call("gb_binary", _l.I(BINARY_IDS[name]), _l.I(_l.dtype_code(a.dtype)), _l.ptr(a), _l.ptr(b),
+                _l.ptr(out), _l.L(out.numel()), _l.I(0), None, None, None, _l.stream_ptr())
+        return out
     shape = torch.broadcast_shapes(a.shape, b.shape)
     out = torch.empty(shape, dtype=a.dtype, device=a.device)
     n = out.numel()
-    if tuple(a.shape) == tuple(shape) == tuple(b.shape) and a.is_contiguous() and b.is_contiguous():
-        _l.call("gb_binary", _l.I(BINARY_IDS[name]), _l.I(_l.dtype_code(a.dtype)), _l.ptr(a), _l.ptr(b),
-                _l.ptr(out), _l.L(n), _l.I(0), None, None, None, _l.stream_ptr())
-        return out
     if len(shape) > 6:
         a, b = a.expand(shape).contiguous(), b.expand(shape).contiguous()
         return binary_forward(name, a, b)
@@ -235,6 +240,8 @@ def binary(name: str, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """Differentiable broadcasting add / sub / mul / div."""
     if name not in BINARY_IDS:
         raise KeyError(f"unknown binary op {name!r}")
+    if not ((a.requires_grad or b.requires_grad) and torch.is_grad_enabled()):
+        return binary_forward(name, a, b)
     return _Binary.apply(a, b, name)
 
 

@@ -202,4 +202,6 @@ def matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
         a3 = a.expand(*bs, *a.shape[-2:]).reshape(-1, *a.shape[-2:])
         b3 = b.expand(*bs, *b.shape[-2:]).reshape(-1, *b.shape[-2:])
         return _MatMul.apply(a3, b3).reshape(*bs, a.shape[-2], b.shape[-1])
+    if not ((a.requires_grad or b.requires_grad) and torch.is_grad_enabled()):
+        return gemm(a, b)                     # nothing to record: skip the tape node
     return _MatMul.apply(a, b)
