@@ -1143,6 +1143,159 @@ __global__ void gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ 
   }
 }
 
+// Register-tiled SIMT GEMM for fp32 / fp64: 256 threads as a 16 x 16 grid, each thread owns
+// TM x TN outputs laid out in 16-byte groups (VEC elements) that interleave across the
+// threads, so that every shared-memory read is one conflict-free 128-bit load and a row of
+// 16 threads writes 256 contiguous bytes of C.  Tiles are staged k-major in two shared-memory
+// buffers; the next tile travels global -> registers while the current one is multiplied.
+template <typename T, int TM, int TN, int BK>
+__global__ void __launch_bounds__(256, 2)
+gemm_simt_tiled_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, int M,
+                       int N, int K, int transA, int transB, long long lda, long long ldb,
+                       long long ldc, long long sA, long long sB, long long sC, T alpha, int beta) {
+  constexpr int VEC = 16 / (int)sizeof(T);
+  constexpr int BM = 16 * TM, BN = 16 * TN, PAD = VEC;
+  constexpr int LA = BM * BK / 256, LB = BN * BK / 256;
+  static_assert(TM % VEC == 0 && TN % VEC == 0, "thread tile must be whole 16-byte groups");
+  static_assert((BM * BK) % 256 == 0 && (BN * BK) % 256 == 0, "tile must divide among 256 threads");
+  struct alignas(16) Vec { T v[VEC]; };
+  __shared__ __align__(16) T As[2][BK][BM + PAD];
+  __shared__ __align__(16) T Bs[2][BK][BN + PAD];
+
+  const int b = blockIdx.z;
+  A += (long long)b * sA;
+  B += (long long)b * sB;
+  C += (long long)b * sC;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+
+  T acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; i++)
+#pragma unroll
+    for (int j = 0; j < TN; j++) acc[i][j] = T(0);
+  T ra[LA], rb[LB];
+
+  auto load_global = [&](int k0) {
+#pragma unroll
+    for (int r = 0; r < LA; r++) {
+      const int i = tid + r * 256;
+      int kk, mm;
+      if (transA) { mm = i % BM; kk = i / BM; } else { kk = i % BK; mm = i / BK; }
+      const int gm = m0 + mm, gk = k0 + kk;
+      T v = T(0);
+      if (gm < M && gk < K) v = transA ? A[(long long)gk * lda + gm] : A[(long long)gm * lda + gk];
+      ra[r] = v;
+    }
+#pragma unroll
+    for (int r = 0; r < LB; r++) {
+      const int i = tid + r * 256;
+      int kk, nn;
+      if (transB) { kk = i % BK; nn = i / BK; } else { nn = i % BN; kk = i / BN; }
+      const int gn = n0 + nn, gk = k0 + kk;
+      T v = T(0);
+      if (gn < N && gk < K) v = transB ? B[(long long)gn * ldb + gk] : B[(long long)gk * ldb + gn];
+      rb[r] = v;
+    }
+  };
+  auto store_shared = [&](int buf) {
+#pragma unroll
+    for (int r = 0; r < LA; r++) {
+      const int i = tid + r * 256;
+      int kk, mm;
+      if (transA) { mm = i % BM; kk = i / BM; } else { kk = i % BK; mm = i / BK; }
+      As[buf][kk][mm] = ra[r];
+    }
+#pragma unroll
+    for (int r = 0; r < LB; r++) {
+      const int i = tid + r * 256;
+      int kk, nn;
+      if (transB) { kk = i % BK; nn = i / BK; } else { nn = i % BN; kk = i / BN; }
+      Bs[buf][kk][nn] = rb[r];
+    }
+  };
+
+  const int nk = (K + BK - 1) / BK;
+  if (nk > 0) {
+    load_global(0);
+    store_shared(0);
+  }
+  __syncthreads();
+  for (int t = 0; t < nk; t++) {
+    const int buf = t & 1;
+    if (t + 1 < nk) load_global((t + 1) * BK);
+#pragma unroll
+    for (int kk = 0; kk < BK; kk++) {
+      T a[TM], bb[TN];
+#pragma unroll
+      for (int g = 0; g < TM / VEC; g++) {
+        const Vec va = *reinterpret_cast<const Vec*>(&As[buf][kk][g * 16 * VEC + ty * VEC]);
+#pragma unroll
+        for (int v = 0; v < VEC; v++) a[g * VEC + v] = va.v[v];
+      }
+#pragma unroll
+      for (int h = 0; h < TN / VEC; h++) {
+        const Vec vb = *reinterpret_cast<const Vec*>(&Bs[buf][kk][h * 16 * VEC + tx * VEC]);
+#pragma unroll
+        for (int v = 0; v < VEC; v++) bb[h * VEC + v] = vb.v[v];
+      }
+#pragma unroll
+      for (int i = 0; i < TM; i++)
+#pragma unroll
+        for (int j = 0; j < TN; j++) acc[i][j] += a[i] * bb[j];
+    }
+    if (t + 1 < nk) store_shared(buf ^ 1);
+    __syncthreads();   // buf^1 is complete, and nobody still reads buf when it is refilled next
+  }
+
+  const bool vec_ok = (reinterpret_cast<unsigned long long>(C) % 16 == 0) && (ldc % VEC == 0);
+#pragma unroll
+  for (int g = 0; g < TM / VEC; g++) {
+#pragma unroll
+    for (int vi = 0; vi < VEC; vi++) {
+      const int gm = m0 + g * 16 * VEC + ty * VEC + vi;
+      if (gm >= M) continue;
+      const int i = g * VEC + vi;
+#pragma unroll
+      for (int h = 0; h < TN / VEC; h++) {
+        const int gn = n0 + h * 16 * VEC + tx * VEC;
+        if (gn >= N) continue;
+        T* p = C + (long long)gm * ldc + gn;
+        if (vec_ok && gn + VEC <= N) {
+          Vec o;
+          if (beta) o = *reinterpret_cast<const Vec*>(p);
+#pragma unroll
+          for (int v = 0; v < VEC; v++) {
+            const T r = alpha * acc[i][h * VEC + v];
+            o.v[v] = beta ? (o.v[v] + r) : r;
+          }
+          *reinterpret_cast<Vec*>(p) = o;
+        } else {
+#pragma unroll
+          for (int v = 0; v < VEC; v++) {
+            if (gn + v >= N) continue;
+            const T r = alpha * acc[i][h * VEC + v];
+            p[v] = beta ? (p[v] + r) : r;
+          }
+        }
+      }
+    }
+  }
+}
+
+int g_simt_tiled = 1;   // 0 selects the plain 64 x 64 kernel above
+
+template <typename T, int TM, int TN, int BK>
+void launch_simt_tiled(const void* A, const void* B, void* C, int M, int N, int K, int batch,
+                       int transA, int transB, long long lda, long long ldb, long long ldc,
+                       long long sA, long long sB, long long sC, double alpha, int beta,
+                       cudaStream_t stream) {
+  dim3 grid((N + 16 * TN - 1) / (16 * TN), (M + 16 * TM - 1) / (16 * TM), batch);
+  gemm_simt_tiled_kernel<T, TM, TN, BK><<<grid, 256, 0, stream>>>(
+      (const T*)A, (const T*)B, (T*)C, M, N, K, transA, transB, lda, ldb, ldc, sA, sB, sC, (T)alpha,
+      beta);
+}
+
 int g_epi_warps = 8;
 
 struct TMaps {
@@ -1449,6 +1602,11 @@ GB_EXPORT int gb_gemm_tune(int epi_warps, int group_m) {
   if (group_m >= 1) g_group_m = group_m;
   return 0;
 }
+// Selects the register-tiled fp32 / fp64 kernel (1, the default) or the plain 64 x 64 one (0).
+GB_EXPORT int gb_gemm_simt_tiled(int on) {
+  g_simt_tiled = on;
+  return 0;
+}
 // Enables (1) or disables (0) the automatic choice of the two-CTA kernel.
 GB_EXPORT int gb_gemm_use_2cta(int on) {
   g_use_2cta = on;
@@ -1533,6 +1691,26 @@ GB_EXPORT int gb_gemm_simt(const void* A, const void* B, void* C, int M, int N, 
   if (grid.y > 65535 || grid.z > 65535) {
     gbh::set_error("gb_gemm_simt: problem too large for this fallback");
     return gbh::E_TOO_LARGE;
+  }
+  if (dtype != DT_F32 && dtype != DT_F64) {
+    gbh::set_error("gb_gemm_simt: dtype must be fp32 or fp64");
+    return gbh::E_BAD_ARG;
+  }
+  if (g_simt_tiled) {
+    // the large tile needs enough tiles to occupy the SMs; otherwise 64 x 64 tiles
+    const long long big_n = dtype == DT_F32 ? 128 : 64;
+    const long long big_tiles = ((M + 127) / 128) * ((N + big_n - 1) / big_n) * (long long)batch;
+    const bool big = big_tiles >= 120;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == DT_F32) {
+      if (big) launch_simt_tiled<float, 8, 8, 16>(A, B, C, M, N, K, batch, transA, transB, lda, ldb, ldc, sA, sB, sC, alpha, beta, st);
+      else launch_simt_tiled<float, 4, 4, 16>(A, B, C, M, N, K, batch, transA, transB, lda, ldb, ldc, sA, sB, sC, alpha, beta, st);
+    } else {
+      if (big) launch_simt_tiled<double, 8, 4, 8>(A, B, C, M, N, K, batch, transA, transB, lda, ldb, ldc, sA, sB, sC, alpha, beta, st);
+      else launch_simt_tiled<double, 4, 4, 8>(A, B, C, M, N, K, batch, transA, transB, lda, ldb, ldc, sA, sB, sC, alpha, beta, st);
+    }
+    GB_CUDA_OK(cudaGetLastError());
+    return gbh::E_OK;
   }
   if (dtype == DT_F32) {
     gemm_simt_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(

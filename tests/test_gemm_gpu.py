@@ -127,6 +127,30 @@ def test_simt_exact(dtype, status_ok):
     assert (c3 - a @ b).abs().max().item() < tol
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_simt_tiled_large_ragged_batched(dtype, status_ok):
+    """Enough tiles for the 128-row configuration, ragged edges, every transposition, batch
+    strides, accumulation onto the output and a scaled product."""
+    tol = 1e-9 if dtype == torch.float64 else 2e-3
+    M, N, K = 1300, 1501, 70
+    a = torch.randn(M, K, device="cuda", dtype=dtype)
+    b = torch.randn(K, N, device="cuda", dtype=dtype)
+    ref = a.double() @ b.double()
+    for ta in (False, True):
+        for tb in (False, True):
+            aa = a.t().contiguous() if ta else a
+            bb = b.t().contiguous() if tb else b
+            c = gemm(aa, bb, trans_a=ta, trans_b=tb)
+            assert (c.double() - ref).abs().max().item() < tol, (ta, tb)
+    out = torch.ones(M, N, device="cuda", dtype=dtype)
+    gemm(a, b, out=out, beta=True, alpha=0.5)
+    assert (out.double() - (0.5 * ref + 1)).abs().max().item() < tol
+    a3 = torch.randn(5, 200, 96, device="cuda", dtype=dtype)
+    b3 = torch.randn(5, 96, 330, device="cuda", dtype=dtype)
+    assert (gemm(a3, b3).double() - torch.bmm(a3.double(), b3.double())).abs().max().item() < tol
+    assert (gemm(a3, b3[0]).double() - torch.matmul(a3.double(), b3[0].double())).abs().max().item() < tol
+
+
 def test_large_matches_reference(status_ok):
     a, b = _mk(2048, 2048, 2048, False, True)
     c = gemm(a, b, trans_b=True)
