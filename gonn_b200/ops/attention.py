@@ -56,12 +56,18 @@ def _tma_ready(t):
     return t
 
 
-def flash_fwd(q, k, v, causal: bool, scale: float):
-    """Returns (out, lse); out is contiguous (B,Sq,H,D), lse is (B,H,Sq) fp32."""
+def flash_fwd(q, k, v, causal: bool, scale: float, out=None):
+    """Returns (out, lse); out is contiguous (B,Sq,H,D) unless a (B,Sq,H,D) view with unit inner
+    stride and 16-byte aligned outer strides is passed in; lse is (B,H,Sq) fp32."""
     q, k, v = _tma_ready(q), _tma_ready(k), _tma_ready(v)
     B, Sq, H, D = q.shape
     Sk = k.shape[1]
-    out = torch.empty((B, Sq, H, D), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((B, Sq, H, D), dtype=q.dtype, device=q.device)
+    elif (tuple(out.shape) != (B, Sq, H, D) or out.dtype != q.dtype or out.stride(-1) != 1
+          or out.data_ptr() % 16 or any(s % 8 for s in out.stride()[:-1])):
+        raise ValueError("flash_fwd: out must be a (B,Sq,H,D) view of the input dtype with unit inner "
+                         "stride and outer strides that are multiples of 8 elements")
     lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
     I, L = _l.I, _l.L
     _l.call("gb_flash_fwd", I(_l.dtype_code(q.dtype)), _l.ptr(q), _l.ptr(k), _l.ptr(v), _l.ptr(out),

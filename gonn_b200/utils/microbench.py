@@ -4,6 +4,7 @@
     python -m gonn_b200.utils.microbench elementwise
     python -m gonn_b200.utils.microbench flash
     python -m gonn_b200.utils.microbench norm
+    python -m gonn_b200.utils.microbench refattn                  # the reference's attention benchmark shapes
     python -m gonn_b200.utils.microbench mlp                      # CPU, config of the reference's quick start
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
         -m gonn_b200.utils.microbench allreduce                   # bus-bandwidth sweep, NVLink kernels vs NCCL
@@ -121,6 +122,33 @@ def bench_flash():
               torch_bwd_ms=rb, flop_convention="4*B*H*S*S*D, halved when causal; backward 2.5x")
 
 
+def bench_reference_attention():
+    """The reference's attention benchmark (benchmark/flashattn/main.go:127-149): forward attention
+    on resident (BH, S, d) inputs for (16, 2048, 64), (32, 1024, 64), (64, 512, 64), causal and
+    not, FLOPs = 4 BH S^2 d (halved when causal), through the flat entry points of
+    ``gonn_b200.cuda``; each line also checks forward and backward against float64 math."""
+    from .. import cuda as C
+    F = torch.nn.functional
+    for BH, S, d in ((16, 2048, 64), (32, 1024, 64), (64, 512, 64)):
+        for causal in (False, True):
+            g = torch.Generator(device="cuda").manual_seed(BH + S)
+            q, k, v, do = (torch.randn(BH, S, d, device="cuda", dtype=torch.bfloat16, generator=g) for _ in range(4))
+            o, lse = C.FlashAttnFwd(q, k, v, BH, S, d, None, causal)
+            dq, dk, dv = C.FlashAttnBwd(q, k, v, o, lse, do, BH, S, d, None, causal)
+            qd, kd, vd = (t.double().requires_grad_(True) for t in (q, k, v))
+            ref = F.scaled_dot_product_attention(qd, kd, vd, is_causal=causal)
+            rq, rk, rv = torch.autograd.grad(ref, (qd, kd, vd), do.double())
+            err = lambda a, b: float((a.double() - b).abs().max() / b.abs().max())
+            ms = C.BenchFlashAttn(BH, S, d, 20, causal)
+            tms = timeit(lambda: F.scaled_dot_product_attention(q[None], k[None], v[None], is_causal=causal),
+                         iters=20, flush=False)
+            fl = 4.0 * BH * S * S * d * (0.5 if causal else 1.0)
+            _emit(bench="reference_attention", dtype="bf16", BH=BH, S=S, d=d, causal=causal, ms=ms,
+                  gflops=fl / 1e9 / (ms / 1e3), torch_sdpa_ms=tms, torch_sdpa_gflops=fl / 1e9 / (tms / 1e3),
+                  rel_err_out=err(o, ref.detach()), rel_err_dq=err(dq, rq), rel_err_dk=err(dk, rk),
+                  rel_err_dv=err(dv, rv), reference_published_gflops_fp64=86.6 if causal else 95.4)
+
+
 def bench_norm():
     from ..ops.norm import layer_norm
     for rows, D in ((16384, 768), (65536, 768), (16384, 2048), (65536, 2048)):
@@ -218,7 +246,7 @@ def bench_allreduce():
 def main(argv):
     kind = argv[0] if argv else "gemm"
     fn = {"gemm": bench_gemm, "elementwise": bench_elementwise, "flash": bench_flash, "norm": bench_norm,
-          "mlp": bench_mlp_cpu, "allreduce": bench_allreduce}.get(kind)
+          "mlp": bench_mlp_cpu, "allreduce": bench_allreduce, "refattn": bench_reference_attention}.get(kind)
     if fn is None:
         raise SystemExit(f"unknown benchmark {kind!r}")
     fn()
