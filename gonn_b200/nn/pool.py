@@ -32,7 +32,33 @@ class _PoolNd(Module):
         idx, outs = sliding_index(tuple(x.shape[2:]), self.kernel_size, self.stride, self.padding, self.dilation,
                                   self.ceil_mode)
         y, arg = _pool(x.reshape(N * C, -1), idx, self.mode, self.count_include_pad, self.norm_type)
+        if self.mode == "avg" and self.ceil_mode and self.count_include_pad:
+            fac = self._overhang_factor(tuple(x.shape[2:]), outs, x.device, y.dtype)
+            if fac is not None:
+                y = y * fac
         return y.reshape(N, C, *outs), arg, idx, outs
+
+    def _overhang_factor(self, in_shape, outs, device, dtype):
+        """Average pooling counts padding cells in its divisor but not the cells a ceil-mode
+        window hangs over the padded end (nn/pool.go:264-300): the divisor is the window
+        clipped to ``in + 2 * pad``.  The kernel divides by the full window, so windows that
+        hang over are rescaled by ``window / clipped``; None when no window does."""
+        key = (in_shape, str(device), dtype)
+        cache = self.__dict__.setdefault("_fac_cache", {})
+        if key not in cache:
+            counts = []
+            for d in range(self.nd):
+                k, st, pad, dil = self.kernel_size[d], self.stride[d], self.padding[d], self.dilation[d]
+                lim = in_shape[d] + pad
+                counts.append(np.array([sum(1 for j in range(k) if o * st - pad + j * dil < lim)
+                                        for o in range(outs[d])], dtype=np.float64))
+            div = counts[0]
+            for c in counts[1:]:
+                div = np.multiply.outer(div, c)
+            full = float(np.prod(self.kernel_size))
+            fac = full / np.maximum(div.reshape(1, -1), 1.0)
+            cache[key] = None if np.all(fac == 1.0) else torch.as_tensor(fac, dtype=dtype, device=device)
+        return cache[key]
 
     def forward(self, x):
         return self._run(x)[0]
