@@ -124,3 +124,47 @@ def test_lbfgs_minimises_rosenbrock_like():
     for _ in range(5):
         loss = o.step(closure)
     assert loss < 1e-6
+
+
+_TORCH_TWINS = [
+    ("SGD", dict(lr=0.1, momentum=0.9, weight_decay=0.01), dict(lr=0.1, momentum=0.9, weight_decay=0.01)),
+    ("SGD", dict(lr=0.1, momentum=0.9, nesterov=True), dict(lr=0.1, momentum=0.9, nesterov=True)),
+    ("Adam", dict(lr=0.01, weight_decay=0.1), dict(lr=0.01, weight_decay=0.1)),
+    ("AdamW", dict(lr=0.01, weight_decay=0.1), dict(lr=0.01, weight_decay=0.1)),
+    ("RMSprop", dict(lr=0.01, momentum=0.5), dict(lr=0.01, momentum=0.5)),
+    ("Adagrad", dict(lr=0.1, lr_decay=0.01), dict(lr=0.1, lr_decay=0.01)),
+    ("Adadelta", dict(lr=1.0), dict(lr=1.0)),
+    ("NAdam", dict(lr=0.01), dict(lr=0.01)),
+    ("Adamax", dict(lr=0.01), dict(lr=0.01)),
+    ("RAdam", dict(lr=0.01), dict(lr=0.01)),
+    ("Rprop", dict(lr=0.01), dict(lr=0.01)),
+    ("ASGD", dict(lr=0.05, t0=3.0), dict(lr=0.05, t0=3.0)),
+]
+
+
+@pytest.mark.parametrize("name,ours_kw,torch_kw", _TORCH_TWINS, ids=[f"{n}{i}" for i, (n, _, _) in enumerate(_TORCH_TWINS)])
+def test_trajectory_matches_torch_optimizer(name, ours_kw, torch_kw):
+    """Ten steps on a fixed non-quadratic objective: parameters equal torch.optim's.  Three
+    documented deviations, all following the reference: RAdam rectifies once rho_t > 4 (the
+    paper's and the reference's threshold, optim/radam.go:73; torch waits for rho_t > 5), so only
+    the first four steps are compared; torch keeps ASGD's eta / mu in float32 tensors (1e-8
+    relative); NAdam differs at the 1e-10 level through where eps enters."""
+    steps = 4 if name == "RAdam" else 10
+    tol = {"ASGD": 1e-6, "NAdam": 1e-8}.get(name, 1e-10)
+    g = torch.Generator().manual_seed(0)
+    init = [torch.randn(3, 4, dtype=torch.float64, generator=g), torch.randn(4, dtype=torch.float64, generator=g)]
+    x = torch.randn(8, 3, dtype=torch.float64, generator=g)
+
+    def run(make):
+        ps = [torch.nn.Parameter(t.clone()) for t in init]
+        o = make(ps)
+        for _ in range(steps):
+            o.zero_grad()
+            (torch.tanh(x @ ps[0] + ps[1]) ** 2).sum().backward()
+            o.step()
+        return [p.detach() for p in ps]
+
+    a = run(lambda ps: getattr(optim, name)(ps, **ours_kw))
+    b = run(lambda ps: getattr(torch.optim, name)(ps, **torch_kw))
+    for u, v in zip(a, b):
+        assert torch.allclose(u, v, rtol=tol, atol=tol * 1e-2), name
