@@ -168,3 +168,36 @@ def test_trajectory_matches_torch_optimizer(name, ours_kw, torch_kw):
     b = run(lambda ps: getattr(torch.optim, name)(ps, **torch_kw))
     for u, v in zip(a, b):
         assert torch.allclose(u, v, rtol=tol, atol=tol * 1e-2), name
+
+
+def _lr_trace(make_opt, make_sched, n, step_arg=None):
+    w = torch.nn.Parameter(torch.zeros(1, dtype=torch.float64))
+    o = make_opt([w])
+    s = make_sched(o)
+    out = []
+    for i in range(n):
+        out.append(o.Groups()[0].lr if hasattr(o, "Groups") else o.param_groups[0]["lr"])
+        w.grad = torch.ones_like(w)
+        o.step()
+        (s.step() if hasattr(s, "step") else s.Step()) if step_arg is None else (
+            s.step(step_arg[i]) if hasattr(s, "step") else s.Step(step_arg[i]))
+    return out
+
+
+_SCHEDS = [
+    ("StepLR", lambda o: optim.StepLR(o, 3, 0.5), lambda o: torch.optim.lr_scheduler.StepLR(o, 3, 0.5)),
+    ("MultiStepLR", lambda o: optim.MultiStepLR(o, [2, 5, 9], 0.3),
+     lambda o: torch.optim.lr_scheduler.MultiStepLR(o, [2, 5, 9], 0.3)),
+    ("ExponentialLR", lambda o: optim.ExponentialLR(o, 0.9), lambda o: torch.optim.lr_scheduler.ExponentialLR(o, 0.9)),
+    ("CosineAnnealingLR", lambda o: optim.CosineAnnealingLR(o, 10, 0.01),
+     lambda o: torch.optim.lr_scheduler.CosineAnnealingLR(o, 10, 0.01)),
+    ("LinearLR", lambda o: optim.LinearLR(o, 0.25, 1.0, 6), lambda o: torch.optim.lr_scheduler.LinearLR(o, 0.25, 1.0, 6)),
+    ("PolynomialLR", lambda o: optim.PolynomialLR(o, 8, 2.0), lambda o: torch.optim.lr_scheduler.PolynomialLR(o, 8, 2.0)),
+]
+
+
+@pytest.mark.parametrize("name,ours,ref", _SCHEDS, ids=[n for n, _, _ in _SCHEDS])
+def test_scheduler_lr_trace_matches_torch(name, ours, ref):
+    a = _lr_trace(lambda ps: optim.SGD(ps, lr=0.1), ours, 14)
+    b = _lr_trace(lambda ps: torch.optim.SGD(ps, lr=0.1), ref, 14)
+    assert len(a) == len(b) and all(abs(x - y) < 1e-12 for x, y in zip(a, b)), (name, a, b)
