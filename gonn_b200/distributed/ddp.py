@@ -101,7 +101,12 @@ class DistributedDataParallel(torch.nn.Module):
         self._esz = 4 if dt == torch.float32 else 2
         self.host = dev.type != "cuda"
         if self.host and world != 1:
-            raise TypeError("DistributedDataParallel: multi-rank runs need CUDA devices")
+            # CPU ranks: the same engine (buckets, hooks, sharded state) with the collectives
+            # carried by torch.distributed's CPU backend instead of the peer-memory kernels
+            import torch.distributed as dist
+            if not (dist.is_available() and dist.is_initialized()):
+                raise TypeError("DistributedDataParallel: multi-rank runs on the host need an "
+                                "initialised torch.distributed process group (gloo)")
         if any(p.dtype != dt or p.device != dev for p in params):
             raise TypeError("DistributedDataParallel: all parameters must share dtype and device")
         self.dtype, self.device = dt, dev
@@ -151,7 +156,8 @@ class DistributedDataParallel(torch.nn.Module):
         if world > 1:
             # every rank starts from rank 0's values (BroadcastParams of the reference)
             self.symm.broadcast(0, self._param_off, self.total * self._esz)
-            torch.cuda.synchronize()
+            if not self.host:
+                torch.cuda.synchronize()
 
         self._fresh = {id(p): True for p in params}
         self._autograd_params: Dict[int, torch.nn.Parameter] = {}

@@ -60,10 +60,18 @@ class SymmetricMemory:
         self.data_bytes = (int(data_bytes) + 255) // 256 * 256
         self._raw: List[torch.Tensor] = []
         self.host = device.type != "cuda"
+        self._pg = process_group
         if self.host:
-            # oracle path: one rank, host memory, the collectives evaluated with tensor math
-            if world != 1 or emulate:
-                raise ValueError("SymmetricMemory on the host supports a single rank")
+            # oracle path: host memory, the collectives evaluated with tensor math; several
+            # ranks exchange through torch.distributed (a CPU backend such as gloo), which
+            # exercises the bucket bookkeeping and the sharded update without GPUs
+            if emulate:
+                raise ValueError("SymmetricMemory on the host does not emulate ranks")
+            if world != 1:
+                import torch.distributed as dist
+                if not (dist.is_available() and dist.is_initialized()):
+                    raise ValueError("SymmetricMemory on the host with several ranks needs an "
+                                     "initialised torch.distributed process group (gloo)")
             self.flag_bytes = 0
             self._raw.append(torch.zeros(self.data_bytes, dtype=torch.uint8))
             return
@@ -138,22 +146,43 @@ class SymmetricMemory:
                         [0, 0, 0, 0, 0, 1, 1, scale], ctas)
 
     def _fused_step_host(self, mode, dtype, grad_off, param_off, n, master, m, v, hyper):
-        """Single-rank restatement of the kernel's arithmetic (fp32, same operation order)."""
+        """Restatement of the kernel's arithmetic on the host (fp32, same operation order):
+        mean of the gradients over ranks, then either the mean written back (mode 0) or AdamW
+        on the slice this rank owns followed by an all-gather of the updated parameters."""
         lr, wd, b1, b2, eps, bc1, bc2, gscale = [float(h) for h in hyper]
-        g = self.view(grad_off, n, dtype).float() * gscale
+        W = self.world
+        g = self.view(grad_off, n, dtype).float()
+        if W > 1:
+            import torch.distributed as dist
+            dist.all_reduce(g, group=self._pg)
+            g /= W
+        g = g * gscale
         if mode == 0:
             self.view(grad_off, n, dtype).copy_(g.to(dtype))
             return
+        L = n // W
+        g = g[self.rank * L:(self.rank + 1) * L]
         p = master
         p.mul_(1 - lr * wd)
         m.mul_(b1).add_(g, alpha=1 - b1)
         v.mul_(b2).addcmul_(g, g, value=1 - b2)
         p.sub_(lr * (m / bc1) / ((v / bc2).sqrt() + eps))
-        self.view(param_off, n, dtype).copy_(p.to(dtype))
+        out = self.view(param_off, n, dtype)
+        if W == 1:
+            out.copy_(p.to(dtype))
+            return
+        import torch.distributed as dist
+        mine = p.to(dtype).contiguous().view(torch.uint8)
+        parts = [torch.empty_like(mine) for _ in range(W)]
+        dist.all_gather(parts, mine, group=self._pg)
+        out.view(torch.uint8).copy_(torch.cat(parts))
 
     def allreduce_small(self, vec, slot_off: int):
         """In-place sum over ranks of a short fp32 vector (list of vectors when emulating)."""
         if self.host:
+            if self.world > 1:
+                import torch.distributed as dist
+                dist.all_reduce(vec, group=self._pg)
             return
         xs = vec if isinstance(vec, (list, tuple)) else [vec]
         n = xs[0].numel()
@@ -165,12 +194,18 @@ class SymmetricMemory:
 
     def broadcast(self, root: int, offset_bytes: int, nbytes: int, ctas: int = 16):
         if self.host:
+            if self.world > 1:
+                import torch.distributed as dist
+                dist.broadcast(self._raw[0][offset_bytes:offset_bytes + nbytes], src=root, group=self._pg)
             return
         _l.call("gb_comm_broadcast", _l.I(root), _l.L(self.abs_offset(offset_bytes)), _l.L(nbytes),
                 _l.I(ctas), _l.I(1 if self.emulate else 0), _l.stream_ptr())
 
     def barrier(self):
         if self.host:
+            if self.world > 1:
+                import torch.distributed as dist
+                dist.barrier(group=self._pg)
             return
         _l.call("gb_comm_barrier", _l.I(1 if self.emulate else 0), _l.stream_ptr())
 
