@@ -104,6 +104,10 @@ def device_maps(idx: np.ndarray, S: int, device, need_inverse: bool):
     dk = (key, str(device))
     ent = _DEV.get(dk)
     if ent is None:
+        # the kernels trust the map: check its range once, on the host, before it is uploaded
+        if idx.size and (int(idx.max()) >= S or int(idx.min()) < -1):
+            raise ValueError(f"window index map out of range: values in [{int(idx.min())}, {int(idx.max())}] "
+                             f"for a plane of {S} elements (-1 marks padding)")
         ent = {"idx": torch.from_numpy(idx.copy()).to(device)}
         _DEV[dk] = ent
     if need_inverse and "offs" not in ent:

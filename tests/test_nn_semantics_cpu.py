@@ -150,3 +150,14 @@ def test_concurrent_backward_into_shared_leaves_is_exact():
         [t.join() for t in ts]
         assert not errs
         assert torch.equal(lin.weight.grad, want_w) and torch.equal(lin.bias.grad, torch.full((4,), 40.0, dtype=D))
+
+
+def test_index_maps_are_range_checked_before_upload():
+    import numpy as np
+    from gonn_b200.ops.window import device_maps
+    good = np.array([[0, 1, -1], [2, 3, 3]], dtype=np.int32)
+    assert device_maps(good, 4, "cpu", True)["idx"].shape == (2, 3)
+    with pytest.raises(ValueError):
+        device_maps(np.array([[0, 4]], dtype=np.int32), 4, "cpu", False)
+    with pytest.raises(ValueError):
+        device_maps(np.array([[-2, 1]], dtype=np.int32), 4, "cpu", False)
