@@ -14,3 +14,7 @@ the native kernels for CUDA tensors:
 """
 from .api import *  # noqa: F401,F403
 from .api import __all__  # noqa: F401
+
+from . import api as _api, methods as _methods
+
+_methods.install(_api)          # x.Add(y).ReLU().Sum(): the reference's method spellings

@@ -143,3 +143,22 @@ def test_cluster_labels_read_as_array_and_as_call():
         lab = m.Labels()
         assert type(lab) is np.ndarray and np.array_equal(lab, np.asarray(m.Labels)) and len(lab) == 40
         assert len(set(lab[:20])) == 1 and lab[0] != lab[-1], type(m).__name__
+
+
+def test_method_spellings_on_tensors():
+    from gonn_b200.tensor import methods
+    assert len(methods.installed()) >= 90 and "T" not in methods.installed()
+    x = T.SetRequiresGrad(T.New([1, -2, 3], 3))
+    y = x.Add(T.Ones(3, dtype=torch.float64)).ReLU().Square().Sum()
+    y.Backward()
+    assert y.Item() == 20.0 and x.grad.tolist() == [4.0, 0.0, 8.0]
+    assert x.Dim() == 1 and x.DType() == torch.float64 and x.Numel() == 3
+    m = T.New([1, 2, 3, 4, 5, 6], 2, 3)
+    assert m.Transpose().shape == (3, 2) and torch.equal(m.Transpose(), m.T)
+    assert m.MatMul(m.Transpose()).tolist() == [[14.0, 32.0], [32.0, 77.0]]
+    assert m.SumAxis(1, False).tolist() == [6.0, 15.0] and m.Reshape(3, 2).shape == (3, 2)
+    assert m.Unary("square").Sum().Item() == 91.0 and m.String().startswith("Tensor(shape=[2 3]")
+    assert torch.equal(m.Softmax(1).Sum().reshape(()), torch.tensor(2.0, dtype=torch.float64)) or \
+        abs(m.Softmax(1).Sum().Item() - 2.0) < 1e-12
+    # torch's own attributes are untouched
+    assert torch.equal(m.T, m.t()) and m.sum().item() == 21.0
