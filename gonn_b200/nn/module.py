@@ -31,6 +31,11 @@ class Module(_tnn.Module):
     def Buffers(self) -> List[Tuple[str, torch.Tensor]]:
         return list(self.named_buffers())
 
+    def Forward(self, *args, **kwargs):
+        """The reference's spelling of the forward pass (nn/module.go:29-33).  As there, it runs
+        the layer directly; hooks run when the module is called (``m(x)`` or ``nn.Call(m, x)``)."""
+        return self.forward(*args, **kwargs)
+
     def SetTraining(self, flag: bool) -> "Module":
         return self.train(flag)
 

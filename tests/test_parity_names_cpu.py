@@ -162,3 +162,17 @@ def test_method_spellings_on_tensors():
         abs(m.Softmax(1).Sum().Item() - 2.0) < 1e-12
     # torch's own attributes are untouched
     assert torch.equal(m.T, m.t()) and m.sum().item() == 21.0
+
+
+def test_forward_spelling_bypasses_hooks_like_the_reference():
+    lin = nn.Linear(3, 2)
+    x = torch.randn(4, 3)
+    seen = []
+    h = nn.RegisterForwardHook(lin, lambda m, inp, out: seen.append(1))
+    assert torch.equal(lin.Forward(x), lin.forward(x)) and seen == []
+    lin(x)
+    assert seen == [1]
+    assert nn.RemoveHook(h)
+    mha = nn.MultiHeadAttention(8, 2)
+    q = torch.randn(2, 5, 8)
+    assert torch.equal(mha.Forward(q, q, q, True), mha(q, q, q, True))
