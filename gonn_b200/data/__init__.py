@@ -90,6 +90,8 @@ class DataLoader:
         n = self.dataset.Len()
         return n // self.BatchSize if self.DropLast else -(-n // self.BatchSize)
 
+    Len = __len__           # number of batches per epoch (data/dataloader.go)
+
     def _batches(self):
         n = self.dataset.Len()
         order = np.arange(n)

@@ -222,14 +222,23 @@ class QDA(Classifier):
             self.Priors.append(len(Xc) / len(X))
         return self
 
-    def Predict(self, X):
+    def _discriminant(self, X):
         X = A(X)
         s = []
         for m, C, p in zip(self.Means, self.Covs, self.Priors):
             Ci = np.linalg.inv(C)
             dlt = X - m
             s.append(-0.5 * np.einsum("ij,jk,ik->i", dlt, Ci, dlt) - 0.5 * np.linalg.slogdet(C)[1] + np.log(p))
-        return self.Classes[np.stack(s, 1).argmax(1)]
+        return np.stack(s, 1)
+
+    def Predict(self, X):
+        return self.Classes[self._discriminant(X).argmax(1)]
+
+    def PredictProba(self, X):
+        """Softmax of the quadratic discriminants (ml/lda.go:365-371)."""
+        s = self._discriminant(X)
+        e = np.exp(s - s.max(1, keepdims=True))
+        return e / e.sum(1, keepdims=True)
 
 
 class GaussianNB(Classifier):

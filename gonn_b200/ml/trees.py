@@ -203,12 +203,21 @@ class AdaBoostClassifier(Classifier):
             w /= w.sum()
         return self
 
-    def Predict(self, X):
+    def _votes(self, X):
         X = A(X)
         votes = np.zeros((len(X), len(self.Classes)))
         for t, a in zip(self.stumps, self.alphas):
             votes[np.arange(len(X)), np.searchsorted(self.Classes, t.Predict(X))] += a
-        return self.Classes[votes.argmax(1)]
+        return votes
+
+    def Predict(self, X):
+        return self.Classes[self._votes(X).argmax(1)]
+
+    def PredictProba(self, X):
+        """Softmax over the weighted votes (ml/adaboost.go:136-161)."""
+        v = self._votes(X)
+        e = np.exp(v - v.max(1, keepdims=True))
+        return e / e.sum(1, keepdims=True)
 
 
 class GradientBoostingRegressor(Regressor):

@@ -69,7 +69,15 @@ class DBSCAN(Clusterer):
                     queue.extend(nb[j])
             c += 1
         self.Labels = as_labels(lab)
+        self.Xtrain = X.numpy().copy()
         return self
+
+    def Predict(self, X):
+        """The label of the nearest training point if it lies within ``Eps``, else -1
+        (ml/cluster_extras.go:65-86)."""
+        d, j = torch.cdist(T(X), T(self.Xtrain)).min(1)
+        lab = np.asarray(self.Labels)[j.numpy()]
+        return np.where(d.numpy() > self.Eps, -1, lab)
 
 
 class AgglomerativeClustering(Clusterer):
@@ -92,7 +100,13 @@ class AgglomerativeClustering(Clusterer):
         for k, (_, members) in enumerate(sorted(clusters.items())):
             lab[members] = k
         self.Labels = as_labels(lab)
+        self.Xtrain = A(X).copy()
         return self
+
+    def Predict(self, X):
+        """The cluster of the nearest training point (ml/cluster_extras.go:200-216)."""
+        j = torch.cdist(T(X), T(self.Xtrain)).argmin(1).numpy()
+        return np.asarray(self.Labels)[j]
 
 
 class MeanShift(Clusterer):
@@ -120,6 +134,10 @@ class MeanShift(Clusterer):
                 lab[i] = len(centers) - 1
         self.Centers, self.Labels = torch.stack(centers).numpy(), as_labels(lab)
         return self
+
+    def Predict(self, X):
+        """Index of the nearest centre (ml/meanshift.go:117-132)."""
+        return torch.cdist(T(X), T(self.Centers)).argmin(1).numpy()
 
 
 class GaussianMixture(Clusterer):
@@ -152,10 +170,18 @@ class GaussianMixture(Clusterer):
         self.Labels = as_labels(R.argmax(1))
         return self
 
-    def Predict(self, X):
+    def PredictProba(self, X):
+        """Posterior probabilities over the components: softmax of log weight + log density
+        (ml/gmm.go:181-193)."""
         X = A(X)
-        logp = -0.5 * (((X[:, None] - self.Means[None]) ** 2 / self.Variances[None]) + np.log(2 * np.pi * self.Variances)[None]).sum(2) + np.log(self.Weights)
-        return logp.argmax(1)
+        logp = -0.5 * (((X[:, None] - self.Means[None]) ** 2 / self.Variances[None])
+                       + np.log(2 * np.pi * self.Variances)[None]).sum(2) + np.log(self.Weights + 1e-300)
+        logp -= logp.max(1, keepdims=True)
+        p = np.exp(logp)
+        return p / p.sum(1, keepdims=True)
+
+    def Predict(self, X):
+        return self.PredictProba(X).argmax(1)
 
 
 class PCA(Transformer):
@@ -250,6 +276,12 @@ class FastICA(Transformer):
 class TSNE(Estimator):
     _defaults = {"NComponents": 2, "Perplexity": 30.0, "LearningRate": 200.0, "NIter": 500, "Seed": 0,
                  "EarlyExaggeration": 12.0}
+
+    def Fit(self, X):
+        """Computes the embedding and keeps it in ``Embedding`` (ml/tsne.go:18-21); t-SNE has no
+        out-of-sample transform."""
+        self.Embedding = self.FitTransform(X)
+        return self
 
     def FitTransform(self, X):
         X = T(X)

@@ -31,6 +31,23 @@ class Module(_tnn.Module):
     def Buffers(self) -> List[Tuple[str, torch.Tensor]]:
         return list(self.named_buffers())
 
+    # ---- hooks as methods (nn/hooks.go:86-160); the functions of the same names take the module
+    def RegisterForwardPreHook(self, fn) -> int:
+        from . import hooks
+        return hooks.RegisterForwardPreHook(self, fn)
+
+    def RegisterForwardHook(self, fn) -> int:
+        from . import hooks
+        return hooks.RegisterForwardHook(self, fn)
+
+    def RegisterFullBackwardHook(self, fn) -> int:
+        from . import hooks
+        return hooks.RegisterFullBackwardHook(self, fn)
+
+    def RemoveHook(self, hook_id: int) -> bool:
+        from . import hooks
+        return hooks.RemoveHook(hook_id)
+
     def Forward(self, *args, **kwargs):
         """The reference's spelling of the forward pass (nn/module.go:29-33).  As there, it runs
         the layer directly; hooks run when the module is called (``m(x)`` or ``nn.Call(m, x)``)."""
@@ -99,6 +116,8 @@ class Sequential(Module):
     def __len__(self):
         return len(self._modules)
 
+    Len = __len__
+
     def __getitem__(self, i):
         if isinstance(i, slice):
             return Sequential(*list(self._modules.values())[i])
@@ -122,6 +141,9 @@ class ModuleList(_tnn.ModuleList, Module):
 
     def Len(self):
         return len(self)
+
+    def Get(self, i: int):
+        return self[i]
 
 
 class ModuleDict(Module):
@@ -152,6 +174,8 @@ class ModuleDict(Module):
     def __len__(self):
         return len(self._modules)
 
+    Len = __len__
+
     def __contains__(self, k):
         return k in self._modules
 
@@ -168,6 +192,12 @@ class ParameterList(_tnn.ParameterList, Module):
     def Append(self, p):
         self.append(p if isinstance(p, torch.nn.Parameter) else torch.nn.Parameter(p))
         return self
+
+    def Get(self, i: int):
+        return self[i]
+
+    def Len(self):
+        return len(self)
 
 
 class ParameterDict(Module):
@@ -196,6 +226,8 @@ class ParameterDict(Module):
 
     def __len__(self):
         return len(self._parameters)
+
+    Len = __len__
 
 
 class Identity(Module):

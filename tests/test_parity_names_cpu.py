@@ -176,3 +176,53 @@ def test_forward_spelling_bypasses_hooks_like_the_reference():
     mha = nn.MultiHeadAttention(8, 2)
     q = torch.randn(2, 5, 8)
     assert torch.equal(mha.Forward(q, q, q, True), mha(q, q, q, True))
+
+
+def test_container_hook_and_loader_method_spellings():
+    ml_ = nn.ModuleList([nn.Linear(2, 2), nn.ReLU()])
+    assert ml_.Len() == 2 and ml_.Get(1) is ml_[1]
+    md = nn.ModuleDict({"b": nn.ReLU(), "a": nn.Tanh()})
+    assert md.Len() == 2 and md.Keys() == ["a", "b"]
+    pl = nn.ParameterList([torch.zeros(2), torch.ones(3)])
+    assert pl.Len() == 2 and pl.Get(1).shape == (3,)
+    pd = nn.ParameterDict({"w": torch.zeros(2)})
+    assert pd.Len() == 1
+    lin = nn.Linear(3, 2)
+    seen = []
+    hid = lin.RegisterForwardHook(lambda m, x, y: seen.append("post"))
+    pid = lin.RegisterForwardPreHook(lambda m, x: seen.append("pre"))
+    bid = lin.RegisterFullBackwardHook(lambda m, g: seen.append("bwd"))
+    lin(torch.randn(4, 3, requires_grad=True)).sum().backward()
+    assert seen == ["pre", "post", "bwd"]
+    assert lin.RemoveHook(hid) and lin.RemoveHook(pid) and lin.RemoveHook(bid) and not lin.RemoveHook(hid)
+    lz = nn.LazyLinear(4)
+    assert lz.Inner() is None
+    lz(torch.randn(2, 3))
+    assert isinstance(lz.Inner(), nn.Linear)
+    dl = data.DataLoader(data.TensorDataset(torch.randn(10, 2), torch.arange(10)), batch_size=4)
+    assert dl.Len() == 3 and data.DataLoader(dl.dataset, batch_size=4, drop_last=True).Len() == 2
+
+
+def test_cluster_predict_and_probability_methods():
+    rng = np.random.default_rng(0)
+    X = np.concatenate([rng.normal(0, 0.2, (30, 2)), rng.normal(4, 0.2, (30, 2))])
+    y = np.array([0] * 30 + [1] * 30)
+    probe = np.array([[0.1, -0.1], [4.1, 3.9], [20.0, 20.0]])
+    db = ml.DBSCAN(Eps=0.6, MinSamples=3).Fit(X)
+    p = db.Predict(probe)
+    assert p[0] == db.Labels()[0] and p[1] == db.Labels()[-1] and p[2] == -1       # too far: noise
+    ag = ml.AgglomerativeClustering(NClusters=2).Fit(X)
+    p = ag.Predict(probe)
+    assert p[0] == ag.Labels()[0] and p[1] == ag.Labels()[-1] and p[2] == p[1]     # nearest training point
+    ms = ml.MeanShift(Bandwidth=1.0).Fit(X)
+    assert ms.Predict(probe[:2]).tolist() == [int(ms.Labels()[0]), int(ms.Labels()[-1])]
+    gm = ml.GaussianMixture(NComponents=2, Seed=0).Fit(X)
+    pr = gm.PredictProba(probe[:2])
+    assert pr.shape == (2, 2) and np.allclose(pr.sum(1), 1) and (pr.max(1) > 0.99).all()
+    assert np.array_equal(gm.Predict(probe[:2]), pr.argmax(1))
+    for clf in (ml.QDA().Fit(X, y), ml.AdaBoostClassifier(NEstimators=5, Seed=0).Fit(X, y)):
+        pr = clf.PredictProba(probe[:2])
+        assert pr.shape == (2, 2) and np.allclose(pr.sum(1), 1)
+        assert np.array_equal(clf.Classes[pr.argmax(1)], clf.Predict(probe[:2])) and pr.argmax(1).tolist() == [0, 1]
+    ts = ml.TSNE(NIter=50, Perplexity=5, Seed=0).Fit(X[::3])
+    assert ts.Embedding.shape == (20, 2)
