@@ -21,6 +21,25 @@ from torch import nn as _tnn
 class Module(_tnn.Module):
     """Base class of every layer."""
 
+    # ---- reference-style field names ---------------------------------------------------
+    def __getattr__(self, name: str):
+        """Exported field names of the reference resolve to the attribute of this module:
+        ``lin.Weight`` is ``lin.weight``, ``lin.InFeatures`` is ``lin.in_features``,
+        ``bn.RunningMean`` is ``bn.running_mean``.  Only consulted when the normal lookup
+        fails, so it costs nothing on the usual paths."""
+        try:
+            return super().__getattr__(name)
+        except AttributeError:
+            if name[:1].isupper():
+                snake = "".join("_" + c.lower() if c.isupper() and i else c.lower() for i, c in enumerate(name))
+                for alt in (snake, name.lower()):
+                    if alt != name:
+                        try:
+                            return getattr(self, alt)
+                        except AttributeError:
+                            pass
+            raise
+
     # ---- reference-style accessors -------------------------------------------------
     def Parameters(self) -> List[torch.nn.Parameter]:
         return list(self.parameters())

@@ -226,3 +226,15 @@ def test_cluster_predict_and_probability_methods():
         assert np.array_equal(clf.Classes[pr.argmax(1)], clf.Predict(probe[:2])) and pr.argmax(1).tolist() == [0, 1]
     ts = ml.TSNE(NIter=50, Perplexity=5, Seed=0).Fit(X[::3])
     assert ts.Embedding.shape == (20, 2)
+
+
+def test_exported_field_names_resolve_on_modules():
+    lin, bn, mha = nn.Linear(3, 2), nn.BatchNorm1d(4), nn.MultiHeadAttention(8, 2)
+    assert lin.Weight is lin.weight and lin.Bias is lin.bias and (lin.InFeatures, lin.OutFeatures) == (3, 2)
+    assert bn.RunningMean is bn.running_mean and bn.Eps == 1e-5 and mha.NumHeads == 2 and mha.EmbedDim == 8
+    with pytest.raises(AttributeError, match="no attribute 'Nope'"):
+        lin.Nope
+    assert not hasattr(lin, "WeightG")
+    import copy, pickle
+    assert torch.equal(copy.deepcopy(lin).Weight, lin.weight)
+    assert torch.equal(pickle.loads(pickle.dumps(lin)).weight, lin.weight)
