@@ -25,8 +25,9 @@ class Module(_tnn.Module):
     def __getattr__(self, name: str):
         """Exported field names of the reference resolve to the attribute of this module:
         ``lin.Weight`` is ``lin.weight``, ``lin.InFeatures`` is ``lin.in_features``,
-        ``bn.RunningMean`` is ``bn.running_mean``.  Only consulted when the normal lookup
-        fails, so it costs nothing on the usual paths."""
+        ``bn.RunningMean`` is ``bn.running_mean``.  The alternative spellings are tried only after
+        torch's own lookup of parameters / buffers / children has failed; the usual lookups pay
+        one extra Python call."""
         try:
             return super().__getattr__(name)
         except AttributeError:
