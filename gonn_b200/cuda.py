@@ -281,3 +281,8 @@ def BenchFlashAttn(BH: int, S: int, d: int, iters: int, causal: bool = False,
         scale = 1.0 / math.sqrt(d)
         return _time_ms(lambda: _attn.flash_fwd(q4, k4, v4, bool(causal), scale, out=o), iters, dev)
     return _time_ms(lambda: FlashAttnFwd(q, k, v, BH, S, d, None, causal, dt, dev), iters, dev)
+
+
+# the reference's names (its kernels are float64-only, hence the suffix); pass dtype=torch.float64
+# for float64 arithmetic, leave it unset for the tensor-core path on 16-bit data
+FlashAttnF64, FlashAttnF64Fwd, FlashAttnF64Bwd, BenchFlashAttnF64 = FlashAttn, FlashAttnFwd, FlashAttnBwd, BenchFlashAttn
