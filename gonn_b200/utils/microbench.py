@@ -4,6 +4,7 @@
     python -m gonn_b200.utils.microbench elementwise
     python -m gonn_b200.utils.microbench flash
     python -m gonn_b200.utils.microbench norm
+    python -m gonn_b200.utils.microbench resident                 # the reference's resident-MLP forward benchmark
     python -m gonn_b200.utils.microbench refattn                  # the reference's attention benchmark shapes
     python -m gonn_b200.utils.microbench mlp                      # CPU, config of the reference's quick start
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
@@ -149,6 +150,61 @@ def bench_reference_attention():
                   rel_err_dv=err(dv, rv), reference_published_gflops_fp64=86.6 if causal else 95.4)
 
 
+def bench_resident_mlp(device=None, iters: int = 20):
+    """The reference's resident-MLP benchmark (benchmark/resident/main.go:75-123): the forward pass
+    of 256 x 1024 -> 1024 -> 1024 -> 1024 (three products, two ReLUs) once through the tensor
+    API and once on device buffers that are uploaded once (``gonn_b200.cuda``); reports both
+    times and the largest difference between the two results.  float64, as there."""
+    from .. import cuda as C
+    from .. import tensor as T
+    dev = torch.device(device) if device is not None else torch.device("cuda" if torch.cuda.is_available() else "cpu")
+    Bn, D = 256, 1024
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(Bn, D, dtype=torch.float64, generator=g)
+    ws = [torch.randn(D, D, dtype=torch.float64, generator=g) / 32 for _ in range(3)]
+
+    def eager():
+        h = x.to(dev)                                   # the eager path pays the upload every call
+        for i, w in enumerate(ws):
+            h = T.MatMul(h, w.to(dev))
+            if i < 2:
+                h = T.Unary(h, "relu")
+        return h.cpu()
+
+    dx = C.DevUpload(x.numpy(), device=dev)
+    dws = [C.DevUpload(w.numpy(), device=dev) for w in ws]
+    h1, h2 = C.DevAlloc(Bn * D, device=dev), C.DevAlloc(Bn * D, device=dev)
+
+    def resident():
+        C.DevMatMul(dx, dws[0], h1, Bn, D, D)
+        C.DevReLU(h1, Bn * D)
+        C.DevMatMul(h1, dws[1], h2, Bn, D, D)
+        C.DevReLU(h2, Bn * D)
+        C.DevMatMul(h2, dws[2], h1, Bn, D, D)
+
+    def wall(fn):
+        for _ in range(3):
+            fn()
+        C.DevSync()
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            fn()
+        C.DevSync()
+        return (time.perf_counter() - t0) * 1e3 / iters
+
+    t_eager, t_res = wall(eager), wall(resident)
+    diff = float(np_abs_max(eager().numpy().reshape(-1) - h1.Download()))
+    rec = dict(bench="resident_mlp", device=dev.type, dtype="float64", eager_ms=t_eager, resident_ms=t_res,
+               speedup=t_eager / t_res, max_abs_diff=diff, reference_published="10.7 ms resident vs 21.4 ms eager")
+    _emit(**rec)
+    return rec
+
+
+def np_abs_max(a):
+    import numpy as np
+    return np.abs(a).max()
+
+
 def bench_norm():
     from ..ops.norm import layer_norm
     for rows, D in ((16384, 768), (65536, 768), (16384, 2048), (65536, 2048)):
@@ -246,7 +302,7 @@ def bench_allreduce():
 def main(argv):
     kind = argv[0] if argv else "gemm"
     fn = {"gemm": bench_gemm, "elementwise": bench_elementwise, "flash": bench_flash, "norm": bench_norm,
-          "mlp": bench_mlp_cpu, "allreduce": bench_allreduce, "refattn": bench_reference_attention}.get(kind)
+          "mlp": bench_mlp_cpu, "allreduce": bench_allreduce, "refattn": bench_reference_attention, "resident": bench_resident_mlp}.get(kind)
     if fn is None:
         raise SystemExit(f"unknown benchmark {kind!r}")
     fn()

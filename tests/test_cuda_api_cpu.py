@@ -78,3 +78,9 @@ def test_availability_without_a_device():
             C.Backend()
         with pytest.raises(RuntimeError):
             C.DevAlloc(4)
+
+
+def test_resident_mlp_benchmark_agrees_with_the_tensor_api():
+    from gonn_b200.utils.microbench import bench_resident_mlp
+    rec = bench_resident_mlp(device="cpu", iters=1)
+    assert rec["max_abs_diff"] == 0.0 and rec["resident_ms"] > 0 and rec["eager_ms"] > 0
