@@ -161,3 +161,21 @@ def test_index_maps_are_range_checked_before_upload():
         device_maps(np.array([[0, 4]], dtype=np.int32), 4, "cpu", False)
     with pytest.raises(ValueError):
         device_maps(np.array([[-2, 1]], dtype=np.int32), 4, "cpu", False)
+
+
+def test_attention_layer_trains_with_adam():
+    """Thirty Adam steps on a fixed regression target through MultiHeadAttention: the loss must
+    fall by a large factor (the reference's benchmark/flashbwd/main.go:97-121 check)."""
+    from gonn_b200 import optim
+    torch.manual_seed(0)
+    mha = nn.MultiHeadAttention(16, 2, dtype=D)
+    x, target = _x(4, 6, 16, seed=1), _x(4, 6, 16, seed=2) * 0.1
+    opt = optim.Adam(mha.parameters(), lr=0.02)
+    losses = []
+    for _ in range(30):
+        opt.zero_grad()
+        loss = nn.MSELoss(mha(x, x, x, True), target)
+        loss.backward()
+        opt.step()
+        losses.append(float(loss))
+    assert losses[-1] < 0.25 * losses[0], losses[::10]
