@@ -238,3 +238,17 @@ def test_exported_field_names_resolve_on_modules():
     import copy, pickle
     assert torch.equal(copy.deepcopy(lin).Weight, lin.weight)
     assert torch.equal(pickle.loads(pickle.dumps(lin)).weight, lin.weight)
+
+
+def test_round_to_dtype_known_patterns():
+    """Rounding emulation against hand-checked IEEE values (round to nearest, ties to even)."""
+    x = torch.tensor([0.1, 65504.0, 1e-8, 2049.0, 2051.0, 1.0 + 2 ** -11, 1.0 + 3 * 2 ** -11, -0.1], dtype=torch.float64)
+    h = T.RoundTo(x, torch.float16)
+    assert h.dtype == torch.float64
+    assert h.tolist() == [0.0999755859375, 65504.0, 0.0, 2048.0, 2052.0, 1.0, 1.001953125, -0.0999755859375]
+    f = T.RoundTo(torch.tensor([0.1, 16777217.0], dtype=torch.float64), torch.float32)
+    assert f.tolist() == [0.10000000149011612, 16777216.0]
+    b = T.RoundTo(torch.tensor([1.0 + 2 ** -8, 1.0 + 3 * 2 ** -8, 257.0, 259.0], dtype=torch.float64), torch.bfloat16)
+    assert b.tolist() == [1.0, 1.015625, 256.0, 260.0]
+    assert torch.equal(T.RoundTo(x, torch.float64), x)
+    assert T.Promote(torch.float16, torch.float32) == torch.float32 and T.Promote(torch.float32, torch.float64) == torch.float64
