@@ -8,3 +8,6 @@ from .trees import (DecisionTreeClassifier, DecisionTreeRegressor, RandomForestC
                     ExtraTreesClassifier, ExtraTreesRegressor, AdaBoostClassifier, GradientBoostingRegressor,
                     GradientBoostingClassifier, IsolationForest)
 from .unsupervised import *  # noqa
+
+# the long names the reference's documentation uses for the discriminant models
+LinearDiscriminantAnalysis, QuadraticDiscriminantAnalysis = LDA, QDA  # noqa: F405

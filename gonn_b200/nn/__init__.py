@@ -10,6 +10,9 @@ from .attention import MultiHeadAttention  # noqa
 from .transformer import (TransformerEncoderLayer, TransformerEncoder, TransformerDecoderLayer,  # noqa
                           TransformerDecoder, Transformer)
 from . import init  # noqa
+from .init import (XavierUniform, XavierNormal, KaimingUniform, KaimingNormal, Constant, ZerosInit, OnesInit,  # noqa
+                   Uniform, Normal, Orthogonal)
+from .module import NamedParameters  # noqa
 from .loss import *  # noqa
 from .loss import (MSELoss, MAELoss, L1Loss, HuberLoss, SmoothL1Loss, CrossEntropyLoss, NLLLoss, BCELoss,  # noqa
                    BCEWithLogitsLoss, KLDivLoss, PoissonNLLLoss, GaussianNLLLoss, MarginRankingLoss,

@@ -39,29 +39,39 @@ def OnesInit(t):
     return Constant(t, 1.0)
 
 
-@torch.no_grad()
-def XavierUniform(t, gain: float = 1.0):
+def _resolve_fans(t, fan_in, fan_out):
+    """Explicit fans (the reference passes them: nn/init.go:11-41) or the tensor's own."""
     fi, fo = _fans(t)
+    return (fi if fan_in is None else int(fan_in)), (fo if fan_out is None else int(fan_out))
+
+
+@torch.no_grad()
+def XavierUniform(t, fan_in=None, fan_out=None, gain: float = 1.0):
+    """U(-a, a), a = gain * sqrt(6 / (fan_in + fan_out)); ``XavierUniform(w, fanIn, fanOut)`` as in the
+    reference, or ``XavierUniform(w)`` with the fans taken from the shape."""
+    fi, fo = _resolve_fans(t, fan_in, fan_out)
     a = gain * math.sqrt(6.0 / (fi + fo))
     return t.uniform_(-a, a)
 
 
 @torch.no_grad()
-def XavierNormal(t, gain: float = 1.0):
-    fi, fo = _fans(t)
+def XavierNormal(t, fan_in=None, fan_out=None, gain: float = 1.0):
+    fi, fo = _resolve_fans(t, fan_in, fan_out)
     return t.normal_(0.0, gain * math.sqrt(2.0 / (fi + fo)))
 
 
 @torch.no_grad()
-def KaimingUniform(t, a: float = 0.0):
-    fi, _ = _fans(t)
+def KaimingUniform(t, fan_in=None, a: float = 0.0):
+    """U(-b, b), b = sqrt(2 / (1 + a^2)) * sqrt(3 / fan_in): sqrt(6 / fan_in) at a = 0, the
+    reference's bound (nn/init.go:27-33)."""
+    fi, _ = _resolve_fans(t, fan_in, None)
     bound = math.sqrt(2.0 / (1 + a * a)) * math.sqrt(3.0 / fi)
     return t.uniform_(-bound, bound)
 
 
 @torch.no_grad()
-def KaimingNormal(t, a: float = 0.0):
-    fi, _ = _fans(t)
+def KaimingNormal(t, fan_in=None, a: float = 0.0):
+    fi, _ = _resolve_fans(t, fan_in, None)
     return t.normal_(0.0, math.sqrt(2.0 / (1 + a * a)) / math.sqrt(fi))
 
 

@@ -110,9 +110,21 @@ class Module(_tnn.Module):
         return sum(p.numel() for p in self.parameters())
 
 
-def FilterParams(module: _tnn.Module, pred: Callable[[str, torch.nn.Parameter], bool]):
-    """Parameters whose (dotted name, tensor) satisfy ``pred`` (nn/module.go:167-175)."""
-    return [p for n, p in module.named_parameters() if pred(n, p)]
+def FilterParams(module: _tnn.Module, pred: Callable[..., bool]):
+    """Parameters selected by ``pred``, which takes the dotted name as in the reference
+    (nn/module.go:167-175) or the name and the tensor."""
+    import inspect
+    try:
+        two = len(inspect.signature(pred).parameters) >= 2
+    except (TypeError, ValueError):
+        two = False
+    return [p for n, p in module.named_parameters() if (pred(n, p) if two else pred(n))]
+
+
+def NamedParameters(module: _tnn.Module):
+    """``[Param(name, tensor), ...]`` in registration order (nn/module.go:12-15, 120-135)."""
+    from .types import Param
+    return [Param(n, p) for n, p in module.named_parameters()]
 
 
 filter_params = FilterParams

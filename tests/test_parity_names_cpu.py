@@ -1,5 +1,7 @@
 """Names and call forms of the reference that have no PyTorch spelling: constructor functions,
 small record types, argument orders of the padding layers, transform objects."""
+import math
+
 import numpy as np
 import pytest
 import torch
@@ -252,3 +254,25 @@ def test_round_to_dtype_known_patterns():
     assert b.tolist() == [1.0, 1.015625, 256.0, 260.0]
     assert torch.equal(T.RoundTo(x, torch.float64), x)
     assert T.Promote(torch.float16, torch.float32) == torch.float32 and T.Promote(torch.float32, torch.float64) == torch.float64
+
+
+def test_init_functions_take_the_reference_arguments():
+    torch.manual_seed(0)
+    w = torch.empty(64, 32, dtype=torch.float64)
+    nn.XavierUniform(w, 32, 64)
+    assert w.abs().max() <= math.sqrt(6 / 96) and w.std() > 0.1
+    nn.KaimingNormal(w, 32)
+    assert abs(float(w.std()) - math.sqrt(2 / 32)) < 0.02
+    nn.KaimingUniform(w, 32)
+    assert w.abs().max() <= math.sqrt(6 / 32)
+    nn.XavierNormal(w)                                     # fans from the shape
+    assert abs(float(w.std()) - math.sqrt(2 / 96)) < 0.01
+    nn.Orthogonal(w[:32], 1.0)
+    assert torch.allclose(w[:32] @ w[:32].t(), torch.eye(32, dtype=torch.float64), atol=1e-10)
+    nn.Constant(w, 0.5)
+    assert bool((w == 0.5).all())
+    lin = nn.Linear(3, 2)
+    assert [p.Name for p in nn.NamedParameters(lin)] == ["weight", "bias"]
+    assert nn.FilterParams(lin, lambda name: name == "bias")[0] is lin.bias
+    assert nn.FilterParams(lin, lambda name, p: p.dim() == 2)[0] is lin.weight
+    assert ml.LinearDiscriminantAnalysis is ml.LDA and ml.QuadraticDiscriminantAnalysis is ml.QDA
