@@ -58,6 +58,34 @@ def ordered_parameters(module: torch.nn.Module) -> List[torch.nn.Parameter]:
     return out
 
 
+def plan_buckets(sizes, world: int, limit: int):
+    """Layout of the flat parameter / gradient buffers.
+
+    Parameters are packed in order, each starting on an 8-element boundary (16 bytes for 16-bit
+    types: the alignment the vector and TMA accesses need).  A bucket is closed once it holds at
+    least ``limit`` elements and is padded to a multiple of ``world * 8`` elements, so that it
+    splits into ``world`` shards of whole 16-byte vectors.  Returns ``(offsets, buckets, total)``:
+    the offset of every parameter, ``(start, length, member indices)`` per bucket, and the
+    buffer length in elements."""
+    align = world * 8
+    limit = max(int(limit), align)
+    offsets, buckets = [], []
+    off = start = 0
+    members = []
+    for i, n in enumerate(sizes):
+        offsets.append(off)
+        members.append(i)
+        off += (int(n) + 7) // 8 * 8
+        if off - start >= limit:
+            off = start + (off - start + align - 1) // align * align
+            buckets.append((start, off - start, members))
+            start, members = off, []
+    if members:
+        off = start + (off - start + align - 1) // align * align
+        buckets.append((start, off - start, members))
+    return offsets, buckets, off
+
+
 class _Bucket:
     __slots__ = ("index", "start", "length", "params", "pending", "launched", "master", "m", "v")
 
@@ -113,29 +141,17 @@ class DistributedDataParallel(torch.nn.Module):
         self.params = params
 
         # ---- layout -------------------------------------------------------------------
-        align = world * 8
-        limit = max(int(bucket_mb * (1 << 20) / self._esz), align)
+        limit = int(bucket_mb * (1 << 20) / self._esz)
+        offsets, spans, self.total = plan_buckets([p.numel() for p in params], world, limit)
         self.buckets: List[_Bucket] = []
         self._where: Dict[int, tuple] = {}
-        off = 0
-        cur = _Bucket(0, 0)
-        for p in params:
-            n = p.numel()
-            # 8-element alignment keeps every parameter 16-byte aligned for TMA / vector access
-            n_pad = (n + 7) // 8 * 8
-            self._where[id(p)] = (cur, off, n)
-            cur.params.append(p)
-            off += n_pad
-            if off - cur.start >= limit:
-                off = cur.start + (off - cur.start + align - 1) // align * align
-                cur.length = off - cur.start
-                self.buckets.append(cur)
-                cur = _Bucket(len(self.buckets), off)
-        if cur.params:
-            off = cur.start + (off - cur.start + align - 1) // align * align
-            cur.length = off - cur.start
-            self.buckets.append(cur)
-        self.total = off
+        for start, length, members in spans:
+            b = _Bucket(len(self.buckets), start)
+            b.length = length
+            for i in members:
+                b.params.append(params[i])
+                self._where[id(params[i])] = (b, offsets[i], params[i].numel())
+            self.buckets.append(b)
         nbytes = self.total * self._esz
         self._param_off = _SLOT_BYTES
         self._grad_off = _SLOT_BYTES + (nbytes + 255) // 256 * 256
