@@ -316,7 +316,10 @@ def _constructor_aliases(ns) -> None:
     """``NewX`` for every public class ``X`` (the reference's constructor functions)."""
     for name, obj in list(ns.items()):
         if isinstance(obj, type) and name[0].isupper() and "New" + name not in ns:
-            ns["New" + name] = obj
+            ns["New" + name] = _accepting_options(obj)
 
+
+from ..options import accepting_options as _accepting_options, package_getattr as _package_getattr  # noqa: E402
 
 _constructor_aliases(globals())
+__getattr__ = _package_getattr(__name__)     # optim.WithMomentum(0.9), optim.WithNesterov(True), ...

@@ -40,15 +40,23 @@ from . import prune  # noqa
 from .types import *  # noqa
 
 
+from ..options import accepting_options as _accepting_options, package_getattr as _package_getattr
+
+
 def _constructor_aliases(ns) -> None:
     """``NewX`` for every public class ``X``: the reference builds modules with constructor
-    functions (``nn.NewLinear(3, 4)``), which read the same here."""
+    functions (``nn.NewLinear(3, 4)``, ``nn.NewConv2d(3, 16, 3, nn.WithPadding(1))``).  Each
+    ``NewX`` calls ``X`` after turning option objects into keyword arguments; the loss functions
+    accept options the same way (``nn.CrossEntropyLoss(z, y, nn.WithLabelSmoothing(0.1))``)."""
     for name, obj in list(ns.items()):
         if (isinstance(obj, type) or name.startswith("Lazy")) and name[0].isupper() and "New" + name not in ns:
-            ns["New" + name] = obj
+            ns["New" + name] = _accepting_options(obj)
+        elif callable(obj) and not isinstance(obj, type) and name.endswith("Loss") and name[0].isupper():
+            ns[name] = _accepting_options(obj)
 
 
 _constructor_aliases(globals())
+__getattr__ = _package_getattr(__name__)     # nn.WithPadding(1), nn.WithBidirectional(), ...
 
 
 def NewLayerNormShape(shape, **kw):

@@ -38,12 +38,12 @@ def test_padding_argument_orders_follow_the_reference():
 
 def test_constructor_aliases_and_small_types():
     lin = nn.NewLinear(3, 4)
-    assert isinstance(lin, nn.Linear) and nn.NewLSTM is nn.LSTM and nn.NewZeroPad1d is nn.ZeroPad1d
+    assert isinstance(lin, nn.Linear) and nn.NewLSTM.__wrapped__ is nn.LSTM and nn.NewZeroPad1d.__wrapped__ is nn.ZeroPad1d
     assert isinstance(nn.NewLazyLinear(5), torch.nn.Module)
     ln = nn.NewLayerNormShape([3, 4])
     assert tuple(ln.weight.shape) == (3, 4)
-    assert optim.NewAdam is optim.Adam and optim.NewStepLR is optim.StepLR
-    assert data.NewTensorDataset is data.TensorDataset and data.NewDataLoader is data.DataLoader
+    assert optim.NewAdam.__wrapped__ is optim.Adam and optim.NewStepLR.__wrapped__ is optim.StepLR
+    assert data.NewTensorDataset.__wrapped__ is data.TensorDataset and data.NewDataLoader.__wrapped__ is data.DataLoader
     assert isinstance(lin, nn.Child) and nn.Base is nn.Module
     assert isinstance(nn.ParametrizedLinear, type)
     p = nn.Param("weight", lin.weight)
@@ -276,3 +276,44 @@ def test_init_functions_take_the_reference_arguments():
     assert nn.FilterParams(lin, lambda name: name == "bias")[0] is lin.bias
     assert nn.FilterParams(lin, lambda name, p: p.dim() == 2)[0] is lin.weight
     assert ml.LinearDiscriminantAnalysis is ml.LDA and ml.QuadraticDiscriminantAnalysis is ml.QDA
+
+
+def test_functional_options_become_keyword_arguments():
+    c = nn.NewConv2d(3, 16, 3, nn.WithPadding(1), nn.WithStride(2), nn.WithNoBias(), nn.WithDilation(1, 1),
+                     nn.WithGroups(1), nn.WithPaddingMode("reflect"))
+    assert isinstance(c, nn.Conv2d) and c.padding == (1, 1) and c.stride == (2, 2) and c.bias is None
+    t = nn.NewConvTranspose2d(4, 2, 3, nn.WithStride(2), nn.WithOutputPadding(1))
+    assert t(torch.randn(1, 4, 5, 5)).shape == (1, 2, 12, 12)
+    r = nn.NewLSTM(4, 8, nn.WithLayers(2), nn.WithBidirectional(), nn.WithProjSize(3))
+    assert r.num_layers == 2 and r.bidirectional and r.proj_size == 3
+    assert nn.NewRNN(4, 8, nn.WithReLU()).cells[0].relu if hasattr(nn.NewRNN(4, 8).cells[0], "relu") else True
+    p = nn.NewMaxPool2d(2, nn.WithPoolStride(1), nn.WithPoolPadding(1), nn.WithPoolCeilMode(), nn.WithPoolDilation(1))
+    assert p.stride == (1, 1) and p.padding == (1, 1) and p.ceil_mode
+    assert not nn.NewAvgPool2d(3, nn.WithCountIncludePad(False)).count_include_pad
+    bn = nn.NewBatchNorm2d(4, nn.WithEps(1e-3), nn.WithMomentum(0.2), nn.WithAffine(False))
+    assert bn.eps == 1e-3 and bn.momentum == 0.2 and bn.weight is None
+    e = nn.NewEmbedding(10, 4, nn.WithPaddingIdx(0), nn.WithMaxNorm(1.0))
+    assert e.padding_idx == 0 and e.max_norm == 1.0
+    assert nn.NewEmbeddingBag(10, 4, nn.WithBagMode("sum"), nn.WithBagPaddingIdx(1)).mode == "sum"
+    enc = nn.NewTransformerEncoderLayer(8, 2, 16, nn.WithPreNorm(), nn.WithCausal(), nn.WithTransformerDropout(0.0))
+    assert enc.pre_norm and enc.causal
+    assert nn.NewMultiHeadAttention(8, 2, nn.WithKDim(6), nn.WithVDim(4)).kdim == 6
+    l = nn.NewLocalResponseNorm(3, nn.WithLRNAlpha(1e-3), nn.WithLRNBeta(0.5), nn.WithLRNK(2.0))
+    assert (l.alpha, l.beta, l.k) == (1e-3, 0.5, 2.0)
+    assert nn.NewUpsample(2, "bilinear", nn.WithAlignCorners(True)).align_corners
+    assert nn.NewSpectralNormLinear(nn.Linear(3, 3), nn.WithNPowerIterations(3), nn.WithSpectralEps(1e-9)).n_power_iterations == 3
+    z, y = torch.randn(4, 5), torch.tensor([0, 1, 2, 1])
+    got = nn.CrossEntropyLoss(z, y, nn.WithLabelSmoothing(0.1), nn.WithReduction(nn.ReduceSum), nn.WithIgnoreIndex(2))
+    assert torch.equal(got, nn.CrossEntropyLoss(z, y, label_smoothing=0.1, reduction="sum", ignore_index=2))
+    w = torch.nn.Parameter(torch.zeros(3))
+    o = optim.NewSGD([w], 0.1, optim.WithMomentum(0.9), optim.WithNesterov(True), optim.WithSGDWeightDecay(0.01))
+    assert (o.momentum, o.nesterov, o.Groups()[0].weight_decay) == (0.9, True, 0.01)
+    a = optim.NewAdamW([w], 0.01, optim.WithAdamWBeta2(0.95), optim.WithAdamWWeightDecay(0.1), optim.WithAdamWEps(1e-6))
+    assert (a.beta1, a.beta2) == (0.9, 0.95) and a.eps == 1e-6 and a.Groups()[0].weight_decay == 0.1
+    rp = optim.NewRprop([w], 0.01, optim.WithRpropEtaMinus(0.4), optim.WithRpropStepBounds(1e-5, 10.0))
+    assert (rp.eta_minus, rp.eta_plus, rp.step_min, rp.step_max) == (0.4, 1.2, 1e-5, 10.0)
+    assert optim.NewASGD([w], 0.01, optim.WithASGDLambda(1e-3), optim.WithASGDT0(5.0)).lambd == 1e-3
+    with pytest.raises(TypeError, match="no argument matches option WithStride"):
+        nn.NewLinear(3, 2, nn.WithStride(2))
+    with pytest.raises(AttributeError):
+        nn.Withlowercase
