@@ -19,6 +19,7 @@ from ..ops.attention import flash_attention, self_attention_qkv
 from ..ops.softmax import softmax as _softmax
 from .init import fan_in_uniform_
 from .linear import Linear
+from ..options import accepting_options as _accepting_options
 from .module import Module
 
 
@@ -93,6 +94,7 @@ class MultiHeadAttention(Module):
         with torch.no_grad():
             return self.forward(q, k, v, causal)
 
+    @_accepting_options
     def ForwardMasked(self, q, k=None, v=None, causal: bool = False, attn_mask=None,
                       key_padding_mask=None, attn_dropout: float = 0.0):
         """General masks: ``attn_mask`` (Tq, Tk) additive float or bool (True = masked),

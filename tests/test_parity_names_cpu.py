@@ -317,3 +317,16 @@ def test_functional_options_become_keyword_arguments():
         nn.NewLinear(3, 2, nn.WithStride(2))
     with pytest.raises(AttributeError):
         nn.Withlowercase
+
+
+def test_attention_call_options():
+    m = nn.MultiHeadAttention(8, 2, dtype=torch.float64)
+    q = torch.randn(2, 5, 8, dtype=torch.float64)
+    pad = torch.zeros(2, 5, dtype=torch.bool)
+    pad[1, 3:] = True
+    mask = torch.triu(torch.ones(5, 5, dtype=torch.bool), 1)
+    a = m.ForwardMasked(q, q, q, nn.WithCausal(), nn.WithKeyPaddingMask(pad))
+    assert torch.equal(a, m.ForwardMasked(q, q, q, causal=True, key_padding_mask=pad))
+    b = m.ForwardMasked(q, q, q, nn.WithAttnMask(mask))
+    assert torch.allclose(b, m.ForwardMasked(q, q, q, causal=True), atol=1e-12)     # a causal mask given explicitly
+    assert torch.allclose(b, m(q, q, q, True), atol=1e-6)
