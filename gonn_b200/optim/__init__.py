@@ -10,8 +10,15 @@ from .scheduler import (Scheduler, StepLR, MultiStepLR, ExponentialLR, CosineAnn
 
 
 def _groups_ctor(cls):
-    def make(groups, **kw):
-        """Constructor over explicit ``Group`` lists; optimizer defaults are NOT injected."""
+    def make(groups, *opts, **kw):
+        """Constructor over explicit ``Group`` lists; optimizer defaults are NOT injected.
+        Functional options (``optim.WithBeta2(0.95)``) are accepted after the groups."""
+        from ..options import Option, resolve
+        bad = [o for o in opts if not isinstance(o, Option)]
+        if bad:
+            raise TypeError(f"{make.__name__}: unexpected positional arguments {bad}")
+        for k, v in resolve(cls, opts).items():
+            kw.setdefault(k, v)
         return cls(groups, **kw)
     make.__name__ = "New" + cls.__name__ + "Groups"
     return make

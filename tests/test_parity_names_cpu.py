@@ -330,3 +330,12 @@ def test_attention_call_options():
     b = m.ForwardMasked(q, q, q, nn.WithAttnMask(mask))
     assert torch.allclose(b, m.ForwardMasked(q, q, q, causal=True), atol=1e-12)     # a causal mask given explicitly
     assert torch.allclose(b, m(q, q, q, True), atol=1e-6)
+
+
+def test_group_constructors_accept_options():
+    w, b = torch.nn.Parameter(torch.zeros(3)), torch.nn.Parameter(torch.zeros(2))
+    o = optim.NewAdamWGroups([optim.Group([w], 1e-3, 0.1), optim.Group([b], 1e-3, 0.0)],
+                             optim.WithAdamWBeta2(0.95), optim.WithAdamWEps(1e-6))
+    assert (o.beta2, o.eps) == (0.95, 1e-6) and [g.weight_decay for g in o.Groups()] == [0.1, 0.0]
+    with pytest.raises(TypeError):
+        optim.NewSGDGroups([optim.Group([w], 0.1, 0.0)], 0.9)
