@@ -66,7 +66,7 @@ _RENAMED = {
     "AdagradLRDecay": "lr_decay", "BagMode": "mode", "BagPaddingIdx": "padding_idx", "BagMaxNorm": "max_norm",
     "FFActivation": "activation", "TransformerDropout": "dropout", "RNNDropout": "dropout", "SpectralEps": "eps",
     "KDim": "kdim", "VDim": "vdim", "RpropStepBounds": "step_sizes", "ClassWeights": "weight",
-    "FractionalSamples": "samples", "NormType": "norm_type", "ASGDT0": "t0",
+    "FractionalSamples": "samples", "NormType": "norm_type", "ASGDT0": "t0", "DType": "dtype",
 }
 # options that set one element of a tuple-valued keyword: option suffix -> (keyword, position)
 _ELEMENT = {"Beta1": ("betas", 0), "Beta2": ("betas", 1), "EtaMinus": ("etas", 0), "EtaPlus": ("etas", 1),

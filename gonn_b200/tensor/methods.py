@@ -36,6 +36,18 @@ def install(namespace) -> list:
         if not hasattr(torch.Tensor, name):
             setattr(torch.Tensor, name, fn)
             added.append(name)
+    # exported fields of the reference's tensor (tensor/tensor.go:14-30) as properties: the values in
+    # row-major order, the shape as a list, the gradient (assignable) and the gradient flag
+    fields = {
+        "Data": property(lambda self: self.detach().reshape(-1)),
+        "Shape": property(lambda self: list(self.shape)),
+        "Grad": property(lambda self: self.grad, lambda self, g: setattr(self, "grad", g)),
+        "RequiresGrad": property(lambda self: self.requires_grad),
+    }
+    for name, prop in fields.items():
+        if not hasattr(torch.Tensor, name):
+            setattr(torch.Tensor, name, prop)
+            added.append(name)
     _installed.extend(added)
     return added
 

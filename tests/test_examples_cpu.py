@@ -45,3 +45,7 @@ def test_package_entry_point_demo(capsys):
     assert "x + y = Tensor(shape=[2 3], data=[8 10 12 14 16 18])" in out
     assert "dy/dx = Tensor(shape=[3 1], data=[6 -3 1.5])" in out and "dy/dW = Tensor(shape=[1 3], data=[3 6 9])" in out
     assert "a @ b = Tensor(shape=[2 2], data=[4 5 10 11])" in out and "unary ops registered" in out
+
+
+def test_reference_style_program():
+    assert _load("reference_style").main(epochs=60, verbose=False) > 0.95

@@ -339,3 +339,12 @@ def test_group_constructors_accept_options():
     assert (o.beta2, o.eps) == (0.95, 1e-6) and [g.weight_decay for g in o.Groups()] == [0.1, 0.0]
     with pytest.raises(TypeError):
         optim.NewSGDGroups([optim.Group([w], 0.1, 0.0)], 0.9)
+
+
+def test_tensor_field_properties():
+    x = T.SetRequiresGrad(T.New([1, 2, 3, 4, 5, 6], 2, 3))
+    assert x.Shape == [2, 3] and x.Data.tolist() == [1, 2, 3, 4, 5, 6] and x.RequiresGrad and x.Grad is None
+    x.Square().Sum().Backward()
+    assert x.Grad.tolist() == [[2, 4, 6], [8, 10, 12]]
+    x.Grad = None
+    assert x.grad is None
