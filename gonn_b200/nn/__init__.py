@@ -55,6 +55,23 @@ def _constructor_aliases(ns) -> None:
             ns[name] = _accepting_options(obj)
 
 
+def NewSequential(*layers):
+    return Sequential(*layers)  # noqa: F405
+
+
+def NewModuleList(*mods):
+    """Variadic, as in the reference (nn/containers.go:27-40); one list is accepted too."""
+    return ModuleList(list(mods[0]) if len(mods) == 1 and isinstance(mods[0], (list, tuple)) else list(mods))  # noqa: F405
+
+
+def NewParameterList(*ps):
+    return ParameterList(list(ps[0]) if len(ps) == 1 and isinstance(ps[0], (list, tuple)) else list(ps))  # noqa: F405
+
+
+def NewUnflatten(dim, *sizes):
+    return Unflatten(dim, tuple(sizes[0]) if len(sizes) == 1 and isinstance(sizes[0], (list, tuple)) else sizes)  # noqa: F405
+
+
 _constructor_aliases(globals())
 __getattr__ = _package_getattr(__name__)     # nn.WithPadding(1), nn.WithBidirectional(), ...
 

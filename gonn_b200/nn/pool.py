@@ -147,8 +147,14 @@ def _adaptive_index_build(in_shape, out_shape):
 class _AdaptivePoolNd(Module):
     nd, mode = 2, "avg"
 
-    def __init__(self, output_size):
+    def __init__(self, *output_size):
+        """``AdaptiveAvgPool2d((2, 3))``, ``AdaptiveAvgPool2d(1)`` or, as in the reference,
+        ``NewAdaptiveAvgPool2d(2, 3)`` (nn/pool_adaptive.go:95-140)."""
         super().__init__()
+        if len(output_size) == 1:
+            output_size = output_size[0]
+        elif len(output_size) != self.nd:
+            raise ValueError(f"{type(self).__name__}: expected 1 or {self.nd} output sizes")
         self.output_size = _tup(output_size, self.nd)
 
     def forward(self, x):
@@ -187,19 +193,32 @@ class _FractionalMaxPoolNd(Module):
     last start = in - k; one ``u`` per dim per forward (``samples`` fixes them)."""
     nd = 2
 
-    def __init__(self, kernel_size, output_size, samples=None):
+    def __init__(self, kernel_size, output_size=None, samples=None, output_ratio=None):
+        """Exactly one of ``output_size`` and ``output_ratio`` (output = floor(input * ratio),
+        nn/pool_fractional.go:60-110) is given."""
         super().__init__()
-        self.kernel_size, self.output_size = _tup(kernel_size, self.nd), _tup(output_size, self.nd)
+        if (output_size is None) == (output_ratio is None):
+            raise ValueError(f"{type(self).__name__}: give output_size or output_ratio")
+        self.kernel_size = _tup(kernel_size, self.nd)
+        self.output_size = _tup(output_size, self.nd) if output_size is not None else None
+        self.output_ratio = None
+        if output_ratio is not None:
+            r = tuple(output_ratio) if isinstance(output_ratio, (tuple, list)) else (output_ratio,) * self.nd
+            if len(r) != self.nd or any(not 0 < v <= 1 for v in r):
+                raise ValueError(f"{type(self).__name__}: output_ratio needs {self.nd} values in (0, 1]")
+            self.output_ratio = r
         self.samples = samples
 
     def forward(self, x):
         N, C = x.shape[:2]
         in_shape = tuple(x.shape[2:])
         nd = self.nd
+        out_size = self.output_size if self.output_size is not None else tuple(
+            max(int(math.floor(in_shape[d] * self.output_ratio[d])), 1) for d in range(nd))
         us = self.samples if self.samples is not None else [float(torch.rand(())) for _ in range(nd)]
         starts = []
         for d in range(nd):
-            i, k, o = in_shape[d], self.kernel_size[d], self.output_size[d]
+            i, k, o = in_shape[d], self.kernel_size[d], out_size[d]
             if k + o - 1 > i:
                 raise ValueError("FractionalMaxPool: kernel + output - 1 must not exceed the input size")
             alpha = (i - k) / (o - 1) if o > 1 else 0.0
@@ -211,12 +230,12 @@ class _FractionalMaxPoolNd(Module):
             strides[d] = strides[d + 1] * in_shape[d + 1]
         import itertools
         wins = []
-        for combo in itertools.product(*[range(o) for o in self.output_size]):
+        for combo in itertools.product(*[range(o) for o in out_size]):
             axes = [range(starts[d][combo[d]], starts[d][combo[d]] + self.kernel_size[d]) for d in range(nd)]
             wins.append([sum(c * s for c, s in zip(pt, strides)) for pt in itertools.product(*axes)])
         idx = np.asarray(wins, dtype=np.int32)
         y, _ = _pool(x.reshape(N * C, -1), idx, "max")
-        return y.reshape(N, C, *self.output_size)
+        return y.reshape(N, C, *out_size)
 
 
 class FractionalMaxPool2d(_FractionalMaxPoolNd):

@@ -348,3 +348,23 @@ def test_tensor_field_properties():
     assert x.Grad.tolist() == [[2, 4, 6], [8, 10, 12]]
     x.Grad = None
     assert x.grad is None
+
+
+def test_variadic_constructor_forms():
+    assert nn.NewAdaptiveAvgPool2d(1, 1).output_size == (1, 1) and nn.AdaptiveAvgPool2d((2, 3)).output_size == (2, 3)
+    assert nn.NewAdaptiveMaxPool3d(1, 2, 3).output_size == (1, 2, 3) and nn.AdaptiveMaxPool1d(3).output_size == (3,)
+    with pytest.raises(ValueError):
+        nn.NewAdaptiveAvgPool2d(1, 2, 3)
+    assert nn.NewParameterList(torch.zeros(2), torch.ones(3)).Len() == 2
+    assert nn.NewModuleList(nn.ReLU(), nn.Tanh()).Len() == 2 and nn.NewModuleList([nn.ReLU()]).Len() == 1
+    assert nn.NewUnflatten(1, 2, 3)(torch.zeros(4, 6)).shape == (4, 2, 3)
+    assert nn.NewSequential(nn.NewLinear(2, 3, True), nn.ReLU())(torch.zeros(1, 2)).shape == (1, 3)
+    x = torch.randn(1, 2, 10, 10)
+    fp = nn.NewFractionalMaxPool2d(2, nn.WithOutputRatio(0.5, 0.7), nn.WithFractionalSamples(0.3, 0.6))
+    assert fp(x).shape == (1, 2, 5, 7)
+    assert nn.NewFractionalMaxPool2d(2, nn.WithOutputSize(4, 4))(x).shape == (1, 2, 4, 4)
+    with pytest.raises(ValueError):
+        nn.NewFractionalMaxPool2d(2)
+    assert nn.NewFold((4, 4), 2, nn.WithStride(2))(torch.randn(1, 8, 4)).shape == (1, 2, 4, 4)
+    assert nn.NewUnfold(2, nn.WithStride(2))(torch.randn(1, 2, 4, 4)).shape == (1, 8, 4)
+    assert nn.NewLPPool2d(2.0, 2)(x.abs()).shape == (1, 2, 5, 5)
