@@ -30,6 +30,41 @@ class Estimator:
                 setattr(self, k, v)
 
 
+def _np(v):
+    return v.numpy() if isinstance(v, torch.Tensor) else v
+
+
+# result fields under the reference's names, derived from what the estimators store
+# (ml/linreg.go, logreg.go, svm.go, kmeans.go, knn.go, gmm.go, pca.go, lda.go ...): name -> getter
+_FIELD_ALIASES = {
+    # linear models keep (Coef, Intercept); classifiers a (d + 1, K) matrix W with the bias row last
+    "Weights": lambda o: o.Coef if "Coef" in o.__dict__ else _np(o.W)[:-1].T,
+    "Bias": lambda o: o.Intercept if "Intercept" in o.__dict__ else _np(o.W)[-1],
+    "Centroids": lambda o: o.Centers,
+    "Xtrain": lambda o: _np(o.__dict__["X"]),
+    "XTrain": lambda o: _np(o.__dict__["X"]),
+    "Ytrain": lambda o: _np(o.__dict__["y"]),
+    "Covariances": lambda o: o.Variances,            # diagonal covariances
+    "AlphaPrec": lambda o: o.AlphaEst,
+    "LambdaPrec": lambda o: o.LambdaEst,
+    "Components": lambda o: np.asarray(o.Scalings).T,                        # LDA: (NComponents, d)
+    "Classes": lambda o: o.Categories[0],                                    # OneHotEncoder on one column
+}
+
+
+def _estimator_getattr(self, name):
+    get = _FIELD_ALIASES.get(name)
+    if get is not None:
+        try:
+            return get(self)
+        except (KeyError, AttributeError):
+            pass
+    raise AttributeError(f"{type(self).__name__!r} object has no attribute {name!r}")
+
+
+Estimator.__getattr__ = _estimator_getattr
+
+
 class Regressor(Estimator):
     def Fit(self, X, y): raise NotImplementedError
     def Predict(self, X): raise NotImplementedError

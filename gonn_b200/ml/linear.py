@@ -98,6 +98,7 @@ class BayesianRidge(Regressor):
             if done:
                 break
         self.Coef, self.Intercept, self.Sigma, self.AlphaEst, self._mu = w, float(ym - mu @ w), S, alpha, mu
+        self.LambdaEst = lam
         return self
 
     def Predict(self, X):

@@ -167,6 +167,7 @@ class GaussianMixture(Clusterer):
                 break
             prev = ll
         self.Means, self.Variances, self.Weights, self.Resp = mu, var, pi, R
+        self.LogLikelihood = ll
         self.Labels = as_labels(R.argmax(1))
         return self
 
@@ -266,6 +267,7 @@ class FastICA(Transformer):
             W = Wn
             if lim < self.Tol:
                 break
+        self.Components = W.numpy()          # the unmixing rotation in whitened space (ml/ica.go:23)
         self.Unmixing = W @ self.Whitening
         return self
 

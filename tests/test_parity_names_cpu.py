@@ -368,3 +368,30 @@ def test_variadic_constructor_forms():
     assert nn.NewFold((4, 4), 2, nn.WithStride(2))(torch.randn(1, 8, 4)).shape == (1, 2, 4, 4)
     assert nn.NewUnfold(2, nn.WithStride(2))(torch.randn(1, 2, 4, 4)).shape == (1, 8, 4)
     assert nn.NewLPPool2d(2.0, 2)(x.abs()).shape == (1, 2, 5, 5)
+
+
+def test_estimator_result_fields_under_the_reference_names():
+    rng = np.random.default_rng(0)
+    x = rng.random((100, 1)) * 10
+    y = 2.5 * x[:, 0] + 1.7 + rng.normal(0, 0.05, 100)
+    lr = ml.LinearRegression().Fit(x, y)
+    assert abs(lr.Weights[0] - 2.5) < 0.02 and abs(lr.Bias - 1.7) < 0.1
+    X = np.concatenate([rng.normal(0, 0.3, (30, 2)), rng.normal(3, 0.3, (30, 2))])
+    lab = np.array([0] * 30 + [1] * 30)
+    km = ml.KMeans(K=2, Seed=1).Fit(X)
+    assert np.asarray(km.Centroids).shape == (2, 2) and km.Centroids is km.Centers
+    lg = ml.LogisticRegression(MaxIter=200).Fit(X, lab)
+    assert np.asarray(lg.Weights).shape == (2, 2) and np.asarray(lg.Bias).shape == (2,)
+    z = X @ np.asarray(lg.Weights).T + np.asarray(lg.Bias)
+    assert np.array_equal(z.argmax(1), lg.Predict(X))
+    knn = ml.KNNClassifier(K=3).Fit(X, lab)
+    assert np.asarray(knn.Xtrain).shape == (60, 2) and np.asarray(knn.Ytrain).shape == (60,)
+    gm = ml.GaussianMixture(NComponents=2, Seed=0).Fit(X)
+    assert np.asarray(gm.Covariances).shape == (2, 2) and np.isfinite(gm.LogLikelihood)
+    br = ml.BayesianRidge().Fit(x, y)
+    assert br.AlphaPrec > 0 and br.LambdaPrec > 0 and abs(br.Weights[0] - 2.5) < 0.05
+    assert np.asarray(ml.LDA(NComponents=1).Fit(X, lab).Components).shape == (1, 2)
+    assert np.asarray(ml.FastICA(NComponents=2, Seed=0).Fit(X).Components).shape == (2, 2)
+    assert ml.OneHotEncoder().Fit(np.array([2, 0, 1, 2])).Classes.tolist() == [0, 1, 2]
+    with pytest.raises(AttributeError):
+        ml.KMeans(K=2).Centroids                      # nothing fitted yet
