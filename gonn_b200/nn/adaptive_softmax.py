@@ -18,7 +18,7 @@ class AdaptiveLogSoftmaxWithLoss(Module):
         cutoffs = list(cutoffs)
         if cutoffs != sorted(set(cutoffs)) or not cutoffs or cutoffs[0] <= 0 or cutoffs[-1] >= n_classes:
             raise ValueError("AdaptiveLogSoftmaxWithLoss: cutoffs must be unique, increasing, in (0, n_classes)")
-        self.in_features, self.n_classes = in_features, n_classes
+        self.in_features, self.n_classes, self.div_value = in_features, n_classes, div_value
         self.cutoffs = cutoffs + [n_classes]
         self.shortlist = self.cutoffs[0]
         self.n_clusters = len(self.cutoffs) - 1

@@ -39,18 +39,34 @@ class EmbeddingBag(Module):
     ``Forward2D`` takes (bags, bag_len).  Empty or all-padding bags give a zero row."""
 
     def __init__(self, num_embeddings: int, embedding_dim: int, mode: str = "mean",
-                 padding_idx: Optional[int] = None, *, dtype=torch.float32, device=None):
+                 padding_idx: Optional[int] = None, max_norm: Optional[float] = None, norm_type: float = 2.0, *,
+                 dtype=torch.float32, device=None):
         super().__init__()
         if mode not in ("sum", "mean", "max"):
             raise ValueError("nn.EmbeddingBag: mode must be sum, mean or max")
         self.mode, self.padding_idx = mode, padding_idx
+        self.max_norm, self.norm_type = max_norm, norm_type
         self.num_embeddings, self.embedding_dim = num_embeddings, embedding_dim
         w = torch.empty(num_embeddings, embedding_dim, dtype=torch.float32).normal_(0, 1)
         if padding_idx is not None:
             w[padding_idx].zero_()
         self.weight = torch.nn.Parameter(w.to(dtype=dtype, device=device))
 
+    def _renorm(self, idx):
+        """Rows that are looked up and whose norm exceeds ``max_norm`` are rescaled in place, as
+        in ``Embedding`` (nn/embedding.go:90-106)."""
+        if self.max_norm is None:
+            return
+        with torch.no_grad():
+            rows = torch.unique(idx.reshape(-1).long())
+            w = self.weight.data[rows]
+            w = w if w.dtype == torch.float64 else w.float()
+            n = w.norm(self.norm_type, dim=1, keepdim=True)
+            scale = torch.where(n > self.max_norm, self.max_norm / (n + 1e-7), torch.ones_like(n))
+            self.weight.data[rows] = (w * scale).to(self.weight.dtype)
+
     def forward(self, idx, offsets=None):
+        self._renorm(idx)
         if offsets is None:
             return self.Forward2D(idx)
         idx = idx.reshape(-1).long()

@@ -18,6 +18,30 @@ import torch
 from torch import nn as _tnn
 
 
+def _pad_side(dim_from_last: int, side: int):
+    return lambda m: m.pads[len(m.pads) - 1 - dim_from_last][side]
+
+
+# exported field names of the reference's module structs that differ from the attribute here by more
+# than spelling: name -> attribute names (or getters) tried in order
+_FIELD_NAMES = {
+    "Kernel": ("kernel_size", "k"), "Pad": ("padding", "p"), "Stride": ("s",), "Dilation": ("d",),
+    "In1Features": ("in1",), "In2Features": ("in2",), "Dropouts": ("dropout",), "Axis": ("dim",),
+    "EmbDim": ("embed_dim", lambda m: m.attn.embed_dim), "EmbedDim": (lambda m: m.encoder.layers[0].attn.embed_dim,),
+    "NumHeads": (lambda m: m.attn.num_heads, lambda m: m.encoder.layers[0].attn.num_heads),
+    "DimFF": (lambda m: m.ff1.out_features, lambda m: m.linear1.out_features),
+    "NumParams": (lambda m: m.weight.numel(),), "ScaleFactor": ("scale",), "UpscaleFactor": ("r",),
+    "DownscaleFactor": ("r",), "G": ("weight_g",), "V": ("weight_v",), "Weight": ("weight_orig",),
+    "InFeatures": (lambda m: m.EffectiveWeight().shape[1],), "OutFeatures": (lambda m: m.EffectiveWeight().shape[0],),
+    "ShortlistSize": ("shortlist",), "HeadSize": (lambda m: m.shortlist + m.n_clusters,),
+    "HeadBias": (lambda m: m.head.bias is not None,),
+    "OutSize": (lambda m: m.output_size[0],), "OutD": (lambda m: m.output_size[-3],),
+    "OutH": (lambda m: m.output_size[-2],), "OutW": (lambda m: m.output_size[-1],),
+    "Left": (_pad_side(0, 0),), "Right": (_pad_side(0, 1),), "Top": (_pad_side(1, 0),), "Bottom": (_pad_side(1, 1),),
+    "Front": (_pad_side(2, 0),), "Back": (_pad_side(2, 1),),
+}
+
+
 class Module(_tnn.Module):
     """Base class of every layer."""
 
@@ -33,11 +57,11 @@ class Module(_tnn.Module):
         except AttributeError:
             if name[:1].isupper():
                 snake = "".join("_" + c.lower() if c.isupper() and i else c.lower() for i, c in enumerate(name))
-                for alt in (snake, name.lower()):
+                for alt in (snake, name.lower()) + _FIELD_NAMES.get(name, ()):
                     if alt != name:
                         try:
-                            return getattr(self, alt)
-                        except AttributeError:
+                            return alt(self) if callable(alt) else getattr(self, alt)
+                        except (AttributeError, IndexError, TypeError):
                             pass
             raise
 

@@ -395,3 +395,23 @@ def test_estimator_result_fields_under_the_reference_names():
     assert ml.OneHotEncoder().Fit(np.array([2, 0, 1, 2])).Classes.tolist() == [0, 1, 2]
     with pytest.raises(AttributeError):
         ml.KMeans(K=2).Centroids                      # nothing fitted yet
+
+
+def test_module_field_aliases_and_embedding_bag_max_norm():
+    assert nn.Bilinear(3, 4, 5).In1Features == 3 and nn.Unfold(2, stride=2).Kernel == (2, 2)
+    assert nn.AdaptiveAvgPool2d((2, 3)).OutH == 2 and nn.AdaptiveAvgPool2d((2, 3)).OutW == 3
+    p = nn.ReflectionPad2d(1, 2, 3, 4)
+    assert (p.Top, p.Bottom, p.Left, p.Right) == (1, 2, 3, 4)
+    p3 = nn.CircularPad3d(1, 2, 3, 4, 5, 6)
+    assert (p3.Left, p3.Right, p3.Top, p3.Bottom, p3.Front, p3.Back) == (1, 2, 3, 4, 5, 6)
+    wn = nn.WeightNormLinear(nn.Linear(3, 2))
+    assert wn.G is wn.weight_g and wn.V is wn.weight_v and (wn.InFeatures, wn.OutFeatures) == (3, 2)
+    assert nn.Softmax(-1).Axis == -1 and nn.Upsample(3).ScaleFactor == 3 and nn.PixelShuffle(2).UpscaleFactor == 2
+    als = nn.AdaptiveLogSoftmaxWithLoss(8, 12, [4, 8], div_value=2.0)
+    assert (als.ShortlistSize, als.HeadSize, als.DivValue, als.HeadBias) == (4, 6, 2.0, False)
+    torch.manual_seed(0)
+    eb = nn.NewEmbeddingBag(10, 4, nn.WithBagMode("sum"), nn.WithBagMaxNorm(0.5), nn.WithDType(torch.float64))
+    eb(torch.tensor([[1, 2], [3, 3]]))
+    norms = eb.weight.detach().norm(dim=1)
+    assert torch.allclose(norms[1:4], torch.full((3,), 0.5, dtype=torch.float64), atol=1e-6) and norms[5] > 0.5
+    assert eb.MaxNorm == 0.5
