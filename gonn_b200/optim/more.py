@@ -258,6 +258,10 @@ class LBFGS:
         self.s: List[torch.Tensor] = []
         self.y: List[torch.Tensor] = []
 
+    # exported fields of the reference's struct (optim/lbfgs.go:15-30)
+    HistorySize = property(lambda self: self.history, lambda self, v: setattr(self, "history", int(v)))
+    MaxIter = property(lambda self: self.max_iter, lambda self, v: setattr(self, "max_iter", int(v)))
+
     def parameters(self):
         return self.params
 
