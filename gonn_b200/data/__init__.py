@@ -91,6 +91,7 @@ class DataLoader:
         return n // self.BatchSize if self.DropLast else -(-n // self.BatchSize)
 
     Len = __len__           # number of batches per epoch (data/dataloader.go)
+    Dataset = property(lambda self: self.dataset)
 
     def _batches(self):
         n = self.dataset.Len()

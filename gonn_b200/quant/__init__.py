@@ -82,6 +82,11 @@ class QTensorPerChannel:
     def Numel(self) -> int:
         return self.Data.numel()
 
+    @property
+    def ZeroPoints(self):
+        """Per-channel zero points: all zero, the scheme is symmetric (quant/perchannel.go:12-20)."""
+        return [0] * self.Scales.numel()
+
     def Channels(self) -> int:
         """Number of quantisation channels: the size of ``Axis`` (quant/perchannel.go:28-29)."""
         return self.Scales.numel()
@@ -336,6 +341,11 @@ class QATLinear(Module):
         self.linear = linear
         self.weight_fq = FakeQuant(symmetric=True)
         self.input_fq = FakeQuant(symmetric=False)
+
+    # exported fields of the reference's struct (quant/qat.go:170-180)
+    L = property(lambda self: self.linear)
+    WeightFQ = property(lambda self: self.weight_fq)
+    InputFQ = property(lambda self: self.input_fq)
 
     def forward(self, x):
         from ..ops.linear import linear as _linear
