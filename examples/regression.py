@@ -11,7 +11,7 @@ from gonn_b200.data import MakeRegression  # noqa: E402
 
 
 def main(steps: int = 200, device: str = "cpu"):
-    X, y = MakeRegression(256, 8, noise=0.05, seed=1)[:2]
+    X, y = MakeRegression(256, 8, noise=0.05, seed=1)
     X, y = X.to(device), y.to(device).reshape(-1, 1)
     model = nn.Linear(8, 1, dtype=X.dtype, device=device)
     opt = optim.SGD(model.parameters(), lr=0.05)

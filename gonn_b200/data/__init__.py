@@ -279,15 +279,25 @@ def LoadCSV(path: str, has_header: bool = True, target_col: int = -1, dtype=torc
 
 
 # ---- synthetic generators (data/synthetic.go:10-170) ---------------------------------------------
+class _XY(tuple):
+    """``(X, y)`` as the reference returns it (data/synthetic.go:16), with the generating
+    coefficients of a regression problem kept in ``Weights``."""
+    Weights = None
+
+
 def MakeRegression(n: int, d: int, noise: float = 0.1, seed: int = 0):
+    """``X, y = MakeRegression(n, d, noise, seed)``; the true coefficients are ``.Weights`` of
+    the returned pair."""
     r = np.random.default_rng(seed)
     X = r.standard_normal((n, d))
     w = r.standard_normal(d)
     y = X @ w + noise * r.standard_normal(n)
-    return torch.from_numpy(X), torch.from_numpy(y), torch.from_numpy(w)
+    out = _XY((torch.from_numpy(X), torch.from_numpy(y)))
+    out.Weights = torch.from_numpy(w)
+    return out
 
 
-def MakeBlobs(n: int, d: int, centers: int, std: float = 1.0, seed: int = 0):
+def MakeBlobs(n: int, d: int, centers: int, seed: int = 0, *, std: float = 1.0):
     r = np.random.default_rng(seed)
     C = r.uniform(-10, 10, (centers, d))
     y = r.integers(0, centers, n)
@@ -295,7 +305,7 @@ def MakeBlobs(n: int, d: int, centers: int, std: float = 1.0, seed: int = 0):
     return torch.from_numpy(X), torch.from_numpy(y.astype(np.int64))
 
 
-def MakeClassification(n: int, d: int, classes: int = 2, sep: float = 3.0, seed: int = 0):
+def MakeClassification(n: int, d: int, classes: int = 2, seed: int = 0, *, sep: float = 3.0):
     r = np.random.default_rng(seed)
     C = r.standard_normal((classes, d)) * sep
     y = r.integers(0, classes, n)

@@ -7,12 +7,13 @@ from gonn_b200 import ml
 
 
 def _blobs():
-    X, y = D.MakeBlobs(240, 4, 3, 1.0, seed=3)
+    X, y = D.MakeBlobs(240, 4, 3, 3, std=1.0)
     return X.numpy(), y.numpy()
 
 
 def test_regressors_recover_linear_model():
-    X, y, w = D.MakeRegression(300, 5, 0.01, seed=1)
+    xy = D.MakeRegression(300, 5, 0.01, 1)
+    (X, y), w = xy, xy.Weights
     X, y, w = X.numpy(), y.numpy(), w.numpy()
     for m in (ml.LinearRegression(), ml.Ridge(Alpha=1e-3), ml.Lasso(Alpha=1e-4), ml.ElasticNet(Alpha=1e-4),
               ml.BayesianRidge()):

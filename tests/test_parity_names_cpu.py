@@ -415,3 +415,19 @@ def test_module_field_aliases_and_embedding_bag_max_norm():
     norms = eb.weight.detach().norm(dim=1)
     assert torch.allclose(norms[1:4], torch.full((3,), 0.5, dtype=torch.float64), atol=1e-6) and norms[5] > 0.5
     assert eb.MaxNorm == 0.5
+
+
+def test_synthetic_generators_take_the_reference_arguments():
+    X, Y = data.MakeClassification(100, 20, 3, 42)               # samples, features, classes, seed
+    assert X.shape == (100, 20) and set(Y.tolist()) <= {0, 1, 2}
+    X2, _ = data.MakeClassification(100, 20, 3, 42)
+    assert torch.equal(X, X2) and not torch.equal(X, data.MakeClassification(100, 20, 3, 43)[0])
+    Xb, yb = data.MakeBlobs(60, 2, 3, 7)
+    assert Xb.shape == (60, 2) and torch.equal(Xb, data.MakeBlobs(60, 2, 3, seed=7)[0])
+    Xr, yr = data.MakeRegression(50, 4, 0.1, 5)
+    assert Xr.shape == (50, 4) and yr.shape == (50,) and data.MakeRegression(50, 4, 0.1, 5).Weights.shape == (4,)
+    Xm, ym = data.MakeMoons(40, 0.05, 1)
+    assert Xm.shape == (40, 2) and ym.sum() == 20
+    loader = data.NewDataLoader(data.NewTensorDataset(X, Y), 32, True)
+    shapes = [tuple(b.X.shape) for b in loader.Iter()]
+    assert shapes == [(32, 20)] * 3 + [(4, 20)] and loader.Len() == 4
