@@ -133,9 +133,17 @@ def accepting_options(callee: Callable) -> Callable:
     def call(*args, **kwargs):
         opts = [a for a in args if isinstance(a, Option)]
         if opts:
-            args = tuple(a for a in args if not isinstance(a, Option))
+            args = [a for a in args if not isinstance(a, Option)]
+            target = callee.__init__ if inspect.isclass(callee) else callee
+            names = [n for n, p in inspect.signature(target).parameters.items()
+                     if p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD)]
+            if inspect.isclass(callee):
+                names = names[1:]                       # self
             for k, v in resolve(callee, opts).items():
-                kwargs.setdefault(k, v)
+                if k in names and names.index(k) < len(args):
+                    args[names.index(k)] = v            # an option overrides the positional value
+                else:
+                    kwargs.setdefault(k, v)
         return callee(*args, **kwargs)
     call.__wrapped__ = callee
     return call

@@ -431,3 +431,9 @@ def test_synthetic_generators_take_the_reference_arguments():
     loader = data.NewDataLoader(data.NewTensorDataset(X, Y), 32, True)
     shapes = [tuple(b.X.shape) for b in loader.Iter()]
     assert shapes == [(32, 20)] * 3 + [(4, 20)] and loader.Len() == 4
+
+
+def test_option_overrides_the_positional_value():
+    c = nn.NewConv2d(3, 8, 3, nn.WithKernel(3, 5), nn.WithStride(1, 2), nn.WithPad(1, 2))
+    assert c.kernel_size == (3, 5) and c.stride == (1, 2) and c.padding == (1, 2)
+    assert c(torch.randn(1, 3, 8, 8)).shape == (1, 8, 8, 4)
