@@ -14,6 +14,20 @@ weights are random-initialised.
 One step = forward + backward + gradient collective + optimizer update.  The
 timed region is exactly ``--steps`` steps between a barrier + synchronise on both
 sides, measured with CUDA events, maximum over ranks.  Rank 0 prints one JSON line.
+
+Kernel configs (``--config gemm | flash | add``) time one operator on resident buffers
+in both arms with the same shapes, FLOP conventions and iteration counts:
+
+* ``--impl reference`` runs the reference's own CUDA library (its ``gonn_cuda.cu``
+  compiled unchanged into ``baseline/_ref/libgonn_cuda.so``) through its stock C ABI:
+  the in-library loops ``gonn_bench_matmul_f16_dev`` / ``gonn_bench_matmul_dev``,
+  ``gonn_bench_flash_attn_f64`` and ``gonn_bench_add_dev`` for the device-timed value, and
+  the host-pointer entry points ``gonn_gemm`` / ``gonn_flash_attn_f64_fwd`` + ``_bwd`` /
+  ``gonn_binary`` (upload, kernel, download per call) for the end-to-end value.
+* ``--impl ours`` runs the same work through ``gonn_b200.cuda`` and ``gonn_b200.backend``.
+
+The reference has no GPU training path, so for the training configs (``lm``, ``gpt``,
+``cnn``) its arm prints an ``unavailable`` line.
 """
 from __future__ import annotations
 
@@ -32,9 +46,10 @@ def parse():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="lm", choices=["lm", "gpt", "cnn"])
+    ap.add_argument("--config", default="lm", choices=["lm", "gpt", "cnn", "gemm", "flash", "add"])
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (0 = the config's value)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--quick", action="store_true", help="kernel configs: headline shape only, no sweep")
     return ap.parse_args()
 
 
@@ -48,14 +63,29 @@ CONFIGS = {
 }
 
 
+KERNEL_CONFIGS = ("gemm", "flash", "add")
+
+
+def kernel_config(args):
+    """One operator on one GPU, either arm (baseline/kernel_bench.py)."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return 0                         # kernel configs are single-GPU: extra ranks have nothing to do
+    from baseline import kernel_bench as kb
+    run = kb.run_reference if args.impl == "reference" else kb.run_ours
+    print(json.dumps(run(args.config, args.steps, args.warmup, args.quick)))
+    return 0
+
+
 def reference_arm(args):
     # The reference is a Go module.  An offline `pip install --target baseline/_ref` of its
     # source tree stops with "Neither 'setup.py' nor 'pyproject.toml' found", no Go toolchain
     # or module cache exists offline, and the reference has no GPU training path and publishes
-    # no training-throughput number: this metric cannot be produced by it here.
+    # no training-throughput number: this metric cannot be produced by it here.  Its CUDA
+    # library does build and runs under --config gemm | flash | add.
     print(json.dumps({"impl": "reference",
                       "unavailable": "reference is a Go module (not pip-installable, no Go toolchain "
-                                     "offline) and has no GPU training path for tokens/s"}))
+                                     "offline) and has no GPU training path for tokens/s; its CUDA library "
+                                     "runs under --config gemm|flash|add"}))
     return 0
 
 
@@ -78,6 +108,8 @@ def build(cfg_name, device, dtype, batch, world=1):
 
 def main():
     args = parse()
+    if args.config in KERNEL_CONFIGS:
+        return kernel_config(args)
     if args.impl == "reference":
         return reference_arm(args)
 
@@ -107,11 +139,13 @@ def main():
 
     # set-up, not a step: about 0.3 s of dense work brings the GPU out of its idle power state,
     # so that the first warm-up steps do not run at ramping clocks
+    from gonn_b200.ops.gemm import gemm as own_gemm
     spin = torch.randn(8192, 8192, device=device, dtype=torch.bfloat16)
+    spin_out = torch.empty_like(spin)
     for _ in range(300):
-        torch.matmul(spin, spin)
+        own_gemm(spin, spin, out=spin_out)
     torch.cuda.synchronize()
-    del spin
+    del spin, spin_out
 
     cfg = CONFIGS[args.config]
     B = args.batch or cfg["batch"]
@@ -156,7 +190,7 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    for _ in range(max(args.warmup, 3) if args.warmup >= 3 else args.warmup):
+    for _ in range(args.warmup):
         train_step(dev_x, dev_y)
     torch.cuda.synchronize()
     gl.assert_status_ok()

@@ -11,6 +11,12 @@ Gradient sinks: when a parameter carries a ``_gb_sink`` attribute (installed by
 the data-parallel wrappers), its gradient is written straight into the sink's
 flat bucket (overwrite on the first write of a step, accumulate afterwards) and
 ``None`` is returned to autograd, so no separate accumulation pass runs.
+
+Ordering rule for every op that uses a sink: ``sink.ready(p)`` may launch the bucket's
+fused optimizer step on another stream, which rewrites ``p`` in place.  An op must
+therefore issue every kernel that reads ``p`` (the data-gradient GEMM reads the weight)
+before it calls ``emit_*`` for ``p``; the sink orders its launch after the kernels
+already issued on the compute stream.
 """
 from __future__ import annotations
 
@@ -144,13 +150,14 @@ class _FeedForward(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dres = dy if ctx.has_res else None
-        # second layer: weight / bias gradients from dy, data gradient with act' folded in
+        # every read of a weight comes before its gradient is declared ready (module docstring):
+        # second layer's data gradient (act' folded in) first, then its weight / bias gradients
+        dpre = gemm(dy2, w2, aux=pre, aux_mode=_DACT_MODE[ctx.act])
         dw2 = emit_weight_grad(w2, dy2, h, True, False) if ctx.needs_input_grad[3] else None
         db2 = emit_vector_grad(ctx.b2, dy2) if (ctx.b2 is not None and ctx.needs_input_grad[4]) else None
-        dpre = gemm(dy2, w2, aux=pre, aux_mode=_DACT_MODE[ctx.act])
+        dx = gemm(dpre, w1).reshape(ctx.xshape) if ctx.needs_input_grad[0] else None
         dw1 = emit_weight_grad(w1, dpre, x2, True, False) if ctx.needs_input_grad[1] else None
         db1 = emit_vector_grad(ctx.b1, dpre) if (ctx.b1 is not None and ctx.needs_input_grad[2]) else None
-        dx = gemm(dpre, w1).reshape(ctx.xshape) if ctx.needs_input_grad[0] else None
         return dx, dw1, db1, dw2, db2, None, dres
 
 
