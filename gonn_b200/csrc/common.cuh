@@ -25,6 +25,7 @@ enum StatusCode : int {
   ST_COMM_TIMEOUT = 3,
   ST_CONV_TIMEOUT = 4,
   ST_BAD_INDEX = 5,
+  ST_NORM_TIMEOUT = 6,
 };
 
 // The status word is four ints in device memory owned by runtime.cu:

@@ -302,25 +302,28 @@ norm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TW* __r
   }
 }
 
-// dgamma[c] = sum_p part[p][0][c], dbeta[c] = sum_p part[p][1][c]: CTA of 32 columns
-// x 32 row lanes, fixed summation order.
-template <typename TW>
-__global__ void norm_param_reduce_kernel(const float* __restrict__ part, int P, int D,
-                                         TW* __restrict__ dgamma, TW* __restrict__ dbeta) {
+// dgamma[c] = sum_p part[p][0][c], dbeta[c] = sum_p part[p][1][c] (and dsum[c] from
+// part[p][2][c] when NP == 3): CTA of 32 columns x 32 row lanes, fixed summation order.
+template <typename TW, typename TS>
+__global__ void norm_param_reduce_kernel(const float* __restrict__ part, int P, int D, int NP,
+                                         TW* __restrict__ dgamma, TW* __restrict__ dbeta,
+                                         TS* __restrict__ dsum, int dsum_accumulate) {
   __shared__ float sm[32][33];
   const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  if (c < 2 * D)
-    for (int p = threadIdx.y; p < P; p += 32) s += part[(long long)p * 2 * D + c];
+  if (c < NP * D)
+    for (int p = threadIdx.y; p < P; p += 32) s += part[(long long)p * NP * D + c];
   sm[threadIdx.y][threadIdx.x] = s;
   __syncthreads();
-  if (threadIdx.y == 0 && c < 2 * D) {
+  if (threadIdx.y == 0 && c < NP * D) {
 #pragma unroll
     for (int k = 1; k < 32; k++) s += sm[k][threadIdx.x];
     if (c < D) {
       if (dgamma) dgamma[c] = (TW)s;
-    } else if (dbeta) {
-      dbeta[c - D] = (TW)s;
+    } else if (c < 2 * D) {
+      if (dbeta) dbeta[c - D] = (TW)s;
+    } else if (dsum) {
+      dsum[c - 2 * D] = dsum_accumulate ? (TS)((float)dsum[c - 2 * D] + s) : (TS)s;
     }
   }
 }
@@ -395,6 +398,415 @@ __global__ void norm_param_generic(const T* __restrict__ x, const T* __restrict_
   if (dbeta) dbeta[c] = (TW)b;
 }
 
+// ---------------------------------------------------------------------------
+// Pipelined kernels (the fast path): a producer warp streams tiles of whole rows
+// into a ring of shared-memory stages with bulk asynchronous copies (rows of a
+// contiguous matrix are one contiguous byte range, so no tensor map is needed),
+// 256 consumer threads take rows out of the ring.  Memory-level parallelism is
+// set by the ring (stages x tile bytes in flight per CTA), not by the number of
+// resident warps.  A group of G consumer threads owns one row (G = 32 .. 256 by
+// row width); thread t of the group keeps vectors t, t+G, ... packed in registers.
+// ---------------------------------------------------------------------------
+constexpr int kPipeConsumers = 256;
+constexpr int kPipeThreads = kPipeConsumers + 32;
+constexpr int kPipeMaxStages = 8;
+constexpr int kPipeHeader = 1024;  // barriers, abort flag, reduction slots
+
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst)),
+      "l"((uint64_t)src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+struct PipeSmem {
+  uint64_t full[kPipeMaxStages];
+  uint64_t empty[kPipeMaxStages];
+  int abort_flag;
+  int pad[3];
+  float2 red[2][4][8];  // [flip][group][warp in group]; groups of one warp need no slot
+};
+static_assert(sizeof(PipeSmem) <= kPipeHeader, "header too small");
+
+// Sum of a pair over the G threads of a group, same value in every thread, fixed order.
+template <int G>
+__device__ __forceinline__ float2 group_sum2(float2 v, PipeSmem* ps, int g, int& flip) {
+  v.x = warp_sum(v.x);
+  v.y = warp_sum(v.y);
+  if (G == 32) return v;
+  constexpr int NW = G / 32;
+  const int wig = (threadIdx.x % G) >> 5;
+  float2* slot = ps->red[flip][g];
+  if ((threadIdx.x & 31) == 0) slot[wig] = v;
+  named_bar_sync(1 + g, G);
+  float2 r = make_float2(0.f, 0.f);
+#pragma unroll
+  for (int j = 0; j < NW; j++) { r.x += slot[j].x; r.y += slot[j].y; }
+  flip ^= 1;  // the other slot set next time: no second barrier needed before reuse
+  return r;
+}
+
+// V consecutive weights starting at vector vi, widened to fp32 (vector loads from shared memory)
+template <typename TW, int V>
+__device__ __forceinline__ void load_wvec(const TW* sw, int vi, float* f) {
+  if constexpr (sizeof(TW) == 2) {
+    static_assert(V == 8, "16-bit weights come with 16-bit rows");
+    IO<TW>::unpack(*reinterpret_cast<const uint4*>(sw + vi * 8), f);
+  } else {
+#pragma unroll
+    for (int j = 0; j < V; j += 4) {
+      const float4 u = *reinterpret_cast<const float4*>(sw + vi * V + j);
+      f[j] = u.x; f[j + 1] = u.y; f[j + 2] = u.z; f[j + 3] = u.w;
+    }
+  }
+}
+
+// Producer loop shared by forward and backward: `nsrc` source matrices per stage.
+template <int NSRC>
+__device__ __forceinline__ void pipe_produce(PipeSmem* ps, unsigned char* stages, size_t stage_bytes,
+                                             size_t src_bytes_per_tile, const unsigned char* s0,
+                                             const unsigned char* s1, const unsigned char* s2, long long rows, int R,
+                                             size_t row_bytes, int S, int* status) {
+  const long long ntiles = (rows + R - 1) / R;
+  int it = 0;
+  for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, it++) {
+    const int s = it % S;
+    const uint32_t ph = (uint32_t)(it / S) & 1u;
+    if (!mbar_wait(&ps->empty[s], ph ^ 1u, &ps->abort_flag, status, ST_NORM_TIMEOUT, 10 + s)) return;
+    const long long r0 = tile * R;
+    const long long nr = (rows - r0 < R) ? (rows - r0) : R;
+    const uint32_t bytes = (uint32_t)(nr * row_bytes);
+    mbar_expect_tx(&ps->full[s], bytes * NSRC);
+    unsigned char* dst = stages + (size_t)s * stage_bytes;
+    bulk_load(dst, s0 + (size_t)r0 * row_bytes, bytes, &ps->full[s]);
+    if (NSRC >= 2) bulk_load(dst + src_bytes_per_tile, s1 + (size_t)r0 * row_bytes, bytes, &ps->full[s]);
+    if (NSRC >= 3) bulk_load(dst + 2 * src_bytes_per_tile, s2 + (size_t)r0 * row_bytes, bytes, &ps->full[s]);
+  }
+}
+
+template <typename T, typename TW, int G, int VPT, bool RMS>
+__global__ void __launch_bounds__(kPipeThreads, 2)
+norm_fwd_pipe_kernel(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b,
+                     T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                     long long rows, int D, float eps, int KR, int S, int* status) {
+  constexpr int V = IO<T>::V;
+  constexpr int NG = kPipeConsumers / G;
+  using Raw = typename IO<T>::Raw;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  PipeSmem* ps = reinterpret_cast<PipeSmem*>(smem_raw);
+  const int R = NG * KR;
+  const size_t row_bytes = (size_t)D * sizeof(T);
+  const size_t stage_bytes = (size_t)R * row_bytes;
+  unsigned char* stages = smem_raw + kPipeHeader;
+  TW* sw = reinterpret_cast<TW*>(stages + (size_t)S * stage_bytes);
+  TW* sb = sw + D;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; s++) { mbar_init(&ps->full[s], 1); mbar_init(&ps->empty[s], kPipeConsumers / 32); }
+    ps->abort_flag = 0;
+    mbar_fence_init();
+  }
+  for (int i = threadIdx.x; i < D; i += kPipeThreads) {
+    sw[i] = w ? w[i] : (TW)1.f;
+    sb[i] = (!RMS && b) ? b[i] : (TW)0.f;
+  }
+  __syncthreads();
+  if (threadIdx.x >= kPipeConsumers) {
+    if (threadIdx.x == kPipeConsumers)
+      pipe_produce<1>(ps, stages, stage_bytes, 0, (const unsigned char*)x, nullptr, nullptr, rows, R, row_bytes, S,
+                      status);
+    return;
+  }
+  const int g = threadIdx.x / G, t = threadIdx.x % G;
+  const int nvec = D / V;
+  const long long ntiles = (rows + R - 1) / R;
+  int flip = 0, it = 0;
+  for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, it++) {
+    const int s = it % S;
+    const uint32_t ph = (uint32_t)(it / S) & 1u;
+    if (!mbar_wait(&ps->full[s], ph, &ps->abort_flag, status, ST_NORM_TIMEOUT, s)) return;
+    const unsigned char* st = stages + (size_t)s * stage_bytes;
+    for (int kk = 0; kk < KR; kk++) {
+      const int r = kk * NG + g;
+      const long long row = tile * R + r;
+      const bool live = row < rows;  // uniform over the group
+      Raw xr[VPT];
+      if (live) {
+#pragma unroll
+        for (int i = 0; i < VPT; i++) {
+          const int vi = t + i * G;
+          if (vi < nvec) xr[i] = *reinterpret_cast<const Raw*>(st + (size_t)r * row_bytes + (size_t)vi * sizeof(Raw));
+        }
+      }
+      if (kk == KR - 1) {  // every row of the stage is in registers: hand the stage back
+        __syncwarp();
+        if ((threadIdx.x & 31) == 0) mbar_arrive(&ps->empty[s]);
+      }
+      if (!live) continue;
+      float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < VPT; i++) {
+        if (t + i * G < nvec) {
+          float f[V];
+          IO<T>::unpack(xr[i], f);
+#pragma unroll
+          for (int j = 0; j < V; j++) { acc.x += f[j]; acc.y += f[j] * f[j]; }
+        }
+      }
+      float mean = 0.f, rstd;
+      if (RMS) {
+        acc = group_sum2<G>(acc, ps, g, flip);
+        rstd = rsqrtf(acc.y / D + eps);
+      } else {
+        acc = group_sum2<G>(acc, ps, g, flip);
+        mean = acc.x / D;
+        float2 q = make_float2(0.f, 0.f);  // variance from centred values
+#pragma unroll
+        for (int i = 0; i < VPT; i++) {
+          if (t + i * G < nvec) {
+            float f[V];
+            IO<T>::unpack(xr[i], f);
+#pragma unroll
+            for (int j = 0; j < V; j++) { const float d = f[j] - mean; q.x += d * d; }
+          }
+        }
+        q = group_sum2<G>(q, ps, g, flip);
+        rstd = rsqrtf(q.x / D + eps);
+      }
+      if (t == 0) {
+        if (mean_out) mean_out[row] = mean;
+        rstd_out[row] = rstd;
+      }
+      T* yr = y + row * D;
+      const float shift = -mean * rstd;
+#pragma unroll
+      for (int i = 0; i < VPT; i++) {
+        const int vi = t + i * G;
+        if (vi < nvec) {
+          float f[V], wv[V], bv[V], o[V];
+          IO<T>::unpack(xr[i], f);
+          load_wvec<TW, V>(sw, vi, wv);
+          load_wvec<TW, V>(sb, vi, bv);
+#pragma unroll
+          for (int j = 0; j < V; j++) o[j] = fmaf(fmaf(f[j], rstd, shift), wv[j], bv[j]);
+          IO<T>::st(yr + vi * V, o);
+        }
+      }
+    }
+  }
+}
+
+// Backward: dx per row; dgamma / dbeta accumulate per thread over the rows its group
+// visits, are combined over the groups of the CTA through shared memory in group order and
+// written to part[blockIdx.x][2][D]; norm_param_reduce_kernel adds the CTAs in index order.
+// RES: a third stream `dres` (the gradient that bypassed the norm through a residual
+// connection) is added to dx, and its column sums go to part[..][2][D]: they are the bias
+// gradient of the linear layer whose output was added to the residual stream after this norm.
+template <typename T, typename TW, int G, int VPT, bool RMS, bool RES>
+__global__ void __launch_bounds__(kPipeThreads, 2)
+norm_bwd_pipe_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T* __restrict__ dres,
+                     const TW* __restrict__ w, const float* __restrict__ mean_in,
+                     const float* __restrict__ rstd_in, T* __restrict__ dx, float* __restrict__ part,
+                     long long rows, int D, int KR, int S, int* status) {
+  constexpr int NP = RES ? 3 : 2;  // partial rows per CTA: dgamma, dbeta (, column sums of dres)
+  constexpr int V = IO<T>::V;
+  constexpr int NG = kPipeConsumers / G;
+  using Raw = typename IO<T>::Raw;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  PipeSmem* ps = reinterpret_cast<PipeSmem*>(smem_raw);
+  const int R = NG * KR;
+  const size_t row_bytes = (size_t)D * sizeof(T);
+  const size_t half_bytes = (size_t)R * row_bytes;
+  const size_t stage_bytes = NP * half_bytes;
+  unsigned char* stages = smem_raw + kPipeHeader;
+  TW* sw = reinterpret_cast<TW*>(stages + (size_t)S * stage_bytes);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; s++) { mbar_init(&ps->full[s], 1); mbar_init(&ps->empty[s], kPipeConsumers / 32); }
+    ps->abort_flag = 0;
+    mbar_fence_init();
+  }
+  for (int i = threadIdx.x; i < D; i += kPipeThreads) sw[i] = w ? w[i] : (TW)1.f;
+  __syncthreads();
+  const bool producer = threadIdx.x >= kPipeConsumers;
+  if (threadIdx.x == kPipeConsumers)
+    pipe_produce<NP>(ps, stages, stage_bytes, half_bytes, (const unsigned char*)x, (const unsigned char*)dy,
+                     (const unsigned char*)dres, rows, R, row_bytes, S, status);
+  const int g = threadIdx.x / G, t = threadIdx.x % G;
+  const int nvec = D / V;
+  float dg[VPT][V], db[VPT][V], ds[RES ? VPT : 1][V];
+#pragma unroll
+  for (int i = 0; i < VPT; i++)
+#pragma unroll
+    for (int j = 0; j < V; j++) { dg[i][j] = 0.f; db[i][j] = 0.f; if (RES) ds[i][j] = 0.f; }
+  if (!producer) {
+    const long long ntiles = (rows + R - 1) / R;
+    int flip = 0, it = 0;
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, it++) {
+      const int s = it % S;
+      const uint32_t ph = (uint32_t)(it / S) & 1u;
+      // the row statistics of this tile's first row are fetched before the wait
+      const long long row_first = tile * R + g;
+      float mean_n = 0.f, rstd_n = 0.f;
+      if (row_first < rows) { mean_n = RMS ? 0.f : mean_in[row_first]; rstd_n = rstd_in[row_first]; }
+      if (!mbar_wait(&ps->full[s], ph, &ps->abort_flag, status, ST_NORM_TIMEOUT, 20 + s)) break;
+      const unsigned char* st = stages + (size_t)s * stage_bytes;
+      for (int kk = 0; kk < KR; kk++) {
+        const int r = kk * NG + g;
+        const long long row = tile * R + r;
+        const bool live = row < rows;
+        Raw xr[VPT], dr[VPT], rr[RES ? VPT : 1];
+        if (live) {
+#pragma unroll
+          for (int i = 0; i < VPT; i++) {
+            const int vi = t + i * G;
+            if (vi < nvec) {
+              const unsigned char* src = st + (size_t)r * row_bytes + (size_t)vi * sizeof(Raw);
+              xr[i] = *reinterpret_cast<const Raw*>(src);
+              dr[i] = *reinterpret_cast<const Raw*>(src + half_bytes);
+              if (RES) rr[i] = *reinterpret_cast<const Raw*>(src + 2 * half_bytes);
+            }
+          }
+        }
+        if (kk == KR - 1) {
+          __syncwarp();
+          if ((threadIdx.x & 31) == 0) mbar_arrive(&ps->empty[s]);
+        }
+        const float mean = mean_n, rstd = rstd_n;
+        const long long row_next = row + NG;
+        if (kk + 1 < KR && row_next < rows) { mean_n = RMS ? 0.f : mean_in[row_next]; rstd_n = rstd_in[row_next]; }
+        if (!live) continue;
+        const float shift = -mean * rstd;
+        float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < VPT; i++) {
+          const int vi = t + i * G;
+          if (vi < nvec) {
+            float a[V], d[V], wv[V];
+            IO<T>::unpack(xr[i], a);
+            IO<T>::unpack(dr[i], d);
+            load_wvec<TW, V>(sw, vi, wv);
+#pragma unroll
+            for (int j = 0; j < V; j++) {
+              const float h = fmaf(a[j], rstd, shift);
+              const float gw = d[j] * wv[j];
+              acc.x += gw;
+              acc.y = fmaf(gw, h, acc.y);
+              dg[i][j] = fmaf(d[j], h, dg[i][j]);
+              db[i][j] += d[j];
+            }
+          }
+        }
+        acc = group_sum2<G>(acc, ps, g, flip);
+        const float m1 = RMS ? 0.f : acc.x / D, m2 = acc.y / D;
+#pragma unroll
+        for (int i = 0; i < VPT; i++) {
+          const int vi = t + i * G;
+          if (vi < nvec) {
+            float a[V], d[V], wv[V], o[V];
+            IO<T>::unpack(xr[i], a);
+            IO<T>::unpack(dr[i], d);
+            load_wvec<TW, V>(sw, vi, wv);
+#pragma unroll
+            for (int j = 0; j < V; j++) {
+              const float h = fmaf(a[j], rstd, shift);
+              o[j] = rstd * (fmaf(d[j], wv[j], -m1) - h * m2);
+            }
+            if (RES) {
+              float e[V];
+              IO<T>::unpack(rr[i], e);
+#pragma unroll
+              for (int j = 0; j < V; j++) { o[j] += e[j]; ds[i][j] += e[j]; }
+            }
+            IO<T>::st(dx + row * D + vi * V, o);
+          }
+        }
+      }
+    }
+  }
+  if (part == nullptr) return;
+  // every tile this CTA was given has been consumed (or the CTA is unwinding after a
+  // time-out, in which case the status word already says so): the ring is free for reuse
+  __syncthreads();
+  float* comb = reinterpret_cast<float*>(stages);  // [NG][NP][D]
+  if (!producer) {
+#pragma unroll
+    for (int i = 0; i < VPT; i++) {
+      const int vi = t + i * G;
+      if (vi < nvec) {
+#pragma unroll
+        for (int j = 0; j < V; j++) {
+          comb[((size_t)g * NP + 0) * D + vi * V + j] = dg[i][j];
+          comb[((size_t)g * NP + 1) * D + vi * V + j] = db[i][j];
+          if (RES) comb[((size_t)g * NP + 2) * D + vi * V + j] = ds[i][j];
+        }
+      }
+    }
+  }
+  __syncthreads();
+  float* out = part + (long long)blockIdx.x * NP * D;
+  for (int c = threadIdx.x; c < NP * D; c += kPipeThreads) {
+    float sacc = 0.f;
+#pragma unroll
+    for (int gg = 0; gg < NG; gg++) sacc += comb[(size_t)gg * NP * D + c];
+    out[c] = sacc;
+  }
+}
+
+// Geometry of the pipelined kernels for a row of `row_bytes`: rows per group per tile
+// (tiles of about 12 KB per source), ring depth within `budget` bytes of shared memory.
+struct PipePlan { int KR, S; size_t smem; bool ok; };
+inline PipePlan pipe_plan(size_t row_bytes, int NG, int nsrc, size_t extra_bytes, size_t comb_bytes) {
+  PipePlan p;
+  size_t tile = (size_t)NG * row_bytes;
+  p.KR = 1;
+  while ((size_t)(p.KR * 2) * tile <= 12288) p.KR *= 2;
+  const size_t stage = (size_t)p.KR * tile * nsrc;
+  const size_t budget = 96 * 1024;
+  int S = (int)(budget / stage);
+  if (S > kPipeMaxStages) S = kPipeMaxStages;
+  while (S >= 2 && (size_t)S * stage < comb_bytes) S++;  // the combine buffer reuses the ring
+  p.S = S;
+  p.smem = kPipeHeader + (size_t)S * stage + extra_bytes;
+  p.ok = S >= 2 && S <= kPipeMaxStages && p.smem <= 110 * 1024;
+  return p;
+}
+
+// (threads per row, vectors per thread) by row width in 16-byte vectors.  The backward keeps
+// 16 fp32 accumulators per vector in registers, so it spreads a row over more threads.
+#define GB_PIPE_DISPATCH(X)      \
+  if (nvec <= 32) X(32, 1)       \
+  else if (nvec <= 64) X(32, 2)  \
+  else if (nvec <= 96) X(32, 3)  \
+  else if (nvec <= 128) X(64, 2) \
+  else if (nvec <= 192) X(64, 3) \
+  else if (nvec <= 256) X(128, 2)\
+  else if (nvec <= 384) X(128, 3)\
+  else if (nvec <= 512) X(256, 2)\
+  else if (nvec <= 768) X(256, 3)\
+  else X(256, 4)
+#define GB_PIPE_DISPATCH_BWD(X)  \
+  if (nvec <= 32) X(32, 1)       \
+  else if (nvec <= 64) X(32, 2)  \
+  else if (nvec <= 128) X(64, 2) \
+  else if (nvec <= 256) X(128, 2)\
+  else if (nvec <= 512) X(256, 2)\
+  else if (nvec <= 768) X(256, 3)\
+  else X(256, 4)
+
+#define GB_PIPE_DISPATCH_RES(X)  \
+  if (nvec <= 32) X(32, 1)       \
+  else if (nvec <= 64) X(64, 1)  \
+  else if (nvec <= 128) X(128, 1)\
+  else if (nvec <= 256) X(256, 1)\
+  else if (nvec <= 512) X(256, 2)\
+  else if (nvec <= 768) X(256, 3)\
+  else X(256, 4)
+
+bool g_norm_pipe = true;  // gb_norm_tune: 0 selects the register-resident kernels without the ring
+
 int pick_grid(long long rows, int gpb, int per_sm = 2) {
   long long need = (rows + gpb - 1) / gpb;
   long long cap = 148 * per_sm;
@@ -407,6 +819,32 @@ int norm_fwd_t(const void* x, const void* w, const void* b, void* y, float* mean
   constexpr int V = IO<T>::V;
   const bool aligned = (D % V == 0) && ((((uintptr_t)x | (uintptr_t)y) & 15) == 0);
   const int nvec = D / V;
+  if (aligned && nvec <= 1024 && g_norm_pipe) {
+    int rc = 1;
+#define GB_FWDP(G, VPT)                                                                                  \
+    {                                                                                                    \
+      PipePlan pl = pipe_plan((size_t)D * sizeof(T), kPipeConsumers / G, 1, 2 * (size_t)D * sizeof(TW), 0); \
+      if (pl.ok) {                                                                                       \
+        auto kern = norm_fwd_pipe_kernel<T, TW, G, VPT, RMS>;                                            \
+        static bool attr_set = false;                                                                    \
+        if (!attr_set) {                                                                                 \
+          GB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024)); \
+          attr_set = true;                                                                               \
+        }                                                                                                \
+        const long long ntiles = (rows + (kPipeConsumers / G) * pl.KR - 1) / ((kPipeConsumers / G) * pl.KR); \
+        const int grid = (int)(ntiles < 296 ? ntiles : 296);                                             \
+        kern<<<grid, kPipeThreads, pl.smem, s>>>((const T*)x, (const TW*)w, (const TW*)b, (T*)y, mean, rstd, \
+                                                 rows, D, eps, pl.KR, pl.S, gbh::status_ptr());          \
+        rc = 0;                                                                                          \
+      }                                                                                                  \
+    }
+    GB_PIPE_DISPATCH(GB_FWDP)
+#undef GB_FWDP
+    if (rc == 0) {
+      GB_CUDA_OK(cudaGetLastError());
+      return gbh::E_OK;
+    }
+  }
 #define GB_FWD(G, VPT)                                                                           \
   norm_fwd_kernel<T, TW, G, VPT, RMS><<<pick_grid(rows, 256 / G, 4), 256, 0, s>>>(               \
       (const T*)x, (const TW*)w, (const TW*)b, (T*)y, mean, rstd, rows, D, eps)
@@ -422,6 +860,49 @@ int norm_fwd_t(const void* x, const void* w, const void* b, void* y, float* mean
                                                                (const TW*)b, (T*)y, mean, rstd, D, eps);
 #undef GB_FWD
   GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}
+
+// Launches the pipelined backward; returns 1 when no plan fits (the caller falls back).
+template <typename T, typename TW, typename TS, bool RMS, bool RES>
+int norm_bwd_pipe_launch(const void* x, const void* dy, const void* dres, const void* w, const float* mean,
+                         const float* rstd, void* dx, void* dgamma, void* dbeta, void* dsum, int dsum_acc,
+                         float* part, int part_rows, long long rows, int D, cudaStream_t s) {
+  constexpr int V = IO<T>::V;
+  constexpr int NP = RES ? 3 : 2;
+  const int nvec = D / V;
+  const bool want_param = dgamma != nullptr || dbeta != nullptr || (RES && dsum != nullptr);
+  int grid = 0, rc = 1;
+#define GB_BWDP(G, VPT)                                                                                  \
+    {                                                                                                    \
+      constexpr int NGc = kPipeConsumers / G;                                                            \
+      PipePlan pl = pipe_plan((size_t)D * sizeof(T), NGc, NP, (size_t)D * sizeof(TW),                    \
+                              want_param ? (size_t)NGc * NP * D * sizeof(float) : 0);                    \
+      if (pl.ok) {                                                                                       \
+        auto kern = norm_bwd_pipe_kernel<T, TW, G, VPT, RMS, RES>;                                       \
+        static bool attr_set = false;                                                                    \
+        if (!attr_set) {                                                                                 \
+          GB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024)); \
+          attr_set = true;                                                                               \
+        }                                                                                                \
+        const long long ntiles = (rows + NGc * pl.KR - 1) / (NGc * pl.KR);                               \
+        grid = (int)(ntiles < 296 ? ntiles : 296);                                                       \
+        if (want_param && grid > part_rows) grid = part_rows;                                            \
+        kern<<<grid, kPipeThreads, pl.smem, s>>>((const T*)x, (const T*)dy, (const T*)dres, (const TW*)w, mean, \
+                                                 rstd, (T*)dx, want_param ? part : nullptr, rows, D, pl.KR, \
+                                                 pl.S, gbh::status_ptr());                               \
+        rc = 0;                                                                                          \
+      }                                                                                                  \
+    }
+  if (RES) { GB_PIPE_DISPATCH_RES(GB_BWDP) } else { GB_PIPE_DISPATCH_BWD(GB_BWDP) }
+#undef GB_BWDP
+  if (rc != 0) return 1;
+  GB_CUDA_OK(cudaGetLastError());
+  if (want_param) {
+    norm_param_reduce_kernel<TW, TS><<<(NP * D + 31) / 32, dim3(32, 32), 0, s>>>(
+        part, grid, D, NP, (TW*)dgamma, (TW*)dbeta, (TS*)dsum, dsum_acc);
+    GB_CUDA_OK(cudaGetLastError());
+  }
   return gbh::E_OK;
 }
 
@@ -443,6 +924,11 @@ int norm_bwd_t(const void* x, const void* dy, const void* w, const float* mean, 
     return gbh::E_OK;
   }
   int grid = 0;
+  if (g_norm_pipe && !(want_param && (part == nullptr || part_rows < 1))) {
+    const int rc = norm_bwd_pipe_launch<T, TW, float, RMS, false>(x, dy, nullptr, w, mean, rstd, dx, dgamma, dbeta,
+                                                                  nullptr, 0, part, part_rows, rows, D, s);
+    if (rc <= 0) return rc;
+  }
 #define GB_BWD(G, VPT)                                                                           \
   {                                                                                              \
     grid = pick_grid(rows, 256 / G);                                                             \
@@ -466,8 +952,8 @@ int norm_bwd_t(const void* x, const void* dy, const void* w, const float* mean, 
 #undef GB_BWD
   GB_CUDA_OK(cudaGetLastError());
   if (want_param) {
-    norm_param_reduce_kernel<TW><<<(2 * D + 31) / 32, dim3(32, 32), 0, s>>>(part, grid, D, (TW*)dgamma,
-                                                                           (TW*)dbeta);
+    norm_param_reduce_kernel<TW, float><<<(2 * D + 31) / 32, dim3(32, 32), 0, s>>>(
+        part, grid, D, 2, (TW*)dgamma, (TW*)dbeta, (float*)nullptr, 0);
     GB_CUDA_OK(cudaGetLastError());
   }
   return gbh::E_OK;
@@ -480,6 +966,13 @@ enum { DT_BF16 = 0, DT_F16 = 1, DT_F32 = 2 };
 // Maximum number of partial rows the backward may use; scratch must hold
 // gb_norm_bwd_scratch_rows() * 2 * D floats.
 GB_EXPORT int gb_norm_bwd_scratch_rows() { return 148 * 2; }
+
+// pipelined = 1 (default): rows stream through a shared-memory ring filled by bulk copies;
+// 0: every warp loads its own rows (kept for comparison and as the fallback).
+GB_EXPORT int gb_norm_tune(int pipelined) {
+  g_norm_pipe = pipelined != 0;
+  return gbh::E_OK;
+}
 
 // kind: 0 = LayerNorm, 1 = RMSNorm.  dtype of x / y; wdtype of weight / bias
 // (the same as dtype, or fp32).  mean may be null for RMSNorm.
@@ -522,6 +1015,53 @@ GB_EXPORT int gb_norm_bwd(int kind, int dtype, int wdtype, const void* x, const 
 #undef GB_N
   gbh::set_error("gb_norm_bwd: unsupported dtype pair %d/%d", dtype, wdtype);
   return gbh::E_BAD_ARG;
+}
+
+// Backward of "norm with a residual bypass": y = norm(x) and x itself both feed later layers,
+// so the gradient of x is norm_bwd(dy) + dres.  One pass produces dx = norm_bwd(dy) + dres,
+// dgamma / dbeta, and dsum = column sums of dres (written, or added when dsum_accumulate, in
+// the input dtype, or fp32 when dsum_f32).  Needs rows of whole 16-byte vectors, at most 1024
+// of them, 16-byte aligned pointers, and scratch of scratch_rows * 3 * D floats; returns
+// E_BAD_ARG otherwise (callers then run the three steps separately).
+GB_EXPORT int gb_norm_bwd_res(int kind, int dtype, int wdtype, const void* x, const void* dy,
+                              const void* dres, const void* w, const float* mean, const float* rstd,
+                              void* dx, void* dgamma, void* dbeta, void* dsum, int dsum_f32,
+                              int dsum_accumulate, float* scratch, int scratch_rows, long long rows,
+                              int D, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (rows <= 0 || D <= 0) return gbh::E_OK;
+  const int V = dtype == DT_F32 ? 4 : 8;
+  const bool aligned = (D % V == 0) && (D / V <= 1024) &&
+                       ((((uintptr_t)x | (uintptr_t)dy | (uintptr_t)dres | (uintptr_t)dx) & 15) == 0);
+  if (!aligned || dres == nullptr || scratch == nullptr || scratch_rows < 1) {
+    gbh::set_error("gb_norm_bwd_res: needs aligned rows of at most 1024 vectors, dres and scratch");
+    return gbh::E_BAD_ARG;
+  }
+  int rc = 1;
+#define GB_N(DTI, T, WDI, TW)                                                                            \
+  if (dtype == DTI && wdtype == WDI) {                                                                   \
+    if (dsum_f32)                                                                                        \
+      rc = kind ? norm_bwd_pipe_launch<T, TW, float, true, true>(x, dy, dres, w, mean, rstd, dx, dgamma, dbeta,  \
+                                                                 dsum, dsum_accumulate, scratch, scratch_rows, rows, D, s) \
+                : norm_bwd_pipe_launch<T, TW, float, false, true>(x, dy, dres, w, mean, rstd, dx, dgamma, dbeta, \
+                                                                  dsum, dsum_accumulate, scratch, scratch_rows, rows, D, s); \
+    else                                                                                                 \
+      rc = kind ? norm_bwd_pipe_launch<T, TW, T, true, true>(x, dy, dres, w, mean, rstd, dx, dgamma, dbeta,      \
+                                                             dsum, dsum_accumulate, scratch, scratch_rows, rows, D, s) \
+                : norm_bwd_pipe_launch<T, TW, T, false, true>(x, dy, dres, w, mean, rstd, dx, dgamma, dbeta,     \
+                                                              dsum, dsum_accumulate, scratch, scratch_rows, rows, D, s); \
+  }
+  GB_N(DT_BF16, __nv_bfloat16, DT_BF16, __nv_bfloat16)
+  GB_N(DT_BF16, __nv_bfloat16, DT_F32, float)
+  GB_N(DT_F16, __half, DT_F16, __half)
+  GB_N(DT_F16, __half, DT_F32, float)
+  GB_N(DT_F32, float, DT_F32, float)
+#undef GB_N
+  if (rc == 1) {
+    gbh::set_error("gb_norm_bwd_res: no kernel plan for dtype pair %d/%d, D %d", dtype, wdtype, D);
+    return gbh::E_BAD_ARG;
+  }
+  return rc;
 }
 
 // ---------------------------------------------------------------------------

@@ -238,6 +238,16 @@ class DistributedDataParallel(torch.nn.Module):
         self._ready.add(id(p))
         b.pending -= 1
         if b.pending == 0 and self._sync and self.overlap:
+            self._launch_ready()
+
+    def _launch_ready(self):
+        """Launches buckets strictly in descending index: a complete bucket waits until every
+        bucket above it has been launched.  Collectives of different ranks are matched by
+        launch order alone, and which gradients arrive first (or at all) may differ from rank
+        to rank, so the order must not depend on it; ``step`` flushes the rest the same way."""
+        while self._next >= 0 and self.buckets[self._next].pending == 0:
+            b = self.buckets[self._next]
+            self._next -= 1
             self._launch(b)
 
     # ---- bucket launch ------------------------------------------------------------------------
@@ -266,6 +276,7 @@ class DistributedDataParallel(torch.nn.Module):
     def _reset_step(self):
         self._ready = set()
         self._launched_any = False
+        self._next = len(self.buckets) - 1      # next bucket to launch (descending order)
         for b in self.buckets:
             b.pending = len(b.params)
             b.launched = False
@@ -298,9 +309,10 @@ class DistributedDataParallel(torch.nn.Module):
                 # in the reference (distributed.go:253-258)
                 _, o, n = self._where[id(p)]
                 self.flat_grads[o:o + n].zero_()
-        for b in reversed(self.buckets):
-            if not b.launched:
-                self._launch(b)
+        while self._next >= 0:                 # the rest, in the same descending order
+            b = self.buckets[self._next]
+            self._next -= 1
+            self._launch(b)
         if self._launched_any:
             torch.cuda.current_stream().wait_stream(self._comm_stream)
         self.t += 1

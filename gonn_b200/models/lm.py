@@ -64,8 +64,16 @@ class GPTBlock(Module):
         self.ff2 = Linear(d_ff, d_model, True, **kw)
 
     def forward(self, x):
-        n = self.norm1(x)
-        x = self.attn(n, n, n, True, residual=x)
+        f1 = self.norm1.fork(x, self.attn.outproj.bias) if torch.is_grad_enabled() else None
+        if f1 is not None:
+            x = self.attn(f1[0], f1[0], f1[0], True, residual=f1[1], out_bias_grad=False)
+        else:
+            n = self.norm1(x)
+            x = self.attn(n, n, n, True, residual=x)
+        f2 = self.norm2.fork(x, self.ff2.bias) if torch.is_grad_enabled() else None
+        if f2 is not None:
+            return _feed_forward(f2[0], self.ff1.weight, self.ff1.bias, self.ff2.weight, self.ff2.bias,
+                                 "gelu", f2[1], False)
         return _feed_forward(self.norm2(x), self.ff1.weight, self.ff1.bias, self.ff2.weight, self.ff2.bias,
                              "gelu", x)
 

@@ -69,8 +69,10 @@ class MultiHeadAttention(Module):
         return r
 
     # -- forward variants -----------------------------------------------------------------
-    def forward(self, q, k=None, v=None, causal: bool = False, residual=None):
-        """(B, Tq, E), (B, Tk, kdim), (B, Tk, vdim) -> (B, Tq, E)."""
+    def forward(self, q, k=None, v=None, causal: bool = False, residual=None, out_bias_grad: bool = True):
+        """(B, Tq, E), (B, Tk, kdim), (B, Tk, vdim) -> (B, Tq, E).  ``residual`` is added in the
+        output projection's epilogue; ``out_bias_grad=False`` leaves the gradient of the output
+        projection's bias to the caller (``LayerNorm.fork`` produces it)."""
         k = q if k is None else k
         v = q if v is None else v
         self._check(q, k, v)
@@ -79,7 +81,7 @@ class MultiHeadAttention(Module):
                                       self.qproj.bias, self.kproj.bias, self.vproj.bias,
                                       self.num_heads, causal)
             if core is not None:
-                return self.outproj(core, residual=residual)
+                return self.outproj(core, residual=residual, bias_grad=out_bias_grad)
         B, Tq, _ = q.shape
         Tk = k.shape[1]
         H, D = self.num_heads, self.head_dim
@@ -87,7 +89,7 @@ class MultiHeadAttention(Module):
         K = self.kproj(k).reshape(B, Tk, H, D)
         V = self.vproj(v).reshape(B, Tk, H, D)
         out = flash_attention(Q, K, V, causal=causal)
-        return self.outproj(out.reshape(B, Tq, H * D), residual=residual)
+        return self.outproj(out.reshape(B, Tq, H * D), residual=residual, bias_grad=out_bias_grad)
 
     def ForwardFused(self, q, k=None, v=None, causal: bool = False):
         """Inference entry point of the reference (no tape): same math under no_grad."""

@@ -23,10 +23,10 @@ class Linear(Module):
         self.bias = torch.nn.Parameter(torch.empty(out_features, dtype=dtype, device=device)) if bias else None
         fan_in_uniform_(self.weight.data, self.bias.data if bias else None, in_features)
 
-    def forward(self, x, residual=None):
+    def forward(self, x, residual=None, bias_grad: bool = True):
         if x.shape[-1] != self.in_features:
             raise ValueError(f"nn.Linear: expected last dim {self.in_features}, got {x.shape[-1]}")
-        return _linear(x, self.weight, self.bias, self.activation, residual)
+        return _linear(x, self.weight, self.bias, self.activation, residual, bias_grad)
 
     def extra_repr(self):
         return f"{self.in_features}, {self.out_features}, bias={self.bias is not None}"

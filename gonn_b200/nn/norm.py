@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 
-from ..ops.norm import layer_norm, rms_norm
+from ..ops.norm import fork_fuses, layer_norm, norm_fork, rms_norm
 from .module import Module
 
 
@@ -32,9 +32,23 @@ class LayerNorm(Module):
         if tuple(shp[-nd:]) != self.normalized_shape:
             raise ValueError(f"nn.LayerNorm: trailing dims {tuple(shp[-nd:])} != {self.normalized_shape}")
         x2 = x.reshape(-1, self._n)
-        w = self.weight.reshape(-1) if self.weight is not None else None
-        b = self.bias.reshape(-1) if self.bias is not None else None
-        return layer_norm(x2, w, b, self.eps).reshape(shp)
+        return layer_norm(x2, self._flat(self.weight), self._flat(self.bias), self.eps).reshape(shp)
+
+    @staticmethod
+    def _flat(p):
+        # a 1-D parameter is passed as itself: the kernels' gradient sinks are looked up on the
+        # parameter object, which a reshaped alias would hide
+        return None if p is None else (p if p.dim() == 1 else p.reshape(-1))
+
+    def fork(self, x, res_bias=None):
+        """``(self(x), x)`` for a block ``x + f(self(x))``: the backward adds the gradient that
+        bypasses the norm inside the norm's own kernel and also yields the gradient of
+        ``res_bias`` (see ``ops.norm.norm_fork``).  Returns None when that path does not apply."""
+        if len(self.normalized_shape) != 1 or x.shape[-1] != self._n or not fork_fuses(x):
+            return None
+        y, xp = norm_fork(x.reshape(-1, self._n), self._flat(self.weight), self._flat(self.bias), self.eps, False,
+                          res_bias)
+        return y.reshape(x.shape), xp.reshape(x.shape)
 
 
 class RMSNorm(Module):
@@ -46,3 +60,10 @@ class RMSNorm(Module):
     def forward(self, x):
         shp = x.shape
         return rms_norm(x.reshape(-1, self.dim), self.weight, self.eps).reshape(shp)
+
+    def fork(self, x, res_bias=None):
+        """``(self(x), x)`` with the fused backward of ``LayerNorm.fork``."""
+        if x.shape[-1] != self.dim or not fork_fuses(x):
+            return None
+        y, xp = norm_fork(x.reshape(-1, self.dim), self.weight, None, self.eps, True, res_bias)
+        return y.reshape(x.shape), xp.reshape(x.shape)

@@ -38,7 +38,7 @@ class TransformerEncoderLayer(Module):
         self.drop2 = Dropout(dropout)
         self.dropff = Dropout(dropout)
 
-    def _ff(self, x, residual=None):
+    def _ff(self, x, residual=None, bias2_grad: bool = True):
         kind = getattr(self.act, "kind", None)
         plain = not (self.training and self.dropff.p > 0)
         if kind in _FUSABLE and plain and type(self.act) is Activation:
@@ -46,17 +46,31 @@ class TransformerEncoderLayer(Module):
             # the activation's derivative into the second layer's data-gradient GEMM
             from ..ops.linear import feed_forward
             return feed_forward(x, self.ff1.weight, self.ff1.bias, self.ff2.weight, self.ff2.bias,
-                                _FUSABLE[kind], residual)
+                                _FUSABLE[kind], residual, bias2_grad)
+        if residual is not None and not (self.training and self.dropff.p > 0):
+            return self.ff2(self.act(self.ff1(x)), residual=residual, bias_grad=bias2_grad)
         y = self.ff2(self.dropff(self.act(self.ff1(x))))
         return y if residual is None else residual + y
 
     def forward(self, x):
         nodrop = not (self.training and self.drop1.p > 0)
         if self.pre_norm:
-            n = self.norm1(x)
             if nodrop:
-                x = self.attn(n, n, n, self.causal, residual=x)
+                # x + attn(norm1(x)), then x + ff(norm2(x)): each norm also hands its input on, so
+                # that its backward kernel adds the bypassing gradient and reduces the bias
+                # gradient of the layer that closes the block
+                f1 = self.norm1.fork(x, self.attn.outproj.bias) if torch.is_grad_enabled() else None
+                if f1 is not None:
+                    n, xp = f1
+                    x = self.attn(n, n, n, self.causal, residual=xp, out_bias_grad=False)
+                else:
+                    n = self.norm1(x)
+                    x = self.attn(n, n, n, self.causal, residual=x)
+                f2 = self.norm2.fork(x, self.ff2.bias) if torch.is_grad_enabled() else None
+                if f2 is not None:
+                    return self._ff(f2[0], residual=f2[1], bias2_grad=False)
                 return self._ff(self.norm2(x), residual=x)
+            n = self.norm1(x)
             x = x + self.drop1(self.attn(n, n, n, self.causal))
             return x + self.drop2(self._ff(self.norm2(x)))
         if nodrop:

@@ -74,7 +74,7 @@ def emit_grad(param: torch.Tensor, grad: torch.Tensor):
 
 class _Linear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, act, residual):
+    def forward(ctx, x, weight, bias, act, residual, bias_grad=True):
         K = x.shape[-1]
         N = weight.shape[0]
         x2 = x.reshape(-1, K)
@@ -92,6 +92,7 @@ class _Linear(torch.autograd.Function):
         ctx.act, ctx.has_bias, ctx.xshape = act, bias is not None, x.shape
         ctx.bias_ref = bias
         ctx.has_res = residual is not None
+        ctx.bias_grad = bias_grad
         return y.reshape(*x.shape[:-1], N)
 
     @staticmethod
@@ -109,15 +110,18 @@ class _Linear(torch.autograd.Function):
             dx = gemm(dy2, weight).reshape(ctx.xshape)
         if ctx.needs_input_grad[1]:
             dw = emit_weight_grad(weight, dy2, x2, True, False)
-        if ctx.has_bias and ctx.needs_input_grad[2]:
+        if ctx.has_bias and ctx.needs_input_grad[2] and ctx.bias_grad:
             db = emit_vector_grad(ctx.bias_ref, dy2)
-        return dx, dw, db, None, dres
+        return dx, dw, db, None, dres, None
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           act: Optional[str] = None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``act(x @ weight.T + bias)`` (+ ``residual`` when no activation); weight is (out, in)."""
-    return _Linear.apply(x, weight, bias, act, residual)
+           act: Optional[str] = None, residual: Optional[torch.Tensor] = None,
+           bias_grad: bool = True) -> torch.Tensor:
+    """``act(x @ weight.T + bias)`` (+ ``residual`` when no activation); weight is (out, in).
+    ``bias_grad=False``: the bias gradient is produced elsewhere (``ops.norm.norm_fork`` yields
+    it from the residual stream's gradient), so the column reduction is skipped here."""
+    return _Linear.apply(x, weight, bias, act, residual, bias_grad)
 
 
 class _FeedForward(torch.autograd.Function):
@@ -130,7 +134,7 @@ class _FeedForward(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, w1, b1, w2, b2, act, residual):
+    def forward(ctx, x, w1, b1, w2, b2, act, residual, bias2_grad=True):
         K, F, N = x.shape[-1], w1.shape[0], w2.shape[0]
         x2 = x.reshape(-1, K)
         pre = torch.empty((x2.shape[0], F), dtype=x.dtype, device=x.device)
@@ -140,6 +144,7 @@ class _FeedForward(torch.autograd.Function):
         ctx.save_for_backward(x2, w1, w2, pre, h)
         ctx.act, ctx.xshape, ctx.has_res = act, x.shape, residual is not None
         ctx.b1, ctx.b2 = b1, b2
+        ctx.bias2_grad = bias2_grad
         return y.reshape(*x.shape[:-1], N)
 
     @staticmethod
@@ -154,18 +159,21 @@ class _FeedForward(torch.autograd.Function):
         # second layer's data gradient (act' folded in) first, then its weight / bias gradients
         dpre = gemm(dy2, w2, aux=pre, aux_mode=_DACT_MODE[ctx.act])
         dw2 = emit_weight_grad(w2, dy2, h, True, False) if ctx.needs_input_grad[3] else None
-        db2 = emit_vector_grad(ctx.b2, dy2) if (ctx.b2 is not None and ctx.needs_input_grad[4]) else None
+        db2 = (emit_vector_grad(ctx.b2, dy2)
+               if (ctx.b2 is not None and ctx.needs_input_grad[4] and ctx.bias2_grad) else None)
         dx = gemm(dpre, w1).reshape(ctx.xshape) if ctx.needs_input_grad[0] else None
         dw1 = emit_weight_grad(w1, dpre, x2, True, False) if ctx.needs_input_grad[1] else None
         db1 = emit_vector_grad(ctx.b1, dpre) if (ctx.b1 is not None and ctx.needs_input_grad[2]) else None
-        return dx, dw1, db1, dw2, db2, None, dres
+        return dx, dw1, db1, dw2, db2, None, dres, None
 
 
-def feed_forward(x, w1, b1, w2, b2, act: str = "gelu", residual: Optional[torch.Tensor] = None):
-    """Two-layer feed-forward block with a fusable activation (relu / gelu / geluexact)."""
+def feed_forward(x, w1, b1, w2, b2, act: str = "gelu", residual: Optional[torch.Tensor] = None,
+                 bias2_grad: bool = True):
+    """Two-layer feed-forward block with a fusable activation (relu / gelu / geluexact).
+    ``bias2_grad=False``: see ``linear``."""
     if act not in _DACT_MODE:
         raise ValueError(f"feed_forward: activation {act!r} cannot be fused")
-    return _FeedForward.apply(x, w1, b1, w2, b2, act, residual)
+    return _FeedForward.apply(x, w1, b1, w2, b2, act, residual, bias2_grad)
 
 
 class _MatMul(torch.autograd.Function):

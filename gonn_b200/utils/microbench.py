@@ -206,15 +206,31 @@ def np_abs_max(a):
 
 
 def bench_norm():
-    from ..ops.norm import layer_norm
-    for rows, D in ((16384, 768), (65536, 768), (16384, 2048), (65536, 2048)):
-        x = torch.randn(rows, D, device="cuda", dtype=torch.bfloat16)
-        w = torch.ones(D, device="cuda", dtype=torch.bfloat16)
-        b = torch.zeros(D, device="cuda", dtype=torch.bfloat16)
-        t = timeit(lambda: layer_norm(x, w, b))
-        r = timeit(lambda: torch.nn.functional.layer_norm(x, (D,), w, b))
-        by = 2.0 * rows * D * 2
-        _emit(bench="layer_norm_fwd", rows=rows, D=D, ms=t, gbs=by / t / 1e6, torch_ms=r, torch_gbs=by / r / 1e6)
+    """LayerNorm / RMSNorm forward and backward against the stock torch ops; bytes are the
+    algorithmic ones (forward reads x and writes y; backward reads x and dy and writes dx)."""
+    from ..ops.norm import layer_norm, rms_norm
+    F = torch.nn.functional
+    for rows, D in ((16384, 768), (65536, 768), (16384, 2048), (65536, 2048), (8192, 4096), (16384, 1024)):
+        for rms in (False, True):
+            x = torch.randn(rows, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+            w = torch.ones(D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+            b = None if rms else torch.zeros(D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+            ours = (lambda: rms_norm(x, w)) if rms else (lambda: layer_norm(x, w, b))
+            stock = (lambda: F.rms_norm(x, (D,), w, 1e-6)) if rms else (lambda: F.layer_norm(x, (D,), w, b))
+            with torch.no_grad():
+                t = timeit(ours)
+                r = timeit(stock)
+            by = 2.0 * rows * D * 2
+            name = "rms_norm" if rms else "layer_norm"
+            _emit(bench=name + "_fwd", rows=rows, D=D, ms=t, gbs=by / t / 1e6, torch_ms=r, torch_gbs=by / r / 1e6)
+            dy = torch.randn(rows, D, device="cuda", dtype=torch.bfloat16)
+            params = (x, w) if rms else (x, w, b)
+            y = ours()
+            t = timeit(lambda: torch.autograd.grad(y, params, dy, retain_graph=True))
+            yt = stock()
+            r = timeit(lambda: torch.autograd.grad(yt, params, dy, retain_graph=True))
+            by = 3.0 * rows * D * 2
+            _emit(bench=name + "_bwd", rows=rows, D=D, ms=t, gbs=by / t / 1e6, torch_ms=r, torch_gbs=by / r / 1e6)
 
 
 def bench_mlp_cpu():

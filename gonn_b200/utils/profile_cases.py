@@ -4,6 +4,8 @@
     python -m gonn_b200.utils.profile_cases flash_fwd 4 2048 16 128 [causal]
     python -m gonn_b200.utils.profile_cases flash_bwd 4 2048 16 128 [causal]
     python -m gonn_b200.utils.profile_cases norm 16384 768
+    python -m gonn_b200.utils.profile_cases norm_bwd 16384 768        # LayerNorm backward
+    python -m gonn_b200.utils.profile_cases norm_fork 16384 768       # backward with the residual bypass fused
     python -m gonn_b200.utils.profile_cases step 50000000
 
 Each case allocates a few hundred MB at most, runs three warm-up launches and
@@ -80,6 +82,24 @@ def main(argv):
         b = torch.zeros(D, device=dev, dtype=torch.bfloat16)
         ms = _time(lambda: layer_norm(x, w, b))
         print(f"layer_norm {rows}x{D}: {ms:.4f} ms, {2 * rows * D * 2 / ms / 1e6:.1f} GB/s")
+    elif kind in ("norm_bwd", "norm_fork"):
+        from ..ops.norm import norm_fork
+        rows, D = int(argv[1]), int(argv[2])
+        x = torch.randn(rows, D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        w = torch.ones(D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        b = torch.zeros(D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        dy = torch.randn(rows, D, device=dev, dtype=torch.bfloat16)
+        if kind == "norm_bwd":
+            y = layer_norm(x, w, b)
+            ms = _time(lambda: torch.autograd.grad(y, (x, w, b), dy, retain_graph=True))
+            nb = 3
+        else:
+            rb = torch.zeros(D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+            y, xp = norm_fork(x, w, b, 1e-5, False, rb)
+            dp = torch.randn(rows, D, device=dev, dtype=torch.bfloat16)
+            ms = _time(lambda: torch.autograd.grad((y, xp), (x, w, b, rb), (dy, dp), retain_graph=True))
+            nb = 4
+        print(f"{kind} {rows}x{D}: {ms:.4f} ms, {nb * rows * D * 2 / ms / 1e6:.1f} GB/s")
     elif kind == "step":
         n = int(argv[1]) // 8 * 8
         from ..distributed.nvlink import SymmetricMemory

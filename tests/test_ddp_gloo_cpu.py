@@ -77,6 +77,19 @@ def _worker(rank, world, port, out):
             d2.step()
             opt.step()
         res["lin"], res["lin_buckets"] = _named(lin), len(d2.buckets)
+        # a layer that only rank 0 uses: its gradients never arrive on rank 1, so the ranks see
+        # their buckets complete in different orders; the collectives must still pair up
+        from gonn_b200 import nn
+        torch.manual_seed(11)
+        br = nn.Sequential(nn.Linear(6, 6), nn.Linear(6, 6), nn.Linear(6, 3))
+        d3 = DistributedDataParallel(br, optimizer=None, bucket_mb=0.00001)
+        h = br[0](x[sl])
+        if rank == 0:
+            h = br[1](h)
+        ((br[2](h) - y[sl]) ** 2).mean().backward()
+        d3.step()
+        res["branch_grads"] = {n: p.grad.detach().clone() for n, p in br.named_parameters()}
+        res["branch_buckets"] = len(d3.buckets)
         out[rank] = res
     finally:
         dist.destroy_process_group()
@@ -126,3 +139,20 @@ def test_two_cpu_ranks_run_the_engine():
     assert _same(r0["lin"], r1["lin"])
     for n, p in _named(lin).items():
         assert torch.allclose(p, r0["lin"][n], rtol=1e-5, atol=1e-6), n
+    # the branch case: identical bytes on both ranks, equal to the mean of the two ranks' local
+    # gradients with zeros where rank 1 had none
+    from gonn_b200 import nn
+    assert r0["branch_buckets"] >= 4 and _same(r0["branch_grads"], r1["branch_grads"])
+    want = None
+    for rank in (0, 1):
+        torch.manual_seed(11)
+        br = nn.Sequential(nn.Linear(6, 6), nn.Linear(6, 6), nn.Linear(6, 3))
+        sl = slice(rank * 4, (rank + 1) * 4)
+        h = br[0](x[sl])
+        if rank == 0:
+            h = br[1](h)
+        ((br[2](h) - y[sl]) ** 2).mean().backward()
+        g = {n: (p.grad if p.grad is not None else torch.zeros_like(p)) * 0.5 for n, p in br.named_parameters()}
+        want = g if want is None else {n: want[n] + g[n] for n in g}
+    for n, g in want.items():
+        assert torch.allclose(g, r0["branch_grads"][n], rtol=1e-5, atol=1e-6), n

@@ -91,6 +91,79 @@ def test_norms(D, dtype, wdtype, rms, status_ok):
         assert (b.grad.double() - br.grad).abs().max().item() < wt * (1 + br.grad.abs().max().item() * 0.05)
 
 
+@pytest.mark.parametrize("pipelined", [1, 0])
+@pytest.mark.parametrize("rows,D", [(1, 768), (7, 256), (300, 512), (4099, 768), (1030, 1024), (515, 1536),
+                                    (300, 2048), (130, 3072), (70, 4096), (33, 6144), (20, 8192)])
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_kernels_tight(rows, D, rms, pipelined, status_ok):
+    """bf16 rows with fp32 weights against float64 math: the output within one bf16 rounding
+    step, the parameter gradients (fp32, deterministic fixed-order sums) to 1e-3 of their
+    scale; every row-width class of the pipelined and of the register-resident kernels, with
+    row counts that leave a ragged last tile."""
+    from gonn_b200 import lib as gl
+    gl.call("gb_norm_tune", gl.I(pipelined))
+    try:
+        g = torch.Generator(device="cuda").manual_seed(rows * 31 + D)
+        x = (torch.randn(rows, D, device="cuda", generator=g) * 2 + 0.5).to(torch.bfloat16).requires_grad_(True)
+        w = (torch.randn(D, device="cuda", generator=g) * 0.5 + 1).requires_grad_(True)
+        b = None if rms else torch.randn(D, device="cuda", generator=g).requires_grad_(True)
+        y = rms_norm(x, w, 1e-6) if rms else layer_norm(x, w, b, 1e-5)
+        xr, wr = x.detach().double().requires_grad_(True), w.detach().double().requires_grad_(True)
+        br = None if rms else b.detach().double().requires_grad_(True)
+        ref = norm_ref(xr, wr, br, 1e-6 if rms else 1e-5, rms)
+        assert ((y.double() - ref).abs() / (1 + ref.abs())).max().item() < 2 ** -8
+        dy = torch.randn(rows, D, device="cuda", generator=g).to(torch.bfloat16)
+        y.backward(dy)
+        ref.backward(dy.double())
+        assert ((x.grad.double() - xr.grad).abs() / (1 + xr.grad.abs())).max().item() < 2 ** -7
+        scale = wr.grad.abs().max().item() + 1
+        assert (w.grad.double() - wr.grad).abs().max().item() < 1e-3 * scale
+        if not rms:
+            assert (b.grad.double() - br.grad).abs().max().item() < 1e-3 * (br.grad.abs().max().item() + 1)
+        # run to run: identical bytes
+        x2 = x.detach().clone().requires_grad_(True)
+        w2 = w.detach().clone().requires_grad_(True)
+        b2 = None if rms else b.detach().clone().requires_grad_(True)
+        y2 = rms_norm(x2, w2, 1e-6) if rms else layer_norm(x2, w2, b2, 1e-5)
+        y2.backward(dy)
+        assert torch.equal(y2, y) and torch.equal(x2.grad, x.grad) and torch.equal(w2.grad, w.grad)
+    finally:
+        gl.call("gb_norm_tune", gl.I(1))
+
+
+@pytest.mark.parametrize("rows,D", [(5, 64), (300, 512), (4099, 768), (1030, 1024), (300, 2048), (70, 4096),
+                                    (20, 8192)])
+@pytest.mark.parametrize("rms", [False, True])
+@pytest.mark.parametrize("wdtype", [torch.bfloat16, torch.float32])
+def test_norm_fork_backward(rows, D, rms, wdtype, status_ok):
+    """``norm_fork`` returns (norm(x), x); its one-kernel backward must equal norm_bwd(dy) + dpass,
+    with the column sums of dpass as the gradient of ``res_bias`` (float64 reference)."""
+    from gonn_b200.ops.norm import norm_fork
+    g = torch.Generator(device="cuda").manual_seed(rows + D)
+    x = (torch.randn(rows, D, device="cuda", generator=g) * 1.5).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(D, device="cuda", generator=g) * 0.5 + 1).to(wdtype).requires_grad_(True)
+    b = None if rms else torch.randn(D, device="cuda", generator=g).to(wdtype).requires_grad_(True)
+    rb = torch.zeros(D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y, xp = norm_fork(x, w, b, 1e-5, rms, rb)
+    assert torch.equal(xp, x)
+    dy = torch.randn(rows, D, device="cuda", generator=g).to(torch.bfloat16)
+    dp = torch.randn(rows, D, device="cuda", generator=g).to(torch.bfloat16)
+    torch.autograd.backward([y, xp], [dy, dp])
+    xr, wr = x.detach().double().requires_grad_(True), w.detach().double().requires_grad_(True)
+    br = None if rms else b.detach().double().requires_grad_(True)
+    ref = norm_ref(xr, wr, br, 1e-5, rms)
+    ref.backward(dy.double())
+    want_dx = xr.grad + dp.double()
+    assert ((y.double() - ref).abs() / (1 + ref.abs())).max().item() < 2 ** -7
+    assert ((x.grad.double() - want_dx).abs() / (1 + want_dx.abs())).max().item() < 2 ** -6
+    wtol = 1e-3 if wdtype == torch.float32 else 2 ** -7
+    assert (w.grad.double() - wr.grad).abs().max().item() < wtol * (wr.grad.abs().max().item() + 1)
+    if not rms:
+        assert (b.grad.double() - br.grad).abs().max().item() < wtol * (br.grad.abs().max().item() + 1)
+    want_rb = dp.double().sum(0)
+    assert (rb.grad.double() - want_rb).abs().max().item() < 2 ** -7 * (want_rb.abs().max().item() + 1)
+
+
 @pytest.mark.parametrize("D", [10, 1000, 32000, 50304])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_softmax_family(D, dtype, status_ok):
