@@ -428,6 +428,7 @@ struct PipeSmem {
   uint64_t empty[kPipeMaxStages];
   int abort_flag;
   int pad[3];
+  float first[4];
   float2 red[2][4][8];  // [flip][group][warp in group]; groups of one warp need no slot
 };
 static_assert(sizeof(PipeSmem) <= kPipeHeader, "header too small");
@@ -451,6 +452,17 @@ __device__ __forceinline__ float2 group_sum2(float2 v, PipeSmem* ps, int g, int&
 }
 
 // V consecutive weights starting at vector vi, widened to fp32 (vector loads from shared memory)
+// The first element of the row (held by thread 0 of the group) for every thread of a group
+// wider than a warp.  Uses its own slot so that it does not disturb group_sum2's double buffer.
+template <int G>
+__device__ __forceinline__ float ps_first_of_row(float k_lane0, PipeSmem* ps, int g) {
+  if ((threadIdx.x % G) == 0) ps->first[g] = k_lane0;
+  named_bar_sync(1 + g, G);
+  const float k = ps->first[g];
+  named_bar_sync(1 + g, G);
+  return k;
+}
+
 template <typename TW, int V>
 __device__ __forceinline__ void load_wvec(const TW* sw, int vi, float* f) {
   if constexpr (sizeof(TW) == 2) {
@@ -488,12 +500,62 @@ __device__ __forceinline__ void pipe_produce(PipeSmem* ps, unsigned char* stages
   }
 }
 
+// Packed fp32 pairs: one instruction handles two lanes of arithmetic (add / mul / fma on
+// float2 operands), which halves the issue slots of these kernels; the measured limiter of a
+// first version with scalar arithmetic was instruction issue, not memory.
+__device__ __forceinline__ float2 f2(float a) { return make_float2(a, a); }
+template <typename T> struct Pairs;   // a 16-byte vector as V/2 float2 pairs
+template <> struct Pairs<__nv_bfloat16> {
+  static constexpr int NP2 = 4;
+  static __device__ __forceinline__ void unpack(const uint4& u, float2* f) {
+    f[0] = unpack_bf16(u.x); f[1] = unpack_bf16(u.y); f[2] = unpack_bf16(u.z); f[3] = unpack_bf16(u.w);
+  }
+  static __device__ __forceinline__ uint4 pack(const float2* f) {
+    uint4 u;
+    u.x = pack_bf16(f[0].x, f[0].y); u.y = pack_bf16(f[1].x, f[1].y);
+    u.z = pack_bf16(f[2].x, f[2].y); u.w = pack_bf16(f[3].x, f[3].y);
+    return u;
+  }
+};
+template <> struct Pairs<__half> {
+  static constexpr int NP2 = 4;
+  static __device__ __forceinline__ void unpack(const uint4& u, float2* f) {
+    f[0] = unpack_f16(u.x); f[1] = unpack_f16(u.y); f[2] = unpack_f16(u.z); f[3] = unpack_f16(u.w);
+  }
+  static __device__ __forceinline__ uint4 pack(const float2* f) {
+    uint4 u;
+    u.x = pack_f16(f[0].x, f[0].y); u.y = pack_f16(f[1].x, f[1].y);
+    u.z = pack_f16(f[2].x, f[2].y); u.w = pack_f16(f[3].x, f[3].y);
+    return u;
+  }
+};
+template <> struct Pairs<float> {
+  static constexpr int NP2 = 2;
+  static __device__ __forceinline__ void unpack(const float4& u, float2* f) {
+    f[0] = make_float2(u.x, u.y); f[1] = make_float2(u.z, u.w);
+  }
+  static __device__ __forceinline__ float4 pack(const float2* f) {
+    return make_float4(f[0].x, f[0].y, f[1].x, f[1].y);
+  }
+};
+// NP2 pairs of fp32 constants (weights widened once per CTA) from shared memory
+template <int NP2>
+__device__ __forceinline__ void load_pairs(const float* s, int vi, float2* f) {
+#pragma unroll
+  for (int j = 0; j < NP2; j += 2) {
+    const float4 u = *reinterpret_cast<const float4*>(s + vi * NP2 * 2 + j * 2);
+    f[j] = make_float2(u.x, u.y);
+    f[j + 1] = make_float2(u.z, u.w);
+  }
+}
+
 template <typename T, typename TW, int G, int VPT, bool RMS>
-__global__ void __launch_bounds__(kPipeThreads, 2)
+__global__ void __launch_bounds__(kPipeThreads, 3)
 norm_fwd_pipe_kernel(const T* __restrict__ x, const TW* __restrict__ w, const TW* __restrict__ b,
                      T* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
                      long long rows, int D, float eps, int KR, int S, int* status) {
   constexpr int V = IO<T>::V;
+  constexpr int NP2 = Pairs<T>::NP2;
   constexpr int NG = kPipeConsumers / G;
   using Raw = typename IO<T>::Raw;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -502,16 +564,16 @@ norm_fwd_pipe_kernel(const T* __restrict__ x, const TW* __restrict__ w, const TW
   const size_t row_bytes = (size_t)D * sizeof(T);
   const size_t stage_bytes = (size_t)R * row_bytes;
   unsigned char* stages = smem_raw + kPipeHeader;
-  TW* sw = reinterpret_cast<TW*>(stages + (size_t)S * stage_bytes);
-  TW* sb = sw + D;
+  float* sw = reinterpret_cast<float*>(stages + (size_t)S * stage_bytes);  // weights, widened
+  float* sb = sw + D;
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; s++) { mbar_init(&ps->full[s], 1); mbar_init(&ps->empty[s], kPipeConsumers / 32); }
     ps->abort_flag = 0;
     mbar_fence_init();
   }
   for (int i = threadIdx.x; i < D; i += kPipeThreads) {
-    sw[i] = w ? w[i] : (TW)1.f;
-    sb[i] = (!RMS && b) ? b[i] : (TW)0.f;
+    sw[i] = w ? (float)w[i] : 1.f;
+    sb[i] = (!RMS && b) ? (float)b[i] : 0.f;
   }
   __syncthreads();
   if (threadIdx.x >= kPipeConsumers) {
@@ -522,6 +584,7 @@ norm_fwd_pipe_kernel(const T* __restrict__ x, const TW* __restrict__ w, const TW
   }
   const int g = threadIdx.x / G, t = threadIdx.x % G;
   const int nvec = D / V;
+  const float invD = 1.f / (float)D;
   const long long ntiles = (rows + R - 1) / R;
   int flip = 0, it = 0;
   for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, it++) {
@@ -533,12 +596,17 @@ norm_fwd_pipe_kernel(const T* __restrict__ x, const TW* __restrict__ w, const TW
       const int r = kk * NG + g;
       const long long row = tile * R + r;
       const bool live = row < rows;  // uniform over the group
-      Raw xr[VPT];
+      float2 f[VPT][NP2];
       if (live) {
 #pragma unroll
         for (int i = 0; i < VPT; i++) {
           const int vi = t + i * G;
-          if (vi < nvec) xr[i] = *reinterpret_cast<const Raw*>(st + (size_t)r * row_bytes + (size_t)vi * sizeof(Raw));
+          if (vi < nvec) {
+            Pairs<T>::unpack(*reinterpret_cast<const Raw*>(st + (size_t)r * row_bytes + (size_t)vi * sizeof(Raw)), f[i]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < NP2; j++) f[i][j] = f2(0.f);
+          }
         }
       }
       if (kk == KR - 1) {  // every row of the stage is in registers: hand the stage back
@@ -546,53 +614,56 @@ norm_fwd_pipe_kernel(const T* __restrict__ x, const TW* __restrict__ w, const TW
         if ((threadIdx.x & 31) == 0) mbar_arrive(&ps->empty[s]);
       }
       if (!live) continue;
-      float2 acc = make_float2(0.f, 0.f);
-#pragma unroll
-      for (int i = 0; i < VPT; i++) {
-        if (t + i * G < nvec) {
-          float f[V];
-          IO<T>::unpack(xr[i], f);
-#pragma unroll
-          for (int j = 0; j < V; j++) { acc.x += f[j]; acc.y += f[j] * f[j]; }
-        }
-      }
-      float mean = 0.f, rstd;
+      float mean = 0.f, rstd, shiftv = 0.f;
       if (RMS) {
-        acc = group_sum2<G>(acc, ps, g, flip);
-        rstd = rsqrtf(acc.y / D + eps);
+        float2 q = f2(0.f);
+#pragma unroll
+        for (int i = 0; i < VPT; i++)
+#pragma unroll
+          for (int j = 0; j < NP2; j++) q = __ffma2_rn(f[i][j], f[i][j], q);
+        float2 tot = group_sum2<G>(make_float2(q.x + q.y, 0.f), ps, g, flip);
+        rstd = rsqrtf(tot.x * invD + eps);
       } else {
-        acc = group_sum2<G>(acc, ps, g, flip);
-        mean = acc.x / D;
-        float2 q = make_float2(0.f, 0.f);  // variance from centred values
+        // One pass, one reduction: sums of (x - K) and (x - K)^2 with K = the row's first
+        // element, so that the variance E[(x-K)^2] - E[x-K]^2 does not cancel when the mean
+        // is large against the spread (K is within the spread of the row).
+        const float K = __shfl_sync(0xffffffffu, f[0][0].x, 0);   // lane 0 of every warp holds vector t = 32 w, ...
+        const float K0 = (G == 32) ? K : ps_first_of_row<G>(K, ps, g);
+        const float2 nk = f2(-K0);
+        float2 a = f2(0.f), q = f2(0.f);
 #pragma unroll
         for (int i = 0; i < VPT; i++) {
           if (t + i * G < nvec) {
-            float f[V];
-            IO<T>::unpack(xr[i], f);
 #pragma unroll
-            for (int j = 0; j < V; j++) { const float d = f[j] - mean; q.x += d * d; }
+            for (int j = 0; j < NP2; j++) {
+              f[i][j] = __fadd2_rn(f[i][j], nk);
+              a = __fadd2_rn(a, f[i][j]);
+              q = __ffma2_rn(f[i][j], f[i][j], q);
+            }
           }
         }
-        q = group_sum2<G>(q, ps, g, flip);
-        rstd = rsqrtf(q.x / D + eps);
+        const float2 tot = group_sum2<G>(make_float2(a.x + a.y, q.x + q.y), ps, g, flip);
+        const float m = tot.x * invD;            // mean of the shifted row
+        mean = K0 + m;
+        rstd = rsqrtf(fmaxf(tot.y * invD - m * m, 0.f) + eps);
+        shiftv = -m * rstd;
       }
       if (t == 0) {
         if (mean_out) mean_out[row] = mean;
         rstd_out[row] = rstd;
       }
       T* yr = y + row * D;
-      const float shift = -mean * rstd;
+      const float2 rs = f2(rstd), sv = f2(shiftv);
 #pragma unroll
       for (int i = 0; i < VPT; i++) {
         const int vi = t + i * G;
         if (vi < nvec) {
-          float f[V], wv[V], bv[V], o[V];
-          IO<T>::unpack(xr[i], f);
-          load_wvec<TW, V>(sw, vi, wv);
-          load_wvec<TW, V>(sb, vi, bv);
+          float2 wv[NP2], bv[NP2], o[NP2];
+          load_pairs<NP2>(sw, vi, wv);
+          load_pairs<NP2>(sb, vi, bv);
 #pragma unroll
-          for (int j = 0; j < V; j++) o[j] = fmaf(fmaf(f[j], rstd, shift), wv[j], bv[j]);
-          IO<T>::st(yr + vi * V, o);
+          for (int j = 0; j < NP2; j++) o[j] = __ffma2_rn(__ffma2_rn(f[i][j], rs, sv), wv[j], bv[j]);
+          *reinterpret_cast<Raw*>(yr + vi * V) = Pairs<T>::pack(o);
         }
       }
     }
@@ -601,7 +672,7 @@ norm_fwd_pipe_kernel(const T* __restrict__ x, const TW* __restrict__ w, const TW
 
 // Backward: dx per row; dgamma / dbeta accumulate per thread over the rows its group
 // visits, are combined over the groups of the CTA through shared memory in group order and
-// written to part[blockIdx.x][2][D]; norm_param_reduce_kernel adds the CTAs in index order.
+// written to part[blockIdx.x][NP][D]; norm_param_reduce_kernel adds the CTAs in index order.
 // RES: a third stream `dres` (the gradient that bypassed the norm through a residual
 // connection) is added to dx, and its column sums go to part[..][2][D]: they are the bias
 // gradient of the linear layer whose output was added to the residual stream after this norm.
@@ -613,6 +684,7 @@ norm_bwd_pipe_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T*
                      long long rows, int D, int KR, int S, int* status) {
   constexpr int NP = RES ? 3 : 2;  // partial rows per CTA: dgamma, dbeta (, column sums of dres)
   constexpr int V = IO<T>::V;
+  constexpr int NP2 = Pairs<T>::NP2;
   constexpr int NG = kPipeConsumers / G;
   using Raw = typename IO<T>::Raw;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -622,13 +694,13 @@ norm_bwd_pipe_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T*
   const size_t half_bytes = (size_t)R * row_bytes;
   const size_t stage_bytes = NP * half_bytes;
   unsigned char* stages = smem_raw + kPipeHeader;
-  TW* sw = reinterpret_cast<TW*>(stages + (size_t)S * stage_bytes);
+  float* sw = reinterpret_cast<float*>(stages + (size_t)S * stage_bytes);
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; s++) { mbar_init(&ps->full[s], 1); mbar_init(&ps->empty[s], kPipeConsumers / 32); }
     ps->abort_flag = 0;
     mbar_fence_init();
   }
-  for (int i = threadIdx.x; i < D; i += kPipeThreads) sw[i] = w ? w[i] : (TW)1.f;
+  for (int i = threadIdx.x; i < D; i += kPipeThreads) sw[i] = w ? (float)w[i] : 1.f;
   __syncthreads();
   const bool producer = threadIdx.x >= kPipeConsumers;
   if (threadIdx.x == kPipeConsumers)
@@ -636,11 +708,12 @@ norm_bwd_pipe_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T*
                      (const unsigned char*)dres, rows, R, row_bytes, S, status);
   const int g = threadIdx.x / G, t = threadIdx.x % G;
   const int nvec = D / V;
-  float dg[VPT][V], db[VPT][V], ds[RES ? VPT : 1][V];
+  const float invD = 1.f / (float)D;
+  float2 dg[VPT][NP2], db[VPT][NP2], ds[RES ? VPT : 1][NP2];
 #pragma unroll
   for (int i = 0; i < VPT; i++)
 #pragma unroll
-    for (int j = 0; j < V; j++) { dg[i][j] = 0.f; db[i][j] = 0.f; if (RES) ds[i][j] = 0.f; }
+    for (int j = 0; j < NP2; j++) { dg[i][j] = f2(0.f); db[i][j] = f2(0.f); if (RES) ds[i][j] = f2(0.f); }
   if (!producer) {
     const long long ntiles = (rows + R - 1) / R;
     int flip = 0, it = 0;
@@ -678,49 +751,47 @@ norm_bwd_pipe_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T*
         const long long row_next = row + NG;
         if (kk + 1 < KR && row_next < rows) { mean_n = RMS ? 0.f : mean_in[row_next]; rstd_n = rstd_in[row_next]; }
         if (!live) continue;
-        const float shift = -mean * rstd;
-        float2 acc = make_float2(0.f, 0.f);
+        const float2 rs = f2(rstd), sh = f2(-mean * rstd);
+        // h = normalised input, gw = dy * weight: both stay in registers for the second pass
+        float2 h[VPT][NP2], gw[VPT][NP2];
+        float2 s1 = f2(0.f), s2 = f2(0.f);
 #pragma unroll
         for (int i = 0; i < VPT; i++) {
           const int vi = t + i * G;
           if (vi < nvec) {
-            float a[V], d[V], wv[V];
-            IO<T>::unpack(xr[i], a);
-            IO<T>::unpack(dr[i], d);
-            load_wvec<TW, V>(sw, vi, wv);
+            float2 d[NP2], wv[NP2];
+            Pairs<T>::unpack(xr[i], h[i]);
+            Pairs<T>::unpack(dr[i], d);
+            load_pairs<NP2>(sw, vi, wv);
 #pragma unroll
-            for (int j = 0; j < V; j++) {
-              const float h = fmaf(a[j], rstd, shift);
-              const float gw = d[j] * wv[j];
-              acc.x += gw;
-              acc.y = fmaf(gw, h, acc.y);
-              dg[i][j] = fmaf(d[j], h, dg[i][j]);
-              db[i][j] += d[j];
+            for (int j = 0; j < NP2; j++) {
+              h[i][j] = __ffma2_rn(h[i][j], rs, sh);
+              gw[i][j] = __fmul2_rn(d[j], wv[j]);
+              s1 = __fadd2_rn(s1, gw[i][j]);
+              s2 = __ffma2_rn(gw[i][j], h[i][j], s2);
+              dg[i][j] = __ffma2_rn(d[j], h[i][j], dg[i][j]);
+              db[i][j] = __fadd2_rn(db[i][j], d[j]);
             }
           }
         }
-        acc = group_sum2<G>(acc, ps, g, flip);
-        const float m1 = RMS ? 0.f : acc.x / D, m2 = acc.y / D;
+        const float2 tot = group_sum2<G>(make_float2(s1.x + s1.y, s2.x + s2.y), ps, g, flip);
+        const float m1 = RMS ? 0.f : tot.x * invD, m2 = tot.y * invD;
+        // dx = rstd * (gw - m1 - h * m2) = gw * rstd + (h * (-rstd m2) + (-rstd m1))
+        const float2 c2 = f2(-rstd * m2), c1 = f2(-rstd * m1);
 #pragma unroll
         for (int i = 0; i < VPT; i++) {
           const int vi = t + i * G;
           if (vi < nvec) {
-            float a[V], d[V], wv[V], o[V];
-            IO<T>::unpack(xr[i], a);
-            IO<T>::unpack(dr[i], d);
-            load_wvec<TW, V>(sw, vi, wv);
+            float2 o[NP2];
 #pragma unroll
-            for (int j = 0; j < V; j++) {
-              const float h = fmaf(a[j], rstd, shift);
-              o[j] = rstd * (fmaf(d[j], wv[j], -m1) - h * m2);
-            }
+            for (int j = 0; j < NP2; j++) o[j] = __ffma2_rn(gw[i][j], rs, __ffma2_rn(h[i][j], c2, c1));
             if (RES) {
-              float e[V];
-              IO<T>::unpack(rr[i], e);
+              float2 e[NP2];
+              Pairs<T>::unpack(rr[i], e);
 #pragma unroll
-              for (int j = 0; j < V; j++) { o[j] += e[j]; ds[i][j] += e[j]; }
+              for (int j = 0; j < NP2; j++) { o[j] = __fadd2_rn(o[j], e[j]); ds[i][j] = __fadd2_rn(ds[i][j], e[j]); }
             }
-            IO<T>::st(dx + row * D + vi * V, o);
+            *reinterpret_cast<Raw*>(dx + row * D + vi * V) = Pairs<T>::pack(o);
           }
         }
       }
@@ -737,10 +808,11 @@ norm_bwd_pipe_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T*
       const int vi = t + i * G;
       if (vi < nvec) {
 #pragma unroll
-        for (int j = 0; j < V; j++) {
-          comb[((size_t)g * NP + 0) * D + vi * V + j] = dg[i][j];
-          comb[((size_t)g * NP + 1) * D + vi * V + j] = db[i][j];
-          if (RES) comb[((size_t)g * NP + 2) * D + vi * V + j] = ds[i][j];
+        for (int j = 0; j < NP2; j++) {
+          const int c = vi * V + 2 * j;
+          *reinterpret_cast<float2*>(comb + ((size_t)g * NP + 0) * D + c) = dg[i][j];
+          *reinterpret_cast<float2*>(comb + ((size_t)g * NP + 1) * D + c) = db[i][j];
+          if (RES) *reinterpret_cast<float2*>(comb + ((size_t)g * NP + 2) * D + c) = ds[i][j];
         }
       }
     }
@@ -758,19 +830,22 @@ norm_bwd_pipe_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T*
 // Geometry of the pipelined kernels for a row of `row_bytes`: rows per group per tile
 // (tiles of about 12 KB per source), ring depth within `budget` bytes of shared memory.
 struct PipePlan { int KR, S; size_t smem; bool ok; };
-inline PipePlan pipe_plan(size_t row_bytes, int NG, int nsrc, size_t extra_bytes, size_t comb_bytes) {
+inline PipePlan pipe_plan(size_t row_bytes, int NG, int nsrc, size_t extra_bytes, size_t comb_bytes,
+                          size_t limit = 110 * 1024, size_t target = 96 * 1024) {
   PipePlan p;
-  size_t tile = (size_t)NG * row_bytes;
+  const size_t tile = (size_t)NG * row_bytes;
   p.KR = 1;
   while ((size_t)(p.KR * 2) * tile <= 12288) p.KR *= 2;
   const size_t stage = (size_t)p.KR * tile * nsrc;
-  const size_t budget = 96 * 1024;
-  int S = (int)(budget / stage);
+  // limit: shared memory one CTA may take (110 KB: two CTAs per SM; 72 KB: three); target: ring size
+  const size_t avail = limit > kPipeHeader + extra_bytes ? limit - kPipeHeader - extra_bytes : 0;
+  int S = (int)(avail / stage);
   if (S > kPipeMaxStages) S = kPipeMaxStages;
-  while (S >= 2 && (size_t)S * stage < comb_bytes) S++;  // the combine buffer reuses the ring
+  while (S > 2 && (size_t)S * stage > target && (size_t)(S - 1) * stage >= comb_bytes) S--;
   p.S = S;
   p.smem = kPipeHeader + (size_t)S * stage + extra_bytes;
-  p.ok = S >= 2 && S <= kPipeMaxStages && p.smem <= 110 * 1024;
+  // the combine buffer of the backward reuses the ring once it has drained
+  p.ok = S >= 2 && (size_t)S * stage >= comb_bytes && p.smem <= limit;
   return p;
 }
 
@@ -823,7 +898,8 @@ int norm_fwd_t(const void* x, const void* w, const void* b, void* y, float* mean
     int rc = 1;
 #define GB_FWDP(G, VPT)                                                                                  \
     {                                                                                                    \
-      PipePlan pl = pipe_plan((size_t)D * sizeof(T), kPipeConsumers / G, 1, 2 * (size_t)D * sizeof(TW), 0); \
+      PipePlan pl = pipe_plan((size_t)D * sizeof(T), kPipeConsumers / G, 1, 2 * (size_t)D * sizeof(float), 0, \
+                              72 * 1024, 56 * 1024); \
       if (pl.ok) {                                                                                       \
         auto kern = norm_fwd_pipe_kernel<T, TW, G, VPT, RMS>;                                            \
         static bool attr_set = false;                                                                    \
@@ -832,7 +908,7 @@ int norm_fwd_t(const void* x, const void* w, const void* b, void* y, float* mean
           attr_set = true;                                                                               \
         }                                                                                                \
         const long long ntiles = (rows + (kPipeConsumers / G) * pl.KR - 1) / ((kPipeConsumers / G) * pl.KR); \
-        const int grid = (int)(ntiles < 296 ? ntiles : 296);                                             \
+        const int grid = (int)(ntiles < 444 ? ntiles : 444);                                             \
         kern<<<grid, kPipeThreads, pl.smem, s>>>((const T*)x, (const TW*)w, (const TW*)b, (T*)y, mean, rstd, \
                                                  rows, D, eps, pl.KR, pl.S, gbh::status_ptr());          \
         rc = 0;                                                                                          \
@@ -876,7 +952,7 @@ int norm_bwd_pipe_launch(const void* x, const void* dy, const void* dres, const 
 #define GB_BWDP(G, VPT)                                                                                  \
     {                                                                                                    \
       constexpr int NGc = kPipeConsumers / G;                                                            \
-      PipePlan pl = pipe_plan((size_t)D * sizeof(T), NGc, NP, (size_t)D * sizeof(TW),                    \
+      PipePlan pl = pipe_plan((size_t)D * sizeof(T), NGc, NP, (size_t)D * sizeof(float),                    \
                               want_param ? (size_t)NGc * NP * D * sizeof(float) : 0);                    \
       if (pl.ok) {                                                                                       \
         auto kern = norm_bwd_pipe_kernel<T, TW, G, VPT, RMS, RES>;                                       \
@@ -894,7 +970,7 @@ int norm_bwd_pipe_launch(const void* x, const void* dy, const void* dres, const 
         rc = 0;                                                                                          \
       }                                                                                                  \
     }
-  if (RES) { GB_PIPE_DISPATCH_RES(GB_BWDP) } else { GB_PIPE_DISPATCH_BWD(GB_BWDP) }
+  GB_PIPE_DISPATCH_RES(GB_BWDP)
 #undef GB_BWDP
   if (rc != 0) return 1;
   GB_CUDA_OK(cudaGetLastError());

@@ -244,9 +244,21 @@ def _time_ms(fn, iters: int, dev: torch.device) -> float:
     return e0.elapsed_time(e1) / iters
 
 
+def _native_loop(name: str, *args) -> float:
+    """Runs one of the library's own benchmark loops (csrc/gemm_exact.cu): buffers, warm-up, the
+    timed loop and the events all live on the native side, as in the reference's library."""
+    ms = float(getattr(_l.lib(), name)(*args))
+    if ms < 0:
+        raise RuntimeError(f"{name}: device allocation or launch failed ({_l.lib().gb_last_error().decode()})")
+    _l.kernel_count += 5 + int(args[-2].value)      # informational: launches made by the loop
+    return ms
+
+
 def BenchMatMulDev(m: int, k: int, n: int, iters: int, f32: bool = False, device=None) -> float:
     """Resident ``(m,k) @ (k,n)`` in float64 (float32 when ``f32``), ms per iteration."""
     dev = _device(device)
+    if dev.type == "cuda":
+        return _native_loop("gb_bench_matmul", _l.I(m), _l.I(k), _l.I(n), _l.I(iters), _l.I(2 if f32 else 3))
     dt = torch.float32 if f32 else torch.float64
     a, b = torch.randn(m, k, dtype=dt, device=dev), torch.randn(k, n, dtype=dt, device=dev)
     c = torch.empty(m, n, dtype=dt, device=dev)
@@ -255,6 +267,9 @@ def BenchMatMulDev(m: int, k: int, n: int, iters: int, f32: bool = False, device
 
 def BenchMatMulF16Dev(m: int, k: int, n: int, iters: int, dtype: torch.dtype = torch.float16, device=None) -> float:
     dev = _device(device)
+    if dev.type == "cuda":
+        return _native_loop("gb_bench_matmul", _l.I(m), _l.I(k), _l.I(n), _l.I(iters),
+                            _l.I(0 if dtype == torch.bfloat16 else 1))
     a, b = torch.randn(m, k, dtype=dtype, device=dev), torch.randn(k, n, dtype=dtype, device=dev)
     c = torch.empty(m, n, dtype=dtype, device=dev)
     return _time_ms(lambda: _gemm(a, b, out=c), iters, dev)
@@ -262,6 +277,8 @@ def BenchMatMulF16Dev(m: int, k: int, n: int, iters: int, dtype: torch.dtype = t
 
 def BenchAddDev(n: int, iters: int, f32: bool = False, device=None) -> float:
     dev = _device(device)
+    if dev.type == "cuda":
+        return _native_loop("gb_bench_add", _l.L(n), _l.I(iters), _l.I(int(f32)))
     dt = torch.float32 if f32 else torch.float64
     a, b = torch.randn(n, dtype=dt, device=dev), torch.randn(n, dtype=dt, device=dev)
     return _time_ms(lambda: _ew.binary_forward("add", a, b), iters, dev)
@@ -272,6 +289,8 @@ def BenchFlashAttn(BH: int, S: int, d: int, iters: int, causal: bool = False,
     """Forward attention on resident ``(BH, S, d)`` inputs, ms per iteration."""
     dev = _device(device)
     dt = _attn_dtype(dtype, dev, d)
+    if dev.type == "cuda" and dt == torch.bfloat16 and d in (64, 128):
+        return _native_loop("gb_bench_flash_attn", _l.I(BH), _l.I(S), _l.I(d), _l.I(iters), _l.I(int(causal)))
     q, k, v = (torch.randn(BH, S, d, dtype=dt, device=dev) for _ in range(3))
     q4, k4, v4 = (_bshd(t, BH, S, d, dt, dev) for t in (q, k, v))
     if _attn._kernel_ok(q4, k4, v4):

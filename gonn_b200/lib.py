@@ -33,7 +33,7 @@ kernel_count = 0  # kernels those calls launched (read by bench.py)
 KERNELS_PER_CALL = {
     "gb_norm_bwd": 2, "gb_ce_fwd": 2, "gb_flash_bwd": 2, "gb_embedding_bwd": 5,
     "gb_status_read": 0, "gb_comm_alloc": 0, "gb_comm_open": 0, "gb_comm_emulate": 0,
-    "gb_comm_free": 0, "gb_reduce": 1,
+    "gb_comm_free": 0, "gb_reduce": 1, "gb_gemm_f32x3": 5, "gb_norm_bwd_res": 2,
 }
 
 
@@ -69,6 +69,10 @@ def lib() -> ctypes.CDLL:
                     f"{LIB_PATH} is missing: run `python -m gonn_b200.build` first")
             l = ctypes.CDLL(LIB_PATH)
             l.gb_last_error.restype = ctypes.c_char_p
+            l.gb_gemm_f32x3_workspace.restype = c_longlong
+            l.gb_gemm_f32x3_workspace.argtypes = [c_int, c_int, c_int, c_int]
+            for name in ("gb_bench_matmul", "gb_bench_add", "gb_bench_flash_attn"):
+                getattr(l, name).restype = c_double
             _lib = l
     return _lib
 

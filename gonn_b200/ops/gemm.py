@@ -3,8 +3,10 @@
 Mirrors the reference's backend contract ``Gemm(a, b, batch, m, k, n, transA,
 transB)`` (backend/backend.go:61-78): row-major operands, contiguous batches,
 ``op(A)`` is (m,k) and is stored (k,m) when ``trans_a``.  On CUDA, bf16/fp16
-operands run on the tcgen05 kernel (csrc/gemm.cu) and fp32/fp64 on the SIMT
-kernel; on CPU the same contract is evaluated with torch as the oracle path.
+operands run on the tcgen05 kernel (csrc/gemm.cu); fp64 on the double-precision
+tensor-core kernel and fp32 as three bf16 planes per operand on tcgen05
+(csrc/gemm_exact.cu), with the register-tiled SIMT kernel for small or unaligned
+problems; on CPU the same contract is evaluated with torch as the oracle path.
 """
 from __future__ import annotations
 
@@ -45,6 +47,28 @@ def _dact_ref(pre, mode):
 
 _WS_BYTES = 256 << 20
 _ws_cache = {}
+_x3_cache = {}
+_FP32_MODE = "bf16x3"
+
+
+def set_fp32_gemm_mode(mode: str) -> str:
+    """``"bf16x3"`` (default): large fp32 products run on the tensor cores as three bf16 planes
+    per operand (error at the rounding level of an fp32 product); ``"simt"``: always the
+    register-tiled fp32 FMA kernel.  Returns the previous mode."""
+    global _FP32_MODE
+    if mode not in ("bf16x3", "simt"):
+        raise ValueError("fp32 GEMM mode must be 'bf16x3' or 'simt'")
+    old, _FP32_MODE = _FP32_MODE, mode
+    return old
+
+
+def _x3_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    key = (device.index, _l.current_stream_handle())
+    buf = _x3_cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _x3_cache[key] = buf
+    return buf
 
 
 def _workspace(device: torch.device) -> torch.Tensor:
@@ -155,6 +179,25 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         sA = a2.stride(0) if a2.dim() == 3 and a2.shape[0] > 1 else 0
         sB = b2.stride(0) if b2.dim() == 3 and b2.shape[0] > 1 else 0
         sC = out.stride(0) if batched else 0
+        if a.dtype == torch.float64 and M >= 64 and N >= 64 and K >= 16:
+            _l.call("gb_gemm_f64", _l.ptr(a2), _l.ptr(b2), _l.ptr(out), _l.I(M), _l.I(N), _l.I(K), _l.I(batch),
+                    _l.I(int(trans_a)), _l.I(int(trans_b)), _l.L(lda), _l.L(ldb), _l.L(out.stride(-2)), _l.L(sA),
+                    _l.L(sB), _l.L(sC), _l.D(alpha), _l.I(int(beta)), _l.stream_ptr())
+            return out
+        if (a.dtype == torch.float32 and out.dtype == torch.float32 and _FP32_MODE == "bf16x3"
+                and 2.0 * M * N * K * batch >= 2.0 ** 28 and M >= 128 and N >= 128
+                and (K % 8 == 0 or (not trans_a and trans_b)) and out.stride(-2) % 4 == 0
+                and out.data_ptr() % 16 == 0):
+            need = int(_l.lib().gb_gemm_f32x3_workspace(M, N, K, batch))
+            if need <= (4 << 30):
+                ws3 = _x3_workspace(a.device, need)
+                ws = _workspace(a.device) if M * N * batch * 4 * 2 <= _WS_BYTES else None
+                _l.call("gb_gemm_f32x3", _l.ptr(a2), _l.ptr(b2), _l.ptr(out), _l.I(M), _l.I(N), _l.I(K),
+                        _l.I(batch), _l.I(int(trans_a)), _l.I(int(trans_b)), _l.L(lda), _l.L(ldb),
+                        _l.L(out.stride(-2)), _l.L(sA), _l.L(sB), _l.L(sC), _l.F(alpha), _l.I(int(beta)),
+                        _l.ptr(ws3), _l.L(ws3.numel()), _l.ptr(ws), _l.L(_WS_BYTES if ws is not None else 0),
+                        _l.stream_ptr())
+                return out
         _l.call("gb_gemm_simt", _l.ptr(a2), _l.ptr(b2), _l.ptr(out), _l.I(M), _l.I(N), _l.I(K),
                 _l.I(batch), _l.I(int(trans_a)), _l.I(int(trans_b)), _l.L(lda), _l.L(ldb),
                 _l.L(out.stride(-2)), _l.L(sA), _l.L(sB), _l.L(sC), _l.I(_l.dtype_code(a.dtype)),

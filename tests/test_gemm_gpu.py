@@ -32,8 +32,14 @@ def test_layouts(ta, tb, shape, bn, status_ok):
     a, b = _mk(M, N, K, ta, tb)
     c = gemm(a, b, trans_a=ta, trans_b=tb, force_bn=bn)
     ref = _ref(a, b, ta, tb)
-    tol = 0.01 * ref.abs().max().item() + 0.05
-    assert (c.float() - ref).abs().max().item() < tol
+    _close16(c, ref)
+
+
+def _close16(c, ref):
+    """A 16-bit result of an fp32 accumulation: every element within one rounding step of its
+    own magnitude (2^-8 relative for bf16) plus the fp32 accumulation error of the row."""
+    assert ((c.float() - ref).abs() <= 2.0 ** -8 * ref.abs() + 2e-3).all(), \
+        float(((c.float() - ref).abs() - 2.0 ** -8 * ref.abs()).max())
 
 
 @pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False)])
@@ -41,7 +47,7 @@ def test_batched(ta, tb, status_ok):
     a, b = _mk(192, 160, 96, ta, tb, batch=5)
     c = gemm(a, b, trans_a=ta, trans_b=tb)
     ref = _ref(a, b, ta, tb)
-    assert (c.float() - ref).abs().max().item() < 0.01 * ref.abs().max().item() + 0.05
+    _close16(c, ref)
 
 
 def test_batch_broadcast(status_ok):
@@ -49,7 +55,85 @@ def test_batch_broadcast(status_ok):
     b = torch.randn(64, 96, device="cuda", dtype=torch.bfloat16)
     c = gemm(a, b)
     ref = a.float() @ b.float()
-    assert (c.float() - ref).abs().max().item() < 0.2
+    _close16(c, ref)
+
+
+@pytest.mark.parametrize("ta", [False, True])
+@pytest.mark.parametrize("tb", [False, True])
+@pytest.mark.parametrize("shape", [(256, 256, 256), (200, 136, 72), (129, 65, 17), (1000, 64, 520)])
+def test_fp64_tensor_core_gemm(ta, tb, shape, status_ok):
+    """The double-precision tensor-core kernel against torch's float64 product: agreement at
+    the level of float64 summation-order differences, all layouts, ragged edges."""
+    M, N, K = shape
+    a, b = _mk(M, N, K, ta, tb, dtype=torch.float64)
+    c = gemm(a, b, trans_a=ta, trans_b=tb)
+    A = a.transpose(-1, -2) if ta else a
+    B = b.transpose(-1, -2) if tb else b
+    ref = A @ B
+    assert c.dtype == torch.float64
+    assert (c - ref).abs().max().item() < 1e-12 * (K ** 0.5) * (1 + ref.abs().max().item())
+
+
+def test_fp64_tensor_core_batched_alpha_beta(status_ok):
+    a, b = _mk(192, 160, 96, False, True, batch=3, dtype=torch.float64)
+    out = torch.randn(3, 192, 160, device="cuda", dtype=torch.float64)
+    want = out + 0.5 * (a @ b.transpose(-1, -2))
+    gemm(a, b, trans_b=True, out=out, beta=True, alpha=0.5)
+    assert (out - want).abs().max().item() < 1e-11
+    # a broadcast right operand
+    b1 = torch.randn(96, 160, device="cuda", dtype=torch.float64)
+    c = gemm(a, b1)
+    assert (c - a @ b1).abs().max().item() < 1e-11
+
+
+@pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("shape", [(1024, 1024, 1024), (640, 520, 1000)])
+def test_fp32_three_plane_gemm(ta, tb, shape, status_ok):
+    """fp32 products on the tensor cores (three bf16 planes per operand): against float64 math the
+    error must stay at the level of an fp32 FMA chain, measured against the same chain in torch."""
+    from gonn_b200.ops.gemm import set_fp32_gemm_mode
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(M + K)
+    sa = (K, M) if ta else (M, K)
+    sb = (N, K) if tb else (K, N)
+    a = torch.randn(sa, device="cuda", generator=g) * torch.exp(torch.randn(sa, device="cuda", generator=g))
+    b = torch.randn(sb, device="cuda", generator=g)
+    A = a.transpose(-1, -2) if ta else a
+    B = b.transpose(-1, -2) if tb else b
+    ref = A.double() @ B.double()
+    scale = (A.double().abs() @ B.double().abs())           # size of the terms that were summed
+    old = set_fp32_gemm_mode("bf16x3")
+    try:
+        c = gemm(a, b, trans_a=ta, trans_b=tb)
+        set_fp32_gemm_mode("simt")
+        c_simt = gemm(a, b, trans_a=ta, trans_b=tb)
+    finally:
+        set_fp32_gemm_mode(old)
+    err = ((c.double() - ref).abs() / scale).max().item()
+    err_simt = ((c_simt.double() - ref).abs() / scale).max().item()
+    assert c.dtype == torch.float32
+    # both within a few units of 2^-24 of the summed magnitude (the three passes by magnitude
+    # class are what keeps the plane scheme there: one pass over all six products loses the low planes)
+    assert err < 6e-7, (err, err_simt)
+    assert err_simt < 6e-7, err_simt
+
+
+def test_fp32_three_plane_alpha_beta_batched_nonfinite(status_ok):
+    a = torch.randn(2, 512, 512, device="cuda")
+    b = torch.randn(2, 512, 512, device="cuda")
+    out = torch.randn(2, 512, 512, device="cuda")
+    want = out.double() + 2.0 * (a.double() @ b.double().transpose(-1, -2))
+    gemm(a, b, trans_b=True, out=out, beta=True, alpha=2.0)
+    assert (out.double() - want).abs().max().item() < 2e-4
+    a2 = torch.randn(512, 1024, device="cuda")
+    b2 = torch.randn(1024, 512, device="cuda")
+    a2[3, 5] = float("inf")
+    c = gemm(a2, b2)
+    row = c[3]
+    assert torch.isinf(row).all() or torch.isnan(row).any()          # the infinite entry stays visible
+    ok = torch.ones(512, dtype=torch.bool, device="cuda")
+    ok[3] = False
+    assert torch.isfinite(c[ok]).all()
 
 
 def test_fp16_and_fp32_out(status_ok):
