@@ -15,8 +15,9 @@
 //                   through their symmetric buffers, publish mean / invstd, update
 //                   the running statistics] then every CTA normalises (+ ReLU)
 //   bn_bwd_apply    the same structure for dx
-// CTA 0 is dispatched first, so the CTAs that wait for its result never wait for a CTA
-// that cannot run; its own wait for the peers is bounded.
+// The CTA that finalises is elected at run time: the first CTA to swap this launch's serial
+// number into an election word.  It is running by construction, so the CTAs that wait for its
+// result never wait for a CTA that has not been dispatched; its own wait for the peers is bounded.
 #include "comm_dev.cuh"
 
 using namespace gb;
@@ -117,6 +118,8 @@ struct BnArgs {
   int rank, world;
   long long slot_off;  // byte offset of the exchange area inside the symmetric buffer
   unsigned int epoch;
+  const unsigned int* epoch_base;   // added to epoch / ready_val at run time when not null
+  const unsigned int* serial_base;  // (launches captured in a CUDA graph: see comm_dev.cuh)
   int N, C;
   long long S;
   float eps, momentum;
@@ -128,7 +131,8 @@ struct BnArgs {
   float* running_var;
   const void* w;           // fp32 affine weight / bias, may be null
   const void* b;
-  int* ready;              // device flag: epoch value when stats are valid
+  int* ready;              // device flag: this launch's serial number once the stats are valid
+  int* elect;              // election word: the first CTA to swap the serial number in finalises
   int ready_val;
   int split;               // 1: the statistics were finalised by a separate launch (one rank): no flag, no wait
   int* status;
@@ -153,7 +157,8 @@ __device__ void combine_and_exchange(const BnArgs& a, float* out2c, float* count
       for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) slot[i] = out2c[i];
       if (threadIdx.x == 0) slot[2 * C] = count;
     }
-    if (!cta_barrier(a.pt, a.rank, a.world, 7, 0, a.epoch, a.status, sm_flag)) {
+    const unsigned int epoch = dyn_value(a.epoch, a.epoch_base);
+    if (!cta_barrier(a.pt, a.rank, a.world, 7, 0, epoch, a.status, sm_flag)) {
       *count_out = count;
       return;
     }
@@ -167,18 +172,26 @@ __device__ void combine_and_exchange(const BnArgs& a, float* out2c, float* count
     for (int p = 0; p < a.world; p++) cs += __ldcg(mine + (long long)p * n + 2 * C);
     count = cs;
     // the slots may be rewritten only after everyone has read them
-    cta_barrier(a.pt, a.rank, a.world, 8, 0, a.epoch + 1, a.status, sm_flag);
+    cta_barrier(a.pt, a.rank, a.world, 8, 0, epoch + 1, a.status, sm_flag);
   }
   *count_out = count;
   __syncthreads();
 }
 
-__device__ __forceinline__ bool wait_ready(const BnArgs& a) {
+// True in exactly one CTA of the launch: the first to arrive.
+__device__ __forceinline__ bool elect_leader(const BnArgs& a, int ready_val) {
+  __shared__ int leader;
+  if (threadIdx.x == 0) leader = atomicExch(a.elect, ready_val) != ready_val;
+  __syncthreads();
+  return leader != 0;
+}
+
+__device__ __forceinline__ bool wait_ready(const BnArgs& a, int ready_val) {
   __shared__ int ok_flag;
   if (threadIdx.x == 0) {
     const uint64_t t0 = globaltimer_ns();
     int ok = 1;
-    while (*((volatile int*)a.ready) != a.ready_val) {
+    while (*((volatile int*)a.ready) != ready_val) {
       if (globaltimer_ns() - t0 > kWaitBudgetNs) {
         set_status(a.status, ST_COMM_TIMEOUT, 77);
         ok = 0;
@@ -256,13 +269,14 @@ bn_apply_kernel(const T* __restrict__ x, T* __restrict__ y, const BnArgs a) {
   __shared__ float s_count;
   const int C = a.C;
   if (a.training && !a.split) {
-    if (blockIdx.x == 0) {
+    const int rv = (int)dyn_value((unsigned int)a.ready_val, a.serial_base);
+    if (elect_leader(a, rv)) {
       bn_fwd_finalise(a, &sm_flag, &s_count);
       __threadfence();
       __syncthreads();
-      if (threadIdx.x == 0) atomicExch(a.ready, a.ready_val);
+      if (threadIdx.x == 0) atomicExch(a.ready, rv);
     }
-    if (!wait_ready(a)) return;
+    if (!wait_ready(a, rv)) return;
   }
   const float* w = (const float*)a.w;
   const float* b = (const float*)a.b;
@@ -315,13 +329,14 @@ bn_bwd_apply_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __rest
   __shared__ float s_count;
   const int C = a.C;
   if (!a.split) {
-    if (blockIdx.x == 0) {
+    const int rv = (int)dyn_value((unsigned int)a.ready_val, a.serial_base);
+    if (elect_leader(a, rv)) {
       bn_bwd_finalise(a, dgamma, dbeta, &sm_flag, &s_count);
       __threadfence();
       __syncthreads();
-      if (threadIdx.x == 0) atomicExch(a.ready, a.ready_val);
+      if (threadIdx.x == 0) atomicExch(a.ready, rv);
     }
-    if (!wait_ready(a)) return;
+    if (!wait_ready(a, rv)) return;
   }
   const float* w = (const float*)a.w;
   const long long planes = (long long)a.N * C;
@@ -352,7 +367,6 @@ bn_bwd_apply_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __rest
   }
 }
 
-int g_ready_counter = 0;
 
 inline int grid_for(long long work) {
   long long g = (work + 255) / 256;
@@ -369,13 +383,17 @@ void fill_comm(BnArgs& a, int sync, long long slot_off) {
     a.slot_off = slot_off;
     if (a.world > 1) a.epoch = gbh::comm_next_epochs(2);
   }
+  a.epoch_base = gbh::comm_epoch_base_ptr();
+  a.serial_base = gbh::comm_serial_base_ptr();
+  a.ready_val = (int)gbh::comm_next_serials(1);
 }
 
 }  // namespace
 
 enum { DT_BF16 = 0, DT_F16 = 1, DT_F32 = 2 };
 
-// floats of workspace the BatchNorm entry points need: partials + sums + ready flag
+// floats of workspace the BatchNorm entry points need: partials + sums + ready flag + election
+// word; the caller zeroes it once when it allocates it (serial numbers start at 1)
 GB_EXPORT long long gb_bn_workspace_floats(int C) { return (long long)C * kSplits * 2 + 2 * C + 8; }
 
 // Forward.  x, y: (N, C, S).  stats: [2C] (mean | invstd), written in training and read
@@ -398,7 +416,7 @@ GB_EXPORT int gb_bn_fwd(int dtype, const void* x, void* y, const float* w, const
   a.N = N; a.C = C; a.S = S; a.eps = eps; a.momentum = momentum; a.training = training; a.relu = relu;
   a.part = work; a.sums = work + (long long)C * kSplits * 2; a.stats = stats;
   a.ready = (int*)(work + (long long)C * kSplits * 2 + 2 * C);
-  a.ready_val = ++g_ready_counter;
+  a.elect = a.ready + 1;
   a.running_mean = running_mean; a.running_var = running_var; a.w = w; a.b = b;
   a.split = a.world == 1;
   a.status = gbh::status_ptr();
@@ -438,7 +456,7 @@ GB_EXPORT int gb_bn_bwd(int dtype, const void* x, const void* dy, void* dx, cons
   a.N = N; a.C = C; a.S = S; a.training = 1;
   a.part = work; a.sums = work + (long long)C * kSplits * 2; a.stats = const_cast<float*>(stats);
   a.ready = (int*)(work + (long long)C * kSplits * 2 + 2 * C);
-  a.ready_val = ++g_ready_counter;
+  a.elect = a.ready + 1;
   a.w = w;
   a.split = a.world == 1;
   a.status = gbh::status_ptr();

@@ -45,6 +45,10 @@ struct Comm {
   PeerTable peers;
   bool opened[kMaxWorld] = {false};
   unsigned int epoch = 0;
+  unsigned int serial = 0;
+  // capture mode (see comm_dev.cuh): device words holding the bases, and relative counters
+  unsigned int* cap_bases = nullptr;  // [0] epoch base, [1] serial base
+  unsigned int cap_epochs = 0, cap_serials = 0;
 };
 
 Comm g_comm;
@@ -61,6 +65,8 @@ struct StepArgs {
   int dtype_bf16;            // element type: 0 fp16, 1 bf16, 2 fp32 (mode 0 only)
   int interleave;            // work mapping of the CTAs (see the kernel)
   unsigned int epoch;        // barrier epochs epoch (start) and epoch+1 (end)
+  const unsigned int* epoch_base;  // added to `epoch` at run time when not null (graph replay)
+  const float* hyper_dev;    // when not null: lr .. gscale are read from these 8 floats at run time
   float* master[kMaxWorld];  // per emulated rank (index 0 in real runs): fp32 shard state
   float* m[kMaxWorld];
   float* v[kMaxWorld];
@@ -94,7 +100,14 @@ fused_step_kernel(const StepArgs a) {
   const int cta = blockIdx.x, G = gridDim.x;
   if (threadIdx.x == 0) sm_flag = 0;
   __syncthreads();
-  if (W > 1 && !cta_barrier(a.pt, rank, W, 0, cta, a.epoch, a.status, &sm_flag)) return;
+  const unsigned int epoch = dyn_value(a.epoch, a.epoch_base);
+  if (W > 1 && !cta_barrier(a.pt, rank, W, 0, cta, epoch, a.status, &sm_flag)) return;
+  float lr = a.lr, wd = a.wd, b1 = a.b1, b2 = a.b2, eps = a.eps, bc1 = a.bc1, bc2 = a.bc2, gscale = a.gscale;
+  if (a.hyper_dev) {
+    lr = __ldg(a.hyper_dev); wd = __ldg(a.hyper_dev + 1); b1 = __ldg(a.hyper_dev + 2); b2 = __ldg(a.hyper_dev + 3);
+    eps = __ldg(a.hyper_dev + 4); bc1 = __ldg(a.hyper_dev + 5); bc2 = __ldg(a.hyper_dev + 6);
+    gscale = __ldg(a.hyper_dev + 7);
+  }
 
   const int epv = a.dtype_bf16 == 2 ? 4 : 8;  // elements per 16-byte vector
   const long long L = a.n / W;          // elements in one rank's slice
@@ -115,7 +128,7 @@ fused_step_kernel(const StepArgs a) {
     vstep = blockDim.x;
   }
   const long long slice_vec0 = (long long)rank * nvec;  // vector index of the slice start
-  const float inv = a.gscale / (float)W;
+  const float inv = gscale / (float)W;
   const int sidx = a.emulate ? rank : 0;
   float* master = a.master[sidx];
   float* mm = a.m[sidx];
@@ -135,7 +148,7 @@ fused_step_kernel(const StepArgs a) {
         ((float4*)((char*)a.pt.base[q] + a.grad_off))[slice_vec0 + i] = acc;
       }
     }
-    if (W > 1) cta_barrier(a.pt, rank, W, 1, cta, a.epoch + 1, a.status, &sm_flag);
+    if (W > 1) cta_barrier(a.pt, rank, W, 1, cta, epoch + 1, a.status, &sm_flag);
     return;
   }
   for (long long i = v0 + threadIdx.x; i < v1; i += vstep) {
@@ -170,10 +183,10 @@ fused_step_kernel(const StepArgs a) {
       for (int j = 0; j < 8; j++) {
         float g = acc[j];
         float p = pw[j];
-        p -= a.lr * a.wd * p;  // decoupled decay first, like optim/adamw.go:77-81
-        float m_ = a.b1 * pm[j] + (1.f - a.b1) * g;
-        float v_ = a.b2 * pv[j] + (1.f - a.b2) * g * g;
-        p -= a.lr * (m_ / a.bc1) / (sqrtf(v_ / a.bc2) + a.eps);
+        p -= lr * wd * p;  // decoupled decay first, like optim/adamw.go:77-81
+        float m_ = b1 * pm[j] + (1.f - b1) * g;
+        float v_ = b2 * pv[j] + (1.f - b2) * g * g;
+        p -= lr * (m_ / bc1) / (sqrtf(v_ / bc2) + eps);
         pw[j] = p; pm[j] = m_; pv[j] = v_;
       }
       mp[0] = *(float4*)&pw[0]; mp[1] = *(float4*)&pw[4];
@@ -189,7 +202,7 @@ fused_step_kernel(const StepArgs a) {
       *dst = out;
     }
   }
-  if (W > 1) cta_barrier(a.pt, rank, W, 1, cta, a.epoch + 1, a.status, &sm_flag);
+  if (W > 1) cta_barrier(a.pt, rank, W, 1, cta, epoch + 1, a.status, &sm_flag);
 }
 
 struct SmallArgs {
@@ -198,6 +211,7 @@ struct SmallArgs {
   long long slot_off;  // byte offset of the exchange area: world slots of n floats
   int n;
   unsigned int epoch;
+  const unsigned int* epoch_base;
   float* io[kMaxWorld];  // in/out vector per emulated rank (index 0 in real runs)
   int* status;
 };
@@ -216,7 +230,8 @@ allreduce_small_kernel(const SmallArgs a) {
     float* slot = (float*)((char*)a.pt.base[p] + a.slot_off) + (long long)rank * a.n;
     for (int i = threadIdx.x; i < a.n; i += blockDim.x) slot[i] = io[i];
   }
-  if (!cta_barrier(a.pt, rank, W, 2, 0, a.epoch, a.status, &sm_flag)) return;
+  const unsigned int epoch = dyn_value(a.epoch, a.epoch_base);
+  if (!cta_barrier(a.pt, rank, W, 2, 0, epoch, a.status, &sm_flag)) return;
   const float* mine = (const float*)((const char*)a.pt.base[rank] + a.slot_off);
   for (int i = threadIdx.x; i < a.n; i += blockDim.x) {
     float s = 0.f;
@@ -224,7 +239,7 @@ allreduce_small_kernel(const SmallArgs a) {
     io[i] = s;
   }
   // slots may be reused by the next call only after everyone has read them
-  cta_barrier(a.pt, rank, W, 3, 0, a.epoch + 1, a.status, &sm_flag);
+  cta_barrier(a.pt, rank, W, 3, 0, epoch + 1, a.status, &sm_flag);
 }
 
 struct BcastArgs {
@@ -232,6 +247,7 @@ struct BcastArgs {
   int rank, world, emulate, root;
   long long off, bytes;
   unsigned int epoch;
+  const unsigned int* epoch_base;
   int* status;
 };
 
@@ -245,7 +261,8 @@ broadcast_kernel(const BcastArgs a) {
   if (threadIdx.x == 0) sm_flag = 0;
   __syncthreads();
   // everyone must have finished with the old contents before root overwrites them
-  if (!cta_barrier(a.pt, rank, W, 4, cta, a.epoch, a.status, &sm_flag)) return;
+  const unsigned int epoch = dyn_value(a.epoch, a.epoch_base);
+  if (!cta_barrier(a.pt, rank, W, 4, cta, epoch, a.status, &sm_flag)) return;
   if (rank == a.root) {
     const long long nvec = a.bytes / 16;
     const uint4* src = (const uint4*)((const char*)a.pt.base[rank] + a.off);
@@ -255,16 +272,16 @@ broadcast_kernel(const BcastArgs a) {
         if (p != rank) ((uint4*)((char*)a.pt.base[p] + a.off))[i] = u;
     }
   }
-  cta_barrier(a.pt, rank, W, 5, cta, a.epoch + 1, a.status, &sm_flag);
+  cta_barrier(a.pt, rank, W, 5, cta, epoch + 1, a.status, &sm_flag);
 }
 
 __global__ void barrier_kernel(const PeerTable pt, int rank_arg, int world, int emulate,
-                               unsigned int epoch, int* status) {
+                               unsigned int epoch, const unsigned int* epoch_base, int* status) {
   __shared__ int sm_flag;
   const int rank = emulate ? (int)blockIdx.y : rank_arg;
   if (threadIdx.x == 0) sm_flag = 0;
   __syncthreads();
-  cta_barrier(pt, rank, world, 6, 0, epoch, status, &sm_flag);
+  cta_barrier(pt, rank, world, 6, 0, dyn_value(epoch, epoch_base), status, &sm_flag);
 }
 
 // Wait for a flag that nobody sets: used by tests of the time-out path.  budget_ns
@@ -371,8 +388,23 @@ GB_EXPORT int gb_comm_free() {
 }
 
 static unsigned int next_epochs(int count) {
+  if (g_comm.cap_bases) {            // capturing: relative to a base the host supplies per replay
+    const unsigned int e = g_comm.cap_epochs;
+    g_comm.cap_epochs += count;
+    return e;
+  }
   unsigned int e = g_comm.epoch + 1;
   g_comm.epoch += count;
+  return e;
+}
+static unsigned int next_serials(int count) {
+  if (g_comm.cap_bases) {
+    const unsigned int e = g_comm.cap_serials;
+    g_comm.cap_serials += count;
+    return e;
+  }
+  unsigned int e = g_comm.serial + 1;
+  g_comm.serial += count;
   return e;
 }
 
@@ -383,7 +415,39 @@ void comm_get(gbc::PeerTable* pt, int* rank, int* world) {
   *world = g_comm.world;
 }
 unsigned int comm_next_epochs(int count) { return next_epochs(count); }
+unsigned int comm_next_serials(int count) { return next_serials(count); }
+const unsigned int* comm_epoch_base_ptr() { return g_comm.cap_bases; }
+const unsigned int* comm_serial_base_ptr() { return g_comm.cap_bases ? g_comm.cap_bases + 1 : nullptr; }
 }  // namespace gbh
+
+// Capture mode for CUDA graphs.  Between begin and end, every kernel that uses barrier epochs
+// or local serial numbers is launched with values counted from zero plus a pointer to
+// `bases` (two device words: epoch base, serial base) that it reads when it runs.  `end`
+// reports how many of each the captured work consumes; before every replay the caller
+// reserves that many with gb_comm_reserve and writes the returned bases into `bases`.
+GB_EXPORT int gb_comm_capture_begin(unsigned int* bases) {
+  if (g_comm.cap_bases) {
+    gbh::set_error("gb_comm_capture_begin: a capture is already open");
+    return gbh::E_BAD_ARG;
+  }
+  g_comm.cap_bases = bases;
+  g_comm.cap_epochs = g_comm.cap_serials = 0;
+  return gbh::E_OK;
+}
+GB_EXPORT int gb_comm_capture_end(unsigned int* counts_out) {
+  counts_out[0] = g_comm.cap_epochs;
+  counts_out[1] = g_comm.cap_serials;
+  g_comm.cap_bases = nullptr;
+  return gbh::E_OK;
+}
+// Reserves `epochs` barrier epochs and `serials` serial numbers; bases_out receives the first of each.
+GB_EXPORT int gb_comm_reserve(unsigned int epochs, unsigned int serials, unsigned int* bases_out) {
+  bases_out[0] = g_comm.epoch + 1;
+  bases_out[1] = g_comm.serial + 1;
+  g_comm.epoch += epochs;
+  g_comm.serial += serials;
+  return gbh::E_OK;
+}
 
 // Work mapping of the fused step: 1 interleaved rows, 0 contiguous ranges, -1 (default)
 // interleaved on one GPU (4.9 vs 3.6 TB/s measured) and contiguous with peers (steady-state
@@ -399,10 +463,14 @@ GB_EXPORT int gb_comm_tune(int interleave) {
 // of world*8.  mode 0: mean of the gradients written to every rank; mode 1:
 // sharded AdamW (master/m/v: this rank's shard of the bucket, n/world floats
 // each) and all-gather of the 16-bit parameters.  hyper: {lr, wd, b1, b2, eps,
-// bc1, bc2, gscale}.  emulate != 0: master/m/v are arrays of `world` pointers.
+// bc1, bc2, gscale}; hyper_dev: when not null, a device copy of the same eight
+// floats that the kernel reads when it runs (a captured launch then follows the
+// values the host writes before each replay).  emulate != 0: master/m/v are
+// arrays of `world` pointers.
 GB_EXPORT int gb_comm_fused_step(int mode, int dtype_bf16, long long grad_off, long long param_off,
                                  long long n, float* const* master, float* const* m, float* const* v,
-                                 const float* hyper, int ctas, int emulate, void* stream) {
+                                 const float* hyper, const float* hyper_dev, int ctas, int emulate,
+                                 void* stream) {
   const int W = g_comm.world;
   if (n % ((long long)W * 8) != 0) {
     gbh::set_error("gb_comm_fused_step: bucket length %lld is not a multiple of world*8", n);
@@ -422,6 +490,8 @@ GB_EXPORT int gb_comm_fused_step(int mode, int dtype_bf16, long long grad_off, l
   a.grad_off = grad_off; a.param_off = param_off; a.n = n; a.mode = mode; a.dtype_bf16 = dtype_bf16;
   a.interleave = g_interleave < 0 ? (W == 1) : (g_interleave != 0);
   a.epoch = W > 1 ? next_epochs(2) : 0;
+  a.epoch_base = g_comm.cap_bases;
+  a.hyper_dev = hyper_dev;
   const int ns = emulate ? W : 1;
   for (int i = 0; i < ns; i++) {
     a.master[i] = master ? master[i] : nullptr;
@@ -449,6 +519,7 @@ GB_EXPORT int gb_comm_allreduce_small(float* const* io, int n, long long slot_of
   a.rank = g_comm.rank; a.world = W; a.emulate = emulate;
   a.slot_off = slot_off; a.n = n;
   a.epoch = next_epochs(2);
+  a.epoch_base = g_comm.cap_bases;
   for (int i = 0; i < (emulate ? W : 1); i++) a.io[i] = io[i];
   a.status = gbh::status_ptr();
   void* args[] = {&a};
@@ -473,6 +544,7 @@ GB_EXPORT int gb_comm_broadcast(int root, long long off, long long bytes, int ct
   a.rank = g_comm.rank; a.world = W; a.emulate = emulate; a.root = root;
   a.off = off; a.bytes = bytes;
   a.epoch = next_epochs(2);
+  a.epoch_base = g_comm.cap_bases;
   a.status = gbh::status_ptr();
   void* args[] = {&a};
   return launch_maybe_coop((const void*)broadcast_kernel, dim3(ctas, emulate ? W : 1), dim3(512), args,
@@ -485,8 +557,9 @@ GB_EXPORT int gb_comm_barrier(int emulate, void* stream) {
   PeerTable pt = g_comm.peers;
   int rank = g_comm.rank, world = W, emu = emulate;
   unsigned int epoch = next_epochs(1);
+  const unsigned int* epoch_base = g_comm.cap_bases;
   int* status = gbh::status_ptr();
-  void* args[] = {&pt, &rank, &world, &emu, &epoch, &status};
+  void* args[] = {&pt, &rank, &world, &emu, &epoch, &epoch_base, &status};
   return launch_maybe_coop((const void*)barrier_kernel, dim3(1, emulate ? W : 1), dim3(32), args, emulate,
                            (cudaStream_t)stream);
 }

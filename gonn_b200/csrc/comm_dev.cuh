@@ -29,6 +29,11 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
   return v;
 }
 
+// value + *base (base may be null): see gbh::comm_next_epochs
+__device__ __forceinline__ unsigned int dyn_value(unsigned int rel, const unsigned int* base) {
+  return base ? rel + __ldcg(base) : rel;
+}
+
 // Barrier between CTA `cta` of all ranks.  Thread t < world handles peer t.
 // Returns false when the wait ran out of budget.
 static __device__ bool cta_barrier(const PeerTable& pt, int rank, int world, int channel, int cta,
@@ -59,5 +64,13 @@ static __device__ bool cta_barrier(const PeerTable& pt, int rank, int world, int
 // host side (comm.cu): the current communicator
 namespace gbh {
 void comm_get(gbc::PeerTable* pt, int* rank, int* world);
+// Barrier epochs (identical sequence on every rank) and local serial numbers (flags that only
+// this rank's kernels compare).  Outside a capture both are absolute and the pointers below are
+// null.  Between gb_comm_capture_begin / _end they count from zero and the kernels add the base
+// they read from device memory at run time (gbc::dyn_value), so that a CUDA graph can be
+// replayed with fresh values: the host writes new bases before every replay.
 unsigned int comm_next_epochs(int count);
+unsigned int comm_next_serials(int count);
+const unsigned int* comm_epoch_base_ptr();
+const unsigned int* comm_serial_base_ptr();
 }

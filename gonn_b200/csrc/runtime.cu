@@ -125,3 +125,24 @@ GB_EXPORT int gb_sm_count() {
 }
 
 GB_EXPORT int gb_abi_version() { return 1; }
+
+namespace {
+struct Words10 { unsigned int u[2]; float f[8]; };
+__global__ void set_words_kernel(unsigned int* up, float* fp, const Words10 w) {
+  if (threadIdx.x < 2 && up) up[threadIdx.x] = w.u[threadIdx.x];
+  if (threadIdx.x < 8 && fp) fp[threadIdx.x] = w.f[threadIdx.x];
+}
+}  // namespace
+
+// Writes two 32-bit words to `words` and eight floats to `floats` (either may be null) in stream
+// order.  The values travel as kernel arguments, so the caller's memory can be reused at once:
+// this is how the per-step bases and optimizer scalars of a replayed CUDA graph are updated.
+GB_EXPORT int gb_set_words(unsigned int* words, unsigned int w0, unsigned int w1, float* floats,
+                           const float* f8, void* stream) {
+  Words10 w;
+  w.u[0] = w0; w.u[1] = w1;
+  for (int i = 0; i < 8; i++) w.f[i] = f8 ? f8[i] : 0.f;
+  set_words_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(words, f8 ? floats : nullptr, w);
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}

@@ -195,7 +195,16 @@ class DistributedDataParallel(torch.nn.Module):
                 b.master = self.flat_params[lo:lo + L].to(torch.float32)
                 b.m = torch.zeros(L, dtype=torch.float32, device=dev)
                 b.v = torch.zeros(L, dtype=torch.float32, device=dev)
+        self._hyper_dev = None      # device copy of the optimizer scalars for captured launches
+        self._capturing = False     # True while a step is being captured into a CUDA graph
         self._reset_step()
+
+    # ---- CUDA-graph support (gonn_b200.utils.graph.GraphedStep) -----------------------------------
+    def graph_hyper_buffer(self) -> torch.Tensor:
+        """Device copy of the eight optimizer scalars that captured launches read at run time."""
+        if self._hyper_dev is None:
+            self._hyper_dev = torch.zeros(8, dtype=torch.float32, device=self.device)
+        return self._hyper_dev
 
     # ---- sink protocol (called by ops) ------------------------------------------------------
     def target(self, p):
@@ -263,7 +272,8 @@ class DistributedDataParallel(torch.nn.Module):
         if self.world == 1 and self.opt is None:
             return  # nothing to reduce and nobody to update
         args = (1 if self.opt is not None else 0, self.dtype, self._grad_off + b.start * self._esz,
-                self._param_off + b.start * self._esz, b.length, b.master, b.m, b.v, self._hyper(), self.comm_ctas)
+                self._param_off + b.start * self._esz, b.length, b.master, b.m, b.v, self._hyper(), self.comm_ctas,
+                self._hyper_dev if self._capturing else None)
         if self.host:
             self.symm.fused_step(*args)
             return

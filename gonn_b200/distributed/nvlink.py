@@ -119,8 +119,10 @@ class SymmetricMemory:
 
     # ---- collectives ------------------------------------------------------------------
     def fused_step(self, mode: int, dtype: torch.dtype, grad_off: int, param_off: int, n: int,
-                   master, m, v, hyper, ctas: int = 32):
-        """See ``gb_comm_fused_step``.  master/m/v: tensors (lists of tensors when emulating)."""
+                   master, m, v, hyper, ctas: int = 32, hyper_dev: torch.Tensor = None):
+        """See ``gb_comm_fused_step``.  master/m/v: tensors (lists of tensors when emulating).
+        ``hyper_dev``: a device tensor of the same eight floats, read by the kernel when it
+        runs (for launches captured in a CUDA graph)."""
         if self.host:
             return self._fused_step_host(mode, dtype, grad_off, param_off, n, master, m, v, hyper)
 
@@ -133,7 +135,7 @@ class SymmetricMemory:
         code = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[dtype]
         _l.call("gb_comm_fused_step", _l.I(mode), _l.I(code),
                 _l.L(self.abs_offset(grad_off)), _l.L(self.abs_offset(param_off)), _l.L(n),
-                arr(master), arr(m), arr(v), hy, _l.I(ctas), _l.I(1 if self.emulate else 0),
+                arr(master), arr(m), arr(v), hy, _l.ptr(hyper_dev), _l.I(ctas), _l.I(1 if self.emulate else 0),
                 _l.stream_ptr())
 
     def all_reduce(self, offset_bytes: int, n: int, dtype: torch.dtype, op: str = "sum", ctas: int = 64):

@@ -1,6 +1,10 @@
 """Convolutions, transposed convolutions, Unfold / Fold (nn/conv.go:17-463, nn/fold.go:45-142).
 
-Forward = im2col by index map (no dense gather matrix) followed by one GEMM per group
+16-bit CUDA tensors with groups = 1 and zero padding run as implicit GEMMs on tcgen05
+(csrc/conv.cu): forward, data gradient and weight gradient gather their operands inside the
+kernel through the window index map, with the bias in the forward epilogue and the weight
+gradient as one GEMM over the whole batch.  Everything else takes the general path:
+forward = im2col by index map (no dense gather matrix) followed by one GEMM per group
 against the flattened weight; the output lands directly in (N, C_out, spatial) layout.
 Transposed convolution is the adjoint: GEMM then col2im.  Options: stride, padding,
 dilation, groups, bias, padding_mode (zeros / reflect / replicate / circular),
@@ -41,6 +45,119 @@ class _ConvGemm(torch.autograd.Function):
         return dw, dcol
 
 
+_INV_CACHE = {}
+
+
+def _inverse_map(idx, S):
+    """inv[s][tap] = the window l whose tap `tap` reads position s (idx[l][tap] == s), or -1.
+    For zero padding each (s, tap) has at most one such window."""
+    import numpy as np
+    key = (idx.shape, hash(idx.tobytes()), S)
+    inv = _INV_CACHE.get(key)
+    if inv is None:
+        L, T = idx.shape
+        inv = np.full((S, T), -1, dtype=np.int32)
+        for t in range(T):
+            ls = np.nonzero(idx[:, t] >= 0)[0]
+            inv[idx[ls, t], t] = ls
+        _INV_CACHE[key] = inv
+    return inv
+
+
+_KTAB_CACHE = {}
+
+
+def _ktab(C, T, S, device):
+    """Device table that splits a contraction index k = c * T + tap into the pair the kernels
+    need: {c * S, tap}, padded with {-1, 0} to a multiple of 128 entries."""
+    import numpy as np
+    key = (C, T, S, str(device))
+    t = _KTAB_CACHE.get(key)
+    if t is None:
+        K = C * T
+        n = (K + 127) // 128 * 128
+        tab = np.zeros((n, 2), dtype=np.int32)
+        tab[:, 0] = -1
+        k = np.arange(K)
+        tab[:K, 0] = (k // T) * S
+        tab[:K, 1] = k % T
+        t = torch.from_numpy(tab).to(device)
+        _KTAB_CACHE[key] = t
+    return t
+
+
+class _ConvImplicit(torch.autograd.Function):
+    """Convolution as implicit GEMMs (csrc/conv.cu): forward, data gradient and weight gradient
+    gather their operands inside the kernels; no (N, L, C*T) column tensor exists."""
+
+    @staticmethod
+    def forward(ctx, x3, weight, bias, idx, S, L):
+        from .. import lib as _l
+        from ..ops.window import device_maps
+        N, C, _ = x3.shape
+        Co = weight.shape[0]
+        T = idx.shape[1]
+        xc = x3.contiguous()
+        wc = weight.contiguous()
+        didx = device_maps(idx, S, x3.device, False)["idx"]
+        y = torch.empty((N, Co, L), dtype=x3.dtype, device=x3.device)
+        _l.call("gb_conv_igemm", _l.I(_l.dtype_code(x3.dtype)), _l.ptr(xc), _l.ptr(wc), _l.ptr(_ktab(C, T, S, x3.device)),
+                _l.ptr(didx), _l.ptr(bias), _l.ptr(y), _l.I(N), _l.I(C), _l.I(S), _l.I(L), _l.I(T), _l.I(Co),
+                _l.stream_ptr())
+        ctx.save_for_backward(xc, wc)
+        ctx.geom = (idx, S, L, T)
+        ctx.weight_ref, ctx.bias_ref = weight, bias
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .. import lib as _l
+        from ..ops.linear import emit_grad
+        from ..ops.window import device_maps
+        xc, wc = ctx.saved_tensors
+        idx, S, L, T = ctx.geom
+        N, C, _ = xc.shape
+        Co = wc.shape[0]
+        dyc = dy.contiguous()
+        dt = _l.dtype_code(xc.dtype)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            inv = device_maps(_inverse_map(idx, S), L, xc.device, False)["idx"]
+            wt = wc.view(Co, C, T).permute(1, 0, 2).contiguous()        # (C_in, C_out * T)
+            dx = torch.empty_like(xc)
+            _l.call("gb_conv_igemm", _l.I(dt), _l.ptr(dyc), _l.ptr(wt), _l.ptr(_ktab(Co, T, L, xc.device)), _l.ptr(inv),
+                    None, _l.ptr(dx), _l.I(N), _l.I(Co), _l.I(L), _l.I(S), _l.I(T), _l.I(C), _l.stream_ptr())
+        if ctx.needs_input_grad[1]:
+            didx = device_maps(idx, S, xc.device, False)["idx"]
+            splits = int(_l.lib().gb_conv_wgrad_splits(N, L, Co, C, T))
+            part = torch.empty(splits * Co * C * T, dtype=torch.float32, device=xc.device)
+            w = ctx.weight_ref
+            sink = getattr(w, "_gb_sink", None)
+            if sink is not None:
+                buf, fresh = sink.target(w)
+                out, beta = buf, not fresh
+            else:
+                out, beta = torch.empty(Co * C * T, dtype=xc.dtype, device=xc.device), False
+            _l.call("gb_conv_wgrad", _l.I(dt), _l.ptr(xc), _l.ptr(dyc), _l.ptr(_ktab(C, T, S, xc.device)), _l.ptr(didx),
+                    _l.ptr(out), _l.ptr(part), _l.I(N), _l.I(C), _l.I(S), _l.I(L), _l.I(T), _l.I(Co), _l.I(int(beta)),
+                    _l.stream_ptr())
+            if sink is not None:
+                sink.ready(w)
+            else:
+                dw = out.view(w.shape)
+        if ctx.bias_ref is not None and ctx.needs_input_grad[2]:
+            per_image = reduce_axis(dyc, 2, "sum", out_dtype=torch.float32)          # (N, Co)
+            db = emit_grad(ctx.bias_ref, reduce_axis(per_image, 0, "sum").to(dyc.dtype))
+        return dx, dw, db, None, None, None
+
+
+def _implicit_ok(x, module):
+    import math as _m
+    return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and module.groups == 1
+            and module.padding_mode == "zeros" and module.weight.dtype == x.dtype and x.shape[0] <= 65535
+            and _m.prod(module.kernel_size) <= 32 and x[0].numel() < 2 ** 31)
+
+
 def _kpad(k, dtype):
     return (k + 7) // 8 * 8 if dtype in (torch.bfloat16, torch.float16) else k
 
@@ -78,6 +195,11 @@ class _ConvNd(Module):
         K = cg * idx.shape[1]
         kp = _kpad(K, x.dtype)
         x3 = x.reshape(N, self.in_channels, S)
+        if _implicit_ok(x, self):
+            # the parameter itself goes in (its data is (C_out, C_in * T) when read flat), so that the
+            # backward finds the gradient sink a data-parallel wrapper may have attached to it
+            y = _ConvImplicit.apply(x3, self.weight, self.bias, idx, S, math.prod(outs))
+            return y.reshape(N, self.out_channels, *outs)
         ys = []
         for g in range(G):
             xg = x3 if G == 1 else x3[:, g * cg:(g + 1) * cg]

@@ -56,10 +56,21 @@ class _BatchNormTrain(torch.autograd.Function):
                 None, None, None, None, None, None)
 
 
+_ws_cache = {}
+
+
 def lib_ws(C, dev):
-    f = _l.lib().gb_bn_workspace_floats
-    f.restype = _l.L
-    return torch.empty(int(f(_l.I(C))), dtype=torch.float32, device=dev)
+    """Scratch of one BatchNorm call (partial sums, the finalised sums, the ready flag and the
+    election word), kept per (device, stream, C) and zeroed once: calls on one stream run in
+    order, and the flag words only ever hold serial numbers, which start at 1."""
+    key = (dev.index, _l.current_stream_handle(), C)
+    buf = _ws_cache.get(key)
+    if buf is None:
+        f = _l.lib().gb_bn_workspace_floats
+        f.restype = _l.L
+        buf = torch.zeros(int(f(_l.I(C))), dtype=torch.float32, device=dev)
+        _ws_cache[key] = buf
+    return buf
 
 
 def batch_norm_eval(x, weight, bias, running_mean, running_var, eps, relu=False):

@@ -7,6 +7,7 @@
     python -m gonn_b200.utils.profile_cases norm_bwd 16384 768        # LayerNorm backward
     python -m gonn_b200.utils.profile_cases norm_fork 16384 768       # backward with the residual bypass fused
     python -m gonn_b200.utils.profile_cases step 50000000
+    python -m gonn_b200.utils.profile_cases conv 256 64 128 15 15     # N C_in C_out H W, 3x3: forward + backward
 
 Each case allocates a few hundred MB at most, runs three warm-up launches and
 then five timed launches (CUDA events), and prints one line with the time and the
@@ -100,6 +101,18 @@ def main(argv):
             ms = _time(lambda: torch.autograd.grad((y, xp), (x, w, b, rb), (dy, dp), retain_graph=True))
             nb = 4
         print(f"{kind} {rows}x{D}: {ms:.4f} ms, {nb * rows * D * 2 / ms / 1e6:.1f} GB/s")
+    elif kind == "conv":
+        from ..nn.conv import Conv2d
+        N, Ci, Co, H, W = (int(a) for a in argv[1:6])
+        conv = Conv2d(Ci, Co, 3, dtype=torch.bfloat16, device=dev)
+        x = torch.randn(N, Ci, H, W, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        y = conv(x)
+        g = torch.randn_like(y)
+        ms_f = _time(lambda: conv(x))
+        ms_b = _time(lambda: torch.autograd.grad(y, (x, conv.weight, conv.bias), g, retain_graph=True))
+        fl = 2.0 * N * Co * Ci * 9 * (H - 2) * (W - 2)
+        print(f"conv {N}x{Ci}->{Co} {H}x{W}: fwd {ms_f:.4f} ms ({fl / ms_f / 1e9:.1f} TFLOP/s), "
+              f"bwd {ms_b:.4f} ms ({2 * fl / ms_b / 1e9:.1f} TFLOP/s)")
     elif kind == "step":
         n = int(argv[1]) // 8 * 8
         from ..distributed.nvlink import SymmetricMemory

@@ -38,6 +38,52 @@ def test_conv2d(dtype, kw, status_ok):
     assert (c.bias.grad.double() - b.grad).abs().max().item() < tol * 30
 
 
+@pytest.mark.parametrize("case", [
+    dict(nd=2, cin=3, cout=64, k=3, hw=(32, 32), n=8),                       # K = 27: one padded k-block
+    dict(nd=2, cin=64, cout=128, k=3, hw=(15, 15), n=6),                     # K = 576: nine k-blocks
+    dict(nd=2, cin=20, cout=192, k=3, hw=(19, 23), n=3, stride=2, padding=1),  # two M tiles, ragged everything
+    dict(nd=2, cin=8, cout=16, k=5, hw=(40, 40), n=2, padding=2, dilation=2),
+    dict(nd=1, cin=16, cout=24, k=7, hw=(300,), n=4, padding=3),
+    dict(nd=3, cin=4, cout=8, k=3, hw=(6, 7, 8), n=2, padding=1),
+])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_implicit_gemm_conv(case, dtype, status_ok):
+    """The implicit-GEMM kernels (forward, data gradient, weight gradient over the whole batch)
+    against torch's float32 convolution of the same 16-bit values: each output within a 16-bit
+    rounding step of its own size plus the fp32 accumulation error."""
+    torch.manual_seed(1)
+    nd = case["nd"]
+    Conv = {1: Conv1d, 2: Conv2d, 3: Conv3d}[nd]
+    fconv = {1: F.conv1d, 2: F.conv2d, 3: F.conv3d}[nd]
+    kw = {k: case[k] for k in ("stride", "padding", "dilation") if k in case}
+    c = Conv(case["cin"], case["cout"], case["k"], dtype=dtype, device="cuda", **kw)
+    x = torch.randn(case["n"], case["cin"], *case["hw"], device="cuda", dtype=dtype, requires_grad=True)
+    y = c(x)
+    xr = x.detach().float().requires_grad_(True)
+    w, b = c.weight.detach().float().requires_grad_(True), c.bias.detach().float().requires_grad_(True)
+    ref = fconv(xr, w, b, **kw)
+    step = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+
+    def close(a, r, extra):
+        assert a.shape == r.shape
+        bad = (a.float() - r).abs() - (2 * step * r.abs() + extra)
+        assert bad.max().item() <= 0, bad.max().item()
+
+    close(y, ref, 1e-3)
+    g = torch.randn_like(y)
+    y.backward(g)
+    ref.backward(g.float())
+    close(x.grad, xr.grad, 2e-3)
+    # the weight gradient sums n * L products: allow the fp32 accumulation error of that many terms
+    close(c.weight.grad, w.grad, 2e-3 * (w.grad.abs().max().item() + 1))
+    close(c.bias.grad, b.grad, 2e-3 * (b.grad.abs().max().item() + 1))
+    # identical bytes from run to run (fixed split order in the weight gradient)
+    c.weight.grad = None
+    x2 = x.detach().clone().requires_grad_(True)
+    c(x2).backward(g)
+    assert torch.equal(x2.grad, x.grad)
+
+
 def test_conv1d_3d_transpose(status_ok):
     torch.manual_seed(0)
     c1 = Conv1d(3, 5, 4, stride=2, device="cuda")
