@@ -166,6 +166,33 @@ __global__ void pool_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
   }
 }
 
+// Backward of max / average pooling whose windows do not overlap (every input position lies in at
+// most one window: the usual stride == kernel case and global pooling).  p2w[pos] = {window, tap}
+// of the position, or {-1, 0}; wcnt[win] = taps of the window that are not padding.  One thread
+// per input element, rows (b) along blockIdx.y: no division, one table read and two dependent
+// loads per element, coalesced stores.
+template <typename T>
+__global__ void pool_bwd_disjoint_kernel(const T* __restrict__ dy, const int* __restrict__ arg,
+                                         const int2* __restrict__ p2w, const int* __restrict__ wcnt,
+                                         T* __restrict__ dx, long long B, int S, int nwin, int T_, int mode,
+                                         int count_include_pad) {
+  for (long long b = blockIdx.y; b < B; b += gridDim.y) {
+    const T* dyb = dy + b * nwin;
+    const int* ab = arg ? arg + b * nwin : nullptr;
+    T* dxb = dx + b * S;
+    for (int pos = blockIdx.x * blockDim.x + threadIdx.x; pos < S; pos += gridDim.x * blockDim.x) {
+      const int2 w = __ldg(p2w + pos);
+      float v = 0.f;
+      if (w.x >= 0) {
+        const float g = (float)dyb[w.x];
+        if (mode == POOL_MAX) v = (ab[w.x] == w.y) ? g : 0.f;
+        else v = g / (float)(count_include_pad ? T_ : max(__ldg(wcnt + w.x), 1));
+      }
+      dxb[pos] = (T)v;
+    }
+  }
+}
+
 inline int grid_for(long long work) {
   long long g = (work + 255) / 256;
   if (g > 148 * 16) g = 148 * 16;
@@ -218,6 +245,23 @@ GB_EXPORT int gb_pool_fwd(int dtype, const void* x, const int* idx, void* y, int
   if (total <= 0) return gbh::E_OK;
   cudaStream_t s = (cudaStream_t)stream;
   GB_DISPATCH_T((pool_fwd_kernel<T><<<grid_for(total), 256, 0, s>>>((const T*)x, idx, (T*)y, arg, B, S, nwin, T_, mode, count_include_pad, p)));
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}
+
+// Backward for non-overlapping windows (max or average): see pool_bwd_disjoint_kernel.
+GB_EXPORT int gb_pool_bwd_disjoint(int dtype, const void* dy, const int* arg, const int* p2w, const int* wcnt,
+                                   void* dx, long long B, long long S, int nwin, int T_, int mode,
+                                   int count_include_pad, void* stream) {
+  if (B <= 0 || S <= 0) return gbh::E_OK;
+  if (mode != POOL_MAX && mode != POOL_AVG) {
+    gbh::set_error("gb_pool_bwd_disjoint: max or average pooling only");
+    return gbh::E_BAD_ARG;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  const int bx = (int)((S + 255) / 256 < 64 ? (S + 255) / 256 : 64);
+  const int by = (int)(B < 65535 ? B : 65535);
+  GB_DISPATCH_T((pool_bwd_disjoint_kernel<T><<<dim3(bx, by), 256, 0, s>>>((const T*)dy, arg, (const int2*)p2w, wcnt, (T*)dx, B, (int)S, nwin, T_, mode, count_include_pad)));
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;
 }

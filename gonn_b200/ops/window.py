@@ -114,6 +114,19 @@ def device_maps(idx: np.ndarray, S: int, device, need_inverse: bool):
         offs, cols = _invert_cached(key, S)
         ent["offs"] = torch.from_numpy(offs.copy()).to(device)
         ent["cols"] = torch.from_numpy(cols.copy()).to(device)
+        # windows that do not overlap (each position in at most one window) get a direct table
+        # position -> (window, tap) for the pooling backward, and the windows' valid-tap counts
+        counts = np.diff(offs)
+        if counts.size and int(counts.max()) <= 1 and S < 2 ** 31:
+            T = idx.shape[1]
+            p2w = np.zeros((S, 2), dtype=np.int32)
+            p2w[:, 0] = -1
+            covered = np.nonzero(counts == 1)[0]
+            wt = cols[offs[covered]]
+            p2w[covered, 0] = wt // T
+            p2w[covered, 1] = wt % T
+            ent["p2w"] = torch.from_numpy(p2w).to(device)
+            ent["wcnt"] = torch.from_numpy((idx >= 0).sum(1).astype(np.int32)).to(device)
     return ent
 
 
@@ -226,6 +239,11 @@ class _Pool(torch.autograd.Function):
         m = device_maps(idx_np, S, xc.device, True)
         dx = torch.empty_like(xc)
         dyc = dy.contiguous()
+        if "p2w" in m and mode in ("max", "avg"):
+            _l.call("gb_pool_bwd_disjoint", _l.I(_l.dtype_code(xc.dtype)), _l.ptr(dyc), _l.ptr(arg), _l.ptr(m["p2w"]),
+                    _l.ptr(m["wcnt"]), _l.ptr(dx), _l.L(B), _l.L(S), _l.I(nwin), _l.I(T), _l.I(_POOL[mode]),
+                    _l.I(int(cip)), _l.stream_ptr())
+            return dx, None, None, None, None
         _l.call("gb_pool_bwd", _l.I(_l.dtype_code(xc.dtype)), _l.ptr(dyc), _l.ptr(xc), _l.ptr(y), _l.ptr(arg),
                 _l.ptr(m["idx"]), _l.ptr(m["offs"]), _l.ptr(m["cols"]), _l.ptr(dx), _l.L(B), _l.L(S), _l.I(nwin),
                 _l.I(T), _l.I(_POOL[mode]), _l.I(int(cip)), _l.F(p), _l.stream_ptr())
