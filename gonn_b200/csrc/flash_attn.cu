@@ -37,6 +37,7 @@ constexpr int kFwdThreads = 192;
 
 struct AttnArgs {
   int B, H, Sq, Sk;
+  int D;  // the tensors' head size: a multiple of 8, at most the kernel's HD (TMA zero-fills the rest)
   float scale_log2;  // scale * log2(e)
   float scale;
   int causal;
@@ -77,6 +78,27 @@ __device__ __forceinline__ void store_row16(void* dst, const float* v, int bf) {
     o.z = pack16(v[j + 4], v[j + 5], bf);
     o.w = pack16(v[j + 6], v[j + 7], bf);
     *reinterpret_cast<uint4*>((uint16_t*)dst + j) = o;
+  }
+}
+
+// The same for a row of which only `ncols` columns (a multiple of 8, counted from this pointer)
+// exist in memory: head sizes below the kernel's compile-time HD.
+template <int N>
+__device__ __forceinline__ void store_row16_lim(void* dst, const float* v, int bf, int ncols) {
+  if (ncols >= N) {
+    store_row16<N>(dst, v, bf);
+    return;
+  }
+#pragma unroll
+  for (int j = 0; j < N; j += 8) {
+    if (j < ncols) {
+      uint4 o;
+      o.x = pack16(v[j], v[j + 1], bf);
+      o.y = pack16(v[j + 2], v[j + 3], bf);
+      o.z = pack16(v[j + 4], v[j + 5], bf);
+      o.w = pack16(v[j + 6], v[j + 7], bf);
+      *reinterpret_cast<uint4*>((uint16_t*)dst + j) = o;
+    }
   }
 }
 
@@ -340,7 +362,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; i++) v[i] = __uint_as_float(ro[i]) * inv;
-        if (row_ok) store_row16<32>(orow + c * 32, v, BF);
+        if (row_ok) store_row16_lim<32>(orow + c * 32, v, BF, args.D - c * 32);
       }
       if (row_ok && args.LSE) {
         // natural-log LSE of the scaled scores
@@ -789,10 +811,10 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
 #pragma unroll
       for (int i = 0; i < W; i++) v[i] = n_it > 0 ? __uint_as_float(ra[i]) : 0.f;
-      if (!row_dead) store_row16<W>(dvrow, v, BF);
+      if (!row_dead) store_row16_lim<W>(dvrow, v, BF, args.D - cw);
 #pragma unroll
       for (int i = 0; i < W; i++) v[i] = n_it > 0 ? __uint_as_float(rb[i]) : 0.f;
-      if (!row_dead) store_row16<W>(dkrow, v, BF);
+      if (!row_dead) store_row16_lim<W>(dkrow, v, BF, args.D - cw);
     }
   }
   tc_fence_before();
@@ -1019,7 +1041,7 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
 #pragma unroll
       for (int i = 0; i < W; i++) v[i] = n_sub > 0 ? __uint_as_float(rr[i]) : 0.f;
-      if (row_ok) store_row16<W>(dqrow, v, BF);
+      if (row_ok) store_row16_lim<W>(dqrow, v, BF, args.D - cw);
     }
   }
   tc_fence_before();
@@ -1098,7 +1120,7 @@ GB_EXPORT int gb_flash_trace(long long* buf) {
 }
 
 // Forward.  q/k/v/o: 16-bit tensors addressed as [b][s][h][d] through element
-// strides (sb, ss, sh) with d contiguous; head_dim 64 or 128.  lse (fp32,
+// strides (sb, ss, sh) with d contiguous; head_dim a multiple of 8 up to 128.  lse (fp32,
 // [B,H,Sq], natural log of the scaled scores' softmax denominator) may be null.
 GB_EXPORT int gb_flash_fwd(int dtype, const void* q, const void* k, const void* v, void* o,
                            float* lse, int B, int H, int Sq, int Sk, int D, long long q_sb,
@@ -1106,8 +1128,8 @@ GB_EXPORT int gb_flash_fwd(int dtype, const void* q, const void* k, const void* 
                            long long k_sh, long long v_sb, long long v_ss, long long v_sh,
                            long long o_sb, long long o_ss, long long o_sh, float scale, int causal,
                            void* stream) {
-  if (D != 64 && D != 128) {
-    gbh::set_error("gb_flash_fwd: head_dim must be 64 or 128 (got %d)", D);
+  if (D < 8 || D > 128 || (D & 7)) {
+    gbh::set_error("gb_flash_fwd: head_dim must be a multiple of 8 up to 128 (got %d)", D);
     return gbh::E_BAD_ARG;
   }
   if (causal && Sq != Sk) {
@@ -1120,7 +1142,7 @@ GB_EXPORT int gb_flash_fwd(int dtype, const void* q, const void* k, const void* 
   }
   AttnArgs a;
   memset(&a, 0, sizeof(a));
-  a.B = B; a.H = H; a.Sq = Sq; a.Sk = Sk;
+  a.B = B; a.H = H; a.Sq = Sq; a.Sk = Sk; a.D = D;
   a.scale = scale; a.scale_log2 = scale * 1.4426950408889634f;
   a.causal = causal; a.in_bf16 = dtype == DT_BF16;
   a.O = o; a.LSE = lse; a.o_sb = o_sb; a.o_ss = o_ss; a.o_sh = o_sh;
@@ -1130,7 +1152,9 @@ GB_EXPORT int gb_flash_fwd(int dtype, const void* q, const void* k, const void* 
   if ((rc = make_qkv_map(&tq, q, a.in_bf16, B, H, Sq, D, q_sb, q_ss, q_sh, BQ))) return rc;
   if ((rc = make_qkv_map(&tk, k, a.in_bf16, B, H, Sk, D, k_sb, k_ss, k_sh, BKF))) return rc;
   if ((rc = make_qkv_map(&tv, v, a.in_bf16, B, H, Sk, D, v_sb, v_ss, v_sh, BKF))) return rc;
-  if (D == 128)
+  // head sizes other than 64 / 128 run the next larger kernel: the tensor maps describe the real
+  // extent, loads beyond it are zero-filled by TMA, stores stop at the real extent
+  if (D > 64)
     return a.in_bf16 ? launch_fwd<128, true>(tq, tk, tv, a, (cudaStream_t)stream)
                      : launch_fwd<128, false>(tq, tk, tv, a, (cudaStream_t)stream);
   return a.in_bf16 ? launch_fwd<64, true>(tq, tk, tv, a, (cudaStream_t)stream)
@@ -1175,8 +1199,8 @@ GB_EXPORT int gb_flash_bwd(int dtype, const void* q, const void* k, const void* 
                            int B, int H, int Sq, int Sk, int D, const long long* strides,
                            float scale, int causal, void* stream) {
   // strides: 7 triples (sb, ss, sh) for q, k, v, dout, dq, dk, dv
-  if (D != 64 && D != 128) {
-    gbh::set_error("gb_flash_bwd: head_dim must be 64 or 128 (got %d)", D);
+  if (D < 8 || D > 128 || (D & 7)) {
+    gbh::set_error("gb_flash_bwd: head_dim must be a multiple of 8 up to 128 (got %d)", D);
     return gbh::E_BAD_ARG;
   }
   if (causal && Sq != Sk) {
@@ -1190,7 +1214,7 @@ GB_EXPORT int gb_flash_bwd(int dtype, const void* q, const void* k, const void* 
     }
   AttnArgs a;
   memset(&a, 0, sizeof(a));
-  a.B = B; a.H = H; a.Sq = Sq; a.Sk = Sk;
+  a.B = B; a.H = H; a.Sq = Sq; a.Sk = Sk; a.D = D;
   a.scale = scale; a.scale_log2 = scale * 1.4426950408889634f;
   a.causal = causal; a.in_bf16 = dtype == DT_BF16;
   a.LSE = const_cast<float*>(lse); a.Delta = delta;
@@ -1210,7 +1234,7 @@ GB_EXPORT int gb_flash_bwd(int dtype, const void* q, const void* k, const void* 
   if ((rc = make_qkv_map(&m.k64, k, a.in_bf16, B, H, Sk, D, strides[3], strides[4], strides[5], 64))) return rc;
   if ((rc = make_qkv_map(&m.v64, v, a.in_bf16, B, H, Sk, D, strides[6], strides[7], strides[8], 64))) return rc;
   if ((rc = make_qkv_map(&m.g64, dout, a.in_bf16, B, H, Sq, D, strides[9], strides[10], strides[11], 64))) return rc;
-  if (D == 128)
+  if (D > 64)
     return a.in_bf16 ? launch_bwd<128, true, false>(m, a, (cudaStream_t)stream)
                      : launch_bwd<128, false, false>(m, a, (cudaStream_t)stream);
   if (g_fa_dual)

@@ -165,7 +165,7 @@ def _attn_dtype(dtype, device, d):
     reference's float64 included) is evaluated in its own precision with tensor ops."""
     if dtype is not None:
         return dtype
-    return torch.bfloat16 if (device.type == "cuda" and d in (64, 128)) else torch.float64
+    return torch.bfloat16 if (device.type == "cuda" and d % 8 == 0 and 8 <= d <= 128) else torch.float64
 
 
 def FlashAttnFwd(Q, K, V, BH: int, S: int, d: int, scale: Optional[float] = None, causal: bool = False,

@@ -46,7 +46,7 @@ def _kernel_ok(q, k, v) -> bool:
     if k.dtype != q.dtype or v.dtype != q.dtype:
         return False
     D = q.shape[-1]
-    return D in (64, 128)
+    return D % 8 == 0 and 8 <= D <= 128
 
 
 def _tma_ready(t):
@@ -230,7 +230,7 @@ def self_attention_qkv(x, wq, wk, wv, bq, bk, bv, num_heads: int, causal: bool, 
     """
     E = x.shape[-1]
     D = E // num_heads
-    if not (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and D in (64, 128) and x.dim() == 3):
+    if not (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and D % 8 == 0 and 8 <= D <= 128 and x.dim() == 3):
         return None
     wqkv = fused_view([wq, wk, wv])
     if wqkv is None:

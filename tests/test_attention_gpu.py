@@ -11,7 +11,12 @@ from gonn_b200.ops.attention import attention_ref, flash_attention, flash_bwd, f
 pytestmark = pytest.mark.gpu
 
 CASES = [(1, 128, 1, 128, False), (1, 128, 1, 64, True), (2, 256, 2, 128, True), (2, 512, 3, 64, True),
-         (1, 200, 2, 128, True), (1, 333, 1, 64, False), (2, 1024, 4, 128, True)]
+         (1, 200, 2, 128, True), (1, 333, 1, 64, False), (2, 1024, 4, 128, True),
+         # the benchmark shapes' sequence lengths
+         (1, 2048, 2, 128, True), (1, 4096, 2, 128, True), (1, 2048, 2, 64, False),
+         # head sizes between the two compiled ones: zero-filled by the loads, clipped by the stores
+         (2, 256, 2, 32, True), (1, 333, 3, 96, False), (1, 200, 2, 8, True), (2, 128, 1, 40, False),
+         (1, 384, 2, 72, True), (1, 256, 2, 112, True)]
 
 
 @pytest.mark.parametrize("B,S,H,D,causal", CASES)
