@@ -180,6 +180,10 @@ def FlashAttnFwd(Q, K, V, BH: int, S: int, d: int, scale: Optional[float] = None
         o = torch.empty(BH, S, d, dtype=dt, device=dev)       # written in place through a strided view
         _, lse = _attn.flash_fwd(q, k, v, bool(causal), scale, out=o.permute(1, 0, 2).unsqueeze(0))
         return o, lse.view(BH, S)
+    if _attn.general_ok(q, k, v):
+        # fp32 / fp64 (the reference's kernels are fp64) and odd head sizes: the general fused kernels
+        o4, lse = _attn.general_fwd(q, k, v, bool(causal), scale)
+        return _flat(o4, BH, S, d), lse.view(BH, S)
     ct = torch.float64 if dt == torch.float64 else torch.float32
     qf, kf, vf = (_flat(t, BH, S, d).to(ct) for t in (q, k, v))
     s = torch.matmul(qf, kf.transpose(1, 2)) * scale
@@ -209,6 +213,9 @@ def FlashAttnBwd(Q, K, V, O, L, dO, BH: int, S: int, d: int, scale: Optional[flo
     if _attn._kernel_ok(q, k, v):
         lse4 = lse.to(torch.float32).contiguous().view(1, BH, S)
         dq, dk, dv, _ = _attn.flash_bwd(q, k, v, o, do, lse4, bool(causal), scale)   # o is read through its strides
+        return tuple(_flat(t, BH, S, d) for t in (dq, dk, dv))
+    if _attn.general_ok(q, k, v):
+        dq, dk, dv = _attn.general_bwd(q, k, v, o, do, lse.view(1, BH, S), bool(causal), scale)
         return tuple(_flat(t, BH, S, d) for t in (dq, dk, dv))
     ct = torch.float64 if dt == torch.float64 else torch.float32
     qf, kf, vf, of, dof = (_flat(t, BH, S, d).to(ct) for t in (q, k, v, o, do))

@@ -15,7 +15,7 @@ from typing import Optional
 
 import torch
 
-from ..ops.attention import flash_attention, self_attention_qkv
+from ..ops.attention import flash_attention, general_attention, general_ok, self_attention_qkv
 from ..ops.softmax import softmax as _softmax
 from .init import fan_in_uniform_
 from .linear import Linear
@@ -100,13 +100,23 @@ class MultiHeadAttention(Module):
     def ForwardMasked(self, q, k=None, v=None, causal: bool = False, attn_mask=None,
                       key_padding_mask=None, attn_dropout: float = 0.0):
         """General masks: ``attn_mask`` (Tq, Tk) additive float or bool (True = masked),
-        ``key_padding_mask`` (B, Tk) bool (True = padded).  Materialises the scores."""
+        ``key_padding_mask`` (B, Tk) bool (True = padded), dropout on the attention weights in
+        training mode.  CUDA tensors run the fused general kernels (no score matrix); CPU
+        tensors evaluate the same formula with tensor ops."""
         k = q if k is None else k
         v = q if v is None else v
         self._check(q, k, v)
         B, Tq, _ = q.shape
         Tk = k.shape[1]
         H, D = self.num_heads, self.head_dim
+        if q.is_cuda:
+            Q4 = self.qproj(q).reshape(B, Tq, H, D)
+            K4 = self.kproj(k).reshape(B, Tk, H, D)
+            V4 = self.vproj(v).reshape(B, Tk, H, D)
+            if general_ok(Q4, K4, V4):
+                pd = float(attn_dropout) if self.training else 0.0
+                o = general_attention(Q4, K4, V4, causal, None, attn_mask, key_padding_mask, pd)
+                return self.outproj(o.reshape(B, Tq, H * D))
         Q = self.qproj(q).reshape(B, Tq, H, D).permute(0, 2, 1, 3)
         K = self.kproj(k).reshape(B, Tk, H, D).permute(0, 2, 1, 3)
         V = self.vproj(v).reshape(B, Tk, H, D).permute(0, 2, 1, 3)

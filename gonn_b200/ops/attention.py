@@ -1,10 +1,12 @@
 """Fused attention: ``softmax(scale * Q K^T [+ causal mask]) V`` without the S x S matrix.
 
-On CUDA with bf16/fp16 inputs and head_dim 64 or 128 this runs the tcgen05
-flash-attention kernels (csrc/flash_attn.cu), forward and backward.  Otherwise
-(CPU, fp32/fp64, other head sizes) the same math is evaluated with tensor ops,
-using the reference's conventions: scale 1/sqrt(D) and an additive causal mask
-of -1e30 (nn/attention.go:124-147, 185-196).
+On CUDA with bf16/fp16 inputs and a head size that is a multiple of 8 (at most 128)
+this runs the tcgen05 flash-attention kernels (csrc/flash_attn.cu), forward and
+backward.  Masks (additive or boolean, key padding), attention dropout, fp32 / fp64
+tensors and other head sizes up to 128 run the general fused kernels
+(csrc/attn_general.cu), which keep no score matrix either.  On CPU the same math is
+evaluated with tensor ops, using the reference's conventions: scale 1/sqrt(D) and an
+additive mask of -1e30 (nn/attention.go:124-147, 185-196, 199-341).
 
 Tensors use the ``(B, S, H, D)`` layout ("bshd"); any strides with a contiguous
 last dimension are accepted, so the q/k/v slices of a fused QKV projection can be
@@ -38,6 +40,141 @@ def attention_ref(q, k, v, causal: bool = False, scale: Optional[float] = None):
 
 def _strides3(t):
     return [t.stride(0), t.stride(1), t.stride(2)]
+
+
+def masked_attention_ref(q, k, v, causal=False, scale=None, attn_mask=None, key_padding_mask=None,
+                         keep=None, p_drop: float = 0.0):
+    """Oracle of the general path.  ``attn_mask``: additive float (Tq, Tk); ``key_padding_mask``: bool
+    (B, Tk), True = padded; ``keep``: bool (B, H, Tq, Tk) dropout keep-mask (with ``p_drop``)."""
+    B, Sq, H, D = q.shape
+    Sk = k.shape[1]
+    scale = (1.0 / math.sqrt(D)) if scale is None else scale
+    ct = torch.float64 if q.dtype == torch.float64 else torch.float32
+    qf, kf, vf = (t.to(ct).permute(0, 2, 1, 3) for t in (q, k, v))
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        s = s + torch.triu(torch.ones(Sq, Sk, dtype=torch.bool, device=q.device), diagonal=1).to(ct) * (-1e30)
+    if attn_mask is not None:
+        s = s + attn_mask.to(ct)[None, None]
+    if key_padding_mask is not None:
+        s = s + key_padding_mask.to(ct)[:, None, None, :] * (-1e30)
+    p = torch.softmax(s, dim=-1)
+    if keep is not None:
+        p = p * keep.to(ct) / (1.0 - p_drop)
+    return torch.matmul(p, vf).permute(0, 2, 1, 3).to(q.dtype)
+
+
+def _general_call(mode, tensors, lse, delta, B, H, Tq, Tk, D, scale, causal, mask, kpm, p_drop, seed):
+    import ctypes
+    dt = None
+    ptrs, strides = [], []
+    for t in tensors:
+        if t is None:
+            ptrs.append(None)
+            strides += [0, 0, 0]
+        else:
+            dt = t.dtype
+            ptrs.append(t.data_ptr())
+            strides += _strides3(t)
+    parr = (ctypes.c_void_p * 8)(*ptrs)
+    sarr = (_l.L * 24)(*strides)
+    _l.call("gb_attn_general", _l.I(mode), _l.I(_l.dtype_code(dt)), parr, sarr, _l.ptr(lse), _l.ptr(delta), _l.I(B),
+            _l.I(H), _l.I(Tq), _l.I(Tk), _l.I(D), _l.D(scale), _l.I(int(causal)), _l.ptr(mask), _l.ptr(kpm),
+            _l.D(p_drop), _l.L(seed), _l.stream_ptr())
+
+
+class _GeneralAttn(torch.autograd.Function):
+    """The general fused kernels: forward, then dQ and dK/dV kernels that regenerate the dropout mask."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale, mask, kpm, p_drop, seed):
+        q, k, v = (t if t.stride(-1) == 1 else t.contiguous() for t in (q, k, v))
+        B, Tq, H, D = q.shape
+        Tk = k.shape[1]
+        out = torch.empty((B, Tq, H, D), dtype=q.dtype, device=q.device)
+        st = torch.float64 if q.dtype == torch.float64 else torch.float32     # row statistics in the compute type
+        lse = torch.empty((B, H, Tq), dtype=st, device=q.device)
+        _general_call(0, [q, k, v, None, out, None, None, None], lse, None, B, H, Tq, Tk, D, scale, causal, mask, kpm,
+                      p_drop, seed)
+        ctx.save_for_backward(q, k, v, out, lse, mask, kpm)
+        ctx.meta = (causal, scale, p_drop, seed)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse, mask, kpm = ctx.saved_tensors
+        causal, scale, p_drop, seed = ctx.meta
+        B, Tq, H, D = q.shape
+        Tk = k.shape[1]
+        dout = dout if dout.stride(-1) == 1 else dout.contiguous()
+        delta = torch.empty((B, H, Tq), dtype=lse.dtype, device=q.device)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        ts = [q, k, v, dout, out, dq, dk, dv]
+        common = (B, H, Tq, Tk, D, scale, causal, mask, kpm, p_drop, seed)
+        _general_call(3, ts, lse, delta, *common)
+        _general_call(1, ts, lse, delta, *common)
+        _general_call(2, ts, lse, delta, *common)
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+def general_fwd(q, k, v, causal: bool, scale: float):
+    """(out, lse) from the general fused kernel; lse is (B, H, Tq) in the compute type."""
+    q, k, v = (t if t.stride(-1) == 1 else t.contiguous() for t in (q, k, v))
+    B, Tq, H, D = q.shape
+    Tk = k.shape[1]
+    out = torch.empty((B, Tq, H, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, H, Tq), dtype=torch.float64 if q.dtype == torch.float64 else torch.float32, device=q.device)
+    _general_call(0, [q, k, v, None, out, None, None, None], lse, None, B, H, Tq, Tk, D, scale, causal, None, None, 0.0, 0)
+    return out, lse
+
+
+def general_bwd(q, k, v, out, dout, lse, causal: bool, scale: float):
+    """(dq, dk, dv) from the general fused kernels, given the forward's output and lse."""
+    q, k, v, out, dout = (t if t.stride(-1) == 1 else t.contiguous() for t in (q, k, v, out, dout))
+    B, Tq, H, D = q.shape
+    Tk = k.shape[1]
+    st = torch.float64 if q.dtype == torch.float64 else torch.float32
+    lse = lse.to(st).contiguous()
+    delta = torch.empty((B, H, Tq), dtype=st, device=q.device)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    ts = [q, k, v, dout, out, dq, dk, dv]
+    for mode in (3, 1, 2):
+        _general_call(mode, ts, lse, delta, B, H, Tq, Tk, D, scale, causal, None, None, 0.0, 0)
+    return dq, dk, dv
+
+
+def general_attention(q, k, v, causal: bool = False, scale: Optional[float] = None, attn_mask=None,
+                      key_padding_mask=None, dropout_p: float = 0.0, seed: Optional[int] = None):
+    """Attention over ``(B, S, H, D)`` CUDA tensors with masks and dropout, fused (no score matrix).
+
+    ``attn_mask``: (Tq, Tk) additive float, or bool with True = masked; ``key_padding_mask``: (B, Tk)
+    bool, True = padded key; ``dropout_p``: probability of dropping an attention weight (the
+    caller passes 0 in evaluation mode); ``seed`` fixes the dropout mask (drawn from torch's
+    generator otherwise)."""
+    B, Tq, H, D = q.shape
+    Tk = k.shape[1]
+    scale = (1.0 / math.sqrt(D)) if scale is None else float(scale)
+    mask = None
+    if attn_mask is not None:
+        m = attn_mask.to(q.device)
+        if tuple(m.shape) != (Tq, Tk):
+            raise ValueError(f"attention: attn_mask must have shape ({Tq}, {Tk})")
+        mask = (m.to(torch.float32) * -1e30 if m.dtype == torch.bool else m.to(torch.float32)).contiguous()
+    kpm = None
+    if key_padding_mask is not None:
+        kp = key_padding_mask.to(q.device)
+        if tuple(kp.shape) != (B, Tk):
+            raise ValueError(f"attention: key_padding_mask must have shape ({B}, {Tk})")
+        kpm = kp.to(torch.uint8).contiguous()
+    if dropout_p > 0 and seed is None:
+        seed = int(torch.randint(0, 2 ** 62, (1,)).item())
+    return _GeneralAttn.apply(q, k, v, bool(causal), scale, mask, kpm, float(dropout_p), int(seed or 0))
+
+
+def general_ok(q, k, v) -> bool:
+    """True when the general fused kernels take these tensors (CUDA, one float dtype, head size <= 128)."""
+    return (q.is_cuda and q.dtype in (torch.bfloat16, torch.float16, torch.float32, torch.float64)
+            and k.dtype == q.dtype and v.dtype == q.dtype and q.shape[-1] <= 128)
 
 
 def _kernel_ok(q, k, v) -> bool:
@@ -129,6 +266,8 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: b
     scale = (1.0 / math.sqrt(D)) if scale is None else float(scale)
     if _kernel_ok(q, k, v) and not (causal and q.shape[1] != k.shape[1]):
         return _FlashAttn.apply(q, k, v, bool(causal), scale)
+    if general_ok(q, k, v):
+        return general_attention(q, k, v, causal, scale)
     return attention_ref(q, k, v, causal, scale)
 
 
