@@ -43,6 +43,8 @@ struct Comm {
   void* local = nullptr;
   size_t bytes = 0;
   PeerTable peers;
+  void* mc_base = nullptr;   // multicast alias of the symmetric buffers (NVSwitch), or null
+  bool attached = false;     // buffers mapped by the caller (gb_comm_attach): nothing to free here
   bool opened[kMaxWorld] = {false};
   unsigned int epoch = 0;
   unsigned int serial = 0;
@@ -52,6 +54,7 @@ struct Comm {
 };
 
 Comm g_comm;
+int g_use_multimem = 1;   // used whenever a multicast mapping is attached; gb_comm_multimem(0) turns it off
 
 
 struct StepArgs {
@@ -66,6 +69,7 @@ struct StepArgs {
   int interleave;            // work mapping of the CTAs (see the kernel)
   unsigned int epoch;        // barrier epochs epoch (start) and epoch+1 (end)
   const unsigned int* epoch_base;  // added to `epoch` at run time when not null (graph replay)
+  void* mc;                  // multicast alias of the buffers: reductions and broadcasts go through NVSwitch
   const float* hyper_dev;    // when not null: lr .. gscale are read from these 8 floats at run time
   float* master[kMaxWorld];  // per emulated rank (index 0 in real runs): fp32 shard state
   float* m[kMaxWorld];
@@ -88,6 +92,35 @@ __device__ __forceinline__ uint4 pack8(const float* f, int bf) {
   u.z = bf ? pack_bf16(f[4], f[5]) : pack_f16(f[4], f[5]);
   u.w = bf ? pack_bf16(f[6], f[7]) : pack_f16(f[6], f[7]);
   return u;
+}
+
+// NVSwitch multicast ("multimem") accesses: one load returns the sum of the addressed vector
+// over all ranks' buffers (added inside the switch, fp32 accumulation for 16-bit types), one
+// store writes every rank's copy.  The multicast address is a second mapping of the same
+// memory, so accesses through it are ordered against ordinary ones with fence.proxy.alias.
+__device__ __forceinline__ void fence_alias() { asm volatile("fence.proxy.alias;" ::: "memory"); }
+__device__ __forceinline__ uint4 mm_ld_reduce_bf16(const void* p) {
+  uint4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+  return r;
+}
+__device__ __forceinline__ uint4 mm_ld_reduce_f16(const void* p) {
+  uint4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+  return r;
+}
+__device__ __forceinline__ float4 mm_ld_reduce_f32(const void* p) {
+  float4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(p) : "memory");
+  return r;
+}
+__device__ __forceinline__ void mm_st(void* p, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
 }
 
 // One kernel = start barrier, reduce-scatter of this rank's slice (+ optimizer),
@@ -134,20 +167,32 @@ fused_step_kernel(const StepArgs a) {
   float* mm = a.m[sidx];
   float* vv = a.v[sidx];
 
+  const bool use_mc = a.mc != nullptr && W > 1 && !a.emulate;
+  if (use_mc) fence_alias();
   if (a.dtype_bf16 == 2) {
     // fp32 all-reduce (mode 0): the same two-shot scheme on vectors of four floats
     for (long long i = v0 + threadIdx.x; i < v1; i += vstep) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int p = 0; p < W; p++) {
-        const float4 u = __ldcg((const float4*)((const char*)a.pt.base[p] + a.grad_off) + slice_vec0 + i);
-        acc.x += u.x; acc.y += u.y; acc.z += u.z; acc.w += u.w;
+      if (use_mc) {
+        acc = mm_ld_reduce_f32((const float4*)((const char*)a.mc + a.grad_off) + slice_vec0 + i);
+      } else {
+        for (int p = 0; p < W; p++) {
+          const float4 u = __ldcg((const float4*)((const char*)a.pt.base[p] + a.grad_off) + slice_vec0 + i);
+          acc.x += u.x; acc.y += u.y; acc.z += u.z; acc.w += u.w;
+        }
       }
       acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
-      for (int p = 0; p < W; p++) {
-        const int q = (rank + 1 + p) % W;
-        ((float4*)((char*)a.pt.base[q] + a.grad_off))[slice_vec0 + i] = acc;
+      if (use_mc) {
+        mm_st((float4*)((char*)a.mc + a.grad_off) + slice_vec0 + i,
+              make_uint4(__float_as_uint(acc.x), __float_as_uint(acc.y), __float_as_uint(acc.z), __float_as_uint(acc.w)));
+      } else {
+        for (int p = 0; p < W; p++) {
+          const int q = (rank + 1 + p) % W;
+          ((float4*)((char*)a.pt.base[q] + a.grad_off))[slice_vec0 + i] = acc;
+        }
       }
     }
+    if (use_mc) fence_alias();
     if (W > 1) cta_barrier(a.pt, rank, W, 1, cta, epoch + 1, a.status, &sm_flag);
     return;
   }
@@ -155,14 +200,21 @@ fused_step_kernel(const StepArgs a) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) acc[j] = 0.f;
-    // fixed rank order => the sum does not depend on who computes it or when
-    for (int p = 0; p < W; p++) {
-      const uint4* src = (const uint4*)((const char*)a.pt.base[p] + a.grad_off) + slice_vec0 + i;
-      uint4 u = __ldcg(src);  // L2 only: a peer's data is never served from this SM's L1
-      float f[8];
-      unpack8(u, f, a.dtype_bf16);
+    if (use_mc) {
+      // the switch adds the W copies (fp32 accumulation) and returns the 16-bit sum
+      const void* src = (const uint4*)((const char*)a.mc + a.grad_off) + slice_vec0 + i;
+      const uint4 u = a.dtype_bf16 ? mm_ld_reduce_bf16(src) : mm_ld_reduce_f16(src);
+      unpack8(u, acc, a.dtype_bf16);
+    } else {
+      // fixed rank order => the sum does not depend on who computes it or when
+      for (int p = 0; p < W; p++) {
+        const uint4* src = (const uint4*)((const char*)a.pt.base[p] + a.grad_off) + slice_vec0 + i;
+        uint4 u = __ldcg(src);  // L2 only: a peer's data is never served from this SM's L1
+        float f[8];
+        unpack8(u, f, a.dtype_bf16);
 #pragma unroll
-      for (int j = 0; j < 8; j++) acc[j] += f[j];
+        for (int j = 0; j < 8; j++) acc[j] += f[j];
+      }
     }
 #pragma unroll
     for (int j = 0; j < 8; j++) acc[j] *= inv;
@@ -195,14 +247,88 @@ fused_step_kernel(const StepArgs a) {
       out = pack8(pw, a.dtype_bf16);
       dst_off = a.param_off;
     }
-    for (int p = 0; p < W; p++) {
-      // own copy last-to-first makes no difference; start with the next rank to spread traffic
-      const int q = (rank + 1 + p) % W;
-      uint4* dst = (uint4*)((char*)a.pt.base[q] + dst_off) + slice_vec0 + i;
-      *dst = out;
+    if (use_mc) {
+      mm_st((uint4*)((char*)a.mc + dst_off) + slice_vec0 + i, out);   // every rank's copy in one store
+    } else {
+      for (int p = 0; p < W; p++) {
+        // own copy last-to-first makes no difference; start with the next rank to spread traffic
+        const int q = (rank + 1 + p) % W;
+        uint4* dst = (uint4*)((char*)a.pt.base[q] + dst_off) + slice_vec0 + i;
+        *dst = out;
+      }
     }
   }
+  if (use_mc) fence_alias();
   if (W > 1) cta_barrier(a.pt, rank, W, 1, cta, epoch + 1, a.status, &sm_flag);
+}
+
+// One-shot all-reduce for short vectors: every rank pushes its vector into slot [parity][rank]
+// of every peer, ONE barrier, then every rank adds the W slots in rank order and writes the
+// result over its own vector.  The two slot sets alternate from call to call, so no second
+// barrier is needed before the slots are reused: a rank can only reach call n+2 (which reuses
+// the set of call n) after every peer has signalled in call n+1, i.e. has finished call n.
+struct OneShotArgs {
+  PeerTable pt;
+  int rank, world, emulate;
+  long long data_off;   // byte offset of the vector inside the symmetric buffer (in place)
+  long long slot_off;   // byte offset of the slot area: 2 sets x world slots x slot_bytes
+  long long slot_bytes; // bytes per slot (>= n * element size, multiple of 16)
+  long long nvec;       // 16-byte vectors in the vector
+  int dtype;            // 0 fp16, 1 bf16, 2 fp32
+  float scale;          // applied to the sum (1/W for the mean)
+  unsigned int epoch;
+  const unsigned int* epoch_base;
+  int* status;
+};
+
+__global__ void __launch_bounds__(256)
+oneshot_allreduce_kernel(const OneShotArgs a) {
+  __shared__ int sm_flag;
+  const int rank = a.emulate ? (int)blockIdx.y : a.rank;
+  const int W = a.world;
+  const int cta = blockIdx.x, G = gridDim.x;
+  if (threadIdx.x == 0) sm_flag = 0;
+  __syncthreads();
+  const unsigned int epoch = dyn_value(a.epoch, a.epoch_base);
+  const long long set_off = a.slot_off + (long long)(epoch & 1u) * W * a.slot_bytes;
+  const uint4* mine = (const uint4*)((const char*)a.pt.base[rank] + a.data_off);
+  const long long per = (a.nvec + G - 1) / G;
+  const long long v0 = (long long)cta * per, v1 = min(v0 + per, a.nvec);
+  for (long long i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
+    const uint4 u = mine[i];
+    for (int p = 0; p < W; p++) {
+      const int q = (rank + 1 + p) % W;
+      ((uint4*)((char*)a.pt.base[q] + set_off + (long long)rank * a.slot_bytes))[i] = u;
+    }
+  }
+  if (!cta_barrier(a.pt, rank, W, 9, cta, epoch, a.status, &sm_flag)) return;
+  const char* slots = (const char*)a.pt.base[rank] + set_off;
+  uint4* outp = (uint4*)((char*)a.pt.base[rank] + a.data_off);
+  for (long long i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
+    if (a.dtype == 2) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int p = 0; p < W; p++) {
+        const float4 u = __ldcg((const float4*)(slots + (long long)p * a.slot_bytes) + i);
+        acc.x += u.x; acc.y += u.y; acc.z += u.z; acc.w += u.w;
+      }
+      acc.x *= a.scale; acc.y *= a.scale; acc.z *= a.scale; acc.w *= a.scale;
+      ((float4*)outp)[i] = acc;
+    } else {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) acc[j] = 0.f;
+      for (int p = 0; p < W; p++) {
+        const uint4 u = __ldcg((const uint4*)(slots + (long long)p * a.slot_bytes) + i);
+        float f[8];
+        unpack8(u, f, a.dtype);
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[j] += f[j];
+      }
+#pragma unroll
+      for (int j = 0; j < 8; j++) acc[j] *= a.scale;
+      outp[i] = pack8(acc, a.dtype);
+    }
+  }
 }
 
 struct SmallArgs {
@@ -372,7 +498,44 @@ GB_EXPORT int gb_comm_emulate(int world, void* const* bases) {
   return gbh::E_OK;
 }
 
+// Adopts symmetric buffers that the caller has already mapped (for example through a virtual-
+// memory allocator that also provides an NVSwitch multicast mapping).  bases: every rank's buffer
+// as mapped in this process, in rank order; mc_base: the multicast alias, or null.  The buffers
+// start with gb_comm_flag_bytes() bytes of flags, which the caller has zeroed.
+GB_EXPORT int gb_comm_attach(int rank, int world, void* const* bases, void* mc_base) {
+  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) {
+    gbh::set_error("gb_comm_attach: bad rank/world %d/%d", rank, world);
+    return gbh::E_BAD_ARG;
+  }
+  if (g_comm.local != nullptr) {
+    gbh::set_error("gb_comm_attach: a symmetric buffer already exists; call gb_comm_free first");
+    return gbh::E_BAD_ARG;
+  }
+  g_comm.rank = rank;
+  g_comm.world = world;
+  for (int p = 0; p < world; p++) g_comm.peers.base[p] = bases[p];
+  g_comm.mc_base = mc_base;
+  g_comm.attached = true;
+  g_comm.epoch = 0;
+  return gbh::E_OK;
+}
+GB_EXPORT int gb_comm_has_multicast() { return g_comm.mc_base != nullptr; }
+// 1 (default): reductions and broadcasts of the fused step go through the multicast mapping when
+// one is attached; 0: plain peer loads and stores in fixed rank order (bit-reproducible sums).
+GB_EXPORT int gb_comm_multimem(int on) {
+  g_use_multimem = on;
+  return gbh::E_OK;
+}
+
 GB_EXPORT int gb_comm_free() {
+  if (g_comm.attached) {
+    for (int p = 0; p < kMaxWorld; p++) g_comm.peers.base[p] = nullptr;
+    g_comm.mc_base = nullptr;
+    g_comm.attached = false;
+    g_comm.world = 1;
+    g_comm.rank = 0;
+    return gbh::E_OK;
+  }
   for (int p = 0; p < kMaxWorld; p++) {
     if (g_comm.opened[p]) {
       cudaIpcCloseMemHandle(g_comm.peers.base[p]);
@@ -492,6 +655,7 @@ GB_EXPORT int gb_comm_fused_step(int mode, int dtype_bf16, long long grad_off, l
   a.epoch = W > 1 ? next_epochs(2) : 0;
   a.epoch_base = g_comm.cap_bases;
   a.hyper_dev = hyper_dev;
+  a.mc = g_use_multimem ? g_comm.mc_base : nullptr;
   const int ns = emulate ? W : 1;
   for (int i = 0; i < ns; i++) {
     a.master[i] = master ? master[i] : nullptr;
@@ -505,6 +669,34 @@ GB_EXPORT int gb_comm_fused_step(int mode, int dtype_bf16, long long grad_off, l
   dim3 grid(ctas, emulate ? W : 1);
   return launch_maybe_coop((const void*)fused_step_kernel, grid, dim3(512), args, emulate && W > 1,
                            (cudaStream_t)stream);
+}
+
+// One-shot all-reduce of a short vector, in place at data_off (see the kernel).  n elements of
+// dtype (0 fp16, 1 bf16, 2 fp32), n * element size a multiple of 16; the slot area at slot_off
+// must hold 2 * world * slot_bytes bytes with slot_bytes >= n * element size.
+GB_EXPORT int gb_comm_allreduce_oneshot(int dtype, long long data_off, long long n, long long slot_off,
+                                        long long slot_bytes, float scale, int ctas, int emulate, void* stream) {
+  const int W = g_comm.world;
+  const long long esz = dtype == 2 ? 4 : 2;
+  if ((n * esz) % 16 != 0 || slot_bytes % 16 != 0 || slot_bytes < n * esz || data_off % 16 != 0 || slot_off % 16 != 0) {
+    gbh::set_error("gb_comm_allreduce_oneshot: sizes and offsets must be multiples of 16 bytes and fit the slots");
+    return gbh::E_BAD_ARG;
+  }
+  if (ctas < 1) ctas = 1;
+  if (ctas > kMaxCtas) ctas = kMaxCtas;
+  if (emulate && ctas * W > 128) ctas = 128 / W;
+  OneShotArgs a;
+  memset(&a, 0, sizeof(a));
+  a.pt = g_comm.peers;
+  a.rank = g_comm.rank; a.world = W; a.emulate = emulate;
+  a.data_off = data_off; a.slot_off = slot_off; a.slot_bytes = slot_bytes; a.nvec = n * esz / 16;
+  a.dtype = dtype; a.scale = scale;
+  a.epoch = next_epochs(1);
+  a.epoch_base = g_comm.cap_bases;
+  a.status = gbh::status_ptr();
+  void* args[] = {&a};
+  return launch_maybe_coop((const void*)oneshot_allreduce_kernel, dim3(ctas, emulate ? W : 1), dim3(256), args,
+                           emulate && W > 1, (cudaStream_t)stream);
 }
 
 // In-place sum over ranks of an fp32 vector of n <= 4096 elements.  slot_off:

@@ -6,6 +6,14 @@ bootstrap channel) and exposes torch views of the local data region.  The
 collectives themselves are the kernels of ``csrc/comm.cu``: they read and write
 the peers' buffers directly over NVLink.
 
+``multicast=True`` (or ``GB_COMM_MULTIMEM=1``) maps the buffers through torch's
+symmetric-memory allocator instead, which also provides an NVSwitch multicast mapping; the
+fused step then reduces with ``multimem.ld_reduce`` and broadcasts with ``multimem.st``
+(the switch adds / replicates; each GPU moves 1/W of the plain peer traffic).  The
+in-switch sum has no fixed rank order, so the default stays the plain peer path, whose
+results are bit-reproducible.  Short vectors are all-reduced by a one-shot kernel (one
+barrier) through a private slot area behind the data region.
+
 With ``world == 1`` no IPC is involved; with ``emulate=W`` the W "ranks" are W
 buffers on one GPU driven by a single cooperative launch (for tests).
 """
@@ -49,15 +57,23 @@ class SymmetricMemory:
     """This rank's symmetric buffer.  Offsets handed to kernels count from the buffer's
     base (the flag area comes first); ``view`` takes offsets into the data region."""
 
+    ONESHOT_BYTES = 2 << 20      # slot area of the one-shot all-reduce: 2 sets x world slots
+
     def __init__(self, data_bytes: int, rank: int = 0, world: int = 1, process_group=None,
-                 emulate: int = 0, device: Optional[torch.device] = None):
+                 emulate: int = 0, device: Optional[torch.device] = None, multicast: Optional[bool] = None):
         _apply_env_tuning()
         self.rank, self.world, self.emulate = rank, world, emulate
         _current[0] = self
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device())
         self.device = device
-        self.data_bytes = (int(data_bytes) + 255) // 256 * 256
+        self.user_bytes = (int(data_bytes) + 255) // 256 * 256
+        # the one-shot slots live behind the caller's data, inside the same symmetric buffer
+        self.data_bytes = self.user_bytes + (self.ONESHOT_BYTES if device.type == "cuda" else 0)
+        self.multicast = False
+        self._symm_handle = None
+        if multicast is None:
+            multicast = os.environ.get("GB_COMM_MULTIMEM", "0") == "1"
         self._raw: List[torch.Tensor] = []
         self.host = device.type != "cuda"
         self._pg = process_group
@@ -90,6 +106,8 @@ class SymmetricMemory:
             self._raw.append(t)
             arr = (ctypes.c_void_p * 1)(t.data_ptr())
             _l.call("gb_comm_emulate", _l.I(1), arr)
+        elif multicast and self._attach_vmm(process_group):
+            pass
         else:
             import torch.distributed as dist
             base = ctypes.c_void_p()
@@ -105,6 +123,33 @@ class SymmetricMemory:
             self._raw[0][self.flag_bytes:].zero_()
             torch.cuda.synchronize()
             dist.barrier(group=process_group)
+
+    def _attach_vmm(self, process_group) -> bool:
+        """Maps the buffers through torch's symmetric-memory allocator (virtual-memory API with
+        an NVSwitch multicast object where the fabric supports it).  Returns False, leaving
+        nothing behind, when that allocator is unavailable; the caller then uses CUDA IPC."""
+        import torch.distributed as dist
+        try:
+            import torch.distributed._symmetric_memory as symm
+            total = self.flag_bytes + self.data_bytes
+            t = symm.empty(total, dtype=torch.uint8, device=self.device)
+            group = process_group if process_group is not None else dist.group.WORLD
+            hdl = symm.rendezvous(t, group)
+        except Exception as e:  # noqa: BLE001 - any failure of the optional path means "use IPC"
+            self._vmm_error = repr(e)
+            return False
+        t.zero_()
+        torch.cuda.synchronize()
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        mc = int(getattr(hdl, "multicast_ptr", 0) or 0)        # 0 where the fabric offers no multicast
+        arr = (ctypes.c_void_p * self.world)(*ptrs)
+        _l.call("gb_comm_attach", _l.I(self.rank), _l.I(self.world), arr, ctypes.c_void_p(mc))
+        self._symm_handle, self._symm_tensor = hdl, t
+        self._raw.append(t)
+        self._ipc = True
+        self.multicast = mc != 0
+        dist.barrier(group=process_group)
+        return True
 
     def view(self, offset_bytes: int, numel: int, dtype: torch.dtype, rank: int = 0) -> torch.Tensor:
         """A typed view of ``numel`` elements at ``offset_bytes`` of the data region
@@ -144,6 +189,17 @@ class SymmetricMemory:
         through peer loads and writes it back to every peer).  ``n`` must be a multiple of
         ``world * 8``; fp16 / bf16 / fp32."""
         scale = float(self.world) if op == "sum" else 1.0
+        esz = torch.empty((), dtype=dtype).element_size()
+        slot = self.ONESHOT_BYTES // (2 * self.world) // 16 * 16
+        if not self.host and self.world > 1 and n * esz <= min(slot, 256 << 10) and (n * esz) % 16 == 0:
+            # short vectors: push + one barrier + local sum (two barriers and a round trip less)
+            code = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[dtype]
+            nb = n * esz
+            ctas1 = 1 if nb <= (8 << 10) else min(ctas, max(1, nb // (8 << 10)))
+            _l.call("gb_comm_allreduce_oneshot", _l.I(code), _l.L(self.abs_offset(offset_bytes)), _l.L(n),
+                    _l.L(self.abs_offset(self.user_bytes)), _l.L(slot), _l.F(scale / self.world), _l.I(ctas1),
+                    _l.I(1 if self.emulate else 0), _l.stream_ptr())
+            return
         self.fused_step(0, dtype, offset_bytes, offset_bytes, n, None, None, None,
                         [0, 0, 0, 0, 0, 1, 1, scale], ctas)
 
@@ -224,6 +280,11 @@ class SymmetricMemory:
     def close(self):
         if getattr(self, "_ipc", False):
             torch.cuda.synchronize()
+            if self._symm_handle is not None and self.world > 1:
+                # every rank stops using the multicast mapping before any rank releases it
+                import torch.distributed as dist
+                dist.barrier(group=self._pg)
             self._raw.clear()
             _l.call("gb_comm_free")
+            self._symm_handle = self._symm_tensor = None
             self._ipc = False

@@ -37,6 +37,30 @@ def test_allreduce_mean_emulated(world, dtype, status_ok):
     sm.check()
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("dtype,n", [(torch.float32, 260), (torch.bfloat16, 8 * 1000), (torch.float16, 8 * 37),
+                                     (torch.float32, 16384)])
+def test_oneshot_allreduce_emulated(world, dtype, n, status_ok):
+    """Short vectors take the one-shot kernel (push, one barrier, local sum in rank order).  Several
+    calls in a row alternate between the two slot sets; every rank must hold identical bytes."""
+    sm = _symm(world, 4 * n + 4096)
+    for call in range(4):
+        vals = [(torch.randn(n, device="cuda") * (call + 1)).to(dtype) for _ in range(world)]
+        for r in range(world):
+            sm.view(0, n, dtype, rank=r).copy_(vals[r])
+        sm.all_reduce(0, n, dtype, "mean" if call % 2 else "sum", ctas=8)
+        torch.cuda.synchronize()
+        acc = torch.zeros(n, device="cuda")
+        for v in vals:
+            acc += v.float()
+        want = (acc * ((1.0 / world) if call % 2 else 1.0)).to(dtype)
+        outs = [sm.view(0, n, dtype, rank=r) for r in range(world)]
+        assert torch.allclose(outs[0].float(), want.float(), rtol=1e-6 if dtype == torch.float32 else 1e-2, atol=1e-6)
+        for o in outs[1:]:
+            assert torch.equal(o, outs[0])
+    sm.check()
+
+
 @pytest.mark.parametrize("world", [2, 8])
 def test_allreduce_fp32_sum_emulated(world, status_ok):
     """fp32 buffers through the same two-shot kernel (``all_reduce`` with op sum)."""

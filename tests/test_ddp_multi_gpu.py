@@ -235,3 +235,56 @@ def test_two_rank_fp32_allreduce_and_syncbn_match_single_process(tmp_path):
     ref_g = cnn.conv1.weight.grad.float().cpu()
     err = (res["conv1_grad"] - ref_g).abs().max() / ref_g.abs().max().clamp_min(1e-6)
     assert err < 0.1, err
+
+
+CHILD_MULTIMEM = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["GB_ROOT"])
+from gonn_b200.distributed.nvlink import SymmetricMemory
+rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+n = world * 8 * 4096
+sm = SymmetricMemory(8 * n + 4096, rank, world, device=torch.device("cuda", rank), multicast=True)
+res = {"multicast": sm.multicast, "vmm_error": getattr(sm, "_vmm_error", None)}
+for dtype, off in ((torch.bfloat16, 0), (torch.float32, 4 * n)):
+    g = torch.Generator(device="cuda").manual_seed(7 + rank)
+    mine = torch.randn(n, device="cuda", generator=g).to(dtype)
+    sm.view(off, n, dtype).copy_(mine)
+    every = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(every, mine)
+    torch.cuda.synchronize(); dist.barrier()
+    sm.fused_step(0, dtype, off, off, n, None, None, None, [0, 0, 0, 0, 0, 1, 1, 1.0], 16)
+    torch.cuda.synchronize(); sm.check()
+    want = sum(t.float() for t in every) / world
+    got = sm.view(off, n, dtype).float()
+    res[str(dtype)] = float((got - want).abs().max())
+    allg = [torch.empty_like(got) for _ in range(world)]
+    dist.all_gather(allg, got.contiguous())
+    res[str(dtype) + "_same"] = all(torch.equal(allg[0], t) for t in allg)
+if rank == 0:
+    torch.save(res, os.environ["GB_OUT"])
+dist.barrier()
+sm.close()
+dist.destroy_process_group()
+'''
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_multimem_allreduce(tmp_path):
+    """The NVSwitch multicast path (multimem.ld_reduce / multimem.st) of the fused step on two ranks:
+    the mean of the ranks' vectors on every rank, identical bytes everywhere.  Where the fabric gives
+    no multicast mapping the same call takes plain peer loads and the check still holds."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "child_mm.py"
+    script.write_text(CHILD_MULTIMEM)
+    out = tmp_path / "out_mm.pt"
+    env = dict(os.environ, GB_ROOT=root, GB_OUT=str(out), MASTER_ADDR="127.0.0.1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29537", str(script)],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    res = torch.load(out)
+    print("multicast mapping:", res["multicast"], res["vmm_error"])
+    assert res["torch.bfloat16"] < 2e-2 and res["torch.float32"] < 1e-5, res
+    assert res["torch.bfloat16_same"] and res["torch.float32_same"], res
