@@ -655,7 +655,9 @@ GB_EXPORT int gb_comm_fused_step(int mode, int dtype_bf16, long long grad_off, l
   a.epoch = W > 1 ? next_epochs(2) : 0;
   a.epoch_base = g_comm.cap_bases;
   a.hyper_dev = hyper_dev;
-  a.mc = g_use_multimem ? g_comm.mc_base : nullptr;
+  // measured on eight GPUs: the multicast path wins from about 4 MiB (835 against 628 GB/s bus at
+  // 1 GiB), plain peer accesses below (30 against 40 us at 1 MiB)
+  a.mc = (g_use_multimem && n * (dtype_bf16 == 2 ? 4 : 2) >= (2LL << 20)) ? g_comm.mc_base : nullptr;
   const int ns = emulate ? W : 1;
   for (int i = 0; i < ns; i++) {
     a.master[i] = master ? master[i] : nullptr;

@@ -263,7 +263,9 @@ def bench_mlp_cpu():
 
 
 def bench_allreduce():
-    """Bus bandwidth of the peer-memory all-reduce against NCCL: 1 KB .. 1 GB."""
+    """Bus bandwidth of the peer-memory all-reduce against NCCL: 1 KB .. 1 GB, with plain peer
+    loads / stores ("p2p", fixed summation order) and through the NVSwitch multicast mapping
+    ("multimem"); sizes up to 64 KiB take the one-shot kernel in both."""
     import torch.distributed as dist
     from ..distributed.nvlink import SymmetricMemory
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -271,47 +273,59 @@ def bench_allreduce():
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     max_bytes = 1 << 30
-    symm = SymmetricMemory(max_bytes, rank, world, device=torch.device("cuda", local))
-    for dt in (torch.bfloat16, torch.float32):
-        esz = 2 if dt == torch.bfloat16 else 4
-        nbytes = 1 << 10
-        while nbytes <= max_bytes:
-            n = nbytes // esz
-            n = max(n // (world * 8) * (world * 8), world * 8)
-            buf = symm.view(0, n, dt)
-            buf.fill_(1.0)
-            ref = torch.ones(n, device="cuda", dtype=dt)
-            ctas = 8 if nbytes <= (1 << 16) else (32 if nbytes <= (1 << 22) else 128)
-
-            def ours():
-                symm.all_reduce(0, n, dt, "mean", ctas)
-
-            def nccl():
-                dist.all_reduce(ref, op=dist.ReduceOp.AVG)
-
-            res = []
-            for fn in (ours, nccl):
-                for _ in range(3):
-                    fn()
-                torch.cuda.synchronize()
-                dist.barrier()
-                iters = 20 if nbytes <= (1 << 24) else 5
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                for _ in range(iters):
-                    fn()
-                e1.record()
-                torch.cuda.synchronize()
-                t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)   # slowest rank
-                res.append(float(t.item()))
-            symm.check()
+    nccl_cache = {}
+    for mode in ("p2p", "multimem"):
+        symm = SymmetricMemory(max_bytes, rank, world, device=torch.device("cuda", local), multicast=mode == "multimem")
+        if mode == "multimem" and not symm.multicast:
             if rank == 0:
-                bus = lambda ms: 2.0 * (world - 1) / world * n * esz / ms / 1e6
-                _emit(bench="allreduce", dtype=str(dt), bytes=n * esz, world=world, ms=res[0], bus_gbs=bus(res[0]),
-                      nccl_ms=res[1], nccl_bus_gbs=bus(res[1]), timing="back-to-back calls, max over ranks")
-            nbytes *= 4
-    symm.close()
+                _emit(bench="allreduce", mode=mode, unavailable="no multicast mapping: " + str(getattr(symm, "_vmm_error", None)))
+            symm.close()
+            continue
+        for dt in (torch.bfloat16, torch.float32):
+            esz = 2 if dt == torch.bfloat16 else 4
+            nbytes = 1 << 10
+            while nbytes <= max_bytes:
+                n = nbytes // esz
+                n = max(n // (world * 8) * (world * 8), world * 8)
+                buf = symm.view(0, n, dt)
+                buf.fill_(1.0)
+                ref = torch.ones(n, device="cuda", dtype=dt)
+                ctas = 8 if nbytes <= (1 << 16) else (32 if nbytes <= (1 << 22) else 128)
+
+                def ours():
+                    symm.all_reduce(0, n, dt, "mean", ctas)
+
+                def nccl():
+                    dist.all_reduce(ref, op=dist.ReduceOp.AVG)
+
+                res = []
+                for name, fn in (("ours", ours), ("nccl", nccl)):
+                    if name == "nccl" and (dt, nbytes) in nccl_cache:
+                        res.append(nccl_cache[(dt, nbytes)])
+                        continue
+                    for _ in range(3):
+                        fn()
+                    torch.cuda.synchronize()
+                    dist.barrier()
+                    iters = 20 if nbytes <= (1 << 24) else 5
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(iters):
+                        fn()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)   # slowest rank
+                    res.append(float(t.item()))
+                nccl_cache[(dt, nbytes)] = res[1]
+                symm.check()
+                if rank == 0:
+                    bus = lambda ms: 2.0 * (world - 1) / world * n * esz / ms / 1e6
+                    _emit(bench="allreduce", mode=mode, dtype=str(dt), bytes=n * esz, world=world, ms=res[0],
+                          bus_gbs=bus(res[0]), nccl_ms=res[1], nccl_bus_gbs=bus(res[1]),
+                          timing="back-to-back calls, max over ranks")
+                nbytes *= 4
+        symm.close()
     dist.destroy_process_group()
 
 
