@@ -74,6 +74,11 @@ struct StepArgs {
   float* master[kMaxWorld];  // per emulated rank (index 0 in real runs): fp32 shard state
   float* m[kMaxWorld];
   float* v[kMaxWorld];
+  int opt_kind;              // mode 1: 0 AdamW, 1 SGD with momentum (coupled decay), 2 Lion
+  int phase;                 // mode 1: 0 whole step; 1 reduce-scatter into gshard + sum of squares; 2 update from gshard + all-gather
+  const unsigned char* wd_mask[kMaxWorld];  // one byte per 8 elements of the shard: 0 = no weight decay (null: all decay)
+  float* gshard[kMaxWorld];  // phases 1 / 2: the averaged gradient shard in fp32
+  float* sqpart[kMaxWorld];  // phase 1: per-CTA sums of squares of the averaged shard, [gridDim.x]
   float lr, wd, b1, b2, eps, bc1, bc2, gscale;
   int* status;
 };
@@ -141,6 +146,7 @@ fused_step_kernel(const StepArgs a) {
     eps = __ldg(a.hyper_dev + 4); bc1 = __ldg(a.hyper_dev + 5); bc2 = __ldg(a.hyper_dev + 6);
     gscale = __ldg(a.hyper_dev + 7);
   }
+  if (a.mode == 1 && a.phase == 1) gscale = 1.f;   // the clip factor is applied in phase 2
 
   const int epv = a.dtype_bf16 == 2 ? 4 : 8;  // elements per 16-byte vector
   const long long L = a.n / W;          // elements in one rank's slice
@@ -196,28 +202,45 @@ fused_step_kernel(const StepArgs a) {
     if (W > 1) cta_barrier(a.pt, rank, W, 1, cta, epoch + 1, a.status, &sm_flag);
     return;
   }
+  float sq_local = 0.f;
+  const unsigned char* wmask = a.wd_mask[sidx];
+  float* gsh = a.gshard[sidx];
   for (long long i = v0 + threadIdx.x; i < v1; i += vstep) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) acc[j] = 0.f;
-    if (use_mc) {
-      // the switch adds the W copies (fp32 accumulation) and returns the 16-bit sum
-      const void* src = (const uint4*)((const char*)a.mc + a.grad_off) + slice_vec0 + i;
-      const uint4 u = a.dtype_bf16 ? mm_ld_reduce_bf16(src) : mm_ld_reduce_f16(src);
-      unpack8(u, acc, a.dtype_bf16);
+    if (a.mode == 1 && a.phase == 2) {
+      // the averaged gradients were left in fp32 by phase 1; gscale (the clip factor) is known now
+      const float4 g0 = *(const float4*)(gsh + i * 8), g1 = *(const float4*)(gsh + i * 8 + 4);
+      acc[0] = g0.x * gscale; acc[1] = g0.y * gscale; acc[2] = g0.z * gscale; acc[3] = g0.w * gscale;
+      acc[4] = g1.x * gscale; acc[5] = g1.y * gscale; acc[6] = g1.z * gscale; acc[7] = g1.w * gscale;
     } else {
-      // fixed rank order => the sum does not depend on who computes it or when
-      for (int p = 0; p < W; p++) {
-        const uint4* src = (const uint4*)((const char*)a.pt.base[p] + a.grad_off) + slice_vec0 + i;
-        uint4 u = __ldcg(src);  // L2 only: a peer's data is never served from this SM's L1
-        float f[8];
-        unpack8(u, f, a.dtype_bf16);
+      if (use_mc) {
+        // the switch adds the W copies (fp32 accumulation) and returns the 16-bit sum
+        const void* src = (const uint4*)((const char*)a.mc + a.grad_off) + slice_vec0 + i;
+        const uint4 u = a.dtype_bf16 ? mm_ld_reduce_bf16(src) : mm_ld_reduce_f16(src);
+        unpack8(u, acc, a.dtype_bf16);
+      } else {
+        // fixed rank order => the sum does not depend on who computes it or when
+        for (int p = 0; p < W; p++) {
+          const uint4* src = (const uint4*)((const char*)a.pt.base[p] + a.grad_off) + slice_vec0 + i;
+          uint4 u = __ldcg(src);  // L2 only: a peer's data is never served from this SM's L1
+          float f[8];
+          unpack8(u, f, a.dtype_bf16);
 #pragma unroll
-        for (int j = 0; j < 8; j++) acc[j] += f[j];
+          for (int j = 0; j < 8; j++) acc[j] += f[j];
+        }
       }
-    }
 #pragma unroll
-    for (int j = 0; j < 8; j++) acc[j] *= inv;
+      for (int j = 0; j < 8; j++) acc[j] *= inv;
+    }
+    if (a.mode == 1 && a.phase == 1) {
+      *(float4*)(gsh + i * 8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *(float4*)(gsh + i * 8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+      for (int j = 0; j < 8; j++) sq_local += acc[j] * acc[j];
+      continue;
+    }
     uint4 out;
     long long dst_off;
     if (a.mode == 0) {
@@ -226,24 +249,46 @@ fused_step_kernel(const StepArgs a) {
     } else {
       float4* mp = (float4*)(master + i * 8);
       float4* m4 = (float4*)(mm + i * 8);
-      float4* v4 = (float4*)(vv + i * 8);
       float pw[8], pm[8], pv[8];
       *(float4*)&pw[0] = mp[0]; *(float4*)&pw[4] = mp[1];
       *(float4*)&pm[0] = m4[0]; *(float4*)&pm[4] = m4[1];
-      *(float4*)&pv[0] = v4[0]; *(float4*)&pv[4] = v4[1];
+      const float wdv = (wmask == nullptr || wmask[i]) ? wd : 0.f;
+      if (a.opt_kind == 0) {
+        float4* v4 = (float4*)(vv + i * 8);
+        *(float4*)&pv[0] = v4[0]; *(float4*)&pv[4] = v4[1];
 #pragma unroll
-      for (int j = 0; j < 8; j++) {
-        float g = acc[j];
-        float p = pw[j];
-        p -= lr * wd * p;  // decoupled decay first, like optim/adamw.go:77-81
-        float m_ = b1 * pm[j] + (1.f - b1) * g;
-        float v_ = b2 * pv[j] + (1.f - b2) * g * g;
-        p -= lr * (m_ / bc1) / (sqrtf(v_ / bc2) + eps);
-        pw[j] = p; pm[j] = m_; pv[j] = v_;
+        for (int j = 0; j < 8; j++) {
+          float g = acc[j];
+          float p = pw[j];
+          p -= lr * wdv * p;  // decoupled decay first, like optim/adamw.go:77-81
+          float m_ = b1 * pm[j] + (1.f - b1) * g;
+          float v_ = b2 * pv[j] + (1.f - b2) * g * g;
+          p -= lr * (m_ / bc1) / (sqrtf(v_ / bc2) + eps);
+          pw[j] = p; pm[j] = m_; pv[j] = v_;
+        }
+        v4[0] = *(float4*)&pv[0]; v4[1] = *(float4*)&pv[4];
+      } else if (a.opt_kind == 1) {
+        // SGD with momentum b1 and coupled weight decay (optim/sgd.go:38-58): g += wd p; v = mu v + g; p -= lr v
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const float g = acc[j] + wdv * pw[j];
+          const float v_ = b1 * pm[j] + g;
+          pw[j] -= lr * v_;
+          pm[j] = v_;
+        }
+      } else {
+        // Lion (optim/lion.go:61-76): c = b1 m + (1-b1) g; p -= lr (sign(c) + wd p); m = b2 m + (1-b2) g
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const float g = acc[j];
+          const float c = b1 * pm[j] + (1.f - b1) * g;
+          const float sg = c > 0.f ? 1.f : (c < 0.f ? -1.f : 0.f);
+          pw[j] -= lr * (sg + wdv * pw[j]);
+          pm[j] = b2 * pm[j] + (1.f - b2) * g;
+        }
       }
       mp[0] = *(float4*)&pw[0]; mp[1] = *(float4*)&pw[4];
       m4[0] = *(float4*)&pm[0]; m4[1] = *(float4*)&pm[4];
-      v4[0] = *(float4*)&pv[0]; v4[1] = *(float4*)&pv[4];
       out = pack8(pw, a.dtype_bf16);
       dst_off = a.param_off;
     }
@@ -257,6 +302,12 @@ fused_step_kernel(const StepArgs a) {
         *dst = out;
       }
     }
+  }
+  if (a.mode == 1 && a.phase == 1) {
+    // per-CTA sum of squares in a fixed order (block_sum is a fixed tree): reproducible
+    __shared__ float red[32];
+    const float tot = block_sum(sq_local, red);
+    if (threadIdx.x == 0) a.sqpart[sidx][cta] = tot;
   }
   if (use_mc) fence_alias();
   if (W > 1) cta_barrier(a.pt, rank, W, 1, cta, epoch + 1, a.status, &sm_flag);
@@ -630,10 +681,15 @@ GB_EXPORT int gb_comm_tune(int interleave) {
 // floats that the kernel reads when it runs (a captured launch then follows the
 // values the host writes before each replay).  emulate != 0: master/m/v are
 // arrays of `world` pointers.
-GB_EXPORT int gb_comm_fused_step(int mode, int dtype_bf16, long long grad_off, long long param_off,
-                                 long long n, float* const* master, float* const* m, float* const* v,
-                                 const float* hyper, const float* hyper_dev, int ctas, int emulate,
-                                 void* stream) {
+// opt: {kind (0 AdamW, 1 SGD with momentum = hyper[2], 2 Lion), phase (0 whole step, 1 reduce-scatter
+// into gshard + per-CTA sums of squares into sqpart, 2 update from gshard + all-gather)}.  wd_mask: one
+// byte per 8 shard elements (0 = no weight decay) or null; gshard: n/world floats; sqpart: `ctas` floats.
+// The three pointer arguments are arrays of `world` pointers when emulating, like master / m / v.
+GB_EXPORT int gb_comm_fused_step2(int mode, int dtype_bf16, long long grad_off, long long param_off,
+                                  long long n, float* const* master, float* const* m, float* const* v,
+                                  const float* hyper, const float* hyper_dev, int opt_kind, int phase,
+                                  const unsigned char* const* wd_mask, float* const* gshard,
+                                  float* const* sqpart, int ctas, int emulate, void* stream) {
   const int W = g_comm.world;
   if (n % ((long long)W * 8) != 0) {
     gbh::set_error("gb_comm_fused_step: bucket length %lld is not a multiple of world*8", n);
@@ -641,6 +697,11 @@ GB_EXPORT int gb_comm_fused_step(int mode, int dtype_bf16, long long grad_off, l
   }
   if (dtype_bf16 == 2 && mode != 0) {
     gbh::set_error("gb_comm_fused_step: fp32 buckets support the all-reduce mode only");
+    return gbh::E_BAD_ARG;
+  }
+  if (opt_kind < 0 || opt_kind > 2 || phase < 0 || phase > 2 || (phase != 0 && (mode != 1 || gshard == nullptr)) ||
+      (phase == 1 && sqpart == nullptr)) {
+    gbh::set_error("gb_comm_fused_step: bad optimizer kind / phase arguments");
     return gbh::E_BAD_ARG;
   }
   if (ctas < 1) ctas = 1;
@@ -655,6 +716,7 @@ GB_EXPORT int gb_comm_fused_step(int mode, int dtype_bf16, long long grad_off, l
   a.epoch = W > 1 ? next_epochs(2) : 0;
   a.epoch_base = g_comm.cap_bases;
   a.hyper_dev = hyper_dev;
+  a.opt_kind = opt_kind; a.phase = phase;
   // measured on eight GPUs: the multicast path wins from about 4 MiB (835 against 628 GB/s bus at
   // 1 GiB), plain peer accesses below (30 against 40 us at 1 MiB)
   a.mc = (g_use_multimem && n * (dtype_bf16 == 2 ? 4 : 2) >= (2LL << 20)) ? g_comm.mc_base : nullptr;
@@ -663,6 +725,9 @@ GB_EXPORT int gb_comm_fused_step(int mode, int dtype_bf16, long long grad_off, l
     a.master[i] = master ? master[i] : nullptr;
     a.m[i] = m ? m[i] : nullptr;
     a.v[i] = v ? v[i] : nullptr;
+    a.wd_mask[i] = wd_mask ? wd_mask[i] : nullptr;
+    a.gshard[i] = gshard ? gshard[i] : nullptr;
+    a.sqpart[i] = sqpart ? sqpart[i] : nullptr;
   }
   a.lr = hyper[0]; a.wd = hyper[1]; a.b1 = hyper[2]; a.b2 = hyper[3]; a.eps = hyper[4];
   a.bc1 = hyper[5]; a.bc2 = hyper[6]; a.gscale = hyper[7];
@@ -671,6 +736,63 @@ GB_EXPORT int gb_comm_fused_step(int mode, int dtype_bf16, long long grad_off, l
   dim3 grid(ctas, emulate ? W : 1);
   return launch_maybe_coop((const void*)fused_step_kernel, grid, dim3(512), args, emulate && W > 1,
                            (cudaStream_t)stream);
+}
+
+GB_EXPORT int gb_comm_fused_step(int mode, int dtype_bf16, long long grad_off, long long param_off,
+                                 long long n, float* const* master, float* const* m, float* const* v,
+                                 const float* hyper, const float* hyper_dev, int ctas, int emulate,
+                                 void* stream) {
+  return gb_comm_fused_step2(mode, dtype_bf16, grad_off, param_off, n, master, m, v, hyper, hyper_dev, 0, 0, nullptr,
+                             nullptr, nullptr, ctas, emulate, stream);
+}
+
+namespace {
+// Gradient clipping by global norm (optim/clip.go:23-65): scale = max_norm / (norm + 1e-6), applied only when
+// below 1.  sq: `count` partial sums of squares (already summed over ranks when there are several); writes the
+// factor to hyper_dev[7] and the norm to norm_out.
+__global__ void clip_scale_kernel(const float* __restrict__ sq, int count, float max_norm, float* hyper_dev,
+                                  float* norm_out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < count; i += blockDim.x) s += sq[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) {
+    const float norm = sqrtf(s);
+    const float scale = max_norm / (norm + 1e-6f);
+    hyper_dev[7] = scale < 1.f ? scale : 1.f;
+    if (norm_out) *norm_out = norm;
+  }
+}
+// out[0] = sum of `count` floats in index order (one thread: the order is part of the contract)
+__global__ void sum_partials_kernel(const float* __restrict__ p, int count, float* out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < count; i += blockDim.x) s += p[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) out[0] = s;
+}
+}  // namespace
+
+// out[0] = sum of count floats (the per-CTA sums of squares of this rank's shards).
+GB_EXPORT int gb_comm_sum_partials(const float* p, int count, float* out, void* stream) {
+  if (p == nullptr || out == nullptr || count < 1) {
+    gbh::set_error("gb_comm_sum_partials: null argument");
+    return gbh::E_BAD_ARG;
+  }
+  sum_partials_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(p, count, out);
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}
+// hyper_dev[7] = min(1, max_norm / (sqrt(sum sq[0..count)) + 1e-6)); norm_out (optional) = the norm.
+GB_EXPORT int gb_comm_clip_scale(const float* sq, int count, float max_norm, float* hyper_dev, float* norm_out,
+                                 void* stream) {
+  if (sq == nullptr || hyper_dev == nullptr || count < 1) {
+    gbh::set_error("gb_comm_clip_scale: null argument");
+    return gbh::E_BAD_ARG;
+  }
+  clip_scale_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(sq, count, max_norm, hyper_dev, norm_out);
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
 }
 
 // One-shot all-reduce of a short vector, in place at data_off (see the kernel).  n elements of

@@ -23,7 +23,9 @@
  *    library routine.
  *  - The first call on each device looks up the array's device address
  *    (cudaGetSymbolAddress, with that device current) and remembers it.  Make that first
- *    call during start-up, before any stream capture begins on the device.
+ *    call during start-up, before any stream capture begins on the device.  Two host
+ *    threads that make the first call on one device at the same time both store the same
+ *    address, so that is harmless.
  *  - All calls on a device share the one array, and it keeps whatever the previous call
  *    left there.  The kernels overwrite every partial row before reading it, so no
  *    clearing is needed; but two calls that can run at the same time on the GPU (two

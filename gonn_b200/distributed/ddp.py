@@ -7,11 +7,17 @@ each bucket to ONE kernel as soon as backward has produced its gradients:
 * ``optimizer=None``: the kernel leaves the mean gradient on every rank
   (all-reduce-mean); any optimizer can then step (``DDPStep`` semantics of the
   reference, distributed/distributed.go:422-428).
-* ``optimizer={"kind": "adamw", ...}``: the kernel reduce-scatters the bucket,
-  runs AdamW on the shard this rank owns (fp32 master, m, v: 1/W of the state per
-  rank, ZeRO-1) and all-gathers the updated 16-bit parameters — gradient
-  collective, scale/cast, optimizer and parameter collective in one launch,
-  overlapped with the rest of backward on a side stream.
+* ``optimizer={"kind": "adamw" | "sgd" | "lion", ...}``: the kernel reduce-scatters the
+  bucket, runs the optimizer on the shard this rank owns (fp32 master and moments: 1/W of
+  the state per rank, ZeRO-1) and all-gathers the updated 16-bit parameters — gradient
+  collective, scale/cast, optimizer and parameter collective in one launch, overlapped
+  with the rest of backward on a side stream.  Options: ``lr``, ``weight_decay``, ``betas``
+  (AdamW, Lion), ``momentum`` (SGD), ``eps``; ``no_decay`` (a predicate on ``(name,
+  parameter)`` or ``"1d"`` for every vector-shaped parameter: biases and norm weights) exempts
+  parameters from weight decay; ``max_grad_norm`` clips by the global norm as the reference's
+  ``ClipGradNorm`` does (optim/clip.go:23-65): the reduce-scatter then still overlaps with
+  backward (it leaves the averaged shard in fp32 and its sum of squares), and the updates
+  run once the norm of all buckets is known.
 
 The reference reduces one flat vector after the whole backward, through rank 0
 over TCP, without overlap or bucketing (distributed.go:249-293, :84-86).  Kept
@@ -87,14 +93,14 @@ def plan_buckets(sizes, world: int, limit: int):
 
 
 class _Bucket:
-    __slots__ = ("index", "start", "length", "params", "pending", "launched", "master", "m", "v")
+    __slots__ = ("index", "start", "length", "params", "pending", "launched", "master", "m", "v", "wd_mask", "gshard")
 
     def __init__(self, index, start):
         self.index, self.start, self.length = index, start, 0
         self.params: List[torch.nn.Parameter] = []
         self.pending = 0
         self.launched = False
-        self.master = self.m = self.v = None
+        self.master = self.m = self.v = self.wd_mask = self.gshard = None
 
 
 class DistributedDataParallel(torch.nn.Module):
@@ -181,22 +187,52 @@ class DistributedDataParallel(torch.nn.Module):
         self._comm_stream = None if self.host else torch.cuda.Stream(device=dev, priority=-1)
         self.t = 0
         self.opt = dict(optimizer) if optimizer is not None else None
+        self._hyper_dev = None      # device copy of the optimizer scalars (captured launches, clip factor)
+        self._capturing = False     # True while a step is being captured into a CUDA graph
+        self.kind = "adamw"
+        self.max_grad_norm = None
+        self.grad_norm = None       # device scalar: the global gradient norm of the last clipped step
         if self.opt is not None:
             kind = self.opt.get("kind", "adamw").lower()
-            if kind != "adamw":
-                raise ValueError("DistributedDataParallel: the fused sharded optimizer is AdamW")
+            if kind not in ("adamw", "sgd", "lion"):
+                raise ValueError("DistributedDataParallel: the fused sharded optimizer is one of adamw, sgd, lion")
+            self.kind = kind
             self.lr = float(self.opt.get("lr", 1e-3))
-            self.weight_decay = float(self.opt.get("weight_decay", 0.01))
-            self.betas = tuple(self.opt.get("betas", (0.9, 0.999)))
+            self.weight_decay = float(self.opt.get("weight_decay", 0.01 if kind == "adamw" else 0.0))
+            default_betas = (0.9, 0.99) if kind == "lion" else (0.9, 0.999)
+            self.betas = tuple(self.opt.get("betas", default_betas))
+            if kind == "sgd":
+                self.betas = (float(self.opt.get("momentum", 0.9)), 0.0)
             self.eps = float(self.opt.get("eps", 1e-8))
+            mg = self.opt.get("max_grad_norm")
+            self.max_grad_norm = float(mg) if mg is not None else None
+            # which parameters are exempt from weight decay: one byte per 8 elements of the flat layout
+            no_decay = self.opt.get("no_decay")
+            mask_full = None
+            if no_decay is not None:
+                names = {id(p): n for n, p in module.named_parameters()}
+                mask_full = torch.ones(self.total // 8, dtype=torch.uint8)
+                for p in params:
+                    exempt = (p.dim() <= 1) if no_decay == "1d" else bool(no_decay(names.get(id(p), ""), p))
+                    if exempt:
+                        _, o, n = self._where[id(p)]
+                        mask_full[o // 8:(o + n + 7) // 8] = 0
+                mask_full = mask_full.to(dev)
             for b in self.buckets:
                 L = b.length // world
                 lo = b.start + rank * L
                 b.master = self.flat_params[lo:lo + L].to(torch.float32)
                 b.m = torch.zeros(L, dtype=torch.float32, device=dev)
-                b.v = torch.zeros(L, dtype=torch.float32, device=dev)
-        self._hyper_dev = None      # device copy of the optimizer scalars for captured launches
-        self._capturing = False     # True while a step is being captured into a CUDA graph
+                b.v = torch.zeros(L, dtype=torch.float32, device=dev) if kind == "adamw" else None
+                b.wd_mask = mask_full[lo // 8:(lo + L) // 8].contiguous() if mask_full is not None else None
+                if self.max_grad_norm is not None:
+                    b.gshard = torch.zeros(L, dtype=torch.float32, device=dev)
+            if self.max_grad_norm is not None:
+                nb = len(self.buckets)
+                self._sq = torch.zeros(nb * self.comm_ctas, dtype=torch.float32, device=dev)
+                self._sq_total = torch.zeros(max(world, 1), dtype=torch.float32, device=dev)
+                self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
+                self._hyper_dev = torch.zeros(8, dtype=torch.float32, device=dev)
         self._reset_step()
 
     # ---- CUDA-graph support (gonn_b200.utils.graph.GraphedStep) -----------------------------------
@@ -265,23 +301,71 @@ class DistributedDataParallel(torch.nn.Module):
             return [0, 0, 0, 0, 0, 1, 1, 1.0]
         t = self.t + 1
         b1, b2 = self.betas
+        if self.kind != "adamw":
+            return [self.lr, self.weight_decay, b1, b2, self.eps, 1.0, 1.0, 1.0]
         return [self.lr, self.weight_decay, b1, b2, self.eps, 1 - b1 ** t, 1 - b2 ** t, 1.0]
 
     def _launch(self, b: _Bucket):
         b.launched = True
         if self.world == 1 and self.opt is None:
             return  # nothing to reduce and nobody to update
+        clip = self.opt is not None and self.max_grad_norm is not None
         args = (1 if self.opt is not None else 0, self.dtype, self._grad_off + b.start * self._esz,
                 self._param_off + b.start * self._esz, b.length, b.master, b.m, b.v, self._hyper(), self.comm_ctas,
-                self._hyper_dev if self._capturing else None)
+                self._hyper_dev if (self._capturing or clip) else None)
+        kw = dict(kind=self.kind, wd_mask=b.wd_mask)
+        if clip:
+            # phase 1 now (overlapped with backward): reduce-scatter, fp32 shard and its sum of squares;
+            # the update waits in step() for the norm of all buckets
+            kw.update(phase=1, gshard=b.gshard,
+                      sqpart=self._sq[b.index * self.comm_ctas:(b.index + 1) * self.comm_ctas])
         if self.host:
-            self.symm.fused_step(*args)
+            self.symm.fused_step(*args, **kw)
             return
         cur = torch.cuda.current_stream()
         self._comm_stream.wait_stream(cur)
         with torch.cuda.stream(self._comm_stream):
-            self.symm.fused_step(*args)
+            self.symm.fused_step(*args, **kw)
         self._launched_any = True
+
+    def _clip_and_update(self):
+        """Second half of a clipped step: global norm from the per-bucket sums of squares (summed
+        over ranks: every rank holds a disjoint shard), clip factor on the device, then the
+        optimizer update and parameter all-gather of every bucket."""
+        from .. import lib as _l
+        import ctypes
+        hy = self._hyper()
+        if self.host:
+            total = self._sq.sum().reshape(1)
+            if self.world > 1:
+                import torch.distributed as dist
+                dist.all_reduce(total)
+            norm = float(total.sqrt())
+            scale = min(1.0, self.max_grad_norm / (norm + 1e-6))
+            self.grad_norm.fill_(norm)
+            hy[7] = scale
+            for b in reversed(self.buckets):
+                self.symm.fused_step(1, self.dtype, self._grad_off + b.start * self._esz,
+                                     self._param_off + b.start * self._esz, b.length, b.master, b.m, b.v, hy,
+                                     self.comm_ctas, None, kind=self.kind, phase=2, wd_mask=b.wd_mask, gshard=b.gshard)
+            return
+        ctx = torch.cuda.stream(self._comm_stream)
+        with ctx:
+            if not self._capturing:
+                # the scalars of this step; element 7 is overwritten by the clip kernel below
+                _l.call("gb_set_words", None, ctypes.c_uint(0), ctypes.c_uint(0), _l.ptr(self._hyper_dev),
+                        (ctypes.c_float * 8)(*[float(h) for h in hy]), _l.stream_ptr())
+            _l.call("gb_comm_sum_partials", _l.ptr(self._sq), _l.I(self._sq.numel()), _l.ptr(self._sq_total),
+                    _l.stream_ptr())
+            if self.world > 1:
+                self.symm.allreduce_small(self._sq_total[:1], 0)
+            _l.call("gb_comm_clip_scale", _l.ptr(self._sq_total), _l.I(1), _l.F(self.max_grad_norm),
+                    _l.ptr(self._hyper_dev), _l.ptr(self.grad_norm), _l.stream_ptr())
+            for b in reversed(self.buckets):
+                self.symm.fused_step(1, self.dtype, self._grad_off + b.start * self._esz,
+                                     self._param_off + b.start * self._esz, b.length, b.master, b.m, b.v, hy,
+                                     self.comm_ctas, self._hyper_dev, kind=self.kind, phase=2, wd_mask=b.wd_mask,
+                                     gshard=b.gshard)
 
     def _reset_step(self):
         self._ready = set()
@@ -323,6 +407,8 @@ class DistributedDataParallel(torch.nn.Module):
             b = self.buckets[self._next]
             self._next -= 1
             self._launch(b)
+        if self.opt is not None and self.max_grad_norm is not None:
+            self._clip_and_update()
         if self._launched_any:
             torch.cuda.current_stream().wait_stream(self._comm_stream)
         self.t += 1
@@ -349,7 +435,10 @@ class DistributedDataParallel(torch.nn.Module):
         self.symm.check()
 
     def state_bytes_per_rank(self) -> int:
-        return sum(3 * 4 * (b.length // self.world) for b in self.buckets) if self.opt is not None else 0
+        if self.opt is None:
+            return 0
+        per = (3 if self.kind == "adamw" else 2) * 4        # master + moments, fp32
+        return sum(per * (b.length // self.world) for b in self.buckets)
 
     def close(self):
         self.symm.close()

@@ -163,13 +163,20 @@ class SymmetricMemory:
         return self.flag_bytes + offset_bytes
 
     # ---- collectives ------------------------------------------------------------------
+    OPT_KINDS = {"adamw": 0, "sgd": 1, "lion": 2}
+
     def fused_step(self, mode: int, dtype: torch.dtype, grad_off: int, param_off: int, n: int,
-                   master, m, v, hyper, ctas: int = 32, hyper_dev: torch.Tensor = None):
-        """See ``gb_comm_fused_step``.  master/m/v: tensors (lists of tensors when emulating).
+                   master, m, v, hyper, ctas: int = 32, hyper_dev: torch.Tensor = None, kind: str = "adamw",
+                   phase: int = 0, wd_mask=None, gshard=None, sqpart=None):
+        """See ``gb_comm_fused_step2``.  master/m/v: tensors (lists of tensors when emulating).
         ``hyper_dev``: a device tensor of the same eight floats, read by the kernel when it
-        runs (for launches captured in a CUDA graph)."""
+        runs (for launches captured in a CUDA graph, and for the clip factor).  ``kind``: the
+        optimizer; ``phase``: 0 whole step, 1 reduce-scatter into ``gshard`` with sums of squares
+        in ``sqpart``, 2 update from ``gshard`` and all-gather; ``wd_mask``: uint8 per 8 shard
+        elements, 0 = no weight decay."""
         if self.host:
-            return self._fused_step_host(mode, dtype, grad_off, param_off, n, master, m, v, hyper)
+            return self._fused_step_host(mode, dtype, grad_off, param_off, n, master, m, v, hyper, kind, phase,
+                                         wd_mask, gshard, sqpart)
 
         def arr(x):
             if x is None:
@@ -178,9 +185,10 @@ class SymmetricMemory:
             return (ctypes.c_void_p * len(xs))(*[t.data_ptr() for t in xs])
         hy = (ctypes.c_float * 8)(*[float(h) for h in hyper])
         code = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}[dtype]
-        _l.call("gb_comm_fused_step", _l.I(mode), _l.I(code),
+        _l.call("gb_comm_fused_step2", _l.I(mode), _l.I(code),
                 _l.L(self.abs_offset(grad_off)), _l.L(self.abs_offset(param_off)), _l.L(n),
-                arr(master), arr(m), arr(v), hy, _l.ptr(hyper_dev), _l.I(ctas), _l.I(1 if self.emulate else 0),
+                arr(master), arr(m), arr(v), hy, _l.ptr(hyper_dev), _l.I(self.OPT_KINDS[kind]), _l.I(phase),
+                arr(wd_mask), arr(gshard), arr(sqpart), _l.I(ctas), _l.I(1 if self.emulate else 0),
                 _l.stream_ptr())
 
     def all_reduce(self, offset_bytes: int, n: int, dtype: torch.dtype, op: str = "sum", ctas: int = 64):
@@ -203,28 +211,46 @@ class SymmetricMemory:
         self.fused_step(0, dtype, offset_bytes, offset_bytes, n, None, None, None,
                         [0, 0, 0, 0, 0, 1, 1, scale], ctas)
 
-    def _fused_step_host(self, mode, dtype, grad_off, param_off, n, master, m, v, hyper):
+    def _fused_step_host(self, mode, dtype, grad_off, param_off, n, master, m, v, hyper, kind="adamw", phase=0,
+                         wd_mask=None, gshard=None, sqpart=None):
         """Restatement of the kernel's arithmetic on the host (fp32, same operation order):
-        mean of the gradients over ranks, then either the mean written back (mode 0) or AdamW
-        on the slice this rank owns followed by an all-gather of the updated parameters."""
+        mean of the gradients over ranks, then either the mean written back (mode 0) or the
+        optimizer on the slice this rank owns followed by an all-gather of the updated parameters."""
         lr, wd, b1, b2, eps, bc1, bc2, gscale = [float(h) for h in hyper]
         W = self.world
-        g = self.view(grad_off, n, dtype).float()
-        if W > 1:
-            import torch.distributed as dist
-            dist.all_reduce(g, group=self._pg)
-            g /= W
-        g = g * gscale
-        if mode == 0:
-            self.view(grad_off, n, dtype).copy_(g.to(dtype))
-            return
         L = n // W
-        g = g[self.rank * L:(self.rank + 1) * L]
+        if phase == 2:
+            g = gshard * gscale
+        else:
+            g = self.view(grad_off, n, dtype).float()
+            if W > 1:
+                import torch.distributed as dist
+                dist.all_reduce(g, group=self._pg)
+                g /= W
+            if phase == 1:
+                gshard.copy_(g[self.rank * L:(self.rank + 1) * L])
+                sqpart.zero_()
+                sqpart[0] = (gshard * gshard).sum()
+                return
+            g = g * gscale
+            if mode == 0:
+                self.view(grad_off, n, dtype).copy_(g.to(dtype))
+                return
+            g = g[self.rank * L:(self.rank + 1) * L]
         p = master
-        p.mul_(1 - lr * wd)
-        m.mul_(b1).add_(g, alpha=1 - b1)
-        v.mul_(b2).addcmul_(g, g, value=1 - b2)
-        p.sub_(lr * (m / bc1) / ((v / bc2).sqrt() + eps))
+        wdv = wd if wd_mask is None else wd * wd_mask.to(torch.float32).repeat_interleave(8)
+        if kind == "adamw":
+            p.mul_(1 - lr * wdv)
+            m.mul_(b1).add_(g, alpha=1 - b1)
+            v.mul_(b2).addcmul_(g, g, value=1 - b2)
+            p.sub_(lr * (m / bc1) / ((v / bc2).sqrt() + eps))
+        elif kind == "sgd":
+            m.mul_(b1).add_(g + wdv * p)
+            p.sub_(lr * m)
+        else:
+            c = b1 * m + (1 - b1) * g
+            p.sub_(lr * (torch.sign(c) + wdv * p))
+            m.mul_(b2).add_(g, alpha=1 - b2)
         out = self.view(param_off, n, dtype)
         if W == 1:
             out.copy_(p.to(dtype))
