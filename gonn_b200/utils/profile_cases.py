@@ -8,6 +8,7 @@
     python -m gonn_b200.utils.profile_cases norm_fork 16384 768       # backward with the residual bypass fused
     python -m gonn_b200.utils.profile_cases step 50000000
     python -m gonn_b200.utils.profile_cases conv 256 64 128 15 15     # N C_in C_out H W, 3x3: forward + backward
+    python -m gonn_b200.utils.profile_cases suite                      # one launch or two of every other kernel family
 
 Each case allocates a few hundred MB at most, runs three warm-up launches and
 then five timed launches (CUDA events), and prints one line with the time and the
@@ -113,6 +114,81 @@ def main(argv):
         fl = 2.0 * N * Co * Ci * 9 * (H - 2) * (W - 2)
         print(f"conv {N}x{Ci}->{Co} {H}x{W}: fwd {ms_f:.4f} ms ({fl / ms_f / 1e9:.1f} TFLOP/s), "
               f"bwd {ms_b:.4f} ms ({2 * fl / ms_b / 1e9:.1f} TFLOP/s)")
+    elif kind == "suite":
+        # Memory-bound and small kernels, each on an input of a few hundred MB at most (larger than the
+        # 126 MB L2 where the kernel streams).  Every op runs twice; a profiler keeps the last launch.
+        from .. import nn, optim, quant
+        from ..nn.batchnorm import BatchNorm2d
+        from ..ops import elementwise as ew
+        from ..ops.attention import general_attention
+        from ..ops.norm import norm_fork, rms_norm
+        from ..ops.reduce import column_sum
+        from ..ops.softmax import cross_entropy
+        bf = torch.bfloat16
+        for rep in range(2):
+            # elementwise: binary add, unary gelu forward / backward, cast
+            a = torch.randn(1 << 26, device=dev, dtype=bf)
+            b = torch.randn(1 << 26, device=dev, dtype=bf)
+            ew.binary_forward("add", a, b)
+            g = ew.unary_forward("gelu", a)
+            ew.unary_backward("gelu", a, b)
+            a.float()
+            del a, b, g
+            # norms: LayerNorm forward / backward / fork backward, RMSNorm forward
+            x = torch.randn(65536, 768, device=dev, dtype=bf, requires_grad=True)
+            w = torch.ones(768, device=dev, dtype=bf, requires_grad=True)
+            bb = torch.zeros(768, device=dev, dtype=bf, requires_grad=True)
+            rb = torch.zeros(768, device=dev, dtype=bf, requires_grad=True)
+            dy = torch.randn(65536, 768, device=dev, dtype=bf)
+            torch.autograd.grad(layer_norm(x, w, bb), (x, w, bb), dy)
+            y, xp = norm_fork(x, w, bb, 1e-5, False, rb)
+            torch.autograd.grad((y, xp), (x, w, bb, rb), (dy, dy))
+            rms_norm(x.detach(), w.detach())
+            column_sum(dy)
+            del x, dy, y, xp
+            # softmax cross-entropy forward + in-place backward on LM-sized logits
+            logits = torch.randn(8192, 32000, device=dev, dtype=bf, requires_grad=True)
+            tgt = torch.randint(0, 32000, (8192,), device=dev)
+            cross_entropy(logits, tgt).backward()
+            del logits
+            # embedding gather and deterministic scatter-add backward
+            emb = nn.Embedding(32000, 768, dtype=bf, device=dev)
+            ids = torch.randint(0, 32000, (16, 1024), device=dev)
+            emb(ids).sum().backward()
+            # BatchNorm forward / backward, max pooling forward / backward
+            bn = BatchNorm2d(64, dtype=bf, device=dev)
+            img = torch.randn(256, 64, 30, 30, device=dev, dtype=bf, requires_grad=True)
+            pool = nn.MaxPool2d(2)
+            pool(bn(img)).sum().backward()
+            # int8 Linear (dynamic quantisation: observe, quantise, int8 tcgen05 GEMM with dequantising epilogue)
+            lin = nn.Linear(4096, 4096, dtype=torch.float32, device=dev)
+            ql = quant.NewDynamicLinearFrom(lin)
+            ql(torch.randn(8192, 4096, device=dev))
+            # multi-tensor AdamW over a few dozen tensors and global-norm clipping
+            ps = [torch.nn.Parameter(torch.randn(1024, 1024, device=dev)) for _ in range(32)]
+            for p_ in ps:
+                p_.grad = torch.randn_like(p_)
+            opt = optim.AdamW(ps, lr=1e-3)
+            optim.ClipGradNorm(ps, 1.0)
+            opt.step()
+            del ps, opt
+            # exact-precision GEMMs: fp64 tensor-core kernel, fp32 as three bf16 planes (split + tcgen05)
+            a64 = torch.randn(2048, 2048, device=dev, dtype=torch.float64)
+            gemm(a64, a64)
+            a32 = torch.randn(2048, 2048, device=dev)
+            gemm(a32, a32)
+            # split-K weight-gradient GEMM with its finish kernel
+            dyw = torch.randn(16384, 768, device=dev, dtype=bf)
+            xw = torch.randn(16384, 3072, device=dev, dtype=bf)
+            gemm(dyw, xw, trans_a=True)
+            # general attention (masked, dropout), forward and backward
+            q = torch.randn(4, 512, 8, 64, device=dev, dtype=bf, requires_grad=True)
+            kk = torch.randn(4, 512, 8, 64, device=dev, dtype=bf, requires_grad=True)
+            vv = torch.randn(4, 512, 8, 64, device=dev, dtype=bf, requires_grad=True)
+            mask = torch.rand(512, 512, device=dev) < 0.2
+            general_attention(q, kk, vv, True, None, mask, None, 0.1, 7).sum().backward()
+            torch.cuda.synchronize()
+        print("suite done")
     elif kind == "step":
         n = int(argv[1]) // 8 * 8
         from ..distributed.nvlink import SymmetricMemory
