@@ -1,6 +1,8 @@
 """NCCL + cuBLAS baseline: the same models written with stock PyTorch layers, trained with
 torch DDP, torch's fused AdamW and bf16 autocast over fp32 parameters (the usual PyTorch
-recipe).  Prints the same JSON line as bench.py with "impl": "torch-ddp".
+recipe), or with ``--twin bf16`` entirely in bf16 (bf16 parameters, no cast kernels, no fp32
+copy of the logits): the faster of the two is the number to compare against.  Prints the same
+JSON line as bench.py with "impl": "torch-ddp".
 
     python baseline/torch_ddp.py --config lm --steps 10 --warmup 3
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 baseline/torch_ddp.py --gpus 8
@@ -73,6 +75,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--config", default="lm", choices=["lm", "gpt", "cnn"])
     ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--twin", default="autocast", choices=["autocast", "bf16"],
+                    help="autocast: fp32 parameters under torch.autocast with fp32 logits into the loss (torch's "
+                         "documented mixed-precision recipe); bf16: parameters, activations and logits all bf16, no "
+                         "cast kernels, fused AdamW on the bf16 parameters (the fastest plain-torch build of the model)")
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -90,20 +96,28 @@ def main():
         model, B, S, V = LM(32000, 768, 12, 12, 3072, 1024).to(dev), a.batch or 16, 1024, 32000
     else:
         model, B, S, V = LM(50304, 2048, 24, 16, 8192, 2048, rms=True).to(dev), a.batch or 4, 2048, 50304
+    pure = a.twin == "bf16"
+    if pure:
+        model = model.to(torch.bfloat16)
     net = nn.parallel.DistributedDataParallel(model, device_ids=[lr], gradient_as_bucket_view=True) if world > 1 else model
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, weight_decay=0.1, fused=True)
     g = torch.Generator().manual_seed(100 + rank)
     if a.config == "cnn":
         x = torch.randn(B, 3, 32, 32, generator=g).to(dev).contiguous(memory_format=torch.channels_last)
+        if pure:
+            x = x.to(torch.bfloat16)
         y = torch.randint(0, 10, (B,), generator=g).to(dev)
     else:
         x = torch.randint(0, V, (B, S), generator=g).to(dev)
         y = torch.roll(x, -1, 1)
 
     def step():
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            logits = net(x)
-        loss = F.cross_entropy(logits.view(-1, V).float(), y.view(-1))
+        if pure:
+            loss = F.cross_entropy(net(x).view(-1, V), y.view(-1))
+        else:
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                logits = net(x)
+            loss = F.cross_entropy(logits.view(-1, V).float(), y.view(-1))
         loss.backward()
         opt.step()
         opt.zero_grad(set_to_none=True)
@@ -127,7 +141,8 @@ def main():
     if rank == 0:
         print(json.dumps({"impl": "torch-ddp", "metric": "training throughput", "config": a.config,
                           "value": B * S * world * a.steps / (ms.item() / 1e3), "unit": "images/s" if a.config == "cnn" else "tokens/s", "n_gpus": world,
-                          "ms_per_step": ms.item() / a.steps, "steps": a.steps, "warmup": a.warmup, "dtype": "bf16 autocast"}))
+                          "ms_per_step": ms.item() / a.steps, "steps": a.steps, "warmup": a.warmup, "twin": a.twin,
+                          "dtype": "bf16 parameters and activations" if pure else "bf16 autocast over fp32 parameters"}))
     if world > 1:
         dist.destroy_process_group()
 

@@ -47,22 +47,39 @@ __global__ void emb_count_kernel(const long long* __restrict__ idx, long long n,
   }
 }
 
-// exclusive scan of count[0..V) into offs[0..V]; single CTA of 1024 threads
+// exclusive scan of count[0..V) into offs[0..V]; single CTA of 1024 threads.  Every thread owns a
+// contiguous run of counters (whole cache lines once V >= 32 K), the 1024 run totals are scanned with
+// warp shuffles (two levels), and the second pass re-reads the run from L1.
 __global__ void emb_scan_kernel(const int* __restrict__ count, int V, int* __restrict__ offs) {
-  __shared__ int part[1024];
+  __shared__ int warp_tot[32];
   const int per = (V + 1023) / 1024;
   const int b = threadIdx.x * per, e = min(b + per, V);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   int s = 0;
+#pragma unroll 8
   for (int i = b; i < e; i++) s += count[i];
-  part[threadIdx.x] = s;
+  int inc = s;                                           // inclusive scan inside the warp
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, d);
+    if (lane >= d) inc += t;
+  }
+  if (lane == 31) warp_tot[wid] = inc;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int run = 0;
-    for (int i = 0; i < 1024; i++) { int t = part[i]; part[i] = run; run += t; }
-    offs[V] = run;
+  if (wid == 0) {
+    const int w = warp_tot[lane];
+    int winc = w;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, winc, d);
+      if (lane >= d) winc += t;
+    }
+    warp_tot[lane] = winc - w;                           // exclusive prefix of the warp totals
+    if (lane == 31) offs[V] = winc;
   }
   __syncthreads();
-  int run = part[threadIdx.x];
+  int run = warp_tot[wid] + inc - s;
+#pragma unroll 8
   for (int i = b; i < e; i++) { offs[i] = run; run += count[i]; }
 }
 

@@ -57,20 +57,23 @@ multi_tensor_kernel(const TensorList tl, const Hyper h, float* __restrict__ aux)
   const int t = find_tensor(tl, blockIdx.x);
   const long long base = (long long)(blockIdx.x - tl.chunk_start[t]) * kChunk;
   const long long n = tl.numel[t];
-  T* p = (T*)tl.p[t];
-  const T* g = (const T*)tl.g[t];
-  float* master = (float*)tl.master[t];
-  ST* s0 = (ST*)tl.s0[t];
-  ST* s1 = (ST*)tl.s1[t];
+  // The five arrays of one tensor never overlap, so loads of the next elements may pass the stores
+  // of this one: with four elements in flight per thread the kernel is bound by DRAM, not by latency.
+  T* __restrict__ p = (T*)tl.p[t];
+  T* __restrict__ g = (T*)tl.g[t];
+  float* __restrict__ master = (float*)tl.master[t];
+  ST* __restrict__ s0 = (ST*)tl.s0[t];
+  ST* __restrict__ s1 = (ST*)tl.s1[t];
   CT acc0 = 0, acc1 = 0;
   float trust = 1.f;
   if (ALGO == A_LAMB2) {
     float pn = sqrtf(aux[2 * t]), un = sqrtf(aux[2 * t + 1]);
     trust = (pn > 0.f && un > 0.f) ? pn / un : 1.f;
   }
-  for (int k = threadIdx.x; k < kChunk; k += kThreads) {
+  const int cnt = (int)(n - base < (long long)kChunk ? n - base : (long long)kChunk);
+#pragma unroll 4
+  for (int k = threadIdx.x; k < cnt; k += kThreads) {
     const long long i = base + k;
-    if (i >= n) break;
     CT gv = ALGO == A_LAMB2 ? CT(0) : (CT)g[i] * (CT)h.gscale;
     CT pv = master ? (CT)master[i] : (CT)p[i];
     if (ALGO == A_SGD) {
@@ -108,7 +111,7 @@ multi_tensor_kernel(const TensorList tl, const Hyper h, float* __restrict__ aux)
       s1[i] = (ST)v;
       CT u = (m / (CT)h.bc1) / (t_sqrt(v / (CT)h.bc2) + (CT)h.eps);
       if (h.wd != 0.f) u += (CT)h.wd * pv;
-      ((T*)g)[i] = (T)u;
+      g[i] = (T)u;
       acc0 += pv * pv;
       acc1 += u * u;
       continue;
@@ -118,7 +121,7 @@ multi_tensor_kernel(const TensorList tl, const Hyper h, float* __restrict__ aux)
       acc0 += gv * gv;
       continue;
     } else if (ALGO == A_SCALE) {
-      ((T*)g)[i] = (T)gv;
+      g[i] = (T)gv;
       continue;
     }
     if (master) master[i] = (float)pv;

@@ -79,6 +79,35 @@ __global__ void quantize_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
   }
 }
 
+// Sixteen elements per thread: 16-byte stores of the int8 output, 16-byte loads of the input.
+// Needs cols and ldq to be multiples of 16 and both base pointers 16-byte aligned, so that a
+// group of sixteen never straddles a row.
+template <typename T>
+__global__ void quantize_vec_kernel(const T* __restrict__ x, int8_t* __restrict__ q, long long rows,
+                                    long long cols, long long ldq, const float* __restrict__ scale,
+                                    const int* __restrict__ zp, int per_row) {
+  const long long groups = rows * cols / 16;
+  const long long gpr = cols / 16;
+  constexpr int LD = 16 / (int)sizeof(T);          // elements per 16-byte load
+  for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < groups;
+       g += (long long)gridDim.x * blockDim.x) {
+    const long long r = g / gpr, c = (g - r * gpr) * 16;
+    const float s = per_row ? scale[r] : scale[0];
+    const int z = zp ? (per_row ? zp[r] : zp[0]) : 0;
+    alignas(16) T v[16];
+#pragma unroll
+    for (int k = 0; k < 16 / LD; ++k)
+      *reinterpret_cast<uint4*>(&v[k * LD]) = *reinterpret_cast<const uint4*>(x + r * cols + c + k * LD);
+    alignas(16) int8_t o[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      int w = (int)roundf((float)v[k] / s) + z;
+      o[k] = (int8_t)(w < -128 ? -128 : (w > 127 ? 127 : w));
+    }
+    *reinterpret_cast<uint4*>(q + r * ldq + c) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
 // MODE 0: y = (q(x) - zp) * s;  MODE 1: dx = dy where x lies inside the representable range
 template <typename T, int MODE>
 __global__ void fake_quant_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __restrict__ y,
@@ -140,7 +169,12 @@ GB_EXPORT int gb_q_quantize(int dtype, const void* x, void* q, long long rows, l
                             void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
   if (rows * cols <= 0) return gbh::E_OK;
-  GB_Q_DISPATCH((quantize_kernel<T><<<grid_for(rows * cols), 256, 0, s>>>((const T*)x, (int8_t*)q, rows, cols, ldq, scale, zp, per_row)));
+  const bool vec = cols % 16 == 0 && ldq % 16 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)q & 15) == 0;
+  if (vec) {
+    GB_Q_DISPATCH((quantize_vec_kernel<T><<<grid_for(rows * cols / 16), 256, 0, s>>>((const T*)x, (int8_t*)q, rows, cols, ldq, scale, zp, per_row)));
+  } else {
+    GB_Q_DISPATCH((quantize_kernel<T><<<grid_for(rows * cols), 256, 0, s>>>((const T*)x, (int8_t*)q, rows, cols, ldq, scale, zp, per_row)));
+  }
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;
 }
