@@ -26,6 +26,7 @@ enum StatusCode : int {
   ST_CONV_TIMEOUT = 4,
   ST_BAD_INDEX = 5,
   ST_NORM_TIMEOUT = 6,
+  ST_OUT_OF_BOUNDS = 7,  // bounds-checked debug build only (bounds.cuh)
 };
 
 // The status word is four ints in device memory owned by runtime.cu:

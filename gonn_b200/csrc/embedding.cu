@@ -8,7 +8,7 @@
 //
 // The reference's Embedding is IndexSelect with a scatter-add backward on the
 // host (tensor/ops_index.go:7-113, nn/embedding.go:108-126).
-#include "common.cuh"
+#include "bounds.cuh"
 
 using namespace gb;
 
@@ -89,7 +89,10 @@ __global__ void emb_place_kernel(const long long* __restrict__ idx, long long n,
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (long long)gridDim.x * blockDim.x) {
     long long v = idx[i];
-    if (v >= 0 && v < V) perm_tmp[offs[v] + atomicAdd(&cursor[v], 1)] = (int)i;
+    if (v >= 0 && v < V) {
+      const int slot = offs[v] + atomicAdd(&cursor[v], 1);
+      if (GB_IN_BOUNDS(slot, n, 201)) perm_tmp[slot] = (int)i;
+    }
   }
 }
 
@@ -101,12 +104,14 @@ __global__ void emb_rank_kernel(const long long* __restrict__ idx, long long n, 
        s += (long long)gridDim.x * blockDim.x) {
     // slot s belongs to the vocabulary row of the token stored there
     const int pos = perm_tmp[s];
-    if (pos < 0) continue;
+    if (pos < 0 || !GB_IN_BOUNDS(pos, n, 202)) continue;
     const long long v = idx[pos];
+    if (!GB_IN_BOUNDS(v, V, 203)) continue;
     const int b = offs[v], e = offs[v + 1];
+    if (!GB_IN_BOUNDS(e, n + 1, 204)) continue;
     int rank = 0;
     for (int j = b; j < e; j++) rank += perm_tmp[j] < pos;
-    perm[b + rank] = pos;
+    if (GB_IN_BOUNDS(b + rank, n, 205)) perm[b + rank] = pos;
   }
 }
 
@@ -116,7 +121,7 @@ template <> struct EAcc<double> { using CT = double; };
 template <typename T, typename TO>
 __global__ void emb_reduce_kernel(const T* __restrict__ dy, const int* __restrict__ offs,
                                   const int* __restrict__ perm, TO* __restrict__ dw, long long V,
-                                  int D, long long padding_idx, int accumulate) {
+                                  int D, long long padding_idx, int accumulate, long long n) {
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (long long v = (long long)blockIdx.x * warps + warp; v < V; v += (long long)gridDim.x * warps) {
     const int b = offs[v], e = (v == padding_idx) ? b : offs[v + 1];
@@ -125,6 +130,7 @@ __global__ void emb_reduce_kernel(const T* __restrict__ dy, const int* __restric
       using CT = typename EAcc<T>::CT;
       CT a0 = 0, a1 = 0, a2 = 0, a3 = 0;
       for (int j = b; j < e; j++) {
+        if (!GB_IN_BOUNDS(j, n, 206) || !GB_IN_BOUNDS(perm[j], n, 207)) break;
         const T* src = dy + (long long)perm[j] * D + c0;
         a0 += (CT)src[0];
         if (c0 + 1 < D) a1 += (CT)src[1];
@@ -191,6 +197,7 @@ GB_EXPORT int gb_embedding_bwd(int dtype, int out_dtype, const void* dy, const l
                                int accumulate, int* scratch, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
   if (V <= 0 || D <= 0) return gbh::E_OK;
+  GB_BOUNDS_BIND();
   if (n > 0x7fffffffLL || V > 0x7fffffffLL) {
     gbh::set_error("gb_embedding_bwd: sizes beyond 2^31 are not supported");
     return gbh::E_TOO_LARGE;
@@ -214,7 +221,7 @@ GB_EXPORT int gb_embedding_bwd(int dtype, int out_dtype, const void* dy, const l
   }
   long long g2 = (V + 7) / 8;
   if (g2 > 148 * 16) g2 = 148 * 16;
-#define GB_E(T, TO) emb_reduce_kernel<T, TO><<<(int)g2, 256, 0, s>>>((const T*)dy, offs, perm, (TO*)dw, V, D, padding_idx, accumulate)
+#define GB_E(T, TO) emb_reduce_kernel<T, TO><<<(int)g2, 256, 0, s>>>((const T*)dy, offs, perm, (TO*)dw, V, D, padding_idx, accumulate, n)
   if (dtype == DT_BF16 && out_dtype == DT_BF16) GB_E(__nv_bfloat16, __nv_bfloat16);
   else if (dtype == DT_BF16 && out_dtype == DT_F32) GB_E(__nv_bfloat16, float);
   else if (dtype == DT_F16 && out_dtype == DT_F16) GB_E(__half, __half);

@@ -6,7 +6,7 @@
 // The reference composes these norms from ~10 elementwise / reduce tape nodes
 // (nn/norm.go:50-78, 115-148); eps 1e-5 for LayerNorm, 1e-6 for RMSNorm, biased
 // variance, RMSNorm = x / sqrt(mean(x^2) + eps) * w.
-#include "common.cuh"
+#include "bounds.cuh"
 
 using namespace gb;
 
@@ -265,6 +265,7 @@ norm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, const TW* __r
     }
   }
   if (part == nullptr) return;
+  if (!GB_IN_EXTENT(blockIdx.x, 0, 401)) return;   // more CTAs than partial rows in the scratch
   float* out = part + (long long)blockIdx.x * 2 * D;
   if (G == 32) {
     // combine the 8 warps of the CTA, one warp at a time
@@ -818,6 +819,7 @@ norm_bwd_pipe_kernel(const T* __restrict__ x, const T* __restrict__ dy, const T*
     }
   }
   __syncthreads();
+  if (!GB_IN_EXTENT(blockIdx.x, 0, 402)) return;   // more CTAs than partial rows in the scratch
   float* out = part + (long long)blockIdx.x * NP * D;
   for (int c = threadIdx.x; c < NP * D; c += kPipeThreads) {
     float sacc = 0.f;
@@ -1077,6 +1079,8 @@ GB_EXPORT int gb_norm_bwd(int kind, int dtype, int wdtype, const void* x, const 
                           long long rows, int D, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
   if (rows <= 0 || D <= 0) return gbh::E_OK;
+  GB_BOUNDS_BIND();
+  GB_BOUNDS_EXTENT(0, scratch_rows, s);
 #define GB_N(DTI, T, WDI, TW)                                                                        \
   if (dtype == DTI && wdtype == WDI)                                                                 \
     return kind ? norm_bwd_t<T, TW, true>(x, dy, w, mean, rstd, dx, dgamma, dbeta, scratch,          \
@@ -1106,6 +1110,8 @@ GB_EXPORT int gb_norm_bwd_res(int kind, int dtype, int wdtype, const void* x, co
                               int D, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
   if (rows <= 0 || D <= 0) return gbh::E_OK;
+  GB_BOUNDS_BIND();
+  GB_BOUNDS_EXTENT(0, scratch_rows, s);
   const int V = dtype == DT_F32 ? 4 : 8;
   const bool aligned = (D % V == 0) && (D / V <= 1024) &&
                        ((((uintptr_t)x | (uintptr_t)dy | (uintptr_t)dres | (uintptr_t)dx) & 15) == 0);

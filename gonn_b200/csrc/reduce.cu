@@ -5,7 +5,7 @@
 //   inner  > 1  column reduction, coalesced along inner, R optionally split
 //               across CTAs with a second fixed-order pass (deterministic)
 // The column form with outer == 1 is the bias-gradient reduction of Linear.
-#include "common.cuh"
+#include "bounds.cuh"
 
 using namespace gb;
 
@@ -121,7 +121,7 @@ __global__ void col_reduce_kernel(const T* __restrict__ x, TO* __restrict__ y,
 #pragma unroll
     for (int k = 1; k < 8; k++) a = r_comb<CT, OP>(a, sm[k][threadIdx.x]);
     if (to_part) {
-      part[(o * splits + blockIdx.y) * inner + col] = a;
+      if (GB_IN_BOUNDS(blockIdx.y, splits, 301)) part[(o * splits + blockIdx.y) * inner + col] = a;
     } else {
       if (OP == R_MEAN) a = a / (CT)R;
       y[o * inner + col] = (TO)a;
@@ -145,7 +145,7 @@ col_reduce_vec_kernel(const T* __restrict__ x, TO* __restrict__ y, float* __rest
   float a[8];
 #pragma unroll
   for (int j = 0; j < 8; j++) a[j] = r_init<float, OP>();
-  if (col0 < inner) {
+  if (col0 < inner && GB_IN_BOUNDS(col0 + 7, inner, 303)) {   // a thread reads eight whole columns
     const T* xp = x + o * R * inner + col0;
     auto take = [&](const uint4& u) {
       const T* e = reinterpret_cast<const T*>(&u);
@@ -172,7 +172,7 @@ col_reduce_vec_kernel(const T* __restrict__ x, TO* __restrict__ y, float* __rest
 #pragma unroll
     for (int k = 1; k < 8; k++) v = r_comb<float, OP>(v, sm[k][ty * 32 + tx]);
     if (to_part) {
-      part[(o * splits + blockIdx.y) * inner + col] = v;
+      if (GB_IN_BOUNDS(blockIdx.y, splits, 302)) part[(o * splits + blockIdx.y) * inner + col] = v;
     } else {
       if (OP == R_MEAN) v = v / (float)R;
       y[o * inner + col] = (TO)v;
@@ -298,6 +298,7 @@ GB_EXPORT int gb_reduce(int op, int dtype, int out_dtype, const void* x, void* y
                         long long scratch_bytes, long long outer, long long R, long long inner,
                         int accumulate, void* stream) {
   cudaStream_t s = (cudaStream_t)stream;
+  GB_BOUNDS_BIND();
   if (scratch == nullptr) scratch_bytes = 0;
   if (dtype == DT_BF16 && out_dtype == DT_BF16) return reduce_t<__nv_bfloat16, __nv_bfloat16>(op, x, y, scratch, scratch_bytes, outer, R, inner, accumulate, s);
   if (dtype == DT_BF16 && out_dtype == DT_F32) return reduce_t<__nv_bfloat16, float>(op, x, y, scratch, scratch_bytes, outer, R, inner, accumulate, s);

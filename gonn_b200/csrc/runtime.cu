@@ -117,6 +117,15 @@ GB_EXPORT int gb_status_read(int* out, int clear) {
   return gbh::E_OK;
 }
 
+// 1 when this library was compiled with -DGB_BOUNDS_CHECK (bounds.cuh), else 0.
+GB_EXPORT int gb_bounds_checked_build() {
+#ifdef GB_BOUNDS_CHECK
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 GB_EXPORT int gb_sm_count() {
   int dev = 0, n = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 0;

@@ -13,7 +13,7 @@
 //   window_scatter  dx[n][c][i] = sum over (win,tap) with idx[win][tap]==i of
 //                   dcol[n][win][c*T + tap]                              (col2im)
 //   pool_fwd / pool_bwd   max (with argmax), average, LP-norm pooling over idx
-#include "common.cuh"
+#include "bounds.cuh"
 
 using namespace gb;
 
@@ -51,7 +51,7 @@ __global__ void window_gather_kernel(const T* __restrict__ x, const int* __restr
     if (k < K) {
       const int c = k / T_, tap = k - c * T_;
       const int src = idx[win * T_ + tap];
-      v = src >= 0 ? x[((long long)n * C + c) * S + src] : (T)fill;
+      v = (src >= 0 && GB_IN_BOUNDS(src, S, 101)) ? x[((long long)n * C + c) * S + src] : (T)fill;
     }
     col[i] = v;
   }
@@ -74,6 +74,7 @@ __global__ void window_scatter_kernel(const T* __restrict__ dcol, const int* __r
     for (int e = offs[pos]; e < offs[pos + 1]; e++) {
       const int wt = cols[e];
       const int win = wt / T_, tap = wt - win * T_;
+      if (!GB_IN_BOUNDS(wt, (long long)nwin * T_, 102)) continue;
       acc += (float)dcol[((long long)n * nwin + win) * kpad + c * T_ + tap];
     }
     dx[i] = accumulate ? (T)((float)dx[i] + acc) : (T)acc;
@@ -101,7 +102,7 @@ __global__ void pool_fwd_kernel(const T* __restrict__ x, const int* __restrict__
       int bt = -1;
       for (int t = 0; t < T_; t++) {
         const int src = iw[t];
-        if (src < 0) continue;
+        if (src < 0 || !GB_IN_BOUNDS(src, S, 103)) continue;
         const float v = (float)xb[src];
         if (v > best || bt < 0) { best = v; bt = t; }
       }
@@ -112,7 +113,7 @@ __global__ void pool_fwd_kernel(const T* __restrict__ x, const int* __restrict__
       int cnt = 0;
       for (int t = 0; t < T_; t++) {
         const int src = iw[t];
-        if (src >= 0) { s += (float)xb[src]; cnt++; }
+        if (src >= 0 && GB_IN_BOUNDS(src, S, 104)) { s += (float)xb[src]; cnt++; }
       }
       const int div = count_include_pad ? T_ : (cnt > 0 ? cnt : 1);
       y[i] = (T)(s / (float)div);
@@ -120,7 +121,7 @@ __global__ void pool_fwd_kernel(const T* __restrict__ x, const int* __restrict__
       float s = 0.f;
       for (int t = 0; t < T_; t++) {
         const int src = iw[t];
-        if (src >= 0) s += powf((float)xb[src], p);
+        if (src >= 0 && GB_IN_BOUNDS(src, S, 105)) s += powf((float)xb[src], p);
       }
       y[i] = (T)powf(s, 1.f / p);
     }
@@ -145,6 +146,7 @@ __global__ void pool_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
     for (int e = offs[pos]; e < offs[pos + 1]; e++) {
       const int wt = cols[e];
       const int win = wt / T_, tap = wt - win * T_;
+      if (!GB_IN_BOUNDS(wt, (long long)nwin * T_, 106)) continue;
       const long long o = b * nwin + win;
       if (mode == POOL_MAX) {
         if (arg[o] == tap) acc += (float)dy[o];
@@ -183,7 +185,7 @@ __global__ void pool_bwd_disjoint_kernel(const T* __restrict__ dy, const int* __
     for (int pos = blockIdx.x * blockDim.x + threadIdx.x; pos < S; pos += gridDim.x * blockDim.x) {
       const int2 w = __ldg(p2w + pos);
       float v = 0.f;
-      if (w.x >= 0) {
+      if (w.x >= 0 && GB_IN_BOUNDS(w.x, nwin, 107)) {
         const float g = (float)dyb[w.x];
         if (mode == POOL_MAX) v = (ab[w.x] == w.y) ? g : 0.f;
         else v = g / (float)(count_include_pad ? T_ : max(__ldg(wcnt + w.x), 1));
@@ -220,6 +222,7 @@ GB_EXPORT int gb_window_gather(int dtype, const void* x, const int* idx, void* c
   const long long total = (long long)N * nwin * kpad;
   if (total <= 0) return gbh::E_OK;
   cudaStream_t s = (cudaStream_t)stream;
+  GB_BOUNDS_BIND();
   GB_DISPATCH_T((window_gather_kernel<T><<<grid_for(total), 256, 0, s>>>((const T*)x, idx, (T*)col, N, C, S, nwin, T_, kpad, fill)));
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;
@@ -232,6 +235,7 @@ GB_EXPORT int gb_window_scatter(int dtype, const void* dcol, const int* offs, co
   const long long total = (long long)N * C * S;
   if (total <= 0) return gbh::E_OK;
   cudaStream_t s = (cudaStream_t)stream;
+  GB_BOUNDS_BIND();
   GB_DISPATCH_T((window_scatter_kernel<T><<<grid_for(total), 256, 0, s>>>((const T*)dcol, offs, cols, (T*)dx, N, C, S, nwin, T_, kpad, accumulate)));
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;
@@ -244,6 +248,7 @@ GB_EXPORT int gb_pool_fwd(int dtype, const void* x, const int* idx, void* y, int
   const long long total = B * nwin;
   if (total <= 0) return gbh::E_OK;
   cudaStream_t s = (cudaStream_t)stream;
+  GB_BOUNDS_BIND();
   GB_DISPATCH_T((pool_fwd_kernel<T><<<grid_for(total), 256, 0, s>>>((const T*)x, idx, (T*)y, arg, B, S, nwin, T_, mode, count_include_pad, p)));
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;
@@ -259,6 +264,7 @@ GB_EXPORT int gb_pool_bwd_disjoint(int dtype, const void* dy, const int* arg, co
     return gbh::E_BAD_ARG;
   }
   cudaStream_t s = (cudaStream_t)stream;
+  GB_BOUNDS_BIND();
   const int bx = (int)((S + 255) / 256 < 64 ? (S + 255) / 256 : 64);
   const int by = (int)(B < 65535 ? B : 65535);
   GB_DISPATCH_T((pool_bwd_disjoint_kernel<T><<<dim3(bx, by), 256, 0, s>>>((const T*)dy, arg, (const int2*)p2w, wcnt, (T*)dx, B, (int)S, nwin, T_, mode, count_include_pad)));
@@ -273,6 +279,7 @@ GB_EXPORT int gb_pool_bwd(int dtype, const void* dy, const void* x, const void* 
   const long long total = B * S;
   if (total <= 0) return gbh::E_OK;
   cudaStream_t s = (cudaStream_t)stream;
+  GB_BOUNDS_BIND();
   GB_DISPATCH_T((pool_bwd_kernel<T><<<grid_for(total), 256, 0, s>>>((const T*)dy, (const T*)x, (const T*)y, arg, idx, offs, cols, (T*)dx, B, S, nwin, T_, mode, count_include_pad, p)));
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;

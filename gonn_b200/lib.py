@@ -18,7 +18,10 @@ from ctypes import c_double, c_float, c_int, c_longlong, c_void_p
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "_C", "libgonn_b200.so")
+# GONN_B200_DEBUG=1 selects the bounds-checked build (python -m gonn_b200.build --debug): its window,
+# embedding, reduction and normalisation kernels report an out-of-range index through the status word.
+DEBUG_BUILD = os.environ.get("GONN_B200_DEBUG", "") not in ("", "0")
+LIB_PATH = os.path.join(_HERE, "_C", "libgonn_b200_debug.so" if DEBUG_BUILD else "libgonn_b200.so")
 
 DT_BF16, DT_F16, DT_F32, DT_F64, DT_I8 = 0, 1, 2, 3, 4
 _DT = {torch.bfloat16: DT_BF16, torch.float16: DT_F16, torch.float32: DT_F32,
