@@ -13,7 +13,8 @@ def __getattr__(name):
     if name in ("SymmetricMemory", "CollectiveTimeout"):
         from . import nvlink
         return getattr(nvlink, name)
-    if name in ("SyncBatchNorm", "SyncBatchNorm1d", "SyncBatchNorm2d", "SyncBatchNorm3d"):
+    if name in ("SyncBatchNorm", "SyncBatchNorm1d", "SyncBatchNorm2d", "SyncBatchNorm3d",
+                "NewSyncBatchNorm1d", "NewSyncBatchNorm2d", "NewSyncBatchNorm3d", "convert_sync_batchnorm"):
         from . import syncbn
         return getattr(syncbn, name)
     raise AttributeError(name)

@@ -15,11 +15,19 @@ class Activation(Module):
 
     def __init__(self, kind: str, alpha: float = 0.0, beta: float = 0.0):
         super().__init__()
-        if kind not in _ew.UNARY_IDS:
-            raise KeyError(f"nn.Activation: unknown kind {kind!r}")
+        # built-in kinds are op ids of the elementwise kernel; any other name must be in the
+        # tensor package's registry (RegisterUnary), as in the reference (nn/activation.go)
+        self._user = kind not in _ew.UNARY_IDS
+        if self._user:
+            from ..tensor import api as _api
+            if _api.LookupUnary(kind) is None:
+                raise KeyError(f"nn.Activation: unknown kind {kind!r}")
         self.kind, self.alpha, self.beta = kind, float(alpha), float(beta)
 
     def forward(self, x):
+        if self._user:
+            from ..tensor import api as _api
+            return _api.Unary(x, self.kind)
         return _ew.unary(self.kind, x, self.alpha, self.beta)
 
     def extra_repr(self):

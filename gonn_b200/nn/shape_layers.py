@@ -215,6 +215,10 @@ def NewUpsamplingBilinear2d(scale_factor: int = 2):
     return Upsample(scale_factor, "bilinear", align_corners=True)
 
 
+UpsamplingNearest2d = NewUpsamplingNearest2d
+UpsamplingBilinear2d = NewUpsamplingBilinear2d
+
+
 class PixelShuffle(Module):
     """(N, C r^2, H, W) -> (N, C, H r, W r): reshape, permute, reshape."""
 
