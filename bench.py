@@ -51,6 +51,9 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch every kernel from Python instead of replaying the step as one CUDA graph")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="run the bucket kernels on the compute stream after backward instead of beside it "
+                         "(to measure how much communication the overlap hides)")
     ap.add_argument("--quick", action="store_true", help="kernel configs: headline shape only, no sweep")
     return ap.parse_args()
 
@@ -156,7 +159,8 @@ def main():
     model = build(args.config, device, dtype, B, world)
     from gonn_b200.distributed.ddp import DistributedDataParallel
     ddp = DistributedDataParallel(model, optimizer=dict(kind="adamw", lr=3e-4, weight_decay=0.1,
-                                                        betas=(0.9, 0.999), eps=1e-8))
+                                                        betas=(0.9, 0.999), eps=1e-8),
+                                  overlap=not args.no_overlap)
 
     g = torch.Generator(device="cpu").manual_seed(100 + rank)
     if args.config == "cnn":
@@ -247,6 +251,7 @@ def main():
                        "global_batch": B * world, "seq_len": S,
                        "parallelism": f"dp{world}" + ("+zero1-fused-rs-adamw-ag" if world >= 1 else ""),
                        "optimizer": "adamw lr3e-4 wd0.1 (fp32 master, sharded 1/W)",
+                       "overlap": not args.no_overlap,
                        "launch": "eager (one launch per kernel)" if graphed is None else
                                  f"CUDA graph replay ({graphed.launches_per_step} kernels per step captured once)",
                        "cache": "per-step working set (weights, activations, logits) is > 1 GB, far "

@@ -52,6 +52,11 @@ struct AttnArgs {
   long long dq_sb, dq_ss, dq_sh;
   long long dk_sb, dk_ss, dk_sh;
   long long dv_sb, dv_ss, dv_sh;
+  // optional spill of dS^T from the dK/dV kernel: [B*H][ds_rows keys][ds_ld queries], 16-bit, already
+  // multiplied by the softmax scale.  When set, dQ is one product of this matrix with K
+  // (fa_bwd_dq_ds_kernel) instead of a second pass that recomputes S, P and dP.
+  void* dS;
+  long long ds_ld, ds_rows;
   int* status;
   // optional timeline of CTA (0,0,0) of the dK/dV kernel: [3 lanes][kTraceSlots] SM clock stamps
   long long* trace;
@@ -59,8 +64,22 @@ struct AttnArgs {
 
 constexpr int kTraceSlots = 512;
 // lane: 0 = MMA thread, 1 / 2 = first warp of elementwise group 0 / 1
+// Compiled in only with -DGB_FA_TRACE: the pointer and the counter cost three registers in a kernel
+// that sits at its register cap.
 __device__ __forceinline__ void trace_stamp(long long* trace, int lane_id, int& n) {
+#ifdef GB_FA_TRACE
   if (trace && n < kTraceSlots) trace[lane_id * kTraceSlots + n++] = clock64();
+#else
+  (void)trace; (void)lane_id; (void)n;
+#endif
+}
+
+// One 32-byte store (a whole DRAM sector) from eight registers; the address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* p, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                             uint32_t a4, uint32_t a5, uint32_t a6, uint32_t a7) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a0), "r"(a1), "r"(a2),
+               "r"(a3), "r"(a4), "r"(a5), "r"(a6), "r"(a7)
+               : "memory");
 }
 
 __device__ __forceinline__ uint32_t pack16(float a, float b, int bf) {
@@ -713,6 +732,9 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     }
     long long* tr = ((blockIdx.x | blockIdx.y | blockIdx.z) == 0 && (e & 7) == 0 && lane == 0) ? args.trace : nullptr;
     int ntr = 0;
+    // where this thread's key row starts in the dS^T spill (its half of each 64-query sub-tile)
+    // (a byte offset from args.dS; the workspace is at most 1 GiB, so 32 bits hold it)
+    const uint32_t ds_off = (uint32_t)(((((long long)b * args.H + h) * args.ds_rows + kvrow) * args.ds_ld + half * 32) * 2);
     for (int it = group; it < n_it; it += C::NBUF) {
       const int st = it % C::NS;
       trace_stamp(tr, 1 + group, ntr);  // starts waiting
@@ -744,6 +766,11 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         for (int i = 0; i < 16; i++) z[i] = 0u;
         tmem_st16(my, z);
         tmem_st16(my + 64, z);
+        if (args.dS) {
+          uint8_t* dst = (uint8_t*)args.dS + ds_off + (uint32_t)(i_begin + it) * (BSUB * 2);
+          st_global_v8(dst, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u);
+          st_global_v8(dst + 32, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u);
+        }
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
@@ -782,6 +809,12 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       trace_stamp(tr, 1 + group, ntr);  // computed
       tmem_st16(my, pp);
       tmem_st16(my + 64, pd);
+      if (args.dS) {
+        // this thread's key row, its 32 query columns: 64 contiguous bytes of dS^T
+        uint8_t* dst = (uint8_t*)args.dS + ds_off + (uint32_t)(i_begin + it) * (BSUB * 2);
+        st_global_v8(dst, pd[0], pd[1], pd[2], pd[3], pd[4], pd[5], pd[6], pd[7]);
+        st_global_v8(dst + 32, pd[8], pd[9], pd[10], pd[11], pd[12], pd[13], pd[14], pd[15]);
+      }
       tmem_st_wait();
       trace_stamp(tr, 1 + group, ntr);  // stored
       tc_fence_before();
@@ -1049,6 +1082,125 @@ fa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, C::TMEM_COLS); }
 }
 
+// dQ from the spilled dS^T: dQ[q, :] = sum over keys of dS^T[key, q] * K[key, :].  One CTA per
+// 128-query tile streams 64-key slices: the dS^T slice (64 keys x 128 queries, two 64-query
+// chunks) is the M-major A operand, the K slice (64 keys x HD) the N-major B operand, both
+// straight from TMA-written shared memory; the accumulator is HD fp32 columns of TMEM.
+// 192 threads: warp 0 TMA, warp 1 MMA, warps 2-5 the epilogue (one query row per thread).
+template <int HD>
+struct DqDsCfg {
+  static constexpr int CH = HD / 64;
+  static constexpr int DS_BYTES = 2 * BSUB * 128;        // two 64-query chunks of 64 key rows
+  static constexpr int K_BYTES = CH * BSUB * 128;
+  static constexpr int STAGE_BYTES = DS_BYTES + K_BYTES;
+  static constexpr int NS = 4;
+  static constexpr int SMEM_BYTES = NS * STAGE_BYTES + 1024 + 256;
+  static constexpr int THREADS = 192;
+};
+
+template <int HD, bool BF>
+__global__ void __launch_bounds__(DqDsCfg<HD>::THREADS, 2)
+fa_bwd_dq_ds_kernel(const __grid_constant__ CUtensorMap tmDS, const __grid_constant__ CUtensorMap tmK,
+                    const AttnArgs args) {
+  using C = DqDsCfg<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* ring = smem;
+  uint64_t* bars = (uint64_t*)(ring + C::NS * C::STAGE_BYTES);
+  uint64_t* full = bars;                 // NS
+  uint64_t* empty = full + C::NS;        // NS
+  uint64_t* acc_done = empty + C::NS;    // 1
+  uint32_t* tmem_slot = (uint32_t*)(acc_done + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_q_tiles = (args.Sq + BQ - 1) / BQ;
+  const int q_tile = args.causal ? (num_q_tiles - 1 - (int)blockIdx.x) : (int)blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = q_tile * BQ;
+  int n_sub = (args.Sk + BSUB - 1) / BSUB;
+  if (args.causal) n_sub = min(n_sub, (q_tile + 1) * (BQ / BSUB));
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::NS; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmDS);
+    tma_prefetch_desc(&tmK);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, HD); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int st = 0;
+      uint32_t ph = 0;
+      for (int j = 0; j < n_sub; j++) {
+        if (!mbar_wait(&empty[st], ph ^ 1, abort_flag, args.status, ST_ATTN_TIMEOUT, 31)) break;
+        mbar_expect_tx(&full[st], C::STAGE_BYTES);
+        uint8_t* sD = ring + st * C::STAGE_BYTES;
+        uint8_t* sK = sD + C::DS_BYTES;
+        tma_load_4d(sD, &tmDS, &full[st], q0, j * BSUB, b * args.H + h, 0);
+        tma_load_4d(sD + BSUB * 128, &tmDS, &full[st], q0 + 64, j * BSUB, b * args.H + h, 0);
+#pragma unroll
+        for (int c = 0; c < C::CH; c++)
+          tma_load_4d(sK + c * BSUB * 128, &tmK, &full[st], c * 64, j * BSUB, h, b);
+        if (++st == C::NS) { st = 0; ph ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      const uint32_t idesc = make_idesc(1u, BF ? 1u : 0u, true, true, 128, HD);
+      int st = 0;
+      uint32_t ph = 0;
+      for (int j = 0; j < n_sub; j++) {
+        if (!mbar_wait(&full[st], ph, abort_flag, args.status, ST_ATTN_TIMEOUT, 32)) break;
+        tc_fence_after();
+        const uint32_t da = smem_u32(ring + st * C::STAGE_BYTES), ka = da + C::DS_BYTES;
+#pragma unroll
+        for (int k = 0; k < BSUB / 16; k++)
+          tc_mma_f16(tmem_base, mndesc_sub(da, k), mndesc_sub(ka, k), idesc, (j | k) != 0);
+        tc_commit(&empty[st]);
+        if (j == n_sub - 1) tc_commit(acc_done);
+        if (++st == C::NS) { st = 0; ph ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int qrow = q0 + r;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    bool ok = true;
+    if (n_sub > 0) ok = mbar_wait(acc_done, 0, abort_flag, args.status, ST_ATTN_TIMEOUT, 33);
+    if (ok) {
+      tc_fence_after();
+      uint16_t* dqrow = (uint16_t*)args.dQ + (long long)b * args.dq_sb + (long long)qrow * args.dq_ss +
+                        (long long)h * args.dq_sh;
+#pragma unroll
+      for (int c = 0; c < HD / 32; c++) {
+        uint32_t rr[32];
+        float v[32];
+        if (n_sub > 0) {
+          tmem_ld32(lane_addr + c * 32, rr);
+          tmem_ld_wait();
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i++) v[i] = n_sub > 0 ? __uint_as_float(rr[i]) : 0.f;
+        if (qrow < args.Sq) store_row16_lim<32>(dqrow + c * 32, v, BF, args.D - c * 32);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, HD); }
+}
+
 int make_qkv_map(CUtensorMap* m, const void* p, int in_bf16, int B, int H, int S, int D,
                  long long sb, long long ss, long long sh, int box_rows) {
   uint64_t dims[4] = {(uint64_t)D, (uint64_t)S, (uint64_t)H, (uint64_t)B};
@@ -1077,6 +1229,7 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
 struct BwdMaps {
   CUtensorMap q128, k128, v128, g128;  // 128-row boxes (resident tiles)
   CUtensorMap q64, k64, v64, g64;      // 64-row boxes (streamed sub-tiles)
+  CUtensorMap ds;                      // the dS^T spill: (query, key, batch*head), boxes of 64 x 64
 };
 
 int g_fa_dual = 1;
@@ -1094,7 +1247,17 @@ int launch_bwd(const BwdMaps& m, const AttnArgs& a, cudaStream_t s) {
   fa_bwd_dkv_kernel<HD, BF, DUAL><<<gkv, C::THREADS, C::SMEM_BYTES, s>>>(m.q64, m.k128, m.v128, m.g64, a);
   GB_CUDA_OK(cudaGetLastError());
   dim3 gq((a.Sq + BQ - 1) / BQ, a.H, a.B);
-  fa_bwd_dq_kernel<HD, BF, DUAL><<<gq, C::THREADS, C::SMEM_BYTES, s>>>(m.q128, m.k64, m.v64, m.g128, a);
+  if (a.dS) {
+    using D = DqDsCfg<HD>;
+    static bool configured_ds = false;
+    if (!configured_ds) {
+      GB_CUDA_OK(cudaFuncSetAttribute(fa_bwd_dq_ds_kernel<HD, BF>, cudaFuncAttributeMaxDynamicSharedMemorySize, D::SMEM_BYTES));
+      configured_ds = true;
+    }
+    fa_bwd_dq_ds_kernel<HD, BF><<<gq, D::THREADS, D::SMEM_BYTES, s>>>(m.ds, m.k64, a);
+  } else {
+    fa_bwd_dq_kernel<HD, BF, DUAL><<<gq, C::THREADS, C::SMEM_BYTES, s>>>(m.q128, m.k64, m.v64, m.g128, a);
+  }
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;
 }
@@ -1105,8 +1268,8 @@ long long* g_trace = nullptr;
 
 enum { DT_BF16 = 0, DT_F16 = 1 };
 
-// Timeline tracing of the dK/dV kernel: `buf` is a device buffer of 3 * 512 int64 (zeroed by
-// the caller) that CTA (0,0,0) fills with SM clock stamps; null switches tracing off.
+// Timeline tracing of the dK/dV kernel (builds with -DGB_FA_TRACE only): `buf` is a device buffer of
+// 3 * 512 int64 (zeroed by the caller) that CTA (0,0,0) fills with SM clock stamps; null switches it off.
 // head_dim 64 backward: 1 = two CTAs per SM with one S/dP buffer each, 0 = one CTA per SM
 // with two buffers and sixteen elementwise warps.
 GB_EXPORT int gb_flash_tune(int dual) {
@@ -1194,10 +1357,32 @@ GB_EXPORT int gb_flash_delta(int dtype, const void* o, const void* dout, float* 
 
 // Backward.  All tensors are [b][s][h][d] through element strides, d contiguous.
 // lse: the forward's output; delta: from gb_flash_delta.  Writes dq, dk, dv.
+// Bytes of workspace with which gb_flash_bwd_ws computes dQ from a spilled dS^T.
+GB_EXPORT long long gb_flash_bwd_ws_bytes(int B, int H, int Sq, int Sk) {
+  const long long ld = (Sq + 127) / 128 * 128, rows = (Sk + 127) / 128 * 128;
+  return (long long)B * H * rows * ld * 2;
+}
+
+GB_EXPORT int gb_flash_bwd_ws(int dtype, const void* q, const void* k, const void* v, const void* dout,
+                              const float* lse, const float* delta, void* dq, void* dk, void* dv,
+                              int B, int H, int Sq, int Sk, int D, const long long* strides,
+                              float scale, int causal, void* ws, long long ws_bytes, void* stream);
+
 GB_EXPORT int gb_flash_bwd(int dtype, const void* q, const void* k, const void* v, const void* dout,
                            const float* lse, const float* delta, void* dq, void* dk, void* dv,
                            int B, int H, int Sq, int Sk, int D, const long long* strides,
                            float scale, int causal, void* stream) {
+  return gb_flash_bwd_ws(dtype, q, k, v, dout, lse, delta, dq, dk, dv, B, H, Sq, Sk, D, strides, scale, causal,
+                         nullptr, 0, stream);
+}
+
+// The same with an optional workspace (32-byte aligned, gb_flash_bwd_ws_bytes bytes, contents
+// arbitrary).  With it the dK/dV kernel also writes dS^T and dQ is one product dS K read back
+// from it; without it (null, or too small) a second kernel recomputes the scores for dQ.
+GB_EXPORT int gb_flash_bwd_ws(int dtype, const void* q, const void* k, const void* v, const void* dout,
+                              const float* lse, const float* delta, void* dq, void* dk, void* dv,
+                              int B, int H, int Sq, int Sk, int D, const long long* strides,
+                              float scale, int causal, void* ws, long long ws_bytes, void* stream) {
   // strides: 7 triples (sb, ss, sh) for q, k, v, dout, dq, dk, dv
   if (D < 8 || D > 128 || (D & 7)) {
     gbh::set_error("gb_flash_bwd: head_dim must be a multiple of 8 up to 128 (got %d)", D);
@@ -1234,6 +1419,17 @@ GB_EXPORT int gb_flash_bwd(int dtype, const void* q, const void* k, const void* 
   if ((rc = make_qkv_map(&m.k64, k, a.in_bf16, B, H, Sk, D, strides[3], strides[4], strides[5], 64))) return rc;
   if ((rc = make_qkv_map(&m.v64, v, a.in_bf16, B, H, Sk, D, strides[6], strides[7], strides[8], 64))) return rc;
   if ((rc = make_qkv_map(&m.g64, dout, a.in_bf16, B, H, Sq, D, strides[9], strides[10], strides[11], 64))) return rc;
+  if (ws != nullptr && ws_bytes >= gb_flash_bwd_ws_bytes(B, H, Sq, Sk) && !((uintptr_t)ws & 31)) {
+    a.dS = ws;
+    a.ds_ld = (Sq + 127) / 128 * 128;
+    a.ds_rows = (Sk + 127) / 128 * 128;
+    uint64_t dims[4] = {(uint64_t)a.ds_ld, (uint64_t)a.ds_rows, (uint64_t)B * H, 1};
+    uint64_t st[3] = {(uint64_t)a.ds_ld * 2, (uint64_t)a.ds_ld * a.ds_rows * 2, (uint64_t)a.ds_ld * a.ds_rows * 2 * B * H};
+    uint32_t box[4] = {64, 64, 1, 1};
+    if ((rc = gbh::encode_tmap(&m.ds, a.in_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                               4, ws, dims, st, box, CU_TENSOR_MAP_SWIZZLE_128B)))
+      return rc;
+  }
   if (D > 64)
     return a.in_bf16 ? launch_bwd<128, true, false>(m, a, (cudaStream_t)stream)
                      : launch_bwd<128, false, false>(m, a, (cudaStream_t)stream);

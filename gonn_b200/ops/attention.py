@@ -214,6 +214,29 @@ def flash_fwd(q, k, v, causal: bool, scale: float, out=None):
     return out, lse
 
 
+# The backward keeps one workspace per device for the spilled dS^T (see gb_flash_bwd_ws): with it the
+# dK / dV kernel also writes dS and dQ is a single product read back from it, instead of a second pass
+# that recomputes the scores.  Problems whose dS^T is larger than the limit take the two-pass path.
+DS_SPILL_LIMIT_BYTES = 1 << 30
+_ds_ws = {}
+
+
+def set_ds_spill_limit(nbytes: int) -> None:
+    """Largest dS^T workspace the attention backward may use (0 turns the spill path off)."""
+    global DS_SPILL_LIMIT_BYTES
+    DS_SPILL_LIMIT_BYTES = int(nbytes)
+    _ds_ws.clear()
+
+
+def _ds_workspace(device, need: int):
+    if need <= 0 or need > DS_SPILL_LIMIT_BYTES:
+        return None
+    ws = _ds_ws.get(device)
+    if ws is None or ws.numel() < need:
+        ws = _ds_ws[device] = torch.empty(need, dtype=torch.uint8, device=device)
+    return ws
+
+
 def flash_bwd(q, k, v, out, dout, lse, causal: bool, scale: float):
     q, k, v, dout = _tma_ready(q), _tma_ready(k), _tma_ready(v), _tma_ready(dout)
     B, Sq, H, D = q.shape
@@ -236,9 +259,12 @@ def flash_bwd(q, k, v, out, dout, lse, causal: bool, scale: float):
     for t in (q, k, v, dout, dq, dk, dv):
         strides += _strides3(t)
     arr = (_l.L * 21)(*strides)
-    _l.call("gb_flash_bwd", I(_l.dtype_code(q.dtype)), _l.ptr(q), _l.ptr(k), _l.ptr(v), _l.ptr(dout),
+    need = (B * H * ((Sk + 127) // 128 * 128) * ((Sq + 127) // 128 * 128)) * 2
+    ws = _ds_workspace(q.device, need)
+    _l.call("gb_flash_bwd_ws", I(_l.dtype_code(q.dtype)), _l.ptr(q), _l.ptr(k), _l.ptr(v), _l.ptr(dout),
             _l.ptr(lse), _l.ptr(delta), _l.ptr(dq), _l.ptr(dk), _l.ptr(dv), I(B), I(H), I(Sq),
-            I(Sk), I(D), arr, _l.F(scale), I(int(causal)), _l.stream_ptr())
+            I(Sk), I(D), arr, _l.F(scale), I(int(causal)), _l.ptr(ws), L(ws.numel() if ws is not None else 0),
+            _l.stream_ptr())
     return dq, dk, dv, dqkv
 
 

@@ -2,7 +2,7 @@
 
     python -m gonn_b200.utils.profile_cases gemm 4096 4096 4096 [nt|nn|tn] [bias_gelu|bias_res|pair]
     python -m gonn_b200.utils.profile_cases flash_fwd 4 2048 16 128 [causal]
-    python -m gonn_b200.utils.profile_cases flash_bwd 4 2048 16 128 [causal]
+    python -m gonn_b200.utils.profile_cases flash_bwd 4 2048 16 128 [causal] [nospill]
     python -m gonn_b200.utils.profile_cases norm 16384 768
     python -m gonn_b200.utils.profile_cases norm_bwd 16384 768        # LayerNorm backward
     python -m gonn_b200.utils.profile_cases norm_fork 16384 768       # backward with the residual bypass fused
@@ -74,6 +74,9 @@ def main(argv):
             print(f"flash_fwd B{B} S{S} H{H} D{D} causal={causal}: {ms:.4f} ms, {fl / ms / 1e9:.1f} TFLOP/s")
         else:
             do = torch.randn_like(out)
+            if "nospill" in argv:          # dQ by a second pass instead of the dS^T workspace
+                from ..ops import attention as _att
+                _att.set_ds_spill_limit(0)
             ms = _time(lambda: flash_bwd(q, k, v, out, do, lse, causal, scale))
             print(f"flash_bwd B{B} S{S} H{H} D{D} causal={causal}: {ms:.4f} ms, {2.5 * fl / ms / 1e9:.1f} TFLOP/s "
                   "(2.5x forward FLOPs convention)")

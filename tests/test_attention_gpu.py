@@ -6,6 +6,7 @@ import math
 import pytest
 import torch
 
+from gonn_b200.ops import attention as A
 from gonn_b200.ops.attention import attention_ref, flash_attention, flash_bwd, flash_fwd
 
 pytestmark = pytest.mark.gpu
@@ -70,3 +71,31 @@ def test_deterministic(status_ok):
     assert torch.equal(o1, o2)
     for a, b in zip(g1, g2):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("B,Sq,Sk,H,D,causal", [(2, 512, 512, 3, 64, True), (1, 200, 200, 2, 128, True),
+                                                (2, 130, 300, 2, 64, False), (1, 1024, 1024, 2, 64, True),
+                                                (1, 333, 333, 1, 96, False), (2, 192, 192, 2, 64, True)])
+def test_backward_with_and_without_the_dS_workspace(B, Sq, Sk, H, D, causal, status_ok):
+    """The two ways to get dQ (one product with the spilled dS^T; a second pass that recomputes the
+    scores) give the same dK / dV bit for bit and the same dQ up to the summation order, and both
+    match fp32 attention."""
+    q = torch.randn(B, Sq, H, D, device="cuda", dtype=torch.bfloat16)
+    k, v = (torch.randn(B, Sk, H, D, device="cuda", dtype=torch.bfloat16) for _ in range(2))
+    scale = 1 / math.sqrt(D)
+    out, lse = flash_fwd(q, k, v, causal, scale)
+    do = torch.randn_like(out)
+    old = A.DS_SPILL_LIMIT_BYTES
+    try:
+        A.set_ds_spill_limit(1 << 30)
+        g_spill = flash_bwd(q, k, v, out, do, lse, causal, scale)[:3]
+        A.set_ds_spill_limit(0)
+        g_two = flash_bwd(q, k, v, out, do, lse, causal, scale)[:3]
+    finally:
+        A.set_ds_spill_limit(old)
+    assert torch.equal(g_spill[1], g_two[1]) and torch.equal(g_spill[2], g_two[2])
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    attention_ref(qf, kf, vf, causal, scale).backward(do.float())
+    for got in (g_spill[0], g_two[0]):
+        assert (got.float() - qf.grad).abs().max().item() < 0.01 * qf.grad.abs().max().item() + 0.03
+    assert (g_spill[0].float() - g_two[0].float()).abs().max().item() < 0.02 * qf.grad.abs().max().item() + 0.01
