@@ -329,10 +329,68 @@ def bench_allreduce():
     dist.destroy_process_group()
 
 
+def bench_host_time():
+    """Host time of one training step of the 12-layer LM: launched kernel by kernel (with the
+    functions that cost the most, from cProfile) and replayed as one CUDA graph.  Host time is the
+    wall-clock time of the Python call without a device synchronisation inside; the device time of
+    the same steps is printed beside it."""
+    import cProfile
+    import io
+    import pstats
+    import time
+    from ..distributed.ddp import DistributedDataParallel
+    from ..models.lm import TransformerLM
+    from ..utils.graph import GraphedStep
+    dev = torch.device("cuda", 0)
+    model = TransformerLM(32000, 768, 12, 12, 3072, 1024, dtype=torch.bfloat16, device=dev)
+    ddp = DistributedDataParallel(model, optimizer=dict(kind="adamw", lr=3e-4, weight_decay=0.1))
+    ids = torch.randint(0, 32000, (16, 1024), device=dev)
+    tgt = torch.roll(ids, -1, 1)
+
+    def step(x, y):
+        loss = model.loss(x, y)
+        loss.backward()
+        ddp.step()
+        return loss
+
+    def host_and_device(fn, n=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        host = 0.0
+        e0.record()
+        for _ in range(n):
+            t0 = time.perf_counter()
+            fn()
+            host += time.perf_counter() - t0
+        e1.record()
+        torch.cuda.synchronize()
+        return host / n * 1e3, e0.elapsed_time(e1) / n
+
+    h, d = host_and_device(lambda: step(ids, tgt))
+    _emit(bench="host_time", mode="eager", host_ms_per_step=h, device_ms_per_step=d)
+    prof = cProfile.Profile()
+    prof.enable()
+    for _ in range(3):
+        step(ids, tgt)
+    prof.disable()
+    torch.cuda.synchronize()
+    out = io.StringIO()
+    pstats.Stats(prof, stream=out).sort_stats("tottime").print_stats(14)
+    print(out.getvalue())
+    graphed = GraphedStep(step, ddp, (ids, tgt), warmup=2)
+    gx, gy = graphed.inputs
+    h, d = host_and_device(lambda: graphed(gx, gy))
+    _emit(bench="host_time", mode="cuda graph replay", host_ms_per_step=h, device_ms_per_step=d,
+          kernels_per_step=graphed.launches_per_step)
+
+
 def main(argv):
     kind = argv[0] if argv else "gemm"
     fn = {"gemm": bench_gemm, "elementwise": bench_elementwise, "flash": bench_flash, "norm": bench_norm,
-          "mlp": bench_mlp_cpu, "allreduce": bench_allreduce, "refattn": bench_reference_attention, "resident": bench_resident_mlp}.get(kind)
+          "mlp": bench_mlp_cpu, "allreduce": bench_allreduce, "refattn": bench_reference_attention, "resident": bench_resident_mlp,
+          "hosttime": bench_host_time}.get(kind)
     if fn is None:
         raise SystemExit(f"unknown benchmark {kind!r}")
     fn()
