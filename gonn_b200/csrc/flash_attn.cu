@@ -733,7 +733,7 @@ fa_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     long long* tr = ((blockIdx.x | blockIdx.y | blockIdx.z) == 0 && (e & 7) == 0 && lane == 0) ? args.trace : nullptr;
     int ntr = 0;
     // where this thread's key row starts in the dS^T spill (its half of each 64-query sub-tile)
-    // (a byte offset from args.dS; the workspace is at most 1 GiB, so 32 bits hold it)
+    // (a byte offset from args.dS; the workspace is at most 4 GiB, so 32 bits hold it)
     const uint32_t ds_off = (uint32_t)(((((long long)b * args.H + h) * args.ds_rows + kvrow) * args.ds_ld + half * 32) * 2);
     for (int it = group; it < n_it; it += C::NBUF) {
       const int st = it % C::NS;
@@ -1419,7 +1419,9 @@ GB_EXPORT int gb_flash_bwd_ws(int dtype, const void* q, const void* k, const voi
   if ((rc = make_qkv_map(&m.k64, k, a.in_bf16, B, H, Sk, D, strides[3], strides[4], strides[5], 64))) return rc;
   if ((rc = make_qkv_map(&m.v64, v, a.in_bf16, B, H, Sk, D, strides[6], strides[7], strides[8], 64))) return rc;
   if ((rc = make_qkv_map(&m.g64, dout, a.in_bf16, B, H, Sq, D, strides[9], strides[10], strides[11], 64))) return rc;
-  if (ws != nullptr && ws_bytes >= gb_flash_bwd_ws_bytes(B, H, Sq, Sk) && !((uintptr_t)ws & 31)) {
+  // (the kernel addresses the spill with 32-bit byte offsets: at most 4 GiB)
+  if (ws != nullptr && ws_bytes >= gb_flash_bwd_ws_bytes(B, H, Sq, Sk) && !((uintptr_t)ws & 31) &&
+      gb_flash_bwd_ws_bytes(B, H, Sq, Sk) <= (1LL << 32)) {
     a.dS = ws;
     a.ds_ld = (Sq + 127) / 128 * 128;
     a.ds_rows = (Sk + 127) / 128 * 128;

@@ -22,6 +22,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # embedding, reduction and normalisation kernels report an out-of-range index through the status word.
 DEBUG_BUILD = os.environ.get("GONN_B200_DEBUG", "") not in ("", "0")
 LIB_PATH = os.path.join(_HERE, "_C", "libgonn_b200_debug.so" if DEBUG_BUILD else "libgonn_b200.so")
+# GONN_B200_LIB=<path> loads another build of the library (to compare two builds in one session)
+LIB_PATH = os.environ.get("GONN_B200_LIB", LIB_PATH)
 
 DT_BF16, DT_F16, DT_F32, DT_F64, DT_I8 = 0, 1, 2, 3, 4
 _DT = {torch.bfloat16: DT_BF16, torch.float16: DT_F16, torch.float32: DT_F32,

@@ -214,26 +214,32 @@ def flash_fwd(q, k, v, causal: bool, scale: float, out=None):
     return out, lse
 
 
-# The backward keeps one workspace per device for the spilled dS^T (see gb_flash_bwd_ws): with it the
+# The backward keeps one workspace per device and stream for the spilled dS^T (see gb_flash_bwd_ws): with it the
 # dK / dV kernel also writes dS and dQ is a single product read back from it, instead of a second pass
 # that recomputes the scores.  Problems whose dS^T is larger than the limit take the two-pass path.
-DS_SPILL_LIMIT_BYTES = 1 << 30
+DS_SPILL_LIMIT_BYTES = 1 << 32          # the kernel's 32-bit offsets allow no more
 _ds_ws = {}
 
 
 def set_ds_spill_limit(nbytes: int) -> None:
     """Largest dS^T workspace the attention backward may use (0 turns the spill path off)."""
     global DS_SPILL_LIMIT_BYTES
-    DS_SPILL_LIMIT_BYTES = int(nbytes)
+    DS_SPILL_LIMIT_BYTES = min(int(nbytes), 1 << 32)
     _ds_ws.clear()
 
 
 def _ds_workspace(device, need: int):
     if need <= 0 or need > DS_SPILL_LIMIT_BYTES:
         return None
-    ws = _ds_ws.get(device)
+    if torch.cuda.is_current_stream_capturing():
+        # a captured graph keeps using the addresses it recorded: take the buffer from the graph's own
+        # pool (which the graph keeps alive and reuses from layer to layer) instead of the cached one,
+        # which a later, larger problem would replace
+        return torch.empty(need, dtype=torch.uint8, device=device)
+    key = (device, _l.current_stream_handle())     # one per stream: concurrent backward passes never share it
+    ws = _ds_ws.get(key)
     if ws is None or ws.numel() < need:
-        ws = _ds_ws[device] = torch.empty(need, dtype=torch.uint8, device=device)
+        ws = _ds_ws[key] = torch.empty(need, dtype=torch.uint8, device=device)
     return ws
 
 
