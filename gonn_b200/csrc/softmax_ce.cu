@@ -168,6 +168,80 @@ ce_fwd_vec_kernel(const T* __restrict__ x, const long long* __restrict__ tgt, co
   }
 }
 
+// Forward and gradient in one kernel, for a loss that is the root of the backward pass: the row is
+// read once from memory (the second pass over it hits the cache), the loss terms are written as in
+// ce_fwd_vec_kernel, and scale * (softmax - onehot) replaces the logits in place.  16-bit logits,
+// class count a multiple of 8, no class weights, no ignored index, no label smoothing; scale is
+// 1 / rows for the mean and 1 for the sum.  The reference computes the same two quantities as
+// separate tape nodes (nn/loss.go CrossEntropyLoss: log-softmax, gather, mean).
+template <typename T>
+__global__ void __launch_bounds__(256)
+ce_fused_vec_kernel(T* x, const long long* __restrict__ tgt, float* __restrict__ loss_row,
+                    float* __restrict__ w_row, int C, float scale, int* status) {
+  __shared__ float red[32];
+  __shared__ float s_lse;
+  const long long row = blockIdx.x;
+  uint4* xr = reinterpret_cast<uint4*>(x + row * C);
+  const int nvec = C / 8;
+  float m = -INFINITY, s = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 u = xr[v];
+    const T* e = reinterpret_cast<const T*>(&u);
+    float f[8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; j++) { f[j] = (float)e[j]; mx = fmaxf(mx, f[j]); }
+    if (mx > m) {
+      s *= __expf(m - mx);
+      m = mx;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) s += __expf(f[j] - m);
+  }
+  const float M = block_max(m, red);
+  s = block_sum(m == -INFINITY ? 0.f : s * __expf(m - M), red);
+  long long t = tgt[row];
+  const bool bad = t < 0 || t >= C;
+  if (threadIdx.x == 0) {
+    const float lse = M + logf(s);
+    s_lse = lse;
+    if (bad) set_status(status, ST_BAD_INDEX, (int)row);
+    loss_row[row] = bad ? 0.f : lse - (float)x[row * C + t];   // read before any thread overwrites the row
+    w_row[row] = bad ? 0.f : 1.f;
+  }
+  __syncthreads();
+  const float lse = s_lse;
+  const float g = bad ? 0.f : scale;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 u = xr[v];
+    const T* e = reinterpret_cast<const T*>(&u);
+    alignas(16) T o[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      float d = g * __expf((float)e[j] - lse);
+      if ((long long)v * 8 + j == t) d -= g;
+      o[j] = (T)d;
+    }
+    xr[v] = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
+// x *= g[0] unless g[0] is exactly 1 (the usual case: the loss is the root of the backward pass),
+// in which case every CTA returns after reading the scalar.
+template <typename T>
+__global__ void scale_unless_one_kernel(T* x, long long nvec, const float* __restrict__ g) {
+  const float gv = g[0];
+  if (gv == 1.f) return;
+  uint4* xv = reinterpret_cast<uint4*>(x);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    uint4 u = xv[i];
+    T* e = reinterpret_cast<T*>(&u);
+#pragma unroll
+    for (int j = 0; j < 8; j++) e[j] = (T)((float)e[j] * gv);
+    xv[i] = u;
+  }
+}
+
 // Sums loss_row and w_row (single CTA, fixed order per thread then tree) and
 // writes out[0] = total loss (mean: / denom), out[1] = denom.
 __global__ void ce_reduce_kernel(const float* __restrict__ loss_row, const float* __restrict__ w_row,
@@ -350,6 +424,43 @@ GB_EXPORT int gb_ce_fwd(int dtype, const void* logits, const long long* targets,
   }
   if (rc) return rc;
   ce_reduce_kernel<<<1, 1024, 0, s>>>(loss_row, w_row, rows, reduction == 0, out2);
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}
+
+// Loss and gradient at once (see ce_fused_vec_kernel): the logits are replaced by the gradient of the
+// reduced loss (reduction 0 = mean over rows, 1 = sum); out2 = {loss, rows}.  Needs 16-bit logits,
+// C a multiple of 8 and a 16-byte aligned buffer; returns E_BAD_ARG otherwise.
+GB_EXPORT int gb_ce_fused(int dtype, void* logits, const long long* targets, float* loss_row, float* w_row,
+                          float* out2, long long rows, int C, int reduction, void* stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (rows <= 0 || C <= 0) return gbh::E_OK;
+  if ((dtype != DT_BF16 && dtype != DT_F16) || (C & 7) || ((uintptr_t)logits & 15) || reduction > 1) {
+    gbh::set_error("gb_ce_fused: 16-bit logits, a class count that is a multiple of 8, mean or sum");
+    return gbh::E_BAD_ARG;
+  }
+  const float scale = reduction == 0 ? 1.f / (float)rows : 1.f;
+  if (dtype == DT_BF16)
+    ce_fused_vec_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, s>>>((__nv_bfloat16*)logits, targets, loss_row, w_row, C, scale, gbh::status_ptr());
+  else
+    ce_fused_vec_kernel<__half><<<(unsigned)rows, 256, 0, s>>>((__half*)logits, targets, loss_row, w_row, C, scale, gbh::status_ptr());
+  GB_CUDA_OK(cudaGetLastError());
+  ce_reduce_kernel<<<1, 1024, 0, s>>>(loss_row, w_row, rows, reduction == 0, out2);
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}
+
+// x (n 16-bit elements, n a multiple of 8, 16-byte aligned) *= g[0], skipped on the device when g[0] == 1.
+GB_EXPORT int gb_scale_unless_one(int dtype, void* x, long long n, const float* g, void* stream) {
+  if (n <= 0) return gbh::E_OK;
+  if ((dtype != DT_BF16 && dtype != DT_F16) || (n & 7) || ((uintptr_t)x & 15) || g == nullptr) {
+    gbh::set_error("gb_scale_unless_one: 16-bit data, a multiple of 8 elements, 16-byte aligned");
+    return gbh::E_BAD_ARG;
+  }
+  const long long nvec = n / 8;
+  const int grid = (int)((nvec + 255) / 256 < 148 * 8 ? (nvec + 255) / 256 : 148 * 8);
+  if (dtype == DT_BF16) scale_unless_one_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)x, nvec, g);
+  else scale_unless_one_kernel<__half><<<grid, 256, 0, (cudaStream_t)stream>>>((__half*)x, nvec, g);
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;
 }

@@ -50,7 +50,8 @@ class TransformerLM(Module):
     def loss(self, ids, targets):
         """Mean next-token cross-entropy; the logits' gradient overwrites the logits."""
         logits = self.forward(ids)
-        return cross_entropy(logits.reshape(-1, self.vocab), targets.reshape(-1), inplace_backward=True)
+        return cross_entropy(logits.reshape(-1, self.vocab), targets.reshape(-1), inplace_backward=True,
+                             consume_logits=True)
 
 
 class GPTBlock(Module):
@@ -105,4 +106,5 @@ class GPT(Module):
 
     def loss(self, ids, targets):
         logits = self.forward(ids)
-        return cross_entropy(logits.reshape(-1, self.vocab), targets.reshape(-1), inplace_backward=True)
+        return cross_entropy(logits.reshape(-1, self.vocab), targets.reshape(-1), inplace_backward=True,
+                             consume_logits=True)

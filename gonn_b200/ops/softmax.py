@@ -125,16 +125,59 @@ class _CrossEntropy(torch.autograd.Function):
         return dx, None, None, None, None, None, None
 
 
+class _CrossEntropyFused(torch.autograd.Function):
+    """Loss and gradient in one kernel: the forward leaves ``softmax - onehot`` (already divided by N
+    for the mean) in the logits' buffer, the backward multiplies it by the upstream scalar with a
+    kernel that returns at once when that scalar is 1."""
+
+    @staticmethod
+    def forward(ctx, logits, targets, reduction):
+        N, C = logits.shape
+        t = targets.to(torch.int64).contiguous()
+        dev = logits.device
+        loss_row = torch.empty(N, dtype=torch.float32, device=dev)
+        w_row = torch.empty(N, dtype=torch.float32, device=dev)
+        out2 = torch.empty(2, dtype=torch.float32, device=dev)
+        _l.call("gb_ce_fused", _l.I(_l.dtype_code(logits.dtype)), _l.ptr(logits), _l.ptr(t), _l.ptr(loss_row),
+                _l.ptr(w_row), _l.ptr(out2), _l.L(N), _l.I(C), _l.I({"mean": 0, "sum": 1}[reduction]),
+                _l.stream_ptr())
+        ctx.grad_buf = logits          # holds the gradient now
+        return out2[0]
+
+    @staticmethod
+    def backward(ctx, g):
+        dx = ctx.grad_buf
+        g = g.to(torch.float32).contiguous()
+        _l.call("gb_scale_unless_one", _l.I(_l.dtype_code(dx.dtype)), _l.ptr(dx), _l.L(dx.numel()), _l.ptr(g),
+                _l.stream_ptr())
+        return dx, None, None
+
+
+def _fused_ok(logits, weight, ignore_index, label_smoothing, reduction) -> bool:
+    return (logits.dtype in (torch.bfloat16, torch.float16) and logits.is_contiguous() and logits.shape[1] % 8 == 0
+            and logits.data_ptr() % 16 == 0 and weight is None and ignore_index is None
+            and label_smoothing == 0.0 and reduction in ("mean", "sum") and logits.requires_grad
+            and torch.is_grad_enabled())
+
+
 def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, weight: Optional[torch.Tensor] = None,
                   ignore_index: Optional[int] = None, label_smoothing: float = 0.0,
-                  reduction: str = "mean", inplace_backward: bool = False) -> torch.Tensor:
+                  reduction: str = "mean", inplace_backward: bool = False,
+                  consume_logits: bool = False) -> torch.Tensor:
     """Cross-entropy over (N, C) logits and (N,) class indices.
 
     ``inplace_backward`` lets the backward kernel write the logits' gradient over
-    the logits buffer (valid when nothing else reads the logits afterwards).
+    the logits buffer (valid when nothing else reads the logits after the backward pass).
+    ``consume_logits`` goes further: the logits are gone when this call returns, because
+    the forward kernel already writes the gradient over them (one pass over the logits
+    instead of two; for models whose loss is computed inside the model and whose logits
+    nobody else sees).  It applies to 16-bit logits with a class count that is a multiple
+    of 8, no class weights, ignored index or label smoothing; other calls ignore the flag.
     """
     if logits.dim() != 2:
         raise ValueError("cross_entropy: logits must be (N, C)")
+    if _native(logits) and consume_logits and _fused_ok(logits, weight, ignore_index, label_smoothing, reduction):
+        return _CrossEntropyFused.apply(logits, targets, reduction)
     if _native(logits):
         return _CrossEntropy.apply(logits, targets, weight, ignore_index, float(label_smoothing),
                                    reduction, bool(inplace_backward))

@@ -226,6 +226,39 @@ def test_cross_entropy_inplace_backward(status_ok):
     assert (lin.grad.double() - xr.grad).abs().max().item() < 1e-3
 
 
+@pytest.mark.parametrize("N,C", [(64, 512), (257, 32000), (5, 8), (100, 1000)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("reduction,upstream", [("mean", 1.0), ("mean", 0.25), ("sum", 1.0)])
+def test_cross_entropy_that_consumes_the_logits(N, C, dtype, reduction, upstream, status_ok):
+    """One kernel for loss and gradient: the loss matches, the gradient that reaches the producer of the
+    logits matches (also when the loss is scaled before backward), and the logits buffer holds it."""
+    x = (torch.randn(N, C, device="cuda") * 2).to(dtype)
+    t = torch.randint(0, C, (N,), device="cuda")
+    src = torch.nn.Parameter(x.clone())
+    logits = src * 1.0                                   # a non-leaf, as a model's head output is
+    loss = cross_entropy(logits, t, reduction=reduction, inplace_backward=True, consume_logits=True)
+    xr = x.double().requires_grad_(True)
+    ref = F.cross_entropy(xr, t, reduction=reduction)
+    assert abs(float(loss) - float(ref)) < 2e-3 * (1 + abs(float(ref)))
+    (loss * upstream).backward()
+    (ref * upstream).backward()
+    tol = (1e-2 if dtype == torch.bfloat16 else 2e-3) * xr.grad.abs().max().item() + 1e-6
+    assert (src.grad.double() - xr.grad).abs().max().item() < tol
+    assert torch.equal(logits.detach(), src.grad)        # written in place: no second (N, C) buffer
+
+
+def test_cross_entropy_consume_flag_is_ignored_where_it_does_not_apply(status_ok):
+    x = torch.randn(16, 50, device="cuda", dtype=torch.float32, requires_grad=True)   # fp32, C % 8 != 0
+    t = torch.randint(0, 50, (16,), device="cuda")
+    keep = x.detach().clone()
+    loss = cross_entropy(x, t, label_smoothing=0.1, consume_logits=True)
+    loss.backward()
+    assert torch.equal(x.detach(), keep)
+    xr = keep.double().requires_grad_(True)
+    F.cross_entropy(xr, t, label_smoothing=0.1).backward()
+    assert (x.grad.double() - xr.grad).abs().max().item() < 1e-5
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float64])
 def test_embedding(dtype, status_ok):
     V, D = 1000, 96
