@@ -75,7 +75,10 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 bn_partial_kernel(const T* __restrict__ a, const T* __restrict__ xin,
                                   const float* __restrict__ mean, const float* __restrict__ invstd,
-                                  float* __restrict__ part, int N, int C, long long S, int mode) {
+                                  float* __restrict__ part, int N, int C, long long S, int mode,
+                                  const T* __restrict__ yrelu) {
+  // yrelu (backward only, may be null): the forward's output after its fused ReLU; the incoming
+  // gradient counts as zero wherever that output is zero
   __shared__ float red[32];
   const int c = blockIdx.x, sp = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -83,7 +86,7 @@ bn_partial_kernel(const T* __restrict__ a, const T* __restrict__ xin,
   const int n0 = sp * per, n1 = min(n0 + per, N);
   float s0 = 0.f, s1 = 0.f;
   const float mu = mode ? mean[c] : 0.f, is = mode ? invstd[c] : 0.f;
-  const bool vec = planes_vectorisable<T>(S, a, mode ? xin : a, a);
+  const bool vec = planes_vectorisable<T>(S, a, mode ? xin : a, yrelu ? yrelu : a);
   for (int n = n0 + warp; n < n1; n += 8) {
     const long long base = ((long long)n * C + c) * S;
     if (vec) {
@@ -91,6 +94,12 @@ bn_partial_kernel(const T* __restrict__ a, const T* __restrict__ xin,
         float v[4], xv[4];
         Vec4<T>::ld(a + base + i, v);
         if (mode) Vec4<T>::ld(xin + base + i, xv);
+        if (yrelu) {
+          float yv[4];
+          Vec4<T>::ld(yrelu + base + i, yv);
+#pragma unroll
+          for (int j = 0; j < 4; j++) v[j] = yv[j] > 0.f ? v[j] : 0.f;
+        }
 #pragma unroll
         for (int j = 0; j < 4; j++) {
           s0 += v[j];
@@ -99,7 +108,8 @@ bn_partial_kernel(const T* __restrict__ a, const T* __restrict__ xin,
       }
     } else {
       for (long long i = lane; i < S; i += 32) {
-        const float v = (float)a[base + i];
+        float v = (float)a[base + i];
+        if (yrelu && !((float)yrelu[base + i] > 0.f)) v = 0.f;
         s0 += v;
         s1 += mode ? v * (((float)xin[base + i] - mu) * is) : v * v;
       }
@@ -134,7 +144,8 @@ struct BnArgs {
   int* ready;              // device flag: this launch's serial number once the stats are valid
   int* elect;              // election word: the first CTA to swap the serial number in finalises
   int ready_val;
-  int split;               // 1: the statistics were finalised by a separate launch (one rank): no flag, no wait
+  int split;               // 1: the statistics were finalised by a separate launch: no flag, no wait;
+                           // 2 (one rank): every plane derives them from the partial sums itself, no finalise at all
   int* status;
 };
 
@@ -176,6 +187,21 @@ __device__ void combine_and_exchange(const BnArgs& a, float* out2c, float* count
   }
   *count_out = count;
   __syncthreads();
+}
+
+// One rank: the two sums of channel c from its kSplits partial pairs.  Lane i takes split i and a
+// butterfly adds them, so every lane of every warp that does this for the channel gets the same bits
+// (a + b == b + a at every level).  Must be called by all 32 lanes.
+static_assert(kSplits == 32, "one partial pair per lane");
+__device__ __forceinline__ void local_sums(const BnArgs& a, int c, float& s0, float& s1) {
+  const int lane = threadIdx.x & 31;
+  s0 = __ldcg(a.part + ((long long)c * kSplits + lane) * 2);
+  s1 = __ldcg(a.part + ((long long)c * kSplits + lane) * 2 + 1);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+  }
 }
 
 // True in exactly one CTA of the launch: the first to arrive.
@@ -287,7 +313,26 @@ bn_apply_kernel(const T* __restrict__ x, T* __restrict__ y, const BnArgs a) {
   for (long long pl = (long long)blockIdx.x * 8 + warp; pl < planes; pl += (long long)gridDim.x * 8) {
     const int c = (int)(pl % C);
     float mean, is;
-    if (a.training) {
+    if (a.training && a.split == 2) {
+      // single rank: mean and 1/std straight from the partial sums; the planes of the first image
+      // publish them for the backward and update the running statistics (one writer per channel)
+      float s0, s1;
+      local_sums(a, c, s0, s1);
+      const float n = (float)a.N * (float)a.S;
+      mean = s0 / n;
+      float var = s1 / n - mean * mean;
+      var = var > 0.f ? var : 0.f;
+      is = rsqrtf(var + a.eps);
+      if (pl < C && lane == 0) {
+        a.stats[c] = mean;
+        a.stats[C + c] = is;
+        if (a.running_mean) {
+          const float unbiased = n > 1.f ? var * n / (n - 1.f) : var;
+          a.running_mean[c] = (1.f - a.momentum) * a.running_mean[c] + a.momentum * mean;
+          a.running_var[c] = (1.f - a.momentum) * a.running_var[c] + a.momentum * unbiased;
+        }
+      }
+    } else if (a.training) {
       mean = __ldcg(a.stats + c);
       is = __ldcg(a.stats + C + c);
     } else {
@@ -324,7 +369,8 @@ bn_apply_kernel(const T* __restrict__ x, T* __restrict__ y, const BnArgs a) {
 template <typename T>
 __global__ void __launch_bounds__(256)
 bn_bwd_apply_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __restrict__ dx,
-                    float* __restrict__ dgamma, float* __restrict__ dbeta, const BnArgs a) {
+                    float* __restrict__ dgamma, float* __restrict__ dbeta, const BnArgs a,
+                    const T* __restrict__ yrelu) {
   __shared__ int sm_flag;
   __shared__ float s_count;
   const int C = a.C;
@@ -342,11 +388,25 @@ bn_bwd_apply_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __rest
   const long long planes = (long long)a.N * C;
   const long long S = a.S;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool vec = planes_vectorisable<T>(S, x, dy, dx);
+  const bool vec = planes_vectorisable<T>(S, x, dy, dx) && (yrelu == nullptr || planes_vectorisable<T>(S, yrelu, dy, dx));
   for (long long pl = (long long)blockIdx.x * 8 + warp; pl < planes; pl += (long long)gridDim.x * 8) {
     const int c = (int)(pl % C);
     const float mean = a.stats[c], is = a.stats[C + c];
-    const float m1 = __ldcg(a.sums + c), m2 = __ldcg(a.sums + C + c);
+    float m1, m2;
+    if (a.split == 2) {
+      float s0, s1;
+      local_sums(a, c, s0, s1);
+      if (pl < C && lane == 0) {
+        if (dbeta) dbeta[c] = s0;
+        if (dgamma) dgamma[c] = s1;
+      }
+      const float n = (float)a.N * (float)a.S;
+      m1 = s0 / n;
+      m2 = s1 / n;
+    } else {
+      m1 = __ldcg(a.sums + c);
+      m2 = __ldcg(a.sums + C + c);
+    }
     const float k = w ? is * w[c] : is;
     const T* xp = x + pl * S;
     const T* gp = dy + pl * S;
@@ -356,17 +416,35 @@ bn_bwd_apply_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __rest
         float xv[4], g[4];
         Vec4<T>::ld(xp + i, xv);
         Vec4<T>::ld(gp + i, g);
+        if (yrelu) {
+          float yv[4];
+          Vec4<T>::ld(yrelu + pl * S + i, yv);
+#pragma unroll
+          for (int j = 0; j < 4; j++) g[j] = yv[j] > 0.f ? g[j] : 0.f;
+        }
 #pragma unroll
         for (int j = 0; j < 4; j++) g[j] = k * (g[j] - m1 - (xv[j] - mean) * is * m2);
         Vec4<T>::st(op + i, g);
       }
     } else {
-      for (long long i = lane; i < S; i += 32)
-        op[i] = (T)(k * ((float)gp[i] - m1 - ((float)xp[i] - mean) * is * m2));
+      for (long long i = lane; i < S; i += 32) {
+        float g = (float)gp[i];
+        if (yrelu && !((float)yrelu[pl * S + i] > 0.f)) g = 0.f;
+        op[i] = (T)(k * (g - m1 - ((float)xp[i] - mean) * is * m2));
+      }
     }
   }
 }
 
+
+template <typename T>
+__global__ void channel_sum_finish_kernel(const float* __restrict__ part, T* __restrict__ out, int C) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float s = 0.f;
+  for (int sp = 0; sp < kSplits; sp++) s += part[((long long)c * kSplits + sp) * 2];
+  out[c] = (T)s;
+}
 
 inline int grid_for(long long work) {
   long long g = (work + 255) / 256;
@@ -418,14 +496,14 @@ GB_EXPORT int gb_bn_fwd(int dtype, const void* x, void* y, const float* w, const
   a.ready = (int*)(work + (long long)C * kSplits * 2 + 2 * C);
   a.elect = a.ready + 1;
   a.running_mean = running_mean; a.running_var = running_var; a.w = w; a.b = b;
-  a.split = a.world == 1;
+  a.split = a.world == 1 ? 2 : 0;
   a.status = gbh::status_ptr();
   const long long total = (long long)N * C * S;
 #define GB_BN(T)                                                                                      \
   {                                                                                                   \
     if (training)                                                                                     \
-      bn_partial_kernel<T><<<dim3(C, kSplits), 256, 0, s>>>((const T*)x, nullptr, nullptr, nullptr, work, N, C, S, 0); \
-    if (training && a.split) bn_finalise_kernel<<<1, 256, 0, s>>>(a, nullptr, nullptr, 0);            \
+      bn_partial_kernel<T><<<dim3(C, kSplits), 256, 0, s>>>((const T*)x, nullptr, nullptr, nullptr, work, N, C, S, 0, nullptr); \
+    if (training && a.split == 1) bn_finalise_kernel<<<1, 256, 0, s>>>(a, nullptr, nullptr, 0);       \
     bn_apply_kernel<T><<<grid_for(total), 256, 0, s>>>((const T*)x, (T*)y, a);                        \
   }
   switch (dtype) {
@@ -441,10 +519,42 @@ GB_EXPORT int gb_bn_fwd(int dtype, const void* x, void* y, const float* w, const
   return gbh::E_OK;
 }
 
+// out[c] = sum over n and s of x[n][c][s] (a convolution's bias gradient), in the tensor's dtype.
+// work: gb_bn_workspace_floats(C) floats.  Two launches: the per-channel partial sums of the
+// BatchNorm forward, then one thread per channel adds the kSplits partials in order.
+GB_EXPORT int gb_channel_sum(int dtype, const void* x, void* out, float* work, int N, int C, long long S,
+                             void* stream) {
+  if (C > kMaxC) {
+    gbh::set_error("gb_channel_sum: at most %d channels", kMaxC);
+    return gbh::E_TOO_LARGE;
+  }
+  if (N <= 0 || C <= 0 || S <= 0) return gbh::E_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+#define GB_CS(T)                                                                                              \
+  {                                                                                                           \
+    bn_partial_kernel<T><<<dim3(C, kSplits), 256, 0, s>>>((const T*)x, nullptr, nullptr, nullptr, work, N, C, S, 0, \
+                                                          nullptr);                                           \
+    channel_sum_finish_kernel<T><<<(C + 127) / 128, 128, 0, s>>>(work, (T*)out, C);                           \
+  }
+  switch (dtype) {
+    case DT_BF16: GB_CS(__nv_bfloat16) break;
+    case DT_F16: GB_CS(__half) break;
+    case DT_F32: GB_CS(float) break;
+    default:
+      gbh::set_error("gb_channel_sum: bad dtype %d", dtype);
+      return gbh::E_BAD_ARG;
+  }
+#undef GB_CS
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}
+
 // Backward of the training forward.  dgamma / dbeta (fp32, may be null) receive the LOCAL sums.
+// yrelu (may be null): the forward's output when it had the ReLU fused in; the gradient is then
+// masked by (yrelu > 0) inside both kernels instead of by separate elementwise launches.
 GB_EXPORT int gb_bn_bwd(int dtype, const void* x, const void* dy, void* dx, const float* w,
                         const float* stats, float* dgamma, float* dbeta, float* work, int N, int C,
-                        long long S, int sync, long long slot_off, void* stream) {
+                        long long S, int sync, long long slot_off, const void* yrelu, void* stream) {
   if (C > kMaxC) {
     gbh::set_error("gb_bn_bwd: at most %d channels", kMaxC);
     return gbh::E_TOO_LARGE;
@@ -458,14 +568,14 @@ GB_EXPORT int gb_bn_bwd(int dtype, const void* x, const void* dy, void* dx, cons
   a.ready = (int*)(work + (long long)C * kSplits * 2 + 2 * C);
   a.elect = a.ready + 1;
   a.w = w;
-  a.split = a.world == 1;
+  a.split = a.world == 1 ? 2 : 0;
   a.status = gbh::status_ptr();
   const long long total = (long long)N * C * S;
 #define GB_BN(T)                                                                                      \
   {                                                                                                   \
-    bn_partial_kernel<T><<<dim3(C, kSplits), 256, 0, s>>>((const T*)dy, (const T*)x, stats, stats + C, work, N, C, S, 1); \
-    if (a.split) bn_finalise_kernel<<<1, 256, 0, s>>>(a, dgamma, dbeta, 1);                           \
-    bn_bwd_apply_kernel<T><<<grid_for(total), 256, 0, s>>>((const T*)x, (const T*)dy, (T*)dx, dgamma, dbeta, a); \
+    bn_partial_kernel<T><<<dim3(C, kSplits), 256, 0, s>>>((const T*)dy, (const T*)x, stats, stats + C, work, N, C, S, 1, (const T*)yrelu); \
+    if (a.split == 1) bn_finalise_kernel<<<1, 256, 0, s>>>(a, dgamma, dbeta, 1);                      \
+    bn_bwd_apply_kernel<T><<<grid_for(total), 256, 0, s>>>((const T*)x, (const T*)dy, (T*)dx, dgamma, dbeta, a, (const T*)yrelu); \
   }
   switch (dtype) {
     case DT_BF16: GB_BN(__nv_bfloat16) break;

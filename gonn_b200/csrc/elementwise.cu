@@ -300,6 +300,55 @@ __global__ void binary_bcast_kernel(const T* __restrict__ a, const T* __restrict
   }
 }
 
+// The commonest broadcast: one operand is contiguous over the whole output, the other repeats along
+// the leading dimensions and is contiguous over the trailing `inner` elements (a bias row, a position
+// table added to every batch entry).  16-byte accesses on both; SWAP: the repeating operand is the
+// left one (matters for sub / div).  Needs inner % V == 0 and 16-byte aligned pointers.
+template <typename T, int OP, bool SWAP>
+__global__ void binary_rowvec_kernel(const T* __restrict__ full, const T* __restrict__ row, T* __restrict__ c,
+                                     long long nvec, long long inner_vec) {
+  using CT = typename Conv<T>::CT;
+  constexpr int V = 16 / sizeof(T);
+  const Vec<T, V>* fv = reinterpret_cast<const Vec<T, V>*>(full);
+  const Vec<T, V>* rv = reinterpret_cast<const Vec<T, V>*>(row);
+  Vec<T, V>* cv = reinterpret_cast<Vec<T, V>*>(c);
+  const long long nth = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += nth) {
+    const long long j = nvec <= 0x7fffffffLL ? (long long)((unsigned)i % (unsigned)inner_vec) : i % inner_vec;
+    const Vec<T, V> x = fv[i], y = rv[j];
+    Vec<T, V> o;
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+      const CT xa = Conv<T>::ld(x.v[k]), yb = Conv<T>::ld(y.v[k]);
+      o.v[k] = Conv<T>::st(SWAP ? bin<CT>(OP, yb, xa) : bin<CT>(OP, xa, yb));
+    }
+    cv[i] = o;
+  }
+}
+
+// Is operand `s` (strides) contiguous over the whole shape?  And does operand `s` repeat (stride 0)
+// over dims [0, j) and run contiguously over dims [j, rank)?  Returns that j, or -1.
+inline bool bcast_full(const BcastDims& d, const long long* s) {
+  long long want = 1;
+  for (int k = d.rank - 1; k >= 0; k--) {
+    if (d.shape[k] != 1 && s[k] != want) return false;
+    want *= d.shape[k];
+  }
+  return true;
+}
+inline int bcast_row_split(const BcastDims& d, const long long* s) {
+  long long want = 1;
+  int k = d.rank - 1;
+  for (; k >= 0; k--) {
+    if (d.shape[k] == 1) { continue; }
+    if (s[k] != want) break;
+    want *= d.shape[k];
+  }
+  for (int q = k; q >= 0; q--)
+    if (d.shape[q] != 1 && s[q] != 0) return -1;
+  return k + 1;
+}
+
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ x, TO* __restrict__ y, long long n) {
   const long long nth = (long long)gridDim.x * blockDim.x;
@@ -347,11 +396,30 @@ template <typename T>
 int launch_binary(int op, const void* a, const void* b, void* c, long long n, const BcastDims* d,
                   cudaStream_t s) {
   constexpr int V = 16 / sizeof(T);
+  // row-vector broadcast (see binary_rowvec_kernel): 1 = b repeats, 2 = a repeats
+  int rv_mode = 0;
+  long long rv_inner = 0;
+  if (d != nullptr && ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) == 0)) {
+    for (int side = 1; side <= 2 && rv_mode == 0; side++) {
+      const long long* sf = side == 1 ? d->sa : d->sb;
+      const long long* sr = side == 1 ? d->sb : d->sa;
+      if (!bcast_full(*d, sf)) continue;
+      const int j = bcast_row_split(*d, sr);
+      if (j <= 0) continue;                       // -1: no such split; 0: nothing repeats
+      long long inner = 1;
+      for (int k = j; k < d->rank; k++) inner *= d->shape[k];
+      if (inner % V == 0 && n % V == 0 && inner >= V) { rv_mode = side; rv_inner = inner; }
+    }
+  }
 #define GB_B(OPID)                                                                                 \
   case OPID:                                                                                       \
     if (d == nullptr) {                                                                            \
       int vec_ok = (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) == 0;                       \
       binary_same_kernel<T, OPID><<<grid_for((n + V - 1) / V, 256), 256, 0, s>>>((const T*)a, (const T*)b, (T*)c, n, vec_ok); \
+    } else if (rv_mode == 1) {                                                                     \
+      binary_rowvec_kernel<T, OPID, false><<<grid_for(n / V, 256), 256, 0, s>>>((const T*)a, (const T*)b, (T*)c, n / V, rv_inner / V); \
+    } else if (rv_mode == 2) {                                                                     \
+      binary_rowvec_kernel<T, OPID, true><<<grid_for(n / V, 256), 256, 0, s>>>((const T*)b, (const T*)a, (T*)c, n / V, rv_inner / V); \
     } else {                                                                                       \
       binary_bcast_kernel<T, OPID><<<grid_for(n, 256), 256, 0, s>>>((const T*)a, (const T*)b, (T*)c, n, *d); \
     }                                                                                              \

@@ -202,21 +202,40 @@ __global__ void col_finish_kernel(const CT* __restrict__ part, TO* __restrict__ 
   }
 }
 
+// Arg-max / arg-min over the rows of (outer, R, inner): CTA = 32 columns x 32 row lanes; a thread
+// scans rows ty, ty + 32, ... of its column (consecutive threads read consecutive columns), then the
+// 32 candidates of a column are combined in row-lane order.  Ties keep the smallest row index, the
+// first occurrence, as a serial scan would.
 template <typename T, int OP>
-__global__ void col_arg_kernel(const T* __restrict__ x, long long* __restrict__ y, long long R,
-                               long long inner, long long total) {
+__global__ void __launch_bounds__(1024)
+col_arg_kernel(const T* __restrict__ x, long long* __restrict__ y, long long R, long long inner) {
   using CT = typename Acc<T>::CT;
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= total) return;
-  const long long o = i / inner, col = i % inner;
-  const T* xp = x + o * R * inner + col;
-  CT best = (CT)xp[0];
-  long long bi = 0;
-  for (long long r = 1; r < R; r++) {
-    CT v = (CT)xp[r * inner];
-    if (OP == R_ARGMAX ? v > best : v < best) { best = v; bi = r; }
+  __shared__ CT sv[32][33];
+  __shared__ long long si[32][33];
+  const long long col = (long long)blockIdx.x * 32 + threadIdx.x;
+  const long long o = blockIdx.y;
+  CT best = 0;
+  long long bi = -1;
+  if (col < inner) {
+    const T* xp = x + o * R * inner + col;
+    for (long long r = threadIdx.y; r < R; r += 32) {
+      const CT v = (CT)xp[r * inner];
+      if (bi < 0 || (OP == R_ARGMAX ? v > best : v < best)) { best = v; bi = r; }
+    }
   }
-  y[i] = bi;
+  sv[threadIdx.y][threadIdx.x] = best;
+  si[threadIdx.y][threadIdx.x] = bi;
+  __syncthreads();
+  if (threadIdx.y == 0 && col < inner) {
+    for (int k = 1; k < 32; k++) {
+      const CT v = sv[k][threadIdx.x];
+      const long long r = si[k][threadIdx.x];
+      if (r < 0) continue;
+      const bool better = OP == R_ARGMAX ? v > best : v < best;
+      if (bi < 0 || better || (v == best && r < bi)) { best = v; bi = r; }
+    }
+    y[o * inner + col] = bi < 0 ? 0 : bi;
+  }
 }
 
 template <typename T, typename TO, int OP>
@@ -239,9 +258,13 @@ int reduce_t(int op, const void* x, void* y, void* scratch, long long scratch_by
       if (op == R_ARGMAX) row_arg_kernel<T, R_ARGMAX><<<(unsigned)outer, blk, 0, s>>>((const T*)x, (long long*)y, R);
       else row_arg_kernel<T, R_ARGMIN><<<(unsigned)outer, blk, 0, s>>>((const T*)x, (long long*)y, R);
     } else {
-      long long total = outer * inner;
-      if (op == R_ARGMAX) col_arg_kernel<T, R_ARGMAX><<<(unsigned)((total + 127) / 128), 128, 0, s>>>((const T*)x, (long long*)y, R, inner, total);
-      else col_arg_kernel<T, R_ARGMIN><<<(unsigned)((total + 127) / 128), 128, 0, s>>>((const T*)x, (long long*)y, R, inner, total);
+      if (outer > 65535) {
+        gbh::set_error("reduce: arg-max over an inner axis supports at most 65535 outer slices");
+        return gbh::E_TOO_LARGE;
+      }
+      const dim3 grid((unsigned)((inner + 31) / 32), (unsigned)outer), blk(32, 32);
+      if (op == R_ARGMAX) col_arg_kernel<T, R_ARGMAX><<<grid, blk, 0, s>>>((const T*)x, (long long*)y, R, inner);
+      else col_arg_kernel<T, R_ARGMIN><<<grid, blk, 0, s>>>((const T*)x, (long long*)y, R, inner);
     }
     GB_CUDA_OK(cudaGetLastError());
     return gbh::E_OK;

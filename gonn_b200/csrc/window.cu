@@ -128,6 +128,90 @@ __global__ void pool_fwd_kernel(const T* __restrict__ x, const int* __restrict__
   }
 }
 
+// Max / average pooling with at most 8 taps per window (2 x 2, 2 x 2 x 2, ...): a thread keeps the
+// tap offsets of its windows in registers and walks the planes of its blockIdx.y slice, so the index
+// map is read once per thread instead of once per output.
+template <typename T>
+__global__ void pool_fwd_small_kernel(const T* __restrict__ x, const int* __restrict__ idx, T* __restrict__ y,
+                                      int* __restrict__ arg, long long B, long long S, int nwin, int T_, int mode,
+                                      int count_include_pad) {
+  for (int win = blockIdx.x * blockDim.x + threadIdx.x; win < nwin; win += gridDim.x * blockDim.x) {
+    int src[8];
+    int cnt = 0;
+#pragma unroll
+    for (int t = 0; t < 8; t++) {
+      src[t] = t < T_ ? __ldg(idx + (long long)win * T_ + t) : -1;
+      if (src[t] >= 0 && !GB_IN_BOUNDS(src[t], S, 108)) src[t] = -1;
+      cnt += src[t] >= 0;
+    }
+    const float inv = 1.f / (float)(count_include_pad ? T_ : (cnt > 0 ? cnt : 1));
+    for (long long b = blockIdx.y; b < B; b += gridDim.y) {
+      const T* xb = x + b * S;
+      float v[8];
+#pragma unroll
+      for (int t = 0; t < 8; t++) v[t] = src[t] >= 0 ? (float)xb[src[t]] : 0.f;
+      if (mode == POOL_MAX) {
+        float best = 0.f;
+        int bt = -1;
+#pragma unroll
+        for (int t = 0; t < 8; t++)
+          if (src[t] >= 0 && (v[t] > best || bt < 0)) { best = v[t]; bt = t; }
+        y[b * nwin + win] = (T)best;
+        if (arg) arg[b * nwin + win] = bt;
+      } else {
+        float sum = 0.f;
+#pragma unroll
+        for (int t = 0; t < 8; t++) sum += v[t];
+        y[b * nwin + win] = (T)(sum * inv);
+      }
+    }
+  }
+}
+
+// Max / average pooling over wide windows (global pooling: one window of H * W taps): one warp per
+// output, lanes along the taps, then a shuffle reduction.  The arg-max is the first tap that holds the
+// maximum, as in the one-thread-per-output kernel.
+template <typename T>
+__global__ void pool_fwd_wide_kernel(const T* __restrict__ x, const int* __restrict__ idx, T* __restrict__ y,
+                                     int* __restrict__ arg, long long B, long long S, int nwin, int T_, int mode,
+                                     int count_include_pad) {
+  const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+  const long long total = B * nwin;
+  for (long long o = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); o < total; o += (long long)gridDim.x * wpb) {
+    const long long b = o / nwin;
+    const int win = (int)(o - b * nwin);
+    const T* xb = x + b * S;
+    const int* iw = idx + (long long)win * T_;
+    float best = -INFINITY, sum = 0.f;
+    int bt = 0x7fffffff, cnt = 0;
+    for (int t = lane; t < T_; t += 32) {
+      const int src = __ldg(iw + t);
+      if (src < 0 || !GB_IN_BOUNDS(src, S, 109)) continue;
+      const float v = (float)xb[src];
+      sum += v;
+      cnt++;
+      if (v > best || bt == 0x7fffffff) { best = v; bt = t; }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+      const int ot = __shfl_xor_sync(0xffffffffu, bt, off);
+      sum += __shfl_xor_sync(0xffffffffu, sum, off);
+      cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
+      // a lane that saw no tap holds (-inf, INT_MAX) and always loses; equal values keep the earlier tap
+      if (ot != 0x7fffffff && (bt == 0x7fffffff || ov > best || (ov == best && ot < bt))) { best = ov; bt = ot; }
+    }
+    if (lane == 0) {
+      if (mode == POOL_MAX) {
+        y[o] = (T)(bt == 0x7fffffff ? 0.f : best);
+        if (arg) arg[o] = bt == 0x7fffffff ? -1 : bt;
+      } else {
+        y[o] = (T)(sum / (float)(count_include_pad ? T_ : (cnt > 0 ? cnt : 1)));
+      }
+    }
+  }
+}
+
 // dx[b][i] = sum over (win,tap) covering i of the window's gradient share
 template <typename T>
 __global__ void pool_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
@@ -178,19 +262,37 @@ __global__ void pool_bwd_disjoint_kernel(const T* __restrict__ dy, const int* __
                                          const int2* __restrict__ p2w, const int* __restrict__ wcnt,
                                          T* __restrict__ dx, long long B, int S, int nwin, int T_, int mode,
                                          int count_include_pad) {
-  for (long long b = blockIdx.y; b < B; b += gridDim.y) {
-    const T* dyb = dy + b * nwin;
-    const int* ab = arg ? arg + b * nwin : nullptr;
-    T* dxb = dx + b * S;
-    for (int pos = blockIdx.x * blockDim.x + threadIdx.x; pos < S; pos += gridDim.x * blockDim.x) {
-      const int2 w = __ldg(p2w + pos);
-      float v = 0.f;
-      if (w.x >= 0 && GB_IN_BOUNDS(w.x, nwin, 107)) {
-        const float g = (float)dyb[w.x];
-        if (mode == POOL_MAX) v = (ab[w.x] == w.y) ? g : 0.f;
-        else v = g / (float)(count_include_pad ? T_ : max(__ldg(wcnt + w.x), 1));
+  // A thread keeps its positions' table entries in registers and walks the planes (b) of its
+  // blockIdx.y slice, four at a time so that their loads are in flight together.
+  for (int pos = blockIdx.x * blockDim.x + threadIdx.x; pos < S; pos += gridDim.x * blockDim.x) {
+    const int2 w = __ldg(p2w + pos);
+    const bool hit = w.x >= 0 && GB_IN_BOUNDS(w.x, nwin, 107);
+    float inv = 1.f;
+    if (hit && mode != POOL_MAX) inv = 1.f / (float)(count_include_pad ? T_ : max(__ldg(wcnt + w.x), 1));
+    long long b = blockIdx.y;
+    const long long step = gridDim.y;
+    for (; b + 3 * step < B; b += 4 * step) {
+      float g[4];
+      int a4[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const long long bb = b + u * step;
+        g[u] = hit ? (float)dy[bb * nwin + w.x] : 0.f;
+        a4[u] = (hit && mode == POOL_MAX) ? arg[bb * nwin + w.x] : w.y;
       }
-      dxb[pos] = (T)v;
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const float v = mode == POOL_MAX ? (a4[u] == w.y ? g[u] : 0.f) : g[u] * inv;
+        dx[(b + u * step) * S + pos] = (T)(hit ? v : 0.f);
+      }
+    }
+    for (; b < B; b += step) {
+      float v = 0.f;
+      if (hit) {
+        const float g = (float)dy[b * nwin + w.x];
+        v = mode == POOL_MAX ? (arg[b * nwin + w.x] == w.y ? g : 0.f) : g * inv;
+      }
+      dx[b * S + pos] = (T)v;
     }
   }
 }
@@ -249,6 +351,21 @@ GB_EXPORT int gb_pool_fwd(int dtype, const void* x, const int* idx, void* y, int
   if (total <= 0) return gbh::E_OK;
   cudaStream_t s = (cudaStream_t)stream;
   GB_BOUNDS_BIND();
+  if (mode != POOL_LP && T_ <= 8 && B >= 64) {
+    const int bx = (nwin + 255) / 256 < 64 ? (nwin + 255) / 256 : 64;
+    long long by = (148 * 8 + bx - 1) / bx;
+    if (by > B) by = B;
+    GB_DISPATCH_T((pool_fwd_small_kernel<T><<<dim3(bx, (unsigned)by), 256, 0, s>>>((const T*)x, idx, (T*)y, arg, B, S, nwin, T_, mode, count_include_pad)));
+    GB_CUDA_OK(cudaGetLastError());
+    return gbh::E_OK;
+  }
+  if (mode != POOL_LP && T_ >= 64) {
+    const long long warps = total;
+    const int grid = (int)((warps + 7) / 8 < 148 * 8 ? (warps + 7) / 8 : 148 * 8);
+    GB_DISPATCH_T((pool_fwd_wide_kernel<T><<<grid, 256, 0, s>>>((const T*)x, idx, (T*)y, arg, B, S, nwin, T_, mode, count_include_pad)));
+    GB_CUDA_OK(cudaGetLastError());
+    return gbh::E_OK;
+  }
   GB_DISPATCH_T((pool_fwd_kernel<T><<<grid_for(total), 256, 0, s>>>((const T*)x, idx, (T*)y, arg, B, S, nwin, T_, mode, count_include_pad, p)));
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;
@@ -266,8 +383,11 @@ GB_EXPORT int gb_pool_bwd_disjoint(int dtype, const void* dy, const int* arg, co
   cudaStream_t s = (cudaStream_t)stream;
   GB_BOUNDS_BIND();
   const int bx = (int)((S + 255) / 256 < 64 ? (S + 255) / 256 : 64);
-  const int by = (int)(B < 65535 ? B : 65535);
-  GB_DISPATCH_T((pool_bwd_disjoint_kernel<T><<<dim3(bx, by), 256, 0, s>>>((const T*)dy, arg, (const int2*)p2w, wcnt, (T*)dx, B, (int)S, nwin, T_, mode, count_include_pad)));
+  // about eight CTAs per SM in total; every CTA walks B / by planes
+  long long by = (148 * 8 + bx - 1) / bx;
+  if (by > B) by = B;
+  if (by < 1) by = 1;
+  GB_DISPATCH_T((pool_bwd_disjoint_kernel<T><<<dim3(bx, (unsigned)by), 256, 0, s>>>((const T*)dy, arg, (const int2*)p2w, wcnt, (T*)dx, B, (int)S, nwin, T_, mode, count_include_pad)));
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;
 }

@@ -36,7 +36,7 @@ kernel_count = 0  # kernels those calls launched (read by bench.py)
 
 # kernels launched per entry point when it is not exactly one
 KERNELS_PER_CALL = {
-    "gb_norm_bwd": 2, "gb_ce_fwd": 2, "gb_ce_fused": 2, "gb_flash_bwd": 2, "gb_flash_bwd_ws": 2, "gb_embedding_bwd": 5,
+    "gb_norm_bwd": 2, "gb_channel_sum": 2, "gb_ce_fwd": 2, "gb_ce_fused": 2, "gb_flash_bwd": 2, "gb_flash_bwd_ws": 2, "gb_embedding_bwd": 5,
     "gb_status_read": 0, "gb_comm_alloc": 0, "gb_comm_open": 0, "gb_comm_emulate": 0,
     "gb_comm_free": 0, "gb_reduce": 1, "gb_gemm_f32x3": 5, "gb_conv_wgrad": 2, "gb_set_words": 1, "gb_norm_bwd_res": 2,
 }

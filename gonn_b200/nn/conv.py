@@ -146,8 +146,15 @@ class _ConvImplicit(torch.autograd.Function):
             else:
                 dw = out.view(w.shape)
         if ctx.bias_ref is not None and ctx.needs_input_grad[2]:
-            per_image = reduce_axis(dyc, 2, "sum", out_dtype=torch.float32)          # (N, Co)
-            db = emit_grad(ctx.bias_ref, reduce_axis(per_image, 0, "sum").to(dyc.dtype))
+            if Co <= 2048:          # the per-channel partial-sum kernel of BatchNorm, then one add per channel
+                from ..ops.batchnorm import lib_ws
+                dbt = torch.empty(Co, dtype=dyc.dtype, device=dyc.device)
+                _l.call("gb_channel_sum", _l.I(dt), _l.ptr(dyc), _l.ptr(dbt), _l.ptr(lib_ws(Co, dyc.device)), _l.I(N),
+                        _l.I(Co), _l.L(L), _l.stream_ptr())
+            else:
+                per_image = reduce_axis(dyc, 2, "sum", out_dtype=torch.float32)          # (N, Co)
+                dbt = reduce_axis(per_image, 0, "sum").to(dyc.dtype)
+            db = emit_grad(ctx.bias_ref, dbt)
         return dx, dw, db, None, None, None
 
 

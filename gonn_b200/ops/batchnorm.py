@@ -42,8 +42,6 @@ class _BatchNormTrain(torch.autograd.Function):
         xc, w32, stats, y = ctx.saved_tensors
         N, C, S, relu, sync, wdt, has_b = ctx.meta
         dyc = dy.contiguous()
-        if relu:
-            dyc = dyc * (y > 0).to(dyc.dtype)
         dx = torch.empty_like(xc)
         dg = torch.empty(C, dtype=torch.float32, device=xc.device)
         db = torch.empty(C, dtype=torch.float32, device=xc.device)
@@ -51,7 +49,7 @@ class _BatchNormTrain(torch.autograd.Function):
         slot = sync.slot_offset if sync is not None else 0
         _l.call("gb_bn_bwd", _l.I(_l.dtype_code(xc.dtype)), _l.ptr(xc), _l.ptr(dyc), _l.ptr(dx), _l.ptr(w32),
                 _l.ptr(stats), _l.ptr(dg), _l.ptr(db), _l.ptr(wf), _l.I(N), _l.I(C), _l.L(S),
-                _l.I(int(sync is not None)), _l.L(slot), _l.stream_ptr())
+                _l.I(int(sync is not None)), _l.L(slot), _l.ptr(y if relu else None), _l.stream_ptr())
         return (dx, dg.to(wdt) if wdt is not None else None, db.to(wdt) if has_b else None,
                 None, None, None, None, None, None)
 

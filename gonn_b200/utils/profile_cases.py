@@ -9,6 +9,7 @@
     python -m gonn_b200.utils.profile_cases step 50000000
     python -m gonn_b200.utils.profile_cases conv 256 64 128 15 15     # N C_in C_out H W, 3x3: forward + backward
     python -m gonn_b200.utils.profile_cases suite                      # one launch or two of every other kernel family
+    python -m gonn_b200.utils.profile_cases suite2                     # ... and of the families `suite` leaves out
 
 Each case allocates a few hundred MB at most, runs three warm-up launches and
 then five timed launches (CUDA events), and prints one line with the time and the
@@ -192,6 +193,49 @@ def main(argv):
             general_attention(q, kk, vv, True, None, mask, None, 0.1, 7).sum().backward()
             torch.cuda.synchronize()
         print("suite done")
+    elif kind == "suite2":
+        # The kernel families that neither the training steps nor `suite` launch: recurrent gates, dropout,
+        # casts, scans, transposes, standalone softmax, fake quantisation, row / column reductions with
+        # arg-max, broadcasting binary ops, the gather / scatter convolution path, overlapping pooling,
+        # the consuming cross-entropy and the attention backward with its dS^T product.
+        from .. import nn, quant
+        from ..ops import elementwise as ew
+        from ..ops.dropout import dropout
+        from ..ops.reduce import reduce_axis
+        from ..ops.shape import cumsum, transpose_last2
+        from ..ops.softmax import cross_entropy, log_softmax, softmax
+        bf = torch.bfloat16
+        for rep in range(2):
+            seq = torch.randn(64, 32, 512, device=dev, dtype=bf, requires_grad=True)
+            for cell in (nn.LSTM(512, 512, dtype=bf, device=dev), nn.GRU(512, 512, dtype=bf, device=dev)):
+                cell(seq).sum().backward()
+            a = torch.randn(1 << 26, device=dev, dtype=bf, requires_grad=True)
+            dropout(a, 0.1).sum().backward()
+            ew.cast(a.detach(), torch.float32)
+            ew.binary_forward("mul", a.detach().view(8192, 8192), torch.randn(8192, device=dev, dtype=bf))
+            del a
+            m = torch.randn(8192, 8192, device=dev, dtype=bf, requires_grad=True)
+            transpose_last2(m.detach())
+            cumsum(m.detach().float(), -1)
+            softmax(m, -1).sum().backward()
+            log_softmax(m.detach(), -1)
+            reduce_axis(m.detach(), 1, "sum"); reduce_axis(m.detach(), 1, "argmax"); reduce_axis(m.detach(), 0, "argmax")
+            reduce_axis(m.detach().float(), 0, "max")
+            fq = quant.FakeQuant()
+            fq(m.float()).sum().backward()
+            del m
+            img = torch.randn(64, 32, 64, 64, device=dev, dtype=bf, requires_grad=True)
+            conv = nn.Conv2d(32, 64, 3, padding=1, dilation=2, groups=2, dtype=bf, device=dev)   # gather + GEMM path
+            nn.MaxPool2d(3, 2, 1)(conv(img)).sum().backward()                                     # overlapping windows
+            lg = torch.randn(8192, 32000, device=dev, dtype=bf, requires_grad=True)
+            cross_entropy(lg * 1, torch.randint(0, 32000, (8192,), device=dev), inplace_backward=True,
+                          consume_logits=True).backward()
+            del lg
+            q, k, v = (torch.randn(16, 1024, 12, 64, device=dev, dtype=bf) for _ in range(3))
+            o, lse = flash_fwd(q, k, v, True, 0.125)
+            flash_bwd(q, k, v, o, torch.randn_like(o), lse, True, 0.125)
+            torch.cuda.synchronize()
+        print("suite2 done")
     elif kind == "step":
         n = int(argv[1]) // 8 * 8
         from ..distributed.nvlink import SymmetricMemory

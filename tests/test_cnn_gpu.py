@@ -146,6 +146,36 @@ def test_batchnorm_train_eval(dtype, status_ok):
     assert (bn(x).double() - tb(xr)).abs().max().item() < tol
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(8, 6, 7, 5), (16, 64, 30, 30), (4, 3, 9, 9)])
+def test_batchnorm_with_fused_relu(dtype, shape, status_ok):
+    """BatchNorm with the ReLU inside its kernels: the backward masks the incoming gradient where the
+    output is zero inside the reduction and apply kernels (no separate elementwise launches)."""
+    C = shape[1]
+    x = (torch.randn(*shape, device="cuda") * 2 + 0.3).to(dtype).requires_grad_(True)
+    bn = BatchNorm2d(C, fused_relu=True, dtype=dtype, device="cuda")
+    with torch.no_grad():
+        bn.weight.copy_(torch.rand(C) + 0.5)
+        bn.bias.copy_(torch.randn(C) * 0.5)
+    tb = torch.nn.BatchNorm2d(C).cuda().double()
+    tb.weight.data.copy_(bn.weight.data.double())
+    tb.bias.data.copy_(bn.bias.data.double())
+    xr = x.detach().double().requires_grad_(True)
+    y, yr = bn(x), torch.relu(tb(xr))
+    tol = 4e-2 if dtype == torch.bfloat16 else 1e-4
+    assert (y.double() - yr).abs().max().item() < tol
+    g = torch.randn_like(yr)
+    # an element that rounds to zero in 16 bits is inactive for the kernel but active for the fp64 reference:
+    # no upstream gradient where the two disagree, so that the comparison is about the masking itself
+    g = g * ((y.detach() > 0) == (yr.detach() > 0)).double()
+    y.backward(g.to(dtype))
+    yr.backward(g)
+    n = x.numel() / C
+    assert (x.grad.double() - xr.grad).abs().max().item() < tol * 2
+    assert (bn.weight.grad.double() - tb.weight.grad).abs().max().item() < tol * 4 * n ** 0.5
+    assert (bn.bias.grad.double() - tb.bias.grad).abs().max().item() < tol * 4 * n ** 0.5
+
+
 def test_cnn_trains(status_ok):
     from gonn_b200.distributed.ddp import DistributedDataParallel
     from gonn_b200.models.cnn import SmallCNN

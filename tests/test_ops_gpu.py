@@ -66,6 +66,38 @@ def test_binary_broadcast_and_grad(name, dtype, status_ok):
     assert (b.grad.double() - bd.grad).abs().max().item() < 20 * tol * (1 + bd.grad.abs().max().item())
 
 
+@pytest.mark.parametrize("name", ["add", "sub", "mul", "div"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float64])
+@pytest.mark.parametrize("shapes", [((37, 64), (64,)), ((3, 5, 48), (1, 5, 48)), ((64,), (9, 64)), ((1, 7, 16), (4, 7, 16)),
+                                    ((6, 40), (40,)), ((2, 3, 4, 8), (4, 8)), ((5, 12), (12,))])
+def test_binary_row_vector_broadcast(name, dtype, shapes, status_ok):
+    """One operand covers the whole output, the other repeats along the leading dimensions: the vectorised
+    kernel when the repeating block is a whole number of 16-byte vectors (either side; the order matters for
+    sub / div), the general kernel otherwise — same results."""
+    sa, sb = shapes
+    a = torch.randn(*sa, device="cuda").to(dtype)
+    b = (torch.randn(*sb, device="cuda").abs() + 0.5).to(dtype)
+    y = ew.binary_forward(name, a, b)
+    ref = getattr(torch, name)(a.double(), b.double())
+    tol = {torch.float64: 1e-12, torch.float32: 1e-5, torch.bfloat16: 5e-2}[dtype]
+    assert y.shape == ref.shape
+    assert (y.double() - ref).abs().max().item() < tol * (1 + ref.abs().max().item())
+
+
+@pytest.mark.parametrize("op", ["argmax", "argmin"])
+@pytest.mark.parametrize("shape,axis", [((1000, 70), 0), ((3, 257, 33), 1), ((64, 5), 0), ((2, 4096, 8), 1)])
+def test_arg_reduction_over_an_inner_axis(op, shape, axis, status_ok):
+    from gonn_b200.ops.reduce import reduce_axis
+    x = torch.randn(*shape, device="cuda").to(torch.bfloat16)       # 16-bit values: ties are common
+    got = reduce_axis(x, axis, op)
+    # the first occurrence wins, as in a serial scan
+    xf = x.float()
+    ext = xf.max(axis, keepdim=True).values if op == "argmax" else xf.min(axis, keepdim=True).values
+    idx = torch.arange(shape[axis], device="cuda").view([-1 if i == axis else 1 for i in range(len(shape))])
+    want = torch.where(xf == ext, idx, shape[axis]).min(axis).values
+    assert torch.equal(got.long(), want)
+
+
 @pytest.mark.parametrize("D", [64, 768, 1000, 2048, 4096, 50])
 @pytest.mark.parametrize("dtype,wdtype", [(torch.bfloat16, torch.bfloat16), (torch.float32, torch.float32),
                                           (torch.bfloat16, torch.float32)])
