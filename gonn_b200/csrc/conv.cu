@@ -336,8 +336,69 @@ __global__ void conv_wgrad_finish_kernel(const float* __restrict__ part, uint16_
                                          int splits, int bf16, int beta) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     float s = beta ? raw16_to_float(dW[i], bf16) : 0.f;
+#pragma unroll 8
     for (int sp = 0; sp < splits; sp++) s += part[(long long)sp * n + i];
     dW[i] = bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(s)) : __half_as_ushort(__float2half_rn(s));
+  }
+}
+
+// Forward convolution with a short contraction (C * T <= 32: the first layer of an image network,
+// 3 channels x 3 x 3).  A tensor-core tile would spend its time on set-up: the implicit-GEMM kernel needs
+// about 15 us per CTA whatever the contraction length.  Here a thread owns one output position of one
+// image: it gathers its K inputs into registers once and then produces every output channel, four at a
+// time, with packed fp32 FMAs against weights that sit in shared memory as [k][channel] (one 16-byte
+// broadcast load feeds two FMA pairs).  Stores are coalesced along the positions.
+constexpr int kDirectK = 32;
+template <int KMAX>
+__global__ void __launch_bounds__(256)
+conv_direct_small_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, const int* __restrict__ idx,
+                         const uint16_t* __restrict__ bias, uint16_t* __restrict__ y, int C, int S, int L, int T,
+                         int M, int bf16) {
+  extern __shared__ __align__(16) float sw[];          // [KMAX][M] weights, then [M] bias
+  float* sbias = sw + KMAX * M;
+  const int K = C * T;
+  for (int i = threadIdx.x; i < KMAX * M; i += blockDim.x) {
+    const int k = i / M, m = i - k * M;
+    sw[i] = k < K ? raw16_to_float(__ldg(w + (long long)m * K + k), bf16) : 0.f;
+  }
+  for (int m = threadIdx.x; m < M; m += blockDim.x) sbias[m] = bias ? raw16_to_float(__ldg(bias + m), bf16) : 0.f;
+  __syncthreads();
+  const int n = blockIdx.y;
+  const int l = blockIdx.x * blockDim.x + threadIdx.x;
+  if (l >= L) return;
+  const uint16_t* xn = x + (long long)n * C * S;
+  float v[KMAX];
+  {
+    int c = 0, tap = 0;
+#pragma unroll
+    for (int k = 0; k < KMAX; k++) {
+      float f = 0.f;
+      if (k < K) {
+        const int src = __ldg(idx + (long long)l * T + tap);
+        if (src >= 0) f = raw16_to_float(__ldg(xn + (long long)c * S + src), bf16);
+        if (++tap == T) { tap = 0; c++; }
+      }
+      v[k] = f;
+    }
+  }
+  uint16_t* yn = y + (long long)n * M * L + l;
+  const float4* sw4 = reinterpret_cast<const float4*>(sw);
+  const int M4 = M >> 2;
+  for (int m4 = 0; m4 < M4; m4++) {
+    float2 a0 = make_float2(sbias[4 * m4], sbias[4 * m4 + 1]);
+    float2 a1 = make_float2(sbias[4 * m4 + 2], sbias[4 * m4 + 3]);
+#pragma unroll
+    for (int k = 0; k < KMAX; k++) {
+      const float4 wv = sw4[k * M4 + m4];
+      const float2 vv = make_float2(v[k], v[k]);
+      a0 = __ffma2_rn(make_float2(wv.x, wv.y), vv, a0);
+      a1 = __ffma2_rn(make_float2(wv.z, wv.w), vv, a1);
+    }
+    const float o[4] = {a0.x, a0.y, a1.x, a1.y};
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+      yn[(long long)(4 * m4 + j) * L] = bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(o[j]))
+                                             : __half_as_ushort(__float2half_rn(o[j]));
   }
 }
 
@@ -385,6 +446,31 @@ GB_EXPORT int gb_conv_igemm(int dtype, const void* x, const void* w, const int* 
   a.status = gbh::status_ptr();
   dim3 grid((L + CBN - 1) / CBN, (M + CBM - 1) / CBM, Nimg);
   conv_igemm_kernel<0><<<grid, CTHREADS, CSMEM, (cudaStream_t)stream>>>(a);
+  GB_CUDA_OK(cudaGetLastError());
+  return gbh::E_OK;
+}
+
+// Whether gb_conv_direct_small takes a forward convolution: a contraction of at most 32 and a channel
+// count that is a multiple of 4 whose weights fit in 48 KB of shared memory.
+GB_EXPORT int gb_conv_direct_ok(int C, int T, int M) {
+  return C * T <= kDirectK && (M & 3) == 0 && M > 0 && (long long)(kDirectK + 1) * M * 4 <= 48 * 1024;
+}
+
+// The forward of gb_conv_igemm for the shapes gb_conv_direct_ok accepts (same arguments, no ktab).
+GB_EXPORT int gb_conv_direct_small(int dtype, const void* x, const void* w, const int* idx, const void* bias,
+                                   void* y, int Nimg, int C, int S, int L, int T, int M, void* stream) {
+  if (dtype != DT_BF16 && dtype != DT_F16) {
+    gbh::set_error("gb_conv_direct_small: bf16 or fp16 tensors");
+    return gbh::E_BAD_ARG;
+  }
+  if (!gb_conv_direct_ok(C, T, M) || Nimg <= 0 || Nimg > 65535 || L <= 0) {
+    gbh::set_error("gb_conv_direct_small: needs C * T <= %d, a channel count that is a multiple of 4, at most 65535 images", kDirectK);
+    return gbh::E_BAD_ARG;
+  }
+  const size_t smem = (size_t)(kDirectK + 1) * M * sizeof(float);
+  dim3 grid((L + 255) / 256, Nimg);
+  conv_direct_small_kernel<kDirectK><<<grid, 256, smem, (cudaStream_t)stream>>>(
+      (const uint16_t*)x, (const uint16_t*)w, idx, (const uint16_t*)bias, (uint16_t*)y, C, S, L, T, M, dtype == DT_BF16);
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;
 }

@@ -145,6 +145,7 @@ __global__ void pool_fwd_small_kernel(const T* __restrict__ x, const int* __rest
       cnt += src[t] >= 0;
     }
     const float inv = 1.f / (float)(count_include_pad ? T_ : (cnt > 0 ? cnt : 1));
+#pragma unroll 4
     for (long long b = blockIdx.y; b < B; b += gridDim.y) {
       const T* xb = x + b * S;
       float v[8];

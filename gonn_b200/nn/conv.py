@@ -101,9 +101,14 @@ class _ConvImplicit(torch.autograd.Function):
         wc = weight.contiguous()
         didx = device_maps(idx, S, x3.device, False)["idx"]
         y = torch.empty((N, Co, L), dtype=x3.dtype, device=x3.device)
-        _l.call("gb_conv_igemm", _l.I(_l.dtype_code(x3.dtype)), _l.ptr(xc), _l.ptr(wc), _l.ptr(_ktab(C, T, S, x3.device)),
-                _l.ptr(didx), _l.ptr(bias), _l.ptr(y), _l.I(N), _l.I(C), _l.I(S), _l.I(L), _l.I(T), _l.I(Co),
-                _l.stream_ptr())
+        if _l.lib().gb_conv_direct_ok(C, T, Co):
+            # a contraction of at most 32 (3 channels x 3 x 3): one thread per output position, no tensor-core tile
+            _l.call("gb_conv_direct_small", _l.I(_l.dtype_code(x3.dtype)), _l.ptr(xc), _l.ptr(wc), _l.ptr(didx),
+                    _l.ptr(bias), _l.ptr(y), _l.I(N), _l.I(C), _l.I(S), _l.I(L), _l.I(T), _l.I(Co), _l.stream_ptr())
+        else:
+            _l.call("gb_conv_igemm", _l.I(_l.dtype_code(x3.dtype)), _l.ptr(xc), _l.ptr(wc),
+                    _l.ptr(_ktab(C, T, S, x3.device)), _l.ptr(didx), _l.ptr(bias), _l.ptr(y), _l.I(N), _l.I(C), _l.I(S),
+                    _l.I(L), _l.I(T), _l.I(Co), _l.stream_ptr())
         ctx.save_for_backward(xc, wc)
         ctx.geom = (idx, S, L, T)
         ctx.weight_ref, ctx.bias_ref = weight, bias

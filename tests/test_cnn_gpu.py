@@ -45,6 +45,10 @@ def test_conv2d(dtype, kw, status_ok):
     dict(nd=2, cin=8, cout=16, k=5, hw=(40, 40), n=2, padding=2, dilation=2),
     dict(nd=1, cin=16, cout=24, k=7, hw=(300,), n=4, padding=3),
     dict(nd=3, cin=4, cout=8, k=3, hw=(6, 7, 8), n=2, padding=1),
+    # contractions of at most 32 with a channel count that is a multiple of 4: the direct forward kernel
+    dict(nd=2, cin=1, cout=8, k=5, hw=(28, 28), n=5, padding=2, stride=2),   # K = 25, padded borders
+    dict(nd=1, cin=2, cout=12, k=9, hw=(301,), n=3, padding=4),              # K = 18, ragged last block of positions
+    dict(nd=2, cin=3, cout=64, k=3, hw=(7, 300), n=2),                       # more than 256 positions per row of CTAs
 ])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_implicit_gemm_conv(case, dtype, status_ok):
