@@ -123,12 +123,15 @@ conv_igemm_kernel(const ConvArgs a) {
     bool ok = true;
     const int e0 = 2 * lane;
     int* sidx = reinterpret_cast<int*>(smem + CSTAGES * CSTAGE_BYTES + 256);   // [128][T] (fwd) or [64][T] (wgrad)
+    // Forward / dgrad tiles run over the positions of ALL images (p = image * L + l), so a plane whose
+    // size is not a multiple of the tile (13 x 13 = 169) does not leave a mostly empty second tile per image.
+    const long long P = (long long)a.Nimg * a.L;
     if (MODE == 0 && !is_a) {
       // the index rows of this CTA's 128 positions, staged once
       const int total = CBN * a.T;
       for (int i = threadIdx.x - CBM; i < total; i += CBN) {
-        const int l = n0 + i / a.T;
-        sidx[i] = l < a.L ? __ldg(a.idx + (long long)l * a.T + i % a.T) : -1;
+        const long long pp = (long long)n0 + i / a.T;
+        sidx[i] = pp < P ? __ldg(a.idx + (pp % a.L) * a.T + i % a.T) : -1;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");   // the four B warps only
     }
@@ -169,7 +172,8 @@ conv_igemm_kernel(const ConvArgs a) {
         // window operand, lanes along positions: consecutive positions read consecutive elements
         const int row = wq * 32 + lane;
         const int* ir = sidx + row * a.T;
-        const uint16_t* xn = a.X + (long long)blockIdx.z * a.C * a.S;
+        const long long pp = (long long)n0 + row;
+        const uint16_t* xn = a.X + (pp < P ? pp / a.L : 0) * a.C * a.S;   // this row's image (padding rows read image 0, zeroed)
         const int2* kt = a.ktab + k0;
 #pragma unroll 1
         for (int h = 0; h < 4; h++) {
@@ -304,14 +308,18 @@ conv_igemm_kernel(const ConvArgs a) {
         __syncwarp();
         const int col = n0 + col0 + lane;
         if (MODE == 0) {
-          uint16_t* yb = (uint16_t*)a.Y + (long long)blockIdx.z * a.M * a.L;
+          const long long pp = (long long)n0 + col0 + lane;          // position over all images
+          const bool live = pp < (long long)a.Nimg * a.L;
+          const long long img = live ? pp / a.L : 0;
+          const int lpos = (int)(pp - img * a.L);
+          uint16_t* yb = (uint16_t*)a.Y + img * a.M * a.L + lpos;
           for (int rr = 0; rr < 32; rr++) {
             const int m = mrow0 + rr;
             if (m >= a.M) break;
-            if (col < a.L) {
+            if (live) {
               const float bv = a.bias ? raw16_to_float(__ldg(a.bias + m), a.bf16) : 0.f;
               const float v = stf[rr * 33 + lane] + bv;
-              yb[(long long)m * a.L + col] =
+              yb[(long long)m * a.L] =
                   a.bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
             }
           }
@@ -429,7 +437,7 @@ GB_EXPORT int gb_conv_igemm(int dtype, const void* x, const void* w, const int* 
     return gbh::E_BAD_ARG;
   }
   if (Nimg <= 0 || C <= 0 || L <= 0 || T <= 0 || M <= 0 || Nimg > 65535 || T > CMAX_T_SMEM ||
-      (long long)C * S >= (1LL << 31) || (long long)M * L >= (1LL << 31)) {
+      (long long)C * S >= (1LL << 31) || (long long)M * L >= (1LL << 31) || (long long)Nimg * L >= (1LL << 31) - CBN) {
     gbh::set_error("gb_conv_igemm: geometry out of range (at most %d taps, 65535 images)", CMAX_T_SMEM);
     return gbh::E_BAD_ARG;
   }
@@ -444,7 +452,7 @@ GB_EXPORT int gb_conv_igemm(int dtype, const void* x, const void* w, const int* 
   a.Nimg = Nimg; a.C = C; a.S = S; a.L = L; a.T = T; a.M = M;
   a.bf16 = dtype == DT_BF16;
   a.status = gbh::status_ptr();
-  dim3 grid((L + CBN - 1) / CBN, (M + CBM - 1) / CBM, Nimg);
+  dim3 grid((unsigned)(((long long)Nimg * L + CBN - 1) / CBN), (M + CBM - 1) / CBM, 1);
   conv_igemm_kernel<0><<<grid, CTHREADS, CSMEM, (cudaStream_t)stream>>>(a);
   GB_CUDA_OK(cudaGetLastError());
   return gbh::E_OK;
