@@ -410,6 +410,112 @@ conv_direct_small_kernel(const uint16_t* __restrict__ x, const uint16_t* __restr
   }
 }
 
+// Weight gradient for the same short contractions (C * T <= 32), M = 32, 64 or 128 output channels:
+//   dW[m][k] = sum over positions p (all images) of dy[p][m] * patch[p][k].
+// A CTA walks its share of the positions in tiles of 256: every thread gathers the K inputs of one
+// position and the M gradients of that position into shared memory (rows padded by four words so that
+// 16-byte accesses of consecutive rows fall into different banks), then the CTA's 256 threads form
+// 256 / M position groups of M threads; a thread accumulates a 4 (channels) x 8 (k) block of dW over its
+// group's positions with three 16-byte shared loads per 32 FMAs.  The groups are added in order at the
+// end and the CTA writes one partial matrix; conv_wgrad_finish_kernel adds the CTAs in index order.
+template <int M>
+__global__ void __launch_bounds__(256, 2)
+conv_wgrad_small_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ dy, const int* __restrict__ idx,
+                        float* __restrict__ part, int Nimg, int C, int S, int L, int T, int bf16) {
+  constexpr int KMAX = kDirectK, PS = KMAX + 4, GS = M + 4, GROUPS = 256 / M;
+  extern __shared__ __align__(16) float smw[];
+  float* sP = smw;                 // [256][PS]  patches
+  float* sG = smw + 256 * PS;      // [256][GS]  gradients
+  const int K = C * T;
+  const long long P = (long long)Nimg * L;
+  const long long per = ((P + gridDim.x - 1) / gridDim.x + 255) / 256 * 256;
+  const long long p_begin = (long long)blockIdx.x * per;
+  const long long p_end = p_begin + per < P ? p_begin + per : P;
+  const int t = threadIdx.x;
+  const int grp = t / M, tm = t % M;           // position group; 4-channel block and k block inside it
+  const int co4 = tm >> 2, kq = tm & 3;
+  float acc[4][8];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
+  for (long long p0 = p_begin; p0 < p_end; p0 += 256) {
+    __syncthreads();                            // the previous tile has been consumed
+    {
+      const long long p = p0 + t;
+      const bool live = p < p_end;
+      const long long n = live ? p / L : 0;
+      const int l = (int)(p - n * L);
+      const uint16_t* xn = x + n * C * S;
+      float v[KMAX];
+      int c = 0, tap = 0;
+#pragma unroll
+      for (int k = 0; k < KMAX; k++) {
+        float f = 0.f;
+        if (k < K) {
+          const int src = live ? __ldg(idx + (long long)l * T + tap) : -1;
+          if (src >= 0) f = raw16_to_float(__ldg(xn + (long long)c * S + src), bf16);
+          if (++tap == T) { tap = 0; c++; }
+        }
+        v[k] = f;
+      }
+#pragma unroll
+      for (int k4 = 0; k4 < KMAX / 4; k4++)
+        *reinterpret_cast<float4*>(sP + t * PS + 4 * k4) = make_float4(v[4 * k4], v[4 * k4 + 1], v[4 * k4 + 2], v[4 * k4 + 3]);
+      const uint16_t* gn = dy + n * M * L + l;
+#pragma unroll 4
+      for (int m4 = 0; m4 < M / 4; m4++) {
+        float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live) {
+          g.x = raw16_to_float(__ldg(gn + (long long)(4 * m4) * L), bf16);
+          g.y = raw16_to_float(__ldg(gn + (long long)(4 * m4 + 1) * L), bf16);
+          g.z = raw16_to_float(__ldg(gn + (long long)(4 * m4 + 2) * L), bf16);
+          g.w = raw16_to_float(__ldg(gn + (long long)(4 * m4 + 3) * L), bf16);
+        }
+        *reinterpret_cast<float4*>(sG + t * GS + 4 * m4) = g;
+      }
+    }
+    __syncthreads();
+    // group grp takes positions grp, grp + GROUPS, ... of the tile
+#pragma unroll 2
+    for (int q = grp; q < 256; q += GROUPS) {
+      const float4 g = *reinterpret_cast<const float4*>(sG + q * GS + 4 * co4);
+      const float4 pa = *reinterpret_cast<const float4*>(sP + q * PS + 8 * kq);
+      const float4 pb = *reinterpret_cast<const float4*>(sP + q * PS + 8 * kq + 4);
+      const float gv[4] = {g.x, g.y, g.z, g.w};
+      const float pv[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = fmaf(gv[i], pv[j], acc[i][j]);
+    }
+  }
+  // add the position groups in order: group 0 writes, the others add one after another
+  __syncthreads();
+  float* red = smw;                             // [M][KMAX], reusing the tile memory
+  for (int gsel = 0; gsel < GROUPS; gsel++) {
+    if (grp == gsel) {
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          float* dst = red + (4 * co4 + i) * KMAX + 8 * kq + j;
+          *dst = gsel == 0 ? acc[i][j] : *dst + acc[i][j];
+        }
+    }
+    __syncthreads();
+  }
+  float* out = part + (long long)blockIdx.x * M * K;
+  for (int i = t; i < M * K; i += 256) out[i] = red[(i / K) * KMAX + i % K];
+}
+
+inline int wgrad_small_ctas(long long P) {
+  long long g = (P + 255) / 256;
+  if (g > 2 * 148) g = 2 * 148;
+  return g < 1 ? 1 : (int)g;
+}
+inline bool wgrad_small_ok(int C, int T, int M) { return C * T <= kDirectK && (M == 32 || M == 64 || M == 128); }
+
 int set_attr_once() {
   static bool done = false;
   if (!done) {
@@ -486,6 +592,7 @@ GB_EXPORT int gb_conv_direct_small(int dtype, const void* x, const void* w, cons
 // Number of K splits the weight gradient uses for a problem (partials: splits * M * C * T floats).
 GB_EXPORT int gb_conv_wgrad_splits(int Nimg, int L, int M, int C, int T) {
   const long long R = (long long)Nimg * L;
+  if (wgrad_small_ok(C, T, M)) return wgrad_small_ctas(R);      // one partial matrix per CTA of the direct kernel
   const long long tiles = (long long)((M + CBM - 1) / CBM) * ((C * T + CBN - 1) / CBN);
   long long want = (2 * 148 + tiles - 1) / tiles;          // about two waves of CTAs
   const long long max_splits = (R + 4 * CBK - 1) / (4 * CBK);  // at least four k-blocks per split
@@ -510,6 +617,27 @@ GB_EXPORT int gb_conv_wgrad(int dtype, const void* x, const void* dy, const int*
   if (rc) return rc;
   const int splits = gb_conv_wgrad_splits(Nimg, L, M, C, T);
   const long long R = (long long)Nimg * L;
+  if (wgrad_small_ok(C, T, M)) {
+    const size_t smem = (size_t)256 * ((kDirectK + 4) + (M + 4)) * sizeof(float);
+    const int bf = dtype == DT_BF16;
+#define GB_WS(MM)                                                                                              \
+  {                                                                                                            \
+    static bool cfg = false;                                                                                   \
+    if (!cfg) {                                                                                                \
+      GB_CUDA_OK(cudaFuncSetAttribute(conv_wgrad_small_kernel<MM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+      cfg = true;                                                                                              \
+    }                                                                                                          \
+    conv_wgrad_small_kernel<MM><<<splits, 256, smem, (cudaStream_t)stream>>>(                                  \
+        (const uint16_t*)x, (const uint16_t*)dy, idx, part, Nimg, C, S, L, T, bf);                             \
+  }
+    if (M == 32) GB_WS(32) else if (M == 64) GB_WS(64) else GB_WS(128)
+#undef GB_WS
+    const long long nn = (long long)M * C * T;
+    conv_wgrad_finish_kernel<<<(int)((nn + 255) / 256 < 592 ? (nn + 255) / 256 : 592), 256, 0, (cudaStream_t)stream>>>(
+        part, (uint16_t*)dw, nn, splits, bf, beta);
+    GB_CUDA_OK(cudaGetLastError());
+    return gbh::E_OK;
+  }
   long long per = (R + splits - 1) / splits;
   per = (per + CBK - 1) / CBK * CBK;
   ConvArgs a;

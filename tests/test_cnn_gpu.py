@@ -49,6 +49,10 @@ def test_conv2d(dtype, kw, status_ok):
     dict(nd=2, cin=1, cout=8, k=5, hw=(28, 28), n=5, padding=2, stride=2),   # K = 25, padded borders
     dict(nd=1, cin=2, cout=12, k=9, hw=(301,), n=3, padding=4),              # K = 18, ragged last block of positions
     dict(nd=2, cin=3, cout=64, k=3, hw=(7, 300), n=2),                       # more than 256 positions per row of CTAs
+    # ... and 32 / 64 / 128 output channels: the direct weight-gradient kernel as well
+    dict(nd=2, cin=3, cout=32, k=3, hw=(20, 20), n=3, padding=1),
+    dict(nd=2, cin=2, cout=128, k=3, hw=(9, 11), n=5),
+    dict(nd=2, cin=3, cout=64, k=3, hw=(32, 32), n=40),                      # more positions than one pass of the CTAs
 ])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_implicit_gemm_conv(case, dtype, status_ok):
