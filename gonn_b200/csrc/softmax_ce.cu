@@ -76,6 +76,76 @@ __global__ void softmax_bwd_kernel(const T* __restrict__ y, const T* __restrict_
   }
 }
 
+// Softmax / log-softmax for 16-bit rows whose length is a multiple of 8: one pass over the row with
+// 16-byte loads and a running (max, sum) pair per thread, then a second pass (served by the cache) that
+// writes 16 bytes at a time.  No shared-memory copy of the row.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+softmax_fwd_vec_kernel(const T* __restrict__ x, T* __restrict__ y, int D) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
+  uint4* yr = reinterpret_cast<uint4*>(y + row * D);
+  const int nvec = D / 8;
+  float m = -INFINITY, s = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 u = xr[v];
+    const T* e = reinterpret_cast<const T*>(&u);
+    float f[8], mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; j++) { f[j] = (float)e[j]; mx = fmaxf(mx, f[j]); }
+    if (mx > m) { s *= __expf(m - mx); m = mx; }
+#pragma unroll
+    for (int j = 0; j < 8; j++) s += __expf(f[j] - m);
+  }
+  const float M = block_max(m, red);
+  s = block_sum(m == -INFINITY ? 0.f : s * __expf(m - M), red);
+  const float inv = 1.f / s, ls = logf(s);
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 u = xr[v];
+    const T* e = reinterpret_cast<const T*>(&u);
+    alignas(16) T o[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const float d = (float)e[j] - M;
+      o[j] = (T)(MODE == 0 ? __expf(d) * inv : d - ls);
+    }
+    yr[v] = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256)
+softmax_bwd_vec_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx, int D) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const uint4* yr = reinterpret_cast<const uint4*>(y + row * D);
+  const uint4* gr = reinterpret_cast<const uint4*>(dy + row * D);
+  uint4* dr = reinterpret_cast<uint4*>(dx + row * D);
+  const int nvec = D / 8;
+  float s = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 a = yr[v], b = gr[v];
+    const T* ya = reinterpret_cast<const T*>(&a);
+    const T* gb_ = reinterpret_cast<const T*>(&b);
+#pragma unroll
+    for (int j = 0; j < 8; j++) s += MODE == 0 ? (float)gb_[j] * (float)ya[j] : (float)gb_[j];
+  }
+  s = block_sum(s, red);
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 a = yr[v], b = gr[v];
+    const T* ya = reinterpret_cast<const T*>(&a);
+    const T* gb_ = reinterpret_cast<const T*>(&b);
+    alignas(16) T o[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const float yv = (float)ya[j], g = (float)gb_[j];
+      o[j] = (T)(MODE == 0 ? yv * (g - s) : g - __expf(yv) * s);
+    }
+    dr[v] = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
 // Cross-entropy forward.  Per row: lse, weighted loss (0 for ignored rows) and
 // the effective weight (the row's contribution to the mean denominator).
 template <typename T>
@@ -331,6 +401,14 @@ int set_smem(const void* kern, int D, int* use_smem, size_t* bytes) {
 
 template <typename T>
 int softmax_fwd_t(int mode, const void* x, void* y, long long rows, int D, cudaStream_t s) {
+  if constexpr (sizeof(T) == 2) {
+    if ((D & 7) == 0 && D >= 256 && ((((uintptr_t)x | (uintptr_t)y) & 15) == 0)) {
+      if (mode) softmax_fwd_vec_kernel<T, 1><<<(unsigned)rows, 256, 0, s>>>((const T*)x, (T*)y, D);
+      else softmax_fwd_vec_kernel<T, 0><<<(unsigned)rows, 256, 0, s>>>((const T*)x, (T*)y, D);
+      GB_CUDA_OK(cudaGetLastError());
+      return gbh::E_OK;
+    }
+  }
   int use_smem;
   size_t bytes;
   const void* k = mode ? (const void*)softmax_fwd_kernel<T, 1> : (const void*)softmax_fwd_kernel<T, 0>;
@@ -344,6 +422,14 @@ int softmax_fwd_t(int mode, const void* x, void* y, long long rows, int D, cudaS
 
 template <typename T>
 int softmax_bwd_t(int mode, const void* y, const void* dy, void* dx, long long rows, int D, cudaStream_t s) {
+  if constexpr (sizeof(T) == 2) {
+    if ((D & 7) == 0 && D >= 256 && ((((uintptr_t)y | (uintptr_t)dy | (uintptr_t)dx) & 15) == 0)) {
+      if (mode) softmax_bwd_vec_kernel<T, 1><<<(unsigned)rows, 256, 0, s>>>((const T*)y, (const T*)dy, (T*)dx, D);
+      else softmax_bwd_vec_kernel<T, 0><<<(unsigned)rows, 256, 0, s>>>((const T*)y, (const T*)dy, (T*)dx, D);
+      GB_CUDA_OK(cudaGetLastError());
+      return gbh::E_OK;
+    }
+  }
   if (mode) softmax_bwd_kernel<T, 1><<<(unsigned)rows, block_for(D), 0, s>>>((const T*)y, (const T*)dy, (T*)dx, D);
   else softmax_bwd_kernel<T, 0><<<(unsigned)rows, block_for(D), 0, s>>>((const T*)y, (const T*)dy, (T*)dx, D);
   GB_CUDA_OK(cudaGetLastError());

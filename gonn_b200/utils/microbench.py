@@ -386,11 +386,28 @@ def bench_host_time():
           kernels_per_step=graphed.launches_per_step)
 
 
+def bench_secondary():
+    """Operators outside the training steps, 2^26 bf16 elements (8192 x 8192): dropout, row softmax, a
+    row-vector broadcast multiply, arg-max over columns, each beside torch's kernel for the same call."""
+    from ..ops import elementwise as ew
+    from ..ops.dropout import dropout
+    from ..ops.reduce import reduce_axis
+    from ..ops.softmax import softmax
+    a = torch.randn(1 << 26, device="cuda", dtype=torch.bfloat16)
+    m = a.view(8192, 8192)
+    b = torch.randn(8192, device="cuda", dtype=torch.bfloat16)
+    for name, ours, ref in (("dropout p=0.1", lambda: dropout(a, 0.1), lambda: torch.nn.functional.dropout(a, 0.1)),
+                            ("softmax rows of 8192", lambda: softmax(m, -1), lambda: torch.softmax(m, -1)),
+                            ("(8192 x 8192) * (8192)", lambda: ew.binary_forward("mul", m, b), lambda: m * b),
+                            ("argmax over columns", lambda: reduce_axis(m, 0, "argmax"), lambda: m.argmax(0))):
+        _emit(bench="secondary", op=name, us=timeit(ours) * 1e3, torch_us=timeit(ref) * 1e3)
+
+
 def main(argv):
     kind = argv[0] if argv else "gemm"
     fn = {"gemm": bench_gemm, "elementwise": bench_elementwise, "flash": bench_flash, "norm": bench_norm,
           "mlp": bench_mlp_cpu, "allreduce": bench_allreduce, "refattn": bench_reference_attention, "resident": bench_resident_mlp,
-          "hosttime": bench_host_time}.get(kind)
+          "hosttime": bench_host_time, "secondary": bench_secondary}.get(kind)
     if fn is None:
         raise SystemExit(f"unknown benchmark {kind!r}")
     fn()

@@ -357,6 +357,21 @@ def test_dropout_statistics_and_backward(status_ok):
     assert torch.equal(x.grad, y.detach())  # same mask regenerated in backward
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_dropout_mask_is_the_same_on_the_vector_and_scalar_paths(dtype, status_ok):
+    """A length that is a multiple of the vector width takes the 16-byte kernel, one more element takes
+    the scalar kernel: element i gets the same draw on both."""
+    from gonn_b200 import lib as L
+    n = 1 << 16
+    x = torch.randn(n + 1, device="cuda").to(dtype)
+    yv, ys = torch.empty(n, device="cuda", dtype=dtype), torch.empty(n + 1, device="cuda", dtype=dtype)
+    for out, cnt in ((yv, n), (ys, n + 1)):
+        L.call("gb_dropout", L.I(L.dtype_code(dtype)), L.ptr(x), L.ptr(out), L.L(cnt), L.F(0.3), L.L(1234), L.L(77),
+               L.stream_ptr())
+    assert torch.equal(yv, ys[:n])
+    assert 0.68 < (yv != 0).float().mean().item() < 0.72
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_fused_rnn_gates_match_oracle(dtype):
     """LSTM / GRU gate kernels, forward and backward, against the torch expression in fp32."""
