@@ -153,6 +153,18 @@ col_reduce_vec_kernel(const T* __restrict__ x, TO* __restrict__ y, float* __rest
       for (int j = 0; j < 8; j++) a[j] = r_comb<float, OP>(a[j], (float)e[j]);
     };
     long long r = r0 + ty;
+    // eight rows in flight per thread while there are that many, then four, then one
+    for (; r + 56 < r1; r += 64) {
+      const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(xp + r * inner));
+      const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(xp + (r + 8) * inner));
+      const uint4 u2 = __ldg(reinterpret_cast<const uint4*>(xp + (r + 16) * inner));
+      const uint4 u3 = __ldg(reinterpret_cast<const uint4*>(xp + (r + 24) * inner));
+      const uint4 u4 = __ldg(reinterpret_cast<const uint4*>(xp + (r + 32) * inner));
+      const uint4 u5 = __ldg(reinterpret_cast<const uint4*>(xp + (r + 40) * inner));
+      const uint4 u6 = __ldg(reinterpret_cast<const uint4*>(xp + (r + 48) * inner));
+      const uint4 u7 = __ldg(reinterpret_cast<const uint4*>(xp + (r + 56) * inner));
+      take(u0); take(u1); take(u2); take(u3); take(u4); take(u5); take(u6); take(u7);
+    }
     for (; r + 24 < r1; r += 32) {
       const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(xp + r * inner));
       const uint4 u1 = __ldg(reinterpret_cast<const uint4*>(xp + (r + 8) * inner));
