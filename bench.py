@@ -133,6 +133,11 @@ def main():
     device = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # whatever NCCL logs (a version banner when NCCL_DEBUG is set) goes to stderr: stdout carries
+        # the one JSON line
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"       # no "NCCL version ..." banner on stdout
         dist.init_process_group("nccl", device_id=device)
 
     if world > 1:
