@@ -21,7 +21,7 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 
 
 def find_source() -> str | None:
-    """Path of the reference's ``gonn_cuda.cu``: ``$GONN_REFERENCE`` or ``/root/reference``."""
+    """Path of the reference's ``gonn_cuda.cu``: under ``$GONN_REFERENCE``, else under the default checkout location."""
     for root in (os.environ.get("GONN_REFERENCE"), "/root/reference"):
         if root:
             p = os.path.join(root, "backend", "cuda", "gonn_cuda.cu")

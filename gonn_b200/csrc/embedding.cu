@@ -55,9 +55,20 @@ __global__ void emb_scan_kernel(const int* __restrict__ count, int V, int* __res
   const int per = (V + 1023) / 1024;
   const int b = threadIdx.x * per, e = min(b + per, V);
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  // whole 16-byte groups when every thread's run is a multiple of four counters and starts aligned
+  const bool vec = (per & 3) == 0 && e - b == per && ((uintptr_t)count & 15) == 0 && ((uintptr_t)offs & 15) == 0;
   int s = 0;
+  if (vec) {
+    const int4* c4 = reinterpret_cast<const int4*>(count + b);
 #pragma unroll 8
-  for (int i = b; i < e; i++) s += count[i];
+    for (int i = 0; i < per / 4; i++) {
+      const int4 v = c4[i];
+      s += v.x + v.y + v.z + v.w;
+    }
+  } else {
+#pragma unroll 8
+    for (int i = b; i < e; i++) s += count[i];
+  }
   int inc = s;                                           // inclusive scan inside the warp
 #pragma unroll
   for (int d = 1; d < 32; d <<= 1) {
@@ -79,8 +90,21 @@ __global__ void emb_scan_kernel(const int* __restrict__ count, int V, int* __res
   }
   __syncthreads();
   int run = warp_tot[wid] + inc - s;
+  if (vec) {
+    const int4* c4 = reinterpret_cast<const int4*>(count + b);
+    int4* o4 = reinterpret_cast<int4*>(offs + b);
 #pragma unroll 8
-  for (int i = b; i < e; i++) { offs[i] = run; run += count[i]; }
+    for (int i = 0; i < per / 4; i++) {
+      const int4 v = c4[i];
+      int4 o;
+      o.x = run; o.y = o.x + v.x; o.z = o.y + v.y; o.w = o.z + v.z;
+      run = o.w + v.w;
+      o4[i] = o;
+    }
+  } else {
+#pragma unroll 8
+    for (int i = b; i < e; i++) { offs[i] = run; run += count[i]; }
+  }
 }
 
 __global__ void emb_place_kernel(const long long* __restrict__ idx, long long n, long long V,

@@ -1381,15 +1381,37 @@ __global__ void splitk_finish_kernel(const float* __restrict__ ws, TO* __restric
        i += (long long)gridDim.x * blockDim.x * 4) {
     // N is a multiple of 4 here, so the four elements share a row
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
     for (int s = 0; s < splits; s++) {
       const float4 v = *reinterpret_cast<const float4*>(ws + s * total + i);
       a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
     }
-    const long long b = i / per, r = i - b * per;
-    const long long m = r / N, n = r - m * N;
+    long long b, m, n;
+    if (total <= 0x7fffffffLL) {          // 32-bit index arithmetic: the 64-bit divisions cost more than the sums
+      const unsigned ui = (unsigned)i, uper = (unsigned)per, uN = (unsigned)N;
+      const unsigned ub = ui / uper, ur = ui - ub * uper, um = ur / uN;
+      b = ub; m = um; n = ur - um * uN;
+    } else {
+      b = i / per;
+      const long long r = i - b * per;
+      m = r / N;
+      n = r - m * N;
+    }
     TO* c = C + b * strideC + m * ldc + n;
-    if (beta) { a.x += (float)c[0]; a.y += (float)c[1]; a.z += (float)c[2]; a.w += (float)c[3]; }
-    c[0] = (TO)a.x; c[1] = (TO)a.y; c[2] = (TO)a.z; c[3] = (TO)a.w;
+    if (sizeof(TO) == 2 && (((uintptr_t)c & 7) == 0)) {
+      // four 16-bit results as one 8-byte access
+      uint2 raw;
+      if (beta) {
+        raw = *reinterpret_cast<const uint2*>(c);
+        const TO* e = reinterpret_cast<const TO*>(&raw);
+        a.x += (float)e[0]; a.y += (float)e[1]; a.z += (float)e[2]; a.w += (float)e[3];
+      }
+      TO o[4] = {(TO)a.x, (TO)a.y, (TO)a.z, (TO)a.w};
+      *reinterpret_cast<uint2*>(c) = *reinterpret_cast<const uint2*>(o);
+    } else {
+      if (beta) { a.x += (float)c[0]; a.y += (float)c[1]; a.z += (float)c[2]; a.w += (float)c[3]; }
+      c[0] = (TO)a.x; c[1] = (TO)a.y; c[2] = (TO)a.z; c[3] = (TO)a.w;
+    }
   }
 }
 
