@@ -1462,14 +1462,15 @@ int gemm_tc(int esz, const void* A, const void* B, GemmArgs& args, int transA, i
     if (N <= 128 || tiles256 < g_num_sms) bn = 128;
   }
   if (force_bn == 128 || force_bn == 256) bn = force_bn;
-  // two-CTA 256 x 256 tiles when they can fill the GPU (force_bn == 512 forces them)
+  // two-CTA 256 x 256 tiles when they fill at least four fifths of the SM pairs (measured at 2048^3: 64 pair
+  // tiles on 74 pairs beat 128 one-CTA tiles on 148 SMs by 8 %); force_bn == 512 forces them
   bool use2 = false;
   if (esz == 2) {
     long long pair_tiles = (long long)((M + 255) / 256) * ((N + 255) / 256) * batch;
     // measured: the pair kernel wins when the main loop dominates (long K, or a plain
     // epilogue); with short K and a heavy epilogue the one-CTA kernel is slightly ahead
     const bool light = args.act == ACT_NONE && args.aux_mode == AUX_NONE;
-    use2 = force_bn == 512 || (force_bn == 0 && g_use_2cta && pair_tiles >= g_num_sms / 2 && M >= 256 &&
+    use2 = force_bn == 512 || (force_bn == 0 && g_use_2cta && pair_tiles * 5 >= (long long)(g_num_sms / 2) * 4 && M >= 256 &&
                                N >= 256 && (K >= 1536 || light));
   }
   // Split-K: a product with few output tiles and a long K is cut into K slices that run as
