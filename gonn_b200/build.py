@@ -50,8 +50,17 @@ def _digest(path: str, extra=()) -> str:
     return h.hexdigest()
 
 
+def _has_checks(name: str) -> bool:
+    """Whether the translation unit changes under -DGB_BOUNDS_CHECK (it includes bounds.cuh or tests the macro)."""
+    with open(os.path.join(CSRC, name)) as f:
+        text = f.read()
+    return "bounds.cuh" in text or "GB_BOUNDS_CHECK" in text
+
+
 def _compile(name: str, verbose: bool, force: bool, debug: bool = False):
     src = os.path.join(CSRC, name)
+    if debug and not _has_checks(name):
+        debug = False              # identical object either way: the debug library links the regular one
     extra = DEBUG_FLAGS if debug else []
     obj = os.path.join(OBJ_DIR, name[:-3] + (".dbg.o" if debug else ".o"))
     stamp = obj + ".sha"
@@ -82,7 +91,7 @@ def build(verbose: bool = False, force: bool = False, debug: bool = False) -> st
             if verbose and log:
                 print(f"--- {name}\n{log}")
     if rebuilt or not os.path.exists(lib):
-        objs = [os.path.join(OBJ_DIR, n[:-3] + (".dbg.o" if debug else ".o")) for n in srcs]
+        objs = [os.path.join(OBJ_DIR, n[:-3] + (".dbg.o" if debug and _has_checks(n) else ".o")) for n in srcs]
         cmd = [NVCC] + ARCH + ["-shared", "-o", lib] + objs + ["-lcudart", "-lpthread"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
