@@ -90,8 +90,9 @@ def build(verbose: bool = False, force: bool = False, debug: bool = False) -> st
             rebuilt |= did
             if verbose and log:
                 print(f"--- {name}\n{log}")
-    if rebuilt or not os.path.exists(lib):
-        objs = [os.path.join(OBJ_DIR, n[:-3] + (".dbg.o" if debug and _has_checks(n) else ".o")) for n in srcs]
+    objs = [os.path.join(OBJ_DIR, n[:-3] + (".dbg.o" if debug and _has_checks(n) else ".o")) for n in srcs]
+    # an object may have been rebuilt by the other flavour's pass (the two libraries share most objects)
+    if rebuilt or not os.path.exists(lib) or any(os.path.getmtime(o) > os.path.getmtime(lib) for o in objs):
         cmd = [NVCC] + ARCH + ["-shared", "-o", lib] + objs + ["-lcudart", "-lpthread"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:

@@ -27,6 +27,7 @@ constexpr int GR = 4;           // rows per warp
 constexpr int GW = 4;           // warps per CTA
 constexpr int GROWS = GR * GW;  // rows per CTA
 constexpr int GT = 32;          // tile rows (one per lane)
+static_assert(GR == 4, "the coefficient buffers are read four rows at a time");
 
 enum { MODE_FWD = 0, MODE_DQ = 1, MODE_DKV = 2 };
 
@@ -90,17 +91,88 @@ __device__ __forceinline__ double exp_ct(double x) { return exp(x); }
 __device__ __forceinline__ float log_ct(float x) { return __logf(x); }
 __device__ __forceinline__ double log_ct(double x) { return log(x); }
 
+// Four consecutive elements of the compute type, read from / written to shared memory with 16-byte
+// accesses (p is a multiple of four elements away from the 16-byte aligned base).
+__device__ __forceinline__ void ld4(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void ld4(const double* p, double (&v)[4]) {
+  const double2 t = *reinterpret_cast<const double2*>(p), u = *reinterpret_cast<const double2*>(p + 2);
+  v[0] = t.x; v[1] = t.y; v[2] = u.x; v[3] = u.y;
+}
+__device__ __forceinline__ void st4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void st4(double* p, const double (&v)[4]) {
+  *reinterpret_cast<double2*>(p) = make_double2(v[0], v[1]);
+  *reinterpret_cast<double2*>(p + 2) = make_double2(v[2], v[3]);
+}
+
+// Four consecutive elements from global memory: one or two vector loads when `vec` (the address is
+// aligned to min(16, 4 * sizeof(T)) bytes), else element by element.
+template <typename T, typename CT>
+__device__ __forceinline__ void gload4(const T* g, bool vec, CT (&v)[4]) {
+  if (vec) {
+    if constexpr (sizeof(T) == 8) {
+      const double2 t = __ldg(reinterpret_cast<const double2*>(g)), u = __ldg(reinterpret_cast<const double2*>(g) + 1);
+      v[0] = (CT)t.x; v[1] = (CT)t.y; v[2] = (CT)u.x; v[3] = (CT)u.y;
+    } else if constexpr (sizeof(T) == 4) {
+      const float4 t = __ldg(reinterpret_cast<const float4*>(g));
+      v[0] = (CT)t.x; v[1] = (CT)t.y; v[2] = (CT)t.z; v[3] = (CT)t.w;
+    } else {
+      const uint2 raw = __ldg(reinterpret_cast<const uint2*>(g));
+      T t[4];
+      memcpy(t, &raw, 8);
+#pragma unroll
+      for (int u = 0; u < 4; u++) v[u] = load_as<T, CT>(t + u);
+    }
+  } else {
+#pragma unroll
+    for (int u = 0; u < 4; u++) v[u] = load_as<T, CT>(g + u);
+  }
+}
+
 // Copies `n` rows of D elements (rows r0.. of tensor p with strides s, fixed b and h) into smem
-// [n][DP]; rows past `limit` and the padding columns become zero.
+// [n][DP]; rows past `limit` and the columns D .. round-up-to-4(D) become zero (nothing reads further).
+// Head sizes that are multiples of 4 move in chunks of four elements, four chunks per thread in
+// flight before the first is stored: the loop is bound by the L2 round trip otherwise.
 template <typename T, typename CT>
 __device__ __forceinline__ void stage_rows(CT* dst, const void* p, const long long* s, int b, int h, int r0, int n,
                                            int limit, int D, int DP) {
   const T* base = (const T*)p + (long long)b * s[0] + (long long)h * s[2];
-  for (int i = threadIdx.x; i < n * DP; i += blockDim.x) {
-    const int r = i / DP, c = i - r * DP;
+  if ((D & 3) == 0) {
+    constexpr int U = 4;
+    constexpr uintptr_t AL = sizeof(T) * 4 < 16 ? sizeof(T) * 4 : 16;
+    const bool vec = ((reinterpret_cast<uintptr_t>(base) | (uintptr_t)(s[1] * (long long)sizeof(T))) & (AL - 1)) == 0;
+    const int nc = D >> 2, total = n * nc;
+    for (int q0 = threadIdx.x; q0 < total; q0 += blockDim.x * U) {
+      CT v[U][4];
+      int off[U];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const int q = q0 + u * blockDim.x;
+#pragma unroll
+        for (int c = 0; c < 4; c++) v[u][c] = 0;
+        off[u] = -1;
+        if (q < total) {
+          const int r = q / nc, c = (q - r * nc) * 4;
+          off[u] = r * DP + c;
+          if (r0 + r < limit) gload4<T, CT>(base + (long long)(r0 + r) * s[1] + c, vec, v[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; u++)
+        if (off[u] >= 0) st4(dst + off[u], v[u]);
+    }
+    return;
+  }
+  const int DR = (D + 3) & ~3;
+  for (int i = threadIdx.x; i < n * DR; i += blockDim.x) {
+    const int r = i / DR, c = i - r * DR;
     CT v = 0;
     if (c < D && r0 + r < limit) v = load_as<T, CT>(base + (long long)(r0 + r) * s[1] + c);
-    dst[i] = v;
+    dst[r * DP + c] = v;
   }
 }
 
@@ -156,6 +228,13 @@ attn_general_kernel(const GArgs a) {
     }
   }
   const int wrow0 = warp * GR;               // this warp's first row inside the CTA
+  // A row of D columns needs ceil(D / 4) lanes in the accumulation step.  With head size <= 64 the
+  // warp splits into 2 (or 4, head size <= 32) lane groups that take interleaved tile rows, so no
+  // lane idles; the groups' partial sums meet after the last tile.
+  const int nl = (D + 3) >> 2;
+  const int groups = nl <= 8 ? 4 : nl <= 16 ? 2 : 1;
+  const int lpg = 32 / groups;
+  const int grp = lane / lpg, c0 = (lane - grp * lpg) * 4;
   // pure causal attention never looks past the diagonal: later tiles contribute exact zeros
   int tile_end = ntile;
   int tile_begin = 0;
@@ -191,17 +270,19 @@ attn_general_kernel(const GArgs a) {
       const CT* tb = tileB + lane * DP;
       for (int c = 0; c < D; c += 4) {
         CT x[4], y[4];
-#pragma unroll
-        for (int u = 0; u < 4; u++) { x[u] = ta[c + u]; y[u] = MODE == MODE_FWD ? (CT)0 : tb[c + u]; }
+        ld4(ta + c, x);
+        if (MODE != MODE_FWD) ld4(tb + c, y);
 #pragma unroll
         for (int r = 0; r < GR; r++) {
-          const CT* ra = rowsA + (wrow0 + r) * DP + c;
+          CT q4[4];
+          ld4(rowsA + (wrow0 + r) * DP + c, q4);
 #pragma unroll
-          for (int u = 0; u < 4; u++) s[r] += ra[u] * x[u];
+          for (int u = 0; u < 4; u++) s[r] += q4[u] * x[u];
           if (MODE != MODE_FWD) {
-            const CT* rb = rowsB + (wrow0 + r) * DP + c;
+            CT g4[4];
+            ld4(rowsB + (wrow0 + r) * DP + c, g4);
 #pragma unroll
-            for (int u = 0; u < 4; u++) dp[r] += rb[u] * y[u];
+            for (int u = 0; u < 4; u++) dp[r] += g4[u] * y[u];
           }
         }
       }
@@ -224,12 +305,15 @@ attn_general_kernel(const GArgs a) {
         // online softmax over the 32 lanes; tile rows past the end do not take part
         const CT sm = tvalid ? sv : (CT)-INFINITY;
         const CT m_new = fmax(m[r], wmax(sm));
-        const CT corr = m[r] == (CT)-INFINITY ? (CT)0 : exp_ct(m[r] - m_new);
         const CT p = tvalid ? exp_ct(sv - m_new) : (CT)0;
-        l[r] = l[r] * corr + wsum(p);
-        m[r] = m_new;
+        if (m_new != m[r]) {      // warp-uniform; after the first tiles the running maximum rarely moves
+          const CT corr = m[r] == (CT)-INFINITY ? (CT)0 : exp_ct(m[r] - m_new);
+          l[r] *= corr;
 #pragma unroll
-        for (int c = 0; c < 4; c++) acc[r][c] *= corr;
+          for (int c = 0; c < 4; c++) acc[r][c] *= corr;
+          m[r] = m_new;
+        }
+        l[r] += wsum(p);
         coef[r] = keep ? p * keep_scale : (CT)0;
         coef2[r] = 0;
       } else {
@@ -249,20 +333,21 @@ attn_general_kernel(const GArgs a) {
 #pragma unroll
     for (int r = 0; r < GR; r++) { pw[r] = coef[r]; if (MODE == MODE_DKV) dw[r] = coef2[r]; }
     __syncwarp();
-    const int c0 = lane * 4;
     if (c0 < D) {
       // FWD: acc += p V      DQ: acc += ds K      DKV: acc += ds Q, acc2 += p' dO
       const CT* src1 = MODE == MODE_FWD ? tileB : tileA;
-      for (int j = 0; j < GT; j++) {
-        const CT* pj = pbuf + (warp * GT + j) * GR;
-        const CT* v1 = src1 + j * DP + c0;
+      for (int j = grp; j < GT; j += groups) {
+        CT pj[4], v1[4];
+        ld4(pbuf + (warp * GT + j) * GR, pj);
+        ld4(src1 + j * DP + c0, v1);
 #pragma unroll
         for (int r = 0; r < GR; r++)
 #pragma unroll
           for (int c = 0; c < 4; c++) acc[r][c] += pj[r] * v1[c];
         if (MODE == MODE_DKV) {
-          const CT* dj = dbuf + (warp * GT + j) * GR;
-          const CT* v2 = tileB + j * DP + c0;
+          CT dj[4], v2[4];
+          ld4(dbuf + (warp * GT + j) * GR, dj);
+          ld4(tileB + j * DP + c0, v2);
 #pragma unroll
           for (int r = 0; r < GR; r++)
 #pragma unroll
@@ -272,12 +357,22 @@ attn_general_kernel(const GArgs a) {
     }
   }
 
-  // ---- outputs ----
-  const int c0 = lane * 4;
+  // the lane groups hold partial sums over interleaved tile rows: add them up (fixed order)
+  for (int o = lpg; o < 32; o <<= 1) {
+#pragma unroll
+    for (int r = 0; r < GR; r++)
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        acc[r][c] += __shfl_xor_sync(0xffffffffu, acc[r][c], o);
+        if (MODE == MODE_DKV) acc2[r][c] += __shfl_xor_sync(0xffffffffu, acc2[r][c], o);
+      }
+  }
+
+  // ---- outputs (the first lane group writes) ----
 #pragma unroll
   for (int r = 0; r < GR; r++) {
     const int row = row0 + wrow0 + r;
-    if (row >= nrows) continue;
+    if (row >= nrows || grp != 0) continue;
     if (MODE == MODE_FWD) {
       const CT inv = l[r] > 0 ? (CT)1 / l[r] : (CT)0;
       T* o = (T*)a.O + (long long)b * a.o_s[0] + (long long)row * a.o_s[1] + (long long)h * a.o_s[2];
