@@ -15,8 +15,8 @@
 //   DKV   rows = keys, tiles = queries:   the same p and ds (transposed roles), dv += p' dO, dk += ds q
 // (p' / dp' = the dropout mask and 1/(1-p_drop) applied).  Every output element has one owner
 // and a fixed summation order: bit-reproducible, no atomics (the reference's backward uses fp64
-// atomicAdd).  The dropout mask comes from Philox-4x32-10 keyed by (seed, b, h, q, k), so forward
-// and both backward kernels regenerate it.
+// atomicAdd).  The dropout mask comes from Philox-4x32-10 keyed by (seed, b, h, q / 4, k), one output word
+// per query, so forward and both backward kernels regenerate it.
 #include "common.cuh"
 
 using namespace gb;
@@ -27,7 +27,7 @@ constexpr int GR = 4;           // rows per warp
 constexpr int GW = 4;           // warps per CTA
 constexpr int GROWS = GR * GW;  // rows per CTA
 constexpr int GT = 32;          // tile rows (one per lane)
-static_assert(GR == 4, "the coefficient buffers are read four rows at a time");
+static_assert(GR == 4, "the coefficient buffers are read four rows at a time; one dropout draw covers a warp's four rows");
 
 enum { MODE_FWD = 0, MODE_DQ = 1, MODE_DKV = 2 };
 
@@ -58,12 +58,18 @@ __device__ __forceinline__ uint4 philox(uint4 ctr, uint2 key) {
   }
   return ctr;
 }
-// keep-flags of the four consecutive rows q0..q0+3 (queries) against key k, or of query q against the
-// four consecutive keys k0..k0+3: one Philox call per (bh, q, k) cell group; here one call per cell.
+// One Philox call serves the four queries 4g .. 4g+3 against key k: counter (g, k, bh), query q takes
+// word q % 4.  A warp's four query rows (forward, dQ) start at a multiple of four, so there one call
+// per lane and tile covers all four rows; the dK/dV role (rows are keys) draws once per cell.
+__device__ __forceinline__ uint4 keep_draw(const GArgs& a, int bh, int qgroup, int k) {
+  return philox(make_uint4((uint32_t)qgroup, (uint32_t)k, (uint32_t)bh, 0u),
+                make_uint2((uint32_t)a.seed, (uint32_t)(a.seed >> 32)));
+}
+__device__ __forceinline__ uint32_t draw_word(const uint4& r, int i) {
+  return i == 0 ? r.x : i == 1 ? r.y : i == 2 ? r.z : r.w;
+}
 __device__ __forceinline__ bool keep_cell(const GArgs& a, int bh, int q, int k, uint32_t thresh) {
-  const uint4 r = philox(make_uint4((uint32_t)q, (uint32_t)k, (uint32_t)bh, 0u),
-                         make_uint2((uint32_t)a.seed, (uint32_t)(a.seed >> 32)));
-  return r.x >= thresh;
+  return draw_word(keep_draw(a, bh, q >> 2, k), q & 3) >= thresh;
 }
 
 template <typename T> struct Cvt {
@@ -289,6 +295,8 @@ attn_general_kernel(const GArgs a) {
     }
     // ---- masks, softmax terms ----
     CT coef[GR], coef2[GR];
+    uint4 draw = make_uint4(0u, 0u, 0u, 0u);
+    if (MODE != MODE_DKV && a.p_drop > 0.0 && tvalid) draw = keep_draw(a, bh, (row0 + wrow0) >> 2, tj);
 #pragma unroll
     for (int r = 0; r < GR; r++) {
       const int row = row0 + wrow0 + r;
@@ -300,7 +308,9 @@ attn_general_kernel(const GArgs a) {
         if (a.mask) sv += (CT)a.mask[(long long)qi * a.Tk + ki];
         if (a.kpm && a.kpm[(long long)b * a.Tk + ki]) sv += NEG;
       }
-      const bool keep = (a.p_drop > 0.0 && tvalid && rvalid) ? keep_cell(a, bh, qi, ki, thresh) : true;
+      bool keep = true;
+      if (a.p_drop > 0.0 && tvalid && rvalid)
+        keep = MODE == MODE_DKV ? keep_cell(a, bh, qi, ki, thresh) : draw_word(draw, r) >= thresh;
       if (MODE == MODE_FWD) {
         // online softmax over the 32 lanes; tile rows past the end do not take part
         const CT sm = tvalid ? sv : (CT)-INFINITY;

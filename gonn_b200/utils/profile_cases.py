@@ -8,6 +8,8 @@
     python -m gonn_b200.utils.profile_cases norm_fork 16384 768       # backward with the residual bypass fused
     python -m gonn_b200.utils.profile_cases step 50000000
     python -m gonn_b200.utils.profile_cases conv 256 64 128 15 15     # N C_in C_out H W, 3x3: forward + backward
+    python -m gonn_b200.utils.profile_cases general_attn 4 512 8 64 [bf16|fp32|fp64] [plain]
+                                                                       # B S H D: masked + dropout attention, fwd and bwd
     python -m gonn_b200.utils.profile_cases suite                      # one launch or two of every other kernel family
     python -m gonn_b200.utils.profile_cases suite2                     # ... and of the families `suite` leaves out
 
@@ -193,6 +195,29 @@ def main(argv):
             general_attention(q, kk, vv, True, None, mask, None, 0.1, 7).sum().backward()
             torch.cuda.synchronize()
         print("suite done")
+    elif kind == "general_attn":
+        # The SIMT attention kernel: causal + boolean mask + dropout 0.1 (or none of the three with `plain`).
+        from ..ops.attention import general_attention
+        B, S, H, D = (int(a) for a in argv[1:5])
+        dt = {"bf16": torch.bfloat16, "fp32": torch.float32, "fp64": torch.float64}[argv[5] if len(argv) > 5 else "bf16"]
+        plain = "plain" in argv
+        q, kk, vv = (torch.randn(B, S, H, D, device=dev, dtype=dt, requires_grad=True) for _ in range(3))
+        mask = None if plain else torch.rand(S, S, device=dev) < 0.2
+        p = 0.0 if plain else 0.1
+
+        def fwd():
+            with torch.no_grad():
+                return general_attention(q, kk, vv, not plain, None, mask, None, p, 7)
+
+        def fwd_bwd():
+            q.grad = kk.grad = vv.grad = None
+            general_attention(q, kk, vv, not plain, None, mask, None, p, 7).sum().backward()
+
+        fl = 4 * B * H * S * S * D
+        tf = _time(fwd)
+        tb = _time(fwd_bwd)
+        print(f"general_attn B{B} S{S} H{H} D{D} {dt} plain={plain}: forward {tf:.4f} ms ({fl / tf / 1e9:.2f} TFLOP/s of "
+              f"the full square), forward + backward {tb:.4f} ms")
     elif kind == "suite2":
         # The kernel families that neither the training steps nor `suite` launch: recurrent gates, dropout,
         # casts, scans, transposes, standalone softmax, fake quantisation, row / column reductions with
