@@ -43,7 +43,14 @@ enum { DT_BF16 = 0, DT_F16 = 1, DT_F32 = 2, DT_F64 = 3 };
 // ---------------------------------------------------------------------------
 // fp64: mma.sync m8n8k4
 // ---------------------------------------------------------------------------
-constexpr int DBM = 128, DBN = 128, DBK = 16, DSTAGES = 3;
+#ifndef GB_F64_BK
+#define GB_F64_BK 16        // k extent of a stage (a multiple of 16)
+#endif
+#ifndef GB_F64_STAGES
+#define GB_F64_STAGES 3
+#endif
+constexpr int DBM = 128, DBN = 128, DBK = GB_F64_BK, DSTAGES = GB_F64_STAGES;
+static_assert(DBK % 16 == 0 && DSTAGES >= 2, "stage shape");
 constexpr int DLD = DBM + 4;  // row pitch of a [k][m] stage in doubles: fragment loads hit 16 distinct bank pairs
 constexpr int DTHREADS = 512;
 constexpr int DSTAGE_DOUBLES = 2 * DBK * DLD;
@@ -82,29 +89,33 @@ __device__ __forceinline__ void load_tile(double* st, const double* src, long lo
                                           int k0, int MN, int K, bool vec_ok) {
   const int tid = threadIdx.x;
   if (k_contig) {
-    // 128 rows x 16 k: thread -> (row = tid / 4, four consecutive k)
-    const int r = tid >> 2, kq = (tid & 3) * 4;
+    // 128 rows x DBK k: thread -> (row = tid / 4, DBK / 4 consecutive k)
+    const int r = tid >> 2, kq = (tid & 3) * (DBK / 4);
     const long long row = (long long)mn0 + r;
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
+    for (int i = 0; i < DBK / 4; i++) {
       const int k = k0 + kq + i;
       const bool ok = row < MN && k < K;
       cp_async8(st + (kq + i) * DLD + r, ok ? src + row * ld + k : src, ok);
     }
   } else {
-    // 16 k rows x 128 contiguous: thread -> (k = tid / 32, four consecutive doubles)
-    const int kk = tid >> 5, c = (tid & 31) * 4;
-    const int k = k0 + kk;
-    const double* g = src + (long long)k * ld + mn0 + c;
-    double* d = st + kk * DLD + c;
-    if (vec_ok && k < K && mn0 + c + 3 < MN) {
-      cp_async16(d, g, true);
-      cp_async16(d + 2, g + 2, true);
-    } else {
+    // DBK k rows x 128 contiguous, 16 rows per pass: thread -> (k = tid / 32, four consecutive doubles)
+    const int c = (tid & 31) * 4;
 #pragma unroll
-      for (int i = 0; i < 4; i++) {
-        const bool ok = k < K && mn0 + c + i < MN;
-        cp_async8(d + i, ok ? g + i : src, ok);
+    for (int pass = 0; pass < DBK / 16; pass++) {
+      const int kk = pass * 16 + (tid >> 5);
+      const int k = k0 + kk;
+      const double* g = src + (long long)k * ld + mn0 + c;
+      double* d = st + kk * DLD + c;
+      if (vec_ok && k < K && mn0 + c + 3 < MN) {
+        cp_async16(d, g, true);
+        cp_async16(d + 2, g + 2, true);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          const bool ok = k < K && mn0 + c + i < MN;
+          cp_async8(d + i, ok ? g + i : src, ok);
+        }
       }
     }
   }
@@ -143,13 +154,13 @@ gemm_f64_mma_kernel(const double* __restrict__ A, const double* __restrict__ B, 
     }
     cp_async_commit();
   };
-  issue(0);
-  issue(1);
+#pragma unroll
+  for (int i = 0; i < DSTAGES - 1; i++) issue(i);
   const int fr = lane >> 2, fk = lane & 3;
   for (int kt = 0; kt < nk; kt++) {
-    cp_async_wait<1>();   // tile kt has landed (one newer group may still be in flight)
-    __syncthreads();      // ... for every thread, and tile kt-1's stage is no longer read
-    issue(kt + 2);
+    cp_async_wait<DSTAGES - 2>();   // tile kt has landed (the newer groups may still be in flight)
+    __syncthreads();                // ... for every thread, and tile kt-1's stage is no longer read
+    issue(kt + DSTAGES - 1);
     const double* sa = dsm + (kt % DSTAGES) * DSTAGE_DOUBLES;
     const double* sb = sa + DBK * DLD;
     if (SHAPE == 0) {
