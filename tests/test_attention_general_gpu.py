@@ -91,3 +91,23 @@ def test_forward_masked_module_uses_fused_kernels(status_ok):
     again = mha_gpu.ForwardMasked(x.cuda(), y.cuda(), y.cuda(), attn_mask=mask.cuda(), key_padding_mask=kpm.cuda(),
                                   attn_dropout=0.5)
     assert torch.equal(again, got)          # dropout is inactive in evaluation mode
+
+
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32, torch.bfloat16])
+def test_misaligned_strided_views_match_contiguous(dtype, status_ok):
+    """Views that start one element into a wider buffer cannot use 16-byte loads: the kernels then
+    stage their tiles element by element and must give the bytes of the aligned path."""
+    B, T, H, D = 2, 77, 3, 40
+    g = torch.Generator(device="cuda").manual_seed(5)
+    wide = [torch.randn(B, T, H, D + 3, device="cuda", generator=g).to(dtype) for _ in range(3)]
+    views = [w[..., 1:D + 1].detach().requires_grad_(True) for w in wide]
+    dense = [w[..., 1:D + 1].detach().contiguous().requires_grad_(True) for w in wide]
+    assert all(v.data_ptr() % 8 != 0 or v.stride(1) % 4 != 0 for v in views)
+    do = torch.randn(B, T, H, D, device="cuda", generator=g).to(dtype)
+    a = general_attention(*views, True, None, None, None, 0.2, 99)
+    b = general_attention(*dense, True, None, None, None, 0.2, 99)
+    assert torch.equal(a, b)
+    a.backward(do)
+    b.backward(do)
+    for x, y in zip(views, dense):
+        assert torch.equal(x.grad, y.grad)
