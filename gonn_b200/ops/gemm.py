@@ -87,7 +87,9 @@ def _gemm_ref(a, b, trans_a, trans_b, bias, act, aux, aux_mode, out_dtype, beta,
     ct = torch.float64 if a.dtype == torch.float64 else torch.float32
     A = a.to(ct).transpose(-1, -2) if trans_a else a.to(ct)
     B = b.to(ct).transpose(-1, -2) if trans_b else b.to(ct)
-    v = torch.matmul(A, B) * alpha
+    v = torch.matmul(A, B)
+    if alpha != 1.0:
+        v = v * alpha
     if bias is not None:
         v = v + bias.to(ct)
     m = AUX[aux_mode] if aux is not None else 0

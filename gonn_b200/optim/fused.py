@@ -44,7 +44,10 @@ class SGD(Optimizer):
                     upd = gr + self.momentum * v if self.nesterov else v
                 else:
                     upd = gr
-                p.data.copy_((pv - g.lr * upd).to(p.dtype))
+                if pv is p.data or pv.data_ptr() == p.data.data_ptr():
+                    p.data.sub_(upd * g.lr)          # same dtype: update in place, one temporary
+                else:
+                    p.data.copy_((pv - g.lr * upd).to(p.dtype))
 
 
 class Adam(Optimizer):
