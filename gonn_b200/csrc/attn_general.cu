@@ -189,8 +189,8 @@ attn_general_kernel(const GArgs a) {
   const int D = a.D;
   const int DP = (D + 3) / 4 * 4 + 4;        // row pitch: a multiple of 4 plus 4 (conflict-free float4 reads per lane)
   CT* rowsA = reinterpret_cast<CT*>(gsm);    // [GROWS][DP]  FWD/DQ: Q rows; DKV: K rows
-  CT* rowsB = rowsA + GROWS * DP;            // [GROWS][DP]  DQ: dO rows; DKV: V rows
-  CT* tileA = rowsB + GROWS * DP;            // [GT][DP]     FWD/DQ: K tile; DKV: Q tile
+  CT* rowsB = rowsA + GROWS * DP;            // [GROWS][DP]  DQ: dO rows; DKV: V rows (absent in FWD)
+  CT* tileA = rowsB + (MODE == MODE_FWD ? 0 : GROWS * DP);   // [GT][DP]  FWD/DQ: K tile; DKV: Q tile
   CT* tileB = tileA + GT * DP;               // [GT][DP]     FWD/DQ: V tile; DKV: dO tile
   CT* pbuf = tileB + GT * DP;                // [GW][GT][GR] coefficients of the first accumulation
   CT* dbuf = pbuf + GW * GT * GR;            // [GW][GT][GR] coefficients of the second (DKV)
@@ -439,21 +439,26 @@ __global__ void attn_keep_mask_kernel(unsigned char* out, int B, int H, int Tq, 
   }
 }
 
+// Shared memory of one CTA: every role has its rows, two tiles and one coefficient buffer; the backward
+// roles add the second row block, dK/dV the second coefficient buffer and the tile's lse / delta.
 template <typename CT>
-size_t general_smem(int D) {
+size_t general_smem(int D, int mode) {
   const int DP = (D + 3) / 4 * 4 + 4;
-  return (size_t)(2 * GROWS + 2 * GT) * DP * sizeof(CT) + 2 * (size_t)GW * GT * GR * sizeof(CT) + 2 * GT * sizeof(CT);
+  size_t elems = (size_t)(GROWS + 2 * GT) * DP + (size_t)GW * GT * GR;
+  if (mode != MODE_FWD) elems += (size_t)GROWS * DP;
+  if (mode == MODE_DKV) elems += (size_t)GW * GT * GR + 2 * GT;
+  return elems * sizeof(CT);
 }
 
 template <typename T, typename CT>
 int launch_general(int mode, const GArgs& a, cudaStream_t s) {
-  const size_t smem = general_smem<CT>(a.D);
+  const size_t smem = general_smem<CT>(a.D, mode);
   static bool set[3] = {false, false, false};
   auto k0 = attn_general_kernel<T, CT, MODE_FWD>;
   auto k1 = attn_general_kernel<T, CT, MODE_DQ>;
   auto k2 = attn_general_kernel<T, CT, MODE_DKV>;
   if (!set[mode]) {
-    const int lim = (int)general_smem<CT>(128);
+    const int lim = (int)general_smem<CT>(128, mode);
     if (mode == 0) GB_CUDA_OK(cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
     if (mode == 1) GB_CUDA_OK(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
     if (mode == 2) GB_CUDA_OK(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
