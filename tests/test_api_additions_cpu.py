@@ -81,6 +81,36 @@ def test_debug_build_recompiles_only_units_with_checks():
     assert build.DEBUG_LIB.endswith("libgonn_b200_debug.so") and build.LIB.endswith("libgonn_b200.so")
 
 
+def test_library_relinks_when_an_object_is_newer(tmp_path, monkeypatch):
+    """The two libraries share most objects: an object rebuilt by one flavour's pass must relink the
+    other library too, although that pass compiled nothing."""
+    from gonn_b200 import build
+    obj_dir = tmp_path / "obj"
+    obj_dir.mkdir()
+    lib = tmp_path / "lib.so"
+    lib.write_bytes(b"")
+    monkeypatch.setattr(build, "OBJ_DIR", str(obj_dir))
+    monkeypatch.setattr(build, "LIB", str(lib))
+    monkeypatch.setattr(build, "_sources", lambda: ["a.cu", "b.cu"])
+    monkeypatch.setattr(build, "_compile", lambda n, v, f, d=False: (n, False, ""))
+    past = os.path.getmtime(lib) - 100
+    for n in ("a.o", "b.o"):
+        (obj_dir / n).write_bytes(b"")
+        os.utime(obj_dir / n, (past, past))
+    links = []
+
+    class Done:
+        returncode, stdout, stderr = 0, "", ""
+
+    monkeypatch.setattr(build.subprocess, "run", lambda cmd, **kw: links.append(cmd) or Done())
+    build.build()
+    assert links == []                                    # nothing compiled, nothing newer: no link
+    future = os.path.getmtime(lib) + 100
+    os.utime(obj_dir / "b.o", (future, future))
+    build.build()
+    assert len(links) == 1 and "-shared" in links[0] and str(obj_dir / "b.o") in links[0]
+
+
 def test_library_path_follows_the_environment():
     code = "import gonn_b200.lib as L; print(L.LIB_PATH); print(L.DEBUG_BUILD)"
     env = dict(os.environ, PYTHONPATH=ROOT)
