@@ -87,6 +87,8 @@ def reference_arm(args):
     # or module cache exists offline, and the reference has no GPU training path and publishes
     # no training-throughput number: this metric cannot be produced by it here.  Its CUDA
     # library does build and runs under --config gemm | flash | add.
+    if int(os.environ.get("RANK", "0")) != 0:
+        return 0                                  # one line per job: rank 0 prints it
     print(json.dumps({"impl": "reference",
                       "unavailable": "reference is a Go module (not pip-installable, no Go toolchain "
                                      "offline) and has no GPU training path for tokens/s; its CUDA library "

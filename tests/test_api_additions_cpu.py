@@ -127,6 +127,10 @@ def test_benchmark_reference_arm_answers_without_a_gpu():
     assert out.returncode == 0
     line = json.loads(out.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and "unavailable" in line
+    assert len(out.stdout.strip().splitlines()) == 1
+    other = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"],
+                           capture_output=True, text=True, cwd=ROOT, timeout=300, env=dict(os.environ, RANK="1"))
+    assert other.returncode == 0 and other.stdout.strip() == ""      # one line per job: only rank 0 prints
     help_text = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--help"], capture_output=True,
                                text=True, cwd=ROOT, timeout=300).stdout
     for flag in ("--gpus", "--steps", "--warmup", "--impl", "--config", "--no-graph", "--no-overlap", "--quick"):
