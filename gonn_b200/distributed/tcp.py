@@ -47,33 +47,56 @@ class GroupClosed(DistributedError):
     pass
 
 
-def _recv_exact(c: socket.socket, n: int, who: str) -> bytes:
-    buf = bytearray()
-    while len(buf) < n:
+def _recv_into(c: socket.socket, view: memoryview, who: str) -> None:
+    """Fills ``view`` (bytes) from the socket: no intermediate copies."""
+    got, n = 0, len(view)
+    while got < n:
         try:
-            chunk = c.recv(min(n - len(buf), 1 << 20))
+            k = c.recv_into(view[got:], min(n - got, 1 << 22))
         except socket.timeout:
             raise PeerTimeout(f"timed out waiting for {who}") from None
         except OSError as e:
             raise PeerClosed(f"connection to {who} failed: {e}") from None
-        if not chunk:
+        if k == 0:
             raise PeerClosed(f"{who} closed the connection")
-        buf += chunk
+        got += k
+
+
+def _recv_exact(c: socket.socket, n: int, who: str) -> bytes:
+    buf = bytearray(n)
+    _recv_into(c, memoryview(buf), who)
     return bytes(buf)
 
 
-def write_frame(c: socket.socket, op: int, vals: Optional[np.ndarray], who: str = "peer") -> None:
+def write_frame(c: socket.socket, op: int, vals: Optional[np.ndarray], who: str = "peer",
+                scratch: Optional[np.ndarray] = None, prepared: bool = False) -> None:
+    """Writes one frame; ``scratch`` (a ``>f8`` array of the same size) holds the byte-swapped payload
+    (already filled by the caller when ``prepared``)."""
     n = 0 if vals is None else int(vals.size)
-    payload = b"" if n == 0 else np.ascontiguousarray(vals, dtype=">f8").tobytes()
     try:
-        c.sendall(struct.pack(">BQ", op, n) + payload)
+        if n == 0:
+            c.sendall(struct.pack(">BQ", op, 0))
+        elif n <= 1024:
+            c.sendall(struct.pack(">BQ", op, n) + np.ascontiguousarray(vals, dtype=">f8").tobytes())
+        else:
+            # one byte-swapping pass, then the socket reads the array's memory directly
+            if scratch is not None and scratch.size == n:
+                be = scratch
+                if not prepared:
+                    be[...] = vals.reshape(-1)
+            else:
+                be = np.ascontiguousarray(vals, dtype=">f8")
+            c.sendall(struct.pack(">BQ", op, n))
+            c.sendall(memoryview(be).cast("B"))
     except socket.timeout:
         raise PeerTimeout(f"timed out sending to {who}") from None
     except OSError as e:
         raise PeerClosed(f"connection to {who} failed: {e}") from None
 
 
-def read_frame(c: socket.socket, want_op: int, want_n: int, who: str = "peer") -> np.ndarray:
+def read_frame(c: socket.socket, want_op: int, want_n: int, who: str = "peer",
+               into: Optional[np.ndarray] = None) -> np.ndarray:
+    """Reads one frame; ``into`` (a ``>f8`` array of ``want_n`` elements) receives the payload in place."""
     op, n = struct.unpack(">BQ", _recv_exact(c, 9, who))
     if op != want_op:
         raise ProtocolError(f"{who}: expected op {want_op}, got {op} (ranks called different collectives)")
@@ -81,7 +104,21 @@ def read_frame(c: socket.socket, want_op: int, want_n: int, who: str = "peer") -
         raise ProtocolError(f"{who}: expected {want_n} elements, got {n}")
     if n == 0:
         return np.empty(0, dtype=np.float64)
-    return np.frombuffer(_recv_exact(c, 8 * n, who), dtype=">f8").astype(np.float64)
+    arr = np.empty(n, dtype=">f8") if into is None else into
+    _recv_into(c, memoryview(arr).cast("B"), who)
+    if arr.dtype.byteorder == ">":                      # a little-endian host: swap in place, reinterpret
+        return arr.byteswap(inplace=True).view(np.float64)
+    return arr.view(np.float64)
+
+
+def _tune(c: socket.socket) -> None:
+    """No Nagle delay, and socket buffers large enough for a gradient frame to move in few wake-ups."""
+    c.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
+    for opt in (socket.SO_SNDBUF, socket.SO_RCVBUF):
+        try:
+            c.setsockopt(socket.SOL_SOCKET, opt, 4 << 20)
+        except OSError:
+            pass
 
 
 class Group:
@@ -112,7 +149,7 @@ class Group:
                     except socket.timeout:
                         raise PeerTimeout("distributed.Init: a rank never connected") from None
                     c.settimeout(timeout)
-                    c.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
+                    _tune(c)
                     magic, r = struct.unpack(">II", _recv_exact(c, 8, f"client {addr}"))
                     if magic != MAGIC:
                         raise ProtocolError(f"distributed.Init: bad handshake magic from {addr}")
@@ -136,7 +173,7 @@ class Group:
                                           f"{peers[0]}: {e}") from None
                     time.sleep(0.02)
             c.settimeout(timeout)
-            c.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
+            _tune(c)
             c.sendall(struct.pack(">II", MAGIC, rank))
             read_frame(c, OP_BARRIER, 0, "coordinator")
             self.conns = [c]
@@ -153,37 +190,59 @@ class Group:
             raise GroupClosed("collective on a closed group")
 
     # ---- collectives ------------------------------------------------------------------
-    def _star(self, op: int, vec: np.ndarray, scale: float) -> np.ndarray:
-        """Gather to rank 0 in rank order, add, scale, send the same bytes back."""
+    def _buf(self, name: str, n: int, dtype) -> np.ndarray:
+        """A per-group scratch array, kept between collectives (a fresh 2 MB array per step costs more
+        in page faults than the reduction itself)."""
+        bufs = self.__dict__.setdefault("_bufs", {})
+        b = bufs.get(name)
+        if b is None or b.size != n or b.dtype != np.dtype(dtype):
+            b = bufs[name] = np.empty(n, dtype=dtype)
+        return b
+
+    def _star(self, op: int, vec: np.ndarray, scale: float, own: bool = False) -> np.ndarray:
+        """Gather to rank 0 in rank order, add, scale, send the same bytes back.  ``own``: ``vec`` is
+        the caller's scratch and may be overwritten with the result."""
         self._alive()
         n = vec.size
         if self.world == 1:
             return vec * scale if scale != 1.0 else vec
+        wire = self._buf("wire", n, ">f8") if n > 1024 else None
         if self.rank == 0:
-            acc = vec.astype(np.float64).copy()
+            acc = vec if own and vec.dtype == np.float64 else np.array(vec, dtype=np.float64, copy=True)
             for r in range(1, self.world):
-                acc += read_frame(self.conns[r], op, n, f"rank {r}")
+                acc += read_frame(self.conns[r], op, n, f"rank {r}", into=wire)
             if scale != 1.0:
                 acc *= scale
+            if wire is not None:
+                wire[...] = acc                       # swap once, send the same bytes to everyone
             for r in range(1, self.world):
-                write_frame(self.conns[r], op, acc, f"rank {r}")
+                if wire is not None:
+                    write_frame(self.conns[r], op, acc, f"rank {r}", scratch=wire, prepared=True)
+                else:
+                    write_frame(self.conns[r], op, acc, f"rank {r}")
             return acc
-        write_frame(self.conns[0], op, vec, "coordinator")
-        return read_frame(self.conns[0], op, n, "coordinator")
+        write_frame(self.conns[0], op, vec, "coordinator", scratch=wire)
+        return read_frame(self.conns[0], op, n, "coordinator", into=wire)
 
     def AllReduceMeanGrads(self, params: Sequence[torch.Tensor]) -> None:
         """Mean of the flattened gradients over ranks; a missing gradient counts as zeros and
         is allocated on return (distributed.go:249-293)."""
-        flat = np.concatenate([
-            (p.grad.detach().double().cpu().numpy().ravel() if p.grad is not None
-             else np.zeros(p.numel(), dtype=np.float64)) for p in params]) if params else np.empty(0)
-        out = self._star(OP_ALLREDUCE, flat, 1.0 / self.world)
+        flat = self._buf("flat", sum(p.numel() for p in params), np.float64)
         off = 0
         for p in params:
             n = p.numel()
-            g = torch.from_numpy(out[off:off + n].copy()).reshape(p.shape).to(dtype=p.dtype, device=p.device)
             if p.grad is None:
-                p.grad = g
+                flat[off:off + n] = 0.0
+            else:
+                flat[off:off + n] = p.grad.detach().cpu().reshape(-1).numpy()    # converts to float64 on assignment
+            off += n
+        out = self._star(OP_ALLREDUCE, flat, 1.0 / self.world, own=True)
+        off = 0
+        for p in params:
+            n = p.numel()
+            g = torch.from_numpy(out[off:off + n]).reshape(p.shape).to(dtype=p.dtype, device=p.device)
+            if p.grad is None:
+                p.grad = g.clone() if g.dtype == torch.float64 and g.device.type == "cpu" else g   # own storage
             else:
                 p.grad.copy_(g)
             off += n

@@ -260,6 +260,55 @@ def bench_mlp_cpu():
         step()
     dt = (time.perf_counter() - t0) / n
     _emit(bench="mlp_cpu", dtype="fp64", batch=64, ms_per_step=dt * 1e3, steps_per_s=1 / dt, images_per_s=64 / dt)
+    # two data-parallel ranks (processes, half the cores each), 64 images per rank, gradients averaged
+    # over the TCP star every step (distributed/distributed.go:249-293, 422-428)
+    import multiprocessing as mp
+    from ..distributed import free_addr
+    ctx = mp.get_context("spawn")
+    addr, q = free_addr(), ctx.Queue()
+    procs = [ctx.Process(target=_mlp_dp_rank, args=(r, 2, addr, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    times = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(30)
+    dt2 = max(times)
+    _emit(bench="mlp_cpu_dp2", dtype="fp64", ranks=2, batch_per_rank=64, transport="TCP star, loopback",
+          ms_per_step=dt2 * 1e3, steps_per_s=1 / dt2, images_per_s=128 / dt2)
+
+
+def _mlp_dp_rank(rank: int, world: int, addr: str, q):
+    """One rank of the two-process data-parallel MLP benchmark; puts its seconds per step on ``q``."""
+    from .. import distributed as D
+    from ..models.mlp import MLP
+    from ..nn.loss import CrossEntropyLoss
+    from ..optim import SGD
+    torch.set_num_threads(max(1, (os.cpu_count() or 2) // world))
+    torch.manual_seed(rank)
+    g = D.Init(rank, world, [addr], timeout=60.0)
+    try:
+        model = MLP([784, 256, 128, 10], dtype=torch.float64)
+        g.BroadcastParams(list(model.parameters()), 0)
+        opt = SGD(model.parameters(), lr=0.05, momentum=0.9)
+        x = torch.randn(64, 784, dtype=torch.float64)
+        y = torch.randint(0, 10, (64,))
+
+        def step():
+            opt.zero_grad()
+            CrossEntropyLoss(model(x), y).backward()
+            D.DDPStep(g, opt)
+
+        for _ in range(5):
+            step()
+        g.Barrier()
+        t0 = time.perf_counter()
+        n = 50
+        for _ in range(n):
+            step()
+        g.Barrier()
+        q.put((time.perf_counter() - t0) / n)
+    finally:
+        g.Close()
 
 
 def bench_allreduce():
