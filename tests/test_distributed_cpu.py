@@ -229,3 +229,49 @@ def test_wire_frame_layout():
     assert raw[0] == 4 and struct.unpack(">Q", raw[1:9])[0] == 2
     assert struct.unpack(">dd", raw[9:25]) == (1.5, -2.0)
     a.close(); b.close()
+
+
+def test_large_frames_reuse_scratch_arrays_and_keep_the_wire_format():
+    """Frames above 1024 elements go out of, and come into, persistent big-endian arrays: the bytes
+    on the wire stay ``[op][count][count x big-endian float64]`` and a second collective through the
+    same arrays is not polluted by the first."""
+    n = 5000
+    a, b = socket.socketpair()
+    a.settimeout(5); b.settimeout(5)
+    vals = np.arange(n, dtype=np.float64) * 0.5 - 7
+    scratch = np.empty(n, dtype=">f8")
+    got = {}
+
+    def reader():
+        got["raw"] = D.tcp._recv_exact(b, 9 + 8 * n, "peer")
+
+    t = threading.Thread(target=reader); t.start()
+    D.tcp.write_frame(a, D.tcp.OP_ALLREDUCE, vals, scratch=scratch)
+    t.join(10)
+    raw = got["raw"]
+    assert raw[0] == 1 and struct.unpack(">Q", raw[1:9])[0] == n
+    assert np.array_equal(np.frombuffer(raw[9:], dtype=">f8").astype(np.float64), vals)
+    # the receiving side, twice into the same array
+    into = np.empty(n, dtype=">f8")
+    for k in (1.0, -3.0):
+        t = threading.Thread(target=lambda: D.tcp.write_frame(a, D.tcp.OP_ALLREDUCE, vals * k)); t.start()
+        out = D.tcp.read_frame(b, D.tcp.OP_ALLREDUCE, n, into=into)
+        t.join(10)
+        assert out.dtype == np.float64 and np.array_equal(out, vals * k)
+    a.close(); b.close()
+
+    # and through a group: two all-reduces of 3000 gradients each give exact means both times
+    def fn(g, r):
+        p = torch.zeros(3000, dtype=torch.float64, requires_grad=True)
+        res = []
+        for step in range(2):
+            p.grad = torch.full((3000,), float(r + 1 + 10 * step), dtype=torch.float64)
+            g.AllReduceMeanGrads([p])
+            res.append(p.grad.clone())
+        return res
+
+    out, errs = run_ranks(2, fn)
+    assert errs == [None, None]
+    for r in range(2):
+        assert torch.equal(out[r][0], torch.full((3000,), 1.5, dtype=torch.float64))
+        assert torch.equal(out[r][1], torch.full((3000,), 11.5, dtype=torch.float64))
