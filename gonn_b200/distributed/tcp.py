@@ -234,7 +234,10 @@ class Group:
             if p.grad is None:
                 flat[off:off + n] = 0.0
             else:
-                flat[off:off + n] = p.grad.detach().cpu().reshape(-1).numpy()    # converts to float64 on assignment
+                t = p.grad.detach().cpu().reshape(-1)
+                if t.dtype not in (torch.float64, torch.float32, torch.float16):
+                    t = t.double()                                  # bfloat16 and integers have no numpy view
+                flat[off:off + n] = t.numpy()                       # converts to float64 on assignment
             off += n
         out = self._star(OP_ALLREDUCE, flat, 1.0 / self.world, own=True)
         off = 0

@@ -275,3 +275,19 @@ def test_large_frames_reuse_scratch_arrays_and_keep_the_wire_format():
     for r in range(2):
         assert torch.equal(out[r][0], torch.full((3000,), 1.5, dtype=torch.float64))
         assert torch.equal(out[r][1], torch.full((3000,), 11.5, dtype=torch.float64))
+
+
+def test_mean_grads_of_bfloat16_and_float32_parameters():
+    def fn(g, r):
+        a = torch.zeros(5, dtype=torch.bfloat16, requires_grad=True)
+        b = torch.zeros(3, dtype=torch.float32, requires_grad=True)
+        a.grad = torch.full((5,), float(r + 1), dtype=torch.bfloat16)
+        b.grad = torch.full((3,), float(2 * r), dtype=torch.float32)
+        g.AllReduceMeanGrads([a, b])
+        return a.grad, b.grad
+
+    out, errs = run_ranks(2, fn)
+    assert errs == [None, None]
+    for ga, gb in out:
+        assert ga.dtype == torch.bfloat16 and torch.equal(ga.float(), torch.full((5,), 1.5))
+        assert gb.dtype == torch.float32 and torch.equal(gb, torch.full((3,), 1.0))
