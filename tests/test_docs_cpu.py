@@ -73,3 +73,23 @@ def test_every_name_in_the_parity_matrix_resolves():
     assert not missing, missing
     # the reference's parity document has 17 sections; this one keeps that granularity
     assert len(re.findall(r"^## ", text, flags=re.M)) >= 17
+
+
+def test_benchmarking_page_names_real_commands():
+    """Every sub-command and flag the measuring page names exists."""
+    import subprocess
+    import sys
+    text = open(os.path.join(ROOT, "docs", "BENCHMARKING.md")).read()
+    mb = open(os.path.join(ROOT, "gonn_b200", "utils", "microbench.py")).read()
+    for kind in re.findall(r"utils\.microbench (\w+)", text):
+        assert f'"{kind}":' in mb, kind
+    pc = open(os.path.join(ROOT, "gonn_b200", "utils", "profile_cases.py")).read()
+    for kind in re.findall(r"utils\.profile_cases (\w+)", text):
+        assert f'"{kind}"' in pc, kind
+    help_text = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--help"], capture_output=True,
+                               text=True, timeout=300).stdout
+    for flag in set(re.findall(r"`(--[a-z0-9-]+)", text)) - {"--clock-control", "--twin", "--debug"}:
+        assert flag.split()[0] in help_text, flag
+    twin_help = subprocess.run([sys.executable, os.path.join(ROOT, "baseline", "torch_ddp.py"), "--help"],
+                               capture_output=True, text=True, timeout=300).stdout
+    assert "--twin" in twin_help and "bf16" in twin_help and "autocast" in twin_help
