@@ -4,7 +4,10 @@ Every ``csrc/*.cu`` file is one translation unit compiled by ``nvcc`` with
 ``-gencode arch=compute_100a,code=sm_100a`` and linked into one shared object
 with a C ABI (loaded through ``ctypes`` by :mod:`gonn_b200.lib`).  No GPU is
 needed to build.  Run ``python -m gonn_b200.build`` (add ``-v`` for
-``-Xptxas -v`` resource usage, ``-f`` to force a full rebuild).
+``-Xptxas -v`` resource usage, ``-f`` to force a full rebuild).  The reference compiles its one CUDA
+source with a single ``nvcc -O3 -arch=sm_86 ... -lcublas`` line
+(benchmark/docker/build_and_run.sh:14); here objects are cached by a digest of source, headers and
+flags, so a change recompiles one unit.
 
 ``python -m gonn_b200.build --debug`` builds a second library,
 ``libgonn_b200_debug.so``, with ``-DGB_BOUNDS_CHECK``: the window, embedding, reduction and

@@ -1,5 +1,9 @@
 """Symmetric peer memory and the in-kernel collectives built on it.
 
+What the reference does over a TCP star on the host (distributed/distributed.go:249-293 mean of the
+gradients, :303-333 sum of a short vector, :338-388 parameter broadcast, :392-416 barrier, :422-428
+all-reduce then optimizer step) happens here inside kernels that address the peers' memory.
+
 ``SymmetricMemory`` owns this rank's buffer (flag area + data), exchanges CUDA IPC
 handles over an existing ``torch.distributed`` process group (used only as the
 bootstrap channel) and exposes torch views of the local data region.  The

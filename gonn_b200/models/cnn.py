@@ -1,5 +1,10 @@
 """Small CNN: Conv 3->64 3x3, BatchNorm, ReLU, MaxPool 2, Conv 64->128 3x3, BatchNorm, ReLU,
-global average pool, Linear 128->10 (3x32x32 inputs)."""
+global average pool, Linear 128->10 (3x32x32 inputs).
+
+The layer sequence of the reference's convolutional example (examples/cnn/main.go:32-37: convolution,
+normalisation, ReLU, pooling, a linear head) at the width of the data-parallel benchmark configuration;
+the reference runs every convolution as a gather + GEMM on the host (nn/conv.go:341-380), here they
+are implicit-GEMM kernels."""
 from __future__ import annotations
 
 import torch

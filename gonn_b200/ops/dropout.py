@@ -1,6 +1,10 @@
 """Dropout with a counter-based generator: the mask is a pure function of
 (seed, offset, element index), so backward regenerates it instead of storing it.
-CUDA: ``csrc/dropout.cu`` (Philox-4x32-10).  CPU: torch's generator."""
+CUDA: ``csrc/dropout.cu`` (Philox-4x32-10).  CPU: torch's generator.
+
+Semantics of the reference's layer (nn/dropout.go:21-37: keep with probability 1 - p, scale the kept
+values by 1 / (1 - p), identity in evaluation mode); the reference draws its mask on the host and
+stores it, here nothing is stored."""
 from __future__ import annotations
 
 import torch

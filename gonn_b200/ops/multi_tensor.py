@@ -1,4 +1,9 @@
-"""Multi-tensor launches of the fused optimizer kernels (csrc/optim.cu)."""
+"""Multi-tensor launches of the fused optimizer kernels (csrc/optim.cu).
+
+The update rules are the reference's per-element loops (optim/sgd.go:47-69, adam.go:61-77,
+adamw.go:64-84, lion.go:61-76, lamb.go:73-108) and its global-norm clipping (optim/clip.go:23-65);
+one launch updates up to 48 tensors in chunks of 4096 elements instead of one host loop per
+parameter."""
 from __future__ import annotations
 
 import ctypes
