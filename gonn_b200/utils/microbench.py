@@ -5,6 +5,7 @@
     python -m gonn_b200.utils.microbench flash
     python -m gonn_b200.utils.microbench norm
     python -m gonn_b200.utils.microbench resident                 # the reference's resident-MLP forward benchmark
+    python -m gonn_b200.utils.microbench mha                      # the reference's MultiHeadAttention Forward / ForwardFused benchmark
     python -m gonn_b200.utils.microbench refattn                  # the reference's attention benchmark shapes
     python -m gonn_b200.utils.microbench mlp                      # CPU, config of the reference's quick start
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
@@ -148,6 +149,49 @@ def bench_reference_attention():
                   gflops=fl / 1e9 / (ms / 1e3), torch_sdpa_ms=tms, torch_sdpa_gflops=fl / 1e9 / (tms / 1e3),
                   rel_err_out=err(o, ref.detach()), rel_err_dq=err(dq, rq), rel_err_dk=err(dk, rk),
                   rel_err_dv=err(dv, rv), reference_published_gflops_fp64=86.6 if causal else 95.4)
+
+
+def bench_mha(device=None, B: int = 8, S: int = 512, E: int = 512, H: int = 8, iters: int = 10):
+    """The reference's MultiHeadAttention benchmark (benchmark/mha/main.go:55-103): ``Forward``
+    (differentiable) against ``ForwardFused`` (inference entry point), first their largest
+    difference at (2, 64, E), causal and not, then the median wall-clock time of 10 calls at
+    B = 8, S = 512, E = 512, H = 8, causal, each call synchronised as there.  bf16 on CUDA
+    (the tcgen05 attention core), float64 on the CPU oracle path."""
+    from .. import nn
+    dev = torch.device(device) if device is not None else torch.device("cuda" if torch.cuda.is_available() else "cpu")
+    dt = torch.bfloat16 if dev.type == "cuda" else torch.float64
+    torch.manual_seed(0)
+    mha = nn.MultiHeadAttention(E, H).to(device=dev, dtype=dt)
+    diffs = {}
+    for causal in (False, True):
+        x = (torch.rand(2, 64, E, device=dev) * 2 - 1).to(dt)
+        ref = mha.Forward(x, x, x, causal) if hasattr(mha, "Forward") else mha(x, x, x, causal)
+        fused = mha.ForwardFused(x, x, x, causal)
+        diffs[causal] = float((ref.detach().double() - fused.double()).abs().max())
+    xl = (torch.rand(B, S, E, device=dev) * 2 - 1).to(dt)
+
+    def sync():
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+
+    def median_ms(fn, warm):
+        for _ in range(warm):
+            fn()
+        sync()
+        ts = []
+        for _ in range(iters):
+            t0 = time.perf_counter()
+            fn()
+            sync()
+            ts.append((time.perf_counter() - t0) * 1e3)
+        return statistics.median(ts)
+
+    t_fwd = median_ms(lambda: mha(xl, xl, xl, True), 2)
+    t_fused = median_ms(lambda: mha.ForwardFused(xl, xl, xl, True), 3)
+    _emit(bench="mha", device=dev.type, dtype=str(dt).replace("torch.", ""), B=B, S=S, E=E, H=H, causal=True,
+          forward_ms=t_fwd, forward_fused_ms=t_fused, max_abs_diff_noncausal=diffs[False],
+          max_abs_diff_causal=diffs[True])
+    return dict(forward_ms=t_fwd, forward_fused_ms=t_fused, diffs=diffs)
 
 
 def bench_resident_mlp(device=None, iters: int = 20):
@@ -456,7 +500,7 @@ def main(argv):
     kind = argv[0] if argv else "gemm"
     fn = {"gemm": bench_gemm, "elementwise": bench_elementwise, "flash": bench_flash, "norm": bench_norm,
           "mlp": bench_mlp_cpu, "allreduce": bench_allreduce, "refattn": bench_reference_attention, "resident": bench_resident_mlp,
-          "hosttime": bench_host_time, "secondary": bench_secondary}.get(kind)
+          "hosttime": bench_host_time, "secondary": bench_secondary, "mha": bench_mha}.get(kind)
     if fn is None:
         raise SystemExit(f"unknown benchmark {kind!r}")
     fn()

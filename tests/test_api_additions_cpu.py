@@ -135,3 +135,14 @@ def test_benchmark_reference_arm_answers_without_a_gpu():
                                text=True, cwd=ROOT, timeout=300).stdout
     for flag in ("--gpus", "--steps", "--warmup", "--impl", "--config", "--no-graph", "--no-overlap", "--quick"):
         assert flag in help_text
+
+
+def test_mha_benchmark_runs_on_the_cpu_path(capsys):
+    """The reference's Forward / ForwardFused benchmark (small size here): both entry points agree and
+    one JSON line comes out."""
+    from gonn_b200.utils import microbench
+    rec = microbench.bench_mha("cpu", B=2, S=32, E=32, H=2, iters=2)
+    assert rec["diffs"][False] < 1e-12 and rec["diffs"][True] < 1e-12
+    assert rec["forward_ms"] > 0 and rec["forward_fused_ms"] > 0
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert line["bench"] == "mha" and line["device"] == "cpu" and line["causal"] is True
