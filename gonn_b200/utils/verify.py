@@ -135,6 +135,58 @@ def verify_attention(rep: Report, dev: torch.device, rng) -> None:
         rep.check(f"attention core causal={causal}", _np(got), want, tol)
 
 
+def verify_attention_backward(rep: Report, dev: torch.device, rng) -> None:
+    """The reference's backward check (benchmark/flashbwd/main.go:41-139): central differences of
+    ``sum(O * dO)`` (eps 1e-6, float64) against the analytic dQ, dK and dV at six positions, (BH, S, D) =
+    (2, 6, 64), causal and not, relative error below 1e-4; then a one-head attention layer of width 64
+    trained for 30 Adam steps on a fixed target must lower its squared error."""
+    from .. import nn, optim
+    from ..ops.attention import flash_attention
+    BH, S, D = 2, 6, 64
+    n = BH * S * D
+    for causal in (False, True):
+        q, k, v, do = (torch.tensor(rng.standard_normal((1, S, BH, D)), dtype=torch.float64, device=dev) for _ in range(4))
+        leaves = [t.clone().requires_grad_(True) for t in (q, k, v)]
+        flash_attention(*leaves, causal).backward(do)
+
+        def loss(ts):
+            with torch.no_grad():
+                return float((flash_attention(*ts, causal) * do).sum())
+
+        got, want = [], []
+        for which in range(3):
+            for idx in (0, 1, 64, 130, 200, n - 1):
+                ts = [q.clone(), k.clone(), v.clone()]
+                flat = ts[which].view(-1)
+                x0 = float(flat[idx])
+                flat[idx] = x0 + 1e-6
+                lp = loss(ts)
+                flat[idx] = x0 - 1e-6
+                lm = loss(ts)
+                want.append((lp - lm) / 2e-6)
+                got.append(float(leaves[which].grad.reshape(-1)[idx]))
+        rep.check(f"attention backward vs central differences causal={causal}", got, want, 1e-4)
+    torch.manual_seed(1)
+    dtype = torch.bfloat16 if dev.type == "cuda" else torch.float64
+    mha = nn.MultiHeadAttention(64, 1).to(device=dev, dtype=dtype)
+    opt = optim.Adam(mha.parameters(), lr=1e-2)
+    x = torch.tensor(rng.standard_normal((2, 8, 64)), dtype=torch.float64).to(dev, dtype)
+    target = torch.tensor(rng.standard_normal((2, 8, 64)), dtype=torch.float64).to(dev, dtype)
+    first = last = 0.0
+    for step in range(30):
+        opt.zero_grad()
+        err = mha(x, x, x, True) - target
+        l = (err * err).mean()
+        l.backward()
+        opt.step()
+        last = float(l.detach())
+        first = last if step == 0 else first
+    ok = last < first
+    rep.failed += 0 if ok else 1
+    print(f"  {'attention layer training, 30 Adam steps':58s} loss {first:.5f} -> {last:.5f}  [{'OK' if ok else 'FAIL'}]",
+          file=rep.out)
+
+
 def run(device: str, out=sys.stdout) -> int:
     dev = torch.device(device)
     prev = B.Use(B.NewCUDA() if dev.type == "cuda" else B.NewCPU())
@@ -149,6 +201,7 @@ def run(device: str, out=sys.stdout) -> int:
             verify_gemm(rep, dev, torch.float16, 4e-3, rng)
         verify_elementwise(rep, dev, rng)
         verify_attention(rep, dev, rng)
+        verify_attention_backward(rep, dev, rng)
         if dev.type == "cuda":
             from .. import lib
             B.Current().Synchronize()

@@ -14,6 +14,8 @@ def test_verify_passes_on_cpu_backend():
     text = out.getvalue()
     assert "ALL CHECKS PASSED" in text and "FAIL" not in text.replace("FAILED", "")
     assert text.count("gemm float64") == 2 * 3 * 4 and "unary GELUExact" in text and "binary Div" in text
+    assert text.count("attention backward vs central differences") == 2
+    assert "attention layer training, 30 Adam steps" in text
 
 
 def test_verify_flags_a_backend_that_ignores_transposition():
